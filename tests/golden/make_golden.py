@@ -1,0 +1,217 @@
+"""Generate the golden fixtures in this directory by EXECUTING THE REFERENCE.
+
+Run once, in a container that has the reference tree mounted (default
+``/root/reference``; override with ``HQEKV_REFERENCE_ROOT``):
+
+    python tests/golden/make_golden.py
+
+It imports the reference's own ``quant/pack_unpack.py``, ``model/public_func.py`` and
+``quant/hqe_2.py`` through ``ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
+the outputs the reference produced as ``*.npz`` files.  The tests read only the ``.npz``
+files; the reference is not needed to run them.
+
+Inputs avoid constant quantisation groups (scale 0 -> NaN code), whose integer conversion
+differs between x86 and the GPU the reference targets.
+"""
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, HERE)
+import ref_shim  # noqa: E402
+
+ref = ref_shim.load_reference()
+pu, pf, hq = ref.pack_unpack, ref.public_func, ref.hqe_2
+
+
+def npy(t):
+    return None if t is None else t.detach().cpu().numpy()
+
+
+def save(name, **arrays):
+    arrays = {k: v for k, v in arrays.items() if v is not None}
+    path = os.path.join(HERE, name + ".npz")
+    np.savez_compressed(path, **arrays)
+    print(f"{name}.npz: {os.path.getsize(path) / 1024:.1f} KiB, {len(arrays)} arrays")
+
+
+def outlier_K(gen, B, H, T, D):
+    K = torch.randn(B, H, T, D, generator=gen)
+    for h in range(H):
+        ch = torch.randperm(D, generator=gen)[:4]
+        K[:, h, :, ch] *= 10
+    return K.half()
+
+
+# ------------------------------------------------------------------------------------------
+# 1. codec known-answer tests: every bit width x group size, V-like and K-like shapes
+# ------------------------------------------------------------------------------------------
+def codec_cases():
+    gen = torch.Generator().manual_seed(1234)
+    out = {}
+    n = 0
+    for bit in (8, 4, 2, 1):
+        for g in (32, 64, 128):
+            # V layout: [B,H,T,D] groups along D
+            x = torch.randn(2, 2, 5, 128, generator=gen).half()
+            code, scale, mn = pu.uniform_group_quantize_pack_last_dim(x.clone(), g, bit)
+            deq = pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, g, bit)
+            out.update({f"c{n}_x": npy(x), f"c{n}_code": npy(code), f"c{n}_scale": npy(scale), f"c{n}_mn": npy(mn),
+                        f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([bit, g, 0])})
+            n += 1
+            # K layout: token-major source viewed channel-major [B,H,D,T], groups along T, outlier channels
+            T = 2 * g
+            k = outlier_K(gen, 1, 2, T, 128)
+            kt = k.transpose(2, 3)
+            code, scale, mn = pu.uniform_group_quantize_pack_last_dim(kt, g, bit)
+            deq = pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, g, bit)
+            out.update({f"c{n}_x": npy(kt.contiguous()), f"c{n}_code": npy(code), f"c{n}_scale": npy(scale),
+                        f"c{n}_mn": npy(mn), f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([bit, g, 1])})
+            n += 1
+    # extreme magnitudes (fp16 max / tiny) and exact .5 rounding ties
+    x = torch.zeros(1, 1, 4, 32).half()
+    x[0, 0, 0] = torch.linspace(-30000, 32000, 32).half()
+    x[0, 0, 1] = torch.linspace(0, 6e-5, 32).half()
+    x[0, 0, 2] = torch.arange(32).half() * 0.5            # scale 0.5 at 5 bit-ish: ties at 8 bit below
+    x[0, 0, 3] = torch.arange(32).half() * 127.5 / 31
+    for bit in (8, 4, 2):
+        code, scale, mn = pu.uniform_group_quantize_pack_last_dim(x.clone(), 32, bit)
+        deq = pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, 32, bit)
+        out.update({f"c{n}_x": npy(x), f"c{n}_code": npy(code), f"c{n}_scale": npy(scale), f"c{n}_mn": npy(mn),
+                    f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([bit, 32, 0])})
+        n += 1
+    out["count"] = np.array(n)
+    save("codec", **out)
+
+
+# ------------------------------------------------------------------------------------------
+# 2. importance ring, token range, block ranking
+# ------------------------------------------------------------------------------------------
+def ranking_cases():
+    gen = torch.Generator().manual_seed(77)
+    out = {}
+    L = 32 * 40
+    ring = pf.last_attn_weights()
+    ring.set_max_length(L + 64)
+    prefill = torch.softmax(torch.randn(1, 8, 24, L, generator=gen) * 2, -1).half()
+    ring.update(prefill)
+    out["prefill_w"] = npy(prefill)
+    out["ring_after_prefill"] = npy(ring.weights.clone())
+    steps = []
+    for s in range(5):
+        w = torch.softmax(torch.randn(2, 8, 1, L + s + 1, generator=gen) * 2, -1).half()
+        ring.update(w)
+        steps.append(w)
+        out[f"step_w{s}"] = npy(w)
+    out["ring_after_steps"] = npy(ring.weights.clone())
+    out["ring_next_line"] = np.array(ring.next_line)
+    imp = ring.calculate_token_importance()
+    out["importance"] = npy(imp)
+    work = imp[:L].clone()
+    ids = pf.get_block_token_idx(32, L // 32, work)
+    out["rank_ids"] = npy(ids)
+    out["rank_importance_after"] = npy(work)
+    # realistic long-context magnitudes (probabilities ~1/L -> fp16 subnormal keys, many ties)
+    L2 = 32 * 256
+    imp2 = (torch.rand(L2, generator=gen) * 2e-3).half()
+    out["imp2"] = npy(imp2)
+    w2 = imp2.clone()
+    out["rank2_ids"] = npy(pf.get_block_token_idx(32, L2 // 32, w2))
+    out["rank2_after"] = npy(w2)
+    w3 = w2.clone()                                         # second division, as on the V side
+    out["rank3_ids"] = npy(pf.get_block_token_idx(32, L2 // 32, w3))
+    # token range
+    v = torch.randn(2, 4, 37, 128, generator=gen).half()
+    out["range_v"] = npy(v)
+    out["range_out"] = npy(pf.calculate_token_range(v, None))
+    arr = torch.tensor([3, 0, 7, 9, 1, 2], dtype=torch.int32)
+    out["mse_in"] = npy(arr.clone())
+    out["mse_out"] = npy(pf.make_sum_equal(arr.clone(), 20))
+    save("ranking", **out)
+
+
+# ------------------------------------------------------------------------------------------
+# 3. flush sequences through KV_cache_hqe_2, then the dense reconstruction
+# ------------------------------------------------------------------------------------------
+def dump_cache(prefix, cache, out):
+    for i, item in enumerate(cache):
+        if item is None:
+            continue
+        out[f"{prefix}_{i}"] = np.array(item) if isinstance(item, int) else npy(item)
+
+
+def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32):
+    """steps: list of (n_new_tokens, bit_num[6]); the first entry is the prefill."""
+    gen = torch.Generator().manual_seed(seed)
+    D = 128
+    out = {"meta": np.array([B, H, D, block, group, int(times_range), len(steps)])}
+    ring = pf.last_attn_weights()
+    ring.set_max_length(4096)
+    cache = None
+    hist = 0
+    cur = 0
+    seq = 0
+    for si, (n_new, bit_num) in enumerate(steps):
+        k = outlier_K(gen, B, H, n_new, D)
+        v = torch.randn(B, H, n_new, D, generator=gen).half()
+        seq += n_new
+        cur += n_new
+        if cache is None:
+            cache = (None,) * 39 + (k, v, seq)
+        else:
+            nk = torch.cat((cache[-3], k), dim=2) if cache[-3] is not None else k
+            nv = torch.cat((cache[-2], v), dim=2) if cache[-2] is not None else v
+            cache = cache[:-3] + (nk, nv, seq)
+        L = hist + cur
+        # a few decode-step probability rows so the ring holds realistic importances
+        for _ in range(3):
+            ring.update(torch.softmax(torch.randn(B, 4 * H, 1, L, generator=gen) * 3, -1).half())
+        compress = cur - cur % block
+        total = hist + compress
+        imp = ring.calculate_token_importance()
+        sort_imp = imp[:total].clone()
+        out[f"s{si}_importance_in"] = npy(sort_imp.clone())
+        K_ids = pf.get_block_token_idx(block, total // block, sort_imp)
+        bn = torch.tensor(bit_num, dtype=torch.int32)
+        assert int(bn.sum()) == total, (int(bn.sum()), total)
+        dump_cache(f"s{si}_in", cache, out)
+        out[f"s{si}_args"] = np.array([compress, hist])
+        out[f"s{si}_K_ids"] = npy(K_ids)
+        out[f"s{si}_bit_num"] = npy(bn)
+        out[f"s{si}_importance_ranked"] = npy(sort_imp.clone())
+        out[f"s{si}_ring_in"] = npy(ring.weights.clone())
+        cache = hq.KV_cache_hqe_2(cache, compress, hist, K_ids, bn, bn.clone(), sort_imp, "uniform_group", ring,
+                                  block, group, times_range)
+        dump_cache(f"s{si}_out", cache, out)
+        out[f"s{si}_ring_out"] = npy(ring.weights.clone())
+        out[f"s{si}_importance_after"] = npy(sort_imp.clone())
+        hist += compress - bit_num[5]
+        cur -= compress
+        ring.kv_seq_len = hist + cur          # the next update() overwrites this anyway
+    rk, rv = hq.KV_cache_reconstruct_hqe(cache, "uniform_group", block, group)
+    out["recon_K"] = npy(rk)
+    out["recon_V"] = npy(rv)
+    save(name, **out)
+
+
+def main():
+    codec_cases()
+    ranking_cases()
+    # totals: 256 | 224+96=320 | 288+64=352
+    flush_sequence("flush_a", 11, 1, 2,
+                   [(262, [64, 32, 64, 64, 0, 32]), (96, [64, 32, 64, 96, 32, 32]), (64, [64, 0, 64, 128, 64, 32])],
+                   times_range=True)
+    # no eviction at all, batch 2, K and V ranked identically
+    flush_sequence("flush_b", 12, 2, 1,
+                   [(130, [32, 32, 32, 32, 0, 0]), (64, [32, 32, 64, 64, 0, 0])], times_range=False)
+    # group 64 (block 64 for K), heavier eviction
+    flush_sequence("flush_c", 13, 1, 2,
+                   [(256 + 5, [64, 64, 64, 0, 0, 64]), (128, [64, 0, 64, 64, 64, 64])], times_range=True,
+                   block=64, group=64)
+
+
+if __name__ == "__main__":
+    main()
