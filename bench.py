@@ -1,0 +1,411 @@
+#!/usr/bin/env python
+"""Decode-attention throughput of the hybrid mixed-precision KV cache on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1]
+
+One "step" = the attention of one decode step of the whole model: for every layer, the fused decode
+(q.K^T, softmax, p.V over the 8/4/2-bit tiers and the fp16 residual window) over that layer's own
+cache.  Default workload (N=1): Llama-3.1-8B shape, 32 layers, batch 1, context 32768, 10 % evicted,
+20/40/40 % of the rest in 8/4/2-bit, group 32, residual 128, synthetic N(0,1) data.  The 32 caches
+total ~1.2 GB, ten times the 126 MB L2, so every step streams its cache from HBM.
+
+N > 1 (launched by torch.distributed.run): kv heads are sharded over the ranks (strong scaling); each
+layer's per-head outputs are all-gathered over NCCL.
+
+Prints ONE JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC = "decode-attn tokens/sec at 32k ctx"
+UNIT = "tokens/s"
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries under
+# profiles/ (None until a capture of that kernel exists).
+NCU_TRAFFIC_BYTES = {"k_pass_kernel": None, "v_pass_kernel": None}
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg1")
+    ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
+    ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons during the timed region (read-only query)."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# -------------------------------------------------------------------------------------------------
+# CPU arm: the numpy oracle (a port of the reference's pure-PyTorch dequant + matmul path) on the host
+# -------------------------------------------------------------------------------------------------
+def cpu_decode_seconds(cache_host, q_host, group, threads):
+    """Seconds for one layer's decode attention on the host: dense dequantisation of every tier
+    (KV_cache_reconstruct_hqe) + fp32 softmax(q K^T) V, kv heads spread over `threads` threads."""
+    from concurrent.futures import ThreadPoolExecutor
+    from oracle import hqkv_oracle as O
+    H = next(x for x in (cache_host[40], cache_host[8], cache_host[16], cache_host[24]) if x is not None).shape[1]
+    rep = q_host.shape[1] // H
+
+    def head_slice(h):
+        out = []
+        for i, item in enumerate(cache_host):
+            if item is None or i == 41 or item.ndim < 4:
+                out.append(item)
+            else:
+                out.append(item[:, h:h + 1])
+        return tuple(out), q_host[:, h * rep:(h + 1) * rep]
+
+    def run(h):
+        c, q = head_slice(h)
+        return O.decode_attention(q, c, None, group, group, dequant="fp16")
+
+    t0 = time.perf_counter()
+    if threads > 1:
+        with ThreadPoolExecutor(threads) as ex:
+            list(ex.map(run, range(H)))
+    else:
+        for h in range(H):
+            run(h)
+    return time.perf_counter() - t0
+
+
+def main():
+    args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world == 1:
+        # convenience: relaunch under torch.distributed.run
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={args.gpus}",
+               "--master-addr", "127.0.0.1", "--master-port", os.environ.get("MASTER_PORT", "29531"),
+               os.path.abspath(__file__)] + sys.argv[1:]
+        sys.exit(subprocess.call(cmd))
+
+    import numpy as np
+    import torch
+    from hqekv_b200 import build
+    build.build()
+    from hqekv_b200 import synthetic
+    from hqekv_b200._lib import check, lib, ptr, stream_ptr
+    from hqekv_b200.quant._cache import build_cache_desc
+    from hqekv_b200.quant.hqe_matmul import qkv_matmul_hqe_2
+
+    cfg = synthetic.CONFIGS[args.workload]
+    layers = args.layers or cfg.layers
+    config = {"workload": cfg.name, "layers": layers, "batch": cfg.batch, "context": cfg.context,
+              "q_heads": cfg.nh_q, "kv_heads": cfg.nh_kv, "head_dim": cfg.head_dim, "group": cfg.group,
+              "residual": cfg.residual, "evicted_frac": cfg.evict, "tier_ratio_8_4_2": list(cfg.ratios),
+              "parallelism": f"kv-head-shard x{world}" if world > 1 else "single-gpu",
+              "l2": "one step streams layers x cache bytes (>> 126 MB L2); no flush needed"}
+
+    # ---------------------------------------------------------------------------------------------
+    # reference arm: CPU only
+    # ---------------------------------------------------------------------------------------------
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        dev = torch.device("cuda:0") if torch.cuda.is_available() else None
+        if dev is None:
+            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device to build the synthetic cache on"}))
+            return
+        threads = min(cfg.nh_kv, os.cpu_count() or 1)
+        cache, q = synthetic.build_cache(cfg, dev, seed=0)
+        cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in cache)
+        q_host = q.cpu().numpy()
+        for _ in range(max(1, min(args.warmup, 1))):
+            cpu_decode_seconds(cache_host, q_host, cfg.group, threads)
+        times = [cpu_decode_seconds(cache_host, q_host, cfg.group, threads) for _ in range(max(1, min(args.steps, 5)))]
+        per_layer = statistics.median(times)
+        step_s = per_layer * layers
+        value = cfg.batch / step_s
+        sample = (f"one layer of {cfg.name} (all {cfg.nh_kv} kv heads, {synthetic.logical_length(cache)} cached tokens), "
+                  f"median of {len(times)}, scaled x{layers} layers to a full step")
+        print(json.dumps({
+            "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}))
+        return
+
+    # ---------------------------------------------------------------------------------------------
+    # our arm
+    # ---------------------------------------------------------------------------------------------
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this package has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+        assert cfg.nh_kv % world == 0, "kv heads must divide over the ranks"
+    heads_per_rank = cfg.nh_kv // world
+    shard = (rank * heads_per_rank, heads_per_rank)
+    rep = cfg.nh_q // cfg.nh_kv
+    nh_q_local = heads_per_rank * rep
+
+    # one cache per layer (distinct memory), seeded per layer
+    caches, qs = [], []
+    for layer in range(layers):
+        cache, q = synthetic.build_cache(cfg, dev, seed=layer, heads=shard)
+        caches.append(cache)
+        qs.append(q)
+    torch.cuda.synchronize()
+    L = synthetic.logical_length(caches[0])
+    bytes_per_layer = synthetic.cache_bytes(caches[0], nh_q_local)
+    config["cached_tokens"] = L
+    config["cache_bytes_per_layer_per_gpu"] = bytes_per_layer
+
+    gathered = [torch.empty(world, cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
+                for _ in range(layers)] if world > 1 else None
+
+    def step_device():
+        outs = []
+        for i in range(layers):
+            w, o = qkv_matmul_hqe_2(qs[i], caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], o)
+            outs.append(o)
+        return outs
+
+    use_graph = not args.no_graph
+    graph = None
+    for _ in range(2):
+        step_device()
+    torch.cuda.synchronize()
+    if use_graph:
+        try:
+            graph = torch.cuda.CUDAGraph()
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                step_device()
+                with torch.cuda.graph(graph, stream=side):
+                    graph_outs = step_device()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+        except Exception as e:  # capture can fail with some NCCL configurations: fall back to eager launches
+            if rank == 0:
+                print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); launching eagerly", file=sys.stderr)
+            graph = None
+            torch.cuda.synchronize()
+    config["launch"] = "cuda_graph" if graph is not None else "eager"
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step_device()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        run_step()
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    ev0.record()
+    for _ in range(args.steps):
+        run_step()
+    ev1.record()
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    ms = ev0.elapsed_time(ev1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = cfg.batch / (ms_per_step * 1e-3)
+
+    # ---- end to end through the public call, host buffers in and out every layer
+    q_host = [q.cpu().pin_memory() for q in qs]
+    out_host = [torch.empty(cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16).pin_memory() for _ in range(layers)]
+    q_dev = [torch.empty_like(q) for q in qs]
+
+    def step_e2e():
+        for i in range(layers):
+            q_dev[i].copy_(q_host[i], non_blocking=True)
+            w, o = qkv_matmul_hqe_2(q_dev[i], caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+            if world > 1:
+                dist.all_gather_into_tensor(gathered[i], o)
+            out_host[i].copy_(o, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for _ in range(3):
+        step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step_e2e()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = cfg.batch / (e2e_ms / args.steps * 1e-3)
+    q_bytes = qs[0].numel() * 2
+    e2e = {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": layers * q_bytes,
+           "d2h_bytes_per_step": layers * q_bytes, "ms_per_step": e2e_ms / args.steps,
+           "note": "per layer: q copied from pinned host memory, attn_output copied back; the cache is resident state"}
+
+    # ---- per-kernel timing for the roofline: each phase launched alone over all layers (own scratch each)
+    peak, peak_kind = load_peaks()
+    descs = []
+    for i in range(layers):
+        desc, keep, Ld, _ = build_cache_desc(caches[i], nh_q_local, cfg.group, cfg.group)
+        need = lib.hqkv_decode_workspace_bytes(desc)
+        ws = torch.zeros(need, dtype=torch.uint8, device=dev)
+        w = torch.empty(cfg.batch, nh_q_local, 1, Ld, dtype=torch.float16, device=dev)
+        o = torch.empty(cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
+        descs.append((desc, keep, ws, w, o))
+    st = stream_ptr(dev)
+
+    def run_phase(phase):
+        for i in range(layers):
+            desc, _, ws, w, o = descs[i]
+            check(lib.hqkv_decode_attention_phases(desc, ptr(qs[i]), ptr(w), ptr(o), ptr(ws), ws.numel(), phase, st))
+
+    kernel_ms = {}
+    reps = max(3, min(args.steps, 10))
+    for phase, name in ((1, "k_pass_kernel"), (2, "v_pass_kernel")):
+        run_phase(1)
+        run_phase(phase)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            run_phase(phase)
+        b.record()
+        torch.cuda.synchronize()
+        kernel_ms[name] = a.elapsed_time(b) / (reps * layers)
+    # algorithmic bytes per launch: K side and V side of one layer's cache on this GPU
+    k_bytes = sum(c.numel() * c.element_size() for s in (0, 4, 6, 7, 12, 14, 15, 20, 22, 23) if (c := caches[0][s]) is not None)
+    k_bytes += caches[0][39].numel() * 2 if caches[0][39] is not None else 0
+    v_bytes = bytes_per_layer - k_bytes
+    kernels = []
+    for name, nbytes in (("k_pass_kernel", k_bytes), ("v_pass_kernel", v_bytes)):
+        achieved = nbytes / (kernel_ms[name] * 1e-3) / 1e9
+        kernels.append({"kernel": name, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
+                        "algorithmic_bytes_per_launch": nbytes, "us_per_launch": kernel_ms[name] * 1e3,
+                        "peak_source": peak_kind})
+    dominant = max(kernels, key=lambda k: k["us_per_launch"])
+    roofline = {k: dominant[k] for k in ("bound", "achieved", "peak", "unit", "frac", "traffic")}
+    roofline.update({"kernel": dominant["kernel"], "peak_source": peak_kind, "kernels": kernels,
+                     "whole_step_GBps": bytes_per_layer * layers / (ms_per_step * 1e-3) / 1e9,
+                     "whole_step_frac": bytes_per_layer * layers / (ms_per_step * 1e-3) / 1e9 / peak})
+
+    # ---- CPU baseline on rank 0, N=1: one layer of the same workload through the oracle
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in caches[0])
+        qh = qs[0].cpu().numpy()
+        threads = 1
+        cpu_decode_seconds(cache_host, qh, cfg.group, threads)
+        ts = [cpu_decode_seconds(cache_host, qh, cfg.group, threads) for _ in range(3)]
+        per_layer = statistics.median(ts)
+        cpu_baseline = {"value": cfg.batch / (per_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
+                        "sample": f"one layer of {cfg.name} ({L} cached tokens, {cfg.nh_kv} kv heads) through the numpy "
+                                  f"oracle (dense dequantisation + fp32 attention), median of 3, scaled x{layers} layers"}
+
+    if rank == 0:
+        print(json.dumps({
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
+            "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
+            "gpu_launches": args.steps * layers * 2, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "tokens_per_sec_per_gpu": value / world}))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

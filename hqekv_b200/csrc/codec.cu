@@ -1,0 +1,331 @@
+// Group quantise + bit-pack, unpack + dequantise (sm_100a).
+//
+// HBM-bound elementwise work: every element is read once and every packed word written once.
+// Algorithmic bytes per element: 2 in, bits/8 + 4/group out.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include "common.cuh"
+
+namespace hqkv {
+
+// ------------------------------------------------------------------------------------------------
+// error plumbing shared by all translation units
+// ------------------------------------------------------------------------------------------------
+static thread_local char g_err[512] = "";
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_cuda(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return 0;
+  return fail(HQKV_E_CUDA, "%s failed: %s", what, cudaGetErrorString(e));
+}
+
+// ------------------------------------------------------------------------------------------------
+// Row path: groups are contiguous in memory (t_stride == 1).  One thread owns 8 consecutive
+// elements (one 16-byte load when aligned), GROUP/8 adjacent lanes own one group.
+// ------------------------------------------------------------------------------------------------
+template <int BITS, int GROUP>
+__global__ void __launch_bounds__(256) quantize_rows_kernel(const __half* __restrict__ x, int64_t rows, int64_t T,
+                                                            int64_t inner, int64_t outer_stride,
+                                                            int64_t inner_stride, bool vec_ok,
+                                                            uint32_t* __restrict__ code, __half* __restrict__ scale,
+                                                            __half* __restrict__ mn_out) {
+  constexpr int LPG = GROUP / 8;  // lanes per group
+  const float levels = static_cast<float>((1 << BITS) - 1);
+  const int64_t units_per_row = T / 8;
+  const int64_t total_units = rows * units_per_row;
+  // all lanes of a warp take part in the shuffles: iterate in whole-warp steps
+  const int64_t n_iter = (total_units + static_cast<int64_t>(gridDim.x) * blockDim.x - 1) /
+                         (static_cast<int64_t>(gridDim.x) * blockDim.x);
+  for (int64_t it = 0; it < n_iter; ++it) {
+    const int64_t u = (it * gridDim.x + blockIdx.x) * static_cast<int64_t>(blockDim.x) + threadIdx.x;
+    const bool live = u < total_units;
+    const int64_t row = live ? u / units_per_row : 0;
+    const int64_t t0 = live ? (u % units_per_row) * 8 : 0;
+    __half v[8];
+    if (live) {
+      const __half* src = x + (row / inner) * outer_stride + (row % inner) * inner_stride + t0;
+      if (vec_ok) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(src);
+        *reinterpret_cast<uint4*>(v) = raw;
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = src[i];
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = __float2half(0.f);
+    }
+    __half lo = v[0], hi = v[0];
+#pragma unroll
+    for (int i = 1; i < 8; ++i) {
+      lo = h_min(lo, v[i]);
+      hi = h_max(hi, v[i]);
+    }
+#pragma unroll
+    for (int off = 1; off < LPG; off <<= 1) {
+      const __half olo = __shfl_xor_sync(0xffffffffu, lo, off);
+      const __half ohi = __shfl_xor_sync(0xffffffffu, hi, off);
+      lo = h_min(lo, olo);
+      hi = h_max(hi, ohi);
+    }
+    const __half sc = quant_scale(lo, hi, levels);
+    uint64_t part = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) part |= static_cast<uint64_t>(quant_code(v[i], lo, sc, levels)) << (i * BITS);
+    const int lane = threadIdx.x & 31;
+    const int64_t out_bit = (row * T + t0) * BITS;  // bit offset of this unit in the packed row-major stream
+    if constexpr (BITS == 8) {
+      if (live) {
+        uint2 w;
+        w.x = static_cast<uint32_t>(part);
+        w.y = static_cast<uint32_t>(part >> 32);
+        *reinterpret_cast<uint2*>(code + out_bit / 32) = w;
+      }
+    } else if constexpr (BITS == 4) {
+      if (live) code[out_bit / 32] = static_cast<uint32_t>(part);
+    } else {
+      // 2 bits: 16 bits per thread, two lanes per word; 1 bit: 8 bits per thread, four lanes per word
+      constexpr int LPW = 32 / (8 * BITS);  // lanes per word
+      uint32_t w = static_cast<uint32_t>(part);
+#pragma unroll
+      for (int off = 1; off < LPW; off <<= 1) {
+        const uint32_t other = __shfl_down_sync(0xffffffffu, w, off);
+        w |= other << (8 * BITS * off);
+      }
+      if (live && (lane % LPW) == 0) code[out_bit / 32] = w;
+    }
+    if (live && (lane % LPG) == 0) {
+      const int64_t gi = (row * T + t0) / GROUP;
+      scale[gi] = sc;
+      mn_out[gi] = lo;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Column path (K): source is token-major [outer, T, inner] and is quantised as [outer*inner, T] with
+// groups of GROUP tokens per channel — the transposed view, never materialised.  One thread owns
+// one channel; a warp reads 64 contiguous bytes per token.  Two passes over the group (the second
+// hits L1/L2): min/max, then codes.
+// ------------------------------------------------------------------------------------------------
+template <int BITS>
+__global__ void __launch_bounds__(128) quantize_cols_kernel(const __half* __restrict__ x, int64_t inner, int64_t T,
+                                                            int64_t outer_stride, int64_t t_stride, int group,
+                                                            uint32_t* __restrict__ code, __half* __restrict__ scale,
+                                                            __half* __restrict__ mn_out) {
+  constexpr int FPI = 32 / BITS;
+  const float levels = static_cast<float>((1 << BITS) - 1);
+  const int64_t d = static_cast<int64_t>(blockIdx.y) * blockDim.x + threadIdx.x;
+  if (d >= inner) return;
+  const int64_t o = blockIdx.z;
+  const int64_t gi = blockIdx.x;  // group index along T
+  const __half* src = x + o * outer_stride + d + gi * group * t_stride;
+  __half lo = src[0], hi = src[0];
+  for (int t = 1; t < group; ++t) {
+    const __half v = src[t * t_stride];
+    lo = h_min(lo, v);
+    hi = h_max(hi, v);
+  }
+  const __half sc = quant_scale(lo, hi, levels);
+  const int64_t row = o * inner + d;
+  const int64_t W = T / FPI;
+  uint32_t* dst = code + row * W + gi * (group / FPI);
+  for (int w = 0; w < group / FPI; ++w) {
+    uint32_t word = 0;
+#pragma unroll
+    for (int i = 0; i < FPI; ++i) word |= quant_code(src[(w * FPI + i) * t_stride], lo, sc, levels) << (i * BITS);
+    dst[w] = word;
+  }
+  const int64_t G = T / group;
+  scale[row * G + gi] = sc;
+  mn_out[row * G + gi] = lo;
+}
+
+// ------------------------------------------------------------------------------------------------
+// unpack + two-rounding dequantise; one thread writes 8 consecutive fp16 values (16 bytes)
+// ------------------------------------------------------------------------------------------------
+template <int BITS>
+__global__ void __launch_bounds__(256) dequantize_kernel(const uint32_t* __restrict__ code,
+                                                         const __half* __restrict__ scale,
+                                                         const __half* __restrict__ mn, int64_t n_units, int group,
+                                                         __half* __restrict__ out) {
+  const int64_t u = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (u >= n_units) return;
+  const int64_t e0 = u * 8;  // first element (row-major over [rows, T]; T is a multiple of the group, group of 8)
+  const int64_t bit0 = e0 * BITS;
+  uint64_t bits = code[bit0 / 32];
+  if (BITS == 8) bits |= static_cast<uint64_t>(code[bit0 / 32 + 1]) << 32;
+  bits >>= (bit0 % 32);
+  const __half sc = scale[e0 / group], z = mn[e0 / group];
+  __half v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = dequant_2r(static_cast<uint32_t>(bits >> (i * BITS)) & ((1u << BITS) - 1), sc, z);
+  *reinterpret_cast<uint4*>(out + e0) = *reinterpret_cast<const uint4*>(v);
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256) pack_kernel(const int32_t* __restrict__ codes, int64_t n_words,
+                                                   uint32_t* __restrict__ words) {
+  constexpr int FPI = 32 / BITS;
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < FPI; ++i) word |= static_cast<uint32_t>(codes[w * FPI + i]) << (i * BITS);
+  words[w] = word;
+}
+
+template <int BITS>
+__global__ void __launch_bounds__(256) unpack_kernel(const uint32_t* __restrict__ words, int64_t n_words,
+                                                     __half* __restrict__ out) {
+  constexpr int FPI = 32 / BITS;
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  const uint32_t word = words[w];
+#pragma unroll
+  for (int i = 0; i < FPI; ++i) out[w * FPI + i] = __uint2half_rn((word >> (i * BITS)) & ((1u << BITS) - 1));
+}
+
+template <int BITS>
+static int launch_quant_rows(const __half* x, int64_t rows, int64_t T, int64_t inner, int64_t os, int64_t is,
+                             int group, bool vec_ok, uint32_t* code, __half* scale, __half* mn, cudaStream_t st) {
+  const int64_t units = rows * (T / 8);
+  const int threads = 256;
+  int64_t blocks = ceil_div(units, threads);
+  if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond 64 CTAs per SM
+  if (blocks < 1) blocks = 1;
+  switch (group) {
+    case 32:
+      quantize_rows_kernel<BITS, 32><<<blocks, threads, 0, st>>>(x, rows, T, inner, os, is, vec_ok, code, scale, mn);
+      break;
+    case 64:
+      quantize_rows_kernel<BITS, 64><<<blocks, threads, 0, st>>>(x, rows, T, inner, os, is, vec_ok, code, scale, mn);
+      break;
+    default:
+      quantize_rows_kernel<BITS, 128><<<blocks, threads, 0, st>>>(x, rows, T, inner, os, is, vec_ok, code, scale, mn);
+      break;
+  }
+  return 0;
+}
+
+}  // namespace hqkv
+
+using namespace hqkv;
+
+extern "C" const char* hqkv_last_error(void) { return g_err; }
+extern "C" int hqkv_version(void) { return 100; }
+
+extern "C" int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, int64_t outer_stride,
+                                  int64_t inner_stride, int64_t t_stride, int group, int bits, void* code,
+                                  void* scale, void* mn, void* stream) {
+  HQKV_REQUIRE(bits == 8 || bits == 4 || bits == 2 || bits == 1, "quantize_pack: bits must be 8, 4, 2 or 1 (got %d)", bits);
+  HQKV_REQUIRE(valid_group(group), "quantize_pack: group must be 32, 64 or 128 (got %d)", group);
+  HQKV_REQUIRE(rows >= 0 && T >= 0 && inner > 0, "quantize_pack: negative size");
+  HQKV_REQUIRE(T % group == 0, "quantize_pack: T (%lld) is not a multiple of the group size %d", (long long)T, group);
+  HQKV_REQUIRE(rows % inner == 0, "quantize_pack: rows (%lld) is not a multiple of inner (%lld)", (long long)rows,
+               (long long)inner);
+  if (rows == 0 || T == 0) return HQKV_OK;
+  HQKV_REQUIRE(x && code && scale && mn, "quantize_pack: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const __half* xs = static_cast<const __half*>(x);
+  uint32_t* c = static_cast<uint32_t*>(code);
+  __half* s = static_cast<__half*>(scale);
+  __half* m = static_cast<__half*>(mn);
+  if (t_stride == 1) {
+    const bool vec_ok = aligned(x, 16) && outer_stride % 8 == 0 && inner_stride % 8 == 0;
+    switch (bits) {
+      case 8: launch_quant_rows<8>(xs, rows, T, inner, outer_stride, inner_stride, group, vec_ok, c, s, m, st); break;
+      case 4: launch_quant_rows<4>(xs, rows, T, inner, outer_stride, inner_stride, group, vec_ok, c, s, m, st); break;
+      case 2: launch_quant_rows<2>(xs, rows, T, inner, outer_stride, inner_stride, group, vec_ok, c, s, m, st); break;
+      default: launch_quant_rows<1>(xs, rows, T, inner, outer_stride, inner_stride, group, vec_ok, c, s, m, st); break;
+    }
+  } else if (inner_stride == 1) {
+    const int64_t outer = rows / inner;
+    HQKV_REQUIRE(outer <= 65535 && ceil_div(inner, 128) <= 65535, "quantize_pack: too many rows for the column path");
+    dim3 grid(static_cast<unsigned>(T / group), static_cast<unsigned>(ceil_div(inner, 128)),
+              static_cast<unsigned>(outer));
+    switch (bits) {
+      case 8: quantize_cols_kernel<8><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+      case 4: quantize_cols_kernel<4><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+      case 2: quantize_cols_kernel<2><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+      default: quantize_cols_kernel<1><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+    }
+  } else {
+    return fail(HQKV_E_INVALID, "quantize_pack: unsupported strides (need t_stride == 1 or inner_stride == 1)");
+  }
+  HQKV_LAUNCH_CHECK("quantize_pack");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_dequantize_unpack(const void* code, const void* scale, const void* mn, int64_t rows, int64_t T,
+                                      int group, int bits, void* out, void* stream) {
+  HQKV_REQUIRE(bits == 8 || bits == 4 || bits == 2 || bits == 1, "dequantize_unpack: bits must be 8, 4, 2 or 1");
+  HQKV_REQUIRE(valid_group(group), "dequantize_unpack: group must be 32, 64 or 128");
+  HQKV_REQUIRE(rows >= 0 && T >= 0 && T % group == 0, "dequantize_unpack: T is not a multiple of the group size");
+  if (rows == 0 || T == 0) return HQKV_OK;
+  HQKV_REQUIRE(code && scale && mn && out, "dequantize_unpack: null pointer");
+  HQKV_REQUIRE(aligned(out, 16), "dequantize_unpack: output must be 16-byte aligned");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int64_t units = rows * T / 8;
+  const unsigned blocks = static_cast<unsigned>(ceil_div(units, 256));
+  const uint32_t* c = static_cast<const uint32_t*>(code);
+  const __half* s = static_cast<const __half*>(scale);
+  const __half* m = static_cast<const __half*>(mn);
+  __half* o = static_cast<__half*>(out);
+  switch (bits) {
+    case 8: dequantize_kernel<8><<<blocks, 256, 0, st>>>(c, s, m, units, group, o); break;
+    case 4: dequantize_kernel<4><<<blocks, 256, 0, st>>>(c, s, m, units, group, o); break;
+    case 2: dequantize_kernel<2><<<blocks, 256, 0, st>>>(c, s, m, units, group, o); break;
+    default: dequantize_kernel<1><<<blocks, 256, 0, st>>>(c, s, m, units, group, o); break;
+  }
+  HQKV_LAUNCH_CHECK("dequantize_unpack");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_pack(const void* codes_i32, int64_t rows, int64_t T, int bits, void* words, void* stream) {
+  HQKV_REQUIRE(bits == 8 || bits == 4 || bits == 2 || bits == 1, "pack: bits must be 8, 4, 2 or 1");
+  HQKV_REQUIRE(rows >= 0 && T >= 0 && T % (32 / bits) == 0, "pack: T is not a multiple of 32/bits");
+  const int64_t n_words = rows * T / (32 / bits);
+  if (n_words == 0) return HQKV_OK;
+  HQKV_REQUIRE(codes_i32 && words, "pack: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>(ceil_div(n_words, 256));
+  const int32_t* c = static_cast<const int32_t*>(codes_i32);
+  uint32_t* w = static_cast<uint32_t*>(words);
+  switch (bits) {
+    case 8: pack_kernel<8><<<blocks, 256, 0, st>>>(c, n_words, w); break;
+    case 4: pack_kernel<4><<<blocks, 256, 0, st>>>(c, n_words, w); break;
+    case 2: pack_kernel<2><<<blocks, 256, 0, st>>>(c, n_words, w); break;
+    default: pack_kernel<1><<<blocks, 256, 0, st>>>(c, n_words, w); break;
+  }
+  HQKV_LAUNCH_CHECK("pack");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_unpack(const void* words, int64_t rows, int64_t W, int bits, void* out_f16, void* stream) {
+  HQKV_REQUIRE(bits == 8 || bits == 4 || bits == 2 || bits == 1, "unpack: bits must be 8, 4, 2 or 1");
+  HQKV_REQUIRE(rows >= 0 && W >= 0, "unpack: negative size");
+  const int64_t n_words = rows * W;
+  if (n_words == 0) return HQKV_OK;
+  HQKV_REQUIRE(words && out_f16, "unpack: null pointer");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned blocks = static_cast<unsigned>(ceil_div(n_words, 256));
+  const uint32_t* w = static_cast<const uint32_t*>(words);
+  __half* o = static_cast<__half*>(out_f16);
+  switch (bits) {
+    case 8: unpack_kernel<8><<<blocks, 256, 0, st>>>(w, n_words, o); break;
+    case 4: unpack_kernel<4><<<blocks, 256, 0, st>>>(w, n_words, o); break;
+    case 2: unpack_kernel<2><<<blocks, 256, 0, st>>>(w, n_words, o); break;
+    default: unpack_kernel<1><<<blocks, 256, 0, st>>>(w, n_words, o); break;
+  }
+  HQKV_LAUNCH_CHECK("unpack");
+  return HQKV_OK;
+}

@@ -1,0 +1,890 @@
+// Fused mixed-precision decode attention over the tiered KV cache (sm_100a).
+//
+// Two launches per call:
+//   k_pass : logits[h, pos] = scale * q_h . K̂_pos for every tier (8/4/2-bit packed, fp16 tier,
+//            fp16 residual), written to an fp32 scratch row at the tokens' logical positions,
+//            plus one (max, sum-exp) pair per CTA and head.
+//   v_pass : every CTA first folds the k_pass pairs into the global (max, sum) of its heads,
+//            then accumulates sum_t exp(logit_t - max) * V̂_t over its token range, normalises a
+//            slice of the probability row into the fp16 output, and the last CTA of each
+//            (batch, kv head) adds the partial sums in chunk order and writes the output.
+//
+// The roofline is HBM: every packed word, scale and zero is read exactly once per call and is
+// shared by all query heads of its kv head (GQA).  At 2-4 bits there are 1.6-2.7 codes per
+// byte; four query heads need four FMAs per code, more than the FP32 pipes can issue at HBM
+// speed.  The codes are therefore dequantised to fp16 pairs in registers (PRMT + LOP3 + HFMA2)
+// straight into m16n8k16 A fragments and the dot products run on the tensor pipe with fp32
+// accumulation; no operand takes a trip through shared memory.  Fragment rows/columns are
+// mapped to tokens and channels so that a thread consumes every code of each word it loads.
+#include <math.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace hqkv {
+
+constexpr int D = 128;           // head dim
+constexpr int NWARP = 4;         // warps per CTA
+constexpr int NTHREADS = NWARP * 32;
+constexpr int MAX_REP = 8;       // query heads per kv head (n of the m16n8k16 tile)
+constexpr int SCALE_PAD = 8;     // halfs of padding per shared-memory scale row
+constexpr int MAX_K_GROUPS = 32; // groups of one K chunk (chunk tokens / group)
+constexpr int MAX_V_CHUNK = 1024;
+
+struct TierDev {
+  const void* k_data;
+  const __half* k_scale;
+  const __half* k_zero;
+  const int64_t* k_idx;
+  const void* v_data;
+  const __half* v_scale;
+  const __half* v_zero;
+  const int64_t* v_idx;
+  int n_k, n_v;
+  int bits;
+  int k_chunk0, k_chunk_tokens;  // first chunk id of this tier in the k_pass grid, tokens per chunk
+  int v_chunk0, v_chunk_tokens;
+};
+
+struct DecodeParams {
+  TierDev tier[HQKV_NUM_TIERS + 1];  // [5] = fp16 residual window (token-major K and V)
+  int B, H, nh_q, rep, L;
+  int gk_shift, gv_shift;
+  int nk_chunks, nv_chunks;
+  int w_slice;  // logical positions normalised per v_pass CTA
+  float scale;
+  const __half* q;
+  __half* weights;
+  __half* out;
+  float* logits;   // [B*nh_q][L]
+  float2* k_part;  // [B*H][nk_chunks][MAX_REP]
+  float* v_part;   // [B*H][nv_chunks][rep][D]
+  unsigned* counters;  // [B*H]
+};
+
+// ------------------------------------------------------------------------------------------------
+// fragments
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Streaming loads: the cache is read once per call, keep it out of L1.
+__device__ __forceinline__ uint32_t ld_stream(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint2 ld_stream(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Storage formats.  A "word" is what one thread loads for one (row, column) slot; it holds FPI
+// values of one row.  SUB = independently decoded sub-units of a word (bytes of a packed word,
+// 32-bit lanes of a uint4 of halfs), CPS = values per sub-unit.
+template <int BITS>
+struct Fmt;
+template <>
+struct Fmt<8> {
+  using word_t = uint2;  // two packed words = 8 codes
+  static constexpr int FPI = 8, SUB = 8, CPS = 1;
+};
+template <>
+struct Fmt<4> {
+  using word_t = uint32_t;
+  static constexpr int FPI = 8, SUB = 4, CPS = 2;
+};
+template <>
+struct Fmt<2> {
+  using word_t = uint32_t;
+  static constexpr int FPI = 16, SUB = 4, CPS = 4;
+};
+template <>
+struct Fmt<16> {
+  using word_t = uint4;  // eight halfs
+  static constexpr int FPI = 8, SUB = 4, CPS = 2;
+};
+
+// Decode sub-unit `sub` of the words wa (first row of the pair) and wb (second row) into CPS
+// half2 values (value of row a in the low half, row b in the high half): v = code*scale + zero
+// with one fp16 rounding; `sz` packs the scales of the two rows, `zz` their zeros.
+template <int BITS>
+struct Decode;
+
+template <>
+struct Decode<8> {
+  template <int SUBI>
+  static __device__ __forceinline__ void run(const uint2& wa, const uint2& wb, __half2 sz, __half2 zz,
+                                             uint32_t (&out)[1]) {
+    const uint32_t a = SUBI < 4 ? wa.x : wa.y, b = SUBI < 4 ? wb.x : wb.y;
+    constexpr int j = SUBI & 3;
+    const uint32_t t = __byte_perm(a, b, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+    const uint32_t x = (t & 0x00FF00FFu) | 0x64006400u;  // 1024 + code
+    const __half2 c = __hsub2(u32_as_h2(x), __half2half2(__float2half(1024.f)));
+    out[0] = h2_as_u32(__hfma2(c, sz, zz));
+  }
+};
+template <>
+struct Decode<4> {
+  template <int SUBI>
+  static __device__ __forceinline__ void run(const uint32_t& wa, const uint32_t& wb, __half2 sz, __half2 zz,
+                                             uint32_t (&out)[2]) {
+    constexpr int j = SUBI;
+    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+    const uint32_t x0 = (t & 0x000F000Fu) | 0x64006400u;  // 1024 + code
+    const uint32_t x1 = (t & 0x00F000F0u) | 0x64006400u;  // 1024 + 16*code
+    const __half2 c0 = __hsub2(u32_as_h2(x0), __half2half2(__float2half(1024.f)));
+    const __half2 c1 = __hfma2(u32_as_h2(x1), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f)));
+    out[0] = h2_as_u32(__hfma2(c0, sz, zz));
+    out[1] = h2_as_u32(__hfma2(c1, sz, zz));
+  }
+};
+template <>
+struct Decode<2> {
+  template <int SUBI>
+  static __device__ __forceinline__ void run(const uint32_t& wa, const uint32_t& wb, __half2 sz, __half2 zz,
+                                             uint32_t (&out)[4]) {
+    constexpr int j = SUBI;
+    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+    const uint32_t x0 = (t & 0x00030003u) | 0x64006400u;  // 1024 + code
+    const uint32_t x1 = (t & 0x000C000Cu) | 0x64006400u;  // 1024 + 4*code
+    const uint32_t x2 = (t & 0x00300030u) | 0x64006400u;  // 1024 + 16*code
+    const uint32_t x3 = (t & 0x00C000C0u) | 0x64006400u;  // 1024 + 64*code
+    const __half2 c0 = __hsub2(u32_as_h2(x0), __half2half2(__float2half(1024.f)));
+    const __half2 c1 = __hfma2(u32_as_h2(x1), __half2half2(__float2half(0.25f)), __half2half2(__float2half(-256.f)));
+    const __half2 c2 = __hfma2(u32_as_h2(x2), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f)));
+    const __half2 c3 = __hfma2(u32_as_h2(x3), __half2half2(__float2half(0.015625f)), __half2half2(__float2half(-16.f)));
+    out[0] = h2_as_u32(__hfma2(c0, sz, zz));
+    out[1] = h2_as_u32(__hfma2(c1, sz, zz));
+    out[2] = h2_as_u32(__hfma2(c2, sz, zz));
+    out[3] = h2_as_u32(__hfma2(c3, sz, zz));
+  }
+};
+template <>
+struct Decode<16> {
+  template <int SUBI>
+  static __device__ __forceinline__ void run(const uint4& wa, const uint4& wb, __half2, __half2, uint32_t (&out)[2]) {
+    const uint32_t a = SUBI == 0 ? wa.x : SUBI == 1 ? wa.y : SUBI == 2 ? wa.z : wa.w;
+    const uint32_t b = SUBI == 0 ? wb.x : SUBI == 1 ? wb.y : SUBI == 2 ? wb.z : wb.w;
+    out[0] = __byte_perm(a, b, 0x5410);
+    out[1] = __byte_perm(a, b, 0x7632);
+  }
+};
+
+template <typename W>
+__device__ __forceinline__ W zero_word();
+template <>
+__device__ __forceinline__ uint32_t zero_word<uint32_t>() { return 0u; }
+template <>
+__device__ __forceinline__ uint2 zero_word<uint2>() { return make_uint2(0u, 0u); }
+template <>
+__device__ __forceinline__ uint4 zero_word<uint4>() { return make_uint4(0u, 0u, 0u, 0u); }
+
+// One 16-deep contraction step over all M-tiles of a thread's slots.
+//   w[p][r]: word of row-pair member p (0,1 -> fragment columns 2tig,2tig+1; 2,3 -> +8,+9) and row
+//            slot r (0 -> fragment row g, 1 -> row g+8)
+//   sz/zz[q][r]: scales/zeros of pair q (0: p=0,1; 1: p=2,3) for slot r
+// M-tile index of sub-unit s, value k: s*CPS + k.
+template <int BITS, int SUBI, int NM>
+__device__ __forceinline__ void mma_sub(float (&acc)[NM][4], const typename Fmt<BITS>::word_t (&w)[4][2],
+                                        const __half2 (&sz)[2][2], const __half2 (&zz)[2][2], uint32_t b0,
+                                        uint32_t b1) {
+  constexpr int CPS = Fmt<BITS>::CPS;
+  uint32_t a0[CPS], a1[CPS], a2[CPS], a3[CPS];
+  Decode<BITS>::template run<SUBI>(w[0][0], w[1][0], sz[0][0], zz[0][0], a0);
+  Decode<BITS>::template run<SUBI>(w[0][1], w[1][1], sz[0][1], zz[0][1], a1);
+  Decode<BITS>::template run<SUBI>(w[2][0], w[3][0], sz[1][0], zz[1][0], a2);
+  Decode<BITS>::template run<SUBI>(w[2][1], w[3][1], sz[1][1], zz[1][1], a3);
+#pragma unroll
+  for (int k = 0; k < CPS; ++k) mma16816(acc[SUBI * CPS + k], a0[k], a1[k], a2[k], a3[k], b0, b1);
+}
+
+template <int BITS, int NM>
+__device__ __forceinline__ void mma_words(float (&acc)[NM][4], const typename Fmt<BITS>::word_t (&w)[4][2],
+                                          const __half2 (&sz)[2][2], const __half2 (&zz)[2][2], uint32_t b0,
+                                          uint32_t b1) {
+  constexpr int SUB = Fmt<BITS>::SUB;
+  mma_sub<BITS, 0, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 1, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 2, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 3, NM>(acc, w, sz, zz, b0, b1);
+  if constexpr (SUB == 8) {
+    mma_sub<BITS, 4, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 5, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 6, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 7, NM>(acc, w, sz, zz, b0, b1);
+  }
+}
+
+// online (max, sum-exp) update
+__device__ __forceinline__ void softmax_push(float& m, float& l, float x) {
+  if (x > m) {
+    l = l * exp2f((m - x) * 1.4426950408889634f) + 1.f;
+    m = x;
+  } else {
+    l += exp2f((x - m) * 1.4426950408889634f);
+  }
+}
+__device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, float l2) {
+  const float mx = fmaxf(m, m2);
+  if (mx == -INFINITY) return;  // both empty
+  l = l * exp2f((m - mx) * 1.4426950408889634f) + l2 * exp2f((m2 - mx) * 1.4426950408889634f);
+  m = mx;
+}
+
+// ------------------------------------------------------------------------------------------------
+// k_pass
+// ------------------------------------------------------------------------------------------------
+struct KShared {
+  uint2 qfrag[8][32];                               // B fragments of q per 16-channel step and lane
+  __half s[MAX_K_GROUPS][D + SCALE_PAD];            // scale[group][channel]
+  __half z[MAX_K_GROUPS][D + SCALE_PAD];
+  float red_m[NWARP][MAX_REP], red_l[NWARP][MAX_REP];
+};
+
+// Quantised / fp16 channel-major tier: rows are channels, words run along tokens.
+// Per warp one span of 16 word slots (16*FPI tokens): fragment row g <-> slot g, row g+8 <-> slot g+8,
+// M-tile i <-> i-th value of every slot.
+template <int BITS>
+__device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                       int chunk_t0, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
+  using F = Fmt<BITS>;
+  using word_t = typename F::word_t;
+  constexpr int FPI = F::FPI;
+  constexpr int NM = FPI;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int n = T.n_k;
+  const int64_t W = n / FPI;  // word slots per channel row
+  const word_t* base = reinterpret_cast<const word_t*>(T.k_data) + static_cast<int64_t>(bh) * D * W;
+  int64_t wc[2];
+  bool ok[2];
+  int gl[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    wc[r] = span_t0 / FPI + r * 8 + g;
+    ok[r] = wc[r] < W;
+    const int tok = static_cast<int>(wc[r]) * FPI;
+    gl[r] = ok[r] ? ((tok >> P.gk_shift) - (chunk_t0 >> P.gk_shift)) : 0;
+  }
+  float acc[NM][4];
+#pragma unroll
+  for (int i = 0; i < NM; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  word_t w[4][2], wn[4][2];
+  auto load = [&](word_t (&dst)[4][2], int kt) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) dst[p][r] = ok[r] ? ld_stream(base + ch * W + wc[r]) : zero_word<word_t>();
+    }
+  };
+  load(w, 0);
+#pragma unroll 1
+  for (int kt = 0; kt < 8; ++kt) {
+    if (kt + 1 < 8) load(wn, kt + 1);
+    __half2 sz[2][2], zz[2][2];
+    if constexpr (BITS != 16) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        const int ch = kt * 16 + 2 * tig + q * 8;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          sz[q][r] = *reinterpret_cast<const __half2*>(&sh.s[gl[r]][ch]);
+          zz[q][r] = *reinterpret_cast<const __half2*>(&sh.z[gl[r]][ch]);
+        }
+      }
+    }
+    const uint2 bq = sh.qfrag[kt][lane];
+    mma_words<BITS, NM>(acc, w, sz, zz, bq.x, bq.y);
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      w[p][0] = wn[p][0];
+      w[p][1] = wn[p][1];
+    }
+  }
+  // scatter the logits of heads 2tig, 2tig+1 to their logical positions
+  const int h0 = 2 * tig;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!ok[r]) continue;
+    const int64_t tok0 = wc[r] * FPI;
+#pragma unroll
+    for (int i = 0; i < NM; ++i) {
+      const int64_t pos = T.k_idx[tok0 + i];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int h = h0 + e;
+        if (h < P.rep) {
+          const float x = acc[i][r * 2 + e] * P.scale;
+          P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L + pos] = x;
+          softmax_push(m_run[e], l_run[e], x);
+        }
+      }
+    }
+  }
+}
+
+// fp16 residual window, token-major [r][D]: A fragments are read directly.
+__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b,
+                                                int kvh, int tile_t0, float (&m_run)[2], float (&l_run)[2]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int n = T.n_k;
+  const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
+  const int t[2] = {tile_t0 + g, tile_t0 + g + 8};
+  const bool ok[2] = {t[0] < n, t[1] < n};
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt) {
+    const int ch = kt * 16 + 2 * tig;
+    uint32_t a[4];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      a[r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch) : 0u;
+      a[2 + r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch + 8) : 0u;
+    }
+    const uint2 bq = sh.qfrag[kt][lane];
+    mma16816(acc, a[0], a[1], a[2], a[3], bq.x, bq.y);
+  }
+  const int h0 = 2 * tig;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!ok[r]) continue;
+    const int64_t pos = P.L - n + t[r];
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = h0 + e;
+      if (h < P.rep) {
+        const float x = acc[r * 2 + e] * P.scale;
+        P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L + pos] = x;
+        softmax_push(m_run[e], l_run[e], x);
+      }
+    }
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                        int chunk_t0, float (&m_run)[2], float (&l_run)[2]) {
+  constexpr int SPAN = 16 * Fmt<BITS>::FPI;
+  const int warp = threadIdx.x >> 5;
+  const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
+  if constexpr (BITS != 16) {
+    // stage scale/zero of this chunk as [group][channel]
+    const int G = T.n_k >> P.gk_shift;
+    const int g0 = chunk_t0 >> P.gk_shift;
+    const int ng = ((chunk_end - chunk_t0) + (1 << P.gk_shift) - 1) >> P.gk_shift;
+    const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G;
+    const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G;
+    for (int i = threadIdx.x; i < D * ng; i += NTHREADS) {
+      const int ch = i / ng, gi = i - ch * ng;
+      sh.s[gi][ch] = s[static_cast<int64_t>(ch) * G + g0 + gi];
+      sh.z[gi][ch] = z[static_cast<int64_t>(ch) * G + g0 + gi];
+    }
+    __syncthreads();
+  }
+  for (int span_t0 = chunk_t0 + warp * SPAN; span_t0 < chunk_end; span_t0 += NWARP * SPAN)
+    k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0, m_run, l_run);
+}
+
+__global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
+  __shared__ KShared sh;
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / P.H, kvh = bh - b * P.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+
+  // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
+  if (warp == 0) {
+    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      uint2 f = make_uint2(0u, 0u);
+      if (g < P.rep) {
+        f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
+        f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
+      }
+      sh.qfrag[kt][lane] = f;
+    }
+  }
+  __syncthreads();
+
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].k_chunk0 && chunk < P.tier[t + 1].k_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  if (ti == HQKV_NUM_TIERS) {
+    const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
+    for (int t0 = chunk_t0 + warp * 16; t0 < chunk_end; t0 += NWARP * 16)
+      k_residual_tile(P, T, sh, bh, b, kvh, t0, m_run, l_run);
+  } else if (T.bits == 8) {
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+  } else if (T.bits == 4) {
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+  } else if (T.bits == 2) {
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+  } else {
+    k_chunk<16>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+  }
+
+  // (max, sum) of this CTA per head: lanes with equal tig hold the same two heads
+#pragma unroll
+  for (int e = 0; e < 2; ++e) {
+#pragma unroll
+    for (int off = 4; off < 32; off <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m_run[e], off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l_run[e], off);
+      softmax_merge(m_run[e], l_run[e], m2, l2);
+    }
+    if (g == 0) {
+      sh.red_m[warp][2 * tig + e] = m_run[e];
+      sh.red_l[warp][2 * tig + e] = l_run[e];
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < MAX_REP) {
+    float m = sh.red_m[0][threadIdx.x], l = sh.red_l[0][threadIdx.x];
+    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, sh.red_m[w][threadIdx.x], sh.red_l[w][threadIdx.x]);
+    P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + threadIdx.x] = make_float2(m, l);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// v_pass
+// ------------------------------------------------------------------------------------------------
+struct VShared {
+  __half e[MAX_REP][MAX_V_CHUNK + 8];        // exp(logit - max) per head and token of the chunk
+  __half s[4][MAX_V_CHUNK + 8];              // scale[channel group][token]
+  __half z[4][MAX_V_CHUNK + 8];
+  float red[NWARP][MAX_REP][D];              // per-warp partial outputs
+  float gm[MAX_REP], gl[MAX_REP];            // global max / sum of this kv head's query heads
+  float wm[NWARP][MAX_REP], wl[NWARP][MAX_REP];
+  unsigned is_last;
+};
+
+// V tier, token-major rows.  Contraction runs over tokens (16 per step): fragment columns
+// 2tig,2tig+1,2tig+8,2tig+9 <-> tokens t0+..., fragment row g <-> channel slot g, row g+8 <-> slot
+// g+8 (2-bit: low/high half of word g), M-tile i <-> i-th value of every slot.
+template <int BITS>
+__device__ __forceinline__ void v_chunk(const DecodeParams& P, const TierDev& T, VShared& sh, int bh,
+                                        int chunk_t0, int chunk_n, float (&acc)[8][4]) {
+  using F = Fmt<BITS>;
+  using word_t = typename F::word_t;
+  constexpr bool HALF_SPLIT = (BITS == 2);  // one word per token row covers both row slots
+  constexpr int WORDS_PER_TOKEN = BITS == 2 ? 8 : 16;  // in units of word_t
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+  const int n = T.n_v;
+  const word_t* base = reinterpret_cast<const word_t*>(T.v_data) + static_cast<int64_t>(bh) * n * WORDS_PER_TOKEN;
+  // channel group of the two row slots
+  int cg[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int ch0 = HALF_SPLIT ? (16 * g + 8 * s) : (8 * (s * 8 + g));
+    cg[s] = ch0 >> P.gv_shift;
+  }
+  for (int kt0 = warp * 16; kt0 < chunk_n; kt0 += NWARP * 16) {
+    // the four tokens of this thread's fragment columns (chunk-local), clamped for the loads
+    int tl[4];
+    tl[0] = kt0 + 2 * tig;
+    tl[1] = tl[0] + 1;
+    tl[2] = tl[0] + 8;
+    tl[3] = tl[0] + 9;
+    word_t w[4][2];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int64_t tok = chunk_t0 + min(tl[p], chunk_n - 1);
+      if constexpr (HALF_SPLIT) {
+        const word_t x = ld_stream(base + tok * WORDS_PER_TOKEN + g);
+        w[p][0] = x;
+        w[p][1] = x >> 16;  // values 8..15 of the word move to bytes 0,1
+      } else {
+        w[p][0] = ld_stream(base + tok * WORDS_PER_TOKEN + g);
+        w[p][1] = ld_stream(base + tok * WORDS_PER_TOKEN + 8 + g);
+      }
+    }
+    __half2 sz[2][2], zz[2][2];
+    if constexpr (BITS != 16) {
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int s = 0; s < 2; ++s) {
+          sz[q][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl[q * 2]]);
+          zz[q][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl[q * 2]]);
+        }
+    }
+    // B fragment: column n = g is head g; e is zero beyond the chunk
+    uint32_t b0 = 0u, b1 = 0u;
+    if (g < P.rep) {
+      b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl[0]]);
+      b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl[2]]);
+    }
+    if constexpr (HALF_SPLIT) {
+      // only sub-units 0,1 (values 0..7) of each (shifted) word are used: 8 M-tiles
+      mma_sub<2, 0, 8>(acc, w, sz, zz, b0, b1);
+      mma_sub<2, 1, 8>(acc, w, sz, zz, b0, b1);
+    } else {
+      mma_words<BITS, 8>(acc, w, sz, zz, b0, b1);
+    }
+  }
+}
+
+// fold acc (fragment layout) into sh.red[warp][head][channel]
+template <int BITS>
+__device__ __forceinline__ void v_store_acc(VShared& sh, const float (&acc)[8][4], int rep) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int ch = (BITS == 2) ? (16 * g + 8 * s + mt) : (8 * (s * 8 + g) + mt);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int h = 2 * tig + e;
+        if (h < rep) sh.red[warp][h][ch] = acc[mt][s * 2 + e];
+      }
+    }
+}
+
+__global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
+  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int b = bh / P.H, kvh = bh - b * P.H;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int rep = P.rep;
+
+  // ---- global (max, sum) of the rep heads from the k_pass pairs
+  {
+    float m[MAX_REP], l[MAX_REP];
+#pragma unroll
+    for (int h = 0; h < MAX_REP; ++h) {
+      m[h] = -INFINITY;
+      l[h] = 0.f;
+    }
+    const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
+    for (int c = threadIdx.x; c < P.nk_chunks; c += NTHREADS) {
+#pragma unroll
+      for (int h = 0; h < MAX_REP; ++h) {
+        if (h < rep) {
+          const float2 v = part[c * MAX_REP + h];
+          softmax_merge(m[h], l[h], v.x, v.y);
+        }
+      }
+    }
+#pragma unroll
+    for (int h = 0; h < MAX_REP; ++h) {
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        const float m2 = __shfl_xor_sync(0xffffffffu, m[h], off);
+        const float l2 = __shfl_xor_sync(0xffffffffu, l[h], off);
+        softmax_merge(m[h], l[h], m2, l2);
+      }
+      if (lane == 0) {
+        sh.wm[warp][h] = m[h];
+        sh.wl[warp][h] = l[h];
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < MAX_REP) {
+      float mm = sh.wm[0][threadIdx.x], ll = sh.wl[0][threadIdx.x];
+      for (int w = 1; w < NWARP; ++w) softmax_merge(mm, ll, sh.wm[w][threadIdx.x], sh.wl[w][threadIdx.x]);
+      sh.gm[threadIdx.x] = mm;
+      sh.gl[threadIdx.x] = ll;
+    }
+    __syncthreads();
+  }
+
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
+  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
+  const int chunk_pad = (chunk_n + 15) & ~15;
+
+  // ---- stage exp(logit - max) and the scale/zero tile of this chunk
+  for (int i = threadIdx.x; i < chunk_pad; i += NTHREADS) {
+    int64_t pos = 0;
+    const bool live = i < chunk_n;
+    if (live) pos = (ti == HQKV_NUM_TIERS) ? (P.L - T.n_v + chunk_t0 + i) : T.v_idx[chunk_t0 + i];
+    for (int h = 0; h < rep; ++h) {
+      float e = 0.f;
+      if (live) {
+        const float x = P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L + pos];
+        e = exp2f((x - sh.gm[h]) * 1.4426950408889634f);
+      }
+      sh.e[h][i] = __float2half_rn(e);
+    }
+  }
+  if (ti != HQKV_NUM_TIERS && T.bits != 16) {
+    const int ng = D >> P.gv_shift;
+    const __half* s = T.v_scale + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
+    const __half* z = T.v_zero + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
+    for (int i = threadIdx.x; i < chunk_pad * ng; i += NTHREADS) {
+      const int t = i / ng, gi = i - t * ng;
+      const bool live = t < chunk_n;
+      sh.s[gi][t] = live ? s[i] : __float2half(0.f);
+      sh.z[gi][t] = live ? z[i] : __float2half(0.f);
+    }
+  }
+  __syncthreads();
+
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  const int vb = (ti == HQKV_NUM_TIERS) ? 16 : T.bits;
+  if (vb == 8) {
+    v_chunk<8>(P, T, sh, bh, chunk_t0, chunk_n, acc);
+    v_store_acc<8>(sh, acc, rep);
+  } else if (vb == 4) {
+    v_chunk<4>(P, T, sh, bh, chunk_t0, chunk_n, acc);
+    v_store_acc<4>(sh, acc, rep);
+  } else if (vb == 2) {
+    v_chunk<2>(P, T, sh, bh, chunk_t0, chunk_n, acc);
+    v_store_acc<2>(sh, acc, rep);
+  } else {
+    v_chunk<16>(P, T, sh, bh, chunk_t0, chunk_n, acc);
+    v_store_acc<16>(sh, acc, rep);
+  }
+  __syncthreads();
+  // partial output of this chunk: warps added in index order
+  float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
+  for (int i = threadIdx.x; i < rep * D; i += NTHREADS) {
+    const int h = i / D, ch = i - h * D;
+    float v = sh.red[0][h][ch];
+#pragma unroll
+    for (int w = 1; w < NWARP; ++w) v += sh.red[w][h][ch];
+    part[i] = v;
+  }
+
+  // ---- this CTA's slice of the probability row
+  {
+    const int p0 = chunk * P.w_slice, p1 = min(p0 + P.w_slice, P.L);
+    for (int h = 0; h < rep; ++h) {
+      const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+      const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
+      for (int p = p0 + threadIdx.x; p < p1; p += NTHREADS)
+        P.weights[row + p] = __float2half_rn(exp2f((P.logits[row + p] - mh) * 1.4426950408889634f) * inv);
+    }
+  }
+
+  // ---- last CTA of this (batch, kv head) sums the partial outputs in chunk order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(&P.counters[bh], 1u);
+    sh.is_last = (prev == static_cast<unsigned>(P.nv_chunks) - 1u) ? 1u : 0u;
+  }
+  __syncthreads();
+  if (sh.is_last) {
+    __threadfence();
+    const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
+    for (int i = threadIdx.x; i < rep * D; i += NTHREADS) {
+      const int h = i / D;
+      float v = 0.f;
+      for (int c = 0; c < P.nv_chunks; ++c) v += __ldcg(all + static_cast<int64_t>(c) * rep * D + i);
+      P.out[(static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i] = __float2half_rn(v / sh.gl[h]);
+    }
+    if (threadIdx.x == 0) P.counters[bh] = 0u;  // ready for the next call
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// host side
+// ------------------------------------------------------------------------------------------------
+static int ilog2(int v) {
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+struct Layout {
+  size_t logits_off, kpart_off, vpart_off, total;
+};
+
+static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay) {
+  HQKV_REQUIRE(c != nullptr, "decode: null cache descriptor");
+  HQKV_REQUIRE(c->B > 0 && c->H > 0 && c->nh_q > 0, "decode: B, H and nh_q must be positive");
+  HQKV_REQUIRE(c->D == D, "decode: head dim must be 128 (got %d)", c->D);
+  HQKV_REQUIRE(c->nh_q % c->H == 0 && c->nh_q / c->H <= MAX_REP,
+               "decode: nh_q (%d) must be a multiple of H (%d) with at most %d query heads per kv head", c->nh_q,
+               c->H, MAX_REP);
+  HQKV_REQUIRE(valid_group(c->group_k) && valid_group(c->group_v), "decode: group sizes must be 32, 64 or 128");
+  HQKV_REQUIRE(static_cast<int64_t>(c->B) * c->H <= 1024, "decode: B*H must not exceed 1024");
+  HQKV_REQUIRE(c->n_new >= 0, "decode: negative residual length");
+  memset(&P, 0, sizeof(P));
+  P.B = c->B;
+  P.H = c->H;
+  P.nh_q = c->nh_q;
+  P.rep = c->nh_q / c->H;
+  P.gk_shift = ilog2(c->group_k);
+  P.gv_shift = ilog2(c->group_v);
+  P.scale = c->softmax_scale;
+  static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
+  int64_t nk_total = 0, nv_total = 0;
+  int kc = 0, vc = 0;
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
+    const hqkv_tier_t& s = c->tier[t];
+    TierDev& d = P.tier[t];
+    HQKV_REQUIRE(s.n_k >= 0 && s.n_v >= 0, "decode: negative tier size");
+    d.bits = expect_bits[t];
+    d.n_k = s.n_k;
+    d.n_v = s.n_v;
+    if (s.n_k > 0 || s.n_v > 0) {
+      HQKV_REQUIRE(s.bits == expect_bits[t], "decode: tier %d must hold %d-bit data (got %d)", t, expect_bits[t], s.bits);
+      if (s.bits == 1) return fail(HQKV_E_UNSUPPORTED, "decode: the 1-bit tier is not built in the fused decode");
+    }
+    if (s.n_k > 0) {
+      HQKV_REQUIRE(s.k_data && s.k_idx, "decode: tier %d K pointers are null", t);
+      if (s.bits < 16) {
+        HQKV_REQUIRE(s.k_scale && s.k_zero, "decode: tier %d K scale/zero pointers are null", t);
+        HQKV_REQUIRE(s.n_k % c->group_k == 0, "decode: tier %d K holds %d tokens, not a multiple of the K group %d", t,
+                     s.n_k, c->group_k);
+        HQKV_REQUIRE(aligned(s.k_data, 8), "decode: tier %d K codes must be 8-byte aligned", t);
+      } else {
+        HQKV_REQUIRE(s.n_k % 8 == 0 && aligned(s.k_data, 16),
+                     "decode: the fp16 K tier needs a token count that is a multiple of 8 and 16-byte alignment");
+      }
+    }
+    if (s.n_v > 0) {
+      HQKV_REQUIRE(s.v_data && s.v_idx, "decode: tier %d V pointers are null", t);
+      if (s.bits < 16) HQKV_REQUIRE(s.v_scale && s.v_zero, "decode: tier %d V scale/zero pointers are null", t);
+      HQKV_REQUIRE(aligned(s.v_data, 16), "decode: tier %d V data must be 16-byte aligned", t);
+    }
+    d.k_data = s.k_data;
+    d.k_scale = static_cast<const __half*>(s.k_scale);
+    d.k_zero = static_cast<const __half*>(s.k_zero);
+    d.k_idx = s.k_idx;
+    d.v_data = s.v_data;
+    d.v_scale = static_cast<const __half*>(s.v_scale);
+    d.v_zero = static_cast<const __half*>(s.v_zero);
+    d.v_idx = s.v_idx;
+    // chunk sizes: about the same number of bytes per CTA whatever the width
+    const int b = d.bits;
+    d.k_chunk_tokens = b == 16 ? 512 : b == 8 ? 512 : b == 4 ? 512 : 1024;
+    if ((d.k_chunk_tokens >> P.gk_shift) > MAX_K_GROUPS) d.k_chunk_tokens = MAX_K_GROUPS << P.gk_shift;
+    d.v_chunk_tokens = b == 16 ? 256 : b == 8 ? 384 : b == 4 ? 640 : 1024;
+    d.k_chunk0 = kc;
+    d.v_chunk0 = vc;
+    kc += static_cast<int>(ceil_div(d.n_k, d.k_chunk_tokens));
+    vc += static_cast<int>(ceil_div(d.n_v, d.v_chunk_tokens));
+    nk_total += d.n_k;
+    nv_total += d.n_v;
+  }
+  HQKV_REQUIRE(nk_total == nv_total, "decode: K side holds %lld quantised tokens, V side %lld", (long long)nk_total,
+               (long long)nv_total);
+  TierDev& r = P.tier[HQKV_NUM_TIERS];
+  r.bits = 16;
+  r.n_k = r.n_v = c->n_new;
+  if (c->n_new > 0) {
+    HQKV_REQUIRE(c->new_k && c->new_v, "decode: residual pointers are null");
+    HQKV_REQUIRE(aligned(c->new_k, 16) && aligned(c->new_v, 16), "decode: residual must be 16-byte aligned");
+  }
+  r.k_data = c->new_k;
+  r.v_data = c->new_v;
+  r.k_chunk_tokens = 128;
+  r.v_chunk_tokens = 128;
+  r.k_chunk0 = kc;
+  r.v_chunk0 = vc;
+  kc += static_cast<int>(ceil_div(r.n_k, r.k_chunk_tokens));
+  vc += static_cast<int>(ceil_div(r.n_v, r.v_chunk_tokens));
+  const int64_t L = nk_total + c->n_new;
+  HQKV_REQUIRE(L > 0, "decode: the cache is empty");
+  HQKV_REQUIRE(L < (1ll << 30), "decode: cache too long");
+  P.L = static_cast<int>(L);
+  P.nk_chunks = kc;
+  P.nv_chunks = vc;
+  P.w_slice = static_cast<int>(ceil_div(L, vc));
+  const int64_t BH = static_cast<int64_t>(c->B) * c->H;
+  lay.logits_off = HQKV_WS_COUNTER_BYTES;
+  size_t off = lay.logits_off + static_cast<size_t>(c->B) * c->nh_q * L * sizeof(float);
+  off = (off + 255) & ~static_cast<size_t>(255);
+  lay.kpart_off = off;
+  off += static_cast<size_t>(BH) * kc * MAX_REP * sizeof(float2);
+  off = (off + 255) & ~static_cast<size_t>(255);
+  lay.vpart_off = off;
+  off += static_cast<size_t>(BH) * vc * P.rep * D * sizeof(float);
+  lay.total = (off + 255) & ~static_cast<size_t>(255);
+  return HQKV_OK;
+}
+
+}  // namespace hqkv
+
+using namespace hqkv;
+
+extern "C" size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host) {
+  DecodeParams P;
+  Layout lay;
+  if (build_params(cache_host, P, lay) != HQKV_OK) return 0;
+  return lay.total;
+}
+
+extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                            void* attn_output, void* workspace, size_t workspace_bytes, int phases,
+                                            void* stream) {
+  HQKV_REQUIRE(phases >= 1 && phases <= 3, "decode: phases must be 1 (K pass), 2 (V pass) or 3 (both)");
+  DecodeParams P;
+  Layout lay;
+  int rc = build_params(cache_host, P, lay);
+  if (rc) return rc;
+  HQKV_REQUIRE(q && attn_weights && attn_output && workspace, "decode: null pointer");
+  HQKV_REQUIRE(aligned(q, 4), "decode: q must be 4-byte aligned");
+  HQKV_REQUIRE(aligned(workspace, 256), "decode: workspace must be 256-byte aligned");
+  if (workspace_bytes < lay.total)
+    return fail(HQKV_E_WORKSPACE, "decode: workspace holds %zu bytes, %zu needed", workspace_bytes, lay.total);
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  P.q = static_cast<const __half*>(q);
+  P.weights = static_cast<__half*>(attn_weights);
+  P.out = static_cast<__half*>(attn_output);
+  P.counters = reinterpret_cast<unsigned*>(ws);
+  P.logits = reinterpret_cast<float*>(ws + lay.logits_off);
+  P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
+  P.v_part = reinterpret_cast<float*>(ws + lay.vpart_off);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const dim3 block(NTHREADS);
+  const unsigned BH = static_cast<unsigned>(P.B * P.H);
+  HQKV_REQUIRE(BH <= 65535, "decode: B*H too large");
+  if (phases & 1) {
+    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, 0, st>>>(P);
+    HQKV_LAUNCH_CHECK("k_pass");
+  }
+  if (phases & 2) {
+    // opt in to >48 KB of dynamic shared memory once per device
+    static bool attr_set[64] = {};
+    int dev = 0;
+    HQKV_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      HQKV_CUDA(cudaFuncSetAttribute(v_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(sizeof(VShared))));
+      if (dev >= 0 && dev < 64) attr_set[dev] = true;
+    }
+    v_pass_kernel<<<dim3(P.nv_chunks, BH), block, sizeof(VShared), st>>>(P);
+    HQKV_LAUNCH_CHECK("v_pass");
+  }
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                     void* attn_output, void* workspace, size_t workspace_bytes, void* stream) {
+  return hqkv_decode_attention_phases(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, stream);
+}

@@ -1,0 +1,648 @@
+// Importance bookkeeping, block ranking and the flush (evict + tier-assign + re-quantise) on the
+// device (sm_100a).  Integer / fp16 elementwise work on at most a few hundred thousand tokens; the
+// quantity that matters is bit-exact agreement with the reference's torch op sequence, so every
+// floating-point reduction here runs in a fixed order with one fp32 accumulator.
+#include <string.h>
+
+#include "common.cuh"
+
+namespace hqkv {
+
+constexpr int D = 128;
+
+// ------------------------------------------------------------------------------------------------
+// importance ring
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) head_sum_kernel(const __half* __restrict__ w, int B, int nh, int64_t L,
+                                                       int64_t bh_stride, __half* __restrict__ out) {
+  const int64_t l = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  float over_heads = 0.f;
+  for (int h = 0; h < nh; ++h) {
+    float over_batch = 0.f;
+    for (int b = 0; b < B; ++b) over_batch = __fadd_rn(over_batch, __half2float(w[(static_cast<int64_t>(b) * nh + h) * bh_stride + l]));
+    over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch)));
+  }
+  out[l] = __float2half_rn(over_heads);
+}
+
+__global__ void __launch_bounds__(256) token_importance_kernel(const __half* __restrict__ ring, int rows,
+                                                               int64_t stride, int64_t L, __half* __restrict__ out) {
+  const int64_t l = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (l >= L) return;
+  float acc = 0.f;
+  for (int r = 0; r < rows; ++r) acc = __fadd_rn(acc, __half2float(ring[r * stride + l]));
+  const int64_t age = L - l;
+  const float count = static_cast<float>(age < rows ? age : rows);
+  out[l] = h_divf(__float2half_rn(acc), count);
+}
+
+// one warp per token: range over D channels per (b,h), summed over b then h
+__global__ void __launch_bounds__(128) token_range_kernel(const __half* __restrict__ v, int B, int H, int64_t T,
+                                                          int Dd, int64_t b_stride, int64_t h_stride,
+                                                          __half* __restrict__ out) {
+  const int lane = threadIdx.x & 31;
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  float over_heads = 0.f;
+  for (int h = 0; h < H; ++h) {
+    float over_batch = 0.f;
+    for (int b = 0; b < B; ++b) {
+      const __half* row = v + b * b_stride + h * h_stride + t * Dd;
+      __half lo = row[lane], hi = row[lane];
+      for (int d = lane + 32; d < Dd; d += 32) {
+        lo = h_min(lo, row[d]);
+        hi = h_max(hi, row[d]);
+      }
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) {
+        lo = h_min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+        hi = h_max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+      }
+      over_batch = __fadd_rn(over_batch, __half2float(h_sub(hi, lo)));
+    }
+    over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch)));
+  }
+  if (lane == 0) out[t] = __float2half_rn(over_heads);
+}
+
+// ------------------------------------------------------------------------------------------------
+// block ranking: one CTA, bitonic sort of (inverted key, block id) in shared memory
+// ------------------------------------------------------------------------------------------------
+constexpr int RANK_THREADS = 1024;
+constexpr int RANK_MAX_BLOCKS = 8192;
+
+__global__ void __launch_bounds__(RANK_THREADS) block_rank_kernel(__half* __restrict__ importance,
+                                                                  const __half* __restrict__ range, int block,
+                                                                  int nblocks, int npow2,
+                                                                  int64_t* __restrict__ sorted_ids) {
+  extern __shared__ uint32_t keys[];  // npow2 entries
+  const int64_t total = static_cast<int64_t>(nblocks) * block;
+  const float fblock = static_cast<float>(block);
+  // elementwise: optional product with the range, then the in-place divide
+  for (int64_t i = threadIdx.x; i < total; i += RANK_THREADS) {
+    __half x = importance[i];
+    if (range) x = h_mul(x, range[i]);
+    importance[i] = h_divf(x, fblock);
+  }
+  __syncthreads();
+  for (int k = threadIdx.x; k < npow2; k += RANK_THREADS) {
+    uint32_t composite = 0xFFFFFFFFu;
+    if (k < nblocks) {
+      float acc = 0.f;
+      const __half* p = importance + static_cast<int64_t>(k) * block;
+      for (int i = 0; i < block; ++i) acc = __fadd_rn(acc, __half2float(p[i]));
+      const __half key = __float2half_rn(acc);
+      uint16_t bits = __half_as_ushort(key);
+      if ((bits & 0x7FFFu) == 0) bits = 0;                                  // -0 sorts like +0
+      const uint16_t asc = (bits & 0x8000u) ? static_cast<uint16_t>(~bits) : static_cast<uint16_t>(bits | 0x8000u);
+      const uint16_t desc = static_cast<uint16_t>(0xFFFFu - asc);           // larger key first
+      composite = (static_cast<uint32_t>(desc) << 16) | static_cast<uint32_t>(k);  // ties: lower id first
+    }
+    keys[k] = composite;
+  }
+  __syncthreads();
+  for (int size = 2; size <= npow2; size <<= 1) {
+    for (int stride = size >> 1; stride > 0; stride >>= 1) {
+      for (int i = threadIdx.x; i < (npow2 >> 1); i += RANK_THREADS) {
+        const int lo = 2 * i - (i & (stride - 1));  // index with the `stride` bit clear
+        const int hi = lo + stride;
+        const bool up = (lo & size) == 0;
+        const uint32_t a = keys[lo], b = keys[hi];
+        if ((a > b) == up) {
+          keys[lo] = b;
+          keys[hi] = a;
+        }
+      }
+      __syncthreads();
+    }
+  }
+  for (int64_t i = threadIdx.x; i < total; i += RANK_THREADS) {
+    const int j = static_cast<int>(i / block);
+    const int64_t blk = keys[j] & 0xFFFFu;
+    sorted_ids[i] = blk * block + (i - static_cast<int64_t>(j) * block);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// flush plan: single CTA
+// ------------------------------------------------------------------------------------------------
+constexpr int PLAN_THREADS = 1024;
+
+struct PlanArgs {
+  const int64_t* tier_idx[HQKV_NUM_TIERS];
+  int32_t tier_n[HQKV_NUM_TIERS];
+  int64_t hist, compress;
+  int64_t cum[6];
+  const int64_t* sorted_ids;
+  int32_t* plan_src;   // [5][total]
+  int64_t* plan_ids;   // [5][total]
+  int64_t* survivors;  // [total]
+  int32_t* counts;     // [8]
+  // scratch, each [total]
+  int8_t* tgt;         // by token id
+  int8_t* fin;         // by enumeration slot
+  int32_t* rank;       // by token id: rank among survivors
+};
+
+// block-wide exclusive scan of one flag per thread; returns the exclusive prefix and the block total
+__device__ __forceinline__ int block_scan_flag(bool flag, int& total, int* warp_sums) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
+  const int within = __popc(ballot & ((1u << lane) - 1u));
+  if (lane == 0) warp_sums[warp] = __popc(ballot);
+  __syncthreads();
+  int before = 0, tot = 0;
+  for (int w = 0; w < PLAN_THREADS / 32; ++w) {
+    const int s = warp_sums[w];
+    if (w < warp) before += s;
+    tot += s;
+  }
+  __syncthreads();
+  total = tot;
+  return before + within;
+}
+
+// Enumeration order of every cached token: residual (ascending id), then the 16-, 8-, 4-, 2-, 1-bit
+// tier in storage order.  Slot -> (source tier, position, token id).
+__device__ __forceinline__ void enum_slot(const PlanArgs& A, int64_t slot, int& src, int64_t& pos, int64_t& id) {
+  if (slot < A.compress) {
+    src = -1;
+    pos = slot;
+    id = A.hist + slot;
+    return;
+  }
+  int64_t s = slot - A.compress;
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
+    if (s < A.tier_n[t]) {
+      src = t;
+      pos = s;
+      id = A.tier_idx[t][s];
+      return;
+    }
+    s -= A.tier_n[t];
+  }
+  src = -2;
+  pos = 0;
+  id = 0;
+}
+
+__global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_constant__ PlanArgs A) {
+  __shared__ int warp_sums[PLAN_THREADS / 32];
+  __shared__ int running;
+  __shared__ int any_evict;
+  const int64_t total = A.hist + A.compress;
+  const int tid = threadIdx.x;
+  if (tid == 0) any_evict = 0;
+  // 1. targets by token id
+  for (int64_t i = tid; i < total; i += PLAN_THREADS) A.tgt[i] = -1;
+  __syncthreads();
+  for (int64_t j = tid; j < total; j += PLAN_THREADS) {
+    int t = -1;
+#pragma unroll
+    for (int k = 5; k >= 0; --k)
+      if (j < A.cum[k] && j >= (k ? A.cum[k - 1] : 0)) t = k;
+    if (t >= 0) {
+      A.tgt[A.sorted_ids[j]] = static_cast<int8_t>(t);
+      if (t == 5) any_evict = 1;
+    }
+  }
+  __syncthreads();
+  // 2. final tier of every enumeration slot: 0..4 tier, 5 evicted, 6 dropped (residual without target)
+  for (int64_t s = tid; s < total; s += PLAN_THREADS) {
+    int src;
+    int64_t pos, id;
+    enum_slot(A, s, src, pos, id);
+    const int tg = A.tgt[id];
+    int f;
+    if (tg == 5) f = 5;
+    else if (src < 0) f = tg < 0 ? 6 : tg;
+    else f = tg > src ? tg : src;  // only moves to fewer bits (larger index); tg == -1 stays
+    A.fin[s] = static_cast<int8_t>(f);
+  }
+  __syncthreads();
+  // 3. survivor ranks by token id (token ids are a permutation of 0..total-1 over the enumeration)
+  //    first mark survival by id in `rank`, then exclusive-scan it in place
+  for (int64_t s = tid; s < total; s += PLAN_THREADS) {
+    int src;
+    int64_t pos, id;
+    enum_slot(A, s, src, pos, id);
+    A.rank[id] = (A.tgt[id] != 5) ? 1 : 0;
+  }
+  __syncthreads();
+  if (tid == 0) running = 0;
+  __syncthreads();
+  for (int64_t base = 0; base < total; base += PLAN_THREADS) {
+    const int64_t i = base + tid;
+    const bool flag = i < total && A.rank[i] != 0;
+    int tot;
+    const int ex = block_scan_flag(flag, tot, warp_sums);
+    const int r = running + ex;
+    if (i < total) A.rank[i] = r;
+    if (flag) A.survivors[r] = i;
+    __syncthreads();
+    if (tid == 0) running += tot;
+    __syncthreads();
+  }
+  if (tid == 0) A.counts[5] = running;
+  __syncthreads();
+  // 4. destination lists: kept members of tier t first, then arrivals in enumeration order
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
+    if (tid == 0) running = 0;
+    __syncthreads();
+    int64_t tier_first = A.compress;
+    for (int k = 0; k < t; ++k) tier_first += A.tier_n[k];
+    for (int pass = 0; pass < 2; ++pass) {
+      // pass 0: slots of tier t itself; pass 1: every slot that is not of tier t
+      const int64_t lo = pass == 0 ? tier_first : 0;
+      const int64_t hi = pass == 0 ? tier_first + A.tier_n[t] : total;
+      for (int64_t base = lo; base < hi; base += PLAN_THREADS) {
+        const int64_t s = base + tid;
+        bool flag = false;
+        int src = 0;
+        int64_t pos = 0, id = 0;
+        if (s < hi) {
+          enum_slot(A, s, src, pos, id);
+          flag = A.fin[s] == t && (pass == 0 || src != t);
+        }
+        int tot;
+        const int ex = block_scan_flag(flag, tot, warp_sums);
+        if (flag) {
+          const int64_t j = running + ex;
+          A.plan_src[t * total + j] = ((src + 1) << 28) | static_cast<int32_t>(pos);
+          A.plan_ids[t * total + j] = any_evict ? static_cast<int64_t>(A.rank[id]) : id;
+        }
+        __syncthreads();
+        if (tid == 0) running += tot;
+        __syncthreads();
+      }
+    }
+    if (tid == 0) A.counts[t] = running;
+    __syncthreads();
+  }
+  if (tid == 0) {
+    A.counts[6] = any_evict;
+    A.counts[7] = 0;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// flush build
+// ------------------------------------------------------------------------------------------------
+struct BuildArgs {
+  const void* data[HQKV_NUM_TIERS];
+  const __half* scale[HQKV_NUM_TIERS];
+  const __half* zero[HQKV_NUM_TIERS];
+  int32_t n[HQKV_NUM_TIERS];
+  const __half* residual;
+  int64_t res_b_stride, res_h_stride;
+  int B, H, group, gshift, dst_tier, dst_bits;
+  const int32_t* plan;  // [n_dst]
+  int64_t n_dst;
+  void* out_data;
+  __half* out_scale;
+  __half* out_zero;
+};
+
+__device__ __forceinline__ int tier_bits(int t) { return 16 >> t; }  // 16, 8, 4, 2, 1
+
+// K side: one CTA per (destination group of `group` tokens, batch*head); one thread per channel.
+// The tokens of a destination group come from one source and are consecutive there (tiers are
+// filled and emptied in whole blocks).
+__device__ __forceinline__ __half k_src_value(const BuildArgs& A, int src, int64_t pos, int b, int h, int d) {
+  const int64_t bh = static_cast<int64_t>(b) * A.H + h;
+  if (src < 0) return A.residual[b * A.res_b_stride + h * A.res_h_stride + pos * D + d];
+  const int64_t n = A.n[src];
+  if (src == 0) return reinterpret_cast<const __half*>(A.data[0])[(bh * D + d) * n + pos];
+  const int bits = tier_bits(src), fpi = 32 / bits;
+  const uint32_t word = reinterpret_cast<const uint32_t*>(A.data[src])[(bh * D + d) * (n / fpi) + pos / fpi];
+  const uint32_t code = (word >> ((pos % fpi) * bits)) & ((1u << bits) - 1u);
+  const int64_t G = n >> A.gshift;
+  const int64_t gi = (bh * D + d) * G + (pos >> A.gshift);
+  return dequant_2r(code, A.scale[src][gi], A.zero[src][gi]);
+}
+
+__global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant__ BuildArgs A) {
+  const int64_t jg = blockIdx.x;  // destination group
+  const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
+  const int d = threadIdx.x;
+  const int32_t enc = A.plan[jg * A.group];
+  const int src = (enc >> 28) - 1;
+  const int64_t pos0 = enc & 0x0FFFFFFF;
+  const int bits = A.dst_bits;
+  const int64_t row = static_cast<int64_t>(bh) * D + d;
+  if (bits == 16) {
+    __half* dst = reinterpret_cast<__half*>(A.out_data) + row * A.n_dst + jg * A.group;
+    for (int i = 0; i < A.group; ++i) dst[i] = k_src_value(A, src, pos0 + i, b, h, d);
+    return;
+  }
+  const int fpi = 32 / bits, wpg = A.group / fpi;
+  const int64_t Wd = A.n_dst / fpi, Gd = A.n_dst >> A.gshift;
+  uint32_t* dst = reinterpret_cast<uint32_t*>(A.out_data) + row * Wd + jg * wpg;
+  if (src == A.dst_tier) {  // kept block: copy words, scale, zero
+    const int64_t n = A.n[src];
+    const uint32_t* s = reinterpret_cast<const uint32_t*>(A.data[src]) + row * (n / fpi) + pos0 / fpi;
+    for (int w = 0; w < wpg; ++w) dst[w] = s[w];
+    const int64_t gi = row * (n >> A.gshift) + (pos0 >> A.gshift);
+    A.out_scale[row * Gd + jg] = A.scale[src][gi];
+    A.out_zero[row * Gd + jg] = A.zero[src][gi];
+    return;
+  }
+  const float levels = static_cast<float>((1 << bits) - 1);
+  __half lo = k_src_value(A, src, pos0, b, h, d), hi = lo;
+  for (int i = 1; i < A.group; ++i) {
+    const __half v = k_src_value(A, src, pos0 + i, b, h, d);
+    lo = h_min(lo, v);
+    hi = h_max(hi, v);
+  }
+  const __half sc = quant_scale(lo, hi, levels);
+  for (int w = 0; w < wpg; ++w) {
+    uint32_t word = 0;
+    for (int i = 0; i < fpi; ++i)
+      word |= quant_code(k_src_value(A, src, pos0 + w * fpi + i, b, h, d), lo, sc, levels) << (i * bits);
+    dst[w] = word;
+  }
+  A.out_scale[row * Gd + jg] = sc;
+  A.out_zero[row * Gd + jg] = lo;
+}
+
+// V side: one warp per (destination token, batch*head); a lane owns 4 consecutive channels.
+__global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constant__ BuildArgs A) {
+  const int lane = threadIdx.x & 31;
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
+  if (j >= A.n_dst) return;  // whole warp leaves together
+  const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
+  const int32_t enc = A.plan[j];
+  const int src = (enc >> 28) - 1;
+  const int64_t pos = enc & 0x0FFFFFFF;
+  const int bits = A.dst_bits;
+  const int ng = D >> A.gshift;
+  const int c0 = lane * 4;
+  // ---- source values of this lane's 4 channels
+  __half v[4];
+  if (src < 0) {
+    const __half* r = A.residual + b * A.res_b_stride + h * A.res_h_stride + pos * D + c0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = r[i];
+  } else if (src == 0) {
+    const __half* r = reinterpret_cast<const __half*>(A.data[0]) + (static_cast<int64_t>(bh) * A.n[0] + pos) * D + c0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = r[i];
+  } else {
+    const int sb = tier_bits(src), fpi = 32 / sb;
+    const int64_t trow = static_cast<int64_t>(bh) * A.n[src] + pos;
+    const uint32_t* words = reinterpret_cast<const uint32_t*>(A.data[src]) + trow * (D / fpi);
+    if (src == A.dst_tier) {  // kept token: copy the row verbatim
+      uint32_t* dw = reinterpret_cast<uint32_t*>(A.out_data) + (static_cast<int64_t>(bh) * A.n_dst + j) * (D / fpi);
+      for (int w = lane; w < D / fpi; w += 32) dw[w] = words[w];
+      if (lane < ng) {
+        A.out_scale[(static_cast<int64_t>(bh) * A.n_dst + j) * ng + lane] = A.scale[src][trow * ng + lane];
+        A.out_zero[(static_cast<int64_t>(bh) * A.n_dst + j) * ng + lane] = A.zero[src][trow * ng + lane];
+      }
+      return;
+    }
+    const __half sc = A.scale[src][trow * ng + (c0 >> A.gshift)];
+    const __half z = A.zero[src][trow * ng + (c0 >> A.gshift)];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int c = c0 + i;
+      const uint32_t code = (words[c / fpi] >> ((c % fpi) * sb)) & ((1u << sb) - 1u);
+      v[i] = dequant_2r(code, sc, z);
+    }
+  }
+  if (bits == 16) {
+    __half* dst = reinterpret_cast<__half*>(A.out_data) + (static_cast<int64_t>(bh) * A.n_dst + j) * D + c0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) dst[i] = v[i];
+    return;
+  }
+  // ---- quantise groups of `group` channels = group/4 adjacent lanes
+  const float levels = static_cast<float>((1 << bits) - 1);
+  __half lo = v[0], hi = v[0];
+#pragma unroll
+  for (int i = 1; i < 4; ++i) {
+    lo = h_min(lo, v[i]);
+    hi = h_max(hi, v[i]);
+  }
+  for (int off = 1; off < (A.group >> 2); off <<= 1) {
+    lo = h_min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+    hi = h_max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+  }
+  const __half sc = quant_scale(lo, hi, levels);
+  uint32_t part = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) part |= quant_code(v[i], lo, sc, levels) << (i * bits);
+  const int lpw = 32 / (4 * bits);  // lanes per word: 1, 2, 4, 8 for 8, 4, 2, 1 bits
+  for (int off = 1; off < lpw; off <<= 1) {
+    const uint32_t other = __shfl_down_sync(0xffffffffu, part, off);
+    part |= other << (4 * bits * off);
+  }
+  const int fpi = 32 / bits;
+  uint32_t* dw = reinterpret_cast<uint32_t*>(A.out_data) + (static_cast<int64_t>(bh) * A.n_dst + j) * (D / fpi);
+  if (lane % lpw == 0) dw[lane / lpw] = part;
+  if ((c0 & (A.group - 1)) == 0) {
+    A.out_scale[(static_cast<int64_t>(bh) * A.n_dst + j) * ng + (c0 >> A.gshift)] = sc;
+    A.out_zero[(static_cast<int64_t>(bh) * A.n_dst + j) * ng + (c0 >> A.gshift)] = lo;
+  }
+}
+
+__global__ void __launch_bounds__(256) gather_columns_kernel(const __half* __restrict__ in, int64_t in_stride,
+                                                             const int64_t* __restrict__ ids, int64_t n,
+                                                             __half* __restrict__ out, int64_t out_stride) {
+  const int64_t j = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (j >= n) return;
+  const int r = blockIdx.y;
+  out[r * out_stride + j] = in[r * in_stride + ids[j]];
+}
+
+static int ilog2(int v) {
+  int s = 0;
+  while ((1 << s) < v) ++s;
+  return s;
+}
+
+static int fill_build_args(BuildArgs& A, const hqkv_flush_src_t* src, int B, int H, int Dd, int group, int dst_tier,
+                           const int32_t* plan, int64_t n_dst, void* out_data, void* out_scale, void* out_zero,
+                           const char* who) {
+  HQKV_REQUIRE(src != nullptr, "%s: null source descriptor", who);
+  HQKV_REQUIRE(Dd == D, "%s: head dim must be 128", who);
+  HQKV_REQUIRE(B > 0 && H > 0 && static_cast<int64_t>(B) * H <= 65535, "%s: bad B/H", who);
+  HQKV_REQUIRE(valid_group(group), "%s: group must be 32, 64 or 128", who);
+  HQKV_REQUIRE(dst_tier >= 0 && dst_tier < HQKV_NUM_TIERS, "%s: dst_tier out of range", who);
+  HQKV_REQUIRE(n_dst >= 0, "%s: negative n_dst", who);
+  memset(&A, 0, sizeof(A));
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
+    A.data[t] = src->data[t];
+    A.scale[t] = static_cast<const __half*>(src->scale[t]);
+    A.zero[t] = static_cast<const __half*>(src->zero[t]);
+    A.n[t] = src->n[t];
+  }
+  A.residual = static_cast<const __half*>(src->residual);
+  A.res_b_stride = src->residual_b_stride;
+  A.res_h_stride = src->residual_h_stride;
+  A.B = B;
+  A.H = H;
+  A.group = group;
+  A.gshift = ilog2(group);
+  A.dst_tier = dst_tier;
+  A.dst_bits = 16 >> dst_tier;
+  A.plan = plan;
+  A.n_dst = n_dst;
+  A.out_data = out_data;
+  A.out_scale = static_cast<__half*>(out_scale);
+  A.out_zero = static_cast<__half*>(out_zero);
+  if (n_dst > 0) {
+    HQKV_REQUIRE(plan && out_data, "%s: null pointer", who);
+    HQKV_REQUIRE(dst_tier == 0 || (out_scale && out_zero), "%s: null scale/zero output", who);
+  }
+  return HQKV_OK;
+}
+
+}  // namespace hqkv
+
+using namespace hqkv;
+
+extern "C" int hqkv_head_sum(const void* w, int B, int nh, int64_t L, int64_t bh_stride, void* out, void* stream) {
+  HQKV_REQUIRE(B > 0 && nh > 0 && L >= 0 && bh_stride >= L, "head_sum: bad sizes");
+  if (L == 0) return HQKV_OK;
+  HQKV_REQUIRE(w && out, "head_sum: null pointer");
+  head_sum_kernel<<<static_cast<unsigned>(ceil_div(L, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(w), B, nh, L, bh_stride, static_cast<__half*>(out));
+  HQKV_LAUNCH_CHECK("head_sum");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_token_importance(const void* ring, int rows, int64_t ring_stride, int64_t L, void* out,
+                                     void* stream) {
+  HQKV_REQUIRE(rows > 0 && L >= 0 && ring_stride >= L, "token_importance: bad sizes");
+  if (L == 0) return HQKV_OK;
+  HQKV_REQUIRE(ring && out, "token_importance: null pointer");
+  token_importance_kernel<<<static_cast<unsigned>(ceil_div(L, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(ring), rows, ring_stride, L, static_cast<__half*>(out));
+  HQKV_LAUNCH_CHECK("token_importance");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_token_range(const void* v, int B, int H, int64_t T, int Dd, int64_t b_stride, int64_t h_stride,
+                                void* out, void* stream) {
+  HQKV_REQUIRE(B > 0 && H > 0 && T >= 0 && Dd >= 32, "token_range: bad sizes");
+  if (T == 0) return HQKV_OK;
+  HQKV_REQUIRE(v && out, "token_range: null pointer");
+  token_range_kernel<<<static_cast<unsigned>(ceil_div(T, 4)), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(v), B, H, T, Dd, b_stride, h_stride, static_cast<__half*>(out));
+  HQKV_LAUNCH_CHECK("token_range");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_block_rank(void* importance, const void* range_or_null, int block, int nblocks,
+                               int64_t* sorted_ids, void* stream) {
+  HQKV_REQUIRE(block > 0 && nblocks >= 0, "block_rank: bad sizes");
+  HQKV_REQUIRE(nblocks <= RANK_MAX_BLOCKS, "block_rank: at most %d blocks (got %d)", RANK_MAX_BLOCKS, nblocks);
+  if (nblocks == 0) return HQKV_OK;
+  HQKV_REQUIRE(importance && sorted_ids, "block_rank: null pointer");
+  int npow2 = 2;
+  while (npow2 < nblocks) npow2 <<= 1;
+  block_rank_kernel<<<1, RANK_THREADS, npow2 * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half*>(importance), static_cast<const __half*>(range_or_null), block, nblocks, npow2, sorted_ids);
+  HQKV_LAUNCH_CHECK("block_rank");
+  return HQKV_OK;
+}
+
+extern "C" size_t hqkv_flush_plan_workspace_bytes(int64_t total) {
+  if (total < 0) return 0;
+  const size_t t = static_cast<size_t>(total);
+  // tgt (1 B) + fin (1 B) + rank (4 B) per token, each region rounded to 256 bytes
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  return up(t) + up(t) + up(4 * t) + 256;
+}
+
+extern "C" int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_t* tier_n_host, int64_t hist,
+                               int64_t compress, const int64_t* sorted_ids, const int64_t* cum_counts_host,
+                               int32_t* plan_src, int64_t* plan_ids, int64_t* survivors, int32_t* counts,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+  HQKV_REQUIRE(tier_idx_host && tier_n_host && cum_counts_host, "flush_plan: null host pointer");
+  HQKV_REQUIRE(hist >= 0 && compress >= 0, "flush_plan: negative length");
+  const int64_t total = hist + compress;
+  HQKV_REQUIRE(total > 0 && total < (1ll << 28), "flush_plan: total length out of range");
+  HQKV_REQUIRE(sorted_ids && plan_src && plan_ids && survivors && counts && workspace, "flush_plan: null pointer");
+  int64_t in_tiers = 0;
+  PlanArgs A;
+  memset(&A, 0, sizeof(A));
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
+    HQKV_REQUIRE(tier_n_host[t] >= 0, "flush_plan: negative tier size");
+    HQKV_REQUIRE(tier_n_host[t] == 0 || tier_idx_host[t], "flush_plan: tier %d has tokens but no id list", t);
+    A.tier_idx[t] = tier_idx_host[t];
+    A.tier_n[t] = tier_n_host[t];
+    in_tiers += tier_n_host[t];
+  }
+  HQKV_REQUIRE(in_tiers == hist, "flush_plan: tiers hold %lld tokens but history_length is %lld", (long long)in_tiers,
+               (long long)hist);
+  int64_t prev = 0;
+  for (int k = 0; k < 6; ++k) {
+    HQKV_REQUIRE(cum_counts_host[k] >= prev && cum_counts_host[k] <= total,
+                 "flush_plan: cumulative counts must be non-decreasing and at most hist+compress");
+    A.cum[k] = cum_counts_host[k];
+    prev = cum_counts_host[k];
+  }
+  const size_t need = hqkv_flush_plan_workspace_bytes(total);
+  if (workspace_bytes < need)
+    return fail(HQKV_E_WORKSPACE, "flush_plan: workspace holds %zu bytes, %zu needed", workspace_bytes, need);
+  auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
+  unsigned char* ws = static_cast<unsigned char*>(workspace);
+  A.tgt = reinterpret_cast<int8_t*>(ws);
+  A.fin = reinterpret_cast<int8_t*>(ws + up(total));
+  A.rank = reinterpret_cast<int32_t*>(ws + 2 * up(total));
+  A.hist = hist;
+  A.compress = compress;
+  A.sorted_ids = sorted_ids;
+  A.plan_src = plan_src;
+  A.plan_ids = plan_ids;
+  A.survivors = survivors;
+  A.counts = counts;
+  flush_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(A);
+  HQKV_LAUNCH_CHECK("flush_plan");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_flush_build_k(const hqkv_flush_src_t* src_host, int B, int H, int Dd, int group, int dst_tier,
+                                  const int32_t* plan_src_row, int64_t n_dst, void* out_data, void* out_scale,
+                                  void* out_zero, void* stream) {
+  BuildArgs A;
+  int rc = fill_build_args(A, src_host, B, H, Dd, group, dst_tier, plan_src_row, n_dst, out_data, out_scale, out_zero,
+                           "flush_build_k");
+  if (rc) return rc;
+  if (n_dst == 0) return HQKV_OK;
+  HQKV_REQUIRE(n_dst % group == 0, "flush_build_k: n_dst (%lld) is not a multiple of the group %d", (long long)n_dst,
+               group);
+  flush_build_k_kernel<<<dim3(static_cast<unsigned>(n_dst / group), B * H), D, 0,
+                         static_cast<cudaStream_t>(stream)>>>(A);
+  HQKV_LAUNCH_CHECK("flush_build_k");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_flush_build_v(const hqkv_flush_src_t* src_host, int B, int H, int Dd, int group, int dst_tier,
+                                  const int32_t* plan_src_row, int64_t n_dst, void* out_data, void* out_scale,
+                                  void* out_zero, void* stream) {
+  BuildArgs A;
+  int rc = fill_build_args(A, src_host, B, H, Dd, group, dst_tier, plan_src_row, n_dst, out_data, out_scale, out_zero,
+                           "flush_build_v");
+  if (rc) return rc;
+  if (n_dst == 0) return HQKV_OK;
+  flush_build_v_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst, 4)), B * H), 128, 0,
+                         static_cast<cudaStream_t>(stream)>>>(A);
+  HQKV_LAUNCH_CHECK("flush_build_v");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_gather_columns_f16(const void* in, int64_t in_stride, int rows, const int64_t* ids, int64_t n,
+                                       void* out, int64_t out_stride, void* stream) {
+  HQKV_REQUIRE(rows >= 0 && n >= 0, "gather_columns: negative size");
+  if (rows == 0 || n == 0) return HQKV_OK;
+  HQKV_REQUIRE(in && ids && out, "gather_columns: null pointer");
+  HQKV_REQUIRE(rows <= 65535, "gather_columns: too many rows");
+  gather_columns_kernel<<<dim3(static_cast<unsigned>(ceil_div(n, 256)), rows), 256, 0,
+                          static_cast<cudaStream_t>(stream)>>>(static_cast<const __half*>(in), in_stride, ids, n,
+                                                               static_cast<__half*>(out), out_stride);
+  HQKV_LAUNCH_CHECK("gather_columns");
+  return HQKV_OK;
+}

@@ -1,0 +1,113 @@
+"""Slot map of the 42-entry ``past_key_value`` tuple and its translation into the C descriptors.
+
+Slot order (fixed by every unpack site of the reference, e.g. quant/hqe_matmul.py:364-368):
+  0-3    sixteen_K, sixteen_K_idx, sixteen_V, sixteen_V_idx
+  4-11   eight_K, _idx, _scale_std, _mn_mean, eight_V, _idx, _scale_std, _mn_mean
+  12-19  four_*      20-27  two_*      28-35  one_*
+  36,37  outliers, outliers_idx (unused)      38 V_token_norm
+  39,40  new_K, new_V (fp16 residual window)  41 kv_seq_len (python int)
+"""
+import ctypes as C
+
+import torch
+
+from .._lib import CacheDesc, FlushSrc, TIER_BITS, ptr
+
+NUM_SLOTS = 42
+SLOT_K = {16: 0, 8: 4, 4: 12, 2: 20, 1: 28}
+SLOT_V = {16: 2, 8: 8, 4: 16, 2: 24, 1: 32}
+SLOT_V_TOKEN_NORM = 38
+SLOT_NEW_K = 39
+SLOT_NEW_V = 40
+SLOT_SEQ_LEN = 41
+
+UNIFORM_STRATEGIES = ("uniform_group", "high_uniform_group_low_normal_group")
+
+
+def _c(t):
+    """Contiguous version of a tensor (None passes through)."""
+    return None if t is None else (t if t.is_contiguous() else t.contiguous())
+
+
+def tier_tensors(cache, bits, side):
+    """(data, idx, scale, zero) of one tier side; scale/zero are None for the fp16 tier."""
+    s = (SLOT_K if side == "K" else SLOT_V)[bits]
+    if bits == 16:
+        return cache[s], cache[s + 1], None, None
+    return cache[s], cache[s + 1], cache[s + 2], cache[s + 3]
+
+
+def cache_geometry(cache):
+    """(B, nh_kv, head_dim, n_quantised_tokens, residual_len, device) read off the V payloads the way
+    qkv_matmul_hqe_2 does (quant/hqe_matmul.py:379-404)."""
+    B = H = D = dev = None
+    n = 0
+    for bits in TIER_BITS:
+        v = cache[SLOT_V[bits]]
+        if v is not None:
+            B, H = v.shape[0], v.shape[1]
+            n += v.shape[2]
+            D = v.shape[3] * (1 if bits == 16 else 32 // bits)
+            dev = v.device
+    r = 0
+    if cache[SLOT_NEW_V] is not None:
+        B, H, r, D = cache[SLOT_NEW_V].shape
+        dev = cache[SLOT_NEW_V].device
+    if n + r == 0:
+        raise ValueError("invalid past_key_value")
+    return B, H, D, n, r, dev
+
+
+def build_cache_desc(cache, nh_q, block_size, group_size):
+    """Fill a CacheDesc for hqkv_decode_attention.  Returns (desc, keepalive, L)."""
+    B, H, D, n, r, dev = cache_geometry(cache)
+    desc = CacheDesc()
+    desc.B, desc.H, desc.nh_q, desc.D = B, H, nh_q, D
+    desc.group_k, desc.group_v = block_size, group_size
+    desc.softmax_scale = 1.0 / (D ** 0.5)
+    keep = []
+    n_k_total = 0
+    for t, bits in enumerate(TIER_BITS):
+        kd, ki, ks, kz = (_c(x) for x in tier_tensors(cache, bits, "K"))
+        vd, vi, vs, vz = (_c(x) for x in tier_tensors(cache, bits, "V"))
+        keep += [kd, ki, ks, kz, vd, vi, vs, vz]
+        tier = desc.tier[t]
+        tier.bits = bits
+        tier.n_k = 0 if ki is None else ki.numel()
+        tier.n_v = 0 if vi is None else vi.numel()
+        n_k_total += tier.n_k
+        for name, x in (("k_data", kd), ("k_scale", ks), ("k_zero", kz), ("k_idx", ki),
+                        ("v_data", vd), ("v_scale", vs), ("v_zero", vz), ("v_idx", vi)):
+            setattr(tier, name, ptr(x))
+        for idx in (ki, vi):
+            if idx is not None and idx.dtype != torch.int64:
+                raise ValueError("tier index lists must be int64")
+    nk, nv = _c(cache[SLOT_NEW_K]), _c(cache[SLOT_NEW_V])
+    keep += [nk, nv]
+    desc.n_new = r
+    desc.new_k, desc.new_v = ptr(nk), ptr(nv)
+    return desc, keep, n_k_total + r, dev
+
+
+def build_flush_src(cache, side, residual):
+    src = FlushSrc()
+    keep = []
+    for t, bits in enumerate(TIER_BITS):
+        d, i, s, z = (_c(x) for x in tier_tensors(cache, bits, side))
+        keep += [d, s, z]
+        src.data[t], src.scale[t], src.zero[t] = ptr(d), ptr(s), ptr(z)
+        src.n[t] = 0 if i is None else i.numel()
+    if residual is not None:
+        if residual.stride(3) != 1 or residual.stride(2) != residual.shape[3]:
+            residual = residual.contiguous()
+        keep.append(residual)
+        src.residual = ptr(residual)
+        src.residual_b_stride, src.residual_h_stride = residual.stride(0), residual.stride(1)
+    return src, keep
+
+
+def void_p_array(tensors):
+    arr = (C.c_void_p * len(tensors))()
+    for i, t in enumerate(tensors):
+        arr[i] = ptr(t)
+    return arr

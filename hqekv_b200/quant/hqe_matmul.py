@@ -1,0 +1,65 @@
+"""Decode attention over the tiered cache — same name, arguments, results and errors as
+qkv_matmul_hqe_2 in the reference's quant/hqe_matmul.py:354-451, in one call into libhqkv
+(hqekv_b200/csrc/decode.cu) instead of up to a dozen per-tier GEMV launches with index scatter /
+gather copies between them.
+"""
+from typing import Tuple
+
+import torch
+
+from .._lib import HqkvError, check, decode_workspace, lib, ptr, require_cuda, stream_ptr
+from ._cache import UNIFORM_STRATEGIES, build_cache_desc
+
+
+def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: torch.Tensor, head_dim: int,
+                     quant_strategy: str, block_size: int = 32, group_size: int = 32):
+    """softmax(q K^T / sqrt(d)) V over all tiers and the fp16 residual window.
+
+    q [B, nh_q, 1, D] float16; ``past_key_value`` the 42-slot tuple.  ``attention_mask`` is accepted
+    and ignored, as on the reference path (its use is commented out at quant/hqe_matmul.py:431);
+    ``head_dim`` is re-derived from the cache as the reference does (:379-404).
+    Returns (attn_weights [B, nh_q, 1, L] float16, attn_output [B, nh_q, 1, D] float16).
+    Raises ValueError('invalid quant_strategy') / ValueError('invalid past_key_value') like the
+    reference.  A non-empty 1-bit tier raises NotImplementedError (not built).
+    """
+    if quant_strategy not in UNIFORM_STRATEGIES:
+        raise ValueError("invalid quant_strategy")
+    if len(past_key_value) != 42:
+        raise ValueError("invalid past_key_value")
+    require_cuda(q)
+    if q.dtype != torch.float16 or q.dim() != 4 or q.shape[2] != 1:
+        raise ValueError("q must be float16 of shape [B, nh_q, 1, head_dim]")
+    desc, keep, L, dev = build_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+    if dev != q.device or q.shape[0] != desc.B or q.shape[3] != desc.D:
+        raise ValueError("q does not match the cache (device, batch or head_dim)")
+    q = q.contiguous()
+    B, nh_q, D = q.shape[0], q.shape[1], q.shape[3]
+    attn_weights = torch.empty(B, nh_q, 1, L, dtype=torch.float16, device=dev)
+    attn_output = torch.empty(B, nh_q, 1, D, dtype=torch.float16, device=dev)
+    with torch.cuda.device(dev):
+        need = lib.hqkv_decode_workspace_bytes(desc)
+        if need == 0:
+            _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), None, 0,
+                                                         None))
+        ws = decode_workspace(dev, need)
+        _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), ptr(ws),
+                                                     ws.numel(), stream_ptr(dev)))
+    return attn_weights, attn_output
+
+
+def _raise_from_status(rc):
+    if rc == -2:
+        raise NotImplementedError(lib.hqkv_last_error().decode())
+    check(rc)
+
+
+def _not_built(name):
+    def f(*args, **kwargs):
+        raise NotImplementedError(f"{name}: this cache layout variant of the reference is not built in hqekv_b200; "
+                                  "use qkv_matmul_hqe_2")
+    f.__name__ = name
+    return f
+
+
+qkv_matmul_hqe = _not_built("qkv_matmul_hqe")
+qkv_matmul_hqe_1 = _not_built("qkv_matmul_hqe_1")

@@ -1,0 +1,127 @@
+"""Seeded synthetic workloads with the shapes and value distributions of the benchmark configurations
+(decode attention over a Llama-3.1-8B / Qwen3-8B shaped cache).  Real prompts and model weights are
+not available offline; these stand in for them.  Used by bench.py, the smoke test and the GPU tests.
+"""
+import math
+from dataclasses import dataclass
+
+import torch
+
+from .model.public_func import get_block_token_idx, make_sum_equal
+from .quant.hqe_2 import KV_cache_hqe_2
+
+
+@dataclass
+class CacheConfig:
+    name: str
+    batch: int
+    nh_q: int
+    nh_kv: int
+    head_dim: int
+    context: int          # tokens seen before the decode step
+    residual: int         # fp16 residual window kept after the flush
+    ratios: tuple         # share of the SURVIVING quantised tokens in the 8-, 4-, 2-bit tiers
+    evict: float          # share of the flushed tokens that is evicted
+    group: int            # K block / group size and V group size
+    k_outliers: bool      # 4 random K channels per head scaled x10
+    layers: int = 1
+
+
+CONFIGS = {
+    # single layer, CPU-checkable
+    "cfg0": CacheConfig("cfg0-llama-1layer-4k", 1, 32, 8, 128, 4096, 128, (0.25, 0.50, 0.25), 0.10, 32, True, 1),
+    # Llama-3.1-8B decode at 32k context (the configuration the headline metric is quoted on)
+    "cfg1": CacheConfig("cfg1-llama3.1-8b-32k", 1, 32, 8, 128, 32768, 128, (0.20, 0.40, 0.40), 0.10, 32, False, 32),
+    # Qwen3-8B, batch 8, 16k, group 64, no eviction
+    "cfg2": CacheConfig("cfg2-qwen3-8b-b8-16k", 8, 32, 8, 128, 16384, 128, (0.25, 0.50, 0.25), 0.0, 64, True, 36),
+    # long-context sizing, heads sharded over 8 GPUs
+    "cfg3": CacheConfig("cfg3-llama3.1-8b-b4-128k", 4, 32, 8, 128, 131072, 256, (0.10, 0.25, 0.65), 0.30, 32, False, 32),
+}
+
+
+def tier_counts(cfg: CacheConfig):
+    """Six token counts (16, 8, 4, 2, 1 bit, evicted), multiples of the block size, for one flush of
+    everything but the residual window.  Eviction takes round(evict * blocks) blocks; the survivors
+    split by ``ratios`` with the rounding surplus taken off the lowest tier first."""
+    block = cfg.group
+    flushed = cfg.context - cfg.residual
+    assert flushed % block == 0, "context - residual must be a multiple of the block size"
+    nblocks = flushed // block
+    ev = int(round(nblocks * cfg.evict))
+    keep = nblocks - ev
+    raw = torch.tensor([0, round(keep * cfg.ratios[0]), round(keep * cfg.ratios[1]), round(keep * cfg.ratios[2]), 0],
+                       dtype=torch.int32)
+    raw = make_sum_equal(raw, keep, start_idx=3)
+    counts = [int(v) * block for v in raw.tolist()] + [ev * block]
+    assert sum(counts) == flushed
+    return counts
+
+
+def make_kv(cfg: CacheConfig, device, seed: int, heads=None):
+    """K, V [B, H, context, D] fp16 ~ N(0,1) (K with 4 outlier channels per head x10 if configured) and
+    q [B, nh_q_local, 1, D].  ``heads`` = (first kv head, number of kv heads) restricts to a head shard;
+    the values of a head do not depend on the shard it is generated in."""
+    h0, nh = heads if heads is not None else (0, cfg.nh_kv)
+    rep = cfg.nh_q // cfg.nh_kv
+    K = torch.empty(cfg.batch, nh, cfg.context, cfg.head_dim, dtype=torch.float16, device=device)
+    V = torch.empty_like(K)
+    q = torch.empty(cfg.batch, nh * rep, 1, cfg.head_dim, dtype=torch.float16, device=device)
+    for i in range(nh):
+        gen = torch.Generator(device=device)
+        gen.manual_seed(seed * 1000003 + (h0 + i))
+        k = torch.randn(cfg.batch, cfg.context, cfg.head_dim, generator=gen, device=device)
+        v = torch.randn(cfg.batch, cfg.context, cfg.head_dim, generator=gen, device=device)
+        qq = torch.randn(cfg.batch, rep, 1, cfg.head_dim, generator=gen, device=device)
+        if cfg.k_outliers:
+            ch = torch.randperm(cfg.head_dim, generator=gen, device=device)[:4]
+            k[:, :, ch] *= 10
+        K[:, i], V[:, i] = k.half(), v.half()
+        q[:, i * rep:(i + 1) * rep] = qq.half()
+    return K, V, q
+
+
+def synthetic_importance(cfg: CacheConfig, device, seed: int, length: int):
+    """Token importance of ``length`` tokens: mean of 8 random softmax rows with the peakedness of real
+    attention, as fp16 (the same on every rank: it depends on the seed only)."""
+    gen = torch.Generator(device=device)
+    gen.manual_seed(seed * 7919 + 17)
+    logits = torch.randn(8, length, generator=gen, device=device) * 2.0
+    return torch.softmax(logits, dim=-1).sum(0).div_(8).half()
+
+
+def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range: bool = False):
+    """Prefill-shaped K/V -> one flush through KV_cache_hqe_2 -> (cache tuple, q).  With
+    ``times_range=False`` K and V are ranked identically, so every rank of a head-sharded run selects
+    the same blocks without exchanging value ranges."""
+    K, V, q = make_kv(cfg, device, seed, heads)
+    flushed = cfg.context - cfg.residual
+    counts = tier_counts(cfg)
+    imp = synthetic_importance(cfg, device, seed, flushed)
+    ids = get_block_token_idx(cfg.group, flushed // cfg.group, imp)
+    cache = (None,) * 39 + (K, V, cfg.context)
+    bit_num = torch.tensor(counts, dtype=torch.int32)
+    cache = KV_cache_hqe_2(cache, flushed, 0, ids, bit_num, bit_num.clone(), imp, "uniform_group", None, cfg.group,
+                           cfg.group, times_range)
+    return cache, q
+
+
+def cache_bytes(cache, nh_q: int):
+    """Algorithmic bytes one decode step reads from this cache: packed codes, scales, zeros and the
+    fp16 payloads of K and V of every tier plus the residual window (index lists and the probability
+    row are not counted)."""
+    total = 0
+    for i, item in enumerate(cache[:36]):
+        if item is None or not torch.is_tensor(item):
+            continue
+        if item.dtype == torch.int64:      # index lists
+            continue
+        total += item.numel() * item.element_size()
+    for i in (39, 40):
+        if cache[i] is not None:
+            total += cache[i].numel() * cache[i].element_size()
+    return total
+
+
+def logical_length(cache):
+    n = sum(cache[s].numel() for s in (1, 5, 13, 21, 29) if cache[s] is not None)
+    return n + (cache[39].shape[2] if cache[39] is not None else 0)

@@ -1,0 +1,261 @@
+/*
+ * hqkv.h — C ABI of libhqkv, the sm_100a implementation of the hybrid mixed-precision
+ * KV-cache decode path (evict / tier-assign, group quantise + bit-pack, fused decode
+ * attention over the packed tiers, residual flush).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host;
+ *   - fp16 data is IEEE binary16 (`__half`), packed codes are int32 words with element i of a
+ *     word at bits [i*bits, (i+1)*bits), index lists are int64;
+ *   - `stream` is a cudaStream_t passed as void*; all work is enqueued on it and no entry
+ *     point synchronises unless its comment says so;
+ *   - every function returns 0 on success or a negative HQKV_E_* code; the text of the last
+ *     failure on the calling thread is available from hqkv_last_error();
+ *   - nothing here allocates device memory unless its comment says so: scratch is passed in.
+ *
+ * Each entry point names the interface of the reference project (skywclouds/HqeKV, paths
+ * relative to its root) that it stands in for.
+ */
+#ifndef HQKV_H
+#define HQKV_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HQKV_OK 0
+#define HQKV_E_INVALID (-1)     /* bad argument (shape, bits, group size, alignment, null pointer) */
+#define HQKV_E_UNSUPPORTED (-2) /* valid in the reference but not built here (e.g. 1-bit tier in the fused decode) */
+#define HQKV_E_WORKSPACE (-3)   /* scratch buffer too small */
+#define HQKV_E_CUDA (-4)        /* a CUDA runtime call failed */
+
+/* Text of the last error raised on this thread ("" if none). Never NULL. */
+const char* hqkv_last_error(void);
+
+/* Library version: major*10000 + minor*100 + patch. */
+int hqkv_version(void);
+
+/* ---------------------------------------------------------------------------------------------
+ * Codec
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * Asymmetric uniform group quantisation + bit-packing along the LAST logical axis of a
+ * [rows, T] fp16 matrix.  Stands in for uniform_group_quantize_pack_last_dim
+ * (quant/pack_unpack.py:156-193) together with the Triton kernel _pack_along_last_dim
+ * (quant/pack_unpack.py:16-51).  Arithmetic: fp16 with a rounding after every step, exactly
+ * as the torch op sequence there (min, max, sub, div, sub_, div_, clamp_, round_).
+ *
+ * The source element (row, t) lives at  x[(row / inner) * outer_stride + (row % inner) * inner_stride + t * t_stride]
+ * (strides in elements).  Two access patterns are built:
+ *   t_stride == 1                      rows contiguous along T (V: one row per token, T = head_dim);
+ *   inner_stride == 1, t_stride >= inner  K: token-major source [outer, T, inner] read as [outer*inner, T]
+ *                                       (the transposed view the reference quantises, without materialising it).
+ * Outputs are dense: code int32 [rows, T*bits/32], scale and mn fp16 [rows, T/group].
+ * bits in {8,4,2,1}; group in {32,64,128}; T a multiple of group.
+ * The source is NOT modified (the reference overwrites it with intermediate values).
+ */
+int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, int64_t outer_stride,
+                       int64_t inner_stride, int64_t t_stride, int group, int bits, void* code, void* scale,
+                       void* mn, void* stream);
+
+/*
+ * Inverse: unpack + dequantise, x = half(half(code * scale) + mn)   (two fp16 roundings).
+ * Stands in for uniform_group_dequantize_unpack_last_dim (quant/pack_unpack.py:316-333) and the
+ * Triton kernel _unpack_along_last_dim (:255-278).  code int32 [rows, T*bits/32] dense,
+ * scale/mn fp16 [rows, T/group] dense, out fp16 [rows, T] dense.
+ */
+int hqkv_dequantize_unpack(const void* code, const void* scale, const void* mn, int64_t rows, int64_t T, int group,
+                           int bits, void* out, void* stream);
+
+/* pack_along_last_dim (quant/pack_unpack.py:53-70): int32 codes [rows, T] -> int32 words [rows, T*bits/32]. */
+int hqkv_pack(const void* codes_i32, int64_t rows, int64_t T, int bits, void* words, void* stream);
+
+/* unpack_along_last_dim (quant/pack_unpack.py:281-297): int32 words [rows, W] -> fp16 integers [rows, W*32/bits]. */
+int hqkv_unpack(const void* words, int64_t rows, int64_t W, int bits, void* out_f16, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Decode attention over the tiered cache
+ * ------------------------------------------------------------------------------------------- */
+
+#define HQKV_NUM_TIERS 5 /* 16-, 8-, 4-, 2-, 1-bit, in the slot order of the reference's cache tuple */
+
+/* One precision tier of the cache (slots 0-35 of the 42-entry tuple, quant/hqe_matmul.py:364-368). */
+typedef struct {
+  int32_t bits; /* 16, 8, 4, 2 or 1 */
+  int32_t n_k;  /* tokens held on the K side (0 = tier absent) */
+  int32_t n_v;  /* tokens held on the V side */
+  int32_t pad_;
+  const void* k_data;   /* bits<16: int32 [B,H,D,n_k*bits/32]; bits==16: fp16 [B,H,D,n_k]  (channel-major) */
+  const void* k_scale;  /* fp16 [B,H,D,n_k/group_k]   (NULL when bits==16) */
+  const void* k_zero;   /* fp16 [B,H,D,n_k/group_k] */
+  const int64_t* k_idx; /* [n_k] logical position of every K token */
+  const void* v_data;   /* bits<16: int32 [B,H,n_v,D*bits/32]; bits==16: fp16 [B,H,n_v,D]  (token-major) */
+  const void* v_scale;  /* fp16 [B,H,n_v,D/group_v] */
+  const void* v_zero;   /* fp16 [B,H,n_v,D/group_v] */
+  const int64_t* v_idx; /* [n_v] logical position of every V token */
+} hqkv_tier_t;
+
+typedef struct {
+  int32_t B;        /* batch */
+  int32_t H;        /* kv heads */
+  int32_t nh_q;     /* query heads, a multiple of H with nh_q/H <= 8 */
+  int32_t D;        /* head dim, must be 128 */
+  int32_t group_k;  /* tokens per K group (the reference passes block_size): 32, 64 or 128 */
+  int32_t group_v;  /* channels per V group: 32, 64 or 128 */
+  int32_t n_new;    /* tokens in the fp16 residual window (may be 0) */
+  float softmax_scale; /* multiplies q.k before the softmax: 1/sqrt(head_dim) */
+  const void* new_k;   /* fp16 [B,H,n_new,D] token-major; logical positions are the last n_new */
+  const void* new_v;   /* fp16 [B,H,n_new,D] */
+  hqkv_tier_t tier[HQKV_NUM_TIERS];
+} hqkv_cache_desc_t;
+
+/* Bytes of scratch hqkv_decode_attention needs for this cache (0 on invalid input). */
+size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
+
+/*
+ * One decode step of attention over the whole tiered cache: q.K^T for every tier with the
+ * packed codes dequantised in registers, softmax in fp32, p.V for every tier, plus the fp16
+ * residual window and the fp16 tier, in two kernel launches.  Stands in for qkv_matmul_hqe_2
+ * (quant/hqe_matmul.py:354-451) and everything below it: the layout glue of
+ * cuda_bmm_fA_qB_uniform_group (quant/matmul.py:263-299), gemv_forward_cuda_uniform_group and
+ * bgemv_kernel_uniform_group_{8,4,2} (quant/csrc/gemv_cuda_uniform.cu:1533-1599, 411-733), the
+ * torch.matmul calls on the fp16 tier and the residual, and the softmax block (:430-433).
+ *
+ *   q            fp16 [B, nh_q, 1, D]
+ *   attn_weights fp16 [B, nh_q, 1, L]   L = sum_t n_k + n_new; normalised probabilities at logical positions
+ *   attn_output  fp16 [B, nh_q, 1, D]
+ *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Its first
+ *                HQKV_WS_COUNTER_BYTES bytes hold arrival counters that must be zero before the
+ *                first call; every call leaves them zero again.  Calls that share a workspace
+ *                must be ordered on one stream.
+ * The K-side and V-side token counts of a tier may differ only in order, not in total
+ * (sum n_k == sum n_v); the 1-bit tier is not built (HQKV_E_UNSUPPORTED if non-empty).
+ */
+#define HQKV_WS_COUNTER_BYTES 4096
+int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * The same call restricted to one of its two launches: phases = 1 runs the K pass only (logits and
+ * per-CTA softmax statistics into the workspace), 2 the V pass only (needs the workspace a K pass
+ * of the same cache left), 3 both.  A measurement aid for timing the two kernels separately; it has
+ * no counterpart in the reference.
+ */
+int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                 void* attn_output, void* workspace, size_t workspace_bytes, int phases, void* stream);
+
+/*
+ * Batched GEMV  C = fA x dequant(qB)  with the reference's un-transposed operand layout, fp32
+ * accumulation, fp16 result.  Stands in for cuda_bmm_fA_qB_uniform_group (quant/matmul.py:263-299)
+ * = transposes + kvhq_gemv.gemv_forward_cuda_uniform_group (quant/csrc/pybind.cpp:11,
+ * quant/csrc/gemv_cuda_uniform.cu:1533-1599), without the transposed copies.
+ *   fA fp16 [B, nh_q, 1, K];  qB int32 [B, nh_kv, K, N*bits/32];  scales/zeros fp16 [B, nh_kv, K, N/group]
+ *   out fp16 [B, nh_q, 1, N].   bits in {8,4,2}; group in {32,64,128}; N a multiple of group.
+ * Both uses of the reference are covered: K = head_dim, N = tokens (q.K^T of one tier) and
+ * K = tokens, N = head_dim (p.V of one tier).
+ */
+int hqkv_gemv_uniform_group(const void* fA, const void* qB, const void* scales, const void* zeros, int B, int nh_q,
+                            int nh_kv, int64_t K, int64_t N, int group, int bits, void* out, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Importance bookkeeping and block ranking
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * Row the importance ring stores for one query row: out[l] = half(sum_h half(sum_b w[b,h,l])),
+ * fp32 accumulation in index order.  Stands in for ``attn_weights.sum(0).sum(0)`` in
+ * last_attn_weights.update (model/public_func.py:243-257).  Row (b,h) of w starts at
+ * w + (b*nh + h)*bh_stride (elements) and holds L fp16 values; out fp16 [L].  For a decode step
+ * (w dense [B, nh, 1, L]) bh_stride = L; for one row r of a prefill block [B, nh, q_len, L] pass
+ * w + r*L and bh_stride = q_len*L.
+ */
+int hqkv_head_sum(const void* w, int B, int nh, int64_t L, int64_t bh_stride, void* out, void* stream);
+
+/*
+ * importance[l] = half( half(sum_r ring[r,l]) / min(last_len, L - l) ) — calculate_token_importance
+ * (model/public_func.py:217-221).  ring fp16 [rows, ring_stride]; out fp16 [L].
+ */
+int hqkv_token_importance(const void* ring, int rows, int64_t ring_stride, int64_t L, void* out, void* stream);
+
+/*
+ * Per-token value range summed over batch and heads: calculate_token_range (model/public_func.py:58-73).
+ * v fp16 [B, H, T, D] with token stride D and the given batch/head strides (elements); out fp16 [T].
+ */
+int hqkv_token_range(const void* v, int B, int H, int64_t T, int D, int64_t b_stride, int64_t h_stride, void* out,
+                     void* stream);
+
+/*
+ * Block ranking: get_block_token_idx (model/public_func.py:92-106).  Divides importance[0 .. nblocks*block)
+ * by `block` IN PLACE (as the reference does to its argument), forms each block's fp16 key, orders blocks by
+ * descending key with ties broken by ascending block id, and writes the expanded int64 token ids.
+ * If range_or_null is given, importance is first multiplied by it elementwise in fp16 into `importance`
+ * (the V-side key of quant/hqe_2.py:515).  nblocks <= 8192.
+ */
+int hqkv_block_rank(void* importance, const void* range_or_null, int block, int nblocks, int64_t* sorted_ids,
+                    void* stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Flush: evict + tier-assign + re-quantise  (KV_cache_hqe_2, quant/hqe_2.py:456-843)
+ * ------------------------------------------------------------------------------------------- */
+
+/*
+ * Phase 1 — plan one side (K or V) of a flush on the device.
+ *
+ * Inputs: the id list of every tier (tier_idx[t], length tier_n[t], NULL if empty), the ranked ids
+ * (sorted_ids, hist+compress entries) and the six cumulative tier counts (cum_counts_host: 16,8,4,2,1-bit,
+ * evict).  A token moves only to a tier of strictly fewer bits than it has now; residual tokens always take
+ * their target (the ladder of quant/hqe_2.py:584-659 / :737-825).
+ *
+ * Outputs (device, sized for total = hist+compress tokens):
+ *   plan_src   int32 [5][total]   for destination tier t, entry j: source of the j-th token, encoded as
+ *                                 (source_tier+1)<<28 | position in that source (source_tier -1 = residual)
+ *   plan_ids   int64 [5][total]   final idx list of every tier (already re-ranked if anything was evicted)
+ *   survivors  int64 [total]      ascending ids of the tokens that are not evicted
+ *   counts     int32 [8]          final size of the five tiers, number of survivors, 0, 0
+ * The caller reads `counts` back (one small copy) to size the new tier tensors.
+ */
+int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_t* tier_n_host, int64_t hist, int64_t compress,
+                    const int64_t* sorted_ids, const int64_t* cum_counts_host, int32_t* plan_src, int64_t* plan_ids,
+                    int64_t* survivors, int32_t* counts, void* workspace, size_t workspace_bytes, void* stream);
+size_t hqkv_flush_plan_workspace_bytes(int64_t total);
+
+/* Source tensors of one side for phase 2 (same layouts as hqkv_tier_t; index 0..4 = 16,8,4,2,1-bit). */
+typedef struct {
+  const void* data[HQKV_NUM_TIERS];
+  const void* scale[HQKV_NUM_TIERS];
+  const void* zero[HQKV_NUM_TIERS];
+  int32_t n[HQKV_NUM_TIERS];
+  int32_t pad_;
+  const void* residual; /* fp16 [B,H,r,D] token-major, first `compress` tokens are flushed */
+  int64_t residual_b_stride, residual_h_stride; /* elements */
+} hqkv_flush_src_t;
+
+/*
+ * Phase 2 — build destination tier `dst_tier` of the K side from the plan: kept blocks are copied,
+ * arrivals are dequantised (two-rounding recipe) if they were quantised, then re-quantised at the
+ * destination width in groups of `group` tokens per channel (K_high_2_low / quant_new_K,
+ * quant/hqe_2.py:16-42, 88-130).  n_dst = counts[dst_tier] from phase 1; outputs dense
+ * [B,H,D,n_dst*bits/32] / [B,H,D,n_dst/group] (fp16 [B,H,D,n_dst] for the 16-bit tier).
+ */
+int hqkv_flush_build_k(const hqkv_flush_src_t* src_host, int B, int H, int D, int group, int dst_tier,
+                       const int32_t* plan_src_row, int64_t n_dst, void* out_data, void* out_scale, void* out_zero,
+                       void* stream);
+/* Same for the V side, groups of `group` channels per token (V_high_2_low, quant/hqe_2.py:132-170). */
+int hqkv_flush_build_v(const hqkv_flush_src_t* src_host, int B, int H, int D, int group, int dst_tier,
+                       const int32_t* plan_src_row, int64_t n_dst, void* out_data, void* out_scale, void* out_zero,
+                       void* stream);
+
+/* out[r, j] = in[r, ids[j]] for fp16 rows — compaction of V_token_norm and of the importance ring to the
+ * survivors (quant/hqe_2.py:733-735, last_attn_weights.eviction model/public_func.py:228-231).
+ * in/out may not overlap. */
+int hqkv_gather_columns_f16(const void* in, int64_t in_stride, int rows, const int64_t* ids, int64_t n, void* out,
+                            int64_t out_stride, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HQKV_H */

@@ -469,14 +469,44 @@ def reconstruct(cache: tuple, block_size: int = 32, group_size: int = 32):
     return K, V
 
 
+def reconstruct_fp32(cache: tuple, block_size: int = 32, group_size: int = 32):
+    """Dense fp32 K and V with the dequantisation the reference's GEMV kernels do in registers:
+    w = scale * code + zero evaluated in fp32 from the fp16 scale and zero, no fp16 rounding
+    (quant/csrc/gemv_cuda_uniform.cu:465-467)."""
+    B, H, D, n, r = cache_dims(cache)
+    L = n + r
+    K = np.zeros((B, H, L, D), dtype=F32)
+    V = np.zeros((B, H, L, D), dtype=F32)
+
+    def deq(words, scale, zero, group, bits):
+        codes = _f(unpack_last_dim(words, bits))
+        lead, T = codes.shape[:-1], codes.shape[-1]
+        cg = codes.reshape(*lead, T // group, group)
+        return (cg * _f(scale)[..., None] + _f(zero)[..., None]).astype(F32).reshape(*lead, T)
+
+    for bits in TIER_BITS:
+        k, v = SLOT_K[bits], SLOT_V[bits]
+        if cache[k] is not None:
+            dense = _f(cache[k]) if bits == 16 else deq(cache[k], cache[k + 2], cache[k + 3], block_size, bits)
+            K[:, :, cache[k + 1], :] = np.swapaxes(dense, 2, 3)
+        if cache[v] is not None:
+            dense = _f(cache[v]) if bits == 16 else deq(cache[v], cache[v + 2], cache[v + 3], group_size, bits)
+            V[:, :, cache[v + 1], :] = dense
+    if r:
+        K[:, :, L - r:, :] = _f(cache[SLOT_NEW_K])
+        V[:, :, L - r:, :] = _f(cache[SLOT_NEW_V])
+    return K, V
+
+
 def decode_attention(q: np.ndarray, cache: tuple, head_dim: int | None = None, block_size: int = 32,
-                     group_size: int = 32):
-    """fp32-accumulated dequant-matmul decode attention: softmax(q K^T / sqrt(d)) V over the
-    reconstructed cache, everything after the dequantisation in fp32.  This is the reference
-    quantity that qkv_matmul_hqe_2 (quant/hqe_matmul.py:354-451) approximates with fp16
-    intermediates.  q [B, nh_q, 1, D] fp16.  Returns (weights fp32 [B,nh_q,1,L], out fp32
-    [B,nh_q,1,D])."""
-    K, V = reconstruct(cache, block_size, group_size)
+                     group_size: int = 32, dequant: str = "fp32"):
+    """fp32-accumulated dequant-matmul decode attention: softmax(q K^T / sqrt(d)) V, everything in
+    fp32.  This is the quantity qkv_matmul_hqe_2 (quant/hqe_matmul.py:354-451) approximates with
+    fp16 intermediates.  ``dequant='fp32'`` dequantises as the reference's CUDA kernels do
+    (:func:`reconstruct_fp32`); ``'fp16'`` uses the dense fp16 reconstruction of
+    KV_cache_reconstruct_hqe (:func:`reconstruct`).  q [B, nh_q, 1, D] fp16.
+    Returns (weights fp32 [B,nh_q,1,L], out fp32 [B,nh_q,1,D])."""
+    K, V = (reconstruct_fp32 if dequant == "fp32" else reconstruct)(cache, block_size, group_size)
     B, H, L, D = K.shape
     nh_q = q.shape[1]
     rep = nh_q // H

@@ -1,0 +1,130 @@
+"""CPU-only checks: the C-ABI library loads and exports every symbol include/hqkv.h declares, argument
+validation works without a GPU (it runs before any CUDA call), the host-side logic (tuple slot map,
+tier counts, error conventions) behaves like the reference's, and nothing falls back to a CPU path."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from hqekv_b200 import build
+    build.build()
+    from hqekv_b200 import _lib
+    return _lib
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "hqkv.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(hqkv_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(lib):
+    names = declared_symbols()
+    assert len(names) >= 18
+    raw = ctypes.CDLL(lib.LIB_PATH)
+    for name in names:
+        assert hasattr(raw, name), f"{name} is declared in include/hqkv.h but not exported"
+    assert set(names) == set(lib.EXPORTED_SYMBOLS), "ctypes signature table and header disagree"
+    assert lib.lib.hqkv_version() >= 100
+
+
+def test_argument_validation_needs_no_gpu(lib):
+    L = lib.lib
+    assert L.hqkv_quantize_pack(None, 4, 32, 4, 32, 32, 1, 32, 3, None, None, None, None) == -1
+    assert b"bits" in L.hqkv_last_error()
+    assert L.hqkv_quantize_pack(None, 4, 48, 4, 48, 48, 1, 32, 4, None, None, None, None) == -1
+    assert b"multiple of the group" in L.hqkv_last_error()
+    assert L.hqkv_quantize_pack(None, 0, 32, 1, 32, 32, 1, 32, 4, None, None, None, None) == 0   # empty input
+    assert L.hqkv_gemv_uniform_group(None, None, None, None, 1, 4, 3, 128, 128, 32, 4, None, None) == -1
+    assert L.hqkv_block_rank(None, None, 32, 9000, None, None) == -1
+    assert L.hqkv_decode_workspace_bytes(None) == 0
+    desc = lib.CacheDesc()
+    desc.B, desc.H, desc.nh_q, desc.D, desc.group_k, desc.group_v = 1, 8, 32, 64, 32, 32
+    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -1
+    assert b"head dim" in L.hqkv_last_error()
+    desc.D = 128
+    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -1
+    assert b"empty" in L.hqkv_last_error()
+    desc.tier[4].bits, desc.tier[4].n_k, desc.tier[4].n_v = 1, 32, 32
+    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -2      # 1-bit tier: not built
+
+
+def test_workspace_size_of_the_benchmark_cache(lib):
+    """Llama-3.1-8B at 32k: 5888/11744/11744 tokens in the 8/4/2-bit tiers + 128 residual."""
+    desc = lib.CacheDesc()
+    desc.B, desc.H, desc.nh_q, desc.D, desc.group_k, desc.group_v, desc.n_new = 1, 8, 32, 128, 32, 32, 128
+    dummy = ctypes.c_void_p(256)
+    desc.new_k, desc.new_v = 256, 256
+    for t, n in ((1, 5888), (2, 11744), (3, 11744)):
+        tier = desc.tier[t]
+        tier.bits, tier.n_k, tier.n_v = (16, 8, 4, 2, 1)[t], n, n
+        for f in ("k_data", "k_scale", "k_zero", "k_idx", "v_data", "v_scale", "v_zero", "v_idx"):
+            setattr(tier, f, 256)
+    need = lib.lib.hqkv_decode_workspace_bytes(desc)
+    L = 5888 + 11744 * 2 + 128
+    assert need >= 4096 + 32 * L * 4
+    assert need < 16 << 20
+    del dummy
+
+
+def test_ops_refuse_cpu_tensors(lib):
+    from hqekv_b200.quant import hqe_matmul, pack_unpack
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        pack_unpack.uniform_group_quantize_pack_last_dim(torch.zeros(1, 1, 1, 32, dtype=torch.float16), 32, 4)
+    cache = (None,) * 39 + (torch.zeros(1, 1, 4, 128, dtype=torch.float16),) * 2 + (4,)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):
+        hqe_matmul.qkv_matmul_hqe_2(torch.zeros(1, 4, 1, 128, dtype=torch.float16), cache, None, 128, "uniform_group")
+
+
+def test_error_conventions_match_the_reference(lib):
+    from hqekv_b200.quant import hqe_2, hqe_matmul
+    q = torch.zeros(1, 4, 1, 128, dtype=torch.float16)
+    with pytest.raises(ValueError, match="invalid quant_strategy"):
+        hqe_matmul.qkv_matmul_hqe_2(q, (None,) * 42, None, 128, "nope")
+    with pytest.raises(ValueError, match="invalid quant_strategy"):
+        hqe_2.KV_cache_hqe_2((None,) * 42, 0, 0, None, None, None, None, "nope")
+    with pytest.raises(ValueError, match="invalid quant_strategy"):
+        hqe_2.KV_cache_reconstruct_hqe((None,) * 42, "nope")
+
+
+def test_reference_import_names(lib):
+    import hqekv_b200
+    hqekv_b200.install_reference_names()
+    import hqe_matmul
+    import quant.hqe_2
+    from model.public_func import get_block_token_idx, last_attn_weights  # noqa: F401
+    from pack_unpack import uniform_group_quantize_pack_last_dim  # noqa: F401
+    import kvhq_gemv
+    assert quant.hqe_2.KV_cache_hqe_2.__module__ == "hqekv_b200.quant.hqe_2"
+    assert hqe_matmul.qkv_matmul_hqe_2.__module__ == "hqekv_b200.quant.hqe_matmul"
+    assert callable(kvhq_gemv.gemv_forward_cuda_uniform_group)
+
+
+def test_tier_counts_of_the_configurations(lib):
+    from hqekv_b200 import synthetic
+    assert synthetic.tier_counts(synthetic.CONFIGS["cfg0"]) == [0, 896, 1792, 896, 0, 384]
+    assert synthetic.tier_counts(synthetic.CONFIGS["cfg1"]) == [0, 5888, 11744, 11744, 0, 3264]
+    c3 = synthetic.tier_counts(synthetic.CONFIGS["cfg3"])
+    assert c3 == [0, 286 * 32, 716 * 32, 1860 * 32, 0, 1226 * 32]
+    c2 = synthetic.tier_counts(synthetic.CONFIGS["cfg2"])
+    assert sum(c2) == 16384 - 128 and c2[5] == 0 and all(v % 64 == 0 for v in c2)
+
+
+def test_make_sum_equal_matches_oracle(lib):
+    from hqekv_b200.model.public_func import make_sum_equal
+    from oracle import hqkv_oracle as O
+    rng = np.random.default_rng(0)
+    for _ in range(50):
+        arr = rng.integers(0, 40, size=6)
+        target = int(arr.sum()) - int(rng.integers(0, 10))
+        a = make_sum_equal(torch.tensor(arr, dtype=torch.int32), target)
+        b = O.make_sum_equal(arr.copy(), target)
+        assert a.tolist() == b.tolist()

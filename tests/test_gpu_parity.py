@@ -1,0 +1,345 @@
+"""GPU parity tests: the CUDA path, called through the C ABI (ctypes -> libhqkv.so), against the numpy
+oracle and against the golden fixtures produced by the reference's own code.
+
+Bit-exact: packed words, fp16 scale/zero, dequantised values, ranked ids, importance, value ranges,
+every slot of a flushed cache.  Tolerance (stated where used): attention outputs within 2e-3 of the
+fp32-accumulated dequant-matmul oracle, relative to the largest output magnitude of the head.
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden_cache, load_golden
+from oracle import hqkv_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+ATTN_REL_TOL = 2e-3        # max |out - oracle| / max |oracle| per head
+# Probabilities are returned in fp16 (subnormal below 6.1e-5, quantum 2^-24) and the logits come from
+# K dequantised to fp16 for the tensor-core operand: with x10 outlier channels that is ~1e-3 rms on a
+# logit, i.e. on the relative value of a probability.  (The reference rounds the logits themselves to
+# fp16, which is an order of magnitude coarser.)
+WEIGHT_ABS_TOL = 2.0 ** -24
+WEIGHT_REL_TOL = 1e-2
+
+
+def dev_cache(cache_np, device):
+    out = []
+    for i, item in enumerate(cache_np):
+        if item is None or i == 41:
+            out.append(item)
+        else:
+            out.append(torch.from_numpy(np.ascontiguousarray(item)).to(device))
+    return tuple(out)
+
+
+def host_cache(cache_t):
+    return tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in cache_t)
+
+
+def bits_equal(a, b, what):
+    if a is None or b is None:
+        assert a is None and b is None, f"{what}: one side is None"
+        return
+    a = a.cpu().numpy() if torch.is_tensor(a) else np.asarray(a)
+    b = b.cpu().numpy() if torch.is_tensor(b) else np.asarray(b)
+    assert a.shape == b.shape, f"{what}: shape {a.shape} vs {b.shape}"
+    assert a.dtype == b.dtype, f"{what}: dtype {a.dtype} vs {b.dtype}"
+    if a.dtype == np.float16:
+        a, b = a.view(np.uint16), b.view(np.uint16)
+    bad = np.argwhere(a != b)
+    assert bad.size == 0, f"{what}: {len(bad)} mismatches, first at {bad[0].tolist()}: {a[tuple(bad[0])]} vs {b[tuple(bad[0])]}"
+
+
+@pytest.fixture(scope="module")
+def ops(cuda_device):
+    from hqekv_b200.model import public_func
+    from hqekv_b200.quant import hqe_2, hqe_matmul, matmul, pack_unpack
+    import types
+    return types.SimpleNamespace(pu=pack_unpack, pf=public_func, hqe_2=hqe_2, hm=hqe_matmul, mm=matmul)
+
+
+# ---------------------------------------------------------------------------------------------
+# codec
+# ---------------------------------------------------------------------------------------------
+def test_codec_golden(ops, cuda_device):
+    z = load_golden("codec")
+    for n in range(int(z["count"])):
+        bit, g, klike = (int(v) for v in z[f"c{n}_meta"])
+        x = torch.from_numpy(z[f"c{n}_x"]).to(cuda_device)
+        if klike:  # feed the transposed view of a token-major tensor, as the flush does for K
+            x = x.transpose(2, 3).contiguous().transpose(2, 3)
+        keep = x.clone()
+        code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(x, g, bit)
+        assert torch.equal(x, keep), "quantiser modified its input"
+        bits_equal(code, z[f"c{n}_code"], f"case {n} code (bit {bit} g {g} klike {klike})")
+        bits_equal(scale, z[f"c{n}_scale"], f"case {n} scale")
+        bits_equal(mn, z[f"c{n}_mn"], f"case {n} mn")
+        deq = ops.pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, g, bit)
+        bits_equal(deq, z[f"c{n}_deq"], f"case {n} dequantised")
+
+
+@pytest.mark.parametrize("bit", [8, 4, 2, 1])
+@pytest.mark.parametrize("group", [32, 64, 128])
+def test_codec_random_vs_oracle(ops, cuda_device, bit, group):
+    rng = np.random.default_rng(100 * bit + group)
+    # row path, unaligned rows included (T = 3 groups), and the column (K) path
+    x = (rng.standard_normal((2, 3, 7, 3 * group)) * 3).astype(np.float16)
+    xt = torch.from_numpy(x).to(cuda_device)
+    code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(xt, group, bit)
+    oc, os_, om = O.quantize_pack_last_dim(x, group, bit)
+    bits_equal(code, oc, "row path code")
+    bits_equal(scale, os_, "row path scale")
+    bits_equal(mn, om, "row path mn")
+    k = (rng.standard_normal((2, 2, 2 * group, 128)) * np.where(rng.random(128) < 0.05, 10, 1)).astype(np.float16)
+    kt = torch.from_numpy(k).to(cuda_device).transpose(2, 3)
+    code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(kt, group, bit)
+    oc, os_, om = O.quantize_pack_last_dim(np.ascontiguousarray(np.swapaxes(k, 2, 3)), group, bit)
+    bits_equal(code, oc, "column path code")
+    bits_equal(scale, os_, "column path scale")
+    bits_equal(mn, om, "column path mn")
+    deq = ops.pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, group, bit)
+    bits_equal(deq, O.dequantize_unpack_last_dim(oc, os_, om, group, bit), "dequantised")
+
+
+def test_codec_constant_group_and_roundtrip(ops, cuda_device):
+    x = torch.full((1, 1, 2, 64), 3.5, dtype=torch.float16, device=cuda_device)
+    x[0, 0, 1, :32] = torch.arange(32, device=cuda_device).half()
+    code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(x, 32, 4)
+    oc, os_, om = O.quantize_pack_last_dim(x.cpu().numpy(), 32, 4)
+    bits_equal(code, oc, "constant-group code")
+    bits_equal(scale, os_, "constant-group scale")
+    rng = np.random.default_rng(5)
+    for bit in (8, 4, 2, 1):
+        codes = rng.integers(0, 2 ** bit, size=(2, 3, 4, 64), dtype=np.int32)
+        words = ops.pu.pack_along_last_dim(torch.from_numpy(codes).to(cuda_device), bit)
+        bits_equal(words, O.pack_last_dim(codes, bit), f"pack {bit}")
+        back = ops.pu.unpack_along_last_dim(words, bit)
+        bits_equal(back, codes.astype(np.float16), f"unpack {bit}")
+
+
+def test_codec_full_size_roundtrip_property(ops, cuda_device):
+    """At the benchmark's full flush size (32k tokens x 8 heads) the dequantised values must lie
+    within half a quantisation step (plus fp16 rounding) of the input."""
+    gen = torch.Generator(device=cuda_device).manual_seed(3)
+    x = torch.randn(1, 8, 32640, 128, generator=gen, device=cuda_device).half()
+    for bit in (8, 4, 2):
+        code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(x, 32, bit)
+        deq = ops.pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, 32, bit)
+        step = scale.float().repeat_interleave(32, dim=-1)
+        err = (deq.float() - x.float()).abs()
+        assert bool((err <= 0.5 * step * 1.01 + 4e-3 * x.float().abs() + 1e-3).all()), f"bit {bit}"
+        kt = x.transpose(2, 3)
+        code_k, scale_k, mn_k = ops.pu.uniform_group_quantize_pack_last_dim(kt, 32, bit)
+        code_c, scale_c, mn_c = ops.pu.uniform_group_quantize_pack_last_dim(kt.contiguous(), 32, bit)
+        assert torch.equal(code_k, code_c) and torch.equal(scale_k, scale_c) and torch.equal(mn_k, mn_c)
+
+
+# ---------------------------------------------------------------------------------------------
+# importance ring, value range, block ranking
+# ---------------------------------------------------------------------------------------------
+def test_ring_and_ranking_golden(ops, cuda_device):
+    z = load_golden("ranking")
+    L = z["prefill_w"].shape[-1]
+    ring = ops.pf.last_attn_weights()
+    ring.set_max_length(L + 64)
+    ring.update(torch.from_numpy(z["prefill_w"]).to(cuda_device))
+    bits_equal(ring.weights, z["ring_after_prefill"], "ring after prefill")
+    for s in range(5):
+        ring.update(torch.from_numpy(z[f"step_w{s}"]).to(cuda_device))
+    bits_equal(ring.weights, z["ring_after_steps"], "ring after steps")
+    assert ring.next_line == int(z["ring_next_line"])
+    imp = ring.calculate_token_importance()
+    bits_equal(imp, z["importance"], "importance")
+    work = imp[:L].clone()
+    ids = ops.pf.get_block_token_idx(32, L // 32, work)
+    bits_equal(ids, z["rank_ids"], "ranked ids")
+    bits_equal(work, z["rank_importance_after"], "importance after the in-place divide")
+    w = torch.from_numpy(z["imp2"]).to(cuda_device)
+    bits_equal(ops.pf.get_block_token_idx(32, w.numel() // 32, w), z["rank2_ids"], "ranking with ties")
+    bits_equal(w, z["rank2_after"], "rank2 importance")
+    bits_equal(ops.pf.get_block_token_idx(32, w.numel() // 32, w), z["rank3_ids"], "ranking, second divide")
+    bits_equal(ops.pf.calculate_token_range(torch.from_numpy(z["range_v"]).to(cuda_device), None), z["range_out"],
+               "token range")
+
+
+def test_ranking_full_size_properties(ops, cuda_device):
+    """4088 blocks (the 128k-context case): output is a permutation, keys are non-increasing along it,
+    equal keys keep ascending block order."""
+    gen = torch.Generator(device=cuda_device).manual_seed(9)
+    n = 4088
+    imp = (torch.rand(n * 32, generator=gen, device=cuda_device) * 1e-4).half()
+    ref = imp.clone().cpu().numpy()
+    ids = ops.pf.get_block_token_idx(32, n, imp)
+    want = O.block_rank(32, n, ref)
+    bits_equal(ids, want, "ranking at 4088 blocks")
+    bits_equal(imp, ref, "divided importance")
+
+
+# ---------------------------------------------------------------------------------------------
+# flush
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
+def test_flush_golden_sequences(ops, cuda_device, name):
+    z = load_golden(name)
+    B, H, D, block, group, times_range, nsteps = (int(v) for v in z["meta"])
+    cache = None
+    for s in range(nsteps):
+        cin = golden_cache(z, f"s{s}_in")
+        if cache is None:
+            cache = dev_cache(cin, cuda_device)
+        else:  # carry our own tiers forward, take the grown residual window from the fixture
+            cache = cache[:39] + dev_cache(cin, cuda_device)[39:]
+        compress, hist = (int(v) for v in z[f"s{s}_args"])
+        imp = torch.from_numpy(z[f"s{s}_importance_in"].copy()).to(cuda_device)
+        ids = ops.pf.get_block_token_idx(block, (hist + compress) // block, imp)
+        bits_equal(ids, z[f"s{s}_K_ids"], f"{name} step {s} K ids")
+        ring = ops.pf.last_attn_weights()
+        ring.weights = torch.from_numpy(z[f"s{s}_ring_in"].copy()).to(cuda_device)
+        bn = torch.from_numpy(z[f"s{s}_bit_num"])
+        cache = ops.hqe_2.KV_cache_hqe_2(cache, compress, hist, ids, bn, bn.clone(), imp, "uniform_group", ring, block,
+                                         group, bool(times_range))
+        want = golden_cache(z, f"s{s}_out")
+        for i in range(41):
+            bits_equal(cache[i], want[i], f"{name} step {s} slot {i}")
+        assert cache[41] == want[41]
+        bits_equal(ring.weights, z[f"s{s}_ring_out"], f"{name} step {s} ring")
+    K, V = ops.hqe_2.KV_cache_reconstruct_hqe(cache, "uniform_group", block, group)
+    oK, oV = O.reconstruct(host_cache(cache), block, group)
+    bits_equal(K, oK, f"{name} reconstructed K")
+    bits_equal(V, oV, f"{name} reconstructed V")
+
+
+def test_flush_errors(ops, cuda_device):
+    k = torch.zeros(1, 1, 32, 128, dtype=torch.float16, device=cuda_device)
+    cache = (None,) * 39 + (k, k.clone(), 32)
+    imp = torch.zeros(32, dtype=torch.float16, device=cuda_device)
+    ids = torch.arange(32, device=cuda_device)
+    with pytest.raises(ValueError, match="invalid quant_strategy"):
+        ops.hqe_2.KV_cache_hqe_2(cache, 32, 0, ids, [0, 32, 0, 0, 0, 0], [0, 32, 0, 0, 0, 0], imp, "bogus")
+    with pytest.raises(NotImplementedError):
+        ops.hqe_2.KV_cache_hqe_2(cache, 32, 0, ids, [0, 32, 0, 0, 0, 0], [0, 32, 0, 0, 0, 0], imp, "normal_group")
+    with pytest.raises(ValueError, match="invalid past_key_value"):
+        ops.hqe_2.KV_cache_hqe_2(cache[:41], 32, 0, ids, [0, 32, 0, 0, 0, 0], [0, 32, 0, 0, 0, 0], imp, "uniform_group")
+
+
+# ---------------------------------------------------------------------------------------------
+# decode attention
+# ---------------------------------------------------------------------------------------------
+def check_attention(ops, cache_t, q, block, group, what):
+    w, out = ops.hm.qkv_matmul_hqe_2(q, cache_t, None, q.shape[-1], "uniform_group", block, group)
+    torch.cuda.synchronize()
+    ow, oo = O.decode_attention(q.cpu().numpy(), host_cache(cache_t), None, block, group)
+    out_f = out.float().cpu().numpy()
+    assert out_f.shape == oo.shape and w.shape == ow.shape, what
+    assert np.isfinite(out_f).all(), f"{what}: non-finite output"
+    per_head = np.abs(out_f - oo).max(axis=-1) / np.abs(oo).max(axis=-1)
+    assert per_head.max() <= ATTN_REL_TOL, f"{what}: attention output rel err {per_head.max():.3e} > {ATTN_REL_TOL}"
+    w_f = w.float().cpu().numpy()
+    werr = np.abs(w_f - ow)
+    assert (werr <= WEIGHT_ABS_TOL + WEIGHT_REL_TOL * ow).all(), \
+        f"{what}: probability error {werr.max():.3e} at p={ow.flat[werr.argmax()]:.3e}"
+    assert abs(w_f.sum(-1) - 1).max() < 2e-2, f"{what}: probabilities do not sum to 1"
+    return per_head.max()
+
+
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
+def test_decode_on_golden_caches(ops, cuda_device, name):
+    """Every flush step of the fixtures gives a cache with a different set of present/absent tiers,
+    K and V ranked differently (flush_a/c), batch 2 (flush_b), group 64 (flush_c)."""
+    z = load_golden(name)
+    B, H, D, block, group, _, nsteps = (int(v) for v in z["meta"])
+    gen = torch.Generator(device=cuda_device).manual_seed(1)
+    for s in range(nsteps):
+        cache_np = golden_cache(z, f"s{s}_out")
+        if any(cache_np[i] is not None for i in (28, 32)):  # drop 1-bit tier tokens: not built in the decode
+            with pytest.raises(NotImplementedError):
+                q = torch.randn(B, 4 * H, 1, D, generator=gen, device=cuda_device).half()
+                ops.hm.qkv_matmul_hqe_2(q, dev_cache(cache_np, cuda_device), None, D, "uniform_group", block, group)
+            continue
+        for rep in (1, 4, 8):
+            q = torch.randn(B, rep * H, 1, D, generator=gen, device=cuda_device).half()
+            check_attention(ops, dev_cache(cache_np, cuda_device), q, block, group, f"{name} step {s} rep {rep}")
+
+
+def test_decode_cfg0_vs_oracle(ops, cuda_device):
+    """Single-layer Llama-3.1-8B-shaped case: ctx 4096, 32/8 heads, group 32, 10 % evicted, 25/50/25 % in
+    the 8/4/2-bit tiers, residual 128, K with outlier channels."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CONFIGS["cfg0"]
+    for times_range in (False, True):
+        cache, q = synthetic.build_cache(cfg, cuda_device, seed=0, times_range=times_range)
+        assert synthetic.logical_length(cache) == 4096 - 12 * 32
+        err = check_attention(ops, cache, q, cfg.group, cfg.group, f"cfg0 times_range={times_range}")
+        # twice in a row: the scratch counters must be left clean
+        w1, o1 = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", cfg.group, cfg.group)
+        w2, o2 = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", cfg.group, cfg.group)
+        assert torch.equal(o1, o2) and torch.equal(w1, w2), "decode is not deterministic call to call"
+
+
+def test_decode_cfg0_flush_matches_oracle_flush(ops, cuda_device):
+    """The cache that the CUDA flush builds for cfg0 equals the oracle's flush of the same inputs."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CONFIGS["cfg0"]
+    K, V, q = synthetic.make_kv(cfg, cuda_device, 0)
+    flushed = cfg.context - cfg.residual
+    counts = synthetic.tier_counts(cfg)
+    imp = synthetic.synthetic_importance(cfg, cuda_device, 0, flushed)
+    imp_np = imp.cpu().numpy().copy()
+    ids = ops.pf.get_block_token_idx(cfg.group, flushed // cfg.group, imp)
+    ids_np = O.block_rank(cfg.group, flushed // cfg.group, imp_np)
+    bits_equal(ids, ids_np, "cfg0 ranked ids")
+    cache = (None,) * 39 + (K, V, cfg.context)
+    got = ops.hqe_2.KV_cache_hqe_2(cache, flushed, 0, ids, counts, list(counts), imp, "uniform_group", None, 32, 32, True)
+    want = O.flush(host_cache(cache), flushed, 0, ids_np, np.array(counts), np.array(counts), imp_np, "uniform_group",
+                   None, 32, 32, True)
+    for i in range(41):
+        bits_equal(got[i], want[i], f"cfg0 flush slot {i}")
+
+
+def test_decode_full_size_properties(ops, cuda_device):
+    """Llama-3.1-8B at 32k context (one layer of the benchmark workload): the fused decode must agree
+    with fp32 attention over the dense reconstruction of the same cache, computed with torch on the
+    GPU (the reconstruction's dequantiser is pinned bit-exactly above), within the same 2e-3."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CONFIGS["cfg1"]
+    cache, q = synthetic.build_cache(cfg, cuda_device, seed=1)
+    L = synthetic.logical_length(cache)
+    assert L == 32768 - 102 * 32
+    w, out = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", 32, 32)
+    Kd, Vd = ops.hqe_2.KV_cache_reconstruct_hqe(cache, "uniform_group", 32, 32)
+    qf = q.float().view(1, 8, 4, 128)
+    logits = torch.matmul(qf, Kd.float().transpose(2, 3)) / (128 ** 0.5)
+    p = torch.softmax(logits, dim=-1)
+    ref = torch.matmul(p, Vd.float()).view(1, 32, 1, 128)
+    rel = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
+    assert rel <= ATTN_REL_TOL, f"32k decode rel err {rel:.3e}"
+    pw = p.view(1, 32, 1, L)
+    assert bool(((w.float() - pw).abs() <= WEIGHT_ABS_TOL + WEIGHT_REL_TOL * pw).all())
+
+
+def test_decode_errors(ops, cuda_device):
+    q = torch.zeros(1, 4, 1, 128, dtype=torch.float16, device=cuda_device)
+    with pytest.raises(ValueError, match="invalid quant_strategy"):
+        ops.hm.qkv_matmul_hqe_2(q, (None,) * 42, None, 128, "bogus")
+    with pytest.raises(ValueError, match="invalid past_key_value"):
+        ops.hm.qkv_matmul_hqe_2(q, (None,) * 42, None, 128, "uniform_group")
+
+
+# ---------------------------------------------------------------------------------------------
+# stand-alone GEMV
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("bits", [8, 4, 2])
+def test_gemv_uniform_group_vs_oracle(ops, cuda_device, bits):
+    """Both uses of cuda_bmm_fA_qB_uniform_group: q.K^T of a tier (K = head_dim rows, N = tokens) and
+    p.V of a tier (K = tokens, N = head_dim).  Tolerance: 2e-3 of the largest output (fp16 result)."""
+    rng = np.random.default_rng(bits)
+    for (K, N, g) in ((128, 32 * 9, 32), (32 * 7, 128, 32), (128, 128, 64)):
+        x = rng.standard_normal((2, 2, K, N)).astype(np.float16)
+        code, scale, mn = O.quantize_pack_last_dim(x, g, bits)
+        fA = rng.standard_normal((2, 8, 1, K)).astype(np.float16)
+        want = O.gemv_dequant(fA, code, scale, mn, g, bits)
+        got = ops.mm.cuda_bmm_fA_qB_uniform_group(g, *(torch.from_numpy(a).to(cuda_device) for a in (fA, code, scale, mn)),
+                                                  bits)
+        err = np.abs(got.float().cpu().numpy() - want).max() / np.abs(want).max()
+        assert err <= 2e-3, f"gemv bits {bits} K {K} N {N}: rel err {err:.3e}"
