@@ -28,7 +28,6 @@ constexpr int NWARP = 4;         // warps per CTA
 constexpr int NTHREADS = NWARP * 32;
 constexpr int MAX_REP = 8;       // query heads per kv head (n of the m16n8k16 tile)
 constexpr int SCALE_PAD = 8;     // halfs of padding per shared-memory scale row
-constexpr int MAX_K_GROUPS = 32; // groups of one K chunk (chunk tokens / group)
 constexpr int MAX_V_CHUNK = 1024;
 
 struct TierDev {
@@ -52,6 +51,7 @@ struct DecodeParams {
   int gk_shift, gv_shift;
   int nk_chunks, nv_chunks;
   int w_slice;  // logical positions normalised per v_pass CTA
+  int k_max_bits;  // widest quantised K tier present (sizes the k_pass shared-memory data region)
   float scale;
   const __half* q;
   __half* weights;
@@ -248,78 +248,294 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
   m = mx;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// cp.async helpers (global -> shared without a register round trip; no barrier objects, nothing to
+// spin on: completion is a per-thread wait_group followed by __syncthreads)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 // ------------------------------------------------------------------------------------------------
 // k_pass
 // ------------------------------------------------------------------------------------------------
-struct KShared {
-  uint2 qfrag[8][32];                               // B fragments of q per 16-channel step and lane
-  __half s[MAX_K_GROUPS][D + SCALE_PAD];            // scale[group][channel]
-  __half z[MAX_K_GROUPS][D + SCALE_PAD];
-  float red_m[NWARP][MAX_REP], red_l[NWARP][MAX_REP];
-};
+// Quantised K tier, rows = channels, packed words along tokens.  A CTA takes a chunk of up to
+// K_MAXBLK blocks of 32 tokens for one (batch, kv head):
+//   1. the chunk's packed bytes of all 128 channel rows stream into shared memory with cp.async
+//      (fully coalesced 16-byte pieces, the whole chunk in flight at once);
+//   2. meanwhile the scale/zero tile is staged and, per scale group, the B operand
+//      q_h[d] * scale[d, group] is formed in fp32 and split into an fp16 high and low part, and
+//      Zq[group][h] = sum_d q_h[d] * zero[d, group] is accumulated in fp32;
+//   3. each warp takes blocks: the A operand holds the EXACT integer codes (fp16 integers), so
+//      logit = sum_d code * (hi + lo) + Zq reproduces the fp32 dequant-matmul to ~2^-22: the only
+//      rounding left is the fp32 accumulation itself.
+// All 16 rows of an M-tile lie in one 32-token block, hence one scale group, which is what lets the
+// scale move into the B operand.  Within a block, lane group g owns tokens 4g..4g+3.
+constexpr int K_BLOCK = 32;
+constexpr int K_MAXBLK = 8;
+constexpr int K_CHUNK = K_BLOCK * K_MAXBLK;  // 256 tokens
+constexpr int K_SROW = D + SCALE_PAD;        // halfs per staged scale row
 
-// Quantised / fp16 channel-major tier: rows are channels, words run along tokens.
-// Per warp one span of 16 word slots (16*FPI tokens): fragment row g <-> slot g, row g+8 <-> slot g+8,
-// M-tile i <-> i-th value of every slot.
+__host__ __device__ constexpr int k_row_bytes(int bits) { return K_MAXBLK * 4 * bits + 16; }  // + pad: no bank conflicts
+
+struct KSmemLayout {
+  int qfrag, qs, s, z, zq, red, bhi, blo, data, total;
+};
+__host__ __device__ inline KSmemLayout k_smem_layout(int rep, int max_bits) {
+  KSmemLayout l;
+  int off = 0;
+  l.qfrag = off; off += 8 * 32 * 8;
+  l.qs = off; off += MAX_REP * D * 2;
+  l.s = off; off += K_MAXBLK * K_SROW * 2;
+  l.z = off; off += K_MAXBLK * K_SROW * 2;
+  l.zq = off; off += K_MAXBLK * MAX_REP * 4;
+  l.red = off; off += 2 * NWARP * MAX_REP * 4;
+  l.bhi = off; off += K_MAXBLK * 8 * 4 * rep * 8;
+  l.blo = off; off += K_MAXBLK * 8 * 4 * rep * 8;
+  off = (off + 15) & ~15;
+  l.data = off; off += D * k_row_bytes(max_bits);
+  l.total = off;
+  return l;
+}
+
+// token offset inside a block of the value held by (row slot, M-tile) of lane group g
 template <int BITS>
-__device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                       int chunk_t0, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
-  using F = Fmt<BITS>;
-  using word_t = typename F::word_t;
-  constexpr int FPI = F::FPI;
-  constexpr int NM = FPI;
+__device__ __forceinline__ int k_token_offset(int g, int slot, int m) {
+  return BITS == 4 ? 4 * g + 2 * slot + m : 4 * g + slot + 2 * m;
+}
+
+// Exact integer codes of one 16-channel step of one block as A fragments for both M-tiles.
+// a[m][0..3] = fragment registers of M-tile m.
+template <int BITS>
+__device__ __forceinline__ void k_codes(const unsigned char* data, int row_bytes, int kt, int blk, int g, int tig,
+                                        uint32_t (&a)[2][4]) {
+  const __half2 k1024 = __half2half2(__float2half(1024.f));
+  uint32_t w[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
+    const unsigned char* src = data + ch * row_bytes + blk * (4 * BITS);
+    if constexpr (BITS == 8) w[p] = *reinterpret_cast<const uint32_t*>(src + 4 * g);
+    else if constexpr (BITS == 4) w[p] = *reinterpret_cast<const uint16_t*>(src + 2 * g);
+    else w[p] = src[g];
+  }
+#pragma unroll
+  for (int q = 0; q < 2; ++q) {  // channel pair (2tig,2tig+1) / (+8,+9) -> fragment registers q*2 + slot
+    const uint32_t wa = w[2 * q], wb = w[2 * q + 1];
+    if constexpr (BITS == 8) {
+      // bytes: 0 = (slot0,m0), 1 = (slot1,m0), 2 = (slot0,m1), 3 = (slot1,m1)
+      const uint32_t lo = __byte_perm(wa, wb, 0x5140);  // [a0 b0 a1 b1]
+      const uint32_t hi = __byte_perm(wa, wb, 0x7362);  // [a2 b2 a3 b3]
+      const uint32_t x00 = __byte_perm(lo, 0x64646464u, 0x4140), x10 = __byte_perm(lo, 0x64646464u, 0x4342);
+      const uint32_t x01 = __byte_perm(hi, 0x64646464u, 0x4140), x11 = __byte_perm(hi, 0x64646464u, 0x4342);
+      a[0][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x00), k1024));
+      a[0][q * 2 + 1] = h2_as_u32(__hsub2(u32_as_h2(x10), k1024));
+      a[1][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x01), k1024));
+      a[1][q * 2 + 1] = h2_as_u32(__hsub2(u32_as_h2(x11), k1024));
+    } else if constexpr (BITS == 4) {
+      // byte 0 = slot 0, byte 1 = slot 1; low nibble = m0, high nibble = m1
+      const __half2 k16th = __half2half2(__float2half(0.0625f)), k64 = __half2half2(__float2half(-64.f));
+#pragma unroll
+      for (int slot = 0; slot < 2; ++slot) {
+        const uint32_t t = __byte_perm(wa, wb, slot == 0 ? 0x4400 : 0x5511);
+        const uint32_t x0 = (t & 0x000F000Fu) | 0x64006400u;
+        const uint32_t x1 = (t & 0x00F000F0u) | 0x64006400u;
+        a[0][q * 2 + slot] = h2_as_u32(__hsub2(u32_as_h2(x0), k1024));
+        a[1][q * 2 + slot] = h2_as_u32(__hfma2(u32_as_h2(x1), k16th, k64));
+      }
+    } else {
+      // one byte: crumb k = slot + 2*m
+      const uint32_t t = __byte_perm(wa, wb, 0x4400);
+      const uint32_t x0 = (t & 0x00030003u) | 0x64006400u;  // slot0 m0
+      const uint32_t x1 = (t & 0x000C000Cu) | 0x64006400u;  // slot1 m0   (1024 + 4c)
+      const uint32_t x2 = (t & 0x00300030u) | 0x64006400u;  // slot0 m1   (1024 + 16c)
+      const uint32_t x3 = (t & 0x00C000C0u) | 0x64006400u;  // slot1 m1   (1024 + 64c)
+      a[0][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x0), k1024));
+      a[0][q * 2 + 1] = h2_as_u32(__hfma2(u32_as_h2(x1), __half2half2(__float2half(0.25f)), __half2half2(__float2half(-256.f))));
+      a[1][q * 2 + 0] = h2_as_u32(__hfma2(u32_as_h2(x2), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f))));
+      a[1][q * 2 + 1] = h2_as_u32(__hfma2(u32_as_h2(x3), __half2half2(__float2half(0.015625f)), __half2half2(__float2half(-16.f))));
+    }
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void k_quant_chunk(const DecodeParams& P, const TierDev& T, unsigned char* smem,
+                                              const KSmemLayout& lay, int bh, int b, int kvh, int chunk_t0,
+                                              float (&m_run)[2], float (&l_run)[2]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+  const int rep = P.rep;
+  const int n = T.n_k;
+  const int ntok = min(K_CHUNK, n - chunk_t0);
+  const int nblk = ntok / K_BLOCK;
+  constexpr int BPB = 4 * BITS;              // bytes per block and channel
+  constexpr int PIECE = BITS == 2 ? 8 : 16;  // cp.async granularity (2-bit rows are only 8-byte aligned)
+  constexpr int ROWB = k_row_bytes(BITS);
+  unsigned char* data = smem + lay.data;
+  // 1. stream the packed bytes of the chunk
+  {
+    const int ppr = nblk * BPB / PIECE;  // pieces per channel row
+    const int64_t row_total = static_cast<int64_t>(n) * BITS / 8;
+    const unsigned char* src0 = reinterpret_cast<const unsigned char*>(T.k_data) +
+                                static_cast<int64_t>(bh) * D * row_total + static_cast<int64_t>(chunk_t0) * BITS / 8;
+    for (int i = tid; i < D * ppr; i += NTHREADS) {
+      const int row = i / ppr, pc = i - row * ppr;
+      if constexpr (PIECE == 16) cp_async_16(data + row * ROWB + pc * 16, src0 + row * row_total + pc * 16);
+      else cp_async_8(data + row * ROWB + pc * 8, src0 + row * row_total + pc * 8);
+    }
+    cp_async_commit();
+  }
+  // 2. stage scale / zero of the chunk as [group][channel]; all loads of a thread are issued before any store
+  const int bshift = P.gk_shift - 5;                     // blocks per scale group = 1 << bshift
+  const int ng = (nblk + (1 << bshift) - 1) >> bshift;   // scale groups of the chunk
+  __half* ssm = reinterpret_cast<__half*>(smem + lay.s);
+  __half* zsm = reinterpret_cast<__half*>(smem + lay.z);
+  {
+    const int G = n >> P.gk_shift, g0 = chunk_t0 >> P.gk_shift;
+    const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G + g0;
+    const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G + g0;
+    __half sv[K_MAXBLK], zv[K_MAXBLK];
+#pragma unroll
+    for (int j = 0; j < K_MAXBLK; ++j) {
+      const int i = tid + j * NTHREADS;
+      if (i < D * ng) {
+        const int ch = i / ng, gi = i - ch * ng;
+        sv[j] = s[static_cast<int64_t>(ch) * G + gi];
+        zv[j] = z[static_cast<int64_t>(ch) * G + gi];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < K_MAXBLK; ++j) {
+      const int i = tid + j * NTHREADS;
+      if (i < D * ng) {
+        const int ch = i / ng, gi = i - ch * ng;
+        ssm[gi * K_SROW + ch] = sv[j];
+        zsm[gi * K_SROW + ch] = zv[j];
+      }
+    }
+  }
+  __syncthreads();
+  // 3. per scale group: B = q*scale split into fp16 hi + lo, Zq = sum_d q*zero.  One warp per group,
+  //    lane = (16-channel step kt, tig) unit, which is also the B-fragment lane layout.
+  const __half* qs = reinterpret_cast<const __half*>(smem + lay.qs);
+  uint2* bhi = reinterpret_cast<uint2*>(smem + lay.bhi);
+  uint2* blo = reinterpret_cast<uint2*>(smem + lay.blo);
+  float* zq = reinterpret_cast<float*>(smem + lay.zq);
+  for (int gi = warp; gi < ng; gi += NWARP) {
+    const int kt = lane >> 2, tg = lane & 3;
+    const int c0 = kt * 16 + 2 * tg;
+    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + gi * K_SROW + c0));
+    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(ssm + gi * K_SROW + c0 + 8));
+    const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(zsm + gi * K_SROW + c0));
+    const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(zsm + gi * K_SROW + c0 + 8));
+    for (int h = 0; h < rep; ++h) {
+      const float2 q01 = __half22float2(*reinterpret_cast<const __half2*>(qs + h * D + c0));
+      const float2 q23 = __half22float2(*reinterpret_cast<const __half2*>(qs + h * D + c0 + 8));
+      const float p0 = q01.x * s01.x, p1 = q01.y * s01.y, p2 = q23.x * s23.x, p3 = q23.y * s23.y;
+      const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
+      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
+      const __half2 l01 = __floats2half2_rn(p0 - f01.x, p1 - f01.y), l23 = __floats2half2_rn(p2 - f23.x, p3 - f23.y);
+      const int e = ((gi * 8 + kt) * 4 + tg) * rep + h;
+      bhi[e] = make_uint2(h2_as_u32(h01), h2_as_u32(h23));
+      blo[e] = make_uint2(h2_as_u32(l01), h2_as_u32(l23));
+      float zs = q01.x * z01.x;
+      zs = fmaf(q01.y, z01.y, zs);
+      zs = fmaf(q23.x, z23.x, zs);
+      zs = fmaf(q23.y, z23.y, zs);
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) zs += __shfl_xor_sync(0xffffffffu, zs, off);
+      if (lane == 0) zq[gi * MAX_REP + h] = zs;
+    }
+  }
+  cp_async_wait_all();
+  __syncthreads();
+  // 4. blocks of this warp
+  for (int blk = warp; blk < nblk; blk += NWARP) {
+    const int gi = blk >> bshift;
+    float acc[2][4];
+#pragma unroll
+    for (int m = 0; m < 2; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      uint32_t a[2][4];
+      k_codes<BITS>(data, ROWB, kt, blk, g, tig, a);
+      uint2 bh2 = make_uint2(0u, 0u), bl2 = make_uint2(0u, 0u);
+      if (g < rep) {
+        const int e = ((gi * 8 + kt) * 4 + tig) * rep + g;
+        bh2 = bhi[e];
+        bl2 = blo[e];
+      }
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        mma16816(acc[m], a[m][0], a[m][1], a[m][2], a[m][3], bh2.x, bh2.y);
+        mma16816(acc[m], a[m][0], a[m][1], a[m][2], a[m][3], bl2.x, bl2.y);
+      }
+    }
+    // logits of heads 2tig, 2tig+1 for this lane's four tokens
+    const int64_t tok0 = static_cast<int64_t>(chunk_t0) + blk * K_BLOCK;
+    int64_t pos[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) pos[k] = T.k_idx[tok0 + 4 * g + k];
+#pragma unroll
+    for (int slot = 0; slot < 2; ++slot)
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        const int k = k_token_offset<BITS>(0, slot, m);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int h = 2 * tig + e;
+          if (h < rep) {
+            const float x = (acc[m][slot * 2 + e] + zq[gi * MAX_REP + h]) * P.scale;
+            P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L + pos[k]] = x;
+            softmax_push(m_run[e], l_run[e], x);
+          }
+        }
+      }
+  }
+}
+
+// fp16 tier, channel-major rows [D][n]: eight tokens per 16-byte word, no scales; B = q exactly.
+// Per warp one span of 16 word slots (128 tokens): fragment row g <-> slot g, row g+8 <-> slot g+8,
+// M-tile i <-> i-th value of every slot.
+__device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev& T, const uint2* qfrag, int bh, int b,
+                                           int kvh, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
+  constexpr int FPI = 8, NM = 8;
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
-  const int64_t W = n / FPI;  // word slots per channel row
-  const word_t* base = reinterpret_cast<const word_t*>(T.k_data) + static_cast<int64_t>(bh) * D * W;
+  const int64_t W = n / FPI;
+  const uint4* base = reinterpret_cast<const uint4*>(T.k_data) + static_cast<int64_t>(bh) * D * W;
   int64_t wc[2];
   bool ok[2];
-  int gl[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     wc[r] = span_t0 / FPI + r * 8 + g;
     ok[r] = wc[r] < W;
-    const int tok = static_cast<int>(wc[r]) * FPI;
-    gl[r] = ok[r] ? ((tok >> P.gk_shift) - (chunk_t0 >> P.gk_shift)) : 0;
   }
   float acc[NM][4];
 #pragma unroll
   for (int i = 0; i < NM; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-
-  word_t w[4][2], wn[4][2];
-  auto load = [&](word_t (&dst)[4][2], int kt) {
+  const __half2 unused = __half2half2(__float2half(0.f));
+  const __half2 sz[2][2] = {{unused, unused}, {unused, unused}};
+#pragma unroll 2
+  for (int kt = 0; kt < 8; ++kt) {
+    uint4 w[4][2];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
 #pragma unroll
-      for (int r = 0; r < 2; ++r) dst[p][r] = ok[r] ? ld_stream(base + ch * W + wc[r]) : zero_word<word_t>();
+      for (int r = 0; r < 2; ++r) w[p][r] = ok[r] ? ld_stream(base + ch * W + wc[r]) : zero_word<uint4>();
     }
-  };
-  load(w, 0);
-#pragma unroll 1
-  for (int kt = 0; kt < 8; ++kt) {
-    if (kt + 1 < 8) load(wn, kt + 1);
-    __half2 sz[2][2], zz[2][2];
-    if constexpr (BITS != 16) {
-#pragma unroll
-      for (int q = 0; q < 2; ++q) {
-        const int ch = kt * 16 + 2 * tig + q * 8;
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          sz[q][r] = *reinterpret_cast<const __half2*>(&sh.s[gl[r]][ch]);
-          zz[q][r] = *reinterpret_cast<const __half2*>(&sh.z[gl[r]][ch]);
-        }
-      }
-    }
-    const uint2 bq = sh.qfrag[kt][lane];
-    mma_words<BITS, NM>(acc, w, sz, zz, bq.x, bq.y);
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      w[p][0] = wn[p][0];
-      w[p][1] = wn[p][1];
-    }
+    const uint2 bq = qfrag[kt * 32 + lane];
+    mma_words<16, NM>(acc, w, sz, sz, bq.x, bq.y);
   }
-  // scatter the logits of heads 2tig, 2tig+1 to their logical positions
   const int h0 = 2 * tig;
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
@@ -342,8 +558,8 @@ __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, 
 }
 
 // fp16 residual window, token-major [r][D]: A fragments are read directly.
-__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b,
-                                                int kvh, int tile_t0, float (&m_run)[2], float (&l_run)[2]) {
+__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, const uint2* qfrag, int bh,
+                                                int b, int kvh, int tile_t0, float (&m_run)[2], float (&l_run)[2]) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
   const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
@@ -359,7 +575,7 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
       a[r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch) : 0u;
       a[2 + r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch + 8) : 0u;
     }
-    const uint2 bq = sh.qfrag[kt][lane];
+    const uint2 bq = qfrag[kt * 32 + lane];
     mma16816(acc, a[0], a[1], a[2], a[3], bq.x, bq.y);
   }
   const int h0 = 2 * tig;
@@ -379,50 +595,35 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
   }
 }
 
-template <int BITS>
-__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                        int chunk_t0, float (&m_run)[2], float (&l_run)[2]) {
-  constexpr int SPAN = 16 * Fmt<BITS>::FPI;
-  const int warp = threadIdx.x >> 5;
-  const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
-  if constexpr (BITS != 16) {
-    // stage scale/zero of this chunk as [group][channel]
-    const int G = T.n_k >> P.gk_shift;
-    const int g0 = chunk_t0 >> P.gk_shift;
-    const int ng = ((chunk_end - chunk_t0) + (1 << P.gk_shift) - 1) >> P.gk_shift;
-    const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G;
-    const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G;
-    for (int i = threadIdx.x; i < D * ng; i += NTHREADS) {
-      const int ch = i / ng, gi = i - ch * ng;
-      sh.s[gi][ch] = s[static_cast<int64_t>(ch) * G + g0 + gi];
-      sh.z[gi][ch] = z[static_cast<int64_t>(ch) * G + g0 + gi];
-    }
-    __syncthreads();
-  }
-  for (int span_t0 = chunk_t0 + warp * SPAN; span_t0 < chunk_end; span_t0 += NWARP * SPAN)
-    k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0, m_run, l_run);
-}
-
 __global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
-  __shared__ KShared sh;
+  extern __shared__ __align__(16) unsigned char smem[];
+  const KSmemLayout lay = k_smem_layout(P.rep, P.k_max_bits);
   const int chunk = blockIdx.x, bh = blockIdx.y;
   const int b = bh / P.H, kvh = bh - b * P.H;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+  uint2* qfrag = reinterpret_cast<uint2*>(smem + lay.qfrag);
+  __half* qs = reinterpret_cast<__half*>(smem + lay.qs);
+  float* red_m = reinterpret_cast<float*>(smem + lay.red);
+  float* red_l = red_m + NWARP * MAX_REP;
 
-  // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
-  if (warp == 0) {
-    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
+  // q of this kv head's query heads: rows for the table build, B fragments for the fp16 paths
+  {
+    const __half* q0 = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * D;
+    for (int i = tid; i < P.rep * (D / 2); i += NTHREADS)
+      reinterpret_cast<uint32_t*>(qs)[i] = reinterpret_cast<const uint32_t*>(q0)[i];
+    if (warp == 0) {
+      const __half* qh = q0 + g * D;
 #pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      uint2 f = make_uint2(0u, 0u);
-      if (g < P.rep) {
-        f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
-        f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
+      for (int kt = 0; kt < 8; ++kt) {
+        uint2 f = make_uint2(0u, 0u);
+        if (g < P.rep) {
+          f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
+          f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
+        }
+        qfrag[kt * 32 + lane] = f;
       }
-      sh.qfrag[kt][lane] = f;
     }
   }
-  __syncthreads();
 
   int ti = HQKV_NUM_TIERS;
 #pragma unroll
@@ -432,18 +633,22 @@ __global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant_
   const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
 
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-  if (ti == HQKV_NUM_TIERS) {
+  if (ti == HQKV_NUM_TIERS || T.bits == 16) {
+    __syncthreads();
     const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
-    for (int t0 = chunk_t0 + warp * 16; t0 < chunk_end; t0 += NWARP * 16)
-      k_residual_tile(P, T, sh, bh, b, kvh, t0, m_run, l_run);
+    if (ti == HQKV_NUM_TIERS) {
+      for (int t0 = chunk_t0 + warp * 16; t0 < chunk_end; t0 += NWARP * 16)
+        k_residual_tile(P, T, qfrag, bh, b, kvh, t0, m_run, l_run);
+    } else {
+      for (int t0 = chunk_t0 + warp * 128; t0 < chunk_end; t0 += NWARP * 128)
+        k_f16_span(P, T, qfrag, bh, b, kvh, t0, m_run, l_run);
+    }
   } else if (T.bits == 8) {
-    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_quant_chunk<8>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
   } else if (T.bits == 4) {
-    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
-  } else if (T.bits == 2) {
-    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_quant_chunk<4>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
   } else {
-    k_chunk<16>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_quant_chunk<2>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
   }
 
   // (max, sum) of this CTA per head: lanes with equal tig hold the same two heads
@@ -456,15 +661,15 @@ __global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant_
       softmax_merge(m_run[e], l_run[e], m2, l2);
     }
     if (g == 0) {
-      sh.red_m[warp][2 * tig + e] = m_run[e];
-      sh.red_l[warp][2 * tig + e] = l_run[e];
+      red_m[warp * MAX_REP + 2 * tig + e] = m_run[e];
+      red_l[warp * MAX_REP + 2 * tig + e] = l_run[e];
     }
   }
   __syncthreads();
-  if (threadIdx.x < MAX_REP) {
-    float m = sh.red_m[0][threadIdx.x], l = sh.red_l[0][threadIdx.x];
-    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, sh.red_m[w][threadIdx.x], sh.red_l[w][threadIdx.x]);
-    P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + threadIdx.x] = make_float2(m, l);
+  if (tid < MAX_REP) {
+    float m = red_m[tid], l = red_l[tid];
+    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, red_m[w * MAX_REP + tid], red_l[w * MAX_REP + tid]);
+    P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + tid] = make_float2(m, l);
   }
 }
 
@@ -480,10 +685,13 @@ struct VShared {
   float wm[NWARP][MAX_REP], wl[NWARP][MAX_REP];
   unsigned is_last;
 };
+constexpr int V_STAGE_ITERS = MAX_V_CHUNK / NTHREADS;  // 8
 
 // V tier, token-major rows.  Contraction runs over tokens (16 per step): fragment columns
 // 2tig,2tig+1,2tig+8,2tig+9 <-> tokens t0+..., fragment row g <-> channel slot g, row g+8 <-> slot
-// g+8 (2-bit: low/high half of word g), M-tile i <-> i-th value of every slot.
+// g+8 (2-bit: low/high half of word g), M-tile i <-> i-th value of every slot.  The values are
+// dequantised to fp16 (code*scale + zero, one rounding) because here the scale varies along the
+// contraction axis; B = exp(logit - max) in fp16.
 template <int BITS>
 __device__ __forceinline__ void v_chunk(const DecodeParams& P, const TierDev& T, VShared& sh, int bh,
                                         int chunk_t0, int chunk_n, float (&acc)[8][4]) {
@@ -491,59 +699,68 @@ __device__ __forceinline__ void v_chunk(const DecodeParams& P, const TierDev& T,
   using word_t = typename F::word_t;
   constexpr bool HALF_SPLIT = (BITS == 2);  // one word per token row covers both row slots
   constexpr int WORDS_PER_TOKEN = BITS == 2 ? 8 : 16;  // in units of word_t
+  constexpr int NW = HALF_SPLIT ? 1 : 2;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
   const int n = T.n_v;
   const word_t* base = reinterpret_cast<const word_t*>(T.v_data) + static_cast<int64_t>(bh) * n * WORDS_PER_TOKEN;
-  // channel group of the two row slots
   int cg[2];
 #pragma unroll
   for (int s = 0; s < 2; ++s) {
     const int ch0 = HALF_SPLIT ? (16 * g + 8 * s) : (8 * (s * 8 + g));
     cg[s] = ch0 >> P.gv_shift;
   }
-  for (int kt0 = warp * 16; kt0 < chunk_n; kt0 += NWARP * 16) {
-    // the four tokens of this thread's fragment columns (chunk-local), clamped for the loads
-    int tl[4];
-    tl[0] = kt0 + 2 * tig;
-    tl[1] = tl[0] + 1;
-    tl[2] = tl[0] + 8;
-    tl[3] = tl[0] + 9;
+  auto load = [&](word_t (&dst)[4][NW], int kt0) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int tl = kt0 + 2 * tig + (p & 1) + (p >> 1) * 8;
+      const int64_t tok = chunk_t0 + min(tl, chunk_n - 1);
+#pragma unroll
+      for (int s = 0; s < NW; ++s) dst[p][s] = ld_stream(base + tok * WORDS_PER_TOKEN + s * 8 + g);
+    }
+  };
+  word_t cur[4][NW], nxt[4][NW];
+  const int step = NWARP * 16;
+  int kt0 = warp * 16;
+  if (kt0 < chunk_n) load(cur, kt0);
+  for (; kt0 < chunk_n; kt0 += step) {
+    if (kt0 + step < chunk_n) load(nxt, kt0 + step);
+    const int tl0 = kt0 + 2 * tig, tl2 = tl0 + 8;
     word_t w[4][2];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
-      const int64_t tok = chunk_t0 + min(tl[p], chunk_n - 1);
       if constexpr (HALF_SPLIT) {
-        const word_t x = ld_stream(base + tok * WORDS_PER_TOKEN + g);
-        w[p][0] = x;
-        w[p][1] = x >> 16;  // values 8..15 of the word move to bytes 0,1
+        w[p][0] = cur[p][0];
+        w[p][1] = cur[p][0] >> 16;  // values 8..15 of the word move to bytes 0,1
       } else {
-        w[p][0] = ld_stream(base + tok * WORDS_PER_TOKEN + g);
-        w[p][1] = ld_stream(base + tok * WORDS_PER_TOKEN + 8 + g);
+        w[p][0] = cur[p][0];
+        w[p][1] = cur[p][1];
       }
     }
     __half2 sz[2][2], zz[2][2];
     if constexpr (BITS != 16) {
 #pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int s = 0; s < 2; ++s) {
-          sz[q][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl[q * 2]]);
-          zz[q][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl[q * 2]]);
-        }
+      for (int s = 0; s < 2; ++s) {
+        sz[0][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl0]);
+        zz[0][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl0]);
+        sz[1][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl2]);
+        zz[1][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl2]);
+      }
     }
-    // B fragment: column n = g is head g; e is zero beyond the chunk
     uint32_t b0 = 0u, b1 = 0u;
     if (g < P.rep) {
-      b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl[0]]);
-      b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl[2]]);
+      b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl0]);
+      b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl2]);
     }
     if constexpr (HALF_SPLIT) {
-      // only sub-units 0,1 (values 0..7) of each (shifted) word are used: 8 M-tiles
       mma_sub<2, 0, 8>(acc, w, sz, zz, b0, b1);
       mma_sub<2, 1, 8>(acc, w, sz, zz, b0, b1);
     } else {
       mma_words<BITS, 8>(acc, w, sz, zz, b0, b1);
     }
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int s = 0; s < NW; ++s) cur[p][s] = nxt[p][s];
   }
 }
 
@@ -569,8 +786,69 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
   VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
   const int chunk = blockIdx.x, bh = blockIdx.y;
   const int b = bh / P.H, kvh = bh - b * P.H;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rep = P.rep;
+
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
+  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
+  const int chunk_pad = (chunk_n + 15) & ~15;
+  const bool is_res = ti == HQKV_NUM_TIERS;
+
+  // ---- logical positions of this chunk's tokens (independent loads, issued before the reduction below)
+  int64_t pos[V_STAGE_ITERS];
+#pragma unroll
+  for (int j = 0; j < V_STAGE_ITERS; ++j) {
+    const int i = tid + j * NTHREADS;
+    pos[j] = 0;
+    if (i < chunk_n) pos[j] = is_res ? (P.L - T.n_v + chunk_t0 + i) : T.v_idx[chunk_t0 + i];
+  }
+  // ---- scale / zero tile: one token row per thread and iteration, transposed into [group][token]
+  if (!is_res && T.bits != 16) {
+    const int ng = D >> P.gv_shift;  // 4, 2 or 1 halfs per token
+    const __half* s = T.v_scale + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
+    const __half* z = T.v_zero + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
+    uint2 sv[V_STAGE_ITERS], zv[V_STAGE_ITERS];
+#pragma unroll
+    for (int j = 0; j < V_STAGE_ITERS; ++j) {
+      const int t = tid + j * NTHREADS;
+      sv[j] = zv[j] = make_uint2(0u, 0u);
+      if (t < chunk_n) {
+        if (ng == 4) {
+          sv[j] = *reinterpret_cast<const uint2*>(s + t * 4);
+          zv[j] = *reinterpret_cast<const uint2*>(z + t * 4);
+        } else if (ng == 2) {
+          sv[j].x = *reinterpret_cast<const uint32_t*>(s + t * 2);
+          zv[j].x = *reinterpret_cast<const uint32_t*>(z + t * 2);
+        } else {
+          sv[j].x = __half_as_ushort(s[t]);
+          zv[j].x = __half_as_ushort(z[t]);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < V_STAGE_ITERS; ++j) {
+      const int t = tid + j * NTHREADS;
+      if (t < chunk_pad) {
+        sh.s[0][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].x & 0xFFFFu));
+        sh.z[0][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].x & 0xFFFFu));
+        if (ng >= 2) {
+          sh.s[1][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].x >> 16));
+          sh.z[1][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].x >> 16));
+        }
+        if (ng == 4) {
+          sh.s[2][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].y & 0xFFFFu));
+          sh.z[2][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].y & 0xFFFFu));
+          sh.s[3][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].y >> 16));
+          sh.z[3][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].y >> 16));
+        }
+      }
+    }
+  }
 
   // ---- global (max, sum) of the rep heads from the k_pass pairs
   {
@@ -581,14 +859,12 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
       l[h] = 0.f;
     }
     const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
-    for (int c = threadIdx.x; c < P.nk_chunks; c += NTHREADS) {
+    for (int c = tid; c < P.nk_chunks; c += NTHREADS) {
+      float2 v[MAX_REP];
 #pragma unroll
-      for (int h = 0; h < MAX_REP; ++h) {
-        if (h < rep) {
-          const float2 v = part[c * MAX_REP + h];
-          softmax_merge(m[h], l[h], v.x, v.y);
-        }
-      }
+      for (int h = 0; h < MAX_REP; ++h) v[h] = h < rep ? part[c * MAX_REP + h] : make_float2(-INFINITY, 0.f);
+#pragma unroll
+      for (int h = 0; h < MAX_REP; ++h) softmax_merge(m[h], l[h], v[h].x, v[h].y);
     }
 #pragma unroll
     for (int h = 0; h < MAX_REP; ++h) {
@@ -604,47 +880,29 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
       }
     }
     __syncthreads();
-    if (threadIdx.x < MAX_REP) {
-      float mm = sh.wm[0][threadIdx.x], ll = sh.wl[0][threadIdx.x];
-      for (int w = 1; w < NWARP; ++w) softmax_merge(mm, ll, sh.wm[w][threadIdx.x], sh.wl[w][threadIdx.x]);
-      sh.gm[threadIdx.x] = mm;
-      sh.gl[threadIdx.x] = ll;
+    if (tid < MAX_REP) {
+      float mm = sh.wm[0][tid], ll = sh.wl[0][tid];
+      for (int w = 1; w < NWARP; ++w) softmax_merge(mm, ll, sh.wm[w][tid], sh.wl[w][tid]);
+      sh.gm[tid] = mm;
+      sh.gl[tid] = ll;
     }
     __syncthreads();
   }
 
-  int ti = HQKV_NUM_TIERS;
+  // ---- exp(logit - max) of the chunk's tokens, per head: gathers batched per head
+  for (int h = 0; h < rep; ++h) {
+    const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+    const float mh = sh.gm[h];
+    float x[V_STAGE_ITERS];
 #pragma unroll
-  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
-    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
-  const TierDev& T = P.tier[ti];
-  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
-  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
-  const int chunk_pad = (chunk_n + 15) & ~15;
-
-  // ---- stage exp(logit - max) and the scale/zero tile of this chunk
-  for (int i = threadIdx.x; i < chunk_pad; i += NTHREADS) {
-    int64_t pos = 0;
-    const bool live = i < chunk_n;
-    if (live) pos = (ti == HQKV_NUM_TIERS) ? (P.L - T.n_v + chunk_t0 + i) : T.v_idx[chunk_t0 + i];
-    for (int h = 0; h < rep; ++h) {
-      float e = 0.f;
-      if (live) {
-        const float x = P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L + pos];
-        e = exp2f((x - sh.gm[h]) * 1.4426950408889634f);
-      }
-      sh.e[h][i] = __float2half_rn(e);
+    for (int j = 0; j < V_STAGE_ITERS; ++j) {
+      const int i = tid + j * NTHREADS;
+      x[j] = i < chunk_n ? __ldcg(row + pos[j]) : -INFINITY;
     }
-  }
-  if (ti != HQKV_NUM_TIERS && T.bits != 16) {
-    const int ng = D >> P.gv_shift;
-    const __half* s = T.v_scale + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
-    const __half* z = T.v_zero + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
-    for (int i = threadIdx.x; i < chunk_pad * ng; i += NTHREADS) {
-      const int t = i / ng, gi = i - t * ng;
-      const bool live = t < chunk_n;
-      sh.s[gi][t] = live ? s[i] : __float2half(0.f);
-      sh.z[gi][t] = live ? z[i] : __float2half(0.f);
+#pragma unroll
+    for (int j = 0; j < V_STAGE_ITERS; ++j) {
+      const int i = tid + j * NTHREADS;
+      if (i < chunk_pad) sh.e[h][i] = __float2half_rn(exp2f((x[j] - mh) * 1.4426950408889634f));
     }
   }
   __syncthreads();
@@ -652,7 +910,7 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const int vb = (ti == HQKV_NUM_TIERS) ? 16 : T.bits;
+  const int vb = is_res ? 16 : T.bits;
   if (vb == 8) {
     v_chunk<8>(P, T, sh, bh, chunk_t0, chunk_n, acc);
     v_store_acc<8>(sh, acc, rep);
@@ -669,7 +927,7 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
   __syncthreads();
   // partial output of this chunk: warps added in index order
   float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
-  for (int i = threadIdx.x; i < rep * D; i += NTHREADS) {
+  for (int i = tid; i < rep * D; i += NTHREADS) {
     const int h = i / D, ch = i - h * D;
     float v = sh.red[0][h][ch];
 #pragma unroll
@@ -683,15 +941,16 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     for (int h = 0; h < rep; ++h) {
       const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
       const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
-      for (int p = p0 + threadIdx.x; p < p1; p += NTHREADS)
-        P.weights[row + p] = __float2half_rn(exp2f((P.logits[row + p] - mh) * 1.4426950408889634f) * inv);
+#pragma unroll 4
+      for (int p = p0 + tid; p < p1; p += NTHREADS)
+        P.weights[row + p] = __float2half_rn(exp2f((__ldcg(P.logits + row + p) - mh) * 1.4426950408889634f) * inv);
     }
   }
 
   // ---- last CTA of this (batch, kv head) sums the partial outputs in chunk order
   __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (tid == 0) {
     const unsigned prev = atomicAdd(&P.counters[bh], 1u);
     sh.is_last = (prev == static_cast<unsigned>(P.nv_chunks) - 1u) ? 1u : 0u;
   }
@@ -699,13 +958,22 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
   if (sh.is_last) {
     __threadfence();
     const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
-    for (int i = threadIdx.x; i < rep * D; i += NTHREADS) {
+    const int64_t stride = static_cast<int64_t>(rep) * D;
+    for (int i = tid; i < rep * D; i += NTHREADS) {
       const int h = i / D;
       float v = 0.f;
-      for (int c = 0; c < P.nv_chunks; ++c) v += __ldcg(all + static_cast<int64_t>(c) * rep * D + i);
+      int c = 0;
+      for (; c + 8 <= P.nv_chunks; c += 8) {  // eight loads in flight, added in chunk order
+        float t[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t[k] = __ldcg(all + (c + k) * stride + i);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) v += t[k];
+      }
+      for (; c < P.nv_chunks; ++c) v += __ldcg(all + c * stride + i);
       P.out[(static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i] = __float2half_rn(v / sh.gl[h]);
     }
-    if (threadIdx.x == 0) P.counters[bh] = 0u;  // ready for the next call
+    if (tid == 0) P.counters[bh] = 0u;  // ready for the next call
   }
 }
 
@@ -740,6 +1008,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.gk_shift = ilog2(c->group_k);
   P.gv_shift = ilog2(c->group_v);
   P.scale = c->softmax_scale;
+  P.k_max_bits = 2;
   static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
   int64_t nk_total = 0, nv_total = 0;
   int kc = 0, vc = 0;
@@ -760,7 +1029,8 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
         HQKV_REQUIRE(s.k_scale && s.k_zero, "decode: tier %d K scale/zero pointers are null", t);
         HQKV_REQUIRE(s.n_k % c->group_k == 0, "decode: tier %d K holds %d tokens, not a multiple of the K group %d", t,
                      s.n_k, c->group_k);
-        HQKV_REQUIRE(aligned(s.k_data, 8), "decode: tier %d K codes must be 8-byte aligned", t);
+        HQKV_REQUIRE(aligned(s.k_data, 16), "decode: tier %d K codes must be 16-byte aligned", t);
+        if (s.bits > P.k_max_bits) P.k_max_bits = s.bits;
       } else {
         HQKV_REQUIRE(s.n_k % 8 == 0 && aligned(s.k_data, 16),
                      "decode: the fp16 K tier needs a token count that is a multiple of 8 and 16-byte alignment");
@@ -768,7 +1038,9 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     }
     if (s.n_v > 0) {
       HQKV_REQUIRE(s.v_data && s.v_idx, "decode: tier %d V pointers are null", t);
-      if (s.bits < 16) HQKV_REQUIRE(s.v_scale && s.v_zero, "decode: tier %d V scale/zero pointers are null", t);
+      if (s.bits < 16)
+        HQKV_REQUIRE(s.v_scale && s.v_zero && aligned(s.v_scale, 8) && aligned(s.v_zero, 8),
+                     "decode: tier %d V scale/zero pointers are null or not 8-byte aligned", t);
       HQKV_REQUIRE(aligned(s.v_data, 16), "decode: tier %d V data must be 16-byte aligned", t);
     }
     d.k_data = s.k_data;
@@ -781,8 +1053,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.v_idx = s.v_idx;
     // chunk sizes: about the same number of bytes per CTA whatever the width
     const int b = d.bits;
-    d.k_chunk_tokens = b == 16 ? 512 : b == 8 ? 512 : b == 4 ? 512 : 1024;
-    if ((d.k_chunk_tokens >> P.gk_shift) > MAX_K_GROUPS) d.k_chunk_tokens = MAX_K_GROUPS << P.gk_shift;
+    d.k_chunk_tokens = b == 16 ? 512 : K_CHUNK;
     d.v_chunk_tokens = b == 16 ? 256 : b == 8 ? 384 : b == 4 ? 640 : 1024;
     d.k_chunk0 = kc;
     d.v_chunk0 = vc;
@@ -864,20 +1135,25 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
   const dim3 block(NTHREADS);
   const unsigned BH = static_cast<unsigned>(P.B * P.H);
   HQKV_REQUIRE(BH <= 65535, "decode: B*H too large");
-  if (phases & 1) {
-    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, 0, st>>>(P);
-    HQKV_LAUNCH_CHECK("k_pass");
-  }
-  if (phases & 2) {
+  {
     // opt in to >48 KB of dynamic shared memory once per device
     static bool attr_set[64] = {};
     int dev = 0;
     HQKV_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+      HQKV_CUDA(cudaFuncSetAttribute(k_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     k_smem_layout(MAX_REP, 8).total));
       HQKV_CUDA(cudaFuncSetAttribute(v_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(sizeof(VShared))));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
+  }
+  if (phases & 1) {
+    const int ksmem = k_smem_layout(P.rep, P.k_max_bits).total;
+    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, ksmem, st>>>(P);
+    HQKV_LAUNCH_CHECK("k_pass");
+  }
+  if (phases & 2) {
     v_pass_kernel<<<dim3(P.nv_chunks, BH), block, sizeof(VShared), st>>>(P);
     HQKV_LAUNCH_CHECK("v_pass");
   }

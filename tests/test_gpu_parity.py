@@ -120,7 +120,9 @@ def test_codec_constant_group_and_roundtrip(ops, cuda_device):
 
 def test_codec_full_size_roundtrip_property(ops, cuda_device):
     """At the benchmark's full flush size (32k tokens x 8 heads) the dequantised values must lie
-    within half a quantisation step (plus fp16 rounding) of the input."""
+    within about half a quantisation step of the input: 0.5 from the rounding to a code, up to 0.0625
+    more because the quotient is itself rounded to fp16 before that (ulp 0.125 above 128), plus the
+    two fp16 roundings of the dequantiser (about 1e-3 of |x| each)."""
     gen = torch.Generator(device=cuda_device).manual_seed(3)
     x = torch.randn(1, 8, 32640, 128, generator=gen, device=cuda_device).half()
     for bit in (8, 4, 2):
@@ -128,7 +130,7 @@ def test_codec_full_size_roundtrip_property(ops, cuda_device):
         deq = ops.pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, 32, bit)
         step = scale.float().repeat_interleave(32, dim=-1)
         err = (deq.float() - x.float()).abs()
-        assert bool((err <= 0.5 * step * 1.01 + 4e-3 * x.float().abs() + 1e-3).all()), f"bit {bit}"
+        assert bool((err <= 0.57 * step + 3e-3 * x.float().abs() + 2e-3).all()), f"bit {bit}"
         kt = x.transpose(2, 3)
         code_k, scale_k, mn_k = ops.pu.uniform_group_quantize_pack_last_dim(kt, 32, bit)
         code_c, scale_c, mn_c = ops.pu.uniform_group_quantize_pack_last_dim(kt.contiguous(), 32, bit)
