@@ -130,7 +130,9 @@ def test_codec_full_size_roundtrip_property(ops, cuda_device):
         deq = ops.pu.uniform_group_dequantize_unpack_last_dim(code, scale, mn, 32, bit)
         step = scale.float().repeat_interleave(32, dim=-1)
         err = (deq.float() - x.float()).abs()
-        assert bool((err <= 0.57 * step + 3e-3 * x.float().abs() + 2e-3).all()), f"bit {bit}"
+        rng = step * (2 ** bit - 1)          # (x - mn) and code*scale reach the group's range: their fp16 ulp
+        bound = 0.57 * step + 2e-3 * rng + 1e-3 * x.float().abs() + 1e-3
+        assert bool((err <= bound).all()), f"bit {bit}: worst excess {(err - bound).max().item():.3e}"
         kt = x.transpose(2, 3)
         code_k, scale_k, mn_k = ops.pu.uniform_group_quantize_pack_last_dim(kt, 32, bit)
         code_c, scale_c, mn_c = ops.pu.uniform_group_quantize_pack_last_dim(kt.contiguous(), 32, bit)
