@@ -51,7 +51,6 @@ struct DecodeParams {
   int gk_shift, gv_shift;
   int nk_chunks, nv_chunks;
   int w_slice;  // logical positions normalised per v_pass CTA
-  int k_max_bits;  // widest quantised K tier present (sizes the k_pass shared-memory data region)
   float scale;
   const __half* q;
   __half* weights;
@@ -250,256 +249,245 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
 
 
 // ------------------------------------------------------------------------------------------------
-// cp.async helpers (global -> shared without a register round trip; no barrier objects, nothing to
-// spin on: completion is a per-thread wait_group followed by __syncthreads)
-// ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src));
-}
-__device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
-  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(smem_u32(dst)), "l"(src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
-
-// ------------------------------------------------------------------------------------------------
 // k_pass
 // ------------------------------------------------------------------------------------------------
-// Quantised K tier, rows = channels, packed words along tokens.  A CTA takes a chunk of up to
-// K_MAXBLK blocks of 32 tokens for one (batch, kv head):
-//   1. the chunk's packed bytes of all 128 channel rows stream into shared memory with cp.async
-//      (fully coalesced 16-byte pieces, the whole chunk in flight at once);
-//   2. meanwhile the scale/zero tile is staged and, per scale group, the B operand
-//      q_h[d] * scale[d, group] is formed in fp32 and split into an fp16 high and low part, and
-//      Zq[group][h] = sum_d q_h[d] * zero[d, group] is accumulated in fp32;
-//   3. each warp takes blocks: the A operand holds the EXACT integer codes (fp16 integers), so
-//      logit = sum_d code * (hi + lo) + Zq reproduces the fp32 dequant-matmul to ~2^-22: the only
-//      rounding left is the fp32 accumulation itself.
-// All 16 rows of an M-tile lie in one 32-token block, hence one scale group, which is what lets the
-// scale move into the B operand.  Within a block, lane group g owns tokens 4g..4g+3.
-constexpr int K_BLOCK = 32;
-constexpr int K_MAXBLK = 8;
-constexpr int K_CHUNK = K_BLOCK * K_MAXBLK;  // 256 tokens
-constexpr int K_SROW = D + SCALE_PAD;        // halfs per staged scale row
+// Quantised K tier: rows = channels, packed words along tokens.  A CTA takes a chunk of 512 tokens
+// (16 scale groups at group 32) of one (batch, kv head); each warp takes one 128-token span:
+// fragment row g <-> the 8 tokens of word slot g, row g+8 <-> slot g+8, M-tile i <-> i-th token of
+// every slot, so a thread uses every code of every word it loads and no operand passes through
+// shared memory.  Words go global -> registers one 16-channel step ahead of their use.
+//
+// Precision: the logits must match an fp32 dequant-matmul, and with x10 outlier channels the fp16
+// rounding of a dequantised K value alone costs ~2e-3 on the attention output.  So the product
+// code*scale (8 + 11 significant bits) is carried EXACTLY as two fp16 numbers, hi = fp16(code*scale)
+// and lo = fma(code, scale, -hi), each multiplied with q on the tensor pipe into the same fp32
+// accumulator, and the zero point enters through Zq[group][head] = sum_d zero[d,group]*q[head][d],
+// itself one small MMA per 16-channel step (fp16 inputs are exact, fp32 accumulation).
+constexpr int K_SPAN = 128;                 // tokens per warp span
+constexpr int K_CHUNK = NWARP * K_SPAN;     // 512 tokens per CTA
+constexpr int K_MAXG = K_CHUNK / 32;        // 16 scale groups per chunk at group size 32
+constexpr int K_SROW = D + SCALE_PAD;       // halfs per staged scale row
 
-__host__ __device__ constexpr int k_row_bytes(int bits) { return K_MAXBLK * 4 * bits + 16; }  // + pad: no bank conflicts
-
-struct KSmemLayout {
-  int qfrag, qs, s, z, zq, red, bhi, blo, data, total;
+struct KShared {
+  uint2 qfrag[8][32];          // B fragments of q per 16-channel step and lane
+  __half s[K_MAXG][K_SROW];    // scale[group][channel]
+  __half z[K_MAXG][K_SROW];    // zero[group][channel]
+  float zq[K_MAXG][MAX_REP];   // sum_d zero*q per group and head
+  float red_m[NWARP][MAX_REP], red_l[NWARP][MAX_REP];
 };
-__host__ __device__ inline KSmemLayout k_smem_layout(int rep, int max_bits) {
-  KSmemLayout l;
-  int off = 0;
-  l.qfrag = off; off += 8 * 32 * 8;
-  l.qs = off; off += MAX_REP * D * 2;
-  l.s = off; off += K_MAXBLK * K_SROW * 2;
-  l.z = off; off += K_MAXBLK * K_SROW * 2;
-  l.zq = off; off += K_MAXBLK * MAX_REP * 4;
-  l.red = off; off += 2 * NWARP * MAX_REP * 4;
-  l.bhi = off; off += K_MAXBLK * 8 * 4 * rep * 8;
-  l.blo = off; off += K_MAXBLK * 8 * 4 * rep * 8;
-  off = (off + 15) & ~15;
-  l.data = off; off += D * k_row_bytes(max_bits);
-  l.total = off;
-  return l;
-}
 
-// token offset inside a block of the value held by (row slot, M-tile) of lane group g
+// one slot = 8 tokens of one channel
 template <int BITS>
-__device__ __forceinline__ int k_token_offset(int g, int slot, int m) {
-  return BITS == 4 ? 4 * g + 2 * slot + m : 4 * g + slot + 2 * m;
-}
+struct KSlot;
+template <>
+struct KSlot<8> {
+  using word_t = uint2;
+  static __device__ __forceinline__ uint2 load(const void* row, int64_t slot) {
+    return ld_stream(reinterpret_cast<const uint2*>(row) + slot);
+  }
+};
+template <>
+struct KSlot<4> {
+  using word_t = uint32_t;
+  static __device__ __forceinline__ uint32_t load(const void* row, int64_t slot) {
+    return ld_stream(reinterpret_cast<const uint32_t*>(row) + slot);
+  }
+};
+template <>
+struct KSlot<2> {
+  using word_t = uint32_t;
+  static __device__ __forceinline__ uint32_t load(const void* row, int64_t slot) {
+    unsigned short v;
+    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(reinterpret_cast<const uint16_t*>(row) + slot));
+    return v;
+  }
+};
 
-// Exact integer codes of one 16-channel step of one block as A fragments for both M-tiles.
-// a[m][0..3] = fragment registers of M-tile m.
+// Exact integer codes (as fp16 pairs: low half = row a, high half = row b) of the 8 tokens of a slot.
 template <int BITS>
-__device__ __forceinline__ void k_codes(const unsigned char* data, int row_bytes, int kt, int blk, int g, int tig,
-                                        uint32_t (&a)[2][4]) {
+__device__ __forceinline__ void slot_codes(const typename KSlot<BITS>::word_t& wa, const typename KSlot<BITS>::word_t& wb,
+                                           __half2 (&c)[8]) {
   const __half2 k1024 = __half2half2(__float2half(1024.f));
-  uint32_t w[4];
+  if constexpr (BITS == 8) {
 #pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
-    const unsigned char* src = data + ch * row_bytes + blk * (4 * BITS);
-    if constexpr (BITS == 8) w[p] = *reinterpret_cast<const uint32_t*>(src + 4 * g);
-    else if constexpr (BITS == 4) w[p] = *reinterpret_cast<const uint16_t*>(src + 2 * g);
-    else w[p] = src[g];
-  }
+    for (int half = 0; half < 2; ++half) {
+      const uint32_t a = half ? wa.y : wa.x, b = half ? wb.y : wb.x;
+      const uint32_t lo = __byte_perm(a, b, 0x5140);  // [a0 b0 a1 b1]
+      const uint32_t hi = __byte_perm(a, b, 0x7362);  // [a2 b2 a3 b3]
+      c[half * 4 + 0] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1024);
+      c[half * 4 + 1] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1024);
+      c[half * 4 + 2] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1024);
+      c[half * 4 + 3] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1024);
+    }
+  } else if constexpr (BITS == 4) {
+    const __half2 k16th = __half2half2(__float2half(0.0625f)), km64 = __half2half2(__float2half(-64.f));
 #pragma unroll
-  for (int q = 0; q < 2; ++q) {  // channel pair (2tig,2tig+1) / (+8,+9) -> fragment registers q*2 + slot
-    const uint32_t wa = w[2 * q], wb = w[2 * q + 1];
-    if constexpr (BITS == 8) {
-      // bytes: 0 = (slot0,m0), 1 = (slot1,m0), 2 = (slot0,m1), 3 = (slot1,m1)
-      const uint32_t lo = __byte_perm(wa, wb, 0x5140);  // [a0 b0 a1 b1]
-      const uint32_t hi = __byte_perm(wa, wb, 0x7362);  // [a2 b2 a3 b3]
-      const uint32_t x00 = __byte_perm(lo, 0x64646464u, 0x4140), x10 = __byte_perm(lo, 0x64646464u, 0x4342);
-      const uint32_t x01 = __byte_perm(hi, 0x64646464u, 0x4140), x11 = __byte_perm(hi, 0x64646464u, 0x4342);
-      a[0][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x00), k1024));
-      a[0][q * 2 + 1] = h2_as_u32(__hsub2(u32_as_h2(x10), k1024));
-      a[1][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x01), k1024));
-      a[1][q * 2 + 1] = h2_as_u32(__hsub2(u32_as_h2(x11), k1024));
-    } else if constexpr (BITS == 4) {
-      // byte 0 = slot 0, byte 1 = slot 1; low nibble = m0, high nibble = m1
-      const __half2 k16th = __half2half2(__float2half(0.0625f)), k64 = __half2half2(__float2half(-64.f));
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+      c[2 * j] = __hsub2(u32_as_h2((t & 0x000F000Fu) | 0x64006400u), k1024);
+      c[2 * j + 1] = __hfma2(u32_as_h2((t & 0x00F000F0u) | 0x64006400u), k16th, km64);
+    }
+  } else {
 #pragma unroll
-      for (int slot = 0; slot < 2; ++slot) {
-        const uint32_t t = __byte_perm(wa, wb, slot == 0 ? 0x4400 : 0x5511);
-        const uint32_t x0 = (t & 0x000F000Fu) | 0x64006400u;
-        const uint32_t x1 = (t & 0x00F000F0u) | 0x64006400u;
-        a[0][q * 2 + slot] = h2_as_u32(__hsub2(u32_as_h2(x0), k1024));
-        a[1][q * 2 + slot] = h2_as_u32(__hfma2(u32_as_h2(x1), k16th, k64));
-      }
-    } else {
-      // one byte: crumb k = slot + 2*m
-      const uint32_t t = __byte_perm(wa, wb, 0x4400);
-      const uint32_t x0 = (t & 0x00030003u) | 0x64006400u;  // slot0 m0
-      const uint32_t x1 = (t & 0x000C000Cu) | 0x64006400u;  // slot1 m0   (1024 + 4c)
-      const uint32_t x2 = (t & 0x00300030u) | 0x64006400u;  // slot0 m1   (1024 + 16c)
-      const uint32_t x3 = (t & 0x00C000C0u) | 0x64006400u;  // slot1 m1   (1024 + 64c)
-      a[0][q * 2 + 0] = h2_as_u32(__hsub2(u32_as_h2(x0), k1024));
-      a[0][q * 2 + 1] = h2_as_u32(__hfma2(u32_as_h2(x1), __half2half2(__float2half(0.25f)), __half2half2(__float2half(-256.f))));
-      a[1][q * 2 + 0] = h2_as_u32(__hfma2(u32_as_h2(x2), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f))));
-      a[1][q * 2 + 1] = h2_as_u32(__hfma2(u32_as_h2(x3), __half2half2(__float2half(0.015625f)), __half2half2(__float2half(-16.f))));
+    for (int j = 0; j < 2; ++j) {
+      const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+      c[4 * j + 0] = __hsub2(u32_as_h2((t & 0x00030003u) | 0x64006400u), k1024);
+      c[4 * j + 1] = __hfma2(u32_as_h2((t & 0x000C000Cu) | 0x64006400u), __half2half2(__float2half(0.25f)),
+                             __half2half2(__float2half(-256.f)));
+      c[4 * j + 2] = __hfma2(u32_as_h2((t & 0x00300030u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
+                             __half2half2(__float2half(-64.f)));
+      c[4 * j + 3] = __hfma2(u32_as_h2((t & 0x00C000C0u) | 0x64006400u), __half2half2(__float2half(0.015625f)),
+                             __half2half2(__float2half(-16.f)));
     }
   }
 }
 
 template <int BITS>
-__device__ __forceinline__ void k_quant_chunk(const DecodeParams& P, const TierDev& T, unsigned char* smem,
-                                              const KSmemLayout& lay, int bh, int b, int kvh, int chunk_t0,
-                                              float (&m_run)[2], float (&l_run)[2]) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-  const int rep = P.rep;
+__device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                       int chunk_t0, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
+  using word_t = typename KSlot<BITS>::word_t;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
-  const int ntok = min(K_CHUNK, n - chunk_t0);
-  const int nblk = ntok / K_BLOCK;
-  constexpr int BPB = 4 * BITS;              // bytes per block and channel
-  constexpr int PIECE = BITS == 2 ? 8 : 16;  // cp.async granularity (2-bit rows are only 8-byte aligned)
-  constexpr int ROWB = k_row_bytes(BITS);
-  unsigned char* data = smem + lay.data;
-  // 1. stream the packed bytes of the chunk
-  {
-    const int ppr = nblk * BPB / PIECE;  // pieces per channel row
-    const int64_t row_total = static_cast<int64_t>(n) * BITS / 8;
-    const unsigned char* src0 = reinterpret_cast<const unsigned char*>(T.k_data) +
-                                static_cast<int64_t>(bh) * D * row_total + static_cast<int64_t>(chunk_t0) * BITS / 8;
-    for (int i = tid; i < D * ppr; i += NTHREADS) {
-      const int row = i / ppr, pc = i - row * ppr;
-      if constexpr (PIECE == 16) cp_async_16(data + row * ROWB + pc * 16, src0 + row * row_total + pc * 16);
-      else cp_async_8(data + row * ROWB + pc * 8, src0 + row * row_total + pc * 8);
-    }
-    cp_async_commit();
+  const int64_t nslot = n / 8;                        // slots per channel row
+  const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
+  const unsigned char* base = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes;
+  int64_t sl[2];
+  bool ok[2];
+  int gl[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    sl[r] = span_t0 / 8 + r * 8 + g;
+    ok[r] = sl[r] < nslot;
+    gl[r] = ok[r] ? (((static_cast<int>(sl[r]) * 8) >> P.gk_shift) - (chunk_t0 >> P.gk_shift)) : 0;
   }
-  // 2. stage scale / zero of the chunk as [group][channel]; all loads of a thread are issued before any store
-  const int bshift = P.gk_shift - 5;                     // blocks per scale group = 1 << bshift
-  const int ng = (nblk + (1 << bshift) - 1) >> bshift;   // scale groups of the chunk
-  __half* ssm = reinterpret_cast<__half*>(smem + lay.s);
-  __half* zsm = reinterpret_cast<__half*>(smem + lay.z);
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+
+  word_t w[4][2], wn[4][2];
+  auto load = [&](word_t (&dst)[4][2], int kt) {
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
+      const unsigned char* row = base + ch * row_bytes;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        if (ok[r]) dst[p][r] = KSlot<BITS>::load(row, sl[r]);
+        else dst[p][r] = word_t{};
+      }
+    }
+  };
+  load(w, 0);
+  int pos[2][8];  // logical positions of this lane's 16 tokens (fetched while the last steps compute)
+#pragma unroll 1
+  for (int kt = 0; kt < 8; ++kt) {
+    if (kt + 1 < 8) load(wn, kt + 1);
+    if (kt == 6) {
+#pragma unroll
+      for (int r = 0; r < 2; ++r)
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pos[r][i] = ok[r] ? static_cast<int>(T.k_idx[sl[r] * 8 + i]) : 0;
+    }
+    const uint2 bq = sh.qfrag[kt][lane];
+    // fragment register q*2 + r: channel pair q (2tig,2tig+1 | +8,+9), row slot r
+    __half2 hi[4][8], lo[4][8];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const __half2 s2 = *reinterpret_cast<const __half2*>(&sh.s[gl[r]][kt * 16 + 2 * tig + q * 8]);
+        __half2 c[8];
+        slot_codes<BITS>(w[2 * q][r], w[2 * q + 1][r], c);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          hi[q * 2 + r][i] = __hmul2(c[i], s2);
+          lo[q * 2 + r][i] = __hfma2(c[i], s2, __hneg2(hi[q * 2 + r][i]));
+        }
+      }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      mma16816(acc[i], h2_as_u32(hi[0][i]), h2_as_u32(hi[1][i]), h2_as_u32(hi[2][i]), h2_as_u32(hi[3][i]), bq.x, bq.y);
+      mma16816(acc[i], h2_as_u32(lo[0][i]), h2_as_u32(lo[1][i]), h2_as_u32(lo[2][i]), h2_as_u32(lo[3][i]), bq.x, bq.y);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      w[p][0] = wn[p][0];
+      w[p][1] = wn[p][1];
+    }
+  }
+  // logits of heads 2tig, 2tig+1 at the tokens' logical positions
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    if (!ok[r]) continue;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int h = 2 * tig + e;
+      if (h < P.rep) {
+        float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L;
+        const float zq = sh.zq[gl[r]][h];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float x = (acc[i][r * 2 + e] + zq) * P.scale;
+          row[pos[r][i]] = x;
+          softmax_push(m_run[e], l_run[e], x);
+        }
+      }
+    }
+  }
+}
+
+template <int BITS>
+__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                        int chunk_t0, float (&m_run)[2], float (&l_run)[2]) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+  const int chunk_end = min(chunk_t0 + K_CHUNK, T.n_k);
+  // stage scale/zero of the chunk as [group][channel]: lanes run along the groups of one channel row
+  // (contiguous in memory), all loads of a thread are issued before the first store
   {
-    const int G = n >> P.gk_shift, g0 = chunk_t0 >> P.gk_shift;
+    const int G = T.n_k >> P.gk_shift, g0 = chunk_t0 >> P.gk_shift;
+    const int ng = ((chunk_end - chunk_t0) + (1 << P.gk_shift) - 1) >> P.gk_shift;  // <= K_MAXG
     const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G + g0;
     const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G + g0;
-    __half sv[K_MAXBLK], zv[K_MAXBLK];
+    __half sv[K_MAXG], zv[K_MAXG];
+    const int gi = tid & (K_MAXG - 1);
 #pragma unroll
-    for (int j = 0; j < K_MAXBLK; ++j) {
-      const int i = tid + j * NTHREADS;
-      if (i < D * ng) {
-        const int ch = i / ng, gi = i - ch * ng;
+    for (int j = 0; j < K_MAXG; ++j) {
+      const int ch = (tid >> 4) + j * (NTHREADS / K_MAXG);
+      sv[j] = zv[j] = __float2half(0.f);
+      if (gi < ng) {
         sv[j] = s[static_cast<int64_t>(ch) * G + gi];
         zv[j] = z[static_cast<int64_t>(ch) * G + gi];
       }
     }
 #pragma unroll
-    for (int j = 0; j < K_MAXBLK; ++j) {
-      const int i = tid + j * NTHREADS;
-      if (i < D * ng) {
-        const int ch = i / ng, gi = i - ch * ng;
-        ssm[gi * K_SROW + ch] = sv[j];
-        zsm[gi * K_SROW + ch] = zv[j];
-      }
+    for (int j = 0; j < K_MAXG; ++j) {
+      const int ch = (tid >> 4) + j * (NTHREADS / K_MAXG);
+      sh.s[gi][ch] = sv[j];
+      sh.z[gi][ch] = zv[j];
     }
   }
   __syncthreads();
-  // 3. per scale group: B = q*scale split into fp16 hi + lo, Zq = sum_d q*zero.  One warp per group,
-  //    lane = (16-channel step kt, tig) unit, which is also the B-fragment lane layout.
-  const __half* qs = reinterpret_cast<const __half*>(smem + lay.qs);
-  uint2* bhi = reinterpret_cast<uint2*>(smem + lay.bhi);
-  uint2* blo = reinterpret_cast<uint2*>(smem + lay.blo);
-  float* zq = reinterpret_cast<float*>(smem + lay.zq);
-  for (int gi = warp; gi < ng; gi += NWARP) {
-    const int kt = lane >> 2, tg = lane & 3;
-    const int c0 = kt * 16 + 2 * tg;
-    const float2 s01 = __half22float2(*reinterpret_cast<const __half2*>(ssm + gi * K_SROW + c0));
-    const float2 s23 = __half22float2(*reinterpret_cast<const __half2*>(ssm + gi * K_SROW + c0 + 8));
-    const float2 z01 = __half22float2(*reinterpret_cast<const __half2*>(zsm + gi * K_SROW + c0));
-    const float2 z23 = __half22float2(*reinterpret_cast<const __half2*>(zsm + gi * K_SROW + c0 + 8));
-    for (int h = 0; h < rep; ++h) {
-      const float2 q01 = __half22float2(*reinterpret_cast<const __half2*>(qs + h * D + c0));
-      const float2 q23 = __half22float2(*reinterpret_cast<const __half2*>(qs + h * D + c0 + 8));
-      const float p0 = q01.x * s01.x, p1 = q01.y * s01.y, p2 = q23.x * s23.x, p3 = q23.y * s23.y;
-      const __half2 h01 = __floats2half2_rn(p0, p1), h23 = __floats2half2_rn(p2, p3);
-      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23);
-      const __half2 l01 = __floats2half2_rn(p0 - f01.x, p1 - f01.y), l23 = __floats2half2_rn(p2 - f23.x, p3 - f23.y);
-      const int e = ((gi * 8 + kt) * 4 + tg) * rep + h;
-      bhi[e] = make_uint2(h2_as_u32(h01), h2_as_u32(h23));
-      blo[e] = make_uint2(h2_as_u32(l01), h2_as_u32(l23));
-      float zs = q01.x * z01.x;
-      zs = fmaf(q01.y, z01.y, zs);
-      zs = fmaf(q23.x, z23.x, zs);
-      zs = fmaf(q23.y, z23.y, zs);
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) zs += __shfl_xor_sync(0xffffffffu, zs, off);
-      if (lane == 0) zq[gi * MAX_REP + h] = zs;
-    }
-  }
-  cp_async_wait_all();
-  __syncthreads();
-  // 4. blocks of this warp
-  for (int blk = warp; blk < nblk; blk += NWARP) {
-    const int gi = blk >> bshift;
-    float acc[2][4];
-#pragma unroll
-    for (int m = 0; m < 2; ++m) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.f;
+  // Zq[group][head]: rows of the A operand are the 16 groups, columns the channels
+  if (warp == 0) {
+    float zacc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt) {
-      uint32_t a[2][4];
-      k_codes<BITS>(data, ROWB, kt, blk, g, tig, a);
-      uint2 bh2 = make_uint2(0u, 0u), bl2 = make_uint2(0u, 0u);
-      if (g < rep) {
-        const int e = ((gi * 8 + kt) * 4 + tig) * rep + g;
-        bh2 = bhi[e];
-        bl2 = blo[e];
-      }
-#pragma unroll
-      for (int m = 0; m < 2; ++m) {
-        mma16816(acc[m], a[m][0], a[m][1], a[m][2], a[m][3], bh2.x, bh2.y);
-        mma16816(acc[m], a[m][0], a[m][1], a[m][2], a[m][3], bl2.x, bl2.y);
-      }
+      const int ch = kt * 16 + 2 * tig;
+      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch]);
+      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sh.z[g + 8][ch]);
+      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch + 8]);
+      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sh.z[g + 8][ch + 8]);
+      const uint2 bq = sh.qfrag[kt][lane];
+      mma16816(zacc, a0, a1, a2, a3, bq.x, bq.y);
     }
-    // logits of heads 2tig, 2tig+1 for this lane's four tokens
-    const int64_t tok0 = static_cast<int64_t>(chunk_t0) + blk * K_BLOCK;
-    int64_t pos[4];
-#pragma unroll
-    for (int k = 0; k < 4; ++k) pos[k] = T.k_idx[tok0 + 4 * g + k];
-#pragma unroll
-    for (int slot = 0; slot < 2; ++slot)
-#pragma unroll
-      for (int m = 0; m < 2; ++m) {
-        const int k = k_token_offset<BITS>(0, slot, m);
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int h = 2 * tig + e;
-          if (h < rep) {
-            const float x = (acc[m][slot * 2 + e] + zq[gi * MAX_REP + h]) * P.scale;
-            P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L + pos[k]] = x;
-            softmax_push(m_run[e], l_run[e], x);
-          }
-        }
-      }
+    sh.zq[g][2 * tig] = zacc[0];
+    sh.zq[g][2 * tig + 1] = zacc[1];
+    sh.zq[g + 8][2 * tig] = zacc[2];
+    sh.zq[g + 8][2 * tig + 1] = zacc[3];
   }
+  __syncthreads();
+  const int span_t0 = chunk_t0 + warp * K_SPAN;
+  if (span_t0 < chunk_end) k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0, m_run, l_run);
 }
 
 // fp16 tier, channel-major rows [D][n]: eight tokens per 16-byte word, no scales; B = q exactly.
@@ -595,33 +583,24 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
   }
 }
 
-__global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  const KSmemLayout lay = k_smem_layout(P.rep, P.k_max_bits);
+__global__ void __launch_bounds__(NTHREADS, 4) k_pass_kernel(const __grid_constant__ DecodeParams P) {
+  __shared__ KShared sh;
   const int chunk = blockIdx.x, bh = blockIdx.y;
   const int b = bh / P.H, kvh = bh - b * P.H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-  uint2* qfrag = reinterpret_cast<uint2*>(smem + lay.qfrag);
-  __half* qs = reinterpret_cast<__half*>(smem + lay.qs);
-  float* red_m = reinterpret_cast<float*>(smem + lay.red);
-  float* red_l = red_m + NWARP * MAX_REP;
+  const uint2* qfrag = &sh.qfrag[0][0];
 
-  // q of this kv head's query heads: rows for the table build, B fragments for the fp16 paths
-  {
-    const __half* q0 = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * D;
-    for (int i = tid; i < P.rep * (D / 2); i += NTHREADS)
-      reinterpret_cast<uint32_t*>(qs)[i] = reinterpret_cast<const uint32_t*>(q0)[i];
-    if (warp == 0) {
-      const __half* qh = q0 + g * D;
+  // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
+  if (warp == 0) {
+    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
 #pragma unroll
-      for (int kt = 0; kt < 8; ++kt) {
-        uint2 f = make_uint2(0u, 0u);
-        if (g < P.rep) {
-          f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
-          f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
-        }
-        qfrag[kt * 32 + lane] = f;
+    for (int kt = 0; kt < 8; ++kt) {
+      uint2 f = make_uint2(0u, 0u);
+      if (g < P.rep) {
+        f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
+        f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
       }
+      sh.qfrag[kt][lane] = f;
     }
   }
 
@@ -644,11 +623,11 @@ __global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant_
         k_f16_span(P, T, qfrag, bh, b, kvh, t0, m_run, l_run);
     }
   } else if (T.bits == 8) {
-    k_quant_chunk<8>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
   } else if (T.bits == 4) {
-    k_quant_chunk<4>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
   } else {
-    k_quant_chunk<2>(P, T, smem, lay, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
   }
 
   // (max, sum) of this CTA per head: lanes with equal tig hold the same two heads
@@ -661,17 +640,18 @@ __global__ void __launch_bounds__(NTHREADS) k_pass_kernel(const __grid_constant_
       softmax_merge(m_run[e], l_run[e], m2, l2);
     }
     if (g == 0) {
-      red_m[warp * MAX_REP + 2 * tig + e] = m_run[e];
-      red_l[warp * MAX_REP + 2 * tig + e] = l_run[e];
+      sh.red_m[warp][2 * tig + e] = m_run[e];
+      sh.red_l[warp][2 * tig + e] = l_run[e];
     }
   }
   __syncthreads();
   if (tid < MAX_REP) {
-    float m = red_m[tid], l = red_l[tid];
-    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, red_m[w * MAX_REP + tid], red_l[w * MAX_REP + tid]);
+    float m = sh.red_m[0][tid], l = sh.red_l[0][tid];
+    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, sh.red_m[w][tid], sh.red_l[w][tid]);
     P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + tid] = make_float2(m, l);
   }
 }
+
 
 // ------------------------------------------------------------------------------------------------
 // v_pass
@@ -890,19 +870,29 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
   }
 
   // ---- exp(logit - max) of the chunk's tokens, per head: gathers batched per head
-  for (int h = 0; h < rep; ++h) {
-    const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
-    const float mh = sh.gm[h];
-    float x[V_STAGE_ITERS];
+  for (int h0 = 0; h0 < rep; h0 += 4) {  // four heads' gathers in flight together
+    float x[4][V_STAGE_ITERS];
 #pragma unroll
-    for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int i = tid + j * NTHREADS;
-      x[j] = i < chunk_n ? __ldcg(row + pos[j]) : -INFINITY;
+    for (int hh = 0; hh < 4; ++hh) {
+      const int h = min(h0 + hh, rep - 1);
+      const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+#pragma unroll
+      for (int j = 0; j < V_STAGE_ITERS; ++j) {
+        const int i = tid + j * NTHREADS;
+        x[hh][j] = i < chunk_n ? __ldcg(row + pos[j]) : -INFINITY;
+      }
     }
 #pragma unroll
-    for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int i = tid + j * NTHREADS;
-      if (i < chunk_pad) sh.e[h][i] = __float2half_rn(exp2f((x[j] - mh) * 1.4426950408889634f));
+    for (int hh = 0; hh < 4; ++hh) {
+      const int h = h0 + hh;
+      if (h < rep) {
+        const float mh = sh.gm[h];
+#pragma unroll
+        for (int j = 0; j < V_STAGE_ITERS; ++j) {
+          const int i = tid + j * NTHREADS;
+          if (i < chunk_pad) sh.e[h][i] = __float2half_rn(exp2f((x[hh][j] - mh) * 1.4426950408889634f));
+        }
+      }
     }
   }
   __syncthreads();
@@ -941,9 +931,19 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     for (int h = 0; h < rep; ++h) {
       const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
       const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
-#pragma unroll 4
-      for (int p = p0 + tid; p < p1; p += NTHREADS)
-        P.weights[row + p] = __float2half_rn(exp2f((__ldcg(P.logits + row + p) - mh) * 1.4426950408889634f) * inv);
+      for (int pb = p0 + tid; pb < p1; pb += 8 * NTHREADS) {
+        float x[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int p = pb + j * NTHREADS;
+          x[j] = p < p1 ? __ldcg(P.logits + row + p) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int p = pb + j * NTHREADS;
+          if (p < p1) P.weights[row + p] = __float2half_rn(exp2f((x[j] - mh) * 1.4426950408889634f) * inv);
+        }
+      }
     }
   }
 
@@ -959,19 +959,27 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     __threadfence();
     const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
     const int64_t stride = static_cast<int64_t>(rep) * D;
-    for (int i = tid; i < rep * D; i += NTHREADS) {
+    for (int i = tid * 4; i < rep * D; i += NTHREADS * 4) {  // four consecutive outputs per thread
       const int h = i / D;
-      float v = 0.f;
-      int c = 0;
-      for (; c + 8 <= P.nv_chunks; c += 8) {  // eight loads in flight, added in chunk order
-        float t[8];
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int c = 0; c < P.nv_chunks; c += 16) {  // sixteen 16-byte loads in flight, added in chunk order
+        float4 t[16];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) t[k] = __ldcg(all + (c + k) * stride + i);
+        for (int k = 0; k < 16; ++k)
+          t[k] = (c + k < P.nv_chunks) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) v += t[k];
+        for (int k = 0; k < 16; ++k) {
+          v.x += t[k].x;
+          v.y += t[k].y;
+          v.z += t[k].z;
+          v.w += t[k].w;
+        }
       }
-      for (; c < P.nv_chunks; ++c) v += __ldcg(all + c * stride + i);
-      P.out[(static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i] = __float2half_rn(v / sh.gl[h]);
+      const float inv = 1.f / sh.gl[h];
+      __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
+      o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
+      o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
     }
     if (tid == 0) P.counters[bh] = 0u;  // ready for the next call
   }
@@ -1008,7 +1016,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.gk_shift = ilog2(c->group_k);
   P.gv_shift = ilog2(c->group_v);
   P.scale = c->softmax_scale;
-  P.k_max_bits = 2;
   static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
   int64_t nk_total = 0, nv_total = 0;
   int kc = 0, vc = 0;
@@ -1030,7 +1037,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
         HQKV_REQUIRE(s.n_k % c->group_k == 0, "decode: tier %d K holds %d tokens, not a multiple of the K group %d", t,
                      s.n_k, c->group_k);
         HQKV_REQUIRE(aligned(s.k_data, 16), "decode: tier %d K codes must be 16-byte aligned", t);
-        if (s.bits > P.k_max_bits) P.k_max_bits = s.bits;
       } else {
         HQKV_REQUIRE(s.n_k % 8 == 0 && aligned(s.k_data, 16),
                      "decode: the fp16 K tier needs a token count that is a multiple of 8 and 16-byte alignment");
@@ -1054,7 +1060,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     // chunk sizes: about the same number of bytes per CTA whatever the width
     const int b = d.bits;
     d.k_chunk_tokens = b == 16 ? 512 : K_CHUNK;
-    d.v_chunk_tokens = b == 16 ? 256 : b == 8 ? 384 : b == 4 ? 640 : 1024;
+    d.v_chunk_tokens = b == 16 ? 256 : b == 8 ? 256 : b == 4 ? 384 : 640;
     d.k_chunk0 = kc;
     d.v_chunk0 = vc;
     kc += static_cast<int>(ceil_div(d.n_k, d.k_chunk_tokens));
@@ -1141,16 +1147,13 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
     int dev = 0;
     HQKV_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-      HQKV_CUDA(cudaFuncSetAttribute(k_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     k_smem_layout(MAX_REP, 8).total));
       HQKV_CUDA(cudaFuncSetAttribute(v_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(sizeof(VShared))));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
   }
   if (phases & 1) {
-    const int ksmem = k_smem_layout(P.rep, P.k_max_bits).total;
-    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, ksmem, st>>>(P);
+    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, 0, st>>>(P);
     HQKV_LAUNCH_CHECK("k_pass");
   }
   if (phases & 2) {

@@ -51,10 +51,11 @@ def gather_head_outputs(out_local: torch.Tensor, group=None, buffer: torch.Tenso
     """All-gather per-rank attention outputs [B, nh_q/world, 1, D] into [B, nh_q, 1, D] (head order =
     rank order).  ``buffer`` ([world, B, nh_q/world, 1, D]) can be passed to avoid the allocation."""
     world = dist.get_world_size(group)
+    B, nh_local, one, D = out_local.shape
     if buffer is None:
         buffer = torch.empty((world,) + tuple(out_local.shape), dtype=out_local.dtype, device=out_local.device)
-    dist.all_gather_into_tensor(buffer, out_local.contiguous(), group=group)
-    B, nh_local, one, D = out_local.shape
+    # the output is the concatenation of the ranks' tensors along dim 0 (the shape every backend accepts)
+    dist.all_gather_into_tensor(buffer.view(world * B, nh_local, one, D), out_local.contiguous(), group=group)
     return buffer.permute(1, 0, 2, 3, 4).reshape(B, world * nh_local, one, D)
 
 
@@ -62,8 +63,10 @@ def reduce_importance_row(partial_f32: torch.Tensor, group=None):
     """Head-summed probability row from per-rank fp32 partial sums [L]: gathered, added in rank order
     (the same order on every rank, so every rank gets the same bits), rounded to fp16 once."""
     world = dist.get_world_size(group)
-    parts = torch.empty((world,) + tuple(partial_f32.shape), dtype=torch.float32, device=partial_f32.device)
-    dist.all_gather_into_tensor(parts, partial_f32.contiguous().float(), group=group)
+    flat = partial_f32.contiguous().float().reshape(-1)
+    parts = torch.empty(world * flat.numel(), dtype=torch.float32, device=flat.device)
+    dist.all_gather_into_tensor(parts, flat, group=group)
+    parts = parts.view((world,) + tuple(partial_f32.shape))
     total = parts[0].clone()
     for r in range(1, world):
         total += parts[r]
