@@ -56,6 +56,8 @@ _SIGNATURES = {
                                         C.c_size_t, C.c_void_p]),
     "hqkv_decode_attention_phases": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_size_t, C.c_int, C.c_void_p]),
+    "hqkv_decode_static_scratch_bytes": (C.c_size_t, []),
+    "hqkv_decode_attention_static": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hqkv_gemv_uniform_group": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                           C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),
     "hqkv_head_sum": (C.c_int, [C.c_void_p, C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),

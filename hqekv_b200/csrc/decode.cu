@@ -1167,3 +1167,57 @@ extern "C" int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const 
                                      void* attn_output, void* workspace, size_t workspace_bytes, void* stream) {
   return hqkv_decode_attention_phases(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, stream);
 }
+
+// ------------------------------------------------------------------------------------------------
+// Decode attention for callers that may not allocate device memory
+// ------------------------------------------------------------------------------------------------
+// Some hosts of this library cannot obtain scratch at call time: a serving loop that has handed all
+// of the GPU's memory to its own pool, a latency-critical loop whose rules forbid allocation after
+// start-up (cudaMalloc may synchronise the device, and may fail late), or a binding whose language
+// runtime owns no device allocator.  For them the scratch of the two decode kernels lives in this
+// fixed array, which every GPU that loads the library holds until the process exits.
+//
+// g_static_scratch names the array in DEVICE code.  In host code the same identifier is only a
+// stand-in for the symbol, not a device address, so the host asks the runtime for the address once
+// per device (cudaGetSymbolAddress with that device current) and passes the pointer it gets.
+static __device__ __align__(256) unsigned char g_static_scratch[HQKV_STATIC_SCRATCH_BYTES];
+
+namespace hqkv {
+static void* g_static_scratch_ptr[64] = {};  // device address of the array, per device ordinal
+
+static int static_scratch_address(void** out) {
+  int dev = 0;
+  HQKV_CUDA(cudaGetDevice(&dev));
+  HQKV_REQUIRE(dev >= 0 && dev < 64, "decode_static: device ordinal %d out of range", dev);
+  if (!g_static_scratch_ptr[dev]) {
+    void* p = nullptr;
+    HQKV_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    HQKV_REQUIRE(p != nullptr, "decode_static: the scratch symbol has no address on device %d", dev);
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return HQKV_OK;
+}
+}  // namespace hqkv
+
+extern "C" size_t hqkv_decode_static_scratch_bytes(void) { return HQKV_STATIC_SCRATCH_BYTES; }
+
+extern "C" int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                            void* attn_output, void* stream) {
+  const size_t need = hqkv_decode_workspace_bytes(cache_host);
+  if (need == 0)  // invalid descriptor: let the regular path produce the precise message
+    return hqkv_decode_attention(cache_host, q, attn_weights, attn_output, nullptr, 0, stream);
+  if (need > HQKV_STATIC_SCRATCH_BYTES)
+    return fail(HQKV_E_WORKSPACE,
+                "decode_static: this cache needs %zu bytes of scratch, the built-in array holds %zu "
+                "(HQKV_STATIC_SCRATCH_BYTES); use hqkv_decode_attention with caller-provided scratch",
+                need, static_cast<size_t>(HQKV_STATIC_SCRATCH_BYTES));
+  void* scratch = nullptr;
+  int rc = static_scratch_address(&scratch);
+  if (rc) return rc;
+  // The array keeps whatever the previous call left.  Only the arrival counters have to start at
+  // zero; a finished call leaves them zero, an aborted one might not, so they are cleared every time
+  // (a stream-ordered memset, not an allocation).
+  HQKV_CUDA(cudaMemsetAsync(scratch, 0, HQKV_WS_COUNTER_BYTES, static_cast<cudaStream_t>(stream)));
+  return hqkv_decode_attention(cache_host, q, attn_weights, attn_output, scratch, HQKV_STATIC_SCRATCH_BYTES, stream);
+}

@@ -149,6 +149,30 @@ int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void
                                  void* attn_output, void* workspace, size_t workspace_bytes, int phases, void* stream);
 
 /*
+ * hqkv_decode_attention for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference, whose wrappers allocate freely through torch.
+ *
+ * Who needs it: a host that has given the whole GPU to its own memory pool, a latency-critical loop
+ * that may not allocate after start-up (cudaMalloc can synchronise the device and can fail late), or a
+ * language binding with no device allocator of its own.  Inputs and outputs are still the caller's; only the scratch of the
+ * two kernels comes from a fixed array of HQKV_STATIC_SCRATCH_BYTES inside the library, resident on
+ * every GPU that loads it for the life of the process.  The call allocates and frees nothing.
+ *
+ *  - Limit: caches whose hqkv_decode_workspace_bytes() exceeds HQKV_STATIC_SCRATCH_BYTES are refused
+ *    with HQKV_E_WORKSPACE (16 MiB covers batch 1 up to ~100k cached tokens with 32 query heads; the
+ *    need grows with B * nh_q * L * 4 bytes).
+ *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
+ *    that device current).  Make that first call outside any stream capture.
+ *  - All calls on a device share the one array, which keeps the previous call's contents (the
+ *    arrival counters are cleared at the start of every call).  Two calls that overlap on the GPU,
+ *    e.g. on different streams, race on it: order them on one stream or with events.
+ */
+#define HQKV_STATIC_SCRATCH_BYTES (16u << 20)
+size_t hqkv_decode_static_scratch_bytes(void);
+int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                 void* attn_output, void* stream);
+
+/*
  * Batched GEMV  C = fA x dequant(qB)  with the reference's un-transposed operand layout, fp32
  * accumulation, fp16 result.  Stands in for cuda_bmm_fA_qB_uniform_group (quant/matmul.py:263-299)
  * = transposes + kvhq_gemv.gemv_forward_cuda_uniform_group (quant/csrc/pybind.cpp:11,
