@@ -345,23 +345,33 @@ def main():
         w = torch.empty(cfg.batch, nh_q_local, 1, Ld, dtype=torch.float16, device=dev)
         o = torch.empty(cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
         descs.append((desc, keep, ws, w, o))
-    st = stream_ptr(dev)
-
     def run_phase(phase):
+        st = stream_ptr(dev)
         for i in range(layers):
             desc, _, ws, w, o = descs[i]
             check(lib.hqkv_decode_attention_phases(desc, ptr(qs[i]), ptr(w), ptr(o), ptr(ws), ws.numel(), phase, st))
 
+    # one launch costs less GPU time than a Python call takes, so each phase is replayed from a CUDA
+    # graph (all layers, back to back) and the event time is divided by the number of launches
     kernel_ms = {}
     reps = max(3, min(args.steps, 10))
     for phase, name in ((1, "k_pass_kernel"), (2, "v_pass_kernel")):
         run_phase(1)
         run_phase(phase)
         torch.cuda.synchronize()
+        pg = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(pg, stream=side):
+                run_phase(phase)
+        torch.cuda.current_stream().wait_stream(side)
+        pg.replay()
+        torch.cuda.synchronize()
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(reps):
-            run_phase(phase)
+            pg.replay()
         b.record()
         torch.cuda.synchronize()
         kernel_ms[name] = a.elapsed_time(b) / (reps * layers)

@@ -28,7 +28,6 @@ constexpr int NWARP = 4;         // warps per CTA
 constexpr int NTHREADS = NWARP * 32;
 constexpr int MAX_REP = 8;       // query heads per kv head (n of the m16n8k16 tile)
 constexpr int SCALE_PAD = 8;     // halfs of padding per shared-memory scale row
-constexpr int MAX_V_CHUNK = 1024;
 
 struct TierDev {
   const void* k_data;
@@ -47,7 +46,7 @@ struct TierDev {
 
 struct DecodeParams {
   TierDev tier[HQKV_NUM_TIERS + 1];  // [5] = fp16 residual window (token-major K and V)
-  int B, H, nh_q, rep, L;
+  int B, H, nh_q, rep, rep_shift, L;
   int gk_shift, gv_shift;
   int nk_chunks, nv_chunks;
   int w_slice;  // logical positions normalised per v_pass CTA
@@ -231,19 +230,26 @@ __device__ __forceinline__ void mma_words(float (&acc)[NM][4], const typename Fm
   }
 }
 
+// 2^x on the special-function unit (about 2 ulp; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // online (max, sum-exp) update
 __device__ __forceinline__ void softmax_push(float& m, float& l, float x) {
   if (x > m) {
-    l = l * exp2f((m - x) * 1.4426950408889634f) + 1.f;
+    l = l * fast_exp2((m - x) * 1.4426950408889634f) + 1.f;
     m = x;
   } else {
-    l += exp2f((x - m) * 1.4426950408889634f);
+    l += fast_exp2((x - m) * 1.4426950408889634f);
   }
 }
 __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, float l2) {
   const float mx = fmaxf(m, m2);
   if (mx == -INFINITY) return;  // both empty
-  l = l * exp2f((m - mx) * 1.4426950408889634f) + l2 * exp2f((m2 - mx) * 1.4426950408889634f);
+  l = l * fast_exp2((m - mx) * 1.4426950408889634f) + l2 * fast_exp2((m2 - mx) * 1.4426950408889634f);
   m = mx;
 }
 
@@ -251,194 +257,221 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
 // ------------------------------------------------------------------------------------------------
 // k_pass
 // ------------------------------------------------------------------------------------------------
-// Quantised K tier: rows = channels, packed words along tokens.  A CTA takes a chunk of 512 tokens
-// (16 scale groups at group 32) of one (batch, kv head); each warp takes one 128-token span:
-// fragment row g <-> the 8 tokens of word slot g, row g+8 <-> slot g+8, M-tile i <-> i-th token of
+// Quantised K tier: rows = channels, packed words along tokens.  A CTA of KWARPS warps takes a chunk of
+// KWARPS*64 tokens (one scale group per 32 tokens at group 32) of one (batch, kv head); each warp takes one 64-token
+// span: fragment row g <-> the 4 tokens of slot g, row g+8 <-> slot g+8, M-tile i <-> i-th token of
 // every slot, so a thread uses every code of every word it loads and no operand passes through
-// shared memory.  Words go global -> registers one 16-channel step ahead of their use.
+// shared memory.  Words go global -> registers one 16-channel step ahead of their use.  Short
+// per-warp programs and many warps per SM matter more here than wide loads: at batch 1 a layer is
+// only ~130 KB of K per SM, and the time is set by the length of one warp's dependent chain.
 //
 // Precision: the logits must match an fp32 dequant-matmul, and with x10 outlier channels the fp16
 // rounding of a dequantised K value alone costs ~2e-3 on the attention output.  So the product
 // code*scale (8 + 11 significant bits) is carried EXACTLY as two fp16 numbers, hi = fp16(code*scale)
-// and lo = fma(code, scale, -hi), each multiplied with q on the tensor pipe into the same fp32
+// and lo = code*scale - hi, each multiplied with q on the tensor pipe into the same fp32
 // accumulator, and the zero point enters through Zq[group][head] = sum_d zero[d,group]*q[head][d],
 // itself one small MMA per 16-channel step (fp16 inputs are exact, fp32 accumulation).
-constexpr int K_SPAN = 128;                 // tokens per warp span
-constexpr int K_CHUNK = NWARP * K_SPAN;     // 512 tokens per CTA
-constexpr int K_MAXG = K_CHUNK / 32;        // 16 scale groups per chunk at group size 32
+#ifndef K_MIN_CTAS
+#define K_MIN_CTAS 7
+#endif
+#ifndef K_WARPS
+#define K_WARPS 4
+#endif
+constexpr int KWARPS = K_WARPS;
+constexpr int KTHREADS = KWARPS * 32;
+constexpr int K_SLOT = 4;                   // tokens per slot (one load of one lane)
+constexpr int K_SPAN = 16 * K_SLOT;         // 64 tokens per warp span
+constexpr int K_CHUNK = KWARPS * K_SPAN;    // 512 tokens per CTA
+constexpr int K_MAXG = K_CHUNK / 32;        // scale groups per chunk at group size 32 (at most 16: rows of the Zq MMA)
+static_assert(K_MAXG == 8 || K_MAXG == 16, "a chunk must hold 8 or 16 groups of 32 tokens");
 constexpr int K_SROW = D + SCALE_PAD;       // halfs per staged scale row
+constexpr int K_TROW = MAX_REP + 1;         // floats per token row of the logit tile (odd: no bank conflicts)
 
 struct KShared {
   uint2 qfrag[8][32];          // B fragments of q per 16-channel step and lane
   __half s[K_MAXG][K_SROW];    // scale[group][channel]
   __half z[K_MAXG][K_SROW];    // zero[group][channel]
   float zq[K_MAXG][MAX_REP];   // sum_d zero*q per group and head
-  float red_m[NWARP][MAX_REP], red_l[NWARP][MAX_REP];
+  float tile[KWARPS][K_SPAN * K_TROW];  // per warp: logits [token][head] for the coalesced write-out
+  float red_m[KWARPS][MAX_REP], red_l[KWARPS][MAX_REP];
 };
 
-// one slot = 8 tokens of one channel
+// one slot = 4 tokens of one channel: 4, 2 or 1 byte
 template <int BITS>
-struct KSlot;
-template <>
-struct KSlot<8> {
-  using word_t = uint2;
-  static __device__ __forceinline__ uint2 load(const void* row, int64_t slot) {
-    return ld_stream(reinterpret_cast<const uint2*>(row) + slot);
-  }
-};
-template <>
-struct KSlot<4> {
-  using word_t = uint32_t;
-  static __device__ __forceinline__ uint32_t load(const void* row, int64_t slot) {
+__device__ __forceinline__ uint32_t kslot_load(const unsigned char* row, int64_t slot) {
+  if constexpr (BITS == 8) {
     return ld_stream(reinterpret_cast<const uint32_t*>(row) + slot);
-  }
-};
-template <>
-struct KSlot<2> {
-  using word_t = uint32_t;
-  static __device__ __forceinline__ uint32_t load(const void* row, int64_t slot) {
+  } else if constexpr (BITS == 4) {
     unsigned short v;
     asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(reinterpret_cast<const uint16_t*>(row) + slot));
     return v;
+  } else {
+    uint32_t v;
+    asm volatile("ld.global.nc.L1::no_allocate.u8 %0, [%1];" : "=r"(v) : "l"(row + slot));
+    return v;
   }
-};
+}
 
-// Exact integer codes (as fp16 pairs: low half = row a, high half = row b) of the 8 tokens of a slot.
+// Exact integer codes (fp16 pairs: low half = row a, high half = row b) of sub-unit j of a slot.
+// 8-bit: one sub-unit of 4 tokens; 4-bit: two bytes of 2 tokens; 2-bit: one byte of 4 tokens.
+// Token index inside the slot = j*NPER + k.
 template <int BITS>
-__device__ __forceinline__ void slot_codes(const typename KSlot<BITS>::word_t& wa, const typename KSlot<BITS>::word_t& wb,
-                                           __half2 (&c)[8]) {
+struct KSub {
+  static constexpr int NSUB = BITS == 4 ? 2 : 1;
+  static constexpr int NPER = K_SLOT / NSUB;
+};
+template <int BITS>
+__device__ __forceinline__ void sub_codes(uint32_t wa, uint32_t wb, int j, __half2 (&c)[KSub<BITS>::NPER]) {
   const __half2 k1024 = __half2half2(__float2half(1024.f));
   if constexpr (BITS == 8) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const uint32_t a = half ? wa.y : wa.x, b = half ? wb.y : wb.x;
-      const uint32_t lo = __byte_perm(a, b, 0x5140);  // [a0 b0 a1 b1]
-      const uint32_t hi = __byte_perm(a, b, 0x7362);  // [a2 b2 a3 b3]
-      c[half * 4 + 0] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1024);
-      c[half * 4 + 1] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1024);
-      c[half * 4 + 2] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1024);
-      c[half * 4 + 3] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1024);
-    }
+    const uint32_t lo = __byte_perm(wa, wb, 0x5140);  // [a0 b0 a1 b1]
+    const uint32_t hi = __byte_perm(wa, wb, 0x7362);  // [a2 b2 a3 b3]
+    c[0] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1024);
+    c[1] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1024);
+    c[2] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1024);
+    c[3] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1024);
   } else if constexpr (BITS == 4) {
-    const __half2 k16th = __half2half2(__float2half(0.0625f)), km64 = __half2half2(__float2half(-64.f));
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-      c[2 * j] = __hsub2(u32_as_h2((t & 0x000F000Fu) | 0x64006400u), k1024);
-      c[2 * j + 1] = __hfma2(u32_as_h2((t & 0x00F000F0u) | 0x64006400u), k16th, km64);
-    }
+    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
+    c[0] = __hsub2(u32_as_h2((t & 0x000F000Fu) | 0x64006400u), k1024);
+    c[1] = __hfma2(u32_as_h2((t & 0x00F000F0u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
+                   __half2half2(__float2half(-64.f)));
   } else {
-#pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-      c[4 * j + 0] = __hsub2(u32_as_h2((t & 0x00030003u) | 0x64006400u), k1024);
-      c[4 * j + 1] = __hfma2(u32_as_h2((t & 0x000C000Cu) | 0x64006400u), __half2half2(__float2half(0.25f)),
-                             __half2half2(__float2half(-256.f)));
-      c[4 * j + 2] = __hfma2(u32_as_h2((t & 0x00300030u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
-                             __half2half2(__float2half(-64.f)));
-      c[4 * j + 3] = __hfma2(u32_as_h2((t & 0x00C000C0u) | 0x64006400u), __half2half2(__float2half(0.015625f)),
-                             __half2half2(__float2half(-16.f)));
-    }
+    const uint32_t t = __byte_perm(wa, wb, 0x4400);
+    c[0] = __hsub2(u32_as_h2((t & 0x00030003u) | 0x64006400u), k1024);
+    c[1] = __hfma2(u32_as_h2((t & 0x000C000Cu) | 0x64006400u), __half2half2(__float2half(0.25f)),
+                   __half2half2(__float2half(-256.f)));
+    c[2] = __hfma2(u32_as_h2((t & 0x00300030u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
+                   __half2half2(__float2half(-64.f)));
+    c[3] = __hfma2(u32_as_h2((t & 0x00C000C0u) | 0x64006400u), __half2half2(__float2half(0.015625f)),
+                   __half2half2(__float2half(-16.f)));
+  }
+}
+
+// Write out a warp's logit tile [ntok][K_TROW] (already scaled) at the tokens' logical positions and
+// leave the warp's (max, sum-exp) per head in red_m / red_l.  Element = (token, head) with the head
+// fastest across lanes, so every lane owns ONE head for the whole call (rep divides 32): its running
+// max and sum are scalars, and index loads and stores are spread over all 32 lanes.
+__device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float* tile, int ntok, const int64_t* idx,
+                                             int64_t first_pos, int b, int kvh, float* red_m, float* red_l) {
+  const int lane = threadIdx.x & 31;
+  const int rep = P.rep, rshift = P.rep_shift;
+  const int h = lane & (rep - 1);
+  float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+  const int tpr = 32 >> rshift;  // tokens per round
+  float mx = -INFINITY;
+#pragma unroll 2
+  for (int t = lane >> rshift; t < ntok; t += tpr) {
+    const int64_t pos = idx ? idx[t] : first_pos + t;
+    const float x = tile[t * K_TROW + h];
+    row[pos] = x;
+    mx = fmaxf(mx, x);
+  }
+  for (int off = rep; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  float sum = 0.f;
+#pragma unroll 2
+  for (int t = lane >> rshift; t < ntok; t += tpr)
+    sum += fast_exp2((tile[t * K_TROW + h] - mx) * 1.4426950408889634f);
+  for (int off = rep; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (lane < rep) {
+    red_m[lane] = mx;
+    red_l[lane] = sum;
   }
 }
 
 template <int BITS>
 __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                       int chunk_t0, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
-  using word_t = typename KSlot<BITS>::word_t;
-  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+                                       int chunk_t0, int span_t0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
-  const int64_t nslot = n / 8;                        // slots per channel row
+  const int nslot = n / K_SLOT;  // slots per channel row
   const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
+  constexpr int SLOT_BYTES = K_SLOT * BITS / 8;
+  // warp-uniform base of this (batch, head); per-lane byte offsets of the 4 channel rows x 2 slots stay
+  // fixed over the 16-channel steps, which only advance the uniform base
   const unsigned char* base = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes;
-  int64_t sl[2];
-  bool ok[2];
+  const int64_t kt_stride = 16 * row_bytes;
+  uint32_t off[4][2];
+  const __half* srow[2];  // staged scales of the two slots' groups, at this lane's first channel pair
   int gl[2];
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
-    sl[r] = span_t0 / 8 + r * 8 + g;
-    ok[r] = sl[r] < nslot;
-    gl[r] = ok[r] ? (((static_cast<int>(sl[r]) * 8) >> P.gk_shift) - (chunk_t0 >> P.gk_shift)) : 0;
+    int sl = span_t0 / K_SLOT + r * 8 + g;
+    if (sl >= nslot) sl = nslot - 1;  // loads stay in range; such rows are never written out
+    gl[r] = max(((sl * K_SLOT) >> P.gk_shift) - (chunk_t0 >> P.gk_shift), 0);
+    srow[r] = &sh.s[gl[r]][2 * tig];
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+      off[p][r] = static_cast<uint32_t>((2 * tig + (p & 1) + (p >> 1) * 8) * row_bytes) + static_cast<uint32_t>(sl) * SLOT_BYTES;
   }
-  float acc[8][4];
+  float acc[K_SLOT][4];
 #pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  word_t w[4][2], wn[4][2];
-  auto load = [&](word_t (&dst)[4][2], int kt) {
+  constexpr int DEPTH = 3;  // steps in flight: the one being used and two ahead
+  uint32_t w[DEPTH][4][2];
+  auto load = [&](uint32_t (&dst)[4][2], int kt) {
+    const unsigned char* kb = base + kt * kt_stride;
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
-      const unsigned char* row = base + ch * row_bytes;
+    for (int p = 0; p < 4; ++p)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        if (ok[r]) dst[p][r] = KSlot<BITS>::load(row, sl[r]);
-        else dst[p][r] = word_t{};
-      }
-    }
+      for (int r = 0; r < 2; ++r) dst[p][r] = kslot_load<BITS>(kb + off[p][r], 0);
   };
-  load(w, 0);
-  int pos[2][8];  // logical positions of this lane's 16 tokens (fetched while the last steps compute)
-#pragma unroll 1
+#pragma unroll
+  for (int d = 0; d < DEPTH - 1; ++d) load(w[d], d);
+  constexpr int NSUB = KSub<BITS>::NSUB, NPER = KSub<BITS>::NPER;
+#pragma unroll
   for (int kt = 0; kt < 8; ++kt) {
-    if (kt + 1 < 8) load(wn, kt + 1);
-    if (kt == 6) {
-#pragma unroll
-      for (int r = 0; r < 2; ++r)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) pos[r][i] = ok[r] ? static_cast<int>(T.k_idx[sl[r] * 8 + i]) : 0;
-    }
+    if (kt + DEPTH - 1 < 8) load(w[(kt + DEPTH - 1) % DEPTH], kt + DEPTH - 1);
+    const uint32_t (&cur)[4][2] = w[kt % DEPTH];
     const uint2 bq = sh.qfrag[kt][lane];
     // fragment register q*2 + r: channel pair q (2tig,2tig+1 | +8,+9), row slot r
-    __half2 hi[4][8], lo[4][8];
+    __half2 s2[4];
 #pragma unroll
     for (int q = 0; q < 2; ++q)
 #pragma unroll
-      for (int r = 0; r < 2; ++r) {
-        const __half2 s2 = *reinterpret_cast<const __half2*>(&sh.s[gl[r]][kt * 16 + 2 * tig + q * 8]);
-        __half2 c[8];
-        slot_codes<BITS>(w[2 * q][r], w[2 * q + 1][r], c);
+      for (int r = 0; r < 2; ++r) s2[q * 2 + r] = *reinterpret_cast<const __half2*>(srow[r] + kt * 16 + q * 8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          hi[q * 2 + r][i] = __hmul2(c[i], s2);
-          lo[q * 2 + r][i] = __hfma2(c[i], s2, __hneg2(hi[q * 2 + r][i]));
+    for (int j = 0; j < NSUB; ++j) {
+      __half2 hi[4][NPER], lo[4][NPER];
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+          __half2 c[NPER];
+          sub_codes<BITS>(cur[2 * q][r], cur[2 * q + 1][r], j, c);
+#pragma unroll
+          for (int k = 0; k < NPER; ++k) {
+            hi[q * 2 + r][k] = __hmul2(c[k], s2[q * 2 + r]);                              // fp16(code*scale)
+            lo[q * 2 + r][k] = __hfma2(c[k], s2[q * 2 + r], __hneg2(hi[q * 2 + r][k]));  // code*scale - hi, exact
+          }
         }
+#pragma unroll
+      for (int k = 0; k < NPER; ++k) {
+        const int i = j * NPER + k;
+        mma16816(acc[i], h2_as_u32(hi[0][k]), h2_as_u32(hi[1][k]), h2_as_u32(hi[2][k]), h2_as_u32(hi[3][k]), bq.x, bq.y);
+        mma16816(acc[i], h2_as_u32(lo[0][k]), h2_as_u32(lo[1][k]), h2_as_u32(lo[2][k]), h2_as_u32(lo[3][k]), bq.x, bq.y);
       }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      mma16816(acc[i], h2_as_u32(hi[0][i]), h2_as_u32(hi[1][i]), h2_as_u32(hi[2][i]), h2_as_u32(hi[3][i]), bq.x, bq.y);
-      mma16816(acc[i], h2_as_u32(lo[0][i]), h2_as_u32(lo[1][i]), h2_as_u32(lo[2][i]), h2_as_u32(lo[3][i]), bq.x, bq.y);
-    }
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      w[p][0] = wn[p][0];
-      w[p][1] = wn[p][1];
     }
   }
-  // logits of heads 2tig, 2tig+1 at the tokens' logical positions
+  // accumulators -> the warp's [token][head] tile, then the lane-per-element write-out
+  float* tile = sh.tile[warp];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (!ok[r]) continue;
+  for (int r = 0; r < 2; ++r)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int h = 2 * tig + e;
-      if (h < P.rep) {
-        float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L;
-        const float zq = sh.zq[gl[r]][h];
+      const float zq = sh.zq[gl[r]][h];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const float x = (acc[i][r * 2 + e] + zq) * P.scale;
-          row[pos[r][i]] = x;
-          softmax_push(m_run[e], l_run[e], x);
-        }
-      }
+      for (int i = 0; i < K_SLOT; ++i)
+        tile[((r * 8 + g) * K_SLOT + i) * K_TROW + h] = (acc[i][r * 2 + e] + zq) * P.scale;
     }
-  }
+  __syncwarp();
+  k_write_tile(P, tile, min(K_SPAN, n - span_t0), T.k_idx + span_t0, 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
 }
 
 template <int BITS>
 __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                        int chunk_t0, float (&m_run)[2], float (&l_run)[2]) {
+                                        int chunk_t0) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int chunk_end = min(chunk_t0 + K_CHUNK, T.n_k);
   // stage scale/zero of the chunk as [group][channel]: lanes run along the groups of one channel row
@@ -448,11 +481,14 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
     const int ng = ((chunk_end - chunk_t0) + (1 << P.gk_shift) - 1) >> P.gk_shift;  // <= K_MAXG
     const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G + g0;
     const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G + g0;
-    __half sv[K_MAXG], zv[K_MAXG];
+    constexpr int ITERS = D * K_MAXG / KTHREADS;
+    constexpr int CH_STEP = KTHREADS / K_MAXG;
+    __half sv[ITERS], zv[ITERS];
+    constexpr int GSHIFT = K_MAXG == 16 ? 4 : 3;
     const int gi = tid & (K_MAXG - 1);
 #pragma unroll
-    for (int j = 0; j < K_MAXG; ++j) {
-      const int ch = (tid >> 4) + j * (NTHREADS / K_MAXG);
+    for (int j = 0; j < ITERS; ++j) {
+      const int ch = (tid >> GSHIFT) + j * CH_STEP;
       sv[j] = zv[j] = __float2half(0.f);
       if (gi < ng) {
         sv[j] = s[static_cast<int64_t>(ch) * G + gi];
@@ -460,8 +496,8 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
       }
     }
 #pragma unroll
-    for (int j = 0; j < K_MAXG; ++j) {
-      const int ch = (tid >> 4) + j * (NTHREADS / K_MAXG);
+    for (int j = 0; j < ITERS; ++j) {
+      const int ch = (tid >> GSHIFT) + j * CH_STEP;
       sh.s[gi][ch] = sv[j];
       sh.z[gi][ch] = zv[j];
     }
@@ -474,85 +510,84 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
     for (int kt = 0; kt < 8; ++kt) {
       const int ch = kt * 16 + 2 * tig;
       const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch]);
-      const uint32_t a1 = *reinterpret_cast<const uint32_t*>(&sh.z[g + 8][ch]);
       const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch + 8]);
-      const uint32_t a3 = *reinterpret_cast<const uint32_t*>(&sh.z[g + 8][ch + 8]);
+      uint32_t a1 = 0u, a3 = 0u;  // rows 8..15 exist only with 16 groups per chunk
+      if constexpr (K_MAXG == 16) {
+        a1 = *reinterpret_cast<const uint32_t*>(&sh.z[(g + 8) & (K_MAXG - 1)][ch]);
+        a3 = *reinterpret_cast<const uint32_t*>(&sh.z[(g + 8) & (K_MAXG - 1)][ch + 8]);
+      }
       const uint2 bq = sh.qfrag[kt][lane];
       mma16816(zacc, a0, a1, a2, a3, bq.x, bq.y);
     }
     sh.zq[g][2 * tig] = zacc[0];
     sh.zq[g][2 * tig + 1] = zacc[1];
-    sh.zq[g + 8][2 * tig] = zacc[2];
-    sh.zq[g + 8][2 * tig + 1] = zacc[3];
+    if constexpr (K_MAXG == 16) {
+      sh.zq[(g + 8) & (K_MAXG - 1)][2 * tig] = zacc[2];
+      sh.zq[(g + 8) & (K_MAXG - 1)][2 * tig + 1] = zacc[3];
+    }
   }
   __syncthreads();
   const int span_t0 = chunk_t0 + warp * K_SPAN;
-  if (span_t0 < chunk_end) k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0, m_run, l_run);
+  if (span_t0 < chunk_end) k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0);
 }
 
-// fp16 tier, channel-major rows [D][n]: eight tokens per 16-byte word, no scales; B = q exactly.
-// Per warp one span of 16 word slots (128 tokens): fragment row g <-> slot g, row g+8 <-> slot g+8,
-// M-tile i <-> i-th value of every slot.
-__device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev& T, const uint2* qfrag, int bh, int b,
-                                           int kvh, int span_t0, float (&m_run)[2], float (&l_run)[2]) {
-  constexpr int FPI = 8, NM = 8;
-  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+// fp16 tier, channel-major rows [D][n]: four tokens per 8-byte slot, no scales; B = q exactly.
+__device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                           int span_t0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
-  const int64_t W = n / FPI;
-  const uint4* base = reinterpret_cast<const uint4*>(T.k_data) + static_cast<int64_t>(bh) * D * W;
-  int64_t wc[2];
-  bool ok[2];
+  const int64_t nslot = n / K_SLOT;
+  const uint2* base = reinterpret_cast<const uint2*>(T.k_data) + static_cast<int64_t>(bh) * D * nslot;
+  int64_t sl[2];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    wc[r] = span_t0 / FPI + r * 8 + g;
-    ok[r] = wc[r] < W;
-  }
-  float acc[NM][4];
+  for (int r = 0; r < 2; ++r) sl[r] = min(static_cast<int64_t>(span_t0 / K_SLOT + r * 8 + g), nslot - 1);
+  float acc[K_SLOT][4];
 #pragma unroll
-  for (int i = 0; i < NM; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const __half2 unused = __half2half2(__float2half(0.f));
-  const __half2 sz[2][2] = {{unused, unused}, {unused, unused}};
+  for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 #pragma unroll 2
   for (int kt = 0; kt < 8; ++kt) {
-    uint4 w[4][2];
+    uint2 w[4][2];
 #pragma unroll
     for (int p = 0; p < 4; ++p) {
       const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
 #pragma unroll
-      for (int r = 0; r < 2; ++r) w[p][r] = ok[r] ? ld_stream(base + ch * W + wc[r]) : zero_word<uint4>();
+      for (int r = 0; r < 2; ++r) w[p][r] = ld_stream(base + ch * nslot + sl[r]);
     }
-    const uint2 bq = qfrag[kt * 32 + lane];
-    mma_words<16, NM>(acc, w, sz, sz, bq.x, bq.y);
-  }
-  const int h0 = 2 * tig;
+    const uint2 bq = sh.qfrag[kt][lane];
+    // token i of a slot: halfs (x.lo, x.hi, y.lo, y.hi); pair the same token of two channel rows
+    uint32_t a[K_SLOT][4];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (!ok[r]) continue;
-    const int64_t tok0 = wc[r] * FPI;
+    for (int q = 0; q < 2; ++q)
 #pragma unroll
-    for (int i = 0; i < NM; ++i) {
-      const int64_t pos = T.k_idx[tok0 + i];
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int h = h0 + e;
-        if (h < P.rep) {
-          const float x = acc[i][r * 2 + e] * P.scale;
-          P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L + pos] = x;
-          softmax_push(m_run[e], l_run[e], x);
-        }
+      for (int r = 0; r < 2; ++r) {
+        const uint2 wa = w[2 * q][r], wb = w[2 * q + 1][r];
+        a[0][q * 2 + r] = __byte_perm(wa.x, wb.x, 0x5410);
+        a[1][q * 2 + r] = __byte_perm(wa.x, wb.x, 0x7632);
+        a[2][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x5410);
+        a[3][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x7632);
       }
-    }
+#pragma unroll
+    for (int i = 0; i < K_SLOT; ++i) mma16816(acc[i], a[i][0], a[i][1], a[i][2], a[i][3], bq.x, bq.y);
   }
+  float* tile = sh.tile[warp];
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+#pragma unroll
+      for (int i = 0; i < K_SLOT; ++i)
+        tile[((r * 8 + g) * K_SLOT + i) * K_TROW + 2 * tig + e] = acc[i][r * 2 + e] * P.scale;
+  __syncwarp();
+  k_write_tile(P, tile, min(K_SPAN, n - span_t0), T.k_idx + span_t0, 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
 }
 
-// fp16 residual window, token-major [r][D]: A fragments are read directly.
-__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, const uint2* qfrag, int bh,
-                                                int b, int kvh, int tile_t0, float (&m_run)[2], float (&l_run)[2]) {
-  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+// fp16 residual window, token-major [r][D]: A fragments are read directly; one 16-token tile per warp.
+__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b,
+                                                int kvh, int tile_t0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
   const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
-  const int t[2] = {tile_t0 + g, tile_t0 + g + 8};
-  const bool ok[2] = {t[0] < n, t[1] < n};
+  const int t[2] = {min(tile_t0 + g, n - 1), min(tile_t0 + g + 8, n - 1)};
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
   for (int kt = 0; kt < 8; ++kt) {
@@ -560,36 +595,32 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
     uint32_t a[4];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      a[r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch) : 0u;
-      a[2 + r] = ok[r] ? *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch + 8) : 0u;
+      a[r] = *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch);
+      a[2 + r] = *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch + 8);
     }
-    const uint2 bq = qfrag[kt * 32 + lane];
+    const uint2 bq = sh.qfrag[kt][lane];
     mma16816(acc, a[0], a[1], a[2], a[3], bq.x, bq.y);
   }
-  const int h0 = 2 * tig;
+  float* tile = sh.tile[warp];
 #pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    if (!ok[r]) continue;
-    const int64_t pos = P.L - n + t[r];
+  for (int r = 0; r < 2; ++r)
 #pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int h = h0 + e;
-      if (h < P.rep) {
-        const float x = acc[r * 2 + e] * P.scale;
-        P.logits[(static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + h) * P.L + pos] = x;
-        softmax_push(m_run[e], l_run[e], x);
-      }
-    }
-  }
+    for (int e = 0; e < 2; ++e) tile[(r * 8 + g) * K_TROW + 2 * tig + e] = acc[r * 2 + e] * P.scale;
+  __syncwarp();
+  k_write_tile(P, tile, min(16, n - tile_t0), nullptr, static_cast<int64_t>(P.L) - n + tile_t0, b, kvh, sh.red_m[warp],
+               sh.red_l[warp]);
 }
 
-__global__ void __launch_bounds__(NTHREADS, 4) k_pass_kernel(const __grid_constant__ DecodeParams P) {
+__global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
   __shared__ KShared sh;
-  const int chunk = blockIdx.x, bh = blockIdx.y;
+  const int chunk = blockIdx.y, bh = blockIdx.x;  // (batch, head) fastest: neighbouring CTAs run the same tier code
   const int b = bh / P.H, kvh = bh - b * P.H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-  const uint2* qfrag = &sh.qfrag[0][0];
 
+  if (tid < KWARPS * MAX_REP) {
+    (&sh.red_m[0][0])[tid] = -INFINITY;
+    (&sh.red_l[0][0])[tid] = 0.f;
+  }
   // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
   if (warp == 0) {
     const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
@@ -611,61 +642,51 @@ __global__ void __launch_bounds__(NTHREADS, 4) k_pass_kernel(const __grid_consta
   const TierDev& T = P.tier[ti];
   const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
 
-  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
   if (ti == HQKV_NUM_TIERS || T.bits == 16) {
     __syncthreads();
     const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
     if (ti == HQKV_NUM_TIERS) {
-      for (int t0 = chunk_t0 + warp * 16; t0 < chunk_end; t0 += NWARP * 16)
-        k_residual_tile(P, T, qfrag, bh, b, kvh, t0, m_run, l_run);
+      const int t0 = chunk_t0 + warp * 16;  // residual chunks are KWARPS * 16 tokens
+      if (t0 < chunk_end) k_residual_tile(P, T, sh, bh, b, kvh, t0);
     } else {
-      for (int t0 = chunk_t0 + warp * 128; t0 < chunk_end; t0 += NWARP * 128)
-        k_f16_span(P, T, qfrag, bh, b, kvh, t0, m_run, l_run);
+      const int t0 = chunk_t0 + warp * K_SPAN;
+      if (t0 < chunk_end) k_f16_span(P, T, sh, bh, b, kvh, t0);
     }
   } else if (T.bits == 8) {
-    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0);
   } else if (T.bits == 4) {
-    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0);
   } else {
-    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, m_run, l_run);
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0);
   }
 
-  // (max, sum) of this CTA per head: lanes with equal tig hold the same two heads
-#pragma unroll
-  for (int e = 0; e < 2; ++e) {
-#pragma unroll
-    for (int off = 4; off < 32; off <<= 1) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m_run[e], off);
-      const float l2 = __shfl_xor_sync(0xffffffffu, l_run[e], off);
-      softmax_merge(m_run[e], l_run[e], m2, l2);
-    }
-    if (g == 0) {
-      sh.red_m[warp][2 * tig + e] = m_run[e];
-      sh.red_l[warp][2 * tig + e] = l_run[e];
-    }
-  }
+  // (max, sum) of this CTA per head from the warps' pairs
   __syncthreads();
   if (tid < MAX_REP) {
     float m = sh.red_m[0][tid], l = sh.red_l[0][tid];
-    for (int w = 1; w < NWARP; ++w) softmax_merge(m, l, sh.red_m[w][tid], sh.red_l[w][tid]);
+    for (int w = 1; w < KWARPS; ++w) softmax_merge(m, l, sh.red_m[w][tid], sh.red_l[w][tid]);
     P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + tid] = make_float2(m, l);
   }
 }
 
-
 // ------------------------------------------------------------------------------------------------
 // v_pass
 // ------------------------------------------------------------------------------------------------
+constexpr int VWARPS = 8;
+constexpr int VTHREADS = VWARPS * 32;
+constexpr int V_MAX_CHUNK = 1024;                       // tokens per CTA at most (multiple of VWARPS*16)
+constexpr int V_STAGE_ITERS = V_MAX_CHUNK / VTHREADS;   // 4
+constexpr int V_EROW = V_MAX_CHUNK + 8;                 // halfs per staged row
+
 struct VShared {
-  __half e[MAX_REP][MAX_V_CHUNK + 8];        // exp(logit - max) per head and token of the chunk
-  __half s[4][MAX_V_CHUNK + 8];              // scale[channel group][token]
-  __half z[4][MAX_V_CHUNK + 8];
-  float red[NWARP][MAX_REP][D];              // per-warp partial outputs
-  float gm[MAX_REP], gl[MAX_REP];            // global max / sum of this kv head's query heads
-  float wm[NWARP][MAX_REP], wl[NWARP][MAX_REP];
+  __half e[MAX_REP][V_EROW];               // exp(logit - max) per head and token of the chunk
+  __half s[4][V_EROW];                     // scale[channel group][token]
+  __half z[4][V_EROW];
+  float red[VWARPS][MAX_REP][D];           // per-warp partial outputs
+  float gm[MAX_REP], gl[MAX_REP];          // global max / sum of this kv head's query heads
+  float wm[VWARPS][MAX_REP], wl[VWARPS][MAX_REP];
   unsigned is_last;
 };
-constexpr int V_STAGE_ITERS = MAX_V_CHUNK / NTHREADS;  // 8
 
 // V tier, token-major rows.  Contraction runs over tokens (16 per step): fragment columns
 // 2tig,2tig+1,2tig+8,2tig+9 <-> tokens t0+..., fragment row g <-> channel slot g, row g+8 <-> slot
@@ -673,129 +694,102 @@ constexpr int V_STAGE_ITERS = MAX_V_CHUNK / NTHREADS;  // 8
 // dequantised to fp16 (code*scale + zero, one rounding) because here the scale varies along the
 // contraction axis; B = exp(logit - max) in fp16.
 template <int BITS>
-__device__ __forceinline__ void v_chunk(const DecodeParams& P, const TierDev& T, VShared& sh, int bh,
-                                        int chunk_t0, int chunk_n, float (&acc)[8][4]) {
-  using F = Fmt<BITS>;
-  using word_t = typename F::word_t;
-  constexpr bool HALF_SPLIT = (BITS == 2);  // one word per token row covers both row slots
-  constexpr int WORDS_PER_TOKEN = BITS == 2 ? 8 : 16;  // in units of word_t
-  constexpr int NW = HALF_SPLIT ? 1 : 2;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
-  const int n = T.n_v;
-  const word_t* base = reinterpret_cast<const word_t*>(T.v_data) + static_cast<int64_t>(bh) * n * WORDS_PER_TOKEN;
-  int cg[2];
+struct VFmt {
+  using word_t = typename Fmt<BITS>::word_t;
+  static constexpr bool HALF_SPLIT = (BITS == 2);        // one word per token row covers both row slots
+  static constexpr int WORDS_PER_TOKEN = BITS == 2 ? 8 : 16;  // in units of word_t
+  static constexpr int NW = HALF_SPLIT ? 1 : 2;          // words a lane loads per token
+};
+
+template <int BITS>
+__device__ __forceinline__ void v_load(typename VFmt<BITS>::word_t (&dst)[4][VFmt<BITS>::NW],
+                                       const typename VFmt<BITS>::word_t* base, int chunk_t0, int chunk_n, int kt0,
+                                       int g, int tig) {
 #pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    const int ch0 = HALF_SPLIT ? (16 * g + 8 * s) : (8 * (s * 8 + g));
-    cg[s] = ch0 >> P.gv_shift;
-  }
-  auto load = [&](word_t (&dst)[4][NW], int kt0) {
+  for (int p = 0; p < 4; ++p) {
+    const int tl = kt0 + 2 * tig + (p & 1) + (p >> 1) * 8;
+    const int64_t tok = chunk_t0 + min(tl, chunk_n - 1);
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const int tl = kt0 + 2 * tig + (p & 1) + (p >> 1) * 8;
-      const int64_t tok = chunk_t0 + min(tl, chunk_n - 1);
-#pragma unroll
-      for (int s = 0; s < NW; ++s) dst[p][s] = ld_stream(base + tok * WORDS_PER_TOKEN + s * 8 + g);
-    }
-  };
-  word_t cur[4][NW], nxt[4][NW];
-  const int step = NWARP * 16;
-  int kt0 = warp * 16;
-  if (kt0 < chunk_n) load(cur, kt0);
-  for (; kt0 < chunk_n; kt0 += step) {
-    if (kt0 + step < chunk_n) load(nxt, kt0 + step);
-    const int tl0 = kt0 + 2 * tig, tl2 = tl0 + 8;
-    word_t w[4][2];
-#pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      if constexpr (HALF_SPLIT) {
-        w[p][0] = cur[p][0];
-        w[p][1] = cur[p][0] >> 16;  // values 8..15 of the word move to bytes 0,1
-      } else {
-        w[p][0] = cur[p][0];
-        w[p][1] = cur[p][1];
-      }
-    }
-    __half2 sz[2][2], zz[2][2];
-    if constexpr (BITS != 16) {
-#pragma unroll
-      for (int s = 0; s < 2; ++s) {
-        sz[0][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl0]);
-        zz[0][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl0]);
-        sz[1][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl2]);
-        zz[1][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl2]);
-      }
-    }
-    uint32_t b0 = 0u, b1 = 0u;
-    if (g < P.rep) {
-      b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl0]);
-      b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl2]);
-    }
-    if constexpr (HALF_SPLIT) {
-      mma_sub<2, 0, 8>(acc, w, sz, zz, b0, b1);
-      mma_sub<2, 1, 8>(acc, w, sz, zz, b0, b1);
-    } else {
-      mma_words<BITS, 8>(acc, w, sz, zz, b0, b1);
-    }
-#pragma unroll
-    for (int p = 0; p < 4; ++p)
-#pragma unroll
-      for (int s = 0; s < NW; ++s) cur[p][s] = nxt[p][s];
+    for (int s = 0; s < VFmt<BITS>::NW; ++s) dst[p][s] = ld_stream(base + tok * VFmt<BITS>::WORDS_PER_TOKEN + s * 8 + g);
   }
 }
 
-// fold acc (fragment layout) into sh.red[warp][head][channel]
 template <int BITS>
-__device__ __forceinline__ void v_store_acc(VShared& sh, const float (&acc)[8][4], int rep) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+__device__ __forceinline__ void v_step(float (&acc)[8][4], const typename VFmt<BITS>::word_t (&cur)[4][VFmt<BITS>::NW],
+                                       const VShared& sh, const int (&cg)[2], int kt0, int g, int tig, int rep) {
+  using word_t = typename VFmt<BITS>::word_t;
+  const int tl0 = kt0 + 2 * tig, tl2 = tl0 + 8;
+  word_t w[4][2];
 #pragma unroll
-  for (int mt = 0; mt < 8; ++mt)
+  for (int p = 0; p < 4; ++p) {
+    if constexpr (VFmt<BITS>::HALF_SPLIT) {
+      w[p][0] = cur[p][0];
+      w[p][1] = cur[p][0] >> 16;  // values 8..15 of the word move to bytes 0,1
+    } else {
+      w[p][0] = cur[p][0];
+      w[p][1] = cur[p][1];
+    }
+  }
+  __half2 sz[2][2], zz[2][2];
+  if constexpr (BITS != 16) {
 #pragma unroll
     for (int s = 0; s < 2; ++s) {
-      const int ch = (BITS == 2) ? (16 * g + 8 * s + mt) : (8 * (s * 8 + g) + mt);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int h = 2 * tig + e;
-        if (h < rep) sh.red[warp][h][ch] = acc[mt][s * 2 + e];
-      }
+      sz[0][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl0]);
+      zz[0][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl0]);
+      sz[1][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl2]);
+      zz[1][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl2]);
     }
+  }
+  uint32_t b0 = 0u, b1 = 0u;
+  if (g < rep) {
+    b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl0]);
+    b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl2]);
+  }
+  if constexpr (VFmt<BITS>::HALF_SPLIT) {
+    mma_sub<2, 0, 8>(acc, w, sz, zz, b0, b1);
+    mma_sub<2, 1, 8>(acc, w, sz, zz, b0, b1);
+  } else {
+    mma_words<BITS, 8>(acc, w, sz, zz, b0, b1);
+  }
 }
 
-__global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
-  const int chunk = blockIdx.x, bh = blockIdx.y;
-  const int b = bh / P.H, kvh = bh - b * P.H;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+// Everything a CTA does for its chunk of one V tier (or of the residual window, BITS = 16).
+template <int BITS>
+__device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, VShared& sh, int bh, int b, int kvh,
+                                       int chunk, int chunk_t0, int chunk_n, bool is_res, bool quantised) {
+  using word_t = typename VFmt<BITS>::word_t;
+  constexpr int NW = VFmt<BITS>::NW;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int rep = P.rep;
-
-  int ti = HQKV_NUM_TIERS;
-#pragma unroll
-  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
-    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
-  const TierDev& T = P.tier[ti];
-  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
-  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
   const int chunk_pad = (chunk_n + 15) & ~15;
-  const bool is_res = ti == HQKV_NUM_TIERS;
+  const int step = VWARPS * 16;
 
-  // ---- logical positions of this chunk's tokens (independent loads, issued before the reduction below)
+  // ---- the first two steps' words of this warp are requested before anything else: their addresses
+  //      depend on nothing, and the prologue below takes about as long as they need to arrive
+  const word_t* base = reinterpret_cast<const word_t*>(T.v_data) +
+                       static_cast<int64_t>(bh) * T.n_v * VFmt<BITS>::WORDS_PER_TOKEN;
+  word_t w0[4][NW], w1[4][NW], w2[4][NW];
+  int kt0 = warp * 16;
+  if (kt0 < chunk_n) v_load<BITS>(w0, base, chunk_t0, chunk_n, kt0, g, tig);
+  if (kt0 + step < chunk_n) v_load<BITS>(w1, base, chunk_t0, chunk_n, kt0 + step, g, tig);
+
+  // ---- logical positions of this chunk's tokens
   int64_t pos[V_STAGE_ITERS];
 #pragma unroll
   for (int j = 0; j < V_STAGE_ITERS; ++j) {
-    const int i = tid + j * NTHREADS;
+    const int i = tid + j * VTHREADS;
     pos[j] = 0;
     if (i < chunk_n) pos[j] = is_res ? (P.L - T.n_v + chunk_t0 + i) : T.v_idx[chunk_t0 + i];
   }
   // ---- scale / zero tile: one token row per thread and iteration, transposed into [group][token]
-  if (!is_res && T.bits != 16) {
+  if (quantised) {
     const int ng = D >> P.gv_shift;  // 4, 2 or 1 halfs per token
     const __half* s = T.v_scale + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
     const __half* z = T.v_zero + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
     uint2 sv[V_STAGE_ITERS], zv[V_STAGE_ITERS];
 #pragma unroll
     for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int t = tid + j * NTHREADS;
+      const int t = tid + j * VTHREADS;
       sv[j] = zv[j] = make_uint2(0u, 0u);
       if (t < chunk_n) {
         if (ng == 4) {
@@ -812,7 +806,7 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     }
 #pragma unroll
     for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int t = tid + j * NTHREADS;
+      const int t = tid + j * VTHREADS;
       if (t < chunk_pad) {
         sh.s[0][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].x & 0xFFFFu));
         sh.z[0][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].x & 0xFFFFu));
@@ -830,47 +824,44 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     }
   }
 
-  // ---- global (max, sum) of the rep heads from the k_pass pairs
+  // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks),
+  //      up to four pairs per thread in flight, then slices are folded by shuffles and across warps
   {
-    float m[MAX_REP], l[MAX_REP];
-#pragma unroll
-    for (int h = 0; h < MAX_REP; ++h) {
-      m[h] = -INFINITY;
-      l[h] = 0.f;
-    }
+    const int h = tid & (MAX_REP - 1), slice = tid >> 3;  // 32 slices
     const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
-    for (int c = tid; c < P.nk_chunks; c += NTHREADS) {
-      float2 v[MAX_REP];
+    float m = -INFINITY, l = 0.f;
+    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * (VTHREADS / MAX_REP)) {
+      float2 v[4];
 #pragma unroll
-      for (int h = 0; h < MAX_REP; ++h) v[h] = h < rep ? part[c * MAX_REP + h] : make_float2(-INFINITY, 0.f);
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + (VTHREADS / MAX_REP) * j;
+        v[j] = c < P.nk_chunks ? __ldcg(part + c * MAX_REP + h) : make_float2(-INFINITY, 0.f);
+      }
 #pragma unroll
-      for (int h = 0; h < MAX_REP; ++h) softmax_merge(m[h], l[h], v[h].x, v[h].y);
+      for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
     }
 #pragma unroll
-    for (int h = 0; h < MAX_REP; ++h) {
-#pragma unroll
-      for (int off = 1; off < 32; off <<= 1) {
-        const float m2 = __shfl_xor_sync(0xffffffffu, m[h], off);
-        const float l2 = __shfl_xor_sync(0xffffffffu, l[h], off);
-        softmax_merge(m[h], l[h], m2, l2);
-      }
-      if (lane == 0) {
-        sh.wm[warp][h] = m[h];
-        sh.wl[warp][h] = l[h];
-      }
+    for (int off = 8; off < 32; off <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+      softmax_merge(m, l, m2, l2);
+    }
+    if (lane < MAX_REP) {
+      sh.wm[warp][lane] = m;
+      sh.wl[warp][lane] = l;
     }
     __syncthreads();
     if (tid < MAX_REP) {
       float mm = sh.wm[0][tid], ll = sh.wl[0][tid];
-      for (int w = 1; w < NWARP; ++w) softmax_merge(mm, ll, sh.wm[w][tid], sh.wl[w][tid]);
+      for (int w = 1; w < VWARPS; ++w) softmax_merge(mm, ll, sh.wm[w][tid], sh.wl[w][tid]);
       sh.gm[tid] = mm;
       sh.gl[tid] = ll;
     }
     __syncthreads();
   }
 
-  // ---- exp(logit - max) of the chunk's tokens, per head: gathers batched per head
-  for (int h0 = 0; h0 < rep; h0 += 4) {  // four heads' gathers in flight together
+  // ---- exp(logit - max) of the chunk's tokens: the gathers of four heads are in flight together
+  for (int h0 = 0; h0 < rep; h0 += 4) {
     float x[4][V_STAGE_ITERS];
 #pragma unroll
     for (int hh = 0; hh < 4; ++hh) {
@@ -878,7 +869,7 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
       const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
 #pragma unroll
       for (int j = 0; j < V_STAGE_ITERS; ++j) {
-        const int i = tid + j * NTHREADS;
+        const int i = tid + j * VTHREADS;
         x[hh][j] = i < chunk_n ? __ldcg(row + pos[j]) : -INFINITY;
       }
     }
@@ -889,41 +880,81 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
         const float mh = sh.gm[h];
 #pragma unroll
         for (int j = 0; j < V_STAGE_ITERS; ++j) {
-          const int i = tid + j * NTHREADS;
-          if (i < chunk_pad) sh.e[h][i] = __float2half_rn(exp2f((x[hh][j] - mh) * 1.4426950408889634f));
+          const int i = tid + j * VTHREADS;
+          if (i < chunk_pad) sh.e[h][i] = __float2half_rn(fast_exp2((x[hh][j] - mh) * 1.4426950408889634f));
         }
       }
     }
   }
   __syncthreads();
 
+  // ---- main loop: this warp's 16-token steps, two steps of words in flight beyond the current one
   float acc[8][4];
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  const int vb = is_res ? 16 : T.bits;
-  if (vb == 8) {
-    v_chunk<8>(P, T, sh, bh, chunk_t0, chunk_n, acc);
-    v_store_acc<8>(sh, acc, rep);
-  } else if (vb == 4) {
-    v_chunk<4>(P, T, sh, bh, chunk_t0, chunk_n, acc);
-    v_store_acc<4>(sh, acc, rep);
-  } else if (vb == 2) {
-    v_chunk<2>(P, T, sh, bh, chunk_t0, chunk_n, acc);
-    v_store_acc<2>(sh, acc, rep);
-  } else {
-    v_chunk<16>(P, T, sh, bh, chunk_t0, chunk_n, acc);
-    v_store_acc<16>(sh, acc, rep);
+  int cg[2];
+#pragma unroll
+  for (int s = 0; s < 2; ++s) {
+    const int ch0 = VFmt<BITS>::HALF_SPLIT ? (16 * g + 8 * s) : (8 * (s * 8 + g));
+    cg[s] = ch0 >> P.gv_shift;
   }
+#pragma unroll 1
+  for (; kt0 < chunk_n; kt0 += step) {
+    if (kt0 + 2 * step < chunk_n) v_load<BITS>(w2, base, chunk_t0, chunk_n, kt0 + 2 * step, g, tig);
+    v_step<BITS>(acc, w0, sh, cg, kt0, g, tig, rep);
+#pragma unroll
+    for (int p = 0; p < 4; ++p)
+#pragma unroll
+      for (int s = 0; s < NW; ++s) {
+        w0[p][s] = w1[p][s];
+        w1[p][s] = w2[p][s];
+      }
+  }
+  // fold acc (fragment layout) into sh.red[warp][head][channel]
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int ch = (BITS == 2) ? (16 * g + 8 * s + mt) : (8 * (s * 8 + g) + mt);
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int h = 2 * tig + e;
+        if (h < rep) sh.red[warp][h][ch] = acc[mt][s * 2 + e];
+      }
+    }
   __syncthreads();
   // partial output of this chunk: warps added in index order
   float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
-  for (int i = tid; i < rep * D; i += NTHREADS) {
+  for (int i = tid; i < rep * D; i += VTHREADS) {
     const int h = i / D, ch = i - h * D;
     float v = sh.red[0][h][ch];
 #pragma unroll
-    for (int w = 1; w < NWARP; ++w) v += sh.red[w][h][ch];
+    for (int w = 1; w < VWARPS; ++w) v += sh.red[w][h][ch];
     part[i] = v;
   }
+}
+
+__global__ void __launch_bounds__(VTHREADS, 2) v_pass_kernel(const __grid_constant__ DecodeParams P) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
+  const int chunk = blockIdx.y, bh = blockIdx.x;
+  const int b = bh / P.H, kvh = bh - b * P.H;
+  const int tid = threadIdx.x;
+  const int rep = P.rep;
+
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
+  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
+  const bool is_res = ti == HQKV_NUM_TIERS;
+  const int vb = is_res ? 16 : T.bits;
+  if (vb == 8) v_body<8>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
+  else if (vb == 4) v_body<4>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
+  else if (vb == 2) v_body<2>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
+  else v_body<16>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, is_res, false);
 
   // ---- this CTA's slice of the probability row
   {
@@ -931,17 +962,17 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     for (int h = 0; h < rep; ++h) {
       const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
       const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
-      for (int pb = p0 + tid; pb < p1; pb += 8 * NTHREADS) {
-        float x[8];
+      for (int pb = p0 + tid; pb < p1; pb += 4 * VTHREADS) {
+        float x[4];
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int p = pb + j * NTHREADS;
+        for (int j = 0; j < 4; ++j) {
+          const int p = pb + j * VTHREADS;
           x[j] = p < p1 ? __ldcg(P.logits + row + p) : 0.f;
         }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int p = pb + j * NTHREADS;
-          if (p < p1) P.weights[row + p] = __float2half_rn(exp2f((x[j] - mh) * 1.4426950408889634f) * inv);
+        for (int j = 0; j < 4; ++j) {
+          const int p = pb + j * VTHREADS;
+          if (p < p1) P.weights[row + p] = __float2half_rn(fast_exp2((x[j] - mh) * 1.4426950408889634f) * inv);
         }
       }
     }
@@ -959,17 +990,17 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
     __threadfence();
     const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
     const int64_t stride = static_cast<int64_t>(rep) * D;
-    for (int i = tid * 4; i < rep * D; i += NTHREADS * 4) {  // four consecutive outputs per thread
+    for (int i = tid * 4; i < rep * D; i += VTHREADS * 4) {  // four consecutive outputs per thread
       const int h = i / D;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = 0; c < P.nv_chunks; c += 16) {  // sixteen 16-byte loads in flight, added in chunk order
-        float4 t[16];
+      for (int c = 0; c < P.nv_chunks; c += 8) {  // eight 16-byte loads in flight, added in chunk order
+        float4 t[8];
 #pragma unroll
-        for (int k = 0; k < 16; ++k)
+        for (int k = 0; k < 8; ++k)
           t[k] = (c + k < P.nv_chunks) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
                                        : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < 16; ++k) {
+        for (int k = 0; k < 8; ++k) {
           v.x += t[k].x;
           v.y += t[k].y;
           v.z += t[k].z;
@@ -988,6 +1019,21 @@ __global__ void __launch_bounds__(NTHREADS) v_pass_kernel(const __grid_constant_
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
+static int sm_count() {
+  static int cached = 0;
+  if (cached == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
+      cached = n;
+    } else {
+      (void)cudaGetLastError();
+      cached = 148;  // B200
+    }
+  }
+  return cached;
+}
+
 static int ilog2(int v) {
   int s = 0;
   while ((1 << s) < v) ++s;
@@ -1013,10 +1059,24 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.H = c->H;
   P.nh_q = c->nh_q;
   P.rep = c->nh_q / c->H;
+  HQKV_REQUIRE((P.rep & (P.rep - 1)) == 0, "decode: nh_q / H must be 1, 2, 4 or 8 (got %d)", P.rep);
+  P.rep_shift = ilog2(P.rep);
   P.gk_shift = ilog2(c->group_k);
   P.gv_shift = ilog2(c->group_v);
   P.scale = c->softmax_scale;
   static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
+  // V chunk: the smallest multiple of 128 tokens (256..1024) with which all CTAs are resident at once
+  // (two 256-thread CTAs per SM); larger caches simply run several waves of 1024-token chunks
+  int v_chunk = 256;
+  {
+    const int64_t slots = 2 * static_cast<int64_t>(sm_count());
+    const int64_t bh = static_cast<int64_t>(c->B) * c->H;
+    for (; v_chunk < V_MAX_CHUNK; v_chunk += 128) {
+      int64_t ctas = ceil_div(c->n_new > 0 ? c->n_new : 0, VWARPS * 16);
+      for (int t = 0; t < HQKV_NUM_TIERS; ++t) ctas += ceil_div(c->tier[t].n_v > 0 ? c->tier[t].n_v : 0, v_chunk);
+      if (ctas * bh <= slots) break;
+    }
+  }
   int64_t nk_total = 0, nv_total = 0;
   int kc = 0, vc = 0;
   for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
@@ -1059,8 +1119,8 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.v_idx = s.v_idx;
     // chunk sizes: about the same number of bytes per CTA whatever the width
     const int b = d.bits;
-    d.k_chunk_tokens = b == 16 ? 512 : K_CHUNK;
-    d.v_chunk_tokens = b == 16 ? 256 : b == 8 ? 256 : b == 4 ? 384 : 640;
+    d.k_chunk_tokens = K_CHUNK;
+    d.v_chunk_tokens = v_chunk;
     d.k_chunk0 = kc;
     d.v_chunk0 = vc;
     kc += static_cast<int>(ceil_div(d.n_k, d.k_chunk_tokens));
@@ -1079,8 +1139,8 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   }
   r.k_data = c->new_k;
   r.v_data = c->new_v;
-  r.k_chunk_tokens = 128;
-  r.v_chunk_tokens = 128;
+  r.k_chunk_tokens = KWARPS * 16;
+  r.v_chunk_tokens = VWARPS * 16;
   r.k_chunk0 = kc;
   r.v_chunk0 = vc;
   kc += static_cast<int>(ceil_div(r.n_k, r.k_chunk_tokens));
@@ -1140,7 +1200,7 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 block(NTHREADS);
   const unsigned BH = static_cast<unsigned>(P.B * P.H);
-  HQKV_REQUIRE(BH <= 65535, "decode: B*H too large");
+  HQKV_REQUIRE(P.nk_chunks <= 65535 && P.nv_chunks <= 65535, "decode: too many chunks");
   {
     // opt in to >48 KB of dynamic shared memory once per device
     static bool attr_set[64] = {};
@@ -1153,11 +1213,11 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
     }
   }
   if (phases & 1) {
-    k_pass_kernel<<<dim3(P.nk_chunks, BH), block, 0, st>>>(P);
+    k_pass_kernel<<<dim3(BH, P.nk_chunks), dim3(KTHREADS), 0, st>>>(P);
     HQKV_LAUNCH_CHECK("k_pass");
   }
   if (phases & 2) {
-    v_pass_kernel<<<dim3(P.nv_chunks, BH), block, sizeof(VShared), st>>>(P);
+    v_pass_kernel<<<dim3(BH, P.nv_chunks), dim3(VTHREADS), sizeof(VShared), st>>>(P);
     HQKV_LAUNCH_CHECK("v_pass");
   }
   return HQKV_OK;
