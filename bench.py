@@ -412,9 +412,15 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
             "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
             "gpu_launches": args.steps * layers * 2, "roofline": roofline, "cpu_baseline": cpu_baseline,
-            "tokens_per_sec_per_gpu": value / world}))
+            "tokens_per_sec_per_gpu": value / world}), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # Leave without tearing the communicator down: destroying a process group whose collectives
+        # were captured into CUDA graphs that are still alive can block forever at interpreter exit.
+        dist.barrier()
+        torch.cuda.synchronize()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -378,9 +378,12 @@ __device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float*
   }
 }
 
-template <int BITS>
+// `stage` (staging of scale/zero and Zq, with its block-wide barriers) runs after the first steps'
+// words have been requested, so that their latency overlaps it; every warp of the CTA calls this
+// function, warps whose span lies beyond the tier only skip the write-out.
+template <int BITS, typename Stage>
 __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                       int chunk_t0, int span_t0) {
+                                       int chunk_t0, int span_t0, Stage stage) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
   const int n = T.n_k;
   const int nslot = n / K_SLOT;  // slots per channel row
@@ -418,6 +421,7 @@ __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, 
   };
 #pragma unroll
   for (int d = 0; d < DEPTH - 1; ++d) load(w[d], d);
+  stage();
   constexpr int NSUB = KSub<BITS>::NSUB, NPER = KSub<BITS>::NPER;
 #pragma unroll
   for (int kt = 0; kt < 8; ++kt) {
@@ -474,6 +478,7 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
                                         int chunk_t0) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int chunk_end = min(chunk_t0 + K_CHUNK, T.n_k);
+  auto stage = [&]() {
   // stage scale/zero of the chunk as [group][channel]: lanes run along the groups of one channel row
   // (contiguous in memory), all loads of a thread are issued before the first store
   {
@@ -527,8 +532,8 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
     }
   }
   __syncthreads();
-  const int span_t0 = chunk_t0 + warp * K_SPAN;
-  if (span_t0 < chunk_end) k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, span_t0);
+  };
+  k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, chunk_t0 + warp * K_SPAN, stage);
 }
 
 // fp16 tier, channel-major rows [D][n]: four tokens per 8-byte slot, no scales; B = q exactly.

@@ -8,7 +8,7 @@ from typing import Tuple
 import torch
 
 from .._lib import HqkvError, check, decode_workspace, lib, ptr, require_cuda, stream_ptr
-from ._cache import UNIFORM_STRATEGIES, build_cache_desc
+from ._cache import UNIFORM_STRATEGIES, cached_cache_desc
 
 
 def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: torch.Tensor, head_dim: int,
@@ -29,7 +29,7 @@ def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: tor
     require_cuda(q)
     if q.dtype != torch.float16 or q.dim() != 4 or q.shape[2] != 1:
         raise ValueError("q must be float16 of shape [B, nh_q, 1, head_dim]")
-    desc, keep, L, dev = build_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+    desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
     if dev != q.device or q.shape[0] != desc.B or q.shape[3] != desc.D:
         raise ValueError("q does not match the cache (device, batch or head_dim)")
     q = q.contiguous()
