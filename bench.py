@@ -30,9 +30,10 @@ if ROOT not in sys.path:
 METRIC = "decode-attn tokens/sec at 32k ctx"
 UNIT = "tokens/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the committed ncu summaries under
-# profiles/ (None until a capture of that kernel exists).
-NCU_TRAFFIC_BYTES = {"k_pass_kernel": None, "v_pass_kernel": None}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload (one cfg1 layer), from
+# the ncu capture summarised in profiles/decode_k_pass_v_pass_cfg1.md.  Only valid for that workload on
+# one GPU; other workloads report null.
+NCU_TRAFFIC_BYTES = {"k_pass_kernel": 19_425_280, "v_pass_kernel": 23_246_080}
 
 
 def parse_args():
@@ -383,7 +384,7 @@ def main():
     for name, nbytes in (("k_pass_kernel", k_bytes), ("v_pass_kernel", v_bytes)):
         achieved = nbytes / (kernel_ms[name] * 1e-3) / 1e9
         kernels.append({"kernel": name, "bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
-                        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name),
+                        "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(name) if (args.workload == "cfg1" and world == 1) else None,
                         "algorithmic_bytes_per_launch": nbytes, "us_per_launch": kernel_ms[name] * 1e3,
                         "peak_source": peak_kind})
     dominant = max(kernels, key=lambda k: k["us_per_launch"])

@@ -622,6 +622,10 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
   const int b = bh / P.H, kvh = bh - b * P.H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
 
+  // Let the V pass of this call (launched with programmatic stream serialisation) start its own
+  // prologue - V words, index lists, scale/zero tiles - as soon as SM resources free up; it waits for
+  // this grid to finish (griddepcontrol.wait) before it touches the logits or the softmax pairs.
+  asm volatile("griddepcontrol.launch_dependents;");
   if (tid < KWARPS * MAX_REP) {
     (&sh.red_m[0][0])[tid] = -INFINITY;
     (&sh.red_l[0][0])[tid] = 0.f;
@@ -829,6 +833,8 @@ __device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, 
     }
   }
 
+  // ---- everything above reads only the cache; from here on the K pass results are needed
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks),
   //      up to four pairs per thread in flight, then slices are folded by shuffles and across warps
   {
@@ -1222,8 +1228,17 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
     HQKV_LAUNCH_CHECK("k_pass");
   }
   if (phases & 2) {
-    v_pass_kernel<<<dim3(BH, P.nv_chunks), dim3(VTHREADS), sizeof(VShared), st>>>(P);
-    HQKV_LAUNCH_CHECK("v_pass");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(BH, P.nv_chunks);
+    cfg.blockDim = dim3(VTHREADS);
+    cfg.dynamicSmemBytes = sizeof(VShared);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // may overlap the tail of the K pass
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HQKV_CUDA(cudaLaunchKernelEx(&cfg, v_pass_kernel, P));
   }
   return HQKV_OK;
 }
