@@ -347,3 +347,43 @@ def test_gemv_uniform_group_vs_oracle(ops, cuda_device, bits):
                                                   bits)
         err = np.abs(got.float().cpu().numpy() - want).max() / np.abs(want).max()
         assert err <= 2e-3, f"gemv bits {bits} K {K} N {N}: rel err {err:.3e}"
+
+
+# ---------------------------------------------------------------------------------------------
+# sweep: uniform and mixed tiers x group size x batch x GQA ratio (shapes of the kernel microbench)
+# ---------------------------------------------------------------------------------------------
+SWEEP_RATIOS = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "mixed": (0.25, 0.5, 0.25)}
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("tiers", ["all8", "all4", "all2", "mixed"])
+def test_decode_sweep_vs_oracle(ops, cuda_device, tiers, group):
+    """Context 1024 + a ragged residual, batch 1 and 3, GQA 4 and 8, K with outlier channels, K and V
+    ranked differently (times_range): the fused decode against the fp32 oracle, tolerance 2e-3."""
+    from hqekv_b200 import synthetic
+    for batch, nh_q, nh_kv, evict in ((1, 32, 8, 0.0), (3, 16, 2, 0.125)):
+        cfg = synthetic.CacheConfig(f"sweep-{tiers}-g{group}", batch, nh_q, nh_kv, 128, 1024 + 40, 40,
+                                    SWEEP_RATIOS[tiers], evict, group, True, 1)
+        cache, q = synthetic.build_cache(cfg, cuda_device, seed=group + batch, times_range=True)
+        check_attention(ops, cache, q, group, group, f"{cfg.name} B{batch} {nh_q}/{nh_kv}")
+
+
+def test_decode_long_context_shard_properties(ops, cuda_device):
+    """One kv head of the 128k-context case (what one of 8 GPUs holds per head, batch 1): 10/25/65 % in
+    8/4/2-bit, 30 % evicted, residual 256.  Checked against torch fp32 attention over the dense
+    reconstruction on the GPU, tolerance 2e-3; the probabilities must sum to 1."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CONFIGS["cfg3"]
+    cfg1 = synthetic.CacheConfig("cfg3-one-head", 1, 4, 1, 128, cfg.context, cfg.residual, cfg.ratios, cfg.evict,
+                                 cfg.group, False, 1)
+    cache, q = synthetic.build_cache(cfg1, cuda_device, seed=3)
+    L = synthetic.logical_length(cache)
+    assert L == 131072 - 1226 * 32
+    w, out = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", 32, 32)
+    Kd, Vd = ops.hqe_2.KV_cache_reconstruct_hqe(cache, "uniform_group", 32, 32)
+    logits = torch.matmul(q.float().view(1, 1, 4, 128), Kd.float().transpose(2, 3)) / (128 ** 0.5)
+    p = torch.softmax(logits, dim=-1)
+    ref = torch.matmul(p, Vd.float()).view(1, 4, 1, 128)
+    rel = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
+    assert rel <= ATTN_REL_TOL, f"128k decode rel err {rel:.3e}"
+    assert (w.float().sum(-1) - 1).abs().max().item() < 2e-2
