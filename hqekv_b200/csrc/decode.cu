@@ -287,12 +287,21 @@ static_assert(K_MAXG == 8 || K_MAXG == 16, "a chunk must hold 8 or 16 groups of 
 constexpr int K_SROW = D + SCALE_PAD;       // halfs per staged scale row
 constexpr int K_TROW = MAX_REP + 1;         // floats per token row of the logit tile (odd: no bank conflicts)
 
+// 8-byte global -> shared copy without a register round trip; completion = wait_group + __syncwarp
+__device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+
 struct KShared {
   uint2 qfrag[8][32];          // B fragments of q per 16-channel step and lane
   __half s[K_MAXG][K_SROW];    // scale[group][channel]
   __half z[K_MAXG][K_SROW];    // zero[group][channel]
   float zq[K_MAXG][MAX_REP];   // sum_d zero*q per group and head
   float tile[KWARPS][K_SPAN * K_TROW];  // per warp: logits [token][head] for the coalesced write-out
+  int64_t idx[KWARPS][K_SPAN];          // per warp: logical positions of the span's tokens (fetched up front)
   float red_m[KWARPS][MAX_REP], red_l[KWARPS][MAX_REP];
 };
 
@@ -410,6 +419,13 @@ __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, 
 #pragma unroll
   for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
+  // logical positions of the span's tokens go to shared memory now, to be there at write-out time
+#pragma unroll
+  for (int j = 0; j < K_SPAN / 32; ++j) {
+    const int t = lane + 32 * j;
+    if (span_t0 + t < n) cp_async_8(&sh.idx[warp][t], T.k_idx + span_t0 + t);
+  }
+  cp_async_commit();
   constexpr int DEPTH = 3;  // steps in flight: the one being used and two ahead
   uint32_t w[DEPTH][4][2];
   auto load = [&](uint32_t (&dst)[4][2], int kt) {
@@ -469,16 +485,18 @@ __device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, 
       for (int i = 0; i < K_SLOT; ++i)
         tile[((r * 8 + g) * K_SLOT + i) * K_TROW + h] = (acc[i][r * 2 + e] + zq) * P.scale;
     }
+  cp_async_wait_all();
   __syncwarp();
-  k_write_tile(P, tile, min(K_SPAN, n - span_t0), T.k_idx + span_t0, 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
+  k_write_tile(P, tile, min(K_SPAN, n - span_t0), sh.idx[warp], 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
 }
 
-template <int BITS>
+template <int BITS, typename StoreQ>
 __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                        int chunk_t0) {
+                                        int chunk_t0, StoreQ store_q) {
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
   const int chunk_end = min(chunk_t0 + K_CHUNK, T.n_k);
   auto stage = [&]() {
+  store_q();
   // stage scale/zero of the chunk as [group][channel]: lanes run along the groups of one channel row
   // (contiguous in memory), all loads of a thread are issued before the first store
   {
@@ -631,18 +649,26 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
     (&sh.red_l[0][0])[tid] = 0.f;
   }
   // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
+  // (requested now, stored to shared memory by store_q() just before the first block-wide barrier, so
+  //  that warp 0 does not sit on this latency before it has requested its K words)
+  uint2 qf[8];
   if (warp == 0) {
     const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
 #pragma unroll
     for (int kt = 0; kt < 8; ++kt) {
-      uint2 f = make_uint2(0u, 0u);
+      qf[kt] = make_uint2(0u, 0u);
       if (g < P.rep) {
-        f.x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
-        f.y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
+        qf[kt].x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
+        qf[kt].y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
       }
-      sh.qfrag[kt][lane] = f;
     }
   }
+  auto store_q = [&]() {
+    if (warp == 0) {
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) sh.qfrag[kt][lane] = qf[kt];
+    }
+  };
 
   int ti = HQKV_NUM_TIERS;
 #pragma unroll
@@ -652,6 +678,7 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
   const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
 
   if (ti == HQKV_NUM_TIERS || T.bits == 16) {
+    store_q();
     __syncthreads();
     const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
     if (ti == HQKV_NUM_TIERS) {
@@ -662,11 +689,11 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
       if (t0 < chunk_end) k_f16_span(P, T, sh, bh, b, kvh, t0);
     }
   } else if (T.bits == 8) {
-    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0);
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
   } else if (T.bits == 4) {
-    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0);
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
   } else {
-    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0);
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
   }
 
   // (max, sum) of this CTA per head from the warps' pairs
@@ -871,6 +898,28 @@ __device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, 
     __syncthreads();
   }
 
+  // ---- this CTA's slice of the probability row (needs only the global max / sum)
+  {
+    const int p0 = chunk * P.w_slice, p1 = min(p0 + P.w_slice, P.L);
+    for (int h = 0; h < rep; ++h) {
+      const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+      const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
+      for (int pb = p0 + tid; pb < p1; pb += 4 * VTHREADS) {
+        float x[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int p = pb + j * VTHREADS;
+          x[j] = p < p1 ? __ldcg(P.logits + row + p) : 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int p = pb + j * VTHREADS;
+          if (p < p1) P.weights[row + p] = __float2half_rn(fast_exp2((x[j] - mh) * 1.4426950408889634f) * inv);
+        }
+      }
+    }
+  }
+
   // ---- exp(logit - max) of the chunk's tokens: the gathers of four heads are in flight together
   for (int h0 = 0; h0 < rep; h0 += 4) {
     float x[4][V_STAGE_ITERS];
@@ -967,28 +1016,6 @@ __global__ void __launch_bounds__(VTHREADS, 2) v_pass_kernel(const __grid_consta
   else if (vb == 2) v_body<2>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
   else v_body<16>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, is_res, false);
 
-  // ---- this CTA's slice of the probability row
-  {
-    const int p0 = chunk * P.w_slice, p1 = min(p0 + P.w_slice, P.L);
-    for (int h = 0; h < rep; ++h) {
-      const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
-      const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
-      for (int pb = p0 + tid; pb < p1; pb += 4 * VTHREADS) {
-        float x[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int p = pb + j * VTHREADS;
-          x[j] = p < p1 ? __ldcg(P.logits + row + p) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int p = pb + j * VTHREADS;
-          if (p < p1) P.weights[row + p] = __float2half_rn(fast_exp2((x[j] - mh) * 1.4426950408889634f) * inv);
-        }
-      }
-    }
-  }
-
   // ---- last CTA of this (batch, kv head) sums the partial outputs in chunk order
   __threadfence();
   __syncthreads();
@@ -999,29 +1026,43 @@ __global__ void __launch_bounds__(VTHREADS, 2) v_pass_kernel(const __grid_consta
   __syncthreads();
   if (sh.is_last) {
     __threadfence();
+    // threads 0..127 add the first half of the chunks, 128..255 the second half (each in chunk order,
+    // four consecutive outputs per thread, eight 16-byte loads in flight), then the halves are added
     const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
     const int64_t stride = static_cast<int64_t>(rep) * D;
-    for (int i = tid * 4; i < rep * D; i += VTHREADS * 4) {  // four consecutive outputs per thread
-      const int h = i / D;
+    const int half = tid >> 7, t4 = (tid & 127) * 4;
+    const int c_mid = (P.nv_chunks + 1) >> 1;
+    const int c_lo = half ? c_mid : 0, c_hi = half ? P.nv_chunks : c_mid;
+    float* scratch = &sh.red[0][0][0];  // rep*D floats, free again after the partial write above
+    for (int i0 = 0; i0 < rep * D; i0 += 512) {
+      const int i = i0 + t4;
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = 0; c < P.nv_chunks; c += 8) {  // eight 16-byte loads in flight, added in chunk order
-        float4 t[8];
+      if (i < rep * D) {
+        for (int c = c_lo; c < c_hi; c += 8) {
+          float4 t[8];
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          t[k] = (c + k < P.nv_chunks) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+          for (int k = 0; k < 8; ++k)
+            t[k] = (c + k < c_hi) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          v.x += t[k].x;
-          v.y += t[k].y;
-          v.z += t[k].z;
-          v.w += t[k].w;
+          for (int k = 0; k < 8; ++k) {
+            v.x += t[k].x;
+            v.y += t[k].y;
+            v.z += t[k].z;
+            v.w += t[k].w;
+          }
         }
+        if (half) *reinterpret_cast<float4*>(scratch + i) = v;
       }
-      const float inv = 1.f / sh.gl[h];
-      __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
-      o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
-      o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
+      __syncthreads();
+      if (!half && i < rep * D) {
+        const float4 u = *reinterpret_cast<const float4*>(scratch + i);
+        const float inv = 1.f / sh.gl[i / D];
+        __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
+        o[0] = __floats2half2_rn((v.x + u.x) * inv, (v.y + u.y) * inv);
+        o[1] = __floats2half2_rn((v.z + u.z) * inv, (v.w + u.w) * inv);
+      }
+      __syncthreads();
     }
     if (tid == 0) P.counters[bh] = 0u;  // ready for the next call
   }
