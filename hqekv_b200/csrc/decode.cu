@@ -708,6 +708,9 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 // ------------------------------------------------------------------------------------------------
 // v_pass
 // ------------------------------------------------------------------------------------------------
+#ifndef V_MIN_CTAS
+#define V_MIN_CTAS 2
+#endif
 constexpr int VWARPS = 8;
 constexpr int VTHREADS = VWARPS * 32;
 constexpr int V_MAX_CHUNK = 1024;                       // tokens per CTA at most (multiple of VWARPS*16)
@@ -994,7 +997,7 @@ __device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, 
   }
 }
 
-__global__ void __launch_bounds__(VTHREADS, 2) v_pass_kernel(const __grid_constant__ DecodeParams P) {
+__global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
   const int chunk = blockIdx.y, bh = blockIdx.x;
@@ -1121,7 +1124,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   // (two 256-thread CTAs per SM); larger caches simply run several waves of 1024-token chunks
   int v_chunk = 256;
   {
-    const int64_t slots = 2 * static_cast<int64_t>(sm_count());
+    const int64_t slots = V_MIN_CTAS * static_cast<int64_t>(sm_count());
     const int64_t bh = static_cast<int64_t>(c->B) * c->H;
     for (; v_chunk < V_MAX_CHUNK; v_chunk += 128) {
       int64_t ctas = ceil_div(c->n_new > 0 ? c->n_new : 0, VWARPS * 16);
