@@ -1,0 +1,126 @@
+"""Kernel microbench sweep of the fused decode and of quantise+pack.
+
+    python -m hqekv_b200.sweep [--out sweep.jsonl] [--quick]
+
+For every point (context, tier mix, group size, batch) a model-shaped stack of 32 layer caches is built
+(8 kv heads x head_dim 128, GQA 4, fp16 N(0,1) data, K with outlier channels, residual 128, no eviction)
+and the K pass, the V pass and the whole decode step are replayed from CUDA graphs and timed with CUDA
+events.  Reported per point: microseconds per layer, achieved GB/s on the algorithmic bytes and the
+fraction of the measured copy bandwidth.  Small contexts fit the 126 MB L2 across layers; the line says
+so (`working_set_MB`).  One JSON object per line.
+"""
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+from . import synthetic
+from ._lib import check, lib, ptr, stream_ptr
+from .quant._cache import build_cache_desc
+from .quant.pack_unpack import uniform_group_quantize_pack_last_dim
+
+TIER_MIXES = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "mixed": (0.25, 0.5, 0.25)}
+
+
+def _graph_time(fn, reps):
+    fn()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(g, stream=side):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    g.replay()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        g.replay()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / reps
+
+
+def decode_point(dev, ctx, mix, group, batch, layers, peak_gbs):
+    cfg = synthetic.CacheConfig(f"sweep-ctx{ctx}-{mix}-g{group}-b{batch}", batch, 32, 8, 128, ctx, 128,
+                                TIER_MIXES[mix], 0.0, group, True, layers)
+    items = []
+    for layer in range(layers):
+        cache, q = synthetic.build_cache(cfg, dev, seed=layer % 4)
+        desc, keep, L, _ = build_cache_desc(cache, cfg.nh_q, group, group)
+        ws = torch.zeros(lib.hqkv_decode_workspace_bytes(desc), dtype=torch.uint8, device=dev)
+        w = torch.empty(batch, cfg.nh_q, 1, L, dtype=torch.float16, device=dev)
+        o = torch.empty(batch, cfg.nh_q, 1, 128, dtype=torch.float16, device=dev)
+        items.append((desc, keep, cache, q, ws, w, o))
+    nbytes = synthetic.cache_bytes(items[0][2], cfg.nh_q)
+
+    def run(phase):
+        st = stream_ptr(dev)
+        for desc, _, _, q, ws, w, o in items:
+            check(lib.hqkv_decode_attention_phases(desc, ptr(q), ptr(w), ptr(o), ptr(ws), ws.numel(), phase, st))
+
+    run(3)
+    out = {"kind": "decode", "context": ctx, "tiers": mix, "group": group, "batch": batch, "layers": layers,
+           "cache_MB_per_layer": nbytes / 1e6, "working_set_MB": nbytes * layers / 1e6}
+    for phase, name in ((1, "k_pass"), (2, "v_pass"), (3, "step")):
+        us = _graph_time(lambda: run(phase), 5) * 1e3 / layers
+        b = nbytes / 2 if phase < 3 else nbytes
+        out[f"{name}_us"] = us
+        out[f"{name}_GBps"] = b / us / 1e3
+        out[f"{name}_frac"] = b / us / 1e3 / peak_gbs
+    out["tokens_per_s"] = batch / (out["step_us"] * 1e-6 * layers) if layers == 32 else None
+    return out
+
+
+def quantize_point(dev, tokens, bit, group, peak_gbs):
+    x = torch.randn(1, 8, tokens, 128, device=dev).half()
+    out = {"kind": "quantize_pack", "tokens": tokens, "bits": bit, "group": group}
+    for name, view in (("v_rows", x), ("k_cols", x.transpose(2, 3))):
+        ms = _graph_time(lambda: uniform_group_quantize_pack_last_dim(view, group, bit), 10)
+        nbytes = x.numel() * (2 + bit / 8 + 4 / group)
+        out[f"{name}_us"] = ms * 1e3
+        out[f"{name}_GBps"] = nbytes / ms / 1e6
+        out[f"{name}_frac"] = nbytes / ms / 1e6 / peak_gbs
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--out", default="gpurun_out/sweep.jsonl")
+    ap.add_argument("--quick", action="store_true")
+    args = ap.parse_args()
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    peaks = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    peak = float(json.load(open(peaks))["hbm_gbs"]) if os.path.exists(peaks) else 6650.0
+    os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
+    ctxs = (1024 + 128, 4096, 32768) if args.quick else (1024 + 128, 4096, 16384, 32768, 131072)
+    points = []
+    for ctx in ctxs:
+        for mix in (("mixed",) if args.quick else ("all8", "all4", "all2", "mixed")):
+            for group in ((32,) if args.quick else (32, 128)):
+                for batch in (1, 8, 32):
+                    per_layer = batch * 8 * ctx * 288          # upper bound, bytes
+                    if per_layer * 32 > 60e9 or (batch == 32 and ctx > 16384):
+                        continue
+                    points.append((ctx, mix, group, batch))
+    with open(args.out, "w") as f:
+        for ctx, mix, group, batch in points:
+            r = decode_point(dev, ctx, mix, group, batch, 32, peak)
+            f.write(json.dumps(r) + "\n")
+            f.flush()
+            print(json.dumps(r), flush=True)
+            torch.cuda.empty_cache()
+        for tokens in ((4096, 32768) if args.quick else (1024, 8192, 32768, 131072)):
+            for bit in (8, 4, 2):
+                r = quantize_point(dev, tokens, bit, 32, peak)
+                f.write(json.dumps(r) + "\n")
+                print(json.dumps(r), flush=True)
+
+
+if __name__ == "__main__":
+    sys.exit(main())
