@@ -257,109 +257,413 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
 // ------------------------------------------------------------------------------------------------
 // k_pass
 // ------------------------------------------------------------------------------------------------
-// Quantised K tier: rows = channels, packed words along tokens.  A CTA of KWARPS warps takes a chunk of
-// KWARPS*64 tokens (one scale group per 32 tokens at group 32) of one (batch, kv head); each warp takes one 64-token
-// span: fragment row g <-> the 4 tokens of slot g, row g+8 <-> slot g+8, M-tile i <-> i-th token of
-// every slot, so a thread uses every code of every word it loads and no operand passes through
-// shared memory.  Words go global -> registers one 16-channel step ahead of their use.  Short
-// per-warp programs and many warps per SM matter more here than wide loads: at batch 1 a layer is
-// only ~130 KB of K per SM, and the time is set by the length of one warp's dependent chain.
+// Quantised K tier: rows = channels, packed words along tokens.  Every warp of a CTA owns one TILE:
+// all 128 channel rows x 64 bytes of codes (32 bytes at 2 bits), i.e. 64 / 128 / 128 tokens at
+// 8 / 4 / 2 bits, plus the tile's logical positions; the CTA shares the scale / zero rows of its 256
+// or 512 tokens and q.  All of it is copied global -> shared with 16-byte cp.async as the first
+// action (no registers are tied up, ~45 KB per CTA are in flight at once) and each warp then works
+// out of shared memory in sub-spans of 64 tokens.  Wide copies in, ldmatrix out: the L1 data pipe
+// moves 128 bytes per wavefront both ways.  (Per-lane loads of the 1-4 bytes a thread needs - from
+// global or from shared memory - saturate that pipe at a quarter of the HBM bandwidth.)
 //
-// Precision: the logits must match an fp32 dequant-matmul, and with x10 outlier channels the fp16
-// rounding of a dequantised K value alone costs ~2e-3 on the attention output.  So the product
-// code*scale (8 + 11 significant bits) is carried EXACTLY as two fp16 numbers, hi = fp16(code*scale)
-// and lo = code*scale - hi, each multiplied with q on the tensor pipe into the same fp32
-// accumulator, and the zero point enters through Zq[group][head] = sum_d zero[d,group]*q[head][d],
-// itself one small MMA per 16-channel step (fp16 inputs are exact, fp32 accumulation).
+// ldmatrix.trans over 8 channel rows x 16 bytes hands lane (g, tig) the 16-bit block g of channels
+// 2*tig and 2*tig+1 in one register: exactly the two K-neighbours of an m16n8k16 A fragment for the
+// tokens of block g (2 / 4 / 8 tokens at 8 / 4 / 2 bits).  What keeps the instruction count low:
+//  * the integer codes enter the tensor pipe as they are: a masked field at bit k < 10 of a 16-bit
+//    lane IS the fp16 subnormal code * 2^(k-24), exactly, so one AND per pair of codes builds an A
+//    fragment register; the power of two comes back out in the epilogue;
+//  * the scale lives in the B operand: logit = sum_c (q_c * scale_c) * code_c + sum_c q_c * zero_c.
+//    A sub-span holds two 32-token scale groups; B columns 0-3 hold q*scale of the first group for
+//    four query heads and columns 4-7 that of the second, and each fragment row keeps the half of
+//    its accumulators whose group matches.  With eight query heads per kv head the warp walks its
+//    tile once per half of the heads;
+//  * q*scale (11 x 11 significant bits) is carried EXACTLY as hi = fp16(q*scale) and
+//    lo = q*scale - hi, two MMAs into the same fp32 accumulator.  (One fp16 rounding of it - or of
+//    the dequantised K value - costs ~2e-3 on the attention output with x10 outlier channels.)
+//  * the zero point enters through Zq[group][head] = sum_c zero_c * q_c, one small MMA per tile;
+//  * every lane scatters its own logits from registers and keeps a running (max, sum-exp).
 #ifndef K_MIN_CTAS
-#define K_MIN_CTAS 7
+#define K_MIN_CTAS 4
 #endif
-#ifndef K_WARPS
-#define K_WARPS 4
-#endif
-constexpr int KWARPS = K_WARPS;
+constexpr int KWARPS = 4;
 constexpr int KTHREADS = KWARPS * 32;
-constexpr int K_SLOT = 4;                   // tokens per slot (one load of one lane)
-constexpr int K_SPAN = 16 * K_SLOT;         // 64 tokens per warp span
-constexpr int K_CHUNK = KWARPS * K_SPAN;    // 512 tokens per CTA
-constexpr int K_MAXG = K_CHUNK / 32;        // scale groups per chunk at group size 32 (at most 16: rows of the Zq MMA)
-static_assert(K_MAXG == 8 || K_MAXG == 16, "a chunk must hold 8 or 16 groups of 32 tokens");
-constexpr int K_SROW = D + SCALE_PAD;       // halfs per staged scale row
-constexpr int K_TROW = MAX_REP + 1;         // floats per token row of the logit tile (odd: no bank conflicts)
+constexpr int K_SPAN = 64;                   // tokens per sub-span: four M-tiles of 16
+constexpr int K_SLOT = 4;                    // fp16 tier: tokens per 8-byte slot
+constexpr int K_TILE_BYTES = D * 64;         // codes of one tile
+constexpr int K_MAX_TT = 128;                // tokens per tile at most
+constexpr int K_CHUNK_GROUPS = KWARPS * K_MAX_TT / 32;  // scale groups per CTA at most (group size 32)
+constexpr int K_RAW_HALFS = K_CHUNK_GROUPS + 8;         // staged halfs per channel row: three aligned 16-byte pieces
+constexpr int K_TROW = MAX_REP + 1;          // floats per token row of the logit tile (odd: no bank conflicts)
+constexpr float LOG2E = 1.4426950408889634f;
 
-// 8-byte global -> shared copy without a register round trip; completion = wait_group + __syncwarp
+template <int BITS>
+struct KTile {
+  static constexpr int PITCH = BITS == 2 ? 32 : 64;       // bytes per channel row
+  static constexpr int TOKENS = PITCH * 8 / BITS;         // 64, 128, 128
+  static constexpr int NSUB = TOKENS / K_SPAN;            // sub-spans: 1, 2, 2
+  static constexpr int TPC = 128 / BITS;                  // tokens per 16-byte piece: 16, 32, 64
+  static constexpr int CPS = K_SPAN / TPC;                // pieces of a row per sub-span: 4, 2, 1
+  // byte offset of 16-byte piece c of a channel row.  The piece index is XORed with row bits so that
+  // the eight rows of an ldmatrix (same logical piece) and the pieces a cp.async instruction writes
+  // both spread over all banks.
+  static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
+    if constexpr (PITCH == 64) {
+      return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
+    } else {
+      return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    }
+  }
+};
+
+// global -> shared copies without a register round trip; completion = wait_group + barrier
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
 __device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
                "l"(src));
 }
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// four 8x8 matrices of 16-bit elements, transposed: lane (g, tig) gets elements (row 2*tig, col g) and
+// (row 2*tig+1, col g) of matrix i in r[i]; lanes 8*i .. 8*i+7 supply the row addresses of matrix i
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row_ptr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row_ptr))));
+}
+
+struct KWarpShared {
+  union {
+    unsigned char codes[K_TILE_BYTES];
+    float tile[64 * K_TROW];  // fp16 tier / residual: logits [token][head]
+  } u;
+  int64_t idx[K_MAX_TT];      // logical positions of the tile's tokens
+  float zq[4][MAX_REP];       // sum_c zero*q per group of the tile and head
+};
 
 struct KShared {
-  uint2 qfrag[8][32];          // B fragments of q per 16-channel step and lane
-  __half s[K_MAXG][K_SROW];    // scale[group][channel]
-  __half z[K_MAXG][K_SROW];    // zero[group][channel]
-  float zq[K_MAXG][MAX_REP];   // sum_d zero*q per group and head
-  float tile[KWARPS][K_SPAN * K_TROW];  // per warp: logits [token][head] for the coalesced write-out
-  int64_t idx[KWARPS][K_SPAN];          // per warp: logical positions of the span's tokens (fetched up front)
+  // B fragments of q per 16-channel step and lane: channels 16*kt + 2*tig + (0,1 | 8,9).  fp16 tier /
+  // residual CTAs: [0] with column n = head n.  Quantised CTAs: [hh] with column n = head
+  // 4*hh + (n & 3) (columns 4-7 repeat 0-3).
+  uint2 qb[2][8][32];
+  // scale / zero rows of the CTA's tokens as they lie in memory: channel c, three aligned 16-byte
+  // pieces starting at or before the chunk's first group
+  __half s[D][K_RAW_HALFS];
+  __half z[D][K_RAW_HALFS];
   float red_m[KWARPS][MAX_REP], red_l[KWARPS][MAX_REP];
+  KWarpShared w[KWARPS];
 };
 
-// one slot = 4 tokens of one channel: 4, 2 or 1 byte
+// Request the scale / zero rows of the CTA's chunk: thread t copies channel t.  The chunk's groups
+// [g0c, g0c + ngc) of a channel are 2*ngc bytes at any 2-byte alignment; the (up to) three aligned
+// 16-byte pieces that cover them go to shared memory as they are, so group gamma of channel c is
+// half ((c*G + g0c) & 7) + gamma of row c.  (The planes hold B*H*128*G halfs, a multiple of 8, and
+// start 16-byte aligned, so every aligned piece that begins inside a plane also ends inside it.)
+__device__ __forceinline__ void k_scales_request(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int g0c,
+                                                 int ngc) {
+  const int ch = threadIdx.x;  // KTHREADS == D
+  const int G = T.n_k >> P.gk_shift;
+  const int64_t e0 = (static_cast<int64_t>(bh) * D + ch) * G + g0c;
+  const int64_t a = e0 & ~static_cast<int64_t>(7);
+#pragma unroll
+  for (int p = 0; p < K_RAW_HALFS / 8; ++p)
+    if (a + 8 * p < e0 + ngc) {
+      cp_async_16(&sh.s[ch][8 * p], T.k_scale + a + 8 * p);
+      cp_async_16(&sh.z[ch][8 * p], T.k_zero + a + 8 * p);
+    }
+}
+static_assert(KTHREADS == D, "one thread per channel row");
+
+// Request a tile: four commit groups, the codes of channel rows 0-31 (with the positions), 32-63,
+// 64-95, 96-127 (two 16-channel steps each).  ntok = valid tokens of the tile (a multiple of 32).
 template <int BITS>
-__device__ __forceinline__ uint32_t kslot_load(const unsigned char* row, int64_t slot) {
-  if constexpr (BITS == 8) {
-    return ld_stream(reinterpret_cast<const uint32_t*>(row) + slot);
-  } else if constexpr (BITS == 4) {
-    unsigned short v;
-    asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=h"(v) : "l"(reinterpret_cast<const uint16_t*>(row) + slot));
-    return v;
-  } else {
-    uint32_t v;
-    asm volatile("ld.global.nc.L1::no_allocate.u8 %0, [%1];" : "=r"(v) : "l"(row + slot));
-    return v;
+__device__ __forceinline__ void k_tile_request(const TierDev& T, KWarpShared& ws, int bh, int tile_t0, int ntok) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31;
+  const int n = T.n_k;
+#pragma unroll
+  for (int j = 0; j < TL::TOKENS / 32; ++j) {
+    const int t = lane + 32 * j;
+    if (t < ntok) cp_async_8(&ws.idx[t], T.k_idx + tile_t0 + t);
+  }
+  const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes +
+                             static_cast<int64_t>(tile_t0) * BITS / 8;
+  const int valid_bytes = ntok * BITS / 8;  // per row: a multiple of 8
+  // a copy instruction moves 8 rows x 64 bytes (16 rows x 32 bytes at 2 bits)
+  constexpr int LPR = BITS == 2 ? 2 : 4;    // lanes per row
+  constexpr int RPI = 32 / LPR;             // rows per instruction
+  const int c = lane % LPR, r0 = lane / LPR;
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int i = 0; i < 32 / RPI; ++i) {
+      const int row = quarter * 32 + i * RPI + r0;
+      const unsigned char* s = src + row * row_bytes + 16 * c;
+      unsigned char* d = ws.u.codes + TL::offset(row, c);
+      if constexpr (BITS == 2) {  // rows of 2-bit codes are only 8-byte aligned in memory
+        if (16 * c < valid_bytes) cp_async_8(d, s);
+        if (16 * c + 8 < valid_bytes) cp_async_8(d + 8, s + 8);
+      } else {
+        if (16 * c < valid_bytes) cp_async_16(d, s);
+      }
+    }
+    cp_async_commit();
   }
 }
 
-// Exact integer codes (fp16 pairs: low half = row a, high half = row b) of sub-unit j of a slot.
-// 8-bit: one sub-unit of 4 tokens; 4-bit: two bytes of 2 tokens; 2-bit: one byte of 4 tokens.
-// Token index inside the slot = j*NPER + k.
+// 16-bit halves of two words -> one half2 register (low half from a)
+__device__ __forceinline__ uint32_t pack_lo16(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }
+
+// Zq[group][head] of the tile for half hh of the heads: rows of the A operand are the tile's groups
+// (at most four; rows 4-7 repeat them, rows 8-15 are zero).  zrow: this lane's two staged zero rows
+// (channels 2*tig and 2*tig+1) at the half of the tile's first group.
+__device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, const __half* z_even, const __half* z_odd) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int gam = g & 3;
+  float zacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt) {
+    const int o = (16 * kt) * K_RAW_HALFS + gam;
+    const uint32_t a0 = pack_lo16(__half_as_ushort(z_even[o]), __half_as_ushort(z_odd[o]));
+    const uint32_t a2 = pack_lo16(__half_as_ushort(z_even[o + 8 * K_RAW_HALFS]), __half_as_ushort(z_odd[o + 8 * K_RAW_HALFS]));
+    const uint2 bq = sh.qb[hh][kt][lane];
+    mma16816(zacc, a0, 0u, a2, 0u, bq.x, bq.y);
+  }
+  __syncwarp();  // readers of the previous half are done
+  if (g < 4 && tig < 2) {  // columns 0-3 are the four heads of this half; 4-7 repeat them
+    ws.zq[g][2 * tig] = zacc[0];
+    ws.zq[g][2 * tig + 1] = zacc[1];
+  }
+  __syncwarp();
+}
+
+// A fragment registers of the four M-tiles of a sub-span from the ldmatrix registers of one 8-channel
+// octet.  R[c]: 16-byte piece c of the sub-span; each 16-bit half = block g of one channel.
+// lo[i] -> fragment row g of M-tile i, hi[i] -> row g+8.  Fields are fp16 subnormals code * 2^(k-24);
+// KField<BITS>::shift(i) gives k of M-tile i.
+//   8 bits: block = 2 tokens.  M-tile i = (piece p = i>>1, token e = i&1): row g <- piece p, row g+8 <-
+//           piece p+2.  Tokens: row g = 16p + 2g + e, row g+8 = 32 + 16p + 2g + e.
+//   4 bits: block = 4 tokens.  M-tile i: row g <- piece 0 token i, row g+8 <- piece 1 token i.
+//           Tokens: row g = 4g + i, row g+8 = 32 + 4g + i.
+//   2 bits: block = 8 tokens, one piece.  M-tile i: row g <- token i, row g+8 <- token 4+i of block g.
+//           Tokens: row g = 8g + i, row g+8 = 8g + 4 + i.
 template <int BITS>
-struct KSub {
-  static constexpr int NSUB = BITS == 4 ? 2 : 1;
-  static constexpr int NPER = K_SLOT / NSUB;
+struct KField {
+  static __host__ __device__ constexpr int shift(int i) { return BITS == 8 ? 0 : BITS == 4 ? 4 * (i & 1) : 2 * i; }
 };
 template <int BITS>
-__device__ __forceinline__ void sub_codes(uint32_t wa, uint32_t wb, int j, __half2 (&c)[KSub<BITS>::NPER]) {
-  const __half2 k1024 = __half2half2(__float2half(1024.f));
+__device__ __forceinline__ void octet_frags(const uint32_t* R, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
   if constexpr (BITS == 8) {
-    const uint32_t lo = __byte_perm(wa, wb, 0x5140);  // [a0 b0 a1 b1]
-    const uint32_t hi = __byte_perm(wa, wb, 0x7362);  // [a2 b2 a3 b3]
-    c[0] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4140)), k1024);
-    c[1] = __hsub2(u32_as_h2(__byte_perm(lo, 0x64646464u, 0x4342)), k1024);
-    c[2] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4140)), k1024);
-    c[3] = __hsub2(u32_as_h2(__byte_perm(hi, 0x64646464u, 0x4342)), k1024);
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      lo[2 * p] = R[p] & 0x00FF00FFu;
+      lo[2 * p + 1] = __byte_perm(R[p], 0u, 0x4341);
+      hi[2 * p] = R[p + 2] & 0x00FF00FFu;
+      hi[2 * p + 1] = __byte_perm(R[p + 2], 0u, 0x4341);
+    }
   } else if constexpr (BITS == 4) {
-    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-    c[0] = __hsub2(u32_as_h2((t & 0x000F000Fu) | 0x64006400u), k1024);
-    c[1] = __hfma2(u32_as_h2((t & 0x00F000F0u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
-                   __half2half2(__float2half(-64.f)));
+    const uint32_t a = R[0], as = R[0] >> 8, b = R[1], bs = R[1] >> 8;
+    lo[0] = a & 0x000F000Fu;
+    lo[1] = a & 0x00F000F0u;
+    lo[2] = as & 0x000F000Fu;
+    lo[3] = as & 0x00F000F0u;
+    hi[0] = b & 0x000F000Fu;
+    hi[1] = b & 0x00F000F0u;
+    hi[2] = bs & 0x000F000Fu;
+    hi[3] = bs & 0x00F000F0u;
   } else {
-    const uint32_t t = __byte_perm(wa, wb, 0x4400);
-    c[0] = __hsub2(u32_as_h2((t & 0x00030003u) | 0x64006400u), k1024);
-    c[1] = __hfma2(u32_as_h2((t & 0x000C000Cu) | 0x64006400u), __half2half2(__float2half(0.25f)),
-                   __half2half2(__float2half(-256.f)));
-    c[2] = __hfma2(u32_as_h2((t & 0x00300030u) | 0x64006400u), __half2half2(__float2half(0.0625f)),
-                   __half2half2(__float2half(-64.f)));
-    c[3] = __hfma2(u32_as_h2((t & 0x00C000C0u) | 0x64006400u), __half2half2(__float2half(0.015625f)),
-                   __half2half2(__float2half(-16.f)));
+    const uint32_t a = R[0], as = R[0] >> 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo[i] = a & (0x00030003u << (2 * i));
+      hi[i] = as & (0x00030003u << (2 * i));
+    }
   }
 }
 
+// running (max, sum-exp) of a lane over values it produces four at a time; -inf marks "no value"
+__device__ __forceinline__ void softmax_push4(float& m, float& l, const float (&x)[4]) {
+  const float mn = fmaxf(fmaxf(m, fmaxf(x[0], x[1])), fmaxf(x[2], x[3]));
+  const float ref = (mn == -INFINITY ? 0.f : mn) * LOG2E;
+  l = l * fast_exp2(fmaf(m, LOG2E, -ref)) + (fast_exp2(fmaf(x[0], LOG2E, -ref)) + fast_exp2(fmaf(x[1], LOG2E, -ref))) +
+      (fast_exp2(fmaf(x[2], LOG2E, -ref)) + fast_exp2(fmaf(x[3], LOG2E, -ref)));
+  m = mn;
+}
+
+// One tile of a quantised tier, already requested: all heads of this kv head.
+// g0c = first scale group of the CTA's chunk.  m/l: this lane's running softmax pairs, [hh][e] for
+// head 4*hh + 2*(tig&1) + e.
+template <int BITS>
+__device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const TierDev& T, KShared& sh, KWarpShared& ws,
+                                               int tile_t0, int ntok, int g0c, int nh, float* row0, float (&m)[2][2],
+                                               float (&l)[2][2]) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int G = T.n_k >> P.gk_shift;
+  // staged scale / zero rows of this lane's channels 2*tig (even) and 2*tig+1 (odd) of step 0, at the
+  // half of the chunk's first group; a step adds 16 rows, the +8 channels add 8 rows
+  const int sh_even = static_cast<int>((static_cast<int64_t>(2 * tig) * G + g0c) & 7);
+  const int sh_odd = static_cast<int>((static_cast<int64_t>(2 * tig + 1) * G + g0c) & 7);
+  const int gt0 = (tile_t0 >> P.gk_shift) - g0c;  // first group of the tile within the chunk
+  // ldmatrix row address of this lane for step 0 / sub-span 0 (see the loop for the matrix order)
+  uint32_t lm_off;
+  {
+    const int mi = lane >> 3, rr = lane & 7;
+    if constexpr (BITS == 8) {
+      lm_off = TL::offset(rr, mi);                           // octet 0; pieces 0..3
+    } else if constexpr (BITS == 4) {
+      lm_off = TL::offset(8 * (mi >> 1) + rr, mi & 1);       // (octet 0, piece 0), (0,1), (1,0), (1,1)
+    } else {
+      lm_off = TL::offset(8 * mi + rr, 0);                   // steps kt, kt+1: octets 0..3 of 32 channels
+    }
+  }
+  const int hp = tig & 1;
+
+  for (int hh = 0; hh < nh; ++hh) {
+    k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0]);
+    const uint2* qb = &sh.qb[hh][0][lane];
+#pragma unroll
+    for (int j = 0; j < TL::NSUB; ++j) {
+      // as a B column this lane is n = g: columns 0-3 carry the scale group of tokens 0-31 of the
+      // sub-span, columns 4-7 that of tokens 32-63
+      const int gam = ((tile_t0 + j * K_SPAN + 32 * (g >> 2)) >> P.gk_shift) - g0c;
+      const __half* s_even = &sh.s[2 * tig][sh_even + gam];
+      const __half* s_odd = &sh.s[2 * tig + 1][sh_odd + gam];
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+      uint32_t R2[4];  // 2 bits: one ldmatrix feeds two steps
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        if (hh == 0 && j == 0 && (kt & 1) == 0) {  // the codes arrive two steps at a time
+          if (kt == 0) cp_async_wait<3>();
+          if (kt == 2) cp_async_wait<2>();
+          if (kt == 4) cp_async_wait<1>();
+          if (kt == 6) cp_async_wait<0>();
+          __syncwarp();
+        }
+        // A fragments: lo/hi of octet 0 -> registers 0/1 (channels 2tig, 2tig+1), of octet 1 -> 2/3 (+8)
+        uint32_t a[4][4];  // [register][M-tile]
+        const unsigned char* kb = ws.u.codes + kt * 16 * TL::PITCH;
+        if constexpr (BITS == 8) {
+          uint32_t R[4];
+          ldmatrix_x4_trans(R, kb + lm_off);
+          octet_frags<8>(R, a[0], a[1]);
+          ldmatrix_x4_trans(R, kb + lm_off + 8 * TL::PITCH);
+          octet_frags<8>(R, a[2], a[3]);
+        } else if constexpr (BITS == 4) {
+          uint32_t R[4];
+          ldmatrix_x4_trans(R, kb + (lm_off ^ (j * 32)));
+          octet_frags<4>(R, a[0], a[1]);
+          octet_frags<4>(R + 2, a[2], a[3]);
+        } else {
+          if ((kt & 1) == 0) ldmatrix_x4_trans(R2, kb + (lm_off ^ (j * 16)));
+          octet_frags<2>(R2 + 2 * (kt & 1), a[0], a[1]);
+          octet_frags<2>(R2 + 2 * (kt & 1) + 1, a[2], a[3]);
+        }
+        const int o = (16 * kt) * K_RAW_HALFS;
+        const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
+        const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]),
+                                               __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS])));
+        const uint2 qv = qb[kt * 32];
+        const __half2 hi0 = __hmul2(u32_as_h2(qv.x), s0);
+        const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
+        const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
+        const __half2 lo1 = __hfma2(u32_as_h2(qv.y), s1, __hneg2(hi1));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
+          mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
+        }
+      }
+      // Epilogue from registers: a lane keeps the accumulator columns whose scale group is its row's.
+      //  8 / 4 bits: rows 0-7 are tokens 0-31, rows 8-15 tokens 32-63: lanes tig 0,1 own row g, lanes
+      //              tig 2,3 own row g+8; heads 2*(tig&1), +1; four tokens each.
+      //  2 bits:     rows g and g+8 are the eight tokens of block g: lanes with (g < 4) == (tig < 2)
+      //              own both rows; the other lanes own nothing.
+      const int sub_t0 = j * K_SPAN;
+      if constexpr (BITS == 2) {
+        const int my_tok = sub_t0 + 8 * g;
+        const bool live = ((g < 4) == (tig < 2)) && my_tok < ntok;
+        const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
+        const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
+        const int4 p01 = ip[0], p23 = ip[1], p45 = ip[2], p67 = ip[3];  // low words of int64 positions: .x and .z
+        const uint32_t pos[8] = {static_cast<uint32_t>(p01.x), static_cast<uint32_t>(p01.z), static_cast<uint32_t>(p23.x),
+                                 static_cast<uint32_t>(p23.z), static_cast<uint32_t>(p45.x), static_cast<uint32_t>(p45.z),
+                                 static_cast<uint32_t>(p67.x), static_cast<uint32_t>(p67.z)};
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int head = 4 * hh + 2 * hp + e;
+          const bool on = live && head < P.rep;
+          const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
+          float* row = row0 + static_cast<int64_t>(head) * P.L;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            float x[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float unscale = static_cast<float>(1 << (24 - KField<2>::shift(i)));
+              x[i] = on ? fmaf(acc[i][2 * half + e], P.scale * unscale, zqs) : -INFINITY;
+              if (on) row[pos[4 * half + i]] = x[i];
+            }
+            softmax_push4(m[hh][e], l[hh][e], x);
+          }
+        }
+      } else {
+        const int r = tig >> 1;
+        // first of this lane's tokens (8 bits: tokens my_tok, +1, +16, +17; 4 bits: my_tok .. my_tok+3)
+        const int my_tok = sub_t0 + 32 * r + (BITS == 8 ? 2 * g : 4 * g);
+        const bool live = my_tok < ntok;
+        const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
+        uint32_t pos[4];
+        if constexpr (BITS == 8) {
+          const int4 pa = *reinterpret_cast<const int4*>(&ws.idx[my_tok]);
+          const int4 pb = *reinterpret_cast<const int4*>(&ws.idx[my_tok + 16]);
+          pos[0] = static_cast<uint32_t>(pa.x), pos[1] = static_cast<uint32_t>(pa.z);
+          pos[2] = static_cast<uint32_t>(pb.x), pos[3] = static_cast<uint32_t>(pb.z);
+        } else {
+          const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
+          const int4 p01 = ip[0], p23 = ip[1];
+          pos[0] = static_cast<uint32_t>(p01.x), pos[1] = static_cast<uint32_t>(p01.z);
+          pos[2] = static_cast<uint32_t>(p23.x), pos[3] = static_cast<uint32_t>(p23.z);
+        }
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          const int head = 4 * hh + 2 * hp + e;
+          const bool on = live && head < P.rep;
+          const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
+          float* row = row0 + static_cast<int64_t>(head) * P.L;
+          float x[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float v = r ? acc[i][2 + e] : acc[i][e];
+            const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
+            x[i] = on ? fmaf(v, P.scale * unscale, zqs) : -INFINITY;
+            if (on) row[pos[i]] = x[i];
+          }
+          softmax_push4(m[hh][e], l[hh][e], x);
+        }
+      }
+    }
+  }
+}
 // Write out a warp's logit tile [ntok][K_TROW] (already scaled) at the tokens' logical positions and
 // leave the warp's (max, sum-exp) per head in red_m / red_l.  Element = (token, head) with the head
 // fastest across lanes, so every lane owns ONE head for the whole call (rep divides 32): its running
 // max and sum are scalars, and index loads and stores are spread over all 32 lanes.
+// (fp16 tier and residual window only; the quantised tiers write from registers.)
 __device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float* tile, int ntok, const int64_t* idx,
                                              int64_t first_pos, int b, int kvh, float* red_m, float* red_l) {
   const int lane = threadIdx.x & 31;
@@ -378,8 +682,7 @@ __device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float*
   for (int off = rep; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
   float sum = 0.f;
 #pragma unroll 2
-  for (int t = lane >> rshift; t < ntok; t += tpr)
-    sum += fast_exp2((tile[t * K_TROW + h] - mx) * 1.4426950408889634f);
+  for (int t = lane >> rshift; t < ntok; t += tpr) sum += fast_exp2((tile[t * K_TROW + h] - mx) * LOG2E);
   for (int off = rep; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
   if (lane < rep) {
     red_m[lane] = mx;
@@ -387,171 +690,48 @@ __device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float*
   }
 }
 
-// `stage` (staging of scale/zero and Zq, with its block-wide barriers) runs after the first steps'
-// words have been requested, so that their latency overlaps it; every warp of the CTA calls this
-// function, warps whose span lies beyond the tier only skip the write-out.
-template <int BITS, typename Stage>
-__device__ __forceinline__ void k_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                       int chunk_t0, int span_t0, Stage stage) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
-  const int n = T.n_k;
-  const int nslot = n / K_SLOT;  // slots per channel row
-  const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
-  constexpr int SLOT_BYTES = K_SLOT * BITS / 8;
-  // warp-uniform base of this (batch, head); per-lane byte offsets of the 4 channel rows x 2 slots stay
-  // fixed over the 16-channel steps, which only advance the uniform base
-  const unsigned char* base = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes;
-  const int64_t kt_stride = 16 * row_bytes;
-  uint32_t off[4][2];
-  const __half* srow[2];  // staged scales of the two slots' groups, at this lane's first channel pair
-  int gl[2];
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    int sl = span_t0 / K_SLOT + r * 8 + g;
-    if (sl >= nslot) sl = nslot - 1;  // loads stay in range; such rows are never written out
-    gl[r] = max(((sl * K_SLOT) >> P.gk_shift) - (chunk_t0 >> P.gk_shift), 0);
-    srow[r] = &sh.s[gl[r]][2 * tig];
-#pragma unroll
-    for (int p = 0; p < 4; ++p)
-      off[p][r] = static_cast<uint32_t>((2 * tig + (p & 1) + (p >> 1) * 8) * row_bytes) + static_cast<uint32_t>(sl) * SLOT_BYTES;
-  }
-  float acc[K_SLOT][4];
-#pragma unroll
-  for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
 
-  // logical positions of the span's tokens go to shared memory now, to be there at write-out time
-#pragma unroll
-  for (int j = 0; j < K_SPAN / 32; ++j) {
-    const int t = lane + 32 * j;
-    if (span_t0 + t < n) cp_async_8(&sh.idx[warp][t], T.k_idx + span_t0 + t);
+// One tile per warp: request everything, agree that q and the scale rows are in shared memory, compute.
+template <int BITS>
+__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                        int chunk_t0, int nh) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  KWarpShared& ws = sh.w[warp];
+  const int chunk_end = min(chunk_t0 + KWARPS * TL::TOKENS, T.n_k);
+  const int g0c = chunk_t0 >> P.gk_shift;
+  const int ngc = ((chunk_end - 1) >> P.gk_shift) - g0c + 1;
+  k_scales_request(P, T, sh, bh, g0c, ngc);
+  cp_async_commit();  // oldest group: q (requested by the caller) and the scale / zero rows
+  const int tile_t0 = chunk_t0 + warp * TL::TOKENS;
+  const int ntok = min(TL::TOKENS, T.n_k - tile_t0);  // <= 0: this warp has no tile
+  if (ntok > 0) {
+    k_tile_request<BITS>(T, ws, bh, tile_t0, ntok);
+    cp_async_wait<4>();
+  } else {
+    cp_async_wait<0>();
   }
-  cp_async_commit();
-  constexpr int DEPTH = 3;  // steps in flight: the one being used and two ahead
-  uint32_t w[DEPTH][4][2];
-  auto load = [&](uint32_t (&dst)[4][2], int kt) {
-    const unsigned char* kb = base + kt * kt_stride;
-#pragma unroll
-    for (int p = 0; p < 4; ++p)
-#pragma unroll
-      for (int r = 0; r < 2; ++r) dst[p][r] = kslot_load<BITS>(kb + off[p][r], 0);
-  };
-#pragma unroll
-  for (int d = 0; d < DEPTH - 1; ++d) load(w[d], d);
-  stage();
-  constexpr int NSUB = KSub<BITS>::NSUB, NPER = KSub<BITS>::NPER;
-#pragma unroll
-  for (int kt = 0; kt < 8; ++kt) {
-    if (kt + DEPTH - 1 < 8) load(w[(kt + DEPTH - 1) % DEPTH], kt + DEPTH - 1);
-    const uint32_t (&cur)[4][2] = w[kt % DEPTH];
-    const uint2 bq = sh.qfrag[kt][lane];
-    // fragment register q*2 + r: channel pair q (2tig,2tig+1 | +8,+9), row slot r
-    __half2 s2[4];
-#pragma unroll
-    for (int q = 0; q < 2; ++q)
-#pragma unroll
-      for (int r = 0; r < 2; ++r) s2[q * 2 + r] = *reinterpret_cast<const __half2*>(srow[r] + kt * 16 + q * 8);
-#pragma unroll
-    for (int j = 0; j < NSUB; ++j) {
-      __half2 hi[4][NPER], lo[4][NPER];
-#pragma unroll
-      for (int q = 0; q < 2; ++q)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          __half2 c[NPER];
-          sub_codes<BITS>(cur[2 * q][r], cur[2 * q + 1][r], j, c);
-#pragma unroll
-          for (int k = 0; k < NPER; ++k) {
-            hi[q * 2 + r][k] = __hmul2(c[k], s2[q * 2 + r]);                              // fp16(code*scale)
-            lo[q * 2 + r][k] = __hfma2(c[k], s2[q * 2 + r], __hneg2(hi[q * 2 + r][k]));  // code*scale - hi, exact
-          }
-        }
-#pragma unroll
-      for (int k = 0; k < NPER; ++k) {
-        const int i = j * NPER + k;
-        mma16816(acc[i], h2_as_u32(hi[0][k]), h2_as_u32(hi[1][k]), h2_as_u32(hi[2][k]), h2_as_u32(hi[3][k]), bq.x, bq.y);
-        mma16816(acc[i], h2_as_u32(lo[0][k]), h2_as_u32(lo[1][k]), h2_as_u32(lo[2][k]), h2_as_u32(lo[3][k]), bq.x, bq.y);
-      }
-    }
+  __syncthreads();
+  float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  if (ntok > 0) {
+    float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * P.L;
+    k_tile_compute<BITS>(P, T, sh, ws, tile_t0, ntok, g0c, nh, row0, m, l);
   }
-  // accumulators -> the warp's [token][head] tile, then the lane-per-element write-out
-  float* tile = sh.tile[warp];
-#pragma unroll
-  for (int r = 0; r < 2; ++r)
+  // the warp's (max, sum-exp) per head: lanes that share tig & 1 hold pairs of the same two heads
+  for (int hh = 0; hh < nh; ++hh)
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
-      const int h = 2 * tig + e;
-      const float zq = sh.zq[gl[r]][h];
+      float mx = m[hh][e];
 #pragma unroll
-      for (int i = 0; i < K_SLOT; ++i)
-        tile[((r * 8 + g) * K_SLOT + i) * K_TROW + h] = (acc[i][r * 2 + e] + zq) * P.scale;
-    }
-  cp_async_wait_all();
-  __syncwarp();
-  k_write_tile(P, tile, min(K_SPAN, n - span_t0), sh.idx[warp], 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
-}
-
-template <int BITS, typename StoreQ>
-__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                        int chunk_t0, StoreQ store_q) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
-  const int chunk_end = min(chunk_t0 + K_CHUNK, T.n_k);
-  auto stage = [&]() {
-  store_q();
-  // stage scale/zero of the chunk as [group][channel]: lanes run along the groups of one channel row
-  // (contiguous in memory), all loads of a thread are issued before the first store
-  {
-    const int G = T.n_k >> P.gk_shift, g0 = chunk_t0 >> P.gk_shift;
-    const int ng = ((chunk_end - chunk_t0) + (1 << P.gk_shift) - 1) >> P.gk_shift;  // <= K_MAXG
-    const __half* s = T.k_scale + static_cast<int64_t>(bh) * D * G + g0;
-    const __half* z = T.k_zero + static_cast<int64_t>(bh) * D * G + g0;
-    constexpr int ITERS = D * K_MAXG / KTHREADS;
-    constexpr int CH_STEP = KTHREADS / K_MAXG;
-    __half sv[ITERS], zv[ITERS];
-    constexpr int GSHIFT = K_MAXG == 16 ? 4 : 3;
-    const int gi = tid & (K_MAXG - 1);
+      for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = l[hh][e] * fast_exp2((m[hh][e] - (mx == -INFINITY ? 0.f : mx)) * LOG2E);
 #pragma unroll
-    for (int j = 0; j < ITERS; ++j) {
-      const int ch = (tid >> GSHIFT) + j * CH_STEP;
-      sv[j] = zv[j] = __float2half(0.f);
-      if (gi < ng) {
-        sv[j] = s[static_cast<int64_t>(ch) * G + gi];
-        zv[j] = z[static_cast<int64_t>(ch) * G + gi];
+      for (int o = 2; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane < 2) {
+        sh.red_m[warp][4 * hh + 2 * lane + e] = mx;
+        sh.red_l[warp][4 * hh + 2 * lane + e] = sum;
       }
     }
-#pragma unroll
-    for (int j = 0; j < ITERS; ++j) {
-      const int ch = (tid >> GSHIFT) + j * CH_STEP;
-      sh.s[gi][ch] = sv[j];
-      sh.z[gi][ch] = zv[j];
-    }
-  }
-  __syncthreads();
-  // Zq[group][head]: rows of the A operand are the 16 groups, columns the channels
-  if (warp == 0) {
-    float zacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      const int ch = kt * 16 + 2 * tig;
-      const uint32_t a0 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch]);
-      const uint32_t a2 = *reinterpret_cast<const uint32_t*>(&sh.z[g][ch + 8]);
-      uint32_t a1 = 0u, a3 = 0u;  // rows 8..15 exist only with 16 groups per chunk
-      if constexpr (K_MAXG == 16) {
-        a1 = *reinterpret_cast<const uint32_t*>(&sh.z[(g + 8) & (K_MAXG - 1)][ch]);
-        a3 = *reinterpret_cast<const uint32_t*>(&sh.z[(g + 8) & (K_MAXG - 1)][ch + 8]);
-      }
-      const uint2 bq = sh.qfrag[kt][lane];
-      mma16816(zacc, a0, a1, a2, a3, bq.x, bq.y);
-    }
-    sh.zq[g][2 * tig] = zacc[0];
-    sh.zq[g][2 * tig + 1] = zacc[1];
-    if constexpr (K_MAXG == 16) {
-      sh.zq[(g + 8) & (K_MAXG - 1)][2 * tig] = zacc[2];
-      sh.zq[(g + 8) & (K_MAXG - 1)][2 * tig + 1] = zacc[3];
-    }
-  }
-  __syncthreads();
-  };
-  k_span<BITS>(P, T, sh, bh, b, kvh, chunk_t0, chunk_t0 + warp * K_SPAN, stage);
 }
 
 // fp16 tier, channel-major rows [D][n]: four tokens per 8-byte slot, no scales; B = q exactly.
@@ -571,12 +751,12 @@ __device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev&
   for (int kt = 0; kt < 8; ++kt) {
     uint2 w[4][2];
 #pragma unroll
-    for (int p = 0; p < 4; ++p) {
-      const int ch = kt * 16 + 2 * tig + (p & 1) + (p >> 1) * 8;
+    for (int e = 0; e < 4; ++e) {
+      const int ch = 16 * kt + 8 * (e >> 1) + 2 * tig + (e & 1);
 #pragma unroll
-      for (int r = 0; r < 2; ++r) w[p][r] = ld_stream(base + ch * nslot + sl[r]);
+      for (int r = 0; r < 2; ++r) w[e][r] = ld_stream(base + ch * nslot + sl[r]);
     }
-    const uint2 bq = sh.qfrag[kt][lane];
+    const uint2 bq = sh.qb[0][kt][lane];
     // token i of a slot: halfs (x.lo, x.hi, y.lo, y.hi); pair the same token of two channel rows
     uint32_t a[K_SLOT][4];
 #pragma unroll
@@ -592,7 +772,7 @@ __device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev&
 #pragma unroll
     for (int i = 0; i < K_SLOT; ++i) mma16816(acc[i], a[i][0], a[i][1], a[i][2], a[i][3], bq.x, bq.y);
   }
-  float* tile = sh.tile[warp];
+  float* tile = sh.w[warp].u.tile;
 #pragma unroll
   for (int r = 0; r < 2; ++r)
 #pragma unroll
@@ -612,19 +792,21 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
   const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
   const int t[2] = {min(tile_t0 + g, n - 1), min(tile_t0 + g + 8, n - 1)};
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t a[8][4];
 #pragma unroll
-  for (int kt = 0; kt < 8; ++kt) {
-    const int ch = kt * 16 + 2 * tig;
-    uint32_t a[4];
+  for (int kt = 0; kt < 8; ++kt)
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      a[r] = *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch);
-      a[2 + r] = *reinterpret_cast<const uint32_t*>(base + static_cast<int64_t>(t[r]) * D + ch + 8);
+      const __half* p = base + static_cast<int64_t>(t[r]) * D + 16 * kt + 2 * tig;
+      a[kt][r] = *reinterpret_cast<const uint32_t*>(p);
+      a[kt][2 + r] = *reinterpret_cast<const uint32_t*>(p + 8);
     }
-    const uint2 bq = sh.qfrag[kt][lane];
-    mma16816(acc, a[0], a[1], a[2], a[3], bq.x, bq.y);
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt) {
+    const uint2 bq = sh.qb[0][kt][lane];
+    mma16816(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq.x, bq.y);
   }
-  float* tile = sh.tile[warp];
+  float* tile = sh.w[warp].u.tile;
 #pragma unroll
   for (int r = 0; r < 2; ++r)
 #pragma unroll
@@ -635,7 +817,8 @@ __device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const Tie
 }
 
 __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
-  __shared__ KShared sh;
+  extern __shared__ __align__(128) unsigned char k_smem[];
+  KShared& sh = *reinterpret_cast<KShared*>(k_smem);
   const int chunk = blockIdx.y, bh = blockIdx.x;  // (batch, head) fastest: neighbouring CTAs run the same tier code
   const int b = bh / P.H, kvh = bh - b * P.H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
@@ -648,27 +831,6 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
     (&sh.red_m[0][0])[tid] = -INFINITY;
     (&sh.red_l[0][0])[tid] = 0.f;
   }
-  // B fragments of q: column n = g is query head kvh*rep + g; rows are channels
-  // (requested now, stored to shared memory by store_q() just before the first block-wide barrier, so
-  //  that warp 0 does not sit on this latency before it has requested its K words)
-  uint2 qf[8];
-  if (warp == 0) {
-    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + g) * D;
-#pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      qf[kt] = make_uint2(0u, 0u);
-      if (g < P.rep) {
-        qf[kt].x = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig);
-        qf[kt].y = *reinterpret_cast<const uint32_t*>(qh + kt * 16 + 2 * tig + 8);
-      }
-    }
-  }
-  auto store_q = [&]() {
-    if (warp == 0) {
-#pragma unroll
-      for (int kt = 0; kt < 8; ++kt) sh.qfrag[kt][lane] = qf[kt];
-    }
-  };
 
   int ti = HQKV_NUM_TIERS;
 #pragma unroll
@@ -676,9 +838,28 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
     if (chunk >= P.tier[t].k_chunk0 && chunk < P.tier[t + 1].k_chunk0) ti = t;
   const TierDev& T = P.tier[ti];
   const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
+  const bool plain = ti == HQKV_NUM_TIERS || T.bits == 16;
 
-  if (ti == HQKV_NUM_TIERS || T.bits == 16) {
-    store_q();
+  // B fragments of q: rows are channels 16*kt + 2*tig + (0,1 | 8,9), column n = g is a query head of
+  // this kv head (see KShared::qb).  Warp hh copies its half global -> shared in its oldest cp.async group.
+  const int nh = (!plain && P.rep > 4) ? 2 : 1;
+  if (warp < nh) {
+    const int head = plain ? g : 4 * warp + (g & 3);
+    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + head) * D + 2 * tig;
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt) {
+      if (head < P.rep) {
+        cp_async_4(&sh.qb[warp][kt][lane].x, qh + 16 * kt);
+        cp_async_4(&sh.qb[warp][kt][lane].y, qh + 16 * kt + 8);
+      } else {
+        sh.qb[warp][kt][lane] = make_uint2(0u, 0u);
+      }
+    }
+  }
+
+  if (plain) {
+    cp_async_commit();
+    cp_async_wait_all();
     __syncthreads();
     const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
     if (ti == HQKV_NUM_TIERS) {
@@ -689,11 +870,11 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
       if (t0 < chunk_end) k_f16_span(P, T, sh, bh, b, kvh, t0);
     }
   } else if (T.bits == 8) {
-    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, nh);
   } else if (T.bits == 4) {
-    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, nh);
   } else {
-    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, store_q);
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, nh);
   }
 
   // (max, sum) of this CTA per head from the warps' pairs
@@ -1148,7 +1329,8 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     if (s.n_k > 0) {
       HQKV_REQUIRE(s.k_data && s.k_idx, "decode: tier %d K pointers are null", t);
       if (s.bits < 16) {
-        HQKV_REQUIRE(s.k_scale && s.k_zero, "decode: tier %d K scale/zero pointers are null", t);
+        HQKV_REQUIRE(s.k_scale && s.k_zero && aligned(s.k_scale, 16) && aligned(s.k_zero, 16),
+                     "decode: tier %d K scale/zero pointers are null or not 16-byte aligned", t);
         HQKV_REQUIRE(s.n_k % c->group_k == 0, "decode: tier %d K holds %d tokens, not a multiple of the K group %d", t,
                      s.n_k, c->group_k);
         HQKV_REQUIRE(aligned(s.k_data, 16), "decode: tier %d K codes must be 16-byte aligned", t);
@@ -1174,7 +1356,8 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.v_idx = s.v_idx;
     // chunk sizes: about the same number of bytes per CTA whatever the width
     const int b = d.bits;
-    d.k_chunk_tokens = K_CHUNK;
+    d.k_chunk_tokens = KWARPS * (b == 8 || b == 16 ? 64 : 128);  // one tile per warp
+    HQKV_REQUIRE(static_cast<int64_t>(s.n_k) * D * b / 8 < (1ll << 31), "decode: tier %d K plane of one head exceeds 2 GiB", t);
     d.v_chunk_tokens = v_chunk;
     d.k_chunk0 = kc;
     d.v_chunk0 = vc;
@@ -1264,11 +1447,13 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
       HQKV_CUDA(cudaFuncSetAttribute(v_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      static_cast<int>(sizeof(VShared))));
+      HQKV_CUDA(cudaFuncSetAttribute(k_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(sizeof(KShared))));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
   }
   if (phases & 1) {
-    k_pass_kernel<<<dim3(BH, P.nk_chunks), dim3(KTHREADS), 0, st>>>(P);
+    k_pass_kernel<<<dim3(BH, P.nk_chunks), dim3(KTHREADS), sizeof(KShared), st>>>(P);
     HQKV_LAUNCH_CHECK("k_pass");
   }
   if (phases & 2) {
