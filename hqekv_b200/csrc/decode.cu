@@ -889,174 +889,414 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 // ------------------------------------------------------------------------------------------------
 // v_pass
 // ------------------------------------------------------------------------------------------------
+// V tier, token-major rows of 128 channels.  Every warp of a CTA owns one TILE of consecutive tokens
+// (8 KB of codes at 8 / 4 bits = 64 / 128 tokens, 4 KB at 2 bits = 128 tokens) with their scales,
+// zeros and logical positions, all copied global -> shared with cp.async before anything else.
+// The contraction runs over tokens, 16 per step.  ldmatrix.trans over 8 token rows x 16 bytes hands
+// lane (g, tig) the 16-bit block g (2 / 4 / 8 channels) of tokens 2*tig and 2*tig+1 in one register:
+// the two K-neighbours of an m16n8k16 A fragment.  As in the K pass the codes enter the tensor pipe
+// as fp16 subnormals (one AND per pair of codes) and the scale - here per token and 32-channel
+// group - is folded into the B operand: out[h][c] = sum_t (p_t * scale_t,G) * code_t,c + sum_t p_t *
+// zero_t,G, with p*scale carried exactly as hi + lo and B columns 0-3 / 4-7 holding the two channel
+// groups of a 64-channel half.  The zero term is one small MMA per step (rows = groups).
 #ifndef V_MIN_CTAS
-#define V_MIN_CTAS 2
+#define V_MIN_CTAS 4
 #endif
-constexpr int VWARPS = 8;
+constexpr int VWARPS = 4;
 constexpr int VTHREADS = VWARPS * 32;
-constexpr int V_MAX_CHUNK = 1024;                       // tokens per CTA at most (multiple of VWARPS*16)
-constexpr int V_STAGE_ITERS = V_MAX_CHUNK / VTHREADS;   // 4
-constexpr int V_EROW = V_MAX_CHUNK + 8;                 // halfs per staged row
+constexpr int V_MAX_TT = 128;                 // tokens per tile at most
+constexpr int V_PROW = V_MAX_TT + 8;          // halfs per staged probability row (pitch 68 words: rows 4 banks apart)
+
+template <int BITS>
+struct VTile {
+  static constexpr int PITCH = 16 * BITS;                  // bytes per token row: 128, 64, 32
+  static constexpr int TOKENS = BITS == 8 ? 64 : 128;
+  static constexpr int STEPS = TOKENS / 16;
+  static constexpr int NPIECE = PITCH / 16;                // 16-byte pieces per row: 8, 4, 2
+  static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
+    if constexpr (PITCH == 128) {
+      return row * 128u + ((c ^ (row & 7u)) << 4);
+    } else if constexpr (PITCH == 64) {
+      return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
+    } else {
+      return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    }
+  }
+};
+
+struct VWarpShared {
+  union {
+    unsigned char codes[8192];
+    float red[4][D];            // partial output of the last walk over the tile (heads of that half)
+  } u;
+  union {
+    struct {
+      int64_t pos[V_MAX_TT];    // logical positions of the tile's tokens
+      __half p[4][V_PROW];      // exp(logit - max) of heads 0-3
+    } a;
+    float red0[4][D];           // eight query heads per kv head: partial output of the first walk
+  } v;
+  __half p_hi[4][V_PROW];       // heads 4-7
+  __half s[V_MAX_TT * 4];       // scales as in memory: [token][group]
+  __half z[V_MAX_TT * 4];
+  float zt[4][MAX_REP];         // sum_t p*zero per channel group and head
+};
+static_assert(sizeof(float) * 4 * D <= sizeof(int64_t) * V_MAX_TT + sizeof(__half) * 4 * V_PROW, "red0 fits its union");
 
 struct VShared {
-  __half e[MAX_REP][V_EROW];               // exp(logit - max) per head and token of the chunk
-  __half s[4][V_EROW];                     // scale[channel group][token]
-  __half z[4][V_EROW];
-  float red[VWARPS][MAX_REP][D];           // per-warp partial outputs
   float gm[MAX_REP], gl[MAX_REP];          // global max / sum of this kv head's query heads
   float wm[VWARPS][MAX_REP], wl[VWARPS][MAX_REP];
   unsigned is_last;
+  unsigned pad_[3 + 12];
+  VWarpShared w[VWARPS];
 };
 
-// V tier, token-major rows.  Contraction runs over tokens (16 per step): fragment columns
-// 2tig,2tig+1,2tig+8,2tig+9 <-> tokens t0+..., fragment row g <-> channel slot g, row g+8 <-> slot
-// g+8 (2-bit: low/high half of word g), M-tile i <-> i-th value of every slot.  The values are
-// dequantised to fp16 (code*scale + zero, one rounding) because here the scale varies along the
-// contraction axis; B = exp(logit - max) in fp16.
+// A fragment registers from one ldmatrix quad R[0..3] = sources of fragment registers a0..a3
+// (a0: row g, tokens 2tig,2tig+1; a1: row g+8; a2 / a3: the same rows, tokens +8).
+//   field f of a 16-bit block as the fp16 subnormal code * 2^(k-24); VField<BITS>::shift(f) gives k.
 template <int BITS>
-struct VFmt {
-  using word_t = typename Fmt<BITS>::word_t;
-  static constexpr bool HALF_SPLIT = (BITS == 2);        // one word per token row covers both row slots
-  static constexpr int WORDS_PER_TOKEN = BITS == 2 ? 8 : 16;  // in units of word_t
-  static constexpr int NW = HALF_SPLIT ? 1 : 2;          // words a lane loads per token
+struct VField {
+  static constexpr int N = BITS == 8 ? 2 : 4;  // fields taken from one register per fragment row
+  static __host__ __device__ constexpr int shift(int f) { return BITS == 8 ? 0 : BITS == 4 ? 4 * (f & 1) : 2 * f; }
 };
-
 template <int BITS>
-__device__ __forceinline__ void v_load(typename VFmt<BITS>::word_t (&dst)[4][VFmt<BITS>::NW],
-                                       const typename VFmt<BITS>::word_t* base, int chunk_t0, int chunk_n, int kt0,
-                                       int g, int tig) {
-#pragma unroll
-  for (int p = 0; p < 4; ++p) {
-    const int tl = kt0 + 2 * tig + (p & 1) + (p >> 1) * 8;
-    const int64_t tok = chunk_t0 + min(tl, chunk_n - 1);
-#pragma unroll
-    for (int s = 0; s < VFmt<BITS>::NW; ++s) dst[p][s] = ld_stream(base + tok * VFmt<BITS>::WORDS_PER_TOKEN + s * 8 + g);
+__device__ __forceinline__ uint32_t v_field(uint32_t r, uint32_t r_shr8, int f) {
+  if constexpr (BITS == 8) {
+    return f == 0 ? (r & 0x00FF00FFu) : __byte_perm(r, 0u, 0x4341);
+  } else if constexpr (BITS == 4) {
+    return (f < 2 ? r : r_shr8) & (0x000F000Fu << (4 * (f & 1)));
+  } else {
+    return r & (0x00030003u << (2 * f));  // 2 bits: fields 0-3 of r (row g) or of r >> 8 (row g+8)
   }
 }
 
+// Request a tile: positions, scales, zeros in the oldest commit group, then the codes in four groups
+// of a quarter of the steps each.  ntok = valid tokens (a multiple of 32), ng = channel groups.
 template <int BITS>
-__device__ __forceinline__ void v_step(float (&acc)[8][4], const typename VFmt<BITS>::word_t (&cur)[4][VFmt<BITS>::NW],
-                                       const VShared& sh, const int (&cg)[2], int kt0, int g, int tig, int rep) {
-  using word_t = typename VFmt<BITS>::word_t;
-  const int tl0 = kt0 + 2 * tig, tl2 = tl0 + 8;
-  word_t w[4][2];
+__device__ __forceinline__ void v_tile_request(const TierDev& T, VWarpShared& ws, int bh, int tile_t0, int ntok, int ng) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31;
+  const int64_t tok0 = static_cast<int64_t>(bh) * T.n_v + tile_t0;
+#pragma unroll
+  for (int j = 0; j < TL::TOKENS / 32; ++j) {
+    const int t = lane + 32 * j;
+    if (t < ntok) cp_async_8(&ws.v.a.pos[t], T.v_idx + tile_t0 + t);
+  }
+  // scale / zero rows are ng halfs per token, contiguous over the tile: 8-byte pieces
+  {
+    const int bytes = ntok * ng * 2;
+    const unsigned char* s = reinterpret_cast<const unsigned char*>(T.v_scale + tok0 * ng);
+    const unsigned char* z = reinterpret_cast<const unsigned char*>(T.v_zero + tok0 * ng);
+#pragma unroll
+    for (int j = 0; j < V_MAX_TT * 4 * 2 / (32 * 8); ++j) {
+      const int o = (lane + 32 * j) * 8;
+      if (o < bytes) {
+        cp_async_8(reinterpret_cast<unsigned char*>(ws.s) + o, s + o);
+        cp_async_8(reinterpret_cast<unsigned char*>(ws.z) + o, z + o);
+      }
+    }
+  }
+  cp_async_commit();
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.v_data) + tok0 * TL::PITCH;
+  constexpr int PIECES = TL::TOKENS * TL::NPIECE;  // 512 (256 at 2 bits)
+  constexpr int PER_Q = PIECES / 4 / 32;           // copies per lane and quarter: 4 (2)
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int i = 0; i < PER_Q; ++i) {
+      const int id = (quarter * PER_Q + i) * 32 + lane;
+      const int row = id / TL::NPIECE, c = id % TL::NPIECE;
+      if (row < ntok) cp_async_16(ws.u.codes + TL::offset(row, c), src + static_cast<int64_t>(id) * 16);
+    }
+    cp_async_commit();
+  }
+}
+
+// exp(logit - max) of the tile's tokens for heads h0..h0+3 into prow[0..3][token], and the
+// normalised probabilities into the output row; the gathers of four heads are in flight together.
+template <int TOKENS>
+__device__ __forceinline__ void v_tile_probs(const DecodeParams& P, const VShared& sh, const int64_t* pos_s, __half (*prow)[V_PROW],
+                                             int b, int kvh, int h0, int ntok, int64_t first_pos) {
+  const int lane = threadIdx.x & 31;
+  const int rep = P.rep;
+  constexpr int PER = TOKENS / 32;
+  uint32_t pos[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int t = lane + 32 * j;
+    pos[j] = t < ntok ? (pos_s ? static_cast<uint32_t>(pos_s[t]) : static_cast<uint32_t>(first_pos + t)) : 0u;
+  }
+  float x[4][PER];
+#pragma unroll
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = min(h0 + hh, rep - 1);
+    const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) x[hh][j] = lane + 32 * j < ntok ? __ldcg(row + pos[j]) : -INFINITY;
+  }
+#pragma unroll
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = h0 + hh;
+    const bool on = h < rep;
+    const float mh = on ? sh.gm[h] * LOG2E : 0.f, inv = on ? 1.f / sh.gl[h] : 0.f;
+    __half* wrow = P.weights + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + min(h, rep - 1)) * P.L;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int t = lane + 32 * j;
+      const float e = on ? fast_exp2(fmaf(x[hh][j], LOG2E, -mh)) : 0.f;  // exp2(-inf) = 0 beyond the tile
+      prow[hh][t] = __float2half_rn(e);
+      if (on && t < ntok) wrow[pos[j]] = __float2half_rn(e * inv);
+    }
+  }
+}
+
+// One tile of a quantised V tier for half hh of the heads: acc[mt] = M-tile mt of the output
+// (channels x heads, see the channel map in v_tile_store), zacc = zero term rows.
+template <int BITS>
+__device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& ws, const __half (*prow)[V_PROW], int ntok,
+                                            float (&acc)[8][4], float (&zacc)[4]) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int ng_shift = 7 - P.gv_shift;  // log2(groups per token): 2, 1, 0
+  // ldmatrix row address of this lane for step 0, quad 0: matrices (token octet, piece) =
+  //   8/4 bits: (0, c), (0, c'), (1, c), (1, c');  2 bits: (0, 0), (0, 1), (1, 0), (1, 1)
+  // with (c, c') = the quad's two pieces: 4 bits (2pp, 2pp+1); 8 bits (4q+u, 4q+2+u)
+  const int mi = lane >> 3, rr = lane & 7;
+  const int lm_row = 8 * (mi >> 1) + rr;
+  // as a B column this lane is n = g: head (n & 3) of this half, channel group of channels
+  // 64q + 32*(n >> 2) for quad set q
+  const __half* pr = &prow[g & 3][2 * tig];
+  int gq[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) gq[q] = (64 * q + 32 * (g >> 2)) >> P.gv_shift;
+  const int zg = (g & 3) & ((1 << ng_shift) - 1);  // zero-term row g = group g (rows beyond ng repeat)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  zacc[0] = zacc[1] = zacc[2] = zacc[3] = 0.f;
+
+  const int nsteps = ntok >> 4;
+#pragma unroll 1
+  for (int st = 0; st < nsteps; ++st) {
+    const int t0 = st * 16;
+    // B operands: p pairs of tokens (2tig, 2tig+1) and (+8, +9); scales of the same tokens
+    const uint32_t p0 = *reinterpret_cast<const uint32_t*>(pr + t0);
+    const uint32_t p1 = *reinterpret_cast<const uint32_t*>(pr + t0 + 8);
+    const __half* sb = ws.s + ((t0 + 2 * tig) << ng_shift);
+    const __half* zb = ws.z + ((t0 + 2 * tig) << ng_shift);
+    uint32_t bh_[2][2], bl_[2][2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(sb[gq[q]]), __half_as_ushort(sb[(1 << ng_shift) + gq[q]])));
+      const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(sb[(8 << ng_shift) + gq[q]]),
+                                             __half_as_ushort(sb[(9 << ng_shift) + gq[q]])));
+      const __half2 h0 = __hmul2(u32_as_h2(p0), s0), h1 = __hmul2(u32_as_h2(p1), s1);
+      bh_[q][0] = h2_as_u32(h0);
+      bh_[q][1] = h2_as_u32(h1);
+      bl_[q][0] = h2_as_u32(__hfma2(u32_as_h2(p0), s0, __hneg2(h0)));  // exact remainder
+      bl_[q][1] = h2_as_u32(__hfma2(u32_as_h2(p1), s1, __hneg2(h1)));
+    }
+    {  // zero term: A rows = channel groups, exact fp16 x fp16 products
+      const uint32_t a0 = pack_lo16(__half_as_ushort(zb[zg]), __half_as_ushort(zb[(1 << ng_shift) + zg]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(zb[(8 << ng_shift) + zg]), __half_as_ushort(zb[(9 << ng_shift) + zg]));
+      mma16816(zacc, a0, 0u, a2, 0u, p0, p1);
+    }
+    const unsigned char* rowp = ws.u.codes;
+    if constexpr (BITS == 2) {
+      uint32_t R[4];
+      ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, mi & 1));
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t lo0 = R[c], hi0 = R[c] >> 8, lo1 = R[2 + c], hi1 = R[2 + c] >> 8;
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint32_t a0 = v_field<2>(lo0, 0u, f), a1 = v_field<2>(hi0, 0u, f);
+          const uint32_t a2 = v_field<2>(lo1, 0u, f), a3 = v_field<2>(hi1, 0u, f);
+          mma16816(acc[4 * c + f], a0, a1, a2, a3, bh_[c][0], bh_[c][1]);
+          mma16816(acc[4 * c + f], a0, a1, a2, a3, bl_[c][0], bl_[c][1]);
+        }
+      }
+    } else if constexpr (BITS == 4) {
+#pragma unroll
+      for (int pp = 0; pp < 2; ++pp) {
+        uint32_t R[4], S[4];
+        ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 2 * pp + (mi & 1)));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) S[k] = R[k] >> 8;
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          mma16816(acc[4 * pp + f], v_field<4>(R[0], S[0], f), v_field<4>(R[1], S[1], f), v_field<4>(R[2], S[2], f),
+                   v_field<4>(R[3], S[3], f), bh_[pp][0], bh_[pp][1]);
+          mma16816(acc[4 * pp + f], v_field<4>(R[0], S[0], f), v_field<4>(R[1], S[1], f), v_field<4>(R[2], S[2], f),
+                   v_field<4>(R[3], S[3], f), bl_[pp][0], bl_[pp][1]);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          uint32_t R[4];
+          ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 4 * q + u + 2 * (mi & 1)));
+#pragma unroll
+          for (int f = 0; f < 2; ++f) {
+            const uint32_t a0 = v_field<8>(R[0], 0u, f), a1 = v_field<8>(R[1], 0u, f);
+            const uint32_t a2 = v_field<8>(R[2], 0u, f), a3 = v_field<8>(R[3], 0u, f);
+            mma16816(acc[4 * q + 2 * u + f], a0, a1, a2, a3, bh_[q][0], bh_[q][1]);
+            mma16816(acc[4 * q + 2 * u + f], a0, a1, a2, a3, bl_[q][0], bl_[q][1]);
+          }
+        }
+    }
+  }
+}
+
+// Accumulators of one walk -> red[head of this half][channel] (every element has exactly one owner).
+//   8 / 4 bits: rows 0-7 and 8-15 of an M-tile are two different channel groups: lanes tig 0,1 own row g
+//               (columns 0-3), lanes tig 2,3 own row g+8 (columns 4-7).
+//   2 bits:     rows g and g+8 are channels of the same block: lanes with (g < 4) == (tig < 2) own both.
+// M-tile -> channels:  8 bits  mt = 4q + 2u + f : row g = 64q + 16u + 2g + f,  row g+8 = +32
+//                      4 bits  mt = 4pp + f     : row g = 64pp + 4g + f,        row g+8 = +32
+//                      2 bits  mt = 4c + f      : row g = 64c + 8g + f,         row g+8 = +4
+template <int BITS>
+__device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)[8][4]) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int hp = tig & 1, r = tig >> 1;
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int f = BITS == 8 ? (mt & 1) : (mt & 3);
+    const float unscale = static_cast<float>(1 << (24 - VField<BITS>::shift(f)));
+    if constexpr (BITS == 2) {
+      if ((g < 4) == (tig < 2)) {
+        const int ch = 64 * (mt >> 2) + 8 * g + f;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          red[2 * hp + e][ch] = acc[mt][e] * unscale;
+          red[2 * hp + e][ch + 4] = acc[mt][2 + e] * unscale;
+        }
+      }
+    } else {
+      const int ch = BITS == 8 ? 64 * (mt >> 2) + 16 * ((mt >> 1) & 1) + 2 * g + f + 32 * r
+                               : 64 * (mt >> 2) + 4 * g + f + 32 * r;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) red[2 * hp + e][ch] = (r ? acc[mt][2 + e] : acc[mt][e]) * unscale;
+    }
+  }
+}
+
+// Everything a warp does for its tile of a quantised V tier.
+template <int BITS>
+__device__ __forceinline__ void v_tile(const DecodeParams& P, const TierDev& T, VShared& sh, VWarpShared& ws, int b,
+                                       int kvh, int ntok, int nh) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  cp_async_wait<4>();  // positions, scales, zeros
+  __syncwarp();
+  for (int hh = 0; hh < nh; ++hh)
+    v_tile_probs<TL::TOKENS>(P, sh, ws.v.a.pos, hh ? ws.p_hi : ws.v.a.p, b, kvh, 4 * hh, ntok, 0);
+  cp_async_wait<0>();  // the gathers above took at least as long as the codes
+  __syncwarp();
+  for (int hh = 0; hh < nh; ++hh) {
+    float acc[8][4], zacc[4];
+    v_tile_walk<BITS>(P, ws, hh ? ws.p_hi : ws.v.a.p, ntok, acc, zacc);
+    __syncwarp();  // all lanes are done with the codes (last walk) or with p of heads 0-3 (first of two)
+    v_tile_store<BITS>(hh + 1 < nh ? ws.v.red0 : ws.u.red, acc);
+    if (g < 4 && tig < 2) {
+      ws.zt[g][4 * hh + 2 * tig] = zacc[0];
+      ws.zt[g][4 * hh + 2 * tig + 1] = zacc[1];
+    }
+  }
+}
+
+// fp16 tier and residual window, token-major rows [n][D] halfs: one 16-token step per warp straight
+// from global memory; B = p.  Writes the partial outputs of all (up to eight) heads.
+__device__ __forceinline__ void v_plain_tile(const DecodeParams& P, const TierDev& T, VShared& sh, VWarpShared& ws, int bh,
+                                             int b, int kvh, int t0, int ntok, bool is_res) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int rep = P.rep;
+  const uint4* base = reinterpret_cast<const uint4*>(T.v_data) + static_cast<int64_t>(bh) * T.n_v * 16;
+  uint4 w[4][2];
 #pragma unroll
   for (int p = 0; p < 4; ++p) {
-    if constexpr (VFmt<BITS>::HALF_SPLIT) {
-      w[p][0] = cur[p][0];
-      w[p][1] = cur[p][0] >> 16;  // values 8..15 of the word move to bytes 0,1
-    } else {
-      w[p][0] = cur[p][0];
-      w[p][1] = cur[p][1];
-    }
-  }
-  __half2 sz[2][2], zz[2][2];
-  if constexpr (BITS != 16) {
+    const int tl = 2 * tig + (p & 1) + (p >> 1) * 8;
+    const int64_t tok = t0 + min(tl, ntok - 1);
 #pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      sz[0][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl0]);
-      zz[0][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl0]);
-      sz[1][s] = *reinterpret_cast<const __half2*>(&sh.s[cg[s]][tl2]);
-      zz[1][s] = *reinterpret_cast<const __half2*>(&sh.z[cg[s]][tl2]);
-    }
+    for (int s = 0; s < 2; ++s) w[p][s] = ld_stream(base + tok * 16 + s * 8 + g);
   }
+  const int64_t first_pos = static_cast<int64_t>(P.L) - T.n_v + t0;
+  for (int hh = 0; hh < (rep > 4 ? 2 : 1); ++hh)
+    v_tile_probs<32>(P, sh, is_res ? nullptr : T.v_idx + t0, hh ? ws.p_hi : ws.v.a.p, b, kvh, 4 * hh, ntok, first_pos);
+  __syncwarp();
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   uint32_t b0 = 0u, b1 = 0u;
   if (g < rep) {
-    b0 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl0]);
-    b1 = *reinterpret_cast<const uint32_t*>(&sh.e[g][tl2]);
+    const __half* pr = g < 4 ? ws.v.a.p[g] : ws.p_hi[g - 4];
+    b0 = *reinterpret_cast<const uint32_t*>(pr + 2 * tig);
+    b1 = *reinterpret_cast<const uint32_t*>(pr + 2 * tig + 8);
   }
-  if constexpr (VFmt<BITS>::HALF_SPLIT) {
-    mma_sub<2, 0, 8>(acc, w, sz, zz, b0, b1);
-    mma_sub<2, 1, 8>(acc, w, sz, zz, b0, b1);
-  } else {
-    mma_words<BITS, 8>(acc, w, sz, zz, b0, b1);
-  }
+  const __half2 none[2][2] = {};
+  mma_words<16, 8>(acc, w, none, none, b0, b1);
+  __syncwarp();
+  // M-tile mt, slot s: channel 8*(8s + g) + mt; columns 2tig, 2tig+1 = heads
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int ch = 8 * (s * 8 + g) + mt;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int h = 2 * tig + e;  // heads 0-3 are the first of two halves when there are eight
+        if (rep > 4) {
+          (h < 4 ? ws.v.red0 : ws.u.red)[h & 3][ch] = acc[mt][s * 2 + e];
+        } else if (h < 4) {
+          ws.u.red[h][ch] = acc[mt][s * 2 + e];
+        }
+      }
+    }
 }
 
-// Everything a CTA does for its chunk of one V tier (or of the residual window, BITS = 16).
-template <int BITS>
-__device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, VShared& sh, int bh, int b, int kvh,
-                                       int chunk, int chunk_t0, int chunk_n, bool is_res, bool quantised) {
-  using word_t = typename VFmt<BITS>::word_t;
-  constexpr int NW = VFmt<BITS>::NW;
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+__global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
+  const int chunk = blockIdx.y, bh = blockIdx.x;
+  const int b = bh / P.H, kvh = bh - b * P.H;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int rep = P.rep;
-  const int chunk_pad = (chunk_n + 15) & ~15;
-  const int step = VWARPS * 16;
+  const int nh = rep > 4 ? 2 : 1;
 
-  // ---- the first two steps' words of this warp are requested before anything else: their addresses
-  //      depend on nothing, and the prologue below takes about as long as they need to arrive
-  const word_t* base = reinterpret_cast<const word_t*>(T.v_data) +
-                       static_cast<int64_t>(bh) * T.n_v * VFmt<BITS>::WORDS_PER_TOKEN;
-  word_t w0[4][NW], w1[4][NW], w2[4][NW];
-  int kt0 = warp * 16;
-  if (kt0 < chunk_n) v_load<BITS>(w0, base, chunk_t0, chunk_n, kt0, g, tig);
-  if (kt0 + step < chunk_n) v_load<BITS>(w1, base, chunk_t0, chunk_n, kt0 + step, g, tig);
-
-  // ---- logical positions of this chunk's tokens
-  int64_t pos[V_STAGE_ITERS];
+  int ti = HQKV_NUM_TIERS;
 #pragma unroll
-  for (int j = 0; j < V_STAGE_ITERS; ++j) {
-    const int i = tid + j * VTHREADS;
-    pos[j] = 0;
-    if (i < chunk_n) pos[j] = is_res ? (P.L - T.n_v + chunk_t0 + i) : T.v_idx[chunk_t0 + i];
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const bool is_res = ti == HQKV_NUM_TIERS;
+  const int vb = is_res ? 16 : T.bits;
+  const int tile_tokens = T.v_chunk_tokens / VWARPS;
+  const int tile_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens + warp * tile_tokens;
+  const int ntok = min(tile_tokens, T.n_v - tile_t0);  // <= 0: this warp has no tile
+  VWarpShared& ws = sh.w[warp];
+  const int ng = D >> P.gv_shift;
+
+  // ---- requests that read only the cache go out before the K pass is known to be complete
+  if (ntok > 0) {
+    if (vb == 8) v_tile_request<8>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 4) v_tile_request<4>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 2) v_tile_request<2>(T, ws, bh, tile_t0, ntok, ng);
   }
-  // ---- scale / zero tile: one token row per thread and iteration, transposed into [group][token]
-  if (quantised) {
-    const int ng = D >> P.gv_shift;  // 4, 2 or 1 halfs per token
-    const __half* s = T.v_scale + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
-    const __half* z = T.v_zero + (static_cast<int64_t>(bh) * T.n_v + chunk_t0) * ng;
-    uint2 sv[V_STAGE_ITERS], zv[V_STAGE_ITERS];
-#pragma unroll
-    for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int t = tid + j * VTHREADS;
-      sv[j] = zv[j] = make_uint2(0u, 0u);
-      if (t < chunk_n) {
-        if (ng == 4) {
-          sv[j] = *reinterpret_cast<const uint2*>(s + t * 4);
-          zv[j] = *reinterpret_cast<const uint2*>(z + t * 4);
-        } else if (ng == 2) {
-          sv[j].x = *reinterpret_cast<const uint32_t*>(s + t * 2);
-          zv[j].x = *reinterpret_cast<const uint32_t*>(z + t * 2);
-        } else {
-          sv[j].x = __half_as_ushort(s[t]);
-          zv[j].x = __half_as_ushort(z[t]);
-        }
-      }
-    }
-#pragma unroll
-    for (int j = 0; j < V_STAGE_ITERS; ++j) {
-      const int t = tid + j * VTHREADS;
-      if (t < chunk_pad) {
-        sh.s[0][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].x & 0xFFFFu));
-        sh.z[0][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].x & 0xFFFFu));
-        if (ng >= 2) {
-          sh.s[1][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].x >> 16));
-          sh.z[1][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].x >> 16));
-        }
-        if (ng == 4) {
-          sh.s[2][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].y & 0xFFFFu));
-          sh.z[2][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].y & 0xFFFFu));
-          sh.s[3][t] = __ushort_as_half(static_cast<unsigned short>(sv[j].y >> 16));
-          sh.z[3][t] = __ushort_as_half(static_cast<unsigned short>(zv[j].y >> 16));
-        }
-      }
-    }
-  }
-
-  // ---- everything above reads only the cache; from here on the K pass results are needed
   asm volatile("griddepcontrol.wait;" ::: "memory");
+
   // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks),
   //      up to four pairs per thread in flight, then slices are folded by shuffles and across warps
   {
-    const int h = tid & (MAX_REP - 1), slice = tid >> 3;  // 32 slices
+    constexpr int SLICES = VTHREADS / MAX_REP;
+    const int h = tid & (MAX_REP - 1), slice = tid >> 3;
     const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
     float m = -INFINITY, l = 0.f;
-    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * (VTHREADS / MAX_REP)) {
+    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * SLICES) {
       float2 v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int c = c0 + (VTHREADS / MAX_REP) * j;
+        const int c = c0 + SLICES * j;
         v[j] = c < P.nk_chunks ? __ldcg(part + c * MAX_REP + h) : make_float2(-INFINITY, 0.f);
       }
 #pragma unroll
@@ -1082,123 +1322,38 @@ __device__ __forceinline__ void v_body(const DecodeParams& P, const TierDev& T, 
     __syncthreads();
   }
 
-  // ---- this CTA's slice of the probability row (needs only the global max / sum)
+  // ---- the warp's tile: probabilities of its tokens, then sum_t p_t * V_t
+  if (ntok > 0 && vb != 16) {
+    if (vb == 8) v_tile<8>(P, T, sh, ws, b, kvh, ntok, nh);
+    else if (vb == 4) v_tile<4>(P, T, sh, ws, b, kvh, ntok, nh);
+    else v_tile<2>(P, T, sh, ws, b, kvh, ntok, nh);
+  } else {
+    if (ntok > 0) {
+      v_plain_tile(P, T, sh, ws, bh, b, kvh, tile_t0, ntok, is_res);
+    } else {
+      for (int i = lane; i < 4 * D; i += 32) {
+        (&ws.u.red[0][0])[i] = 0.f;
+        if (nh == 2) (&ws.v.red0[0][0])[i] = 0.f;
+      }
+    }
+    (&ws.zt[0][0])[lane] = 0.f;  // 4 x MAX_REP floats
+  }
+  __syncthreads();
+  // ---- partial output of this chunk: warps added in index order
   {
-    const int p0 = chunk * P.w_slice, p1 = min(p0 + P.w_slice, P.L);
-    for (int h = 0; h < rep; ++h) {
-      const int64_t row = (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
-      const float mh = sh.gm[h], inv = 1.f / sh.gl[h];
-      for (int pb = p0 + tid; pb < p1; pb += 4 * VTHREADS) {
-        float x[4];
+    float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
+    for (int i = tid; i < rep * D; i += VTHREADS) {
+      const int h = i >> 7, ch = i & (D - 1);
+      const bool first_of_two = (h >> 2) + 1 < nh;
+      float v = 0.f;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int p = pb + j * VTHREADS;
-          x[j] = p < p1 ? __ldcg(P.logits + row + p) : 0.f;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int p = pb + j * VTHREADS;
-          if (p < p1) P.weights[row + p] = __float2half_rn(fast_exp2((x[j] - mh) * 1.4426950408889634f) * inv);
-        }
+      for (int w = 0; w < VWARPS; ++w) {
+        const VWarpShared& o = sh.w[w];
+        v += (first_of_two ? o.v.red0[h & 3][ch] : o.u.red[h & 3][ch]) + o.zt[ch >> P.gv_shift][h];
       }
+      part[i] = v;
     }
   }
-
-  // ---- exp(logit - max) of the chunk's tokens: the gathers of four heads are in flight together
-  for (int h0 = 0; h0 < rep; h0 += 4) {
-    float x[4][V_STAGE_ITERS];
-#pragma unroll
-    for (int hh = 0; hh < 4; ++hh) {
-      const int h = min(h0 + hh, rep - 1);
-      const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
-#pragma unroll
-      for (int j = 0; j < V_STAGE_ITERS; ++j) {
-        const int i = tid + j * VTHREADS;
-        x[hh][j] = i < chunk_n ? __ldcg(row + pos[j]) : -INFINITY;
-      }
-    }
-#pragma unroll
-    for (int hh = 0; hh < 4; ++hh) {
-      const int h = h0 + hh;
-      if (h < rep) {
-        const float mh = sh.gm[h];
-#pragma unroll
-        for (int j = 0; j < V_STAGE_ITERS; ++j) {
-          const int i = tid + j * VTHREADS;
-          if (i < chunk_pad) sh.e[h][i] = __float2half_rn(fast_exp2((x[hh][j] - mh) * 1.4426950408889634f));
-        }
-      }
-    }
-  }
-  __syncthreads();
-
-  // ---- main loop: this warp's 16-token steps, two steps of words in flight beyond the current one
-  float acc[8][4];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-  int cg[2];
-#pragma unroll
-  for (int s = 0; s < 2; ++s) {
-    const int ch0 = VFmt<BITS>::HALF_SPLIT ? (16 * g + 8 * s) : (8 * (s * 8 + g));
-    cg[s] = ch0 >> P.gv_shift;
-  }
-#pragma unroll 1
-  for (; kt0 < chunk_n; kt0 += step) {
-    if (kt0 + 2 * step < chunk_n) v_load<BITS>(w2, base, chunk_t0, chunk_n, kt0 + 2 * step, g, tig);
-    v_step<BITS>(acc, w0, sh, cg, kt0, g, tig, rep);
-#pragma unroll
-    for (int p = 0; p < 4; ++p)
-#pragma unroll
-      for (int s = 0; s < NW; ++s) {
-        w0[p][s] = w1[p][s];
-        w1[p][s] = w2[p][s];
-      }
-  }
-  // fold acc (fragment layout) into sh.red[warp][head][channel]
-#pragma unroll
-  for (int mt = 0; mt < 8; ++mt)
-#pragma unroll
-    for (int s = 0; s < 2; ++s) {
-      const int ch = (BITS == 2) ? (16 * g + 8 * s + mt) : (8 * (s * 8 + g) + mt);
-#pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        const int h = 2 * tig + e;
-        if (h < rep) sh.red[warp][h][ch] = acc[mt][s * 2 + e];
-      }
-    }
-  __syncthreads();
-  // partial output of this chunk: warps added in index order
-  float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
-  for (int i = tid; i < rep * D; i += VTHREADS) {
-    const int h = i / D, ch = i - h * D;
-    float v = sh.red[0][h][ch];
-#pragma unroll
-    for (int w = 1; w < VWARPS; ++w) v += sh.red[w][h][ch];
-    part[i] = v;
-  }
-}
-
-__global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
-  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
-  const int chunk = blockIdx.y, bh = blockIdx.x;
-  const int b = bh / P.H, kvh = bh - b * P.H;
-  const int tid = threadIdx.x;
-  const int rep = P.rep;
-
-  int ti = HQKV_NUM_TIERS;
-#pragma unroll
-  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
-    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
-  const TierDev& T = P.tier[ti];
-  const int chunk_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
-  const int chunk_n = min(T.v_chunk_tokens, T.n_v - chunk_t0);
-  const bool is_res = ti == HQKV_NUM_TIERS;
-  const int vb = is_res ? 16 : T.bits;
-  if (vb == 8) v_body<8>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
-  else if (vb == 4) v_body<4>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
-  else if (vb == 2) v_body<2>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, false, true);
-  else v_body<16>(P, T, sh, bh, b, kvh, chunk, chunk_t0, chunk_n, is_res, false);
 
   // ---- last CTA of this (batch, kv head) sums the partial outputs in chunk order
   __threadfence();
@@ -1210,43 +1365,29 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
   __syncthreads();
   if (sh.is_last) {
     __threadfence();
-    // threads 0..127 add the first half of the chunks, 128..255 the second half (each in chunk order,
-    // four consecutive outputs per thread, eight 16-byte loads in flight), then the halves are added
+    // four consecutive outputs per thread, eight 16-byte loads in flight
     const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
     const int64_t stride = static_cast<int64_t>(rep) * D;
-    const int half = tid >> 7, t4 = (tid & 127) * 4;
-    const int c_mid = (P.nv_chunks + 1) >> 1;
-    const int c_lo = half ? c_mid : 0, c_hi = half ? P.nv_chunks : c_mid;
-    float* scratch = &sh.red[0][0][0];  // rep*D floats, free again after the partial write above
-    for (int i0 = 0; i0 < rep * D; i0 += 512) {
-      const int i = i0 + t4;
+    for (int i = tid * 4; i < rep * D; i += VTHREADS * 4) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (i < rep * D) {
-        for (int c = c_lo; c < c_hi; c += 8) {
-          float4 t[8];
+      for (int c = 0; c < P.nv_chunks; c += 8) {
+        float4 t[8];
 #pragma unroll
-          for (int k = 0; k < 8; ++k)
-            t[k] = (c + k < c_hi) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
-                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < 8; ++k)
+          t[k] = (c + k < P.nv_chunks) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
+                                       : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
-            v.x += t[k].x;
-            v.y += t[k].y;
-            v.z += t[k].z;
-            v.w += t[k].w;
-          }
+        for (int k = 0; k < 8; ++k) {
+          v.x += t[k].x;
+          v.y += t[k].y;
+          v.z += t[k].z;
+          v.w += t[k].w;
         }
-        if (half) *reinterpret_cast<float4*>(scratch + i) = v;
       }
-      __syncthreads();
-      if (!half && i < rep * D) {
-        const float4 u = *reinterpret_cast<const float4*>(scratch + i);
-        const float inv = 1.f / sh.gl[i / D];
-        __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
-        o[0] = __floats2half2_rn((v.x + u.x) * inv, (v.y + u.y) * inv);
-        o[1] = __floats2half2_rn((v.z + u.z) * inv, (v.w + u.w) * inv);
-      }
-      __syncthreads();
+      const float inv = 1.f / sh.gl[i >> 7];
+      __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
+      o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
+      o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
     }
     if (tid == 0) P.counters[bh] = 0u;  // ready for the next call
   }
@@ -1301,18 +1442,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.gv_shift = ilog2(c->group_v);
   P.scale = c->softmax_scale;
   static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
-  // V chunk: the smallest multiple of 128 tokens (256..1024) with which all CTAs are resident at once
-  // (two 256-thread CTAs per SM); larger caches simply run several waves of 1024-token chunks
-  int v_chunk = 256;
-  {
-    const int64_t slots = V_MIN_CTAS * static_cast<int64_t>(sm_count());
-    const int64_t bh = static_cast<int64_t>(c->B) * c->H;
-    for (; v_chunk < V_MAX_CHUNK; v_chunk += 128) {
-      int64_t ctas = ceil_div(c->n_new > 0 ? c->n_new : 0, VWARPS * 16);
-      for (int t = 0; t < HQKV_NUM_TIERS; ++t) ctas += ceil_div(c->tier[t].n_v > 0 ? c->tier[t].n_v : 0, v_chunk);
-      if (ctas * bh <= slots) break;
-    }
-  }
   int64_t nk_total = 0, nv_total = 0;
   int kc = 0, vc = 0;
   for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
@@ -1358,7 +1487,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     const int b = d.bits;
     d.k_chunk_tokens = KWARPS * (b == 8 || b == 16 ? 64 : 128);  // one tile per warp
     HQKV_REQUIRE(static_cast<int64_t>(s.n_k) * D * b / 8 < (1ll << 31), "decode: tier %d K plane of one head exceeds 2 GiB", t);
-    d.v_chunk_tokens = v_chunk;
+    d.v_chunk_tokens = VWARPS * (b == 8 ? 64 : b == 16 ? 16 : 128);  // one tile per warp
     d.k_chunk0 = kc;
     d.v_chunk0 = vc;
     kc += static_cast<int>(ceil_div(d.n_k, d.k_chunk_tokens));
