@@ -57,6 +57,8 @@ struct DecodeParams {
   float* logits;   // [B*nh_q][L]
   float2* k_part;  // [B*H][nk_chunks][MAX_REP]
   float* v_part;   // [B*H][nv_chunks][rep][D]
+  float* v_part2;  // [B*H][nv_groups][rep][D]: sums of V_MERGE consecutive chunks
+  int nv_groups;   // 0: one-level merge
   unsigned* counters;  // [B*H]
 };
 
@@ -433,7 +435,7 @@ __device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, 
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int gam = g & 3;
   float zacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+#pragma unroll 2
   for (int kt = 0; kt < 8; ++kt) {
     const int o = (16 * kt) * K_RAW_HALFS + gam;
     const uint32_t a0 = pack_lo16(__half_as_ushort(z_even[o]), __half_as_ushort(z_odd[o]));
@@ -534,59 +536,69 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
   for (int hh = 0; hh < nh; ++hh) {
     k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0]);
     const uint2* qb = &sh.qb[hh][0][lane];
-#pragma unroll
+#pragma unroll 1
     for (int j = 0; j < TL::NSUB; ++j) {
       // as a B column this lane is n = g: columns 0-3 carry the scale group of tokens 0-31 of the
       // sub-span, columns 4-7 that of tokens 32-63
       const int gam = ((tile_t0 + j * K_SPAN + 32 * (g >> 2)) >> P.gk_shift) - g0c;
       const __half* s_even = &sh.s[2 * tig][sh_even + gam];
       const __half* s_odd = &sh.s[2 * tig + 1][sh_odd + gam];
+      const unsigned char* kb = ws.u.codes + (lm_off ^ (j * TL::CPS * 16));
+      const uint2* qk = qb;
       float acc[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-      uint32_t R2[4];  // 2 bits: one ldmatrix feeds two steps
-#pragma unroll
-      for (int kt = 0; kt < 8; ++kt) {
-        if (hh == 0 && j == 0 && (kt & 1) == 0) {  // the codes arrive two steps at a time
-          if (kt == 0) cp_async_wait<3>();
-          if (kt == 2) cp_async_wait<2>();
-          if (kt == 4) cp_async_wait<1>();
-          if (kt == 6) cp_async_wait<0>();
+      // two 16-channel steps per iteration (short loop body: the instruction cache is cold in every CTA
+      // when the whole cache is one wave of CTAs)
+#pragma unroll 1
+      for (int kk = 0; kk < 4; ++kk) {
+        if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
+          if (kk == 0) cp_async_wait<3>();
+          else if (kk == 1) cp_async_wait<2>();
+          else if (kk == 2) cp_async_wait<1>();
+          else cp_async_wait<0>();
           __syncwarp();
         }
-        // A fragments: lo/hi of octet 0 -> registers 0/1 (channels 2tig, 2tig+1), of octet 1 -> 2/3 (+8)
-        uint32_t a[4][4];  // [register][M-tile]
-        const unsigned char* kb = ws.u.codes + kt * 16 * TL::PITCH;
-        if constexpr (BITS == 8) {
-          uint32_t R[4];
-          ldmatrix_x4_trans(R, kb + lm_off);
-          octet_frags<8>(R, a[0], a[1]);
-          ldmatrix_x4_trans(R, kb + lm_off + 8 * TL::PITCH);
-          octet_frags<8>(R, a[2], a[3]);
-        } else if constexpr (BITS == 4) {
-          uint32_t R[4];
-          ldmatrix_x4_trans(R, kb + (lm_off ^ (j * 32)));
-          octet_frags<4>(R, a[0], a[1]);
-          octet_frags<4>(R + 2, a[2], a[3]);
-        } else {
-          if ((kt & 1) == 0) ldmatrix_x4_trans(R2, kb + (lm_off ^ (j * 16)));
-          octet_frags<2>(R2 + 2 * (kt & 1), a[0], a[1]);
-          octet_frags<2>(R2 + 2 * (kt & 1) + 1, a[2], a[3]);
-        }
-        const int o = (16 * kt) * K_RAW_HALFS;
-        const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
-        const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]),
-                                               __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS])));
-        const uint2 qv = qb[kt * 32];
-        const __half2 hi0 = __hmul2(u32_as_h2(qv.x), s0);
-        const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
-        const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
-        const __half2 lo1 = __hfma2(u32_as_h2(qv.y), s1, __hneg2(hi1));
+        uint32_t R2[4];  // 2 bits: one ldmatrix feeds both steps
+        if constexpr (BITS == 2) ldmatrix_x4_trans(R2, kb);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
-          mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
+        for (int k2 = 0; k2 < 2; ++k2) {
+          // A fragments: lo/hi of octet 0 -> registers 0/1 (channels 2tig, 2tig+1), of octet 1 -> 2/3 (+8)
+          uint32_t a[4][4];  // [register][M-tile]
+          if constexpr (BITS == 8) {
+            uint32_t R[4];
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH);
+            octet_frags<8>(R, a[0], a[1]);
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH + 8 * TL::PITCH);
+            octet_frags<8>(R, a[2], a[3]);
+          } else if constexpr (BITS == 4) {
+            uint32_t R[4];
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH);
+            octet_frags<4>(R, a[0], a[1]);
+            octet_frags<4>(R + 2, a[2], a[3]);
+          } else {
+            octet_frags<2>(R2 + 2 * k2, a[0], a[1]);
+            octet_frags<2>(R2 + 2 * k2 + 1, a[2], a[3]);
+          }
+          const int o = (16 * k2) * K_RAW_HALFS;
+          const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
+          const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]),
+                                                 __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS])));
+          const uint2 qv = qk[k2 * 32];
+          const __half2 hi0 = __hmul2(u32_as_h2(qv.x), s0);
+          const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
+          const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
+          const __half2 lo1 = __hfma2(u32_as_h2(qv.y), s1, __hneg2(hi1));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
+            mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
+          }
         }
+        kb += 32 * TL::PITCH;
+        s_even += 32 * K_RAW_HALFS;
+        s_odd += 32 * K_RAW_HALFS;
+        qk += 64;
       }
       // Epilogue from registers: a lane keeps the accumulator columns whose scale group is its row's.
       //  8 / 4 bits: rows 0-7 are tokens 0-31, rows 8-15 tokens 32-63: lanes tig 0,1 own row g, lanes
@@ -715,6 +727,9 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
   float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   if (ntok > 0) {
     float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * P.L;
+#ifdef HQKV_X_NOKCOMPUTE
+    if (P.L < 0)
+#endif
     k_tile_compute<BITS>(P, T, sh, ws, tile_t0, ntok, g0c, nh, row0, m, l);
   }
   // the warp's (max, sum-exp) per head: lanes that share tig & 1 hold pairs of the same two heads
@@ -905,6 +920,7 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 constexpr int VWARPS = 4;
 constexpr int VTHREADS = VWARPS * 32;
 constexpr int V_MAX_TT = 128;                 // tokens per tile at most
+constexpr int V_MERGE = 8;                   // chunks per first-level merge group
 constexpr int V_PROW = V_MAX_TT + 8;          // halfs per staged probability row (pitch 68 words: rows 4 banks apart)
 
 template <int BITS>
@@ -1045,7 +1061,9 @@ __device__ __forceinline__ void v_tile_probs(const DecodeParams& P, const VShare
       const int t = lane + 32 * j;
       const float e = on ? fast_exp2(fmaf(x[hh][j], LOG2E, -mh)) : 0.f;  // exp2(-inf) = 0 beyond the tile
       prow[hh][t] = __float2half_rn(e);
+#ifndef HQKV_X_NOWEIGHTS
       if (on && t < ntok) wrow[pos[j]] = __float2half_rn(e * inv);
+#endif
     }
   }
 }
@@ -1074,7 +1092,11 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   zacc[0] = zacc[1] = zacc[2] = zacc[3] = 0.f;
 
+#ifdef HQKV_X_NOWALK
+  const int nsteps = P.L < 0 ? 1 : 0;
+#else
   const int nsteps = ntok >> 4;
+#endif
 #pragma unroll 1
   for (int st = 0; st < nsteps; ++st) {
     const int t0 = st * 16;
@@ -1355,27 +1377,46 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
     }
   }
 
-  // ---- last CTA of this (batch, kv head) sums the partial outputs in chunk order
-  __threadfence();
-  __syncthreads();
-  if (tid == 0) {
-    const unsigned prev = atomicAdd(&P.counters[bh], 1u);
-    sh.is_last = (prev == static_cast<unsigned>(P.nv_chunks) - 1u) ? 1u : 0u;
+  // ---- Deterministic merge of the partial outputs.  The last CTA to finish in each group of V_MERGE
+  //      consecutive chunks adds the group's partials in chunk order; the last group to be added adds
+  //      the group sums in group order, normalises and writes the output.  (One level would leave the
+  //      very last CTA with nv_chunks dependent rounds of loads while the GPU idles.)
+  const float* src = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
+  int first = 0, count = P.nv_chunks;
+  unsigned* counter = &P.counters[bh];
+  bool final_level = true;
+  if (P.nv_groups > 0) {
+    const int grp = chunk / V_MERGE;
+    first = grp * V_MERGE;
+    count = min(V_MERGE, P.nv_chunks - first);
+    counter = &P.counters[P.B * P.H + bh * P.nv_groups + grp];
+    final_level = false;
   }
-  __syncthreads();
-  if (sh.is_last) {
+  for (int level = 0; level < 2; ++level) {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned prev = atomicAdd(counter, 1u);
+      sh.is_last = (prev == static_cast<unsigned>(count) - 1u) ? 1u : 0u;
+      if (sh.is_last) *counter = 0u;  // ready for the next call
+    }
+    __syncthreads();
+#ifdef HQKV_X_NOMERGE
+    if (P.L > 0) return;
+#endif
+    if (!sh.is_last) return;
     __threadfence();
     // four consecutive outputs per thread, eight 16-byte loads in flight
-    const float* all = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
     const int64_t stride = static_cast<int64_t>(rep) * D;
+    float* dst2 = P.v_part2 + (static_cast<int64_t>(bh) * max(P.nv_groups, 1) + chunk / V_MERGE) * stride;
     for (int i = tid * 4; i < rep * D; i += VTHREADS * 4) {
       float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = 0; c < P.nv_chunks; c += 8) {
+      for (int c = first; c < first + count; c += 8) {
         float4 t[8];
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          t[k] = (c + k < P.nv_chunks) ? __ldcg(reinterpret_cast<const float4*>(all + (c + k) * stride + i))
-                                       : make_float4(0.f, 0.f, 0.f, 0.f);
+          t[k] = (c + k < first + count) ? __ldcg(reinterpret_cast<const float4*>(src + (c + k) * stride + i))
+                                         : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           v.x += t[k].x;
@@ -1384,12 +1425,22 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
           v.w += t[k].w;
         }
       }
-      const float inv = 1.f / sh.gl[i >> 7];
-      __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
-      o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
-      o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
+      if (final_level) {
+        const float inv = 1.f / sh.gl[i >> 7];
+        __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
+        o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
+        o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
+      } else {
+        *reinterpret_cast<float4*>(dst2 + i) = v;
+      }
     }
-    if (tid == 0) P.counters[bh] = 0u;  // ready for the next call
+    if (final_level) return;
+    // second level: the group sums of this (batch, kv head)
+    src = P.v_part2 + static_cast<int64_t>(bh) * P.nv_groups * stride;
+    first = 0;
+    count = P.nv_groups;
+    counter = &P.counters[bh];
+    final_level = true;
   }
 }
 
@@ -1418,7 +1469,7 @@ static int ilog2(int v) {
 }
 
 struct Layout {
-  size_t logits_off, kpart_off, vpart_off, total;
+  size_t logits_off, kpart_off, vpart_off, vpart2_off, total;
 };
 
 static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay) {
@@ -1528,6 +1579,12 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   off = (off + 255) & ~static_cast<size_t>(255);
   lay.vpart_off = off;
   off += static_cast<size_t>(BH) * vc * P.rep * D * sizeof(float);
+  off = (off + 255) & ~static_cast<size_t>(255);
+  // two-level merge when it pays (more than two groups) and its counters fit the counter block
+  P.nv_groups = static_cast<int>(ceil_div(vc, V_MERGE));
+  if (P.nv_groups < 3 || (BH + BH * P.nv_groups) * sizeof(unsigned) > HQKV_WS_COUNTER_BYTES) P.nv_groups = 0;
+  lay.vpart2_off = off;
+  off += static_cast<size_t>(BH) * (P.nv_groups > 0 ? P.nv_groups : 1) * P.rep * D * sizeof(float);
   lay.total = (off + 255) & ~static_cast<size_t>(255);
   return HQKV_OK;
 }
@@ -1564,6 +1621,7 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
   P.logits = reinterpret_cast<float*>(ws + lay.logits_off);
   P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
   P.v_part = reinterpret_cast<float*>(ws + lay.vpart_off);
+  P.v_part2 = reinterpret_cast<float*>(ws + lay.vpart2_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 block(NTHREADS);
   const unsigned BH = static_cast<unsigned>(P.B * P.H);
