@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libhqkv.so")
 
 NUM_TIERS = 5
 TIER_BITS = (16, 8, 4, 2, 1)
-WS_COUNTER_BYTES = 65536
+WS_COUNTER_BYTES = 4096
 
 
 class HqkvError(RuntimeError):

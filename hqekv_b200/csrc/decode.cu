@@ -56,11 +56,33 @@ struct DecodeParams {
   __half* out;
   float* logits;   // [B*nh_q][L]
   float2* k_part;  // [B*H][nk_chunks][MAX_REP]
-  float* v_part;   // [B*H][nv_chunks][rep][D]
-  float* v_part2;  // [B*H][nv_groups][rep][D]: sums of V_MERGE consecutive chunks
-  int nv_groups;   // 0: one-level merge
+  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K pass, summed into by the V pass
   unsigned* counters;  // [B*H]
 };
+
+#ifdef HQKV_X_TIMELINE
+// experiment: per-CTA time stamps.  record = 8 x uint64: [0] kernel(1=K,2=V) | bh<<8 | chunk<<32, [1..7] stamps
+constexpr int TL_MAX = 1 << 16;
+__device__ unsigned long long g_tl[TL_MAX * 8];
+__device__ unsigned g_tl_n;
+__device__ __forceinline__ unsigned long long tl_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __noinline__ unsigned long long* tl_buf() {
+  __shared__ unsigned long long t[8];
+  return t;
+}
+#define TL_STAMP(i) do { if (threadIdx.x == 0) tl_buf()[i] = tl_now(); } while (0)
+#define TL_FLUSH(kern) do { if (threadIdx.x == 0) { unsigned slot = atomicAdd(&g_tl_n, 1u); if (slot < TL_MAX) { \
+  unsigned long long* tl_ = tl_buf(); \
+  tl_[0] = (unsigned long long)(kern) | ((unsigned long long)blockIdx.x << 8) | ((unsigned long long)blockIdx.y << 32); \
+  for (int q_ = 0; q_ < 8; ++q_) g_tl[slot * 8 + q_] = tl_[q_]; } } } while (0)
+#else
+#define TL_STAMP(i)
+#define TL_FLUSH(kern)
+#endif
 
 // ------------------------------------------------------------------------------------------------
 // fragments
@@ -703,10 +725,11 @@ __device__ __forceinline__ void k_write_tile(const DecodeParams& P, const float*
 }
 
 
-// One tile per warp: request everything, agree that q and the scale rows are in shared memory, compute.
-template <int BITS>
+// One tile per warp: request everything that depends only on the cache, wait for the kernels before
+// this one, fetch q, agree that q and the scale rows are in shared memory, compute.
+template <int BITS, typename LoadQ>
 __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
-                                        int chunk_t0, int nh) {
+                                        int chunk_t0, int nh, LoadQ load_q) {
   using TL = KTile<BITS>;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   KWarpShared& ws = sh.w[warp];
@@ -714,16 +737,23 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
   const int g0c = chunk_t0 >> P.gk_shift;
   const int ngc = ((chunk_end - 1) >> P.gk_shift) - g0c + 1;
   k_scales_request(P, T, sh, bh, g0c, ngc);
-  cp_async_commit();  // oldest group: q (requested by the caller) and the scale / zero rows
+  cp_async_commit();  // oldest group: the scale / zero rows
   const int tile_t0 = chunk_t0 + warp * TL::TOKENS;
   const int ntok = min(TL::TOKENS, T.n_k - tile_t0);  // <= 0: this warp has no tile
+  if (ntok > 0) k_tile_request<BITS>(T, ws, bh, tile_t0, ntok);
+  // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
+  // the previous decode call of the stream may still be using: wait for the kernels before it.
+  TL_STAMP(2);
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  TL_STAMP(3);
+  load_q();
   if (ntok > 0) {
-    k_tile_request<BITS>(T, ws, bh, tile_t0, ntok);
     cp_async_wait<4>();
   } else {
     cp_async_wait<0>();
   }
   __syncthreads();
+  TL_STAMP(4);
   float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   if (ntok > 0) {
     float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * P.L;
@@ -842,6 +872,7 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
   // prologue - V words, index lists, scale/zero tiles - as soon as SM resources free up; it waits for
   // this grid to finish (griddepcontrol.wait) before it touches the logits or the softmax pairs.
   asm volatile("griddepcontrol.launch_dependents;");
+  TL_STAMP(1);
   if (tid < KWARPS * MAX_REP) {
     (&sh.red_m[0][0])[tid] = -INFINITY;
     (&sh.red_l[0][0])[tid] = 0.f;
@@ -856,25 +887,30 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
   const bool plain = ti == HQKV_NUM_TIERS || T.bits == 16;
 
   // B fragments of q: rows are channels 16*kt + 2*tig + (0,1 | 8,9), column n = g is a query head of
-  // this kv head (see KShared::qb).  Warp hh copies its half global -> shared in its oldest cp.async group.
+  // this kv head (see KShared::qb); warp hh stores its half.  q is the only input that an earlier
+  // kernel of the stream may still be writing, so it is read after griddepcontrol.wait.
   const int nh = (!plain && P.rep > 4) ? 2 : 1;
-  if (warp < nh) {
-    const int head = plain ? g : 4 * warp + (g & 3);
-    const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + head) * D + 2 * tig;
+  auto load_q = [&]() {
+    if (warp < nh) {
+      const int head = plain ? g : 4 * warp + (g & 3);
+      const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + head) * D + 2 * tig;
+      uint2 qf[8];
 #pragma unroll
-    for (int kt = 0; kt < 8; ++kt) {
-      if (head < P.rep) {
-        cp_async_4(&sh.qb[warp][kt][lane].x, qh + 16 * kt);
-        cp_async_4(&sh.qb[warp][kt][lane].y, qh + 16 * kt + 8);
-      } else {
-        sh.qb[warp][kt][lane] = make_uint2(0u, 0u);
+      for (int kt = 0; kt < 8; ++kt) {
+        qf[kt] = make_uint2(0u, 0u);
+        if (head < P.rep) {
+          qf[kt].x = *reinterpret_cast<const uint32_t*>(qh + 16 * kt);
+          qf[kt].y = *reinterpret_cast<const uint32_t*>(qh + 16 * kt + 8);
+        }
       }
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) sh.qb[warp][kt][lane] = qf[kt];
     }
-  }
+  };
 
   if (plain) {
-    cp_async_commit();
-    cp_async_wait_all();
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    load_q();
     __syncthreads();
     const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
     if (ti == HQKV_NUM_TIERS) {
@@ -885,20 +921,30 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
       if (t0 < chunk_end) k_f16_span(P, T, sh, bh, b, kvh, t0);
     }
   } else if (T.bits == 8) {
-    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, nh);
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
   } else if (T.bits == 4) {
-    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, nh);
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
   } else {
-    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, nh);
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
   }
 
+  // the output accumulators of this (batch, kv head) start from zero in every call (the V pass, which
+  // adds into them, starts after this grid has finished); both branches above have passed their
+  // griddepcontrol.wait, so the previous call is done with them
+  if (chunk == 0) {
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * P.rep * D;
+    for (int i = tid; i < P.rep * D; i += KTHREADS) accum[i] = 0.0;
+  }
   // (max, sum) of this CTA per head from the warps' pairs
   __syncthreads();
+  TL_STAMP(5);
   if (tid < MAX_REP) {
     float m = sh.red_m[0][tid], l = sh.red_l[0][tid];
     for (int w = 1; w < KWARPS; ++w) softmax_merge(m, l, sh.red_m[w][tid], sh.red_l[w][tid]);
     P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + tid] = make_float2(m, l);
   }
+  TL_STAMP(6);
+  TL_FLUSH(1);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -920,7 +966,6 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 constexpr int VWARPS = 4;
 constexpr int VTHREADS = VWARPS * 32;
 constexpr int V_MAX_TT = 128;                 // tokens per tile at most
-constexpr int V_MERGE = 8;                   // chunks per first-level merge group
 constexpr int V_PROW = V_MAX_TT + 8;          // halfs per staged probability row (pitch 68 words: rows 4 banks apart)
 
 template <int BITS>
@@ -1299,13 +1344,19 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
   VWarpShared& ws = sh.w[warp];
   const int ng = D >> P.gv_shift;
 
+  // The next kernel of the stream - the K pass of the next decode call, if it was launched with
+  // programmatic stream serialisation - may start its cache-only prologue while this grid drains.
+  asm volatile("griddepcontrol.launch_dependents;");
+  TL_STAMP(1);
   // ---- requests that read only the cache go out before the K pass is known to be complete
   if (ntok > 0) {
     if (vb == 8) v_tile_request<8>(T, ws, bh, tile_t0, ntok, ng);
     else if (vb == 4) v_tile_request<4>(T, ws, bh, tile_t0, ntok, ng);
     else if (vb == 2) v_tile_request<2>(T, ws, bh, tile_t0, ntok, ng);
   }
+  TL_STAMP(2);
   asm volatile("griddepcontrol.wait;" ::: "memory");
+  TL_STAMP(3);
 
   // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks),
   //      up to four pairs per thread in flight, then slices are folded by shuffles and across warps
@@ -1344,6 +1395,7 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
     __syncthreads();
   }
 
+  TL_STAMP(4);
   // ---- the warp's tile: probabilities of its tokens, then sum_t p_t * V_t
   if (ntok > 0 && vb != 16) {
     if (vb == 8) v_tile<8>(P, T, sh, ws, b, kvh, ntok, nh);
@@ -1361,9 +1413,14 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
     (&ws.zt[0][0])[lane] = 0.f;  // 4 x MAX_REP floats
   }
   __syncthreads();
-  // ---- partial output of this chunk: warps added in index order
+  TL_STAMP(5);
+  // ---- partial output of this chunk (warps added in index order) joins the accumulators of this
+  //      (batch, kv head).  The adds are fire-and-forget fp64 reductions: the sum of the fp32 partials
+  //      depends on their order only below 2^-53, far below the fp16 rounding of the output, and no
+  //      CTA has to read other CTAs' partials back (a chain of dependent L2 round trips that used to
+  //      be a quarter of the kernel at batch 1).
   {
-    float* part = P.v_part + (static_cast<int64_t>(bh) * P.nv_chunks + chunk) * rep * D;
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
     for (int i = tid; i < rep * D; i += VTHREADS) {
       const int h = i >> 7, ch = i & (D - 1);
       const bool first_of_two = (h >> 2) + 1 < nh;
@@ -1373,75 +1430,34 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
         const VWarpShared& o = sh.w[w];
         v += (first_of_two ? o.v.red0[h & 3][ch] : o.u.red[h & 3][ch]) + o.zt[ch >> P.gv_shift][h];
       }
-      part[i] = v;
+      atomicAdd(accum + i, static_cast<double>(v));
     }
   }
-
-  // ---- Deterministic merge of the partial outputs.  The last CTA to finish in each group of V_MERGE
-  //      consecutive chunks adds the group's partials in chunk order; the last group to be added adds
-  //      the group sums in group order, normalises and writes the output.  (One level would leave the
-  //      very last CTA with nv_chunks dependent rounds of loads while the GPU idles.)
-  const float* src = P.v_part + static_cast<int64_t>(bh) * P.nv_chunks * rep * D;
-  int first = 0, count = P.nv_chunks;
-  unsigned* counter = &P.counters[bh];
-  bool final_level = true;
-  if (P.nv_groups > 0) {
-    const int grp = chunk / V_MERGE;
-    first = grp * V_MERGE;
-    count = min(V_MERGE, P.nv_chunks - first);
-    counter = &P.counters[P.B * P.H + bh * P.nv_groups + grp];
-    final_level = false;
+  // ---- the last CTA of this (batch, kv head) normalises and writes the output
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&P.counters[bh], 1u);
+    sh.is_last = (prev == static_cast<unsigned>(P.nv_chunks) - 1u) ? 1u : 0u;
+    if (sh.is_last) P.counters[bh] = 0u;  // ready for the next call
   }
-  for (int level = 0; level < 2; ++level) {
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned prev = atomicAdd(counter, 1u);
-      sh.is_last = (prev == static_cast<unsigned>(count) - 1u) ? 1u : 0u;
-      if (sh.is_last) *counter = 0u;  // ready for the next call
-    }
-    __syncthreads();
+  __syncthreads();
+  TL_STAMP(6);
 #ifdef HQKV_X_NOMERGE
-    if (P.L > 0) return;
+  if (P.L > 0) return;
 #endif
-    if (!sh.is_last) return;
+  if (sh.is_last) {
     __threadfence();
-    // four consecutive outputs per thread, eight 16-byte loads in flight
-    const int64_t stride = static_cast<int64_t>(rep) * D;
-    float* dst2 = P.v_part2 + (static_cast<int64_t>(bh) * max(P.nv_groups, 1) + chunk / V_MERGE) * stride;
-    for (int i = tid * 4; i < rep * D; i += VTHREADS * 4) {
-      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int c = first; c < first + count; c += 8) {
-        float4 t[8];
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          t[k] = (c + k < first + count) ? __ldcg(reinterpret_cast<const float4*>(src + (c + k) * stride + i))
-                                         : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          v.x += t[k].x;
-          v.y += t[k].y;
-          v.z += t[k].z;
-          v.w += t[k].w;
-        }
-      }
-      if (final_level) {
-        const float inv = 1.f / sh.gl[i >> 7];
-        __half2* o = reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i);
-        o[0] = __floats2half2_rn(v.x * inv, v.y * inv);
-        o[1] = __floats2half2_rn(v.z * inv, v.w * inv);
-      } else {
-        *reinterpret_cast<float4*>(dst2 + i) = v;
-      }
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
+    for (int i = tid * 2; i < rep * D; i += VTHREADS * 2) {
+      const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + i));
+      const float inv = 1.f / sh.gl[i >> 7];
+      *reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i) =
+          __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
     }
-    if (final_level) return;
-    // second level: the group sums of this (batch, kv head)
-    src = P.v_part2 + static_cast<int64_t>(bh) * P.nv_groups * stride;
-    first = 0;
-    count = P.nv_groups;
-    counter = &P.counters[bh];
-    final_level = true;
+    TL_STAMP(7);
   }
+  TL_FLUSH(2);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1469,7 +1485,7 @@ static int ilog2(int v) {
 }
 
 struct Layout {
-  size_t logits_off, kpart_off, vpart_off, vpart2_off, total;
+  size_t acc_off, logits_off, kpart_off, total;
 };
 
 static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay) {
@@ -1571,20 +1587,12 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.nv_chunks = vc;
   P.w_slice = static_cast<int>(ceil_div(L, vc));
   const int64_t BH = static_cast<int64_t>(c->B) * c->H;
-  lay.logits_off = HQKV_WS_COUNTER_BYTES;
+  lay.acc_off = HQKV_WS_COUNTER_BYTES;
+  lay.logits_off = (lay.acc_off + static_cast<size_t>(BH) * P.rep * D * sizeof(double) + 255) & ~static_cast<size_t>(255);
   size_t off = lay.logits_off + static_cast<size_t>(c->B) * c->nh_q * L * sizeof(float);
   off = (off + 255) & ~static_cast<size_t>(255);
   lay.kpart_off = off;
   off += static_cast<size_t>(BH) * kc * MAX_REP * sizeof(float2);
-  off = (off + 255) & ~static_cast<size_t>(255);
-  lay.vpart_off = off;
-  off += static_cast<size_t>(BH) * vc * P.rep * D * sizeof(float);
-  off = (off + 255) & ~static_cast<size_t>(255);
-  // two-level merge when it pays (more than two groups) and its counters fit the counter block
-  P.nv_groups = static_cast<int>(ceil_div(vc, V_MERGE));
-  if (P.nv_groups < 3 || (BH + BH * P.nv_groups) * sizeof(unsigned) > HQKV_WS_COUNTER_BYTES) P.nv_groups = 0;
-  lay.vpart2_off = off;
-  off += static_cast<size_t>(BH) * (P.nv_groups > 0 ? P.nv_groups : 1) * P.rep * D * sizeof(float);
   lay.total = (off + 255) & ~static_cast<size_t>(255);
   return HQKV_OK;
 }
@@ -1620,8 +1628,7 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
   P.counters = reinterpret_cast<unsigned*>(ws);
   P.logits = reinterpret_cast<float*>(ws + lay.logits_off);
   P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
-  P.v_part = reinterpret_cast<float*>(ws + lay.vpart_off);
-  P.v_part2 = reinterpret_cast<float*>(ws + lay.vpart2_off);
+  P.v_acc = reinterpret_cast<double*>(ws + lay.acc_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const dim3 block(NTHREADS);
   const unsigned BH = static_cast<unsigned>(P.B * P.H);
@@ -1640,8 +1647,20 @@ extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host,
     }
   }
   if (phases & 1) {
-    k_pass_kernel<<<dim3(BH, P.nk_chunks), dim3(KTHREADS), sizeof(KShared), st>>>(P);
-    HQKV_LAUNCH_CHECK("k_pass");
+    // programmatic stream serialisation: the grid may start while the kernel before it drains, if that
+    // kernel allows it (the V pass of the previous decode call does); everything it does before its
+    // griddepcontrol.wait reads only the cache tiers
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(BH, P.nk_chunks);
+    cfg.blockDim = dim3(KTHREADS);
+    cfg.dynamicSmemBytes = sizeof(KShared);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HQKV_CUDA(cudaLaunchKernelEx(&cfg, k_pass_kernel, P));
   }
   if (phases & 2) {
     cudaLaunchConfig_t cfg = {};
@@ -1717,3 +1736,16 @@ extern "C" int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host,
   HQKV_CUDA(cudaMemsetAsync(scratch, 0, HQKV_WS_COUNTER_BYTES, static_cast<cudaStream_t>(stream)));
   return hqkv_decode_attention(cache_host, q, attn_weights, attn_output, scratch, HQKV_STATIC_SCRATCH_BYTES, stream);
 }
+
+#ifdef HQKV_X_TIMELINE
+extern "C" int hqkv_x_timeline(void* dst, unsigned* n, int reset) {
+  unsigned cnt = 0;
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(&cnt, hqkv::g_tl_n, sizeof(cnt));
+  if (cnt > (unsigned)hqkv::TL_MAX) cnt = hqkv::TL_MAX;
+  if (dst) cudaMemcpyFromSymbol(dst, hqkv::g_tl, (size_t)cnt * 64);
+  if (n) *n = cnt;
+  if (reset) { unsigned z = 0; cudaMemcpyToSymbol(hqkv::g_tl_n, &z, sizeof(z)); }
+  return 0;
+}
+#endif

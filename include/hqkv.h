@@ -135,7 +135,7 @@ size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
  * The K-side and V-side token counts of a tier may differ only in order, not in total
  * (sum n_k == sum n_v); the 1-bit tier is not built (HQKV_E_UNSUPPORTED if non-empty).
  */
-#define HQKV_WS_COUNTER_BYTES 65536
+#define HQKV_WS_COUNTER_BYTES 4096
 int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                           void* workspace, size_t workspace_bytes, void* stream);
 
