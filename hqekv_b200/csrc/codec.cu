@@ -47,11 +47,17 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __half* __rest
   for (int64_t it = 0; it < n_iter; ++it) {
     const int64_t u = (it * gridDim.x + blockIdx.x) * static_cast<int64_t>(blockDim.x) + threadIdx.x;
     const bool live = u < total_units;
-    const int64_t row = live ? u / units_per_row : 0;
-    const int64_t t0 = live ? (u % units_per_row) * 8 : 0;
+    // packed source (the usual case): unit u is elements [8u, 8u+8) and no 64-bit division is needed;
+    // (row*T + t0) below is 8u either way
+    const bool packed = inner_stride == T && outer_stride == inner * T;
+    int64_t row = 0, t0 = live ? u * 8 : 0;
+    if (!packed && live) {
+      row = u / units_per_row;
+      t0 = (u % units_per_row) * 8;
+    }
     __half v[8];
     if (live) {
-      const __half* src = x + (row / inner) * outer_stride + (row % inner) * inner_stride + t0;
+      const __half* src = packed ? x + t0 : x + (row / inner) * outer_stride + (row % inner) * inner_stride + t0;
       if (vec_ok) {
         const uint4 raw = *reinterpret_cast<const uint4*>(src);
         *reinterpret_cast<uint4*>(v) = raw;
@@ -63,23 +69,26 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __half* __rest
 #pragma unroll
       for (int i = 0; i < 8; ++i) v[i] = __float2half(0.f);
     }
-    __half lo = v[0], hi = v[0];
-#pragma unroll
-    for (int i = 1; i < 8; ++i) {
-      lo = h_min(lo, v[i]);
-      hi = h_max(hi, v[i]);
-    }
+    // min / max of the group on half2 pairs (NaN propagates, as in torch.min / torch.max)
+    const __half2* v2 = reinterpret_cast<const __half2*>(v);
+    __half2 lo2 = __hmin2_nan(__hmin2_nan(v2[0], v2[1]), __hmin2_nan(v2[2], v2[3]));
+    __half2 hi2 = __hmax2_nan(__hmax2_nan(v2[0], v2[1]), __hmax2_nan(v2[2], v2[3]));
 #pragma unroll
     for (int off = 1; off < LPG; off <<= 1) {
-      const __half olo = __shfl_xor_sync(0xffffffffu, lo, off);
-      const __half ohi = __shfl_xor_sync(0xffffffffu, hi, off);
-      lo = h_min(lo, olo);
-      hi = h_max(hi, ohi);
+      lo2 = __hmin2_nan(lo2, __shfl_xor_sync(0xffffffffu, lo2, off));
+      hi2 = __hmax2_nan(hi2, __shfl_xor_sync(0xffffffffu, hi2, off));
     }
+    lo2 = __hmin2_nan(lo2, __lowhigh2highlow(lo2));
+    hi2 = __hmax2_nan(hi2, __lowhigh2highlow(hi2));
+    const __half lo = __low2half(lo2), hi = __low2half(hi2);
     const __half sc = quant_scale(lo, hi, levels);
+    const QuantGroup qg = quant_group(lo, sc, levels);
     uint64_t part = 0;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) part |= static_cast<uint64_t>(quant_code(v[i], lo, sc, levels)) << (i * BITS);
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t c2 = quant_code_fast2(*reinterpret_cast<const __half2*>(&v[2 * i]), qg);
+      part |= static_cast<uint64_t>((c2 & 0xFFFFu) | ((c2 >> 16) << BITS)) << (2 * i * BITS);
+    }
     const int lane = threadIdx.x & 31;
     const int64_t out_bit = (row * T + t0) * BITS;  // bit offset of this unit in the packed row-major stream
     if constexpr (BITS == 8) {
@@ -135,18 +144,66 @@ __global__ void __launch_bounds__(128) quantize_cols_kernel(const __half* __rest
     hi = h_max(hi, v);
   }
   const __half sc = quant_scale(lo, hi, levels);
+  const QuantGroup qg = quant_group(lo, sc, levels);
   const int64_t row = o * inner + d;
   const int64_t W = T / FPI;
   uint32_t* dst = code + row * W + gi * (group / FPI);
   for (int w = 0; w < group / FPI; ++w) {
     uint32_t word = 0;
 #pragma unroll
-    for (int i = 0; i < FPI; ++i) word |= quant_code(src[(w * FPI + i) * t_stride], lo, sc, levels) << (i * BITS);
+    for (int i = 0; i < FPI; ++i) word |= quant_code_fast(src[(w * FPI + i) * t_stride], qg) << (i * BITS);
     dst[w] = word;
   }
   const int64_t G = T / group;
   scale[row * G + gi] = sc;
   mn_out[row * G + gi] = lo;
+}
+
+// Same, two adjacent channels per thread (4-byte loads, half2 arithmetic): the usual case of an even,
+// 4-byte aligned channel count.  A warp reads 128 contiguous bytes per token.
+template <int BITS>
+__global__ void __launch_bounds__(64) quantize_cols2_kernel(const __half* __restrict__ x, int64_t inner, int64_t T,
+                                                            int64_t outer_stride, int64_t t_stride, int group,
+                                                            uint32_t* __restrict__ code, __half* __restrict__ scale,
+                                                            __half* __restrict__ mn_out) {
+  constexpr int FPI = 32 / BITS;
+  const float levels = static_cast<float>((1 << BITS) - 1);
+  const int64_t d = 2 * (static_cast<int64_t>(blockIdx.y) * blockDim.x + threadIdx.x);
+  if (d >= inner) return;
+  const int64_t o = blockIdx.z;
+  const int64_t gi = blockIdx.x;  // group index along T
+  const __half* src = x + o * outer_stride + d + gi * group * t_stride;
+  auto at = [&](int t) { return *reinterpret_cast<const __half2*>(src + t * t_stride); };
+  __half2 lo = at(0), hi = lo;
+#pragma unroll 8
+  for (int t = 1; t < group; ++t) {
+    const __half2 v = at(t);
+    lo = __hmin2_nan(lo, v);
+    hi = __hmax2_nan(hi, v);
+  }
+  const __half sc0 = quant_scale(__low2half(lo), __low2half(hi), levels);
+  const __half sc1 = quant_scale(__high2half(lo), __high2half(hi), levels);
+  const QuantGroup g0 = quant_group(__low2half(lo), sc0, levels), g1 = quant_group(__high2half(lo), sc1, levels);
+  const int64_t row = o * inner + d;
+  const int64_t W = T / FPI;
+  uint32_t* dst0 = code + row * W + gi * (group / FPI);
+  uint32_t* dst1 = dst0 + W;
+  for (int w = 0; w < group / FPI; ++w) {
+    uint32_t word0 = 0, word1 = 0;
+#pragma unroll
+    for (int i = 0; i < FPI; ++i) {
+      const uint32_t c2 = quant_code_fast2(at(w * FPI + i), g0, g1);
+      word0 |= (c2 & 0xFFFFu) << (i * BITS);
+      word1 |= (c2 >> 16) << (i * BITS);
+    }
+    dst0[w] = word0;
+    dst1[w] = word1;
+  }
+  const int64_t G = T / group;
+  scale[row * G + gi] = sc0;
+  mn_out[row * G + gi] = __low2half(lo);
+  scale[(row + 1) * G + gi] = sc1;
+  mn_out[(row + 1) * G + gi] = __high2half(lo);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -252,6 +309,16 @@ extern "C" int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_
     HQKV_REQUIRE(outer <= 65535 && ceil_div(inner, 128) <= 65535, "quantize_pack: too many rows for the column path");
     dim3 grid(static_cast<unsigned>(T / group), static_cast<unsigned>(ceil_div(inner, 128)),
               static_cast<unsigned>(outer));
+    if (inner % 2 == 0 && aligned(x, 4) && outer_stride % 2 == 0 && t_stride % 2 == 0) {
+      dim3 grid2(static_cast<unsigned>(T / group), static_cast<unsigned>(ceil_div(inner, 128)),
+                 static_cast<unsigned>(outer));
+      switch (bits) {
+        case 8: quantize_cols2_kernel<8><<<grid2, 64, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+        case 4: quantize_cols2_kernel<4><<<grid2, 64, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+        case 2: quantize_cols2_kernel<2><<<grid2, 64, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+        default: quantize_cols2_kernel<1><<<grid2, 64, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
+      }
+    } else
     switch (bits) {
       case 8: quantize_cols_kernel<8><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;
       case 4: quantize_cols_kernel<4><<<grid, 128, 0, st>>>(xs, inner, T, outer_stride, t_stride, group, c, s, m); break;

@@ -59,6 +59,45 @@ __device__ __forceinline__ uint32_t quant_code(__half x, __half mn, __half scale
   return static_cast<uint32_t>(__float2int_rn(u));
 }
 
+// The same code for many elements of one group.  x - mn with the native fp16 subtract (one rounding
+// of the exact difference equals the two roundings of "widen, subtract, narrow": fp32 carries 2*11 + 2
+// bits).  The quotient by Markstein's sequence: r = RN(1/scale) once per group, q0 = RN(d*r),
+// e = d - q0*scale (exact in one FMA), q1 = RN(q0 + e*r) is the correctly rounded fp32 quotient (the
+// scale has an 11-bit significand, never the all-ones fp32 significand the theorem excludes), so
+// half(q1) is what h_div returns; three FP32 instructions per element instead of a full IEEE divide.
+// A NaN or infinite intermediate (scale 0 or inf) ends as code 0 exactly as in quant_code.
+struct QuantGroup {
+  __half mn;
+  float scale, rcp, levels;
+};
+__device__ __forceinline__ QuantGroup quant_group(__half mn, __half scale, float levels) {
+  QuantGroup g;
+  g.mn = mn;
+  g.scale = __half2float(scale);
+  g.rcp = __frcp_rn(g.scale);
+  g.levels = levels;
+  return g;
+}
+__device__ __forceinline__ float quant_quotient(float d, const QuantGroup& g) {
+  const float q0 = __fmul_rn(d, g.rcp);
+  const float e = __fmaf_rn(-q0, g.scale, d);
+  return __fmaf_rn(e, g.rcp, q0);
+}
+__device__ __forceinline__ uint32_t quant_code_fast(__half x, const QuantGroup& g) {
+  float u = __half2float(__float2half_rn(quant_quotient(__half2float(__hsub(x, g.mn)), g)));
+  u = fminf(fmaxf(u, 0.f), g.levels);  // fmaxf(NaN, 0) == 0
+  return static_cast<uint32_t>(__float2int_rn(u));
+}
+// two elements (low half in group g, high half in group gh): codes in bits [0,10) and [16,26)
+__device__ __forceinline__ uint32_t quant_code_fast2(__half2 x, const QuantGroup& g, const QuantGroup& gh) {
+  const float2 d = __half22float2(__hsub2(x, __halves2half2(g.mn, gh.mn)));
+  __half2 u = __floats2half2_rn(quant_quotient(d.x, g), quant_quotient(d.y, gh));
+  u = __hmin2(__hmax2(u, __float2half2_rn(0.f)), __float2half2_rn(g.levels));  // max(NaN, 0) == 0
+  u = __hadd2(u, __float2half2_rn(1024.f));  // 1024 + rint(u): fp16 has unit spacing there, ties to even
+  return *reinterpret_cast<uint32_t*>(&u) & 0x03FF03FFu;
+}
+__device__ __forceinline__ uint32_t quant_code_fast2(__half2 x, const QuantGroup& g) { return quant_code_fast2(x, g, g); }
+
 // scale = half(half(mx - mn) / levels)
 __device__ __forceinline__ __half quant_scale(__half mn, __half mx, float levels) {
   return h_divf(h_sub(mx, mn), levels);

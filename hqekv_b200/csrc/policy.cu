@@ -356,10 +356,11 @@ __global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant_
     hi = h_max(hi, v);
   }
   const __half sc = quant_scale(lo, hi, levels);
+  const QuantGroup qg = quant_group(lo, sc, levels);
   for (int w = 0; w < wpg; ++w) {
     uint32_t word = 0;
     for (int i = 0; i < fpi; ++i)
-      word |= quant_code(k_src_value(A, src, pos0 + w * fpi + i, b, h, d), lo, sc, levels) << (i * bits);
+      word |= quant_code_fast(k_src_value(A, src, pos0 + w * fpi + i, b, h, d), qg) << (i * bits);
     dst[w] = word;
   }
   A.out_scale[row * Gd + jg] = sc;
@@ -431,7 +432,7 @@ __global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constan
   const __half sc = quant_scale(lo, hi, levels);
   uint32_t part = 0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) part |= quant_code(v[i], lo, sc, levels) << (i * bits);
+  for (int i = 0; i < 4; ++i) part |= quant_code_fast(v[i], quant_group(lo, sc, levels)) << (i * bits);
   const int lpw = 32 / (4 * bits);  // lanes per word: 1, 2, 4, 8 for 8, 4, 2, 1 bits
   for (int off = 1; off < lpw; off <<= 1) {
     const uint32_t other = __shfl_down_sync(0xffffffffu, part, off);
