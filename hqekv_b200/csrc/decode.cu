@@ -1358,35 +1358,35 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
   asm volatile("griddepcontrol.wait;" ::: "memory");
   TL_STAMP(3);
 
-  // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks),
-  //      up to four pairs per thread in flight, then slices are folded by shuffles and across warps
+  // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks);
+  //      only the heads that exist are read, up to four pairs per thread in flight (one round of loads
+  //      up to 4 * 128 / rep chunks), then slices are folded by shuffles and across warps
   {
-    constexpr int SLICES = VTHREADS / MAX_REP;
-    const int h = tid & (MAX_REP - 1), slice = tid >> 3;
+    const int rs = P.rep_shift;
+    const int h = tid & (rep - 1), slice = tid >> rs, slices = VTHREADS >> rs;
     const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
     float m = -INFINITY, l = 0.f;
-    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * SLICES) {
+    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * slices) {
       float2 v[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int c = c0 + SLICES * j;
+        const int c = c0 + slices * j;
         v[j] = c < P.nk_chunks ? __ldcg(part + c * MAX_REP + h) : make_float2(-INFINITY, 0.f);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
     }
-#pragma unroll
-    for (int off = 8; off < 32; off <<= 1) {
+    for (int off = rep; off < 32; off <<= 1) {
       const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
       const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
       softmax_merge(m, l, m2, l2);
     }
-    if (lane < MAX_REP) {
+    if (lane < rep) {
       sh.wm[warp][lane] = m;
       sh.wl[warp][lane] = l;
     }
     __syncthreads();
-    if (tid < MAX_REP) {
+    if (tid < rep) {
       float mm = sh.wm[0][tid], ll = sh.wl[0][tid];
       for (int w = 1; w < VWARPS; ++w) softmax_merge(mm, ll, sh.wm[w][tid], sh.wl[w][tid]);
       sh.gm[tid] = mm;
