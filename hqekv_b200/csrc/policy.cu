@@ -145,24 +145,6 @@ struct PlanArgs {
   int32_t* rank;       // by token id: rank among survivors
 };
 
-// block-wide exclusive scan of one flag per thread; returns the exclusive prefix and the block total
-__device__ __forceinline__ int block_scan_flag(bool flag, int& total, int* warp_sums) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const unsigned ballot = __ballot_sync(0xffffffffu, flag);
-  const int within = __popc(ballot & ((1u << lane) - 1u));
-  if (lane == 0) warp_sums[warp] = __popc(ballot);
-  __syncthreads();
-  int before = 0, tot = 0;
-  for (int w = 0; w < PLAN_THREADS / 32; ++w) {
-    const int s = warp_sums[w];
-    if (w < warp) before += s;
-    tot += s;
-  }
-  __syncthreads();
-  total = tot;
-  return before + within;
-}
-
 // Enumeration order of every cached token: residual (ascending id), then the 16-, 8-, 4-, 2-, 1-bit
 // tier in storage order.  Slot -> (source tier, position, token id).
 __device__ __forceinline__ void enum_slot(const PlanArgs& A, int64_t slot, int& src, int64_t& pos, int64_t& id) {
@@ -187,13 +169,28 @@ __device__ __forceinline__ void enum_slot(const PlanArgs& A, int64_t slot, int& 
   id = 0;
 }
 
+// One CTA of 32 warps.  Every pass walks the enumeration (or the token ids) in warp-contiguous ranges,
+// PLAN_BATCH iterations at a time so that the dependent loads of a batch (index list -> target ->
+// rank) are in flight together; ordered positions come from per-warp counts, one scan over the 32
+// warps, and ballot / match prefixes inside a warp.  Categories: 2*t = kept member of tier t,
+// 2*t + 1 = arrival in tier t (destination order: kept members first, then arrivals, both in
+// enumeration order); 10 = surviving token id.
+constexpr int PLAN_WARPS = PLAN_THREADS / 32;
+constexpr int PLAN_BATCH = 8;
+constexpr int PLAN_CATS = 2 * HQKV_NUM_TIERS + 1;
+
 __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_constant__ PlanArgs A) {
-  __shared__ int warp_sums[PLAN_THREADS / 32];
-  __shared__ int running;
+  __shared__ int cnt[PLAN_CATS][PLAN_WARPS];  // per-warp totals, then exclusive offsets over the warps
+  __shared__ int tot[PLAN_CATS];
   __shared__ int any_evict;
   const int64_t total = A.hist + A.compress;
-  const int tid = threadIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const unsigned lt = (1u << lane) - 1u;
+  // warp w owns elements [w * span, (w + 1) * span), span a multiple of 32
+  const int64_t iters = (total + PLAN_THREADS - 1) / PLAN_THREADS;
+  const int64_t span = iters * 32, first = warp * span;
   if (tid == 0) any_evict = 0;
+  if (tid < PLAN_CATS * PLAN_WARPS) (&cnt[0][0])[tid] = 0;
   // 1. targets by token id
   for (int64_t i = tid; i < total; i += PLAN_THREADS) A.tgt[i] = -1;
   __syncthreads();
@@ -208,79 +205,128 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
     }
   }
   __syncthreads();
-  // 2. final tier of every enumeration slot: 0..4 tier, 5 evicted, 6 dropped (residual without target)
-  for (int64_t s = tid; s < total; s += PLAN_THREADS) {
-    int src;
-    int64_t pos, id;
-    enum_slot(A, s, src, pos, id);
-    const int tg = A.tgt[id];
-    int f;
-    if (tg == 5) f = 5;
-    else if (src < 0) f = tg < 0 ? 6 : tg;
-    else f = tg > src ? tg : src;  // only moves to fewer bits (larger index); tg == -1 stays
-    A.fin[s] = static_cast<int8_t>(f);
+  // 2. final tier of every enumeration slot (0..4 tier, 5 evicted, 6 dropped: residual without target),
+  //    survival by token id, and the per-warp category counts
+  for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
+    int src[PLAN_BATCH];
+    int64_t id[PLAN_BATCH];
+    int tg[PLAN_BATCH];
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) {
+      const int64_t s = first + (j0 + u) * 32 + lane;
+      int64_t pos;
+      src[u] = -2;
+      id[u] = 0;
+      if (j0 + u < iters && s < total) enum_slot(A, s, src[u], pos, id[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) tg[u] = src[u] != -2 ? A.tgt[id[u]] : -1;
+#pragma unroll
+    for (int u = 0; u < PLAN_BATCH; ++u) {
+      if (src[u] == -2) continue;
+      const int64_t s = first + (j0 + u) * 32 + lane;
+      int f;
+      if (tg[u] == 5) f = 5;
+      else if (src[u] < 0) f = tg[u] < 0 ? 6 : tg[u];
+      else f = tg[u] > src[u] ? tg[u] : src[u];  // only moves to fewer bits (larger index); tg == -1 stays
+      A.fin[s] = static_cast<int8_t>(f);
+      A.rank[id[u]] = (tg[u] != 5) ? 1 : 0;  // token ids are a permutation of 0..total-1 over the enumeration
+      if (f < HQKV_NUM_TIERS) atomicAdd(&cnt[2 * f + (src[u] == f ? 0 : 1)][warp], 1);
+    }
   }
   __syncthreads();
-  // 3. survivor ranks by token id (token ids are a permutation of 0..total-1 over the enumeration)
-  //    first mark survival by id in `rank`, then exclusive-scan it in place
-  for (int64_t s = tid; s < total; s += PLAN_THREADS) {
-    int src;
-    int64_t pos, id;
-    enum_slot(A, s, src, pos, id);
-    A.rank[id] = (A.tgt[id] != 5) ? 1 : 0;
+  // 3. survivor counts per warp range of token ids
+  {
+    int mine = 0;
+    for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
+      int fl[PLAN_BATCH];
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) {
+        const int64_t i = first + (j0 + u) * 32 + lane;
+        fl[u] = (j0 + u < iters && i < total) ? A.rank[i] : 0;
+      }
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) mine += fl[u];
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
+    if (lane == 0) cnt[PLAN_CATS - 1][warp] = mine;
   }
   __syncthreads();
-  if (tid == 0) running = 0;
-  __syncthreads();
-  for (int64_t base = 0; base < total; base += PLAN_THREADS) {
-    const int64_t i = base + tid;
-    const bool flag = i < total && A.rank[i] != 0;
-    int tot;
-    const int ex = block_scan_flag(flag, tot, warp_sums);
-    const int r = running + ex;
-    if (i < total) A.rank[i] = r;
-    if (flag) A.survivors[r] = i;
-    __syncthreads();
-    if (tid == 0) running += tot;
-    __syncthreads();
+  // exclusive offsets of every category over the warps
+  if (tid < PLAN_CATS) {
+    int acc = 0;
+    for (int w = 0; w < PLAN_WARPS; ++w) {
+      const int c = cnt[tid][w];
+      cnt[tid][w] = acc;
+      acc += c;
+    }
+    tot[tid] = acc;
   }
-  if (tid == 0) A.counts[5] = running;
   __syncthreads();
-  // 4. destination lists: kept members of tier t first, then arrivals in enumeration order
-  for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
-    if (tid == 0) running = 0;
-    __syncthreads();
-    int64_t tier_first = A.compress;
-    for (int k = 0; k < t; ++k) tier_first += A.tier_n[k];
-    for (int pass = 0; pass < 2; ++pass) {
-      // pass 0: slots of tier t itself; pass 1: every slot that is not of tier t
-      const int64_t lo = pass == 0 ? tier_first : 0;
-      const int64_t hi = pass == 0 ? tier_first + A.tier_n[t] : total;
-      for (int64_t base = lo; base < hi; base += PLAN_THREADS) {
-        const int64_t s = base + tid;
-        bool flag = false;
-        int src = 0;
-        int64_t pos = 0, id = 0;
-        if (s < hi) {
-          enum_slot(A, s, src, pos, id);
-          flag = A.fin[s] == t && (pass == 0 || src != t);
-        }
-        int tot;
-        const int ex = block_scan_flag(flag, tot, warp_sums);
-        if (flag) {
-          const int64_t j = running + ex;
-          A.plan_src[t * total + j] = ((src + 1) << 28) | static_cast<int32_t>(pos);
-          A.plan_ids[t * total + j] = any_evict ? static_cast<int64_t>(A.rank[id]) : id;
-        }
-        __syncthreads();
-        if (tid == 0) running += tot;
-        __syncthreads();
+  // 4. survivor ranks by token id: rank[i] = survivors with a smaller id; survivors[rank] = id
+  {
+    int running = cnt[PLAN_CATS - 1][warp];
+    for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
+      int fl[PLAN_BATCH];
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) {
+        const int64_t i = first + (j0 + u) * 32 + lane;
+        fl[u] = (j0 + u < iters && i < total) ? A.rank[i] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) {
+        const unsigned ballot = __ballot_sync(0xffffffffu, fl[u] > 0);
+        const int64_t i = first + (j0 + u) * 32 + lane;
+        const int r = running + __popc(ballot & lt);
+        if (fl[u] >= 0) A.rank[i] = r;
+        if (fl[u] > 0) A.survivors[r] = i;
+        running += __popc(ballot);
       }
     }
-    if (tid == 0) A.counts[t] = running;
-    __syncthreads();
   }
+  __syncthreads();
+  // 5. destination lists
+  {
+    for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
+      int src[PLAN_BATCH], f[PLAN_BATCH];
+      int64_t pos[PLAN_BATCH], id[PLAN_BATCH];
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) {
+        const int64_t s = first + (j0 + u) * 32 + lane;
+        src[u] = -2;
+        pos[u] = id[u] = 0;
+        f[u] = 6;
+        if (j0 + u < iters && s < total) {
+          enum_slot(A, s, src[u], pos[u], id[u]);
+          f[u] = A.fin[s];
+        }
+      }
+      int64_t outid[PLAN_BATCH];
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u)
+        outid[u] = (any_evict && f[u] < HQKV_NUM_TIERS) ? static_cast<int64_t>(A.rank[id[u]]) : id[u];
+#pragma unroll
+      for (int u = 0; u < PLAN_BATCH; ++u) {
+        const bool on = f[u] < HQKV_NUM_TIERS;
+        const int cat = on ? 2 * f[u] + (src[u] == f[u] ? 0 : 1) : PLAN_CATS;  // PLAN_CATS: no destination
+        const unsigned same = __match_any_sync(0xffffffffu, cat);
+        if (on) {
+          const int base = cnt[cat][warp];  // this warp's running offset of the category (only this warp touches it)
+          const int64_t j = (cat & 1 ? tot[cat - 1] : 0) + base + __popc(same & lt);
+          A.plan_src[f[u] * total + j] = ((src[u] + 1) << 28) | static_cast<int32_t>(pos[u]);
+          A.plan_ids[f[u] * total + j] = outid[u];
+        }
+        __syncwarp();
+        if (on && (same & lt) == 0) cnt[cat][warp] += __popc(same);
+        __syncwarp();
+      }
+    }
+  }
+  __syncthreads();
+  if (tid < HQKV_NUM_TIERS) A.counts[tid] = tot[2 * tid] + tot[2 * tid + 1];
   if (tid == 0) {
+    A.counts[5] = tot[PLAN_CATS - 1];
     A.counts[6] = any_evict;
     A.counts[7] = 0;
   }
