@@ -622,73 +622,60 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
         s_odd += 32 * K_RAW_HALFS;
         qk += 64;
       }
-      // Epilogue from registers: a lane keeps the accumulator columns whose scale group is its row's.
+      // Epilogue from registers: a lane keeps the accumulator columns whose scale group is its row's, and
+      // every lane ends up with four tokens x two heads (heads 2*(tig&1), +1).
       //  8 / 4 bits: rows 0-7 are tokens 0-31, rows 8-15 tokens 32-63: lanes tig 0,1 own row g, lanes
-      //              tig 2,3 own row g+8; heads 2*(tig&1), +1; four tokens each.
-      //  2 bits:     rows g and g+8 are the eight tokens of block g: lanes with (g < 4) == (tig < 2)
-      //              own both rows; the other lanes own nothing.
+      //              tig 2,3 own row g+8.
+      //  2 bits:     rows g and g+8 are the eight tokens of block g, valid in the lanes with
+      //              (g < 4) == (tig < 2); such a lane keeps the row of its tig half and hands the
+      //              other row to lane tig ^ 2, whose own accumulators belong to the wrong scale group.
       const int sub_t0 = j * K_SPAN;
+      const int r = tig >> 1;
+      float val[4][2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) val[i][e] = r ? acc[i][2 + e] : acc[i][e];
       if constexpr (BITS == 2) {
-        const int my_tok = sub_t0 + 8 * g;
-        const bool live = ((g < 4) == (tig < 2)) && my_tok < ntok;
-        const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
-        const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
-        const int4 p01 = ip[0], p23 = ip[1], p45 = ip[2], p67 = ip[3];  // low words of int64 positions: .x and .z
-        const uint32_t pos[8] = {static_cast<uint32_t>(p01.x), static_cast<uint32_t>(p01.z), static_cast<uint32_t>(p23.x),
-                                 static_cast<uint32_t>(p23.z), static_cast<uint32_t>(p45.x), static_cast<uint32_t>(p45.z),
-                                 static_cast<uint32_t>(p67.x), static_cast<uint32_t>(p67.z)};
+        const bool valid = (g < 4) == (tig < 2);
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int head = 4 * hh + 2 * hp + e;
-          const bool on = live && head < P.rep;
-          const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
-          float* row = row0 + static_cast<int64_t>(head) * P.L;
+        for (int i = 0; i < 4; ++i)
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            float x[4];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float unscale = static_cast<float>(1 << (24 - KField<2>::shift(i)));
-              x[i] = on ? fmaf(acc[i][2 * half + e], P.scale * unscale, zqs) : -INFINITY;
-              if (on) row[pos[4 * half + i]] = x[i];
-            }
-            softmax_push4(m[hh][e], l[hh][e], x);
+          for (int e = 0; e < 2; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, r ? acc[i][e] : acc[i][2 + e], 2);
+            if (!valid) val[i][e] = other;
           }
-        }
+      }
+      // first of this lane's tokens (8 bits: tokens my_tok, +1, +16, +17; 4 and 2 bits: my_tok .. my_tok+3)
+      const int my_tok = sub_t0 + (BITS == 8 ? 32 * r + 2 * g : BITS == 4 ? 32 * r + 4 * g : 8 * g + 4 * r);
+      const bool live = my_tok < ntok;
+      const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
+      uint32_t pos[4];
+      if constexpr (BITS == 8) {
+        const int4 pa = *reinterpret_cast<const int4*>(&ws.idx[my_tok]);  // low words of int64 positions: .x and .z
+        const int4 pb = *reinterpret_cast<const int4*>(&ws.idx[my_tok + 16]);
+        pos[0] = static_cast<uint32_t>(pa.x), pos[1] = static_cast<uint32_t>(pa.z);
+        pos[2] = static_cast<uint32_t>(pb.x), pos[3] = static_cast<uint32_t>(pb.z);
       } else {
-        const int r = tig >> 1;
-        // first of this lane's tokens (8 bits: tokens my_tok, +1, +16, +17; 4 bits: my_tok .. my_tok+3)
-        const int my_tok = sub_t0 + 32 * r + (BITS == 8 ? 2 * g : 4 * g);
-        const bool live = my_tok < ntok;
-        const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
-        uint32_t pos[4];
-        if constexpr (BITS == 8) {
-          const int4 pa = *reinterpret_cast<const int4*>(&ws.idx[my_tok]);
-          const int4 pb = *reinterpret_cast<const int4*>(&ws.idx[my_tok + 16]);
-          pos[0] = static_cast<uint32_t>(pa.x), pos[1] = static_cast<uint32_t>(pa.z);
-          pos[2] = static_cast<uint32_t>(pb.x), pos[3] = static_cast<uint32_t>(pb.z);
-        } else {
-          const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
-          const int4 p01 = ip[0], p23 = ip[1];
-          pos[0] = static_cast<uint32_t>(p01.x), pos[1] = static_cast<uint32_t>(p01.z);
-          pos[2] = static_cast<uint32_t>(p23.x), pos[3] = static_cast<uint32_t>(p23.z);
-        }
+        const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
+        const int4 p01 = ip[0], p23 = ip[1];
+        pos[0] = static_cast<uint32_t>(p01.x), pos[1] = static_cast<uint32_t>(p01.z);
+        pos[2] = static_cast<uint32_t>(p23.x), pos[3] = static_cast<uint32_t>(p23.z);
+      }
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int head = 4 * hh + 2 * hp + e;
-          const bool on = live && head < P.rep;
-          const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
-          float* row = row0 + static_cast<int64_t>(head) * P.L;
-          float x[4];
+      for (int e = 0; e < 2; ++e) {
+        const int head = 4 * hh + 2 * hp + e;
+        const bool on = live && head < P.rep;
+        const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
+        float* row = row0 + static_cast<int64_t>(head) * P.L;
+        float x[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float v = r ? acc[i][2 + e] : acc[i][e];
-            const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
-            x[i] = on ? fmaf(v, P.scale * unscale, zqs) : -INFINITY;
-            if (on) row[pos[i]] = x[i];
-          }
-          softmax_push4(m[hh][e], l[hh][e], x);
+        for (int i = 0; i < 4; ++i) {
+          const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
+          x[i] = on ? fmaf(val[i][e], P.scale * unscale, zqs) : -INFINITY;
+          if (on) row[pos[i]] = x[i];
         }
+        softmax_push4(m[hh][e], l[hh][e], x);
       }
     }
   }
