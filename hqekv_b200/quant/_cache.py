@@ -108,14 +108,17 @@ def cached_cache_desc(cache, nh_q, block_size, group_size):
     entry) and only the residual fields are refreshed.  Tiers that are not contiguous take the
     uncached path.  Returns (desc, keepalive, L, device)."""
     tiers = cache[:36]
-    if all(t is None for t in tiers) or any(t is not None and not t.is_contiguous() for t in tiers):
-        return build_cache_desc(cache, nh_q, block_size, group_size)
-    key = (nh_q, block_size, group_size) + tuple(id(t) for t in tiers)
+    key = (nh_q, block_size, group_size) + tuple(map(id, tiers))
     ent = _desc_memo.get(key)
-    if ent is not None and any(r() is None for r in ent.refs):
-        ent = None
+    if ent is not None:
+        for r in ent.refs:
+            if r() is None:
+                ent = None
+                break
     nk, nv = cache[SLOT_NEW_K], cache[SLOT_NEW_V]
     if ent is None:
+        if all(t is None for t in tiers) or any(t is not None and not t.is_contiguous() for t in tiers):
+            return build_cache_desc(cache, nh_q, block_size, group_size)
         desc, _, L, dev = build_cache_desc(cache, nh_q, block_size, group_size)
         ent = _DescEntry()
         ent.desc, ent.dev = desc, dev

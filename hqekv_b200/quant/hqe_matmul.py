@@ -36,15 +36,23 @@ def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: tor
     B, nh_q, D = q.shape[0], q.shape[1], q.shape[3]
     attn_weights = torch.empty(B, nh_q, 1, L, dtype=torch.float16, device=dev)
     attn_output = torch.empty(B, nh_q, 1, D, dtype=torch.float16, device=dev)
-    with torch.cuda.device(dev):
-        need = lib.hqkv_decode_workspace_bytes(desc)
-        if need == 0:
-            _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), None, 0,
-                                                         None))
-        ws = decode_workspace(dev, need)
-        _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), ptr(ws),
-                                                     ws.numel(), stream_ptr(dev)))
+    if dev.index is None or dev.index == torch.cuda.current_device():
+        _launch(desc, q, attn_weights, attn_output, dev)
+    else:
+        with torch.cuda.device(dev):
+            _launch(desc, q, attn_weights, attn_output, dev)
     return attn_weights, attn_output
+
+
+def _launch(desc, q, attn_weights, attn_output, dev):
+    need = lib.hqkv_decode_workspace_bytes(desc)
+    if need == 0:
+        _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), None, 0, None))
+    ws = decode_workspace(dev, need)
+    rc = lib.hqkv_decode_attention(desc, q.data_ptr(), attn_weights.data_ptr(), attn_output.data_ptr(), ws.data_ptr(),
+                                   ws.numel(), stream_ptr(dev))
+    if rc:
+        _raise_from_status(rc)
 
 
 def _raise_from_status(rc):
