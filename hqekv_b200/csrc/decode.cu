@@ -322,19 +322,21 @@ constexpr float LOG2E = 1.4426950408889634f;
 
 template <int BITS>
 struct KTile {
-  static constexpr int PITCH = BITS == 2 ? 32 : 64;       // bytes per channel row
-  static constexpr int TOKENS = PITCH * 8 / BITS;         // 64, 128, 128
-  static constexpr int NSUB = TOKENS / K_SPAN;            // sub-spans: 1, 2, 2
-  static constexpr int TPC = 128 / BITS;                  // tokens per 16-byte piece: 16, 32, 64
-  static constexpr int CPS = K_SPAN / TPC;                // pieces of a row per sub-span: 4, 2, 1
+  static constexpr int PITCH = BITS == 1 ? 16 : BITS == 2 ? 32 : 64;  // bytes per channel row
+  static constexpr int TOKENS = PITCH * 8 / BITS;         // 64, 128, 128, 128 at 8, 4, 2, 1 bits
+  static constexpr int NSUB = TOKENS / K_SPAN;            // sub-spans: 1, 2, 2, 2
+  static constexpr int TPC = 128 / BITS;                  // tokens per 16-byte piece: 16, 32, 64, 128
+  static constexpr int CPS = BITS == 1 ? 1 : K_SPAN / TPC;  // pieces of a row per sub-span: 4, 2, 1 (1 bit: half a piece)
   // byte offset of 16-byte piece c of a channel row.  The piece index is XORed with row bits so that
   // the eight rows of an ldmatrix (same logical piece) and the pieces a cp.async instruction writes
   // both spread over all banks.
   static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
     if constexpr (PITCH == 64) {
       return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
-    } else {
+    } else if constexpr (PITCH == 32) {
       return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    } else {
+      return row * 16u;  // 1 bit: read with 2-byte loads, see k_tile_compute
     }
   }
 };
@@ -424,7 +426,20 @@ __device__ __forceinline__ void k_tile_request(const TierDev& T, KWarpShared& ws
   const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
   const unsigned char* src = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes +
                              static_cast<int64_t>(tile_t0) * BITS / 8;
-  const int valid_bytes = ntok * BITS / 8;  // per row: a multiple of 8
+  const int valid_bytes = ntok * BITS / 8;  // per row: a multiple of 8 (of 4 at 1 bit)
+  if constexpr (BITS == 1) {
+    // 16 bytes per row at 4-byte alignment: four 4-byte pieces; a copy instruction moves 8 rows
+#pragma unroll
+    for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = quarter * 32 + i * 8 + (lane >> 2), c4 = 4 * (lane & 3);
+        if (c4 < valid_bytes) cp_async_4(ws.u.codes + row * 16 + c4, src + row * row_bytes + c4);
+      }
+      cp_async_commit();
+    }
+    return;
+  }
   // a copy instruction moves 8 rows x 64 bytes (16 rows x 32 bytes at 2 bits)
   constexpr int LPR = BITS == 2 ? 2 : 4;    // lanes per row
   constexpr int RPI = 32 / LPR;             // rows per instruction
@@ -483,9 +498,14 @@ __device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, 
 //           Tokens: row g = 4g + i, row g+8 = 32 + 4g + i.
 //   2 bits: block = 8 tokens, one piece.  M-tile i: row g <- token i, row g+8 <- token 4+i of block g.
 //           Tokens: row g = 8g + i, row g+8 = 8g + 4 + i.
+//   1 bit:  block = 16 tokens, four blocks per sub-span (no ldmatrix: lane g reads block g & 3 with a
+//           2-byte load).  M-tile i: row g <- token 4*(g>>2) + i, row g+8 <- token 8 + 4*(g>>2) + i of
+//           block g & 3.  Tokens: row g = 16*(g&3) + 4*(g>>2) + i, row g+8 = +8.
 template <int BITS>
 struct KField {
-  static __host__ __device__ constexpr int shift(int i) { return BITS == 8 ? 0 : BITS == 4 ? 4 * (i & 1) : 2 * i; }
+  static __host__ __device__ constexpr int shift(int i) {
+    return BITS == 8 ? 0 : BITS == 4 ? 4 * (i & 1) : BITS == 2 ? 2 * i : i;
+  }
 };
 template <int BITS>
 __device__ __forceinline__ void octet_frags(const uint32_t* R, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
@@ -549,8 +569,10 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       lm_off = TL::offset(rr, mi);                           // octet 0; pieces 0..3
     } else if constexpr (BITS == 4) {
       lm_off = TL::offset(8 * (mi >> 1) + rr, mi & 1);       // (octet 0, piece 0), (0,1), (1,0), (1,1)
-    } else {
+    } else if constexpr (BITS == 2) {
       lm_off = TL::offset(8 * mi + rr, 0);                   // steps kt, kt+1: octets 0..3 of 32 channels
+    } else {
+      lm_off = (2 * tig) * 16 + 2 * (g & 3);                 // 1 bit: this lane's block of channel 2*tig
     }
   }
   const int hp = tig & 1;
@@ -565,7 +587,7 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       const int gam = ((tile_t0 + j * K_SPAN + 32 * (g >> 2)) >> P.gk_shift) - g0c;
       const __half* s_even = &sh.s[2 * tig][sh_even + gam];
       const __half* s_odd = &sh.s[2 * tig + 1][sh_odd + gam];
-      const unsigned char* kb = ws.u.codes + (lm_off ^ (j * TL::CPS * 16));
+      const unsigned char* kb = ws.u.codes + (BITS == 1 ? lm_off + j * 8 : (lm_off ^ (j * TL::CPS * 16)));
       const uint2* qk = qb;
       float acc[4][4];
 #pragma unroll
@@ -583,6 +605,7 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
         }
         uint32_t R2[4];  // 2 bits: one ldmatrix feeds both steps
         if constexpr (BITS == 2) ldmatrix_x4_trans(R2, kb);
+        (void)R2;
 #pragma unroll
         for (int k2 = 0; k2 < 2; ++k2) {
           // A fragments: lo/hi of octet 0 -> registers 0/1 (channels 2tig, 2tig+1), of octet 1 -> 2/3 (+8)
@@ -598,9 +621,21 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
             ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH);
             octet_frags<4>(R, a[0], a[1]);
             octet_frags<4>(R + 2, a[2], a[3]);
-          } else {
+          } else if constexpr (BITS == 2) {
             octet_frags<2>(R2 + 2 * k2, a[0], a[1]);
             octet_frags<2>(R2 + 2 * k2 + 1, a[2], a[3]);
+          } else {
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {  // channels 2tig, 2tig+1 (o = 0) and +8, +9 (o = 1)
+              const unsigned char* cb = kb + (k2 * 16 + o * 8) * 16;
+              const uint32_t t = pack_lo16(*reinterpret_cast<const uint16_t*>(cb), *reinterpret_cast<const uint16_t*>(cb + 16));
+              const uint32_t lo = t >> (4 * (g >> 2)), hi = lo >> 8;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                a[2 * o][i] = lo & (0x00010001u << i);
+                a[2 * o + 1][i] = hi & (0x00010001u << i);
+              }
+            }
           }
           const int o = (16 * k2) * K_RAW_HALFS;
           const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
@@ -629,6 +664,7 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       //  2 bits:     rows g and g+8 are the eight tokens of block g, valid in the lanes with
       //              (g < 4) == (tig < 2); such a lane keeps the row of its tig half and hands the
       //              other row to lane tig ^ 2, whose own accumulators belong to the wrong scale group.
+      //  1 bit:      the same with block g & 3: valid where ((g & 3) < 2) == (tig < 2).
       const int sub_t0 = j * K_SPAN;
       const int r = tig >> 1;
       float val[4][2];
@@ -636,8 +672,8 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       for (int i = 0; i < 4; ++i)
 #pragma unroll
         for (int e = 0; e < 2; ++e) val[i][e] = r ? acc[i][2 + e] : acc[i][e];
-      if constexpr (BITS == 2) {
-        const bool valid = (g < 4) == (tig < 2);
+      if constexpr (BITS <= 2) {
+        const bool valid = BITS == 2 ? (g < 4) == (tig < 2) : ((g & 3) < 2) == (tig < 2);
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -647,7 +683,8 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
           }
       }
       // first of this lane's tokens (8 bits: tokens my_tok, +1, +16, +17; 4 and 2 bits: my_tok .. my_tok+3)
-      const int my_tok = sub_t0 + (BITS == 8 ? 32 * r + 2 * g : BITS == 4 ? 32 * r + 4 * g : 8 * g + 4 * r);
+      const int my_tok = sub_t0 + (BITS == 8 ? 32 * r + 2 * g : BITS == 4 ? 32 * r + 4 * g : BITS == 2 ? 8 * g + 4 * r
+                                                                : 16 * (g & 3) + 4 * (g >> 2) + 8 * r);
       const bool live = my_tok < ntok;
       const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
       uint32_t pos[4];
@@ -911,8 +948,10 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
     k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
   } else if (T.bits == 4) {
     k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
-  } else {
+  } else if (T.bits == 2) {
     k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
+  } else {
+    k_chunk<1>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
   }
 
   // the output accumulators of this (batch, kv head) start from zero in every call (the V pass, which
@@ -957,17 +996,19 @@ constexpr int V_PROW = V_MAX_TT + 8;          // halfs per staged probability ro
 
 template <int BITS>
 struct VTile {
-  static constexpr int PITCH = 16 * BITS;                  // bytes per token row: 128, 64, 32
+  static constexpr int PITCH = 16 * BITS;                  // bytes per token row: 128, 64, 32, 16
   static constexpr int TOKENS = BITS == 8 ? 64 : 128;
   static constexpr int STEPS = TOKENS / 16;
-  static constexpr int NPIECE = PITCH / 16;                // 16-byte pieces per row: 8, 4, 2
+  static constexpr int NPIECE = PITCH / 16;                // 16-byte pieces per row: 8, 4, 2, 1
   static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
     if constexpr (PITCH == 128) {
       return row * 128u + ((c ^ (row & 7u)) << 4);
     } else if constexpr (PITCH == 64) {
       return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
-    } else {
+    } else if constexpr (PITCH == 32) {
       return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    } else {
+      return row * 16u;  // 1 bit: read with 2-byte loads
     }
   }
 };
@@ -1005,7 +1046,9 @@ struct VShared {
 template <int BITS>
 struct VField {
   static constexpr int N = BITS == 8 ? 2 : 4;  // fields taken from one register per fragment row
-  static __host__ __device__ constexpr int shift(int f) { return BITS == 8 ? 0 : BITS == 4 ? 4 * (f & 1) : 2 * f; }
+  static __host__ __device__ constexpr int shift(int f) {
+    return BITS == 8 ? 0 : BITS == 4 ? 4 * (f & 1) : BITS == 2 ? 2 * f : f;
+  }
 };
 template <int BITS>
 __device__ __forceinline__ uint32_t v_field(uint32_t r, uint32_t r_shr8, int f) {
@@ -1046,8 +1089,8 @@ __device__ __forceinline__ void v_tile_request(const TierDev& T, VWarpShared& ws
   }
   cp_async_commit();
   const unsigned char* src = reinterpret_cast<const unsigned char*>(T.v_data) + tok0 * TL::PITCH;
-  constexpr int PIECES = TL::TOKENS * TL::NPIECE;  // 512 (256 at 2 bits)
-  constexpr int PER_Q = PIECES / 4 / 32;           // copies per lane and quarter: 4 (2)
+  constexpr int PIECES = TL::TOKENS * TL::NPIECE;  // 512 (256 at 2 bits, 128 at 1 bit)
+  constexpr int PER_Q = PIECES / 4 / 32;           // copies per lane and quarter: 4 (2, 1)
 #pragma unroll
   for (int quarter = 0; quarter < 4; ++quarter) {
 #pragma unroll
@@ -1155,7 +1198,23 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
       mma16816(zacc, a0, 0u, a2, 0u, p0, p1);
     }
     const unsigned char* rowp = ws.u.codes;
-    if constexpr (BITS == 2) {
+    if constexpr (BITS == 1) {
+      // block = 16 channels, four blocks per 64-channel half c; lane g reads block 4c + (g & 3) of tokens
+      // 2tig, 2tig+1 (+8, +9) with 2-byte loads; rows g / g+8 of M-tile f are channels 4*(g>>2) + f and +8
+      const unsigned char* tb = rowp + (t0 + 2 * tig) * 16 + 2 * (g & 3);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t r0 = pack_lo16(*reinterpret_cast<const uint16_t*>(tb + 8 * c), *reinterpret_cast<const uint16_t*>(tb + 8 * c + 16));
+        const uint32_t r1 = pack_lo16(*reinterpret_cast<const uint16_t*>(tb + 8 * c + 128), *reinterpret_cast<const uint16_t*>(tb + 8 * c + 144));
+        const uint32_t lo0 = r0 >> (4 * (g >> 2)), hi0 = lo0 >> 8, lo1 = r1 >> (4 * (g >> 2)), hi1 = lo1 >> 8;
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint32_t msk = 0x00010001u << f;
+          mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bh_[c][0], bh_[c][1]);
+          mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bl_[c][0], bl_[c][1]);
+        }
+      }
+    } else if constexpr (BITS == 2) {
       uint32_t R[4];
       ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, mi & 1));
 #pragma unroll
@@ -1210,6 +1269,8 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
 // M-tile -> channels:  8 bits  mt = 4q + 2u + f : row g = 64q + 16u + 2g + f,  row g+8 = +32
 //                      4 bits  mt = 4pp + f     : row g = 64pp + 4g + f,        row g+8 = +32
 //                      2 bits  mt = 4c + f      : row g = 64c + 8g + f,         row g+8 = +4
+//                      1 bit   mt = 4c + f      : row g = 64c + 16(g&3) + 4(g>>2) + f, row g+8 = +8
+//                              (owned by the lanes with ((g & 3) < 2) == (tig < 2))
 template <int BITS>
 __device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)[8][4]) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
@@ -1218,13 +1279,15 @@ __device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)
   for (int mt = 0; mt < 8; ++mt) {
     const int f = BITS == 8 ? (mt & 1) : (mt & 3);
     const float unscale = static_cast<float>(1 << (24 - VField<BITS>::shift(f)));
-    if constexpr (BITS == 2) {
-      if ((g < 4) == (tig < 2)) {
-        const int ch = 64 * (mt >> 2) + 8 * g + f;
+    if constexpr (BITS <= 2) {
+      const bool mine = BITS == 2 ? (g < 4) == (tig < 2) : ((g & 3) < 2) == (tig < 2);
+      if (mine) {
+        const int ch = 64 * (mt >> 2) + (BITS == 2 ? 8 * g : 16 * (g & 3) + 4 * (g >> 2)) + f;
+        constexpr int UP = BITS == 2 ? 4 : 8;  // channel distance of row g+8
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           red[2 * hp + e][ch] = acc[mt][e] * unscale;
-          red[2 * hp + e][ch + 4] = acc[mt][2 + e] * unscale;
+          red[2 * hp + e][ch + UP] = acc[mt][2 + e] * unscale;
         }
       }
     } else {
@@ -1340,6 +1403,7 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
     if (vb == 8) v_tile_request<8>(T, ws, bh, tile_t0, ntok, ng);
     else if (vb == 4) v_tile_request<4>(T, ws, bh, tile_t0, ntok, ng);
     else if (vb == 2) v_tile_request<2>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 1) v_tile_request<1>(T, ws, bh, tile_t0, ntok, ng);
   }
   TL_STAMP(2);
   asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -1387,7 +1451,8 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
   if (ntok > 0 && vb != 16) {
     if (vb == 8) v_tile<8>(P, T, sh, ws, b, kvh, ntok, nh);
     else if (vb == 4) v_tile<4>(P, T, sh, ws, b, kvh, ntok, nh);
-    else v_tile<2>(P, T, sh, ws, b, kvh, ntok, nh);
+    else if (vb == 2) v_tile<2>(P, T, sh, ws, b, kvh, ntok, nh);
+    else v_tile<1>(P, T, sh, ws, b, kvh, ntok, nh);
   } else {
     if (ntok > 0) {
       v_plain_tile(P, T, sh, ws, bh, b, kvh, tile_t0, ntok, is_res);
@@ -1507,7 +1572,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.n_v = s.n_v;
     if (s.n_k > 0 || s.n_v > 0) {
       HQKV_REQUIRE(s.bits == expect_bits[t], "decode: tier %d must hold %d-bit data (got %d)", t, expect_bits[t], s.bits);
-      if (s.bits == 1) return fail(HQKV_E_UNSUPPORTED, "decode: the 1-bit tier is not built in the fused decode");
     }
     if (s.n_k > 0) {
       HQKV_REQUIRE(s.k_data && s.k_idx, "decode: tier %d K pointers are null", t);

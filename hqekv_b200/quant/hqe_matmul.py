@@ -20,12 +20,16 @@ def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: tor
     ``head_dim`` is re-derived from the cache as the reference does (:379-404).
     Returns (attn_weights [B, nh_q, 1, L] float16, attn_output [B, nh_q, 1, D] float16).
     Raises ValueError('invalid quant_strategy') / ValueError('invalid past_key_value') like the
-    reference.  A non-empty 1-bit tier raises NotImplementedError (not built).
+    reference.  All five tiers are uniform-group tiers here (the Gaussian-codebook 1-bit codec is not built).
     """
     if quant_strategy not in UNIFORM_STRATEGIES:
         raise ValueError("invalid quant_strategy")
     if len(past_key_value) != 42:
         raise ValueError("invalid past_key_value")
+    if quant_strategy != "uniform_group" and (past_key_value[28] is not None or past_key_value[32] is not None):
+        # under 'high_uniform_group_low_normal_group' the 1-bit slots hold (std, mean) of the Gaussian codebook
+        raise NotImplementedError("qkv_matmul_hqe_2: the Gaussian-codebook 1-bit tier of "
+                                  f"quant_strategy '{quant_strategy}' is not built; 'uniform_group' reads all tiers")
     require_cuda(q)
     if q.dtype != torch.float16 or q.dim() != 4 or q.shape[2] != 1:
         raise ValueError("q must be float16 of shape [B, nh_q, 1, head_dim]")

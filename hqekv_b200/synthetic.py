@@ -49,9 +49,10 @@ def tier_counts(cfg: CacheConfig):
     nblocks = flushed // block
     ev = int(round(nblocks * cfg.evict))
     keep = nblocks - ev
-    raw = torch.tensor([0, round(keep * cfg.ratios[0]), round(keep * cfg.ratios[1]), round(keep * cfg.ratios[2]), 0],
+    one = round(keep * cfg.ratios[3]) if len(cfg.ratios) > 3 else 0  # optional uniform 1-bit share
+    raw = torch.tensor([0, round(keep * cfg.ratios[0]), round(keep * cfg.ratios[1]), round(keep * cfg.ratios[2]), one],
                        dtype=torch.int32)
-    raw = make_sum_equal(raw, keep, start_idx=3)
+    raw = make_sum_equal(raw, keep, start_idx=4 if one else 3)
     counts = [int(v) * block for v in raw.tolist()] + [ev * block]
     assert sum(counts) == flushed
     return counts

@@ -28,7 +28,7 @@ extern "C" {
 
 #define HQKV_OK 0
 #define HQKV_E_INVALID (-1)     /* bad argument (shape, bits, group size, alignment, null pointer) */
-#define HQKV_E_UNSUPPORTED (-2) /* valid in the reference but not built here (e.g. 1-bit tier in the fused decode) */
+#define HQKV_E_UNSUPPORTED (-2) /* valid in the reference but not built here (e.g. the Gaussian-codebook codec) */
 #define HQKV_E_WORKSPACE (-3)   /* scratch buffer too small */
 #define HQKV_E_CUDA (-4)        /* a CUDA runtime call failed */
 
@@ -133,7 +133,7 @@ size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
  *                first call; every call leaves them zero again.  Calls that share a workspace
  *                must be ordered on one stream.
  * The K-side and V-side token counts of a tier may differ only in order, not in total
- * (sum n_k == sum n_v); the 1-bit tier is not built (HQKV_E_UNSUPPORTED if non-empty).
+ * (sum n_k == sum n_v).  The 1-bit tier is read as a uniform tier (code * scale + zero), like the others.
  */
 #define HQKV_WS_COUNTER_BYTES 4096
 int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,

@@ -54,7 +54,8 @@ def test_argument_validation_needs_no_gpu(lib):
     assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -1
     assert b"empty" in L.hqkv_last_error()
     desc.tier[4].bits, desc.tier[4].n_k, desc.tier[4].n_v = 1, 32, 32
-    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -2      # 1-bit tier: not built
+    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -1      # 1-bit tier: null pointers
+    assert b"pointers are null" in L.hqkv_last_error()
 
 
 def test_workspace_size_of_the_benchmark_cache(lib):

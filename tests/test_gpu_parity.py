@@ -249,18 +249,14 @@ def check_attention(ops, cache_t, q, block, group, what):
 
 @pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
 def test_decode_on_golden_caches(ops, cuda_device, name):
-    """Every flush step of the fixtures gives a cache with a different set of present/absent tiers,
-    K and V ranked differently (flush_a/c), batch 2 (flush_b), group 64 (flush_c)."""
+    """Every flush step of the fixtures gives a cache with a different set of present/absent tiers (the
+    uniform 1-bit tier included), K and V ranked differently (flush_a/c), batch 2 (flush_b), group 64
+    (flush_c)."""
     z = load_golden(name)
     B, H, D, block, group, _, nsteps = (int(v) for v in z["meta"])
     gen = torch.Generator(device=cuda_device).manual_seed(1)
     for s in range(nsteps):
         cache_np = golden_cache(z, f"s{s}_out")
-        if any(cache_np[i] is not None for i in (28, 32)):  # drop 1-bit tier tokens: not built in the decode
-            with pytest.raises(NotImplementedError):
-                q = torch.randn(B, 4 * H, 1, D, generator=gen, device=cuda_device).half()
-                ops.hm.qkv_matmul_hqe_2(q, dev_cache(cache_np, cuda_device), None, D, "uniform_group", block, group)
-            continue
         for rep in (1, 4, 8):
             q = torch.randn(B, rep * H, 1, D, generator=gen, device=cuda_device).half()
             check_attention(ops, dev_cache(cache_np, cuda_device), q, block, group, f"{name} step {s} rep {rep}")
@@ -352,11 +348,12 @@ def test_gemv_uniform_group_vs_oracle(ops, cuda_device, bits):
 # ---------------------------------------------------------------------------------------------
 # sweep: uniform and mixed tiers x group size x batch x GQA ratio (shapes of the kernel microbench)
 # ---------------------------------------------------------------------------------------------
-SWEEP_RATIOS = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "mixed": (0.25, 0.5, 0.25)}
+SWEEP_RATIOS = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "mixed": (0.25, 0.5, 0.25),
+                "all1": (0.0, 0.0, 0.0, 1.0), "mixed1": (0.25, 0.25, 0.25, 0.25)}
 
 
 @pytest.mark.parametrize("group", [32, 64, 128])
-@pytest.mark.parametrize("tiers", ["all8", "all4", "all2", "mixed"])
+@pytest.mark.parametrize("tiers", ["all8", "all4", "all2", "mixed", "all1", "mixed1"])
 def test_decode_sweep_vs_oracle(ops, cuda_device, tiers, group):
     """Context 1024 + a ragged residual, batch 1 and 3, GQA 4 and 8, K with outlier channels, K and V
     ranked differently (times_range): the fused decode against the fp32 oracle, tolerance 2e-3."""
