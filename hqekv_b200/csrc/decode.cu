@@ -21,6 +21,10 @@
 
 #include "common.cuh"
 
+#define HQKV_STR2(x) #x
+#define HQKV_STR(x) HQKV_STR2(x)
+#define HQKV_UNROLL(n) _Pragma(HQKV_STR(unroll n))
+
 namespace hqkv {
 
 constexpr int D = 128;           // head dim
@@ -309,6 +313,9 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
 #ifndef K_MIN_CTAS
 #define K_MIN_CTAS 4
 #endif
+#ifndef K_KK_UNROLL
+#define K_KK_UNROLL 1  // iterations of the two-step loop unrolled together
+#endif
 constexpr int KWARPS = 4;
 constexpr int KTHREADS = KWARPS * 32;
 constexpr int K_SPAN = 64;                   // tokens per sub-span: four M-tiles of 16
@@ -594,7 +601,7 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
       // two 16-channel steps per iteration (short loop body: the instruction cache is cold in every CTA
       // when the whole cache is one wave of CTAs)
-#pragma unroll 1
+HQKV_UNROLL(K_KK_UNROLL)
       for (int kk = 0; kk < 4; ++kk) {
         if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
           if (kk == 0) cp_async_wait<3>();
@@ -646,11 +653,11 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
           const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
           const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
           const __half2 lo1 = __hfma2(u32_as_h2(qv.y), s1, __hneg2(hi1));
+          // the two MMAs into one accumulator are issued four apart (they depend on each other)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
-            mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
-          }
+          for (int i = 0; i < 4; ++i) mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
         }
         kb += 32 * TL::PITCH;
         s_even += 32 * K_RAW_HALFS;
@@ -781,9 +788,6 @@ __device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T,
   float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   if (ntok > 0) {
     float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * P.L;
-#ifdef HQKV_X_NOKCOMPUTE
-    if (P.L < 0)
-#endif
     k_tile_compute<BITS>(P, T, sh, ws, tile_t0, ntok, g0c, nh, row0, m, l);
   }
   // the warp's (max, sum-exp) per head: lanes that share tig & 1 hold pairs of the same two heads
@@ -989,6 +993,9 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 #ifndef V_MIN_CTAS
 #define V_MIN_CTAS 4
 #endif
+#ifndef V_STEP_UNROLL
+#define V_STEP_UNROLL 1  // 16-token steps unrolled together
+#endif
 constexpr int VWARPS = 4;
 constexpr int VTHREADS = VWARPS * 32;
 constexpr int V_MAX_TT = 128;                 // tokens per tile at most
@@ -1136,9 +1143,7 @@ __device__ __forceinline__ void v_tile_probs(const DecodeParams& P, const VShare
       const int t = lane + 32 * j;
       const float e = on ? fast_exp2(fmaf(x[hh][j], LOG2E, -mh)) : 0.f;  // exp2(-inf) = 0 beyond the tile
       prow[hh][t] = __float2half_rn(e);
-#ifndef HQKV_X_NOWEIGHTS
       if (on && t < ntok) wrow[pos[j]] = __float2half_rn(e * inv);
-#endif
     }
   }
 }
@@ -1167,12 +1172,8 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   zacc[0] = zacc[1] = zacc[2] = zacc[3] = 0.f;
 
-#ifdef HQKV_X_NOWALK
-  const int nsteps = P.L < 0 ? 1 : 0;
-#else
   const int nsteps = ntok >> 4;
-#endif
-#pragma unroll 1
+HQKV_UNROLL(V_STEP_UNROLL)
   for (int st = 0; st < nsteps; ++st) {
     const int t0 = st * 16;
     // B operands: p pairs of tokens (2tig, 2tig+1) and (+8, +9); scales of the same tokens
@@ -1211,6 +1212,10 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
         for (int f = 0; f < 4; ++f) {
           const uint32_t msk = 0x00010001u << f;
           mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bh_[c][0], bh_[c][1]);
+        }
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint32_t msk = 0x00010001u << f;
           mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bl_[c][0], bl_[c][1]);
         }
       }
@@ -1220,13 +1225,16 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         const uint32_t lo0 = R[c], hi0 = R[c] >> 8, lo1 = R[2 + c], hi1 = R[2 + c] >> 8;
+        uint32_t fa[4][4];
 #pragma unroll
         for (int f = 0; f < 4; ++f) {
-          const uint32_t a0 = v_field<2>(lo0, 0u, f), a1 = v_field<2>(hi0, 0u, f);
-          const uint32_t a2 = v_field<2>(lo1, 0u, f), a3 = v_field<2>(hi1, 0u, f);
-          mma16816(acc[4 * c + f], a0, a1, a2, a3, bh_[c][0], bh_[c][1]);
-          mma16816(acc[4 * c + f], a0, a1, a2, a3, bl_[c][0], bl_[c][1]);
+          fa[f][0] = v_field<2>(lo0, 0u, f), fa[f][1] = v_field<2>(hi0, 0u, f);
+          fa[f][2] = v_field<2>(lo1, 0u, f), fa[f][3] = v_field<2>(hi1, 0u, f);
         }
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * c + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[c][0], bh_[c][1]);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * c + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[c][0], bl_[c][1]);
       }
     } else if constexpr (BITS == 4) {
 #pragma unroll
@@ -1235,13 +1243,15 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
         ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 2 * pp + (mi & 1)));
 #pragma unroll
         for (int k = 0; k < 4; ++k) S[k] = R[k] >> 8;
+        uint32_t fa[4][4];
 #pragma unroll
-        for (int f = 0; f < 4; ++f) {
-          mma16816(acc[4 * pp + f], v_field<4>(R[0], S[0], f), v_field<4>(R[1], S[1], f), v_field<4>(R[2], S[2], f),
-                   v_field<4>(R[3], S[3], f), bh_[pp][0], bh_[pp][1]);
-          mma16816(acc[4 * pp + f], v_field<4>(R[0], S[0], f), v_field<4>(R[1], S[1], f), v_field<4>(R[2], S[2], f),
-                   v_field<4>(R[3], S[3], f), bl_[pp][0], bl_[pp][1]);
-        }
+        for (int f = 0; f < 4; ++f)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) fa[f][k] = v_field<4>(R[k], S[k], f);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * pp + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[pp][0], bh_[pp][1]);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * pp + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[pp][0], bl_[pp][1]);
       }
     } else {
 #pragma unroll
@@ -1250,13 +1260,15 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
         for (int u = 0; u < 2; ++u) {
           uint32_t R[4];
           ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 4 * q + u + 2 * (mi & 1)));
+          uint32_t fa[2][4];
 #pragma unroll
-          for (int f = 0; f < 2; ++f) {
-            const uint32_t a0 = v_field<8>(R[0], 0u, f), a1 = v_field<8>(R[1], 0u, f);
-            const uint32_t a2 = v_field<8>(R[2], 0u, f), a3 = v_field<8>(R[3], 0u, f);
-            mma16816(acc[4 * q + 2 * u + f], a0, a1, a2, a3, bh_[q][0], bh_[q][1]);
-            mma16816(acc[4 * q + 2 * u + f], a0, a1, a2, a3, bl_[q][0], bl_[q][1]);
-          }
+          for (int f = 0; f < 2; ++f)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) fa[f][k] = v_field<8>(R[k], 0u, f);
+#pragma unroll
+          for (int f = 0; f < 2; ++f) mma16816(acc[4 * q + 2 * u + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[q][0], bh_[q][1]);
+#pragma unroll
+          for (int f = 0; f < 2; ++f) mma16816(acc[4 * q + 2 * u + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[q][0], bl_[q][1]);
         }
     }
   }
@@ -1495,9 +1507,6 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
   }
   __syncthreads();
   TL_STAMP(6);
-#ifdef HQKV_X_NOMERGE
-  if (P.L > 0) return;
-#endif
   if (sh.is_last) {
     __threadfence();
     double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
