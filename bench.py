@@ -46,6 +46,9 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--peer-gather", action="store_true",
+                    help="multi-GPU: the decode kernel stores its rows into the peers' buffers (symmetric memory) "
+                         "instead of an NCCL all-gather per layer")
     return ap.parse_args()
 
 
@@ -237,14 +240,41 @@ def main():
     gathered = [torch.empty(world, cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
                 for _ in range(layers)] if world > 1 else None
 
+    # Multi-GPU exchange of the per-head outputs: NCCL all-gather per layer, or (--peer-gather) the decode
+    # kernel stores its rows into every peer's gathered buffer and runs a bounded cross-GPU barrier
+    # (sharding.PeerGather; falls back to NCCL when symmetric memory is not available or the two disagree
+    # on the first layer).  Measured at batch 1: NCCL is faster at N=2.
+    peer = None
+    if world > 1 and args.peer_gather:
+        try:
+            from hqekv_b200.sharding import PeerGather
+            peer = PeerGather(layers, cfg.batch, nh_q_local, cfg.head_dim, dev)
+            _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+            dist.all_gather_into_tensor(gathered[0], o_ref)
+            _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group)
+            torch.cuda.synchronize()
+            ok = torch.tensor([int(torch.equal(got, gathered[0]) and peer.status() == 0)], device=dev)
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+            if int(ok.item()) != 1:
+                raise RuntimeError("peer-store gather differs from the NCCL all-gather")
+        except Exception as e:
+            if rank == 0:
+                print(f"[bench] peer-store gather unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
+            peer = None
+    if world > 1:
+        config["exchange"] = "peer stores from the decode kernel + bounded cross-GPU barrier" if peer else "nccl all_gather per layer"
+
+    def decode_layer(i, q):
+        if peer is not None:
+            w, g = peer.decode(i, q, caches[i], cfg.group, cfg.group)
+            return g[rank]
+        w, o = qkv_matmul_hqe_2(q, caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+        if world > 1:
+            dist.all_gather_into_tensor(gathered[i], o)
+        return o
+
     def step_device():
-        outs = []
-        for i in range(layers):
-            w, o = qkv_matmul_hqe_2(qs[i], caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[i], o)
-            outs.append(o)
-        return outs
+        return [decode_layer(i, qs[i]) for i in range(layers)]
 
     use_graph = not args.no_graph
     graph = None
@@ -295,6 +325,8 @@ def main():
     barrier()
     clocks = sampler.stop() if rank == 0 else None
     ms = ev0.elapsed_time(ev1)
+    if peer is not None and peer.status() != 0:
+        raise RuntimeError(f"rank {rank}: a cross-GPU barrier gave up waiting for rank {peer.status() - 1}")
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -312,10 +344,7 @@ def main():
         q_dev.copy_(q_host, non_blocking=True)
         outs = []
         for i in range(layers):
-            w, o = qkv_matmul_hqe_2(q_dev[i], caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
-            if world > 1:
-                dist.all_gather_into_tensor(gathered[i], o)
-            outs.append(o)
+            outs.append(decode_layer(i, q_dev[i]))
         out_host.copy_(torch.stack(outs), non_blocking=True)
 
     # The way a serving loop drives the operator: the step's host->device copies, the public call for

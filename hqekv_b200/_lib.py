@@ -57,6 +57,10 @@ _SIGNATURES = {
     "hqkv_decode_attention_phases": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                C.c_size_t, C.c_int, C.c_void_p]),
     "hqkv_decode_static_scratch_bytes": (C.c_size_t, []),
+    "hqkv_decode_attention_gather": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                               C.c_size_t, C.POINTER(C.c_void_p), C.c_int, C.POINTER(C.c_void_p), C.c_int,
+                                               C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
+    "hqkv_peer_barrier": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "hqkv_decode_attention_static": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hqkv_gemv_uniform_group": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int,
                                           C.c_int64, C.c_int64, C.c_int, C.c_int, C.c_void_p, C.c_void_p]),

@@ -61,6 +61,13 @@ struct DecodeParams {
   float* logits;   // [B*nh_q][L]
   float2* k_part;  // [B*H][nk_chunks][MAX_REP]
   double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K pass, summed into by the V pass
+  __half* peer_out[HQKV_MAX_PEERS];  // copies of `out` in other GPUs' memory (kv-head sharding), n_peers used
+  int n_peers;
+  // cross-GPU barrier run by the last CTA of the V pass (world == 0: none)
+  unsigned* pad[HQKV_MAX_PEERS + 1];  // the ranks' signal pads, own one included
+  int rank, world;
+  unsigned* peer_state;  // call number, status, finished (batch, kv head) count
+  long long max_spins;
   unsigned* counters;  // [B*H]
 };
 
@@ -1384,6 +1391,37 @@ __device__ __forceinline__ void v_plain_tile(const DecodeParams& P, const TierDe
     }
 }
 
+// Cross-GPU barrier of one call, run by up to `world` threads of one CTA: thread r tells peer r "my stores
+// of call number n are done" by raising a counter in the peer's signal pad, then waits until peer r has
+// told it the same.  The call number lives in device memory and is advanced here, so the launch can
+// sit in a CUDA graph that is replayed.  Every wait is bounded: after max_spins polls the thread gives
+// up, records which peer was missing in the status word and returns, so a rank that died cannot hang
+// the others' GPUs (the step's gathered data is then incomplete; the host checks the status).
+template <bool FENCE_FIRST>
+__device__ __forceinline__ void peer_barrier_device(unsigned* const* pad, int rank, int world, unsigned* call_no,
+                                                    int* status, long long max_spins, unsigned* shared_n) {
+  const int r = threadIdx.x;
+  if (r == 0) *shared_n = *call_no + 1u;
+  __syncthreads();
+  const unsigned n = *shared_n;
+  if (r < world && r != rank) {
+    if (FENCE_FIRST) __threadfence_system();  // this GPU's earlier peer stores first (the V pass has fenced them already)
+    atomicAdd_system(pad[r] + rank, 1u);      // slot `rank` of peer r's pad counts my arrivals
+    volatile unsigned* mine = pad[rank] + r;  // slot r of my pad counts peer r's arrivals
+    long long spins = 0;
+    while (static_cast<int>(*mine - n) < 0) {
+      if (++spins > max_spins) {
+        atomicExch(status, r + 1);  // gave up waiting for peer r
+        break;
+      }
+      __nanosleep(20);
+    }
+    __threadfence_system();
+  }
+  __syncthreads();
+  if (r == 0) *call_no = n;
+}
+
 __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
@@ -1513,10 +1551,33 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
     for (int i = tid * 2; i < rep * D; i += VTHREADS * 2) {
       const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + i));
       const float inv = 1.f / sh.gl[i >> 7];
-      *reinterpret_cast<__half2*>(P.out + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i) =
-          __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
+      const __half2 o = __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
+      const int64_t at = (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i;
+      *reinterpret_cast<__half2*>(P.out + at) = o;
+      // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
+      // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
+      for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
     }
     TL_STAMP(7);
+    if (P.world > 1) {
+      // the CTA that finishes the last (batch, kv head) of this GPU runs the cross-GPU barrier: when this
+      // kernel completes, every rank's rows are in this GPU's gathered buffer
+      __threadfence_system();
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned done = atomicAdd(P.peer_state + 2, 1u);
+        sh.is_last = (done == static_cast<unsigned>(P.B * P.H) - 1u) ? 1u : 0u;
+        if (sh.is_last) P.peer_state[2] = 0u;
+      }
+      __syncthreads();
+      if (sh.is_last) {
+        __threadfence();
+        // every CTA fenced its peer stores system-wide before it counted itself in, and this CTA saw the
+        // full count: the signal may go out at once
+        peer_barrier_device<false>(P.pad, P.rank, P.world, P.peer_state, reinterpret_cast<int*>(P.peer_state + 1),
+                                   P.max_spins, &sh.pad_[0]);
+      }
+    }
   }
   TL_FLUSH(2);
 }
@@ -1668,14 +1729,66 @@ extern "C" size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_hos
   return lay.total;
 }
 
+namespace hqkv {
+struct PeerArgs {
+  void* const* out = nullptr;   // where this rank's block starts in each peer's gathered buffer
+  int n_peers = 0;
+  void* const* pads = nullptr;  // signal pads of all ranks (own one included); null: no barrier
+  int rank = 0, world = 0;
+  void* state = nullptr;
+  long long max_spins = 0;
+};
+static int decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
+                         void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream);
+}
+
 extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
                                             void* attn_output, void* workspace, size_t workspace_bytes, int phases,
                                             void* stream) {
+  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, phases, hqkv::PeerArgs(), stream);
+}
+
+extern "C" int hqkv_decode_attention_gather(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                            void* attn_output, void* workspace, size_t workspace_bytes,
+                                            void* const* peer_outputs_host, int n_peers, void* const* peer_pads_host,
+                                            int rank, int world, void* state, long long max_spins, void* stream) {
+  HQKV_REQUIRE(n_peers >= 0 && n_peers <= HQKV_MAX_PEERS, "decode_gather: at most %d peers (got %d)", HQKV_MAX_PEERS, n_peers);
+  HQKV_REQUIRE(n_peers == 0 || peer_outputs_host, "decode_gather: null peer list");
+  for (int p = 0; p < n_peers; ++p)
+    HQKV_REQUIRE(peer_outputs_host[p] && aligned(peer_outputs_host[p], 4), "decode_gather: peer output %d is null or misaligned", p);
+  hqkv::PeerArgs pa;
+  pa.out = peer_outputs_host;
+  pa.n_peers = n_peers;
+  if (peer_pads_host) {
+    HQKV_REQUIRE(world >= 2 && world <= HQKV_MAX_PEERS + 1 && rank >= 0 && rank < world, "decode_gather: bad rank/world");
+    HQKV_REQUIRE(state && aligned(state, 4) && max_spins > 0, "decode_gather: null state or non-positive spin limit");
+    for (int r = 0; r < world; ++r)
+      HQKV_REQUIRE(peer_pads_host[r] && aligned(peer_pads_host[r], 4), "decode_gather: pad %d is null or misaligned", r);
+    pa.pads = peer_pads_host;
+    pa.rank = rank;
+    pa.world = world;
+    pa.state = state;
+    pa.max_spins = max_spins;
+  }
+  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, pa, stream);
+}
+
+static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
+                               void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream) {
   HQKV_REQUIRE(phases >= 1 && phases <= 3, "decode: phases must be 1 (K pass), 2 (V pass) or 3 (both)");
   DecodeParams P;
   Layout lay;
   int rc = build_params(cache_host, P, lay);
   if (rc) return rc;
+  P.n_peers = peers.n_peers;
+  for (int p = 0; p < peers.n_peers; ++p) P.peer_out[p] = static_cast<__half*>(peers.out[p]);
+  if (peers.pads) {
+    P.rank = peers.rank;
+    P.world = peers.world;
+    for (int r = 0; r < peers.world; ++r) P.pad[r] = static_cast<unsigned*>(peers.pads[r]);
+    P.peer_state = static_cast<unsigned*>(peers.state);
+    P.max_spins = peers.max_spins;
+  }
   HQKV_REQUIRE(q && attn_weights && attn_output && workspace, "decode: null pointer");
   HQKV_REQUIRE(aligned(q, 4), "decode: q must be 4-byte aligned");
   HQKV_REQUIRE(aligned(workspace, 256), "decode: workspace must be 256-byte aligned");
@@ -1809,3 +1922,44 @@ extern "C" int hqkv_x_timeline(void* dst, unsigned* n, int reset) {
   return 0;
 }
 #endif
+
+// ------------------------------------------------------------------------------------------------
+// Cross-GPU barrier for the kv-head-sharded decode (one process per GPU)
+// ------------------------------------------------------------------------------------------------
+// After hqkv_decode_attention_gather every rank has written its heads' output rows into every peer's
+// gathered buffer.  This kernel, launched by every rank on the same stream right after, (1) tells every
+// peer "my stores of call number n are done" by raising a counter in the peer's signal pad, and (2)
+// waits until every peer has told it the same.  The call number lives in device memory and is advanced
+// by the kernel itself, so the launch can sit in a CUDA graph that is replayed.  Every wait is bounded:
+// after max_spins polls the kernel gives up, records which peer was missing in *status and returns, so
+// a rank that died cannot hang the others' GPUs (the data of that step is then incomplete and the host
+// must check *status before it trusts it).
+namespace hqkv {
+struct PeerPads {
+  unsigned* pad[HQKV_MAX_PEERS + 1];  // the ranks' signal pads, own one included
+};
+
+__global__ void peer_barrier_kernel(const __grid_constant__ PeerPads pads, int rank, int world, unsigned* call_no,
+                                    int* status, long long max_spins) {
+  __shared__ unsigned n;
+  peer_barrier_device<true>(pads.pad, rank, world, call_no, status, max_spins, &n);
+}
+}  // namespace hqkv
+
+extern "C" int hqkv_peer_barrier(void* const* peer_pads_host, int rank, int world, void* state, long long max_spins,
+                                 void* stream) {
+  HQKV_REQUIRE(world >= 1 && world <= HQKV_MAX_PEERS + 1 && rank >= 0 && rank < world, "peer_barrier: bad rank/world");
+  HQKV_REQUIRE(peer_pads_host && state && aligned(state, 8) && max_spins > 0,
+               "peer_barrier: null or misaligned pointer, or non-positive spin limit");
+  hqkv::PeerPads pads = {};
+  for (int r = 0; r < world; ++r) {
+    HQKV_REQUIRE(peer_pads_host[r] && aligned(peer_pads_host[r], 4), "peer_barrier: pad %d is null or misaligned", r);
+    pads.pad[r] = static_cast<unsigned*>(peer_pads_host[r]);
+  }
+  // state (8 bytes of this GPU's memory, zero before the first call): call number, status
+  unsigned* st = static_cast<unsigned*>(state);
+  hqkv::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, st,
+                                                                             reinterpret_cast<int*>(st + 1), max_spins);
+  HQKV_LAUNCH_CHECK("peer_barrier");
+  return HQKV_OK;
+}

@@ -71,3 +71,81 @@ def reduce_importance_row(partial_f32: torch.Tensor, group=None):
     for r in range(1, world):
         total += parts[r]
     return total.half()
+
+
+class PeerGather:
+    """All-gather of the per-rank attention outputs done by the decode kernel itself.
+
+    ``slots`` gathered buffers ``[world, B, nh_q/world, 1, D]`` (one per layer of a step, so that a
+    layer's rows stay valid until the same layer of the next step) live in symmetric memory: every
+    rank can store into every other rank's copy.  :meth:`decode` runs the fused decode with the peers'
+    addresses of this rank's block (``hqkv_decode_attention_gather``: the kernel's last CTAs write the
+    output rows locally and over NVLink to all peers, and the CTA that finishes last runs a bounded
+    cross-GPU barrier), after which ``self.buffers[slot]`` holds all ranks' rows on every rank.  Everything is stream-ordered
+    kernel launches with fixed arguments, so a step can be captured into a CUDA graph.
+
+    Needs torch's symmetric memory (CUDA IPC between the GPUs of one node); construct it inside a
+    try block and fall back to :func:`gather_head_outputs` (NCCL) when it is not available.
+    """
+
+    def __init__(self, slots: int, batch: int, nh_q_local: int, head_dim: int, device, group=None,
+                 max_spins: int = 4_000_000):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm_mem
+        from ._lib import lib  # fails loudly without the CUDA library
+        self._lib, self._C = lib, C
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if self.world - 1 > 7:
+            raise ValueError("at most 8 ranks")
+        block = batch * nh_q_local * head_dim
+        self._block = block
+        self._all = symm_mem.empty(slots * self.world * block, dtype=torch.float16, device=device)
+        self._all.zero_()
+        self._hdl = symm_mem.rendezvous(self._all, group)
+        self.buffers = [self._all[s * self.world * block:(s + 1) * self.world * block]
+                        .view(self.world, batch, nh_q_local, 1, head_dim) for s in range(slots)]
+        # where THIS rank's block of slot s starts inside peer p's buffer
+        base = [int(p) for p in self._hdl.buffer_ptrs]
+        self._peers = [p for p in range(self.world) if p != self.rank]
+        self._peer_args = []
+        for s in range(slots):
+            arr = (C.c_void_p * max(len(self._peers), 1))()
+            for i, p in enumerate(self._peers):
+                arr[i] = base[p] + 2 * ((s * self.world + self.rank) * block)
+            self._peer_args.append(arr)
+        # arrival counters: `world` 32-bit words in every rank's signal pad, away from the first words,
+        # which torch's own symmetric-memory collectives use
+        pad_off = 1024 if int(getattr(self._hdl, "signal_pad_size", 0)) >= 1024 + 4 * self.world else 0
+        pads = (C.c_void_p * self.world)()
+        for r in range(self.world):
+            pads[r] = int(self._hdl.signal_pad_ptrs[r]) + pad_off
+        self._pads = pads
+        self._state = torch.zeros(4, dtype=torch.int32, device=device)  # call number, status, finished heads
+        self._max_spins = max_spins
+        # nobody may signal before every rank has zeroed its buffers and built its tables
+        torch.cuda.synchronize(device)
+        dist.barrier(group)
+
+    def local_block(self, slot: int) -> torch.Tensor:
+        """This rank's rows inside its own gathered buffer ([B, nh_q/world, 1, D])."""
+        return self.buffers[slot][self.rank]
+
+    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int):
+        """Fused decode of this rank's heads; returns (attn_weights_local, gathered [world, B, nh_q/world, 1, D])."""
+        from ._lib import check, decode_workspace, stream_ptr
+        from .quant._cache import cached_cache_desc
+        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+        q = q.contiguous()
+        weights = torch.empty(q.shape[0], q.shape[1], 1, L, dtype=torch.float16, device=dev)
+        out = self.local_block(slot)
+        ws = decode_workspace(dev, self._lib.hqkv_decode_workspace_bytes(desc))
+        st = stream_ptr(dev)
+        check(self._lib.hqkv_decode_attention_gather(desc, q.data_ptr(), weights.data_ptr(), out.data_ptr(), ws.data_ptr(),
+                                                     ws.numel(), self._peer_args[slot], len(self._peers), self._pads,
+                                                     self.rank, self.world, self._state.data_ptr(), self._max_spins, st))
+        return weights, self.buffers[slot]
+
+    def status(self) -> int:
+        """0, or 1 + the rank that some barrier gave up waiting for (synchronises the device)."""
+        return int(self._state[1].item())

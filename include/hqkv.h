@@ -82,6 +82,7 @@ int hqkv_unpack(const void* words, int64_t rows, int64_t W, int bits, void* out_
  * ------------------------------------------------------------------------------------------- */
 
 #define HQKV_NUM_TIERS 5 /* 16-, 8-, 4-, 2-, 1-bit, in the slot order of the reference's cache tuple */
+#define HQKV_MAX_PEERS 7 /* other GPUs a kv-head-sharded decode can write its output rows to */
 
 /* One precision tier of the cache (slots 0-35 of the 42-entry tuple, quant/hqe_matmul.py:364-368). */
 typedef struct {
@@ -147,6 +148,29 @@ int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, vo
  */
 int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
                                  void* attn_output, void* workspace, size_t workspace_bytes, int phases, void* stream);
+
+/*
+ * kv-head sharding over the GPUs of one node (one process per GPU; reference: none - the reference is
+ * single-GPU; the head split follows its per-(batch*head) kernel indexing, quant/csrc/gemv_cuda_uniform.cu:415-428).
+ * hqkv_decode_attention_gather is hqkv_decode_attention whose last step also stores this GPU's output
+ * rows [B, nh_q_local, 1, D] into n_peers other GPUs' memory (peer_outputs_host[p] = where THIS rank's
+ * block starts inside peer p's gathered buffer; peer-accessible device pointers, e.g. CUDA IPC or
+ * torch symmetric memory).  The stores are plain NVLink writes.  With peer_pads_host != NULL the CTA
+ * that finishes this GPU's last (batch, kv head) then runs a cross-GPU barrier before the kernel ends,
+ * so that once the call has completed on a rank, every rank's rows are in that rank's gathered buffer;
+ * with NULL the caller orders the GPUs itself (hqkv_peer_barrier, or any collective).
+ *
+ * Barrier arguments: peer_pads_host[r] = rank r's signal pad (>= 4*world bytes, zero before the first
+ * call, written by the peers); state = 12 bytes of this GPU's memory, zero before the first call (call
+ * number, status, finished-head count).  Waits are bounded by max_spins polls per peer; when a peer
+ * does not arrive the kernel stores (peer + 1) in the status word (state + 4) and returns - no trap,
+ * no endless loop.  hqkv_peer_barrier is the same barrier as a kernel of its own (state: 8 bytes).
+ */
+int hqkv_decode_attention_gather(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                 void* attn_output, void* workspace, size_t workspace_bytes,
+                                 void* const* peer_outputs_host, int n_peers, void* const* peer_pads_host, int rank,
+                                 int world, void* state, long long max_spins, void* stream);
+int hqkv_peer_barrier(void* const* peer_pads_host, int rank, int world, void* state, long long max_spins, void* stream);
 
 /*
  * hqkv_decode_attention for callers that cannot allocate device memory.  It has no counterpart in the

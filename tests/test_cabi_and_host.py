@@ -58,6 +58,24 @@ def test_argument_validation_needs_no_gpu(lib):
     assert b"pointers are null" in L.hqkv_last_error()
 
 
+def test_peer_entry_points_validate_without_gpu(lib):
+    """kv-head sharding entry points: argument checks run before anything touches a device."""
+    import ctypes as C
+    L = lib.lib
+    desc = lib.CacheDesc()
+    desc.B, desc.H, desc.nh_q, desc.D, desc.group_k, desc.group_v = 1, 8, 32, 128, 32, 32
+    peers = (C.c_void_p * 8)()
+    assert L.hqkv_decode_attention_gather(desc, None, None, None, None, 0, peers, 8, None, 0, 0, None, 0, None) == -1
+    assert b"at most 7 peers" in L.hqkv_last_error()
+    assert L.hqkv_decode_attention_gather(desc, None, None, None, None, 0, peers, 2, None, 0, 0, None, 0, None) == -1
+    assert b"peer output 0 is null" in L.hqkv_last_error()
+    pads = (C.c_void_p * 2)()
+    assert L.hqkv_peer_barrier(pads, 2, 2, None, 1000, None) == -1      # rank out of range
+    assert b"bad rank/world" in L.hqkv_last_error()
+    assert L.hqkv_peer_barrier(pads, 0, 2, None, 1000, None) == -1      # no state block
+    assert L.hqkv_peer_barrier(pads, 0, 2, C.c_void_p(4096), 0, None) == -1  # spin limit must be positive: waits are bounded
+
+
 def test_workspace_size_of_the_benchmark_cache(lib):
     """Llama-3.1-8B at 32k: 5888/11744/11744 tokens in the 8/4/2-bit tiers + 128 residual."""
     desc = lib.CacheDesc()
