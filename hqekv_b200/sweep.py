@@ -90,7 +90,7 @@ def quantize_point(dev, tokens, bit, group, peak_gbs):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/sweep.jsonl")
+    ap.add_argument("--out", default="sweep.jsonl")
     ap.add_argument("--quick", action="store_true")
     args = ap.parse_args()
     dev = torch.device("cuda:0")

@@ -1,7 +1,6 @@
 """Generate the golden fixtures in this directory by EXECUTING THE REFERENCE.
 
-Run once, in a container that has the reference tree mounted (default
-``/root/reference``; override with ``HQEKV_REFERENCE_ROOT``):
+Run once, where a checkout of the reference is available (point ``HQEKV_REFERENCE_ROOT`` at it):
 
     python tests/golden/make_golden.py
 

@@ -365,6 +365,25 @@ def test_decode_sweep_vs_oracle(ops, cuda_device, tiers, group):
         check_attention(ops, cache, q, group, group, f"{cfg.name} B{batch} {nh_q}/{nh_kv}")
 
 
+@pytest.mark.parametrize("case", [
+    # name, batch, nh_q, nh_kv, context, residual, ratios (8/4/2/1-bit), evict, group
+    ("one-block-per-tier", 1, 8, 2, 4 * 32 + 5, 5, (0.25, 0.25, 0.25, 0.25), 0.0, 32),
+    ("single-8bit-block-ragged-residual", 2, 4, 2, 32 + 7, 7, (1.0, 0.0, 0.0), 0.0, 32),
+    ("gqa-2", 1, 8, 4, 640 + 33, 33, (0.2, 0.4, 0.4), 0.1, 32),
+    ("mha", 2, 4, 4, 512 + 16, 16, (0.25, 0.5, 0.25), 0.0, 64),
+    ("many-heads-short", 32, 32, 8, 160 + 1, 1, (0.2, 0.4, 0.4), 0.0, 32),
+    ("group128-tiles-straddle-groups", 1, 32, 8, 128 * 9 + 100, 100, (0.34, 0.33, 0.33), 0.0, 128),
+])
+def test_decode_edge_shapes(ops, cuda_device, case):
+    """Shapes at the edges of the tiling: tiers of a single block, a residual of 1..100 tokens, GQA ratios 1 and
+    2, 256 (batch, kv head) pairs, tiles that cover part of a 128-token scale group.  Against the fp32 oracle."""
+    from hqekv_b200 import synthetic
+    name, batch, nh_q, nh_kv, ctx, res, ratios, evict, group = case
+    cfg = synthetic.CacheConfig(name, batch, nh_q, nh_kv, 128, ctx, res, ratios, evict, group, True, 1)
+    cache, q = synthetic.build_cache(cfg, cuda_device, seed=7, times_range=True)
+    check_attention(ops, cache, q, group, group, name)
+
+
 def test_decode_long_context_shard_properties(ops, cuda_device):
     """One kv head of the 128k-context case (what one of 8 GPUs holds per head, batch 1): 10/25/65 % in
     8/4/2-bit, 30 % evicted, residual 256.  Checked against torch fp32 attention over the dense
