@@ -46,9 +46,10 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--peer-gather", action="store_true",
+    ap.add_argument("--peer-gather", choices=["off", "flagged", "barrier"], default="flagged",
                     help="multi-GPU: the decode kernel stores its rows into the peers' buffers (symmetric memory) "
-                         "instead of an NCCL all-gather per layer")
+                         "instead of an NCCL all-gather per layer: 'flagged' = values travel with the call number, "
+                         "'barrier' = plain stores + cross-GPU barrier")
     return ap.parse_args()
 
 
@@ -240,15 +241,17 @@ def main():
     gathered = [torch.empty(world, cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
                 for _ in range(layers)] if world > 1 else None
 
-    # Multi-GPU exchange of the per-head outputs: NCCL all-gather per layer, or (--peer-gather) the decode
-    # kernel stores its rows into every peer's gathered buffer and runs a bounded cross-GPU barrier
-    # (sharding.PeerGather; falls back to NCCL when symmetric memory is not available or the two disagree
-    # on the first layer).  Measured at batch 1: NCCL is faster at N=2.
+    # Multi-GPU exchange of the per-head outputs.  Default: the decode kernel stores its rows, each pair of
+    # values in one 8-byte word with the call number, into every peer's receive buffer and a bounded
+    # unpack kernel follows (sharding.FlaggedPeerGather).  --peer-gather barrier: plain stores + cross-GPU
+    # barrier; off: NCCL all-gather per layer, also the fallback when symmetric memory is not available
+    # or the result differs from NCCL's on the first layer (checked every run).
     peer = None
-    if world > 1 and args.peer_gather:
+    if world > 1 and args.peer_gather != "off":
         try:
-            from hqekv_b200.sharding import PeerGather
-            peer = PeerGather(layers, cfg.batch, nh_q_local, cfg.head_dim, dev)
+            from hqekv_b200.sharding import FlaggedPeerGather, PeerGather
+            peer = (PeerGather if args.peer_gather == "barrier" else FlaggedPeerGather)(
+                max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
             _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
             dist.all_gather_into_tensor(gathered[0], o_ref)
             _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group)
@@ -262,7 +265,7 @@ def main():
                 print(f"[bench] peer-store gather unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
             peer = None
     if world > 1:
-        config["exchange"] = "peer stores from the decode kernel + bounded cross-GPU barrier" if peer else "nccl all_gather per layer"
+        config["exchange"] = (f"peer stores from the decode kernel ({args.peer_gather})" if peer else "nccl all_gather per layer")
 
     def decode_layer(i, q):
         if peer is not None:

@@ -63,6 +63,7 @@ struct DecodeParams {
   double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K pass, summed into by the V pass
   __half* peer_out[HQKV_MAX_PEERS];  // copies of `out` in other GPUs' memory (kv-head sharding), n_peers used
   int n_peers;
+  int peer_flagged;  // 1: peer_out are flagged 8-byte entries {two fp16 values, call number}, see peer_unpack_kernel
   // cross-GPU barrier run by the last CTA of the V pass (world == 0: none)
   unsigned* pad[HQKV_MAX_PEERS + 1];  // the ranks' signal pads, own one included
   int rank, world;
@@ -1556,7 +1557,13 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
       *reinterpret_cast<__half2*>(P.out + at) = o;
       // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
       // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
-      for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
+      if (P.peer_flagged) {
+        // value and call number travel in ONE 8-byte store: the receiver needs no fence and no signal
+        const uint2 e = make_uint2(h2_as_u32(o), P.peer_state[0] + 1u);
+        for (int p = 0; p < P.n_peers; ++p) reinterpret_cast<uint2*>(P.peer_out[p])[at >> 1] = e;
+      } else {
+        for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
+      }
     }
     TL_STAMP(7);
     if (P.world > 1) {
@@ -1733,6 +1740,7 @@ namespace hqkv {
 struct PeerArgs {
   void* const* out = nullptr;   // where this rank's block starts in each peer's gathered buffer
   int n_peers = 0;
+  bool flagged = false;         // peers take flagged 8-byte entries
   void* const* pads = nullptr;  // signal pads of all ranks (own one included); null: no barrier
   int rank = 0, world = 0;
   void* state = nullptr;
@@ -1781,6 +1789,8 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
   int rc = build_params(cache_host, P, lay);
   if (rc) return rc;
   P.n_peers = peers.n_peers;
+  P.peer_flagged = peers.flagged ? 1 : 0;
+  if (peers.flagged) P.peer_state = static_cast<unsigned*>(peers.state);
   for (int p = 0; p < peers.n_peers; ++p) P.peer_out[p] = static_cast<__half*>(peers.out[p]);
   if (peers.pads) {
     P.rank = peers.rank;
@@ -1961,5 +1971,78 @@ extern "C" int hqkv_peer_barrier(void* const* peer_pads_host, int rank, int worl
   hqkv::peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pads, rank, world, st,
                                                                              reinterpret_cast<int*>(st + 1), max_spins);
   HQKV_LAUNCH_CHECK("peer_barrier");
+  return HQKV_OK;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Flagged exchange: the low-latency form of the kv-head-sharded gather
+// ------------------------------------------------------------------------------------------------
+// hqkv_decode_attention_gather_flagged makes the V pass store every pair of output values together with
+// the call number as ONE 8-byte word into the peers' receive buffers: a word whose flag equals the
+// call number is complete, so no fence, no signal and no round trip is needed - the exchange costs
+// one NVLink store latency.  hqkv_peer_unpack, enqueued by every rank right after, polls its own
+// receive buffer (bounded), strips the flags into the plain gathered buffer [world][entries] of fp16
+// pairs and advances the call number (device memory: the pair of launches replays from a CUDA graph).
+// A receive buffer must not be reused before the peers have unpacked it: callers rotate at least two.
+namespace hqkv {
+__global__ void __launch_bounds__(256) peer_unpack_kernel(const uint2* recv, uint32_t* plain, int rank, int world,
+                                                          int entries, unsigned* state, long long max_spins) {
+  asm volatile("griddepcontrol.launch_dependents;");
+  asm volatile("griddepcontrol.wait;" ::: "memory");  // this GPU's own decode call has finished
+  const unsigned n = state[0] + 1u;
+  for (int i = threadIdx.x; i < world * entries; i += blockDim.x) {
+    const int r = i / entries;
+    if (r == rank) continue;  // own rows were written in place by the decode kernel
+    long long spins = 0;
+    uint2 e;
+    for (;;) {
+      asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(recv + i));
+      if (e.y == n) break;
+      if (++spins > max_spins) {
+        atomicExch(reinterpret_cast<int*>(state + 1), r + 1);  // gave up waiting for rank r
+        break;
+      }
+      __nanosleep(20);
+    }
+    plain[i] = e.x;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) state[0] = n;
+}
+}  // namespace hqkv
+
+extern "C" int hqkv_decode_attention_gather_flagged(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                                    void* attn_output, void* workspace, size_t workspace_bytes,
+                                                    void* const* peer_recv_host, int n_peers, void* state, void* stream) {
+  HQKV_REQUIRE(n_peers >= 1 && n_peers <= HQKV_MAX_PEERS, "decode_gather_flagged: 1..%d peers (got %d)", HQKV_MAX_PEERS, n_peers);
+  HQKV_REQUIRE(peer_recv_host && state && aligned(state, 4), "decode_gather_flagged: null pointer");
+  for (int p = 0; p < n_peers; ++p)
+    HQKV_REQUIRE(peer_recv_host[p] && aligned(peer_recv_host[p], 8), "decode_gather_flagged: peer buffer %d is null or misaligned", p);
+  hqkv::PeerArgs pa;
+  pa.out = peer_recv_host;
+  pa.n_peers = n_peers;
+  pa.flagged = true;
+  pa.state = state;
+  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, pa, stream);
+}
+
+extern "C" int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int entries_per_rank, void* state,
+                                long long max_spins, void* stream) {
+  HQKV_REQUIRE(world >= 2 && world <= HQKV_MAX_PEERS + 1 && rank >= 0 && rank < world, "peer_unpack: bad rank/world");
+  HQKV_REQUIRE(recv && gathered && state && aligned(recv, 8) && aligned(gathered, 4) && aligned(state, 4),
+               "peer_unpack: null or misaligned pointer");
+  HQKV_REQUIRE(entries_per_rank > 0 && max_spins > 0, "peer_unpack: sizes and the spin limit must be positive");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(1);
+  cfg.blockDim = dim3(256);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // polls may start while the decode call drains
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HQKV_CUDA(cudaLaunchKernelEx(&cfg, hqkv::peer_unpack_kernel, static_cast<const uint2*>(recv),
+                               static_cast<uint32_t*>(gathered), rank, world, entries_per_rank,
+                               static_cast<unsigned*>(state), max_spins));
   return HQKV_OK;
 }

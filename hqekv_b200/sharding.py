@@ -149,3 +149,71 @@ class PeerGather:
     def status(self) -> int:
         """0, or 1 + the rank that some barrier gave up waiting for (synchronises the device)."""
         return int(self._state[1].item())
+
+
+class FlaggedPeerGather:
+    """The low-latency form of :class:`PeerGather`: values travel with the call number in 8-byte words.
+
+    Per slot a RECEIVE buffer of ``world * entries`` 8-byte words lives in symmetric memory; the decode
+    kernel of every rank stores {two fp16 values, call number} words into the peers' receive buffers
+    (``hqkv_decode_attention_gather_flagged``), and ``hqkv_peer_unpack`` on every rank polls its own
+    receive buffer, bounded, and writes the plain gathered tensor ``[world, B, nh_q/world, 1, D]``.
+    No fence, signal or collective is involved; both launches have fixed arguments (CUDA-graph safe).
+    A slot is reused only one full round of slots later, so ``slots`` must be at least 2.
+    """
+
+    def __init__(self, slots: int, batch: int, nh_q_local: int, head_dim: int, device, group=None,
+                 max_spins: int = 4_000_000):
+        import ctypes as C
+        import torch.distributed._symmetric_memory as symm_mem
+        from ._lib import lib  # fails loudly without the CUDA library
+        if slots < 2:
+            raise ValueError("at least two slots: a receive buffer is reused only after the peers unpacked it")
+        self._lib = lib
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if not 2 <= self.world <= 8:
+            raise ValueError("2 to 8 ranks")
+        block = batch * nh_q_local * head_dim
+        self._entries = block // 2
+        words = slots * self.world * self._entries * 2  # int32 words
+        self._recv = symm_mem.empty(words, dtype=torch.int32, device=device)
+        self._recv.zero_()
+        self._hdl = symm_mem.rendezvous(self._recv, group)
+        self.buffers = [torch.zeros(self.world, batch, nh_q_local, 1, head_dim, dtype=torch.float16, device=device)
+                        for _ in range(slots)]
+        base = [int(p) for p in self._hdl.buffer_ptrs]
+        self._peers = [p for p in range(self.world) if p != self.rank]
+        self._peer_args, self._recv_ptr = [], []
+        for s in range(slots):
+            arr = (C.c_void_p * len(self._peers))()
+            for i, p in enumerate(self._peers):
+                arr[i] = base[p] + 8 * ((s * self.world + self.rank) * self._entries)
+            self._peer_args.append(arr)
+            self._recv_ptr.append(base[self.rank] + 8 * (s * self.world * self._entries))
+        self._state = torch.zeros(2, dtype=torch.int32, device=device)  # call number, status
+        self._max_spins = max_spins
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # nobody sends before every receive buffer is zero
+
+    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int):
+        """Fused decode of this rank's heads; returns (attn_weights_local, gathered [world, B, nh_q/world, 1, D])."""
+        from ._lib import check, decode_workspace, stream_ptr
+        from .quant._cache import cached_cache_desc
+        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+        q = q.contiguous()
+        weights = torch.empty(q.shape[0], q.shape[1], 1, L, dtype=torch.float16, device=dev)
+        gathered = self.buffers[slot]
+        out = gathered[self.rank]
+        ws = decode_workspace(dev, self._lib.hqkv_decode_workspace_bytes(desc))
+        st = stream_ptr(dev)
+        check(self._lib.hqkv_decode_attention_gather_flagged(desc, q.data_ptr(), weights.data_ptr(), out.data_ptr(),
+                                                             ws.data_ptr(), ws.numel(), self._peer_args[slot],
+                                                             len(self._peers), self._state.data_ptr(), st))
+        check(self._lib.hqkv_peer_unpack(self._recv_ptr[slot], gathered.data_ptr(), self.rank, self.world, self._entries,
+                                         self._state.data_ptr(), self._max_spins, st))
+        return weights, gathered
+
+    def status(self) -> int:
+        """0, or 1 + the rank that some unpack gave up waiting for (synchronises the device)."""
+        return int(self._state[1].item())

@@ -173,6 +173,24 @@ int hqkv_decode_attention_gather(const hqkv_cache_desc_t* cache_host, const void
 int hqkv_peer_barrier(void* const* peer_pads_host, int rank, int world, void* state, long long max_spins, void* stream);
 
 /*
+ * Low-latency form of the same exchange (no counterpart in the reference).  The decode kernel stores each
+ * pair of output values together with the call number as one 8-byte word into the peers' RECEIVE
+ * buffers (peer_recv_host[p] = where THIS rank's entries start in peer p's receive buffer of
+ * world * entries_per_rank 8-byte words, zero before the first call); hqkv_peer_unpack, enqueued by every
+ * rank right after, polls its own receive buffer until every word carries the current call number
+ * (bounded by max_spins per word; a missing rank is recorded as rank + 1 in the status word at
+ * state + 4), writes the values into the plain gathered buffer [world][entries_per_rank] of fp16 pairs
+ * and advances the call number at state + 0.  entries_per_rank = B * nh_q_local * D / 2.  A receive buffer
+ * may be reused only after every peer has unpacked it: rotate at least two.  state: 8 bytes of this
+ * GPU's memory, zero before the first call, shared by the two functions.
+ */
+int hqkv_decode_attention_gather_flagged(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                         void* attn_output, void* workspace, size_t workspace_bytes,
+                                         void* const* peer_recv_host, int n_peers, void* state, void* stream);
+int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int entries_per_rank, void* state,
+                     long long max_spins, void* stream);
+
+/*
  * hqkv_decode_attention for callers that cannot allocate device memory.  It has no counterpart in the
  * reference, whose wrappers allocate freely through torch.
  *
