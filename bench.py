@@ -487,7 +487,8 @@ def main():
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
             "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * layers * 2, "roofline": roofline, "cpu_baseline": cpu_baseline,
+            "gpu_launches": args.steps * layers * (3 if (peer is not None and args.peer_gather == "flagged") else 2),
+            "roofline": roofline, "cpu_baseline": cpu_baseline,
             "tokens_per_sec_per_gpu": value / world}), flush=True)
     if world > 1:
         # Leave without tearing the communicator down: destroying a process group whose collectives

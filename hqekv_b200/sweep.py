@@ -21,7 +21,8 @@ from ._lib import check, lib, ptr, stream_ptr
 from .quant._cache import build_cache_desc
 from .quant.pack_unpack import uniform_group_quantize_pack_last_dim
 
-TIER_MIXES = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "mixed": (0.25, 0.5, 0.25)}
+TIER_MIXES = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "all1": (0.0, 0.0, 0.0, 1.0),
+              "mixed": (0.25, 0.5, 0.25)}
 
 
 def _graph_time(fn, reps):
@@ -101,7 +102,7 @@ def main():
     ctxs = (1024 + 128, 4096, 32768) if args.quick else (1024 + 128, 4096, 16384, 32768, 131072)
     points = []
     for ctx in ctxs:
-        for mix in (("mixed",) if args.quick else ("all8", "all4", "all2", "mixed")):
+        for mix in (("mixed",) if args.quick else ("all8", "all4", "all2", "all1", "mixed")):
             for group in ((32,) if args.quick else (32, 128)):
                 for batch in (1, 8, 32):
                     per_layer = batch * 8 * ctx * 288          # upper bound, bytes

@@ -74,6 +74,11 @@ def test_peer_entry_points_validate_without_gpu(lib):
     assert b"bad rank/world" in L.hqkv_last_error()
     assert L.hqkv_peer_barrier(pads, 0, 2, None, 1000, None) == -1      # no state block
     assert L.hqkv_peer_barrier(pads, 0, 2, C.c_void_p(4096), 0, None) == -1  # spin limit must be positive: waits are bounded
+    assert L.hqkv_decode_attention_gather_flagged(desc, None, None, None, None, 0, peers, 0, None, None) == -1
+    assert b"1..7 peers" in L.hqkv_last_error()
+    assert L.hqkv_peer_unpack(None, None, 0, 2, 256, None, 1000, None) == -1
+    assert b"null or misaligned" in L.hqkv_last_error()
+    assert L.hqkv_peer_unpack(C.c_void_p(4096), C.c_void_p(4096), 0, 2, 256, C.c_void_p(4096), 0, None) == -1  # bounded waits only
 
 
 def test_workspace_size_of_the_benchmark_cache(lib):
