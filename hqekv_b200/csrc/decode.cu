@@ -1,21 +1,23 @@
 // Fused mixed-precision decode attention over the tiered KV cache (sm_100a).
 //
 // Two launches per call:
-//   k_pass : logits[h, pos] = scale * q_h . K̂_pos for every tier (8/4/2-bit packed, fp16 tier,
+//   k_pass : logits[h, pos] = scale * q_h . K^_pos for every tier (8/4/2/1-bit packed, fp16 tier,
 //            fp16 residual), written to an fp32 scratch row at the tokens' logical positions,
 //            plus one (max, sum-exp) pair per CTA and head.
-//   v_pass : every CTA first folds the k_pass pairs into the global (max, sum) of its heads,
-//            then accumulates sum_t exp(logit_t - max) * V̂_t over its token range, normalises a
-//            slice of the probability row into the fp16 output, and the last CTA of each
-//            (batch, kv head) adds the partial sums in chunk order and writes the output.
+//   v_pass : every CTA first folds the k_pass pairs into the global (max, sum) of its heads; each
+//            warp then writes the normalised probabilities of its own tokens and accumulates
+//            sum_t exp(logit_t - max) * V^_t over them; the CTA's partial output joins fp64
+//            accumulators, and the last CTA of each (batch, kv head) normalises and writes fp16.
 //
 // The roofline is HBM: every packed word, scale and zero is read exactly once per call and is
-// shared by all query heads of its kv head (GQA).  At 2-4 bits there are 1.6-2.7 codes per
-// byte; four query heads need four FMAs per code, more than the FP32 pipes can issue at HBM
-// speed.  The codes are therefore dequantised to fp16 pairs in registers (PRMT + LOP3 + HFMA2)
-// straight into m16n8k16 A fragments and the dot products run on the tensor pipe with fp32
-// accumulation; no operand takes a trip through shared memory.  Fragment rows/columns are
-// mapped to tokens and channels so that a thread consumes every code of each word it loads.
+// shared by all query heads of its kv head (GQA).  At 2-4 bits there are 1.6-2.7 codes per byte;
+// four query heads need four FMAs per code, more than the FP32 pipes can issue at HBM speed, so the
+// dot products run on the tensor pipe (mma.sync m16n8k16, fp32 accumulation).  Tiles of codes are
+// staged in shared memory with 16-byte cp.async and read back with ldmatrix.trans, which delivers the
+// two K-neighbours of an A fragment in one register; the codes enter the MMA as fp16 subnormals (one
+// AND per pair) and the scale is folded into the B operand, carried exactly as hi + lo.
+// Both kernels are chained with programmatic dependent launch: whatever a kernel needs only from the
+// cache is requested before it waits for the kernel ahead of it.
 #include <math.h>
 #include <string.h>
 
@@ -28,10 +30,7 @@
 namespace hqkv {
 
 constexpr int D = 128;           // head dim
-constexpr int NWARP = 4;         // warps per CTA
-constexpr int NTHREADS = NWARP * 32;
 constexpr int MAX_REP = 8;       // query heads per kv head (n of the m16n8k16 tile)
-constexpr int SCALE_PAD = 8;     // halfs of padding per shared-memory scale row
 
 struct TierDev {
   const void* k_data;
@@ -53,7 +52,6 @@ struct DecodeParams {
   int B, H, nh_q, rep, rep_shift, L;
   int gk_shift, gv_shift;
   int nk_chunks, nv_chunks;
-  int w_slice;  // logical positions normalised per v_pass CTA
   float scale;
   const __half* q;
   __half* weights;
@@ -111,11 +109,6 @@ __device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_c
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
 
 // Streaming loads: the cache is read once per call, keep it out of L1.
-__device__ __forceinline__ uint32_t ld_stream(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
 __device__ __forceinline__ uint2 ld_stream(const uint2* p) {
   uint2 v;
   asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
@@ -135,21 +128,6 @@ __device__ __forceinline__ uint4 ld_stream(const uint4* p) {
 template <int BITS>
 struct Fmt;
 template <>
-struct Fmt<8> {
-  using word_t = uint2;  // two packed words = 8 codes
-  static constexpr int FPI = 8, SUB = 8, CPS = 1;
-};
-template <>
-struct Fmt<4> {
-  using word_t = uint32_t;
-  static constexpr int FPI = 8, SUB = 4, CPS = 2;
-};
-template <>
-struct Fmt<2> {
-  using word_t = uint32_t;
-  static constexpr int FPI = 16, SUB = 4, CPS = 4;
-};
-template <>
 struct Fmt<16> {
   using word_t = uint4;  // eight halfs
   static constexpr int FPI = 8, SUB = 4, CPS = 2;
@@ -162,55 +140,6 @@ template <int BITS>
 struct Decode;
 
 template <>
-struct Decode<8> {
-  template <int SUBI>
-  static __device__ __forceinline__ void run(const uint2& wa, const uint2& wb, __half2 sz, __half2 zz,
-                                             uint32_t (&out)[1]) {
-    const uint32_t a = SUBI < 4 ? wa.x : wa.y, b = SUBI < 4 ? wb.x : wb.y;
-    constexpr int j = SUBI & 3;
-    const uint32_t t = __byte_perm(a, b, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-    const uint32_t x = (t & 0x00FF00FFu) | 0x64006400u;  // 1024 + code
-    const __half2 c = __hsub2(u32_as_h2(x), __half2half2(__float2half(1024.f)));
-    out[0] = h2_as_u32(__hfma2(c, sz, zz));
-  }
-};
-template <>
-struct Decode<4> {
-  template <int SUBI>
-  static __device__ __forceinline__ void run(const uint32_t& wa, const uint32_t& wb, __half2 sz, __half2 zz,
-                                             uint32_t (&out)[2]) {
-    constexpr int j = SUBI;
-    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-    const uint32_t x0 = (t & 0x000F000Fu) | 0x64006400u;  // 1024 + code
-    const uint32_t x1 = (t & 0x00F000F0u) | 0x64006400u;  // 1024 + 16*code
-    const __half2 c0 = __hsub2(u32_as_h2(x0), __half2half2(__float2half(1024.f)));
-    const __half2 c1 = __hfma2(u32_as_h2(x1), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f)));
-    out[0] = h2_as_u32(__hfma2(c0, sz, zz));
-    out[1] = h2_as_u32(__hfma2(c1, sz, zz));
-  }
-};
-template <>
-struct Decode<2> {
-  template <int SUBI>
-  static __device__ __forceinline__ void run(const uint32_t& wa, const uint32_t& wb, __half2 sz, __half2 zz,
-                                             uint32_t (&out)[4]) {
-    constexpr int j = SUBI;
-    const uint32_t t = __byte_perm(wa, wb, j | (j << 4) | ((4 + j) << 8) | ((4 + j) << 12));
-    const uint32_t x0 = (t & 0x00030003u) | 0x64006400u;  // 1024 + code
-    const uint32_t x1 = (t & 0x000C000Cu) | 0x64006400u;  // 1024 + 4*code
-    const uint32_t x2 = (t & 0x00300030u) | 0x64006400u;  // 1024 + 16*code
-    const uint32_t x3 = (t & 0x00C000C0u) | 0x64006400u;  // 1024 + 64*code
-    const __half2 c0 = __hsub2(u32_as_h2(x0), __half2half2(__float2half(1024.f)));
-    const __half2 c1 = __hfma2(u32_as_h2(x1), __half2half2(__float2half(0.25f)), __half2half2(__float2half(-256.f)));
-    const __half2 c2 = __hfma2(u32_as_h2(x2), __half2half2(__float2half(0.0625f)), __half2half2(__float2half(-64.f)));
-    const __half2 c3 = __hfma2(u32_as_h2(x3), __half2half2(__float2half(0.015625f)), __half2half2(__float2half(-16.f)));
-    out[0] = h2_as_u32(__hfma2(c0, sz, zz));
-    out[1] = h2_as_u32(__hfma2(c1, sz, zz));
-    out[2] = h2_as_u32(__hfma2(c2, sz, zz));
-    out[3] = h2_as_u32(__hfma2(c3, sz, zz));
-  }
-};
-template <>
 struct Decode<16> {
   template <int SUBI>
   static __device__ __forceinline__ void run(const uint4& wa, const uint4& wb, __half2, __half2, uint32_t (&out)[2]) {
@@ -220,15 +149,6 @@ struct Decode<16> {
     out[1] = __byte_perm(a, b, 0x7632);
   }
 };
-
-template <typename W>
-__device__ __forceinline__ W zero_word();
-template <>
-__device__ __forceinline__ uint32_t zero_word<uint32_t>() { return 0u; }
-template <>
-__device__ __forceinline__ uint2 zero_word<uint2>() { return make_uint2(0u, 0u); }
-template <>
-__device__ __forceinline__ uint4 zero_word<uint4>() { return make_uint4(0u, 0u, 0u, 0u); }
 
 // One 16-deep contraction step over all M-tiles of a thread's slots.
 //   w[p][r]: word of row-pair member p (0,1 -> fragment columns 2tig,2tig+1; 2,3 -> +8,+9) and row
@@ -273,15 +193,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
-// online (max, sum-exp) update
-__device__ __forceinline__ void softmax_push(float& m, float& l, float x) {
-  if (x > m) {
-    l = l * fast_exp2((m - x) * 1.4426950408889634f) + 1.f;
-    m = x;
-  } else {
-    l += fast_exp2((x - m) * 1.4426950408889634f);
-  }
-}
 __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, float l2) {
   const float mx = fmaxf(m, m2);
   if (mx == -INFINITY) return;  // both empty
@@ -1713,7 +1624,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.L = static_cast<int>(L);
   P.nk_chunks = kc;
   P.nv_chunks = vc;
-  P.w_slice = static_cast<int>(ceil_div(L, vc));
   const int64_t BH = static_cast<int64_t>(c->B) * c->H;
   lay.acc_off = HQKV_WS_COUNTER_BYTES;
   lay.logits_off = (lay.acc_off + static_cast<size_t>(BH) * P.rep * D * sizeof(double) + 255) & ~static_cast<size_t>(255);
@@ -1813,7 +1723,6 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
   P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
   P.v_acc = reinterpret_cast<double*>(ws + lay.acc_off);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const dim3 block(NTHREADS);
   const unsigned BH = static_cast<unsigned>(P.B * P.H);
   HQKV_REQUIRE(P.nk_chunks <= 65535 && P.nv_chunks <= 65535, "decode: too many chunks");
   {
