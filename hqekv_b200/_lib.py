@@ -14,6 +14,7 @@ LIB_PATH = os.path.join(HERE, "libhqkv.so")
 NUM_TIERS = 5
 TIER_BITS = (16, 8, 4, 2, 1)
 WS_COUNTER_BYTES = 4096
+CODEC_UNIFORM, CODEC_NORMAL = 0, 1
 
 
 class HqkvError(RuntimeError):
@@ -25,7 +26,7 @@ class HqkvError(RuntimeError):
 
 
 class Tier(C.Structure):
-    _fields_ = [("bits", C.c_int32), ("n_k", C.c_int32), ("n_v", C.c_int32), ("pad_", C.c_int32),
+    _fields_ = [("bits", C.c_int32), ("n_k", C.c_int32), ("n_v", C.c_int32), ("codec", C.c_int32),
                 ("k_data", C.c_void_p), ("k_scale", C.c_void_p), ("k_zero", C.c_void_p), ("k_idx", C.c_void_p),
                 ("v_data", C.c_void_p), ("v_scale", C.c_void_p), ("v_zero", C.c_void_p), ("v_idx", C.c_void_p)]
 
@@ -38,7 +39,7 @@ class CacheDesc(C.Structure):
 
 class FlushSrc(C.Structure):
     _fields_ = [("data", C.c_void_p * NUM_TIERS), ("scale", C.c_void_p * NUM_TIERS), ("zero", C.c_void_p * NUM_TIERS),
-                ("n", C.c_int32 * NUM_TIERS), ("pad_", C.c_int32), ("residual", C.c_void_p),
+                ("n", C.c_int32 * NUM_TIERS), ("low_codec", C.c_int32), ("residual", C.c_void_p),
                 ("residual_b_stride", C.c_int64), ("residual_h_stride", C.c_int64)]
 
 
@@ -47,6 +48,10 @@ _SIGNATURES = {
     "hqkv_version": (C.c_int, []),
     "hqkv_quantize_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                      C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hqkv_normal1_quantize_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
+                                             C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
+    "hqkv_normal1_dequantize_unpack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int,
+                                                 C.c_void_p, C.c_void_p]),
     "hqkv_dequantize_unpack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_int,
                                          C.c_void_p, C.c_void_p]),
     "hqkv_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),

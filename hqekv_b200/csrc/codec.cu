@@ -273,6 +273,60 @@ static int launch_quant_rows(const __half* x, int64_t rows, int64_t T, int64_t i
   return 0;
 }
 
+
+// ------------------------------------------------------------------------------------------------
+// Gaussian-codebook codec at 1 bit (the low tier of 'high_uniform_group_low_normal_group')
+// ------------------------------------------------------------------------------------------------
+// One thread per group, two passes over its `group` elements.  std and mean are the unbiased
+// torch.std_mean of the group computed in fp64 (the sum of fp16 values is exact there) and rounded ONCE
+// to fp16, which is what torch returns for fp16 input; then (x - mean) / std in fp16 with a rounding after
+// each step, code = 1 where the quotient is > 0 (decision bounds [0, inf]; NaN gives 0).
+__global__ void __launch_bounds__(128) normal1_quantize_kernel(const __half* __restrict__ x, int64_t rows, int64_t T,
+                                                               int64_t inner, int64_t outer_stride, int64_t inner_stride,
+                                                               int64_t t_stride, int group, uint32_t* __restrict__ code,
+                                                               __half* __restrict__ std_out, __half* __restrict__ mean_out) {
+  const int64_t G = T / group;
+  const int64_t gid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (gid >= rows * G) return;
+  const int64_t row = gid / G, gi = gid - row * G;
+  const __half* src = x + (row / inner) * outer_stride + (row % inner) * inner_stride + gi * group * t_stride;
+  double sum = 0.0;
+  for (int t = 0; t < group; ++t) sum += static_cast<double>(__half2float(src[t * t_stride]));
+  const double mean64 = sum / group;
+  double ss = 0.0;
+  for (int t = 0; t < group; ++t) {
+    const double d = static_cast<double>(__half2float(src[t * t_stride])) - mean64;
+    ss += d * d;
+  }
+  const __half mean = __double2half(mean64);
+  const __half sd = normal1_sd(ss, group);
+  uint32_t* dst = code + (row * T + gi * group) / 32;
+  for (int w = 0; w < group / 32; ++w) {
+    uint32_t word = 0;
+    for (int i = 0; i < 32; ++i) {
+      word |= normal1_code(src[(w * 32 + i) * t_stride], mean, sd) << i;
+    }
+    dst[w] = word;
+  }
+  std_out[gid] = sd;
+  mean_out[gid] = mean;
+}
+
+// x = half(half(center[code] * std) + mean), center = +-fp16(0.67448974); one thread per packed word
+__global__ void __launch_bounds__(256) normal1_dequantize_kernel(const uint32_t* __restrict__ code,
+                                                                 const __half* __restrict__ sd,
+                                                                 const __half* __restrict__ mean, int64_t n_words,
+                                                                 int group, __half* __restrict__ out) {
+  const int64_t w = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (w >= n_words) return;
+  const uint32_t word = code[w];
+  const int64_t gi = (w * 32) / group;
+  const __half s = sd[gi], m = mean[gi];
+  const __half cpos = __float2half_rn(HQKV_NORMAL1_CENTER), cneg = __float2half_rn(-HQKV_NORMAL1_CENTER);
+  __half* dst = out + w * 32;
+  for (int i = 0; i < 32; ++i) dst[i] = h_add(h_mul((word >> i) & 1u ? cpos : cneg, s), m);
+}
+
 }  // namespace hqkv
 
 using namespace hqkv;
@@ -394,5 +448,36 @@ extern "C" int hqkv_unpack(const void* words, int64_t rows, int64_t W, int bits,
     default: unpack_kernel<1><<<blocks, 256, 0, st>>>(w, n_words, o); break;
   }
   HQKV_LAUNCH_CHECK("unpack");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_normal1_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, int64_t outer_stride,
+                                          int64_t inner_stride, int64_t t_stride, int group, void* code, void* std_out,
+                                          void* mean_out, void* stream) {
+  HQKV_REQUIRE(valid_group(group), "normal1_quantize_pack: group size must be 32, 64 or 128 (got %d)", group);
+  HQKV_REQUIRE(rows >= 0 && T >= 0 && inner > 0, "normal1_quantize_pack: negative size");
+  HQKV_REQUIRE(T % group == 0, "normal1_quantize_pack: T (%lld) is not a multiple of the group size %d", (long long)T, group);
+  HQKV_REQUIRE(rows % inner == 0, "normal1_quantize_pack: rows is not a multiple of inner");
+  if (rows == 0 || T == 0) return HQKV_OK;
+  HQKV_REQUIRE(x && code && std_out && mean_out, "normal1_quantize_pack: null pointer");
+  const int64_t groups = rows * (T / group);
+  normal1_quantize_kernel<<<static_cast<unsigned>(ceil_div(groups, 128)), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(x), rows, T, inner, outer_stride, inner_stride, t_stride, group,
+      static_cast<uint32_t*>(code), static_cast<__half*>(std_out), static_cast<__half*>(mean_out));
+  HQKV_LAUNCH_CHECK("normal1_quantize_pack");
+  return HQKV_OK;
+}
+
+extern "C" int hqkv_normal1_dequantize_unpack(const void* code, const void* std_in, const void* mean_in, int64_t rows,
+                                              int64_t T, int group, void* out, void* stream) {
+  HQKV_REQUIRE(valid_group(group), "normal1_dequantize_unpack: group size must be 32, 64 or 128 (got %d)", group);
+  HQKV_REQUIRE(rows >= 0 && T >= 0 && T % group == 0, "normal1_dequantize_unpack: bad sizes");
+  if (rows == 0 || T == 0) return HQKV_OK;
+  HQKV_REQUIRE(code && std_in && mean_in && out, "normal1_dequantize_unpack: null pointer");
+  const int64_t n_words = rows * T / 32;
+  normal1_dequantize_kernel<<<static_cast<unsigned>(ceil_div(n_words, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(code), static_cast<const __half*>(std_in), static_cast<const __half*>(mean_in),
+      n_words, group, static_cast<__half*>(out));
+  HQKV_LAUNCH_CHECK("normal1_dequantize_unpack");
   return HQKV_OK;
 }

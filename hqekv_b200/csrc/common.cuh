@@ -108,6 +108,17 @@ __device__ __forceinline__ __half dequant_2r(uint32_t code, __half scale, __half
   return h_add(h_mul(__uint2half_rn(code), scale), mn);
 }
 
+// Gaussian-codebook codec at 1 bit.  std and mean of a group are torch.std_mean (unbiased) of its fp16
+// values: computed in fp64 (the sum of up to 128 fp16 values is exact there) and rounded once to fp16.
+__device__ __forceinline__ __half normal1_sd(double sum_sq_dev, int group) {
+  return __double2half(sqrt(sum_sq_dev / (group - 1)));
+}
+// code = 1 where half(half(x - mean) / std) > 0 (decision bounds [0, inf]); a NaN quotient gives 0
+__device__ __forceinline__ uint32_t normal1_code(__half x, __half mean, __half sd) {
+  return __half2float(h_div(h_sub(x, mean), sd)) > 0.f ? 1u : 0u;
+}
+#define HQKV_NORMAL1_CENTER 0.67448974f
+
 __device__ __forceinline__ __half h_min(__half a, __half b) { return __half2float(b) < __half2float(a) ? b : a; }
 __device__ __forceinline__ __half h_max(__half a, __half b) { return __half2float(b) > __half2float(a) ? b : a; }
 

@@ -43,6 +43,7 @@ struct TierDev {
   const int64_t* v_idx;
   int n_k, n_v;
   int bits;
+  int normal;  // 1-bit tier in the Gaussian-codebook codec: value = std * (+-C) + mean, scale slots = std, zero = mean
   int k_chunk0, k_chunk_tokens;  // first chunk id of this tier in the k_pass grid, tokens per chunk
   int v_chunk0, v_chunk_tokens;
 };
@@ -394,7 +395,10 @@ __device__ __forceinline__ uint32_t pack_lo16(uint32_t a, uint32_t b) { return _
 // Zq[group][head] of the tile for half hh of the heads: rows of the A operand are the tile's groups
 // (at most four; rows 4-7 repeat them, rows 8-15 are zero).  zrow: this lane's two staged zero rows
 // (channels 2*tig and 2*tig+1) at the half of the tile's first group.
-__device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, const __half* z_even, const __half* z_odd) {
+// Gaussian-codebook tier (s_even / s_odd non-null: the std rows at the same halves): a value is
+// std * C * (2 code - 1) + mean, so the term that does not depend on the code is sum_c (mean - C std) q.
+__device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, const __half* z_even, const __half* z_odd,
+                                          const __half* s_even = nullptr, const __half* s_odd = nullptr) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int gam = g & 3;
   float zacc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -405,6 +409,19 @@ __device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, 
     const uint32_t a2 = pack_lo16(__half_as_ushort(z_even[o + 8 * K_RAW_HALFS]), __half_as_ushort(z_odd[o + 8 * K_RAW_HALFS]));
     const uint2 bq = sh.qb[hh][kt][lane];
     mma16816(zacc, a0, 0u, a2, 0u, bq.x, bq.y);
+  }
+  if (s_even) {
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int kt = 0; kt < 8; ++kt) {
+      const int o = (16 * kt) * K_RAW_HALFS + gam;
+      const uint32_t a0 = pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]), __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS]));
+      const uint2 bq = sh.qb[hh][kt][lane];
+      mma16816(sacc, a0, 0u, a2, 0u, bq.x, bq.y);
+    }
+    zacc[0] = fmaf(-HQKV_NORMAL1_CENTER, sacc[0], zacc[0]);
+    zacc[1] = fmaf(-HQKV_NORMAL1_CENTER, sacc[1], zacc[1]);
   }
   __syncwarp();  // readers of the previous half are done
   if (g < 4 && tig < 2) {  // columns 0-3 are the four heads of this half; 4-7 repeat them
@@ -502,9 +519,16 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
     }
   }
   const int hp = tig & 1;
+  // Gaussian-codebook 1-bit tier: the code term carries the factor 2C
+  const bool normal = BITS == 1 && T.normal != 0;
+  const float pscale = normal ? P.scale * (2.f * HQKV_NORMAL1_CENTER) : P.scale;
 
   for (int hh = 0; hh < nh; ++hh) {
-    k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0]);
+    if (normal)
+      k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0], &sh.s[2 * tig][sh_even + gt0],
+                &sh.s[2 * tig + 1][sh_odd + gt0]);
+    else
+      k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0]);
     const uint2* qb = &sh.qb[hh][0][lane];
 #pragma unroll 1
     for (int j = 0; j < TL::NSUB; ++j) {
@@ -635,7 +659,7 @@ HQKV_UNROLL(K_KK_UNROLL)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
-          x[i] = on ? fmaf(val[i][e], P.scale * unscale, zqs) : -INFINITY;
+          x[i] = on ? fmaf(val[i][e], pscale * unscale, zqs) : -INFINITY;
           if (on) row[pos[i]] = x[i];
         }
         softmax_push4(m[hh][e], l[hh][e], x);
@@ -1071,7 +1095,7 @@ __device__ __forceinline__ void v_tile_probs(const DecodeParams& P, const VShare
 // (channels x heads, see the channel map in v_tile_store), zacc = zero term rows.
 template <int BITS>
 __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& ws, const __half (*prow)[V_PROW], int ntok,
-                                            float (&acc)[8][4], float (&zacc)[4]) {
+                                            float (&acc)[8][4], float (&zacc)[4], bool normal) {
   using TL = VTile<BITS>;
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int ng_shift = 7 - P.gv_shift;  // log2(groups per token): 2, 1, 0
@@ -1090,6 +1114,7 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
 #pragma unroll
   for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
   zacc[0] = zacc[1] = zacc[2] = zacc[3] = 0.f;
+  float sacc[4] = {0.f, 0.f, 0.f, 0.f};  // Gaussian-codebook tier: sum_t p * std per channel group
 
   const int nsteps = ntok >> 4;
 HQKV_UNROLL(V_STEP_UNROLL)
@@ -1116,6 +1141,11 @@ HQKV_UNROLL(V_STEP_UNROLL)
       const uint32_t a0 = pack_lo16(__half_as_ushort(zb[zg]), __half_as_ushort(zb[(1 << ng_shift) + zg]));
       const uint32_t a2 = pack_lo16(__half_as_ushort(zb[(8 << ng_shift) + zg]), __half_as_ushort(zb[(9 << ng_shift) + zg]));
       mma16816(zacc, a0, 0u, a2, 0u, p0, p1);
+    }
+    if (BITS == 1 && normal) {
+      const uint32_t a0 = pack_lo16(__half_as_ushort(sb[zg]), __half_as_ushort(sb[(1 << ng_shift) + zg]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(sb[(8 << ng_shift) + zg]), __half_as_ushort(sb[(9 << ng_shift) + zg]));
+      mma16816(sacc, a0, 0u, a2, 0u, p0, p1);
     }
     const unsigned char* rowp = ws.u.codes;
     if constexpr (BITS == 1) {
@@ -1191,6 +1221,10 @@ HQKV_UNROLL(V_STEP_UNROLL)
         }
     }
   }
+  if (BITS == 1 && normal) {  // value = std * C * (2 code - 1) + mean: the code-free term is sum_t p (mean - C std)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) zacc[i] = fmaf(-HQKV_NORMAL1_CENTER, sacc[i], zacc[i]);
+  }
 }
 
 // Accumulators of one walk -> red[head of this half][channel] (every element has exactly one owner).
@@ -1203,13 +1237,13 @@ HQKV_UNROLL(V_STEP_UNROLL)
 //                      1 bit   mt = 4c + f      : row g = 64c + 16(g&3) + 4(g>>2) + f, row g+8 = +8
 //                              (owned by the lanes with ((g & 3) < 2) == (tig < 2))
 template <int BITS>
-__device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)[8][4]) {
+__device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)[8][4], float gain) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int hp = tig & 1, r = tig >> 1;
 #pragma unroll
   for (int mt = 0; mt < 8; ++mt) {
     const int f = BITS == 8 ? (mt & 1) : (mt & 3);
-    const float unscale = static_cast<float>(1 << (24 - VField<BITS>::shift(f)));
+    const float unscale = static_cast<float>(1 << (24 - VField<BITS>::shift(f))) * gain;
     if constexpr (BITS <= 2) {
       const bool mine = BITS == 2 ? (g < 4) == (tig < 2) : ((g & 3) < 2) == (tig < 2);
       if (mine) {
@@ -1244,9 +1278,10 @@ __device__ __forceinline__ void v_tile(const DecodeParams& P, const TierDev& T, 
   __syncwarp();
   for (int hh = 0; hh < nh; ++hh) {
     float acc[8][4], zacc[4];
-    v_tile_walk<BITS>(P, ws, hh ? ws.p_hi : ws.v.a.p, ntok, acc, zacc);
+    const bool normal = BITS == 1 && T.normal != 0;
+    v_tile_walk<BITS>(P, ws, hh ? ws.p_hi : ws.v.a.p, ntok, acc, zacc, normal);
     __syncwarp();  // all lanes are done with the codes (last walk) or with p of heads 0-3 (first of two)
-    v_tile_store<BITS>(hh + 1 < nh ? ws.v.red0 : ws.u.red, acc);
+    v_tile_store<BITS>(hh + 1 < nh ? ws.v.red0 : ws.u.red, acc, normal ? 2.f * HQKV_NORMAL1_CENTER : 1.f);
     if (g < 4 && tig < 2) {
       ws.zt[g][4 * hh + 2 * tig] = zacc[0];
       ws.zt[g][4 * hh + 2 * tig + 1] = zacc[1];
@@ -1560,6 +1595,10 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.n_v = s.n_v;
     if (s.n_k > 0 || s.n_v > 0) {
       HQKV_REQUIRE(s.bits == expect_bits[t], "decode: tier %d must hold %d-bit data (got %d)", t, expect_bits[t], s.bits);
+      HQKV_REQUIRE(s.codec == HQKV_CODEC_UNIFORM || (s.codec == HQKV_CODEC_NORMAL && s.bits == 1),
+                   "decode: tier %d: codec %d is not valid at %d bits (the Gaussian codebook is built for the 1-bit tier)", t,
+                   s.codec, s.bits);
+      d.normal = s.codec == HQKV_CODEC_NORMAL ? 1 : 0;
     }
     if (s.n_k > 0) {
       HQKV_REQUIRE(s.k_data && s.k_idx, "decode: tier %d K pointers are null", t);

@@ -381,6 +381,7 @@ struct BuildArgs {
   const __half* residual;
   int64_t res_b_stride, res_h_stride;
   int B, H, group, gshift, dst_tier, dst_bits;
+  int normal_dst;  // the destination is the 1-bit tier in the Gaussian-codebook codec
   const int32_t* plan;  // [n_dst]
   int64_t n_dst;
   void* out_data;
@@ -430,6 +431,25 @@ __global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant_
     const int64_t gi = row * (n >> A.gshift) + (pos0 >> A.gshift);
     A.out_scale[row * Gd + jg] = A.scale[src][gi];
     A.out_zero[row * Gd + jg] = A.zero[src][gi];
+    return;
+  }
+  if (A.normal_dst) {  // group statistics in fp64, then one code per token
+    double sum = 0.0;
+    for (int i = 0; i < A.group; ++i) sum += static_cast<double>(__half2float(k_src_value(A, src, pos0 + i, b, h, d)));
+    const double mean64 = sum / A.group;
+    double ss = 0.0;
+    for (int i = 0; i < A.group; ++i) {
+      const double dv = static_cast<double>(__half2float(k_src_value(A, src, pos0 + i, b, h, d))) - mean64;
+      ss += dv * dv;
+    }
+    const __half mean = __double2half(mean64), sd = normal1_sd(ss, A.group);
+    for (int w = 0; w < wpg; ++w) {
+      uint32_t word = 0;
+      for (int i = 0; i < 32; ++i) word |= normal1_code(k_src_value(A, src, pos0 + w * 32 + i, b, h, d), mean, sd) << i;
+      dst[w] = word;
+    }
+    A.out_scale[row * Gd + jg] = sd;
+    A.out_zero[row * Gd + jg] = mean;
     return;
   }
   const float levels = static_cast<float>((1 << bits) - 1);
@@ -502,21 +522,42 @@ __global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constan
     return;
   }
   // ---- quantise groups of `group` channels = group/4 adjacent lanes
-  const float levels = static_cast<float>((1 << bits) - 1);
-  __half lo = v[0], hi = v[0];
-#pragma unroll
-  for (int i = 1; i < 4; ++i) {
-    lo = h_min(lo, v[i]);
-    hi = h_max(hi, v[i]);
-  }
-  for (int off = 1; off < (A.group >> 2); off <<= 1) {
-    lo = h_min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
-    hi = h_max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
-  }
-  const __half sc = quant_scale(lo, hi, levels);
+  __half lo, sc;  // zero and scale of the group (mean and std in the Gaussian-codebook codec)
   uint32_t part = 0;
+  if (A.normal_dst) {
+    double sum = 0.0;
 #pragma unroll
-  for (int i = 0; i < 4; ++i) part |= quant_code_fast(v[i], quant_group(lo, sc, levels)) << (i * bits);
+    for (int i = 0; i < 4; ++i) sum += static_cast<double>(__half2float(v[i]));
+    for (int off = 1; off < (A.group >> 2); off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const double mean64 = sum / A.group;
+    double ss = 0.0;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const double dv = static_cast<double>(__half2float(v[i])) - mean64;
+      ss += dv * dv;
+    }
+    for (int off = 1; off < (A.group >> 2); off <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, off);
+    lo = __double2half(mean64);
+    sc = normal1_sd(ss, A.group);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) part |= normal1_code(v[i], lo, sc) << i;
+  } else {
+    const float levels = static_cast<float>((1 << bits) - 1);
+    __half hi = v[0];
+    lo = v[0];
+#pragma unroll
+    for (int i = 1; i < 4; ++i) {
+      lo = h_min(lo, v[i]);
+      hi = h_max(hi, v[i]);
+    }
+    for (int off = 1; off < (A.group >> 2); off <<= 1) {
+      lo = h_min(lo, __shfl_xor_sync(0xffffffffu, lo, off));
+      hi = h_max(hi, __shfl_xor_sync(0xffffffffu, hi, off));
+    }
+    sc = quant_scale(lo, hi, levels);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) part |= quant_code_fast(v[i], quant_group(lo, sc, levels)) << (i * bits);
+  }
   const int lpw = 32 / (4 * bits);  // lanes per word: 1, 2, 4, 8 for 8, 4, 2, 1 bits
   for (int off = 1; off < lpw; off <<= 1) {
     const uint32_t other = __shfl_down_sync(0xffffffffu, part, off);
@@ -571,6 +612,9 @@ static int fill_build_args(BuildArgs& A, const hqkv_flush_src_t* src, int B, int
   A.gshift = ilog2(group);
   A.dst_tier = dst_tier;
   A.dst_bits = 16 >> dst_tier;
+  HQKV_REQUIRE(src->low_codec == HQKV_CODEC_UNIFORM || src->low_codec == HQKV_CODEC_NORMAL, "%s: unknown low_codec %d",
+               who, src->low_codec);
+  A.normal_dst = (A.dst_bits == 1 && src->low_codec == HQKV_CODEC_NORMAL) ? 1 : 0;
   A.plan = plan;
   A.n_dst = n_dst;
   A.out_data = out_data;

@@ -59,8 +59,9 @@ def cache_geometry(cache):
     return B, H, D, n, r, dev
 
 
-def build_cache_desc(cache, nh_q, block_size, group_size):
-    """Fill a CacheDesc for hqkv_decode_attention.  Returns (desc, keepalive, L)."""
+def build_cache_desc(cache, nh_q, block_size, group_size, low_codec=0):
+    """Fill a CacheDesc for hqkv_decode_attention.  ``low_codec``: codec of the 1-bit tier
+    (0 uniform, 1 Gaussian codebook).  Returns (desc, keepalive, L)."""
     B, H, D, n, r, dev = cache_geometry(cache)
     desc = CacheDesc()
     desc.B, desc.H, desc.nh_q, desc.D = B, H, nh_q, D
@@ -74,6 +75,7 @@ def build_cache_desc(cache, nh_q, block_size, group_size):
         keep += [kd, ki, ks, kz, vd, vi, vs, vz]
         tier = desc.tier[t]
         tier.bits = bits
+        tier.codec = low_codec if bits == 1 else 0
         tier.n_k = 0 if ki is None else ki.numel()
         tier.n_v = 0 if vi is None else vi.numel()
         n_k_total += tier.n_k
@@ -98,7 +100,7 @@ _desc_memo = {}
 _DESC_MEMO_MAX = 512
 
 
-def cached_cache_desc(cache, nh_q, block_size, group_size):
+def cached_cache_desc(cache, nh_q, block_size, group_size, low_codec=0):
     """Like :func:`build_cache_desc`, but the tier part of the descriptor is remembered between calls.
 
     During decoding the 36 tier slots of a layer's tuple are the same tensor objects from one flush to
@@ -108,7 +110,7 @@ def cached_cache_desc(cache, nh_q, block_size, group_size):
     entry) and only the residual fields are refreshed.  Tiers that are not contiguous take the
     uncached path.  Returns (desc, keepalive, L, device)."""
     tiers = cache[:36]
-    key = (nh_q, block_size, group_size) + tuple(map(id, tiers))
+    key = (nh_q, block_size, group_size, low_codec) + tuple(map(id, tiers))
     ent = _desc_memo.get(key)
     if ent is not None:
         for r in ent.refs:
@@ -118,8 +120,8 @@ def cached_cache_desc(cache, nh_q, block_size, group_size):
     nk, nv = cache[SLOT_NEW_K], cache[SLOT_NEW_V]
     if ent is None:
         if all(t is None for t in tiers) or any(t is not None and not t.is_contiguous() for t in tiers):
-            return build_cache_desc(cache, nh_q, block_size, group_size)
-        desc, _, L, dev = build_cache_desc(cache, nh_q, block_size, group_size)
+            return build_cache_desc(cache, nh_q, block_size, group_size, low_codec)
+        desc, _, L, dev = build_cache_desc(cache, nh_q, block_size, group_size, low_codec)
         ent = _DescEntry()
         ent.desc, ent.dev = desc, dev
         ent.n_quantised = L - (0 if nv is None else nv.shape[2])
@@ -140,8 +142,9 @@ def cached_cache_desc(cache, nh_q, block_size, group_size):
     return desc, (nk, nv), ent.n_quantised + r, ent.dev if ent.dev is not None else nv.device
 
 
-def build_flush_src(cache, side, residual):
+def build_flush_src(cache, side, residual, low_codec=0):
     src = FlushSrc()
+    src.low_codec = low_codec
     keep = []
     for t, bits in enumerate(TIER_BITS):
         d, i, s, z = (_c(x) for x in tier_tensors(cache, bits, side))

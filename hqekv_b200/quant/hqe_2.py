@@ -9,15 +9,16 @@ copy of ten integers in between to size the new tensors.
 """
 import torch
 
-from .._lib import TIER_BITS, check, lib, ptr, require_cuda, stream_ptr
+from .._lib import CODEC_NORMAL, CODEC_UNIFORM, TIER_BITS, check, lib, ptr, require_cuda, stream_ptr
 from ..model.public_func import calculate_token_range, get_block_token_idx, last_attn_weights
 from ._cache import (NUM_SLOTS, SLOT_K, SLOT_NEW_K, SLOT_NEW_V, SLOT_SEQ_LEN, SLOT_V, SLOT_V_TOKEN_NORM,
                      build_flush_src, cache_geometry, tier_tensors, void_p_array)
-from .pack_unpack import uniform_group_dequantize_unpack_last_dim
+from .pack_unpack import normal_group_dequantize_unpack_last_dim, uniform_group_dequantize_unpack_last_dim
 
 import ctypes as C
 
-_FLUSH_STRATEGIES = ("uniform_group",)
+# strategies built here -> codec of the 1-bit tier (every other tier is uniform in both)
+_FLUSH_STRATEGIES = {"uniform_group": CODEC_UNIFORM, "high_uniform_group_low_normal_group": CODEC_NORMAL}
 _KNOWN_STRATEGIES = ("uniform", "normal", "uniform_group", "normal_group", "high_uniform_group_low_normal_group")
 
 
@@ -50,9 +51,9 @@ def _plan_side(cache, side, hist, compress, sorted_idx, bit_num, dev, out_counts
     return plan_src, plan_ids, survivors, (idx_lists, sorted_idx, ws)
 
 
-def _build_side(cache, side, residual, plan_src, plan_ids, counts, B, H, D, group, dev):
+def _build_side(cache, side, residual, plan_src, plan_ids, counts, B, H, D, group, dev, low_codec):
     """Build the five destination tiers of one side.  Returns [(data, idx, scale, zero)] * 5."""
-    src, keep = build_flush_src(cache, side, residual)
+    src, keep = build_flush_src(cache, side, residual, low_codec)
     build = lib.hqkv_flush_build_k if side == "K" else lib.hqkv_flush_build_v
     out = []
     for t, bits in enumerate(TIER_BITS):
@@ -89,14 +90,17 @@ def KV_cache_hqe_2(past_key_value: tuple, compress_length: int, history_length: 
     importance / block_size, because get_block_token_idx divides its argument in place); V is ranked
     here from it (times the per-token value range when ``times_range``).  ``last_weights`` and
     slot 38 (V_token_norm) are compacted to the V-side survivors.  Returns the new 42-slot tuple.
-    Only quant_strategy='uniform_group' is built; the other strategy names of the reference raise
-    NotImplementedError, unknown names ValueError('invalid quant_strategy').
+    quant_strategy 'uniform_group' and 'high_uniform_group_low_normal_group' (1-bit tier in the
+    Gaussian-codebook codec, slots +2/+3 then hold std/mean) are built; the other strategy names of the
+    reference raise NotImplementedError, unknown names ValueError('invalid quant_strategy').
     """
     if quant_strategy not in _KNOWN_STRATEGIES:
         raise ValueError("invalid quant_strategy")
     if quant_strategy not in _FLUSH_STRATEGIES:
-        raise NotImplementedError(f"KV_cache_hqe_2: quant_strategy '{quant_strategy}' needs the Gaussian-codebook or "
-                                  "un-grouped codec, which is not built; use 'uniform_group'")
+        raise NotImplementedError(f"KV_cache_hqe_2: quant_strategy '{quant_strategy}' needs the un-grouped codec or the "
+                                  "Gaussian codebook above 1 bit, which are not built; use 'uniform_group' or "
+                                  "'high_uniform_group_low_normal_group'")
+    low_codec = _FLUSH_STRATEGIES[quant_strategy]
     if len(past_key_value) != NUM_SLOTS:
         raise ValueError("invalid past_key_value")
     cache = tuple(past_key_value)
@@ -128,8 +132,8 @@ def KV_cache_hqe_2(past_key_value: tuple, compress_length: int, history_length: 
         vp_src, vp_ids, v_surv, keep_v = _plan_side(cache, "V", history_length, compress_length, V_sorted_idx,
                                                     V_bit_num, dev, counts_dev[1])
         counts = counts_dev.cpu().tolist()  # the one synchronisation of the flush
-        outK = _build_side(cache, "K", flush_K, kp_src, kp_ids, counts[0], B, H, D, block_size, dev)
-        outV = _build_side(cache, "V", flush_V, vp_src, vp_ids, counts[1], B, H, D, group_size, dev)
+        outK = _build_side(cache, "K", flush_K, kp_src, kp_ids, counts[0], B, H, D, block_size, dev, low_codec)
+        outV = _build_side(cache, "V", flush_V, vp_src, vp_ids, counts[1], B, H, D, group_size, dev, low_codec)
         if counts[1][6]:  # something was evicted on the V side: compact the range vector and the ring
             surv = v_surv[:counts[1][5]]
             norm = norm[surv]
@@ -161,6 +165,13 @@ def KV_cache_reconstruct_hqe(past_key_value: tuple, quant_strategy: str, block_s
         raise ValueError("invalid quant_strategy")
     if quant_strategy not in _FLUSH_STRATEGIES:
         raise NotImplementedError(f"KV_cache_reconstruct_hqe: quant_strategy '{quant_strategy}' is not built")
+    normal_low = _FLUSH_STRATEGIES[quant_strategy] == CODEC_NORMAL
+
+    def dense_of(data, a, b, group, bits):
+        if bits == 1 and normal_low:
+            return normal_group_dequantize_unpack_last_dim(data, a, b, group, bits)
+        return uniform_group_dequantize_unpack_last_dim(data, a, b, group, bits)
+
     cache = tuple(past_key_value)
     B, H, D, n, r, dev = cache_geometry(cache)
     L = n + r
@@ -169,11 +180,11 @@ def KV_cache_reconstruct_hqe(past_key_value: tuple, quant_strategy: str, block_s
     for bits in TIER_BITS:
         kd, ki, ks, kz = tier_tensors(cache, bits, "K")
         if kd is not None:
-            dense = kd if bits == 16 else uniform_group_dequantize_unpack_last_dim(kd, ks, kz, block_size, bits)
+            dense = kd if bits == 16 else dense_of(kd, ks, kz, block_size, bits)
             K[:, :, ki, :] = dense.transpose(2, 3)
         vd, vi, vs, vz = tier_tensors(cache, bits, "V")
         if vd is not None:
-            dense = vd if bits == 16 else uniform_group_dequantize_unpack_last_dim(vd, vs, vz, group_size, bits)
+            dense = vd if bits == 16 else dense_of(vd, vs, vz, group_size, bits)
             V[:, :, vi, :] = dense
     if r:
         K[:, :, L - r:, :] = cache[SLOT_NEW_K]

@@ -7,7 +7,7 @@ from typing import Tuple
 
 import torch
 
-from .._lib import HqkvError, check, decode_workspace, lib, ptr, require_cuda, stream_ptr
+from .._lib import CODEC_NORMAL, CODEC_UNIFORM, HqkvError, check, decode_workspace, lib, ptr, require_cuda, stream_ptr
 from ._cache import UNIFORM_STRATEGIES, cached_cache_desc
 
 
@@ -20,20 +20,19 @@ def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: tor
     ``head_dim`` is re-derived from the cache as the reference does (:379-404).
     Returns (attn_weights [B, nh_q, 1, L] float16, attn_output [B, nh_q, 1, D] float16).
     Raises ValueError('invalid quant_strategy') / ValueError('invalid past_key_value') like the
-    reference.  All five tiers are uniform-group tiers here (the Gaussian-codebook 1-bit codec is not built).
+    reference.  Under 'uniform_group' all five tiers are uniform-group tiers; under
+    'high_uniform_group_low_normal_group' the 1-bit tier is read in the Gaussian-codebook codec
+    (slots +2 / +3 hold std / mean; cuda_bmm_fA_qB_normal_group, quant/matmul.py:72-95).
     """
     if quant_strategy not in UNIFORM_STRATEGIES:
         raise ValueError("invalid quant_strategy")
     if len(past_key_value) != 42:
         raise ValueError("invalid past_key_value")
-    if quant_strategy != "uniform_group" and (past_key_value[28] is not None or past_key_value[32] is not None):
-        # under 'high_uniform_group_low_normal_group' the 1-bit slots hold (std, mean) of the Gaussian codebook
-        raise NotImplementedError("qkv_matmul_hqe_2: the Gaussian-codebook 1-bit tier of "
-                                  f"quant_strategy '{quant_strategy}' is not built; 'uniform_group' reads all tiers")
+    low_codec = CODEC_UNIFORM if quant_strategy == "uniform_group" else CODEC_NORMAL
     require_cuda(q)
     if q.dtype != torch.float16 or q.dim() != 4 or q.shape[2] != 1:
         raise ValueError("q must be float16 of shape [B, nh_q, 1, head_dim]")
-    desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+    desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size, low_codec)
     if dev != q.device or q.shape[0] != desc.B or q.shape[3] != desc.D:
         raise ValueError("q does not match the cache (device, batch or head_dim)")
     q = q.contiguous()

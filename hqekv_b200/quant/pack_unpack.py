@@ -113,8 +113,57 @@ def _not_built(name):
 
 normal_quantize_pack_last_dim = _not_built("normal_quantize_pack_last_dim")
 normal_dequantize_unpack_last_dim = _not_built("normal_dequantize_unpack_last_dim")
-normal_group_quantize_pack_last_dim = _not_built("normal_group_quantize_pack_last_dim")
-normal_group_dequantize_unpack_last_dim = _not_built("normal_group_dequantize_unpack_last_dim")
-normal_group_fake_quant = _not_built("normal_group_fake_quant")
+
+
+def normal_group_quantize_pack_last_dim(data: torch.Tensor, group_size: int, bit: int):
+    """quant/pack_unpack.py:218-253 at bit = 1 (the only width the live strategy
+    'high_uniform_group_low_normal_group' uses it at): data fp16 [B, nh, D, T] (any strides) ->
+    (code int32 [B,nh,D,T/32], std fp16 [B,nh,D,T/group], mean fp16 [B,nh,D,T/group]).
+    The source is not modified (the reference overwrites it with the normalised values)."""
+    if bit != 1:
+        raise NotImplementedError("normal_group_quantize_pack_last_dim: only bit = 1 is built in hqekv_b200")
+    require_cuda(data)
+    if data.dtype != torch.float16 or data.dim() != 4:
+        raise ValueError("data must be a 4-D float16 tensor")
+    B, nh, D, T = data.shape
+    if T % group_size:
+        raise ValueError("last dimension must be a multiple of group_size")
+    sb, sh, sd, st = data.stride()
+    if not (B == 1 or sb == nh * sh):
+        data = data.contiguous()
+        sb, sh, sd, st = data.stride()
+    code = torch.empty(B, nh, D, T // 32, dtype=torch.int32, device=data.device)
+    std = torch.empty(B, nh, D, T // group_size, dtype=torch.float16, device=data.device)
+    mean = torch.empty_like(std)
+    with torch.cuda.device(data.device):
+        check(lib.hqkv_normal1_quantize_pack(ptr(data), B * nh * D, T, D, sh, sd, st, group_size, ptr(code), ptr(std),
+                                             ptr(mean), stream_ptr(data.device)))
+    return code, std, mean
+
+
+def normal_group_dequantize_unpack_last_dim(code: torch.Tensor, std: torch.Tensor, mean: torch.Tensor,
+                                            group_size: int, bit: int):
+    """quant/pack_unpack.py:356-376 at bit = 1: x = half(half(center[code] * std) + mean), fp16 [B, nh, D, T]."""
+    if bit != 1:
+        raise NotImplementedError("normal_group_dequantize_unpack_last_dim: only bit = 1 is built in hqekv_b200")
+    require_cuda(code, std, mean)
+    B, nh, D, T_d = code.shape
+    T = T_d * 32
+    code, std, mean = code.contiguous(), std.contiguous(), mean.contiguous()
+    out = torch.empty(B, nh, D, T, dtype=torch.float16, device=code.device)
+    with torch.cuda.device(code.device):
+        check(lib.hqkv_normal1_dequantize_unpack(ptr(code), ptr(std), ptr(mean), B * nh * D, T, group_size, ptr(out),
+                                                 stream_ptr(code.device)))
+    return out
+
+
+def normal_group_fake_quant(data: torch.Tensor, group_size: int, bit: int):
+    """quant/pack_unpack.py:195-216: quantise then dequantise with the Gaussian codebook (bit = 1 only)."""
+    if bit == 0:
+        return 0
+    code, std, mean = normal_group_quantize_pack_last_dim(data, group_size, bit)
+    return normal_group_dequantize_unpack_last_dim(code, std, mean, group_size, bit)
+
+
 uniform_quantize_pack_last_dim = _not_built("uniform_quantize_pack_last_dim")
 uniform_dequantize_unpack_last_dim = _not_built("uniform_dequantize_unpack_last_dim")

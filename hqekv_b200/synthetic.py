@@ -90,7 +90,8 @@ def synthetic_importance(cfg: CacheConfig, device, seed: int, length: int):
     return torch.softmax(logits, dim=-1).sum(0).div_(8).half()
 
 
-def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range: bool = False):
+def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range: bool = False,
+                quant_strategy: str = "uniform_group"):
     """Prefill-shaped K/V -> one flush through KV_cache_hqe_2 -> (cache tuple, q).  With
     ``times_range=False`` K and V are ranked identically, so every rank of a head-sharded run selects
     the same blocks without exchanging value ranges."""
@@ -101,7 +102,7 @@ def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range
     ids = get_block_token_idx(cfg.group, flushed // cfg.group, imp)
     cache = (None,) * 39 + (K, V, cfg.context)
     bit_num = torch.tensor(counts, dtype=torch.int32)
-    cache = KV_cache_hqe_2(cache, flushed, 0, ids, bit_num, bit_num.clone(), imp, "uniform_group", None, cfg.group,
+    cache = KV_cache_hqe_2(cache, flushed, 0, ids, bit_num, bit_num.clone(), imp, quant_strategy, None, cfg.group,
                            cfg.group, times_range)
     return cache, q
 

@@ -71,6 +71,20 @@ int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, in
 int hqkv_dequantize_unpack(const void* code, const void* scale, const void* mn, int64_t rows, int64_t T, int group,
                            int bits, void* out, void* stream);
 
+/*
+ * Gaussian-codebook codec at 1 bit: the quantiser of the 1-bit tier under quant_strategy
+ * 'high_uniform_group_low_normal_group'.  Stands in for normal_group_quantize_pack_last_dim /
+ * normal_group_dequantize_unpack_last_dim with bit = 1 (quant/pack_unpack.py:218-253, 356-376).
+ * std / mean = unbiased torch.std_mean of each group (fp16); code = ((x - mean) / std > 0) with fp16
+ * roundings after the subtract and the divide; x^ = half(half(c * std) + mean), c = +-fp16(0.67448974).
+ * Same source addressing and output layout as hqkv_quantize_pack with bits = 1.
+ */
+int hqkv_normal1_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, int64_t outer_stride,
+                               int64_t inner_stride, int64_t t_stride, int group, void* code, void* std_out,
+                               void* mean_out, void* stream);
+int hqkv_normal1_dequantize_unpack(const void* code, const void* std_in, const void* mean_in, int64_t rows, int64_t T,
+                                   int group, void* out, void* stream);
+
 /* pack_along_last_dim (quant/pack_unpack.py:53-70): int32 codes [rows, T] -> int32 words [rows, T*bits/32]. */
 int hqkv_pack(const void* codes_i32, int64_t rows, int64_t T, int bits, void* words, void* stream);
 
@@ -82,6 +96,11 @@ int hqkv_unpack(const void* words, int64_t rows, int64_t W, int bits, void* out_
  * ------------------------------------------------------------------------------------------- */
 
 #define HQKV_NUM_TIERS 5 /* 16-, 8-, 4-, 2-, 1-bit, in the slot order of the reference's cache tuple */
+#define HQKV_CODEC_UNIFORM 0 /* code * scale + zero (min/max groups) */
+#define HQKV_CODEC_NORMAL 1  /* 1-bit tier only: center[code] * std + mean with the centres -+0.67448974, the
+                                low tier of quant_strategy 'high_uniform_group_low_normal_group'
+                                (quant/hqe_2.py:488-492, quant/pack_unpack.py:6-14, 218-253); the scale slots then
+                                hold std and the zero slots hold mean */
 #define HQKV_MAX_PEERS 7 /* other GPUs a kv-head-sharded decode can write its output rows to */
 
 /* One precision tier of the cache (slots 0-35 of the 42-entry tuple, quant/hqe_matmul.py:364-368). */
@@ -89,7 +108,7 @@ typedef struct {
   int32_t bits; /* 16, 8, 4, 2 or 1 */
   int32_t n_k;  /* tokens held on the K side (0 = tier absent) */
   int32_t n_v;  /* tokens held on the V side */
-  int32_t pad_;
+  int32_t codec; /* HQKV_CODEC_UNIFORM, or HQKV_CODEC_NORMAL (bits == 1 only) */
   const void* k_data;   /* bits<16: int32 [B,H,D,n_k*bits/32]; bits==16: fp16 [B,H,D,n_k]  (channel-major) */
   const void* k_scale;  /* fp16 [B,H,D,n_k/group_k]   (NULL when bits==16) */
   const void* k_zero;   /* fp16 [B,H,D,n_k/group_k] */
@@ -295,7 +314,8 @@ typedef struct {
   const void* scale[HQKV_NUM_TIERS];
   const void* zero[HQKV_NUM_TIERS];
   int32_t n[HQKV_NUM_TIERS];
-  int32_t pad_;
+  int32_t low_codec; /* codec the 1-bit DESTINATION tier is written in (and its kept blocks already are):
+                        HQKV_CODEC_UNIFORM or HQKV_CODEC_NORMAL; the other tiers are always uniform */
   const void* residual; /* fp16 [B,H,r,D] token-major, first `compress` tokens are flushed */
   int64_t residual_b_stride, residual_h_stride; /* elements */
 } hqkv_flush_src_t;

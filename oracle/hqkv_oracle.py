@@ -120,6 +120,54 @@ def dequantize_unpack_last_dim(words, scale, mn, group_size: int, bit: int) -> n
     return out.reshape(*lead, T)
 
 
+# Gaussian-codebook codec at 1 bit: the low tier of quant_strategy 'high_uniform_group_low_normal_group'.
+# Quantile centres norm.ppf(0.25), norm.ppf(0.75) as the reference holds them (float32, then cast to the
+# fp16 of std); the decision bounds are [0, inf] (quant/pack_unpack.py:6-14).
+NORMAL1_CENTER = np.array([-0.67448974, 0.67448974], dtype=F32)
+
+
+def normal1_quantize_codes_last_dim(x: np.ndarray, group_size: int):
+    """normal_group_quantize_pack_last_dim at bit = 1 before packing — quant/pack_unpack.py:218-253.
+
+    std, mean = torch.std_mean (unbiased) of every group, returned in fp16.  torch's result on fp16
+    input equals the exactly computed value rounded once to fp16, which is what float64 gives here.
+    data.sub_(mean), data.div_(std) in fp16 with a rounding after each; code = searchsorted([0, inf], v):
+    0 for v <= 0, 1 for v > 0.  NaN (a constant group: 0/0) is given code 0.
+    Returns (codes int32 [..., T], std f16 [..., T/g], mean f16 [..., T/g])."""
+    x = np.asarray(x, dtype=F16)
+    lead, T = x.shape[:-1], x.shape[-1]
+    if T % group_size:
+        raise ValueError("last dimension must be a multiple of the group size")
+    xg = x.reshape(*lead, T // group_size, group_size)
+    x64 = xg.astype(np.float64)
+    with np.errstate(all="ignore"):
+        mean64 = x64.sum(axis=-1, keepdims=True) / group_size
+        var64 = ((x64 - mean64) ** 2).sum(axis=-1, keepdims=True) / (group_size - 1)
+        mean = mean64.astype(F16)
+        std = np.sqrt(var64).astype(F16)
+        t = _h(_f(xg) - _f(mean))
+        v = _h(_f(t) / _f(std))
+        codes = (_f(v) > 0).astype(np.int32)  # NaN > 0 is False
+    return codes.reshape(*lead, T), std[..., 0], mean[..., 0]
+
+
+def normal1_quantize_pack_last_dim(x: np.ndarray, group_size: int):
+    codes, std, mean = normal1_quantize_codes_last_dim(x, group_size)
+    return pack_last_dim(codes, 1), std, mean
+
+
+def normal1_dequantize_unpack_last_dim(words, std, mean, group_size: int) -> np.ndarray:
+    """normal_group_dequantize_unpack_last_dim at bit = 1 — quant/pack_unpack.py:356-376:
+    x = half(half(center[code] * std) + mean) with center cast to fp16 first."""
+    codes = unpack_last_dim(words, 1).astype(np.int64)
+    lead, T = codes.shape[:-1], codes.shape[-1]
+    cg = NORMAL1_CENTER.astype(F16)[codes].reshape(*lead, T // group_size, group_size)
+    with np.errstate(all="ignore"):
+        prod = _h(_f(cg) * _f(std)[..., None])
+        out = _h(_f(prod) + _f(mean)[..., None])
+    return out.reshape(*lead, T)
+
+
 # ==========================================================================================
 # importance bookkeeping, token range, block ranking
 # ==========================================================================================
@@ -290,22 +338,36 @@ def _rerank(id_lists):
     return [None if x is None else np.searchsorted(allv, x).astype(np.int64) for x in id_lists]
 
 
-def _requant(values_last_dim: np.ndarray, group: int, bit: int):
+STRATEGIES = ("uniform_group", "high_uniform_group_low_normal_group")
+
+
+def _low_is_normal(quant_strategy: str) -> bool:
+    """Under 'high_uniform_group_low_normal_group' the 1-bit tier alone uses the Gaussian-codebook
+    codec (quant/hqe_2.py:488-492: the *_low functions are only ever handed to the 1-bit tier, :588-608,
+    :741-762); every other tier and every source of a demotion is uniform."""
+    if quant_strategy not in STRATEGIES:
+        raise ValueError("invalid quant_strategy")
+    return quant_strategy == "high_uniform_group_low_normal_group"
+
+
+def _requant(values_last_dim: np.ndarray, group: int, bit: int, normal_low: bool = False):
+    if bit == 1 and normal_low:
+        return normal1_quantize_pack_last_dim(values_last_dim, group)
     return quantize_pack_last_dim(values_last_dim, group, bit)
 
 
 def flush(cache: tuple, compress_length: int, history_length: int, K_sorted_idx, K_bit_num, V_bit_num,
           token_importance: np.ndarray, quant_strategy: str, ring: ImportanceRing | None = None,
           block_size: int = 32, group_size: int = 32, times_range: bool = True) -> tuple:
-    """KV_cache_hqe_2 (quant/hqe_2.py:456-843) for ``quant_strategy='uniform_group'``.
+    """KV_cache_hqe_2 (quant/hqe_2.py:456-843) for ``quant_strategy`` 'uniform_group' and
+    'high_uniform_group_low_normal_group' (1-bit destination tier in the Gaussian-codebook codec).
 
     K is quantised in groups of ``block_size`` tokens per channel, V in groups of
     ``group_size`` channels per token.  ``token_importance`` is the array the caller already
     passed through :func:`block_rank` for K (so it holds importance/block_size); it is
     divided a second time, in place, when V is ranked — as in the reference.
     """
-    if quant_strategy != "uniform_group":
-        raise ValueError("invalid quant_strategy")
+    normal_low = _low_is_normal(quant_strategy)
     cache = list(cache)
     new_K, new_V = cache[SLOT_NEW_K], cache[SLOT_NEW_V]
     res_K = new_K[:, :, compress_length:, :].copy()
@@ -363,7 +425,7 @@ def flush(cache: tuple, compress_length: int, history_length: int, K_sorted_idx,
             if bits == 16:
                 payload.append(np.ascontiguousarray(dense))
             else:
-                w, s, z = _requant(dense, block_size, bits)
+                w, s, z = _requant(dense, block_size, bits, normal_low)
                 payload.append(w); sc.append(s); zp.append(z)
         ids = _ids_of(destK[t], K_idx, new_ids)
         outK.append((np.concatenate(payload, axis=3) if payload else None, ids,
@@ -402,7 +464,7 @@ def flush(cache: tuple, compress_length: int, history_length: int, K_sorted_idx,
             if bits == 16:
                 payload.append(np.ascontiguousarray(dense))
             else:
-                w, s, z = _requant(dense, group_size, bits)
+                w, s, z = _requant(dense, group_size, bits, normal_low)
                 payload.append(w); sc.append(s); zp.append(z)
         ids = _ids_of(destV[t], V_idx, new_ids)
         outV.append((np.concatenate(payload, axis=2) if payload else None, ids,
@@ -448,9 +510,16 @@ def cache_dims(cache: tuple):
     return B, H, D, n, r
 
 
-def reconstruct(cache: tuple, block_size: int = 32, group_size: int = 32):
+def reconstruct(cache: tuple, block_size: int = 32, group_size: int = 32, quant_strategy: str = "uniform_group"):
     """Dense fp16 K and V [B,H,L,D] at logical positions (KV_cache_reconstruct_hqe,
     quant/hqe_2.py:967-1084), every tier dequantised with the two-rounding recipe."""
+    normal_low = _low_is_normal(quant_strategy)
+
+    def tier_dense(words, a, b, group, bits):
+        if bits == 1 and normal_low:
+            return normal1_dequantize_unpack_last_dim(words, a, b, group)
+        return dequantize_unpack_last_dim(words, a, b, group, bits)
+
     B, H, D, n, r = cache_dims(cache)
     L = n + r
     K = np.zeros((B, H, L, D), dtype=F16)
@@ -458,10 +527,10 @@ def reconstruct(cache: tuple, block_size: int = 32, group_size: int = 32):
     for bits in TIER_BITS:
         k, v = SLOT_K[bits], SLOT_V[bits]
         if cache[k] is not None:
-            dense = cache[k] if bits == 16 else dequantize_unpack_last_dim(cache[k], cache[k + 2], cache[k + 3], block_size, bits)
+            dense = cache[k] if bits == 16 else tier_dense(cache[k], cache[k + 2], cache[k + 3], block_size, bits)
             K[:, :, cache[k + 1], :] = np.swapaxes(dense, 2, 3)
         if cache[v] is not None:
-            dense = cache[v] if bits == 16 else dequantize_unpack_last_dim(cache[v], cache[v + 2], cache[v + 3], group_size, bits)
+            dense = cache[v] if bits == 16 else tier_dense(cache[v], cache[v + 2], cache[v + 3], group_size, bits)
             V[:, :, cache[v + 1], :] = dense
     if r:
         K[:, :, L - r:, :] = cache[SLOT_NEW_K]
@@ -469,17 +538,21 @@ def reconstruct(cache: tuple, block_size: int = 32, group_size: int = 32):
     return K, V
 
 
-def reconstruct_fp32(cache: tuple, block_size: int = 32, group_size: int = 32):
+def reconstruct_fp32(cache: tuple, block_size: int = 32, group_size: int = 32,
+                     quant_strategy: str = "uniform_group"):
     """Dense fp32 K and V with the dequantisation the reference's GEMV kernels do in registers:
     w = scale * code + zero evaluated in fp32 from the fp16 scale and zero, no fp16 rounding
-    (quant/csrc/gemv_cuda_uniform.cu:465-467)."""
+    (quant/csrc/gemv_cuda_uniform.cu:465-467); for the Gaussian-codebook 1-bit tier
+    w = std * center[code] + mean with the float32 centres (quant/csrc/gemv_cuda_normal.cu:104-106)."""
+    normal_low = _low_is_normal(quant_strategy)
     B, H, D, n, r = cache_dims(cache)
     L = n + r
     K = np.zeros((B, H, L, D), dtype=F32)
     V = np.zeros((B, H, L, D), dtype=F32)
 
     def deq(words, scale, zero, group, bits):
-        codes = _f(unpack_last_dim(words, bits))
+        codes = unpack_last_dim(words, bits)
+        codes = NORMAL1_CENTER[codes.astype(np.int64)] if (bits == 1 and normal_low) else _f(codes)
         lead, T = codes.shape[:-1], codes.shape[-1]
         cg = codes.reshape(*lead, T // group, group)
         return (cg * _f(scale)[..., None] + _f(zero)[..., None]).astype(F32).reshape(*lead, T)
@@ -499,14 +572,14 @@ def reconstruct_fp32(cache: tuple, block_size: int = 32, group_size: int = 32):
 
 
 def decode_attention(q: np.ndarray, cache: tuple, head_dim: int | None = None, block_size: int = 32,
-                     group_size: int = 32, dequant: str = "fp32"):
+                     group_size: int = 32, dequant: str = "fp32", quant_strategy: str = "uniform_group"):
     """fp32-accumulated dequant-matmul decode attention: softmax(q K^T / sqrt(d)) V, everything in
     fp32.  This is the quantity qkv_matmul_hqe_2 (quant/hqe_matmul.py:354-451) approximates with
     fp16 intermediates.  ``dequant='fp32'`` dequantises as the reference's CUDA kernels do
     (:func:`reconstruct_fp32`); ``'fp16'`` uses the dense fp16 reconstruction of
     KV_cache_reconstruct_hqe (:func:`reconstruct`).  q [B, nh_q, 1, D] fp16.
     Returns (weights fp32 [B,nh_q,1,L], out fp32 [B,nh_q,1,D])."""
-    K, V = (reconstruct_fp32 if dequant == "fp32" else reconstruct)(cache, block_size, group_size)
+    K, V = (reconstruct_fp32 if dequant == "fp32" else reconstruct)(cache, block_size, group_size, quant_strategy)
     B, H, L, D = K.shape
     nh_q = q.shape[1]
     rep = nh_q // H

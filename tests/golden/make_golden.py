@@ -2,7 +2,7 @@
 
 Run once, where a checkout of the reference is available (point ``HQEKV_REFERENCE_ROOT`` at it):
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [fixture names; none = all]
 
 It imports the reference's own ``quant/pack_unpack.py``, ``model/public_func.py`` and
 ``quant/hqe_2.py`` through ``ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
@@ -30,7 +30,12 @@ def npy(t):
     return None if t is None else t.detach().cpu().numpy()
 
 
+ONLY = set(sys.argv[1:])      # fixture names to (re)write; none given = all
+
+
 def save(name, **arrays):
+    if ONLY and name not in ONLY:
+        return
     arrays = {k: v for k, v in arrays.items() if v is not None}
     path = os.path.join(HERE, name + ".npz")
     np.savez_compressed(path, **arrays)
@@ -84,6 +89,44 @@ def codec_cases():
         n += 1
     out["count"] = np.array(n)
     save("codec", **out)
+
+
+# ------------------------------------------------------------------------------------------
+# 1b. Gaussian-codebook codec at 1 bit (the low tier of 'high_uniform_group_low_normal_group')
+# ------------------------------------------------------------------------------------------
+def normal_codec_cases():
+    gen = torch.Generator().manual_seed(4321)
+    out = {}
+    n = 0
+    for g in (32, 64, 128):
+        x = (torch.randn(2, 2, 5, 128, generator=gen) * 1.7 + 0.3).half()
+        code, std, mean = pu.normal_group_quantize_pack_last_dim(x.clone(), g, 1)
+        deq = pu.normal_group_dequantize_unpack_last_dim(code, std, mean, g, 1)
+        out.update({f"c{n}_x": npy(x), f"c{n}_code": npy(code), f"c{n}_std": npy(std), f"c{n}_mean": npy(mean),
+                    f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([1, g, 0])})
+        n += 1
+        T = 2 * g
+        k = outlier_K(gen, 1, 2, T, 128)
+        kt = k.transpose(2, 3)
+        code, std, mean = pu.normal_group_quantize_pack_last_dim(kt.contiguous(), g, 1)
+        deq = pu.normal_group_dequantize_unpack_last_dim(code, std, mean, g, 1)
+        out.update({f"c{n}_x": npy(kt.contiguous()), f"c{n}_code": npy(code), f"c{n}_std": npy(std),
+                    f"c{n}_mean": npy(mean), f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([1, g, 1])})
+        n += 1
+    # values that straddle the group mean closely, and tiny magnitudes
+    x = torch.zeros(1, 1, 3, 32).half()
+    x[0, 0, 0] = (1.0 + torch.arange(32) * 9.765625e-4).half()
+    x[0, 0, 1] = torch.linspace(-6e-5, 6e-5, 32).half()
+    x[0, 0, 2] = (torch.randn(32, generator=gen) * 300).half()
+    code, std, mean = pu.normal_group_quantize_pack_last_dim(x.clone(), 32, 1)
+    deq = pu.normal_group_dequantize_unpack_last_dim(code, std, mean, 32, 1)
+    out.update({f"c{n}_x": npy(x), f"c{n}_code": npy(code), f"c{n}_std": npy(std), f"c{n}_mean": npy(mean),
+                f"c{n}_deq": npy(deq), f"c{n}_meta": np.array([1, 32, 0])})
+    n += 1
+    out["count"] = np.array(n)
+    out["center_f32"] = pu.normal_quantiles_center[1].numpy()
+    out["upper_f32"] = pu.normal_quantiles_upper_bound[1].numpy()
+    save("codec_normal", **out)
 
 
 # ------------------------------------------------------------------------------------------
@@ -142,7 +185,7 @@ def dump_cache(prefix, cache, out):
         out[f"{prefix}_{i}"] = np.array(item) if isinstance(item, int) else npy(item)
 
 
-def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32):
+def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32, strategy="uniform_group"):
     """steps: list of (n_new_tokens, bit_num[6]); the first entry is the prefill."""
     gen = torch.Generator().manual_seed(seed)
     D = 128
@@ -182,7 +225,7 @@ def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32):
         out[f"s{si}_bit_num"] = npy(bn)
         out[f"s{si}_importance_ranked"] = npy(sort_imp.clone())
         out[f"s{si}_ring_in"] = npy(ring.weights.clone())
-        cache = hq.KV_cache_hqe_2(cache, compress, hist, K_ids, bn, bn.clone(), sort_imp, "uniform_group", ring,
+        cache = hq.KV_cache_hqe_2(cache, compress, hist, K_ids, bn, bn.clone(), sort_imp, strategy, ring,
                                   block, group, times_range)
         dump_cache(f"s{si}_out", cache, out)
         out[f"s{si}_ring_out"] = npy(ring.weights.clone())
@@ -190,7 +233,8 @@ def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32):
         hist += compress - bit_num[5]
         cur -= compress
         ring.kv_seq_len = hist + cur          # the next update() overwrites this anyway
-    rk, rv = hq.KV_cache_reconstruct_hqe(cache, "uniform_group", block, group)
+    rk, rv = hq.KV_cache_reconstruct_hqe(cache, strategy, block, group)
+    out["strategy"] = np.array(strategy)
     out["recon_K"] = npy(rk)
     out["recon_V"] = npy(rv)
     save(name, **out)
@@ -198,6 +242,7 @@ def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32):
 
 def main():
     codec_cases()
+    normal_codec_cases()
     ranking_cases()
     # totals: 256 | 224+96=320 | 288+64=352
     flush_sequence("flush_a", 11, 1, 2,
@@ -210,6 +255,13 @@ def main():
     flush_sequence("flush_c", 13, 1, 2,
                    [(256 + 5, [64, 64, 64, 0, 0, 64]), (128, [64, 0, 64, 64, 64, 64])], times_range=True,
                    block=64, group=64)
+    # 1-bit tier in the Gaussian-codebook codec: arrivals from the residual and from every higher tier
+    flush_sequence("flush_n", 14, 1, 2,
+                   [(262, [64, 32, 64, 32, 32, 32]), (96, [64, 32, 32, 96, 64, 32]), (64, [32, 32, 64, 96, 96, 32])],
+                   times_range=True, strategy="high_uniform_group_low_normal_group")
+    flush_sequence("flush_n64", 15, 2, 1,
+                   [(256 + 7, [64, 64, 64, 0, 64, 0]), (128, [64, 0, 64, 64, 128, 64])], times_range=True,
+                   block=64, group=64, strategy="high_uniform_group_low_normal_group")
 
 
 if __name__ == "__main__":

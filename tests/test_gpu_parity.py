@@ -183,9 +183,12 @@ def test_ranking_full_size_properties(ops, cuda_device):
 # ---------------------------------------------------------------------------------------------
 # flush
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c", "flush_n", "flush_n64"])
 def test_flush_golden_sequences(ops, cuda_device, name):
+    """flush_n / flush_n64: quant_strategy 'high_uniform_group_low_normal_group' (1-bit tier in the
+    Gaussian-codebook codec, fed from the residual and from every higher tier)."""
     z = load_golden(name)
+    strategy = str(z["strategy"]) if "strategy" in z else "uniform_group"
     B, H, D, block, group, times_range, nsteps = (int(v) for v in z["meta"])
     cache = None
     for s in range(nsteps):
@@ -201,17 +204,42 @@ def test_flush_golden_sequences(ops, cuda_device, name):
         ring = ops.pf.last_attn_weights()
         ring.weights = torch.from_numpy(z[f"s{s}_ring_in"].copy()).to(cuda_device)
         bn = torch.from_numpy(z[f"s{s}_bit_num"])
-        cache = ops.hqe_2.KV_cache_hqe_2(cache, compress, hist, ids, bn, bn.clone(), imp, "uniform_group", ring, block,
+        cache = ops.hqe_2.KV_cache_hqe_2(cache, compress, hist, ids, bn, bn.clone(), imp, strategy, ring, block,
                                          group, bool(times_range))
         want = golden_cache(z, f"s{s}_out")
         for i in range(41):
             bits_equal(cache[i], want[i], f"{name} step {s} slot {i}")
         assert cache[41] == want[41]
         bits_equal(ring.weights, z[f"s{s}_ring_out"], f"{name} step {s} ring")
-    K, V = ops.hqe_2.KV_cache_reconstruct_hqe(cache, "uniform_group", block, group)
-    oK, oV = O.reconstruct(host_cache(cache), block, group)
+    K, V = ops.hqe_2.KV_cache_reconstruct_hqe(cache, strategy, block, group)
+    oK, oV = O.reconstruct(host_cache(cache), block, group, strategy)
     bits_equal(K, oK, f"{name} reconstructed K")
     bits_equal(V, oV, f"{name} reconstructed V")
+
+
+def test_normal_codec_1bit_golden(ops, cuda_device):
+    """Gaussian-codebook codec at 1 bit: std, mean, packed codes and dequantised values bit for bit against
+    the reference's output; row layout and the transposed (K) view."""
+    z = load_golden("codec_normal")
+    for n in range(int(z["count"])):
+        bit, g, klayout = (int(v) for v in z[f"c{n}_meta"])
+        x = torch.from_numpy(z[f"c{n}_x"]).to(cuda_device)
+        if klayout:  # hand the kernel the transposed view of a token-major tensor, as the flush does
+            x = x.transpose(2, 3).contiguous().transpose(2, 3)
+        code, std, mean = ops.pu.normal_group_quantize_pack_last_dim(x, g, 1)
+        bits_equal(std, z[f"c{n}_std"], f"normal case {n} std")
+        bits_equal(mean, z[f"c{n}_mean"], f"normal case {n} mean")
+        bits_equal(code, z[f"c{n}_code"], f"normal case {n} codes")
+        deq = ops.pu.normal_group_dequantize_unpack_last_dim(code, std, mean, g, 1)
+        bits_equal(deq, z[f"c{n}_deq"], f"normal case {n} dequantised")
+    # random cross-check against the oracle at a larger size
+    rng = np.random.default_rng(5)
+    x = (rng.standard_normal((2, 3, 64, 256)) * 2 + 0.5).astype(np.float16)
+    oc, os_, om = O.normal1_quantize_pack_last_dim(x, 64)
+    code, std, mean = ops.pu.normal_group_quantize_pack_last_dim(torch.from_numpy(x).to(cuda_device), 64, 1)
+    bits_equal(std, os_, "normal random std"); bits_equal(mean, om, "normal random mean"); bits_equal(code, oc, "normal random codes")
+    with pytest.raises(NotImplementedError):
+        ops.pu.normal_group_quantize_pack_last_dim(torch.from_numpy(x).to(cuda_device), 64, 2)
 
 
 def test_flush_errors(ops, cuda_device):
@@ -230,10 +258,10 @@ def test_flush_errors(ops, cuda_device):
 # ---------------------------------------------------------------------------------------------
 # decode attention
 # ---------------------------------------------------------------------------------------------
-def check_attention(ops, cache_t, q, block, group, what):
-    w, out = ops.hm.qkv_matmul_hqe_2(q, cache_t, None, q.shape[-1], "uniform_group", block, group)
+def check_attention(ops, cache_t, q, block, group, what, strategy="uniform_group"):
+    w, out = ops.hm.qkv_matmul_hqe_2(q, cache_t, None, q.shape[-1], strategy, block, group)
     torch.cuda.synchronize()
-    ow, oo = O.decode_attention(q.cpu().numpy(), host_cache(cache_t), None, block, group)
+    ow, oo = O.decode_attention(q.cpu().numpy(), host_cache(cache_t), None, block, group, quant_strategy=strategy)
     out_f = out.float().cpu().numpy()
     assert out_f.shape == oo.shape and w.shape == ow.shape, what
     assert np.isfinite(out_f).all(), f"{what}: non-finite output"
@@ -247,19 +275,20 @@ def check_attention(ops, cache_t, q, block, group, what):
     return per_head.max()
 
 
-@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c", "flush_n", "flush_n64"])
 def test_decode_on_golden_caches(ops, cuda_device, name):
     """Every flush step of the fixtures gives a cache with a different set of present/absent tiers (the
     uniform 1-bit tier included), K and V ranked differently (flush_a/c), batch 2 (flush_b), group 64
-    (flush_c)."""
+    (flush_c); flush_n / flush_n64 hold the 1-bit tier in the Gaussian-codebook codec."""
     z = load_golden(name)
+    strategy = str(z["strategy"]) if "strategy" in z else "uniform_group"
     B, H, D, block, group, _, nsteps = (int(v) for v in z["meta"])
     gen = torch.Generator(device=cuda_device).manual_seed(1)
     for s in range(nsteps):
         cache_np = golden_cache(z, f"s{s}_out")
         for rep in (1, 4, 8):
             q = torch.randn(B, rep * H, 1, D, generator=gen, device=cuda_device).half()
-            check_attention(ops, dev_cache(cache_np, cuda_device), q, block, group, f"{name} step {s} rep {rep}")
+            check_attention(ops, dev_cache(cache_np, cuda_device), q, block, group, f"{name} step {s} rep {rep}", strategy)
 
 
 def test_decode_cfg0_vs_oracle(ops, cuda_device):
@@ -363,6 +392,30 @@ def test_decode_sweep_vs_oracle(ops, cuda_device, tiers, group):
                                     SWEEP_RATIOS[tiers], evict, group, True, 1)
         cache, q = synthetic.build_cache(cfg, cuda_device, seed=group + batch, times_range=True)
         check_attention(ops, cache, q, group, group, f"{cfg.name} B{batch} {nh_q}/{nh_kv}")
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
+@pytest.mark.parametrize("tiers", ["all1", "mixed1"])
+def test_decode_normal_low_tier_vs_oracle(ops, cuda_device, tiers, group):
+    """quant_strategy 'high_uniform_group_low_normal_group': the 1-bit tier (all of the cache, or a quarter of
+    it beside 8/4/2-bit tiers) in the Gaussian-codebook codec, written by the flush and read by the fused
+    decode; flushed tiers bit for bit against the oracle's flush, attention against the fp32 oracle at 2e-3."""
+    from hqekv_b200 import synthetic
+    strategy = "high_uniform_group_low_normal_group"
+    for batch, nh_q, nh_kv, evict in ((1, 32, 8, 0.0), (3, 16, 2, 0.125), (2, 2, 2, 0.0)):
+        cfg = synthetic.CacheConfig(f"normal-{tiers}-g{group}", batch, nh_q, nh_kv, 128, 1024 + 40, 40,
+                                    SWEEP_RATIOS[tiers], evict, group, True, 1)
+        cache, q = synthetic.build_cache(cfg, cuda_device, seed=group + batch, times_range=True, quant_strategy=strategy)
+        assert cache[28] is not None and cache[32] is not None
+        Kd, Vd = ops.hqe_2.KV_cache_reconstruct_hqe(cache, strategy, group, group)
+        oK, oV = O.reconstruct(host_cache(cache), group, group, strategy)
+        bits_equal(Kd, oK, f"{cfg.name} reconstructed K")
+        bits_equal(Vd, oV, f"{cfg.name} reconstructed V")
+        check_attention(ops, cache, q, group, group, f"{cfg.name} B{batch} {nh_q}/{nh_kv}", strategy)
+    # the same 1-bit payload read as a uniform tier gives a different answer: the codec flag is honoured
+    w_u, o_u = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", group, group)
+    w_n, o_n = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, strategy, group, group)
+    assert not torch.equal(o_u, o_n)
 
 
 @pytest.mark.parametrize("case", [

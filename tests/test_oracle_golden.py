@@ -82,9 +82,10 @@ def test_token_range_and_make_sum_equal():
     same(O.make_sum_equal(z["mse_in"].copy(), 20), z["mse_out"], "make_sum_equal")
 
 
-@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c"])
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c", "flush_n", "flush_n64"])
 def test_flush_sequence(name):
     z = load_golden(name)
+    strategy = str(z["strategy"]) if "strategy" in z else "uniform_group"
     B, H, D, block, group, times_range, nsteps = (int(v) for v in z["meta"])
     cache = None
     for s in range(nsteps):
@@ -100,14 +101,14 @@ def test_flush_sequence(name):
         ring = O.ImportanceRing()
         ring.weights = z[f"s{s}_ring_in"].copy()
         cache = O.flush(cin, compress, hist, ids, z[f"s{s}_bit_num"], z[f"s{s}_bit_num"].copy(), imp,
-                        "uniform_group", ring, block, group, bool(times_range))
+                        strategy, ring, block, group, bool(times_range))
         want = golden_cache(z, f"s{s}_out")
         for i in range(41):
             same(cache[i], want[i], f"{name} step {s} slot {i}")
         assert cache[41] == want[41]
         same(ring.weights, z[f"s{s}_ring_out"], f"{name} step {s} ring")
         same(imp, z[f"s{s}_importance_after"], f"{name} step {s} importance after flush")
-    K, V = O.reconstruct(cache, block, group)
+    K, V = O.reconstruct(cache, block, group, strategy)
     same(K, z["recon_K"], f"{name} reconstructed K")
     want_V = z["recon_V"].copy()
     if cache[8] is None and cache[16] is not None:
@@ -121,3 +122,39 @@ def test_flush_sequence(name):
 def test_flush_rejects_unknown_strategy():
     with pytest.raises(ValueError, match="invalid quant_strategy"):
         O.flush((None,) * 42, 0, 0, None, None, None, None, "nope")
+
+
+def test_normal_codec_1bit_matches_reference_fixtures():
+    """Gaussian-codebook codec at 1 bit (std / mean / codes / dequantised values) against the reference's output."""
+    z = load_golden("codec_normal")
+    assert np.array_equal(z["center_f32"], O.NORMAL1_CENTER) and z["upper_f32"][0] == 0 and np.isinf(z["upper_f32"][1])
+    for n in range(int(z["count"])):
+        bit, g, _ = (int(v) for v in z[f"c{n}_meta"])
+        assert bit == 1
+        code, std, mean = O.normal1_quantize_pack_last_dim(z[f"c{n}_x"], g)
+        assert np.array_equal(std.view(np.uint16), z[f"c{n}_std"].view(np.uint16)), f"case {n}: std"
+        assert np.array_equal(mean.view(np.uint16), z[f"c{n}_mean"].view(np.uint16)), f"case {n}: mean"
+        assert np.array_equal(code, z[f"c{n}_code"]), f"case {n}: packed codes"
+        deq = O.normal1_dequantize_unpack_last_dim(code, std, mean, g)
+        assert np.array_equal(deq.view(np.uint16), z[f"c{n}_deq"].view(np.uint16)), f"case {n}: dequantised"
+
+
+@pytest.mark.parametrize("name", ["flush_n", "flush_n64"])
+def test_decode_oracle_reads_normal_low_tier(name):
+    """The fp32 decode oracle under 'high_uniform_group_low_normal_group': dequantising the 1-bit tier in
+    registers (float32 centres) and attending over the reference's own dense reconstruction agree to fp16
+    accuracy, and reading the same payload as a uniform tier does not."""
+    z = load_golden(name)
+    B, H, D, block, group, _, nsteps = (int(v) for v in z["meta"])
+    strategy = str(z["strategy"])
+    cache = golden_cache(z, f"s{nsteps - 1}_out")
+    assert cache[28] is not None and cache[32] is not None
+    rng = np.random.default_rng(3)
+    q = rng.standard_normal((B, 4 * H, 1, D)).astype(np.float16)
+    w32, o32 = O.decode_attention(q, cache, None, block, group, "fp32", strategy)
+    w16, o16 = O.decode_attention(q, cache, None, block, group, "fp16", strategy)
+    assert np.abs(o32 - o16).max() <= 2e-3 * np.abs(o32).max()
+    K, V = O.reconstruct(cache, block, group, strategy)
+    same(K, z["recon_K"], f"{name} K")
+    wu, ou = O.decode_attention(q, cache, None, block, group, "fp32", "uniform_group")
+    assert np.abs(ou - o32).max() > 1e-2 * np.abs(o32).max()
