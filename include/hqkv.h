@@ -28,7 +28,7 @@ extern "C" {
 
 #define HQKV_OK 0
 #define HQKV_E_INVALID (-1)     /* bad argument (shape, bits, group size, alignment, null pointer) */
-#define HQKV_E_UNSUPPORTED (-2) /* valid in the reference but not built here (e.g. the Gaussian-codebook codec) */
+#define HQKV_E_UNSUPPORTED (-2) /* valid in the reference but not built here (e.g. Gaussian codebooks above 1 bit) */
 #define HQKV_E_WORKSPACE (-3)   /* scratch buffer too small */
 #define HQKV_E_CUDA (-4)        /* a CUDA runtime call failed */
 
@@ -239,12 +239,18 @@ int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host, const void
  * = transposes + kvhq_gemv.gemv_forward_cuda_uniform_group (quant/csrc/pybind.cpp:11,
  * quant/csrc/gemv_cuda_uniform.cu:1533-1599), without the transposed copies.
  *   fA fp16 [B, nh_q, 1, K];  qB int32 [B, nh_kv, K, N*bits/32];  scales/zeros fp16 [B, nh_kv, K, N/group]
- *   out fp16 [B, nh_q, 1, N].   bits in {8,4,2}; group in {32,64,128}; N a multiple of group.
+ *   out fp16 [B, nh_q, 1, N].   bits in {8,4,2,1}; group in {32,64,128}; N a multiple of group.
  * Both uses of the reference are covered: K = head_dim, N = tokens (q.K^T of one tier) and
  * K = tokens, N = head_dim (p.V of one tier).
  */
 int hqkv_gemv_uniform_group(const void* fA, const void* qB, const void* scales, const void* zeros, int B, int nh_q,
                             int nh_kv, int64_t K, int64_t N, int group, int bits, void* out, void* stream);
+/* The same over a Gaussian-codebook tier: value = std * (code ? C : -C) + mean, C = 0.67448974 in float32.
+ * Stands in for cuda_bmm_fA_qB_normal_group (quant/matmul.py:72-95) = transposes +
+ * kvhq_gemv.gemv_forward_cuda_normalize_group (quant/csrc/gemv_cuda_normal.cu) at bits = 1, the width the
+ * live strategy 'high_uniform_group_low_normal_group' uses; other widths return HQKV_E_INVALID. */
+int hqkv_gemv_normal_group(const void* fA, const void* qB, const void* stds, const void* means, int B, int nh_q,
+                           int nh_kv, int64_t K, int64_t N, int group, int bits, void* out, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Importance bookkeeping and block ranking

@@ -606,3 +606,18 @@ def gemv_dequant(fA: np.ndarray, qB: np.ndarray, scales: np.ndarray, zeros: np.n
     nh_q, M = fA.shape[1], fA.shape[2]
     a = _f(fA).reshape(B, H, (nh_q // H) * M, Kd)
     return np.matmul(a, w).reshape(B, nh_q, M, N)
+
+
+def gemv_dequant_normal1(fA: np.ndarray, qB: np.ndarray, stds: np.ndarray, means: np.ndarray,
+                         group_size: int) -> np.ndarray:
+    """C = fA x dequant(qB) over a Gaussian-codebook 1-bit tier with fp32 accumulation — what
+    cuda_bmm_fA_qB_normal_group (quant/matmul.py:72-95) computes through the kernels of
+    quant/csrc/gemv_cuda_normal.cu (:104-106: w = std * center[code] + mean in fp32, float32 centres).
+    Shapes as in :func:`gemv_dequant`."""
+    c = NORMAL1_CENTER[unpack_last_dim(qB, 1).astype(np.int64)]
+    B, H, Kd, N = c.shape
+    w = c.reshape(B, H, Kd, N // group_size, group_size) * _f(stds)[..., None] + _f(means)[..., None]
+    w = w.reshape(B, H, Kd, N).astype(F32)
+    nh_q, M = fA.shape[1], fA.shape[2]
+    a = _f(fA).reshape(B, H, (nh_q // H) * M, Kd)
+    return np.matmul(a, w).reshape(B, nh_q, M, N)

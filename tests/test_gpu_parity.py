@@ -358,7 +358,7 @@ def test_decode_errors(ops, cuda_device):
 # ---------------------------------------------------------------------------------------------
 # stand-alone GEMV
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("bits", [8, 4, 2])
+@pytest.mark.parametrize("bits", [8, 4, 2, 1])
 def test_gemv_uniform_group_vs_oracle(ops, cuda_device, bits):
     """Both uses of cuda_bmm_fA_qB_uniform_group: q.K^T of a tier (K = head_dim rows, N = tokens) and
     p.V of a tier (K = tokens, N = head_dim).  Tolerance: 2e-3 of the largest output (fp16 result)."""
@@ -372,6 +372,22 @@ def test_gemv_uniform_group_vs_oracle(ops, cuda_device, bits):
                                                   bits)
         err = np.abs(got.float().cpu().numpy() - want).max() / np.abs(want).max()
         assert err <= 2e-3, f"gemv bits {bits} K {K} N {N}: rel err {err:.3e}"
+
+
+@pytest.mark.parametrize("rep", [1, 4, 8])
+def test_gemv_normal_group_vs_oracle(ops, cuda_device, rep):
+    """cuda_bmm_fA_qB_normal_group at 1 bit (Gaussian codebook), both operand shapes, GQA 1 / 4 / 8."""
+    rng = np.random.default_rng(40 + rep)
+    for (K, N, g) in ((128, 32 * 9, 32), (32 * 7, 128, 32), (128, 128, 64), (64, 256, 128)):
+        x = (rng.standard_normal((2, 2, K, N)) * 1.5 + 0.25).astype(np.float16)
+        code, std, mean = O.normal1_quantize_pack_last_dim(x, g)
+        fA = rng.standard_normal((2, 2 * rep, 1, K)).astype(np.float16)
+        want = O.gemv_dequant_normal1(fA, code, std, mean, g)
+        got = ops.mm.cuda_bmm_fA_qB_normal_group(g, *(torch.from_numpy(a).to(cuda_device) for a in (fA, code, std, mean)), 1)
+        err = np.abs(got.float().cpu().numpy() - want).max() / np.abs(want).max()
+        assert err <= 2e-3, f"normal gemv rep {rep} K {K} N {N}: rel err {err:.3e}"
+    with pytest.raises(NotImplementedError):
+        ops.mm.cuda_bmm_fA_qB_normal_group(32, *(torch.from_numpy(a).to(cuda_device) for a in (fA, code, std, mean)), 2)
 
 
 # ---------------------------------------------------------------------------------------------
