@@ -592,6 +592,55 @@ def decode_attention(q: np.ndarray, cache: tuple, head_dim: int | None = None, b
     return p.reshape(B, nh_q, 1, L), out.reshape(B, nh_q, 1, D)
 
 
+def decode_attention_fp16_flow(q: np.ndarray, cache: tuple, block_size: int = 32, group_size: int = 32,
+                               quant_strategy: str = "uniform_group"):
+    """qkv_matmul_hqe_2 with the reference's fp16 intermediates (quant/hqe_matmul.py:405-451): every tier's
+    q.K^T is an fp32-accumulated GEMV rounded to fp16 and scattered into an fp16 row, the row is divided by
+    sqrt(head_dim) in fp16, softmax runs in fp32 and is rounded to fp16, and the tiers' p.V products (each
+    rounded to fp16) are added into an fp16 output one after the other in tier order 16, 8, 4, 2, 1, residual.
+    Returns (weights f16 [B,nh_q,1,L], out f16 [B,nh_q,1,D]).  Used to pin the oracle against decode outputs
+    produced by the reference's own function; the parity target of the CUDA path is :func:`decode_attention`."""
+    normal_low = _low_is_normal(quant_strategy)
+    B, H, D, n, r = cache_dims(cache)
+    L = n + r
+    nh_q = q.shape[1]
+    rep = nh_q // H
+    qf = _f(q).reshape(B, H, rep, D)
+
+    def dense32(words, a, b, group, bits):
+        codes = unpack_last_dim(words, bits)
+        cg = NORMAL1_CENTER[codes.astype(np.int64)] if (bits == 1 and normal_low) else _f(codes)
+        lead, T = cg.shape[:-1], cg.shape[-1]
+        cg = cg.reshape(*lead, T // group, group)
+        return (cg * _f(a)[..., None] + _f(b)[..., None]).astype(F32).reshape(*lead, T)
+
+    logits = np.zeros((B, H, rep, L), dtype=F16)
+    for bits in TIER_BITS:
+        k = SLOT_K[bits]
+        if cache[k] is None:
+            continue
+        Kd = _f(cache[k]) if bits == 16 else dense32(cache[k], cache[k + 2], cache[k + 3], block_size, bits)  # [B,H,D,n]
+        logits[..., cache[k + 1]] = _h(np.matmul(qf, Kd))
+    if r:
+        logits[..., L - r:] = _h(np.matmul(qf, np.swapaxes(_f(cache[SLOT_NEW_K]), 2, 3)))
+    with np.errstate(all="ignore"):
+        logits = _h(_f(logits) / F32(D ** 0.5))
+    x = _f(logits)
+    x = x - x.max(axis=-1, keepdims=True)
+    e = np.exp(x, dtype=F32)
+    p = _h(e / e.sum(axis=-1, keepdims=True, dtype=F32))
+    out = np.zeros((B, H, rep, D), dtype=F16)
+    for bits in TIER_BITS:
+        v = SLOT_V[bits]
+        if cache[v] is None:
+            continue
+        Vd = _f(cache[v]) if bits == 16 else dense32(cache[v], cache[v + 2], cache[v + 3], group_size, bits)  # [B,H,n,D]
+        out = _h(_f(out) + _f(_h(np.matmul(_f(p[..., cache[v + 1]]), Vd))))
+    if r:
+        out = _h(_f(out) + _f(_h(np.matmul(_f(p[..., L - r:]), _f(cache[SLOT_NEW_V])))))
+    return p.reshape(B, nh_q, 1, L), out.reshape(B, nh_q, 1, D)
+
+
 def gemv_dequant(fA: np.ndarray, qB: np.ndarray, scales: np.ndarray, zeros: np.ndarray, group_size: int,
                  bits: int) -> np.ndarray:
     """C = fA x dequant(qB) with fp32 accumulation — what cuda_bmm_fA_qB_uniform_group

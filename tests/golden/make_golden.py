@@ -4,8 +4,8 @@ Run once, where a checkout of the reference is available (point ``HQEKV_REFERENC
 
     python tests/golden/make_golden.py [fixture names; none = all]
 
-It imports the reference's own ``quant/pack_unpack.py``, ``model/public_func.py`` and
-``quant/hqe_2.py`` through ``ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
+It imports the reference's own ``quant/pack_unpack.py``, ``model/public_func.py``,
+``quant/hqe_2.py``, ``quant/hqe_matmul.py`` and ``model/llama_hqe.py`` through ``ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
 the outputs the reference produced as ``*.npz`` files.  The tests read only the ``.npz``
 files; the reference is not needed to run them.
 
@@ -22,8 +22,8 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, HERE)
 import ref_shim  # noqa: E402
 
-ref = ref_shim.load_reference()
-pu, pf, hq = ref.pack_unpack, ref.public_func, ref.hqe_2
+ref = ref_shim.load_reference_model()
+pu, pf, hq, hm = ref.pack_unpack, ref.public_func, ref.hqe_2, ref.hqe_matmul
 
 
 def npy(t):
@@ -228,6 +228,11 @@ def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32, str
         cache = hq.KV_cache_hqe_2(cache, compress, hist, K_ids, bn, bn.clone(), sort_imp, strategy, ring,
                                   block, group, times_range)
         dump_cache(f"s{si}_out", cache, out)
+        # one decode step over the new cache through the reference's own qkv_matmul_hqe_2 (CPU stand-in GEMV)
+        qgen = torch.Generator().manual_seed(seed * 1000 + si)
+        q = torch.randn(B, 4 * H, 1, D, generator=qgen).half()
+        aw, ao = hm.qkv_matmul_hqe_2(q, cache, None, D, strategy, block, group)
+        out[f"s{si}_q"], out[f"s{si}_attn_weights"], out[f"s{si}_attn_output"] = npy(q), npy(aw), npy(ao)
         out[f"s{si}_ring_out"] = npy(ring.weights.clone())
         out[f"s{si}_importance_after"] = npy(sort_imp.clone())
         hist += compress - bit_num[5]

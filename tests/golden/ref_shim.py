@@ -4,13 +4,18 @@ Used only by ``make_golden.py`` (the script that produced the committed
 ``*.npz`` fixtures).  Nothing in the test-suite or the product imports this
 module: the reference tree is not available where the GPU tests run.
 
-The reference modules are imported *unmodified*; four stand-ins make them
+The reference modules are imported *unmodified*; these stand-ins make them
 executable without a GPU:
 
 1. ``fast_hadamard_transform`` (imported at the top of ``model/public_func.py``
    but absent here) becomes an empty module.
-2. ``kvhq_gemv`` (the reference's unbuilt CUDA extension) becomes an empty
-   module, so ``quant/matmul.py`` imports; none of its functions are called.
+2. ``kvhq_gemv`` (the reference's unbuilt CUDA extension) becomes a module with CPU
+   callables for the two entry points the live path uses, ``gemv_forward_cuda_uniform_group`` and
+   ``gemv_forward_cuda_normalize_group``: same arguments and result shape, the kernels' arithmetic
+   (w = scale * code + zero, resp. std * center[code] + mean, in fp32; fp32 accumulation; fp16 result —
+   quant/csrc/gemv_cuda_uniform.cu:455-489, gemv_cuda_normal.cu:104-106).  With them the reference's own
+   ``qkv_matmul_hqe_2`` and ``LlamaAttention_hqe.forward`` run unmodified on the CPU; what the fixtures
+   pin there is the reference's control flow and fp16 intermediate roundings, not its CUDA summation order.
 3. ``torch.sort`` as seen by ``model/public_func.py`` is forced to ``stable=True``.  The
    reference sorts block keys with the default (unstable) sort, whose order among equal fp16
    keys is unspecified and differs between torch's CPU and CUDA sorts; a stable sort is one of
@@ -55,6 +60,56 @@ def _cpu_unpack(bits, intensor, data, n_rows, num_feats, feat_per_int, BLOCK_SIZ
     data.copy_(vals.reshape(n_rows, num_feats * feat_per_int).to(data.dtype))
 
 
+def _cpu_unpack_words(qB, bits):
+    """qB int32 [BH, N/fpi, K] (the transposed layout the reference hands its kernels) -> codes [BH, N, K]."""
+    fpi = 32 // bits
+    words = qB.to(torch.int64) & 0xFFFFFFFF
+    shifts = (torch.arange(fpi, dtype=torch.int64) * bits).view(1, 1, fpi, 1)
+    codes = (words.unsqueeze(2) >> shifts) & ((1 << bits) - 1)          # [BH, N/fpi, fpi, K]
+    return codes.reshape(qB.shape[0], qB.shape[1] * fpi, qB.shape[2])
+
+
+def _cpu_gemv(fA, w, nh_q, nh_kv):
+    """fA fp16 [B*nh_q, M, K], w fp32 [B*nh_kv, N, K] -> fp16 [B*nh_q, M, N] with fp32 accumulation."""
+    rep = nh_q // nh_kv
+    w = w.repeat_interleave(rep, dim=0)
+    return torch.matmul(fA.float(), w.transpose(1, 2)).to(torch.float16)
+
+
+def _cpu_gemv_uniform_group(fA, qB, scales, zeros, bits, group_size, nh_q, nh_kv):
+    codes = _cpu_unpack_words(qB, bits).float()                           # [BH, N, K]
+    s = scales.float().repeat_interleave(group_size, dim=1)               # [BH, G, K] -> [BH, N, K]
+    z = zeros.float().repeat_interleave(group_size, dim=1)
+    return _cpu_gemv(fA, s * codes + z, nh_q, nh_kv)
+
+
+def _cpu_gemv_normalize_group(fA, qB, stds, means, center, bits, group_size, nh_q, nh_kv):
+    codes = _cpu_unpack_words(qB, bits)
+    c = center.float()[codes]
+    s = stds.float().repeat_interleave(group_size, dim=1)
+    m = means.float().repeat_interleave(group_size, dim=1)
+    return _cpu_gemv(fA, s * c + m, nh_q, nh_kv)
+
+
+def load_reference_model():
+    """The reference's decode function and Llama attention module (imports transformers: slow).
+    One more stand-in: ``transformers.utils.LossKwargs``, which newer transformers releases no longer
+    export and ``model/llama_hqe.py`` only uses as a base of a typing class."""
+    ns = load_reference()
+    import transformers.utils as tu
+    if not hasattr(tu, "LossKwargs"):
+        from typing import TypedDict
+
+        class LossKwargs(TypedDict, total=False):
+            pass
+
+        tu.LossKwargs = LossKwargs
+    import hqe_matmul  # noqa: E402
+    from model import llama_hqe  # noqa: E402
+    ns.hqe_matmul, ns.llama_hqe = hqe_matmul, llama_hqe
+    return ns
+
+
 def load_reference():
     """Return a namespace with the reference modules of the hot path."""
     if not os.path.isdir(REFERENCE_ROOT):
@@ -63,7 +118,11 @@ def load_reference():
         if p not in sys.path:
             sys.path.insert(0, p)
     sys.modules.setdefault("fast_hadamard_transform", types.ModuleType("fast_hadamard_transform"))
-    sys.modules.setdefault("kvhq_gemv", types.ModuleType("kvhq_gemv"))
+    if "kvhq_gemv" not in sys.modules:
+        gemv = types.ModuleType("kvhq_gemv")
+        gemv.gemv_forward_cuda_uniform_group = _cpu_gemv_uniform_group
+        gemv.gemv_forward_cuda_normalize_group = _cpu_gemv_normalize_group
+        sys.modules["kvhq_gemv"] = gemv
 
     real_device_ctx = torch.cuda.device
 

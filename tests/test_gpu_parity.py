@@ -289,6 +289,14 @@ def test_decode_on_golden_caches(ops, cuda_device, name):
         for rep in (1, 4, 8):
             q = torch.randn(B, rep * H, 1, D, generator=gen, device=cuda_device).half()
             check_attention(ops, dev_cache(cache_np, cuda_device), q, block, group, f"{name} step {s} rep {rep}", strategy)
+        # the reference's own qkv_matmul_hqe_2 on this cache (fixture: fp16 intermediates, fp32-accumulating CPU
+        # stand-in for its GEMV extension): agreement to the accuracy of that fp16 flow (5e-3 of the largest output)
+        q = torch.from_numpy(z[f"s{s}_q"]).to(cuda_device)
+        w, out = ops.hm.qkv_matmul_hqe_2(q, dev_cache(cache_np, cuda_device), None, D, strategy, block, group)
+        ro = z[f"s{s}_attn_output"].astype(np.float32)
+        got = out.float().cpu().numpy()
+        assert (np.abs(got - ro).max(-1) <= 5e-3 * np.abs(ro).max(-1)).all(), f"{name} step {s}: vs reference decode output"
+        assert np.abs(w.float().cpu().numpy() - z[f"s{s}_attn_weights"].astype(np.float32)).max() <= 2.5e-3
 
 
 def test_decode_cfg0_vs_oracle(ops, cuda_device):

@@ -158,3 +158,28 @@ def test_decode_oracle_reads_normal_low_tier(name):
     same(K, z["recon_K"], f"{name} K")
     wu, ou = O.decode_attention(q, cache, None, block, group, "fp32", "uniform_group")
     assert np.abs(ou - o32).max() > 1e-2 * np.abs(o32).max()
+
+
+@pytest.mark.parametrize("name", ["flush_a", "flush_b", "flush_c", "flush_n", "flush_n64"])
+def test_decode_oracle_against_reference_decode_outputs(name):
+    """attn_weights / attn_output the reference's own qkv_matmul_hqe_2 returned for every cache of the flush
+    sequences (its CUDA GEMV replaced by an fp32-accumulating CPU stand-in).  The oracle's restatement of the
+    reference's fp16 flow must agree to within one fp16 ulp of a logit and be identical in at least 95 % of the probabilities (summation order is the only freedom); the fp32 oracle,
+    which is the parity target of the CUDA path, must agree to the accuracy of that fp16 flow."""
+    z = load_golden(name)
+    B, H, D, block, group, _, nsteps = (int(v) for v in z["meta"])
+    strategy = str(z["strategy"])
+    for s in range(nsteps):
+        cache = golden_cache(z, f"s{s}_out")
+        q = z[f"s{s}_q"]
+        rw = z[f"s{s}_attn_weights"].astype(np.float32)
+        ro = z[f"s{s}_attn_output"].astype(np.float32)
+        w, o = O.decode_attention_fp16_flow(q, cache, block, group, strategy)
+        w, o = w.astype(np.float32), o.astype(np.float32)
+        # one fp16 ulp of a row's largest logit (summation order) moves all its probabilities by up to 0.4 %
+        assert (np.abs(w - rw) <= 2.0 ** -8 * rw + 2.0 ** -24).all(), f"{name} step {s}: weights"
+        assert (w != rw).mean() <= 0.05 and (o != ro).mean() <= 0.15, f"{name} step {s}: too many one-ulp differences"
+        assert np.abs(o - ro).max() <= 1e-3 * np.abs(ro).max(), f"{name} step {s}: output"
+        w32, o32 = O.decode_attention(q, cache, None, block, group, "fp32", strategy)
+        assert (np.abs(o32 - ro).max(-1) <= 5e-3 * np.abs(o32).max(-1)).all(), f"{name} step {s}: fp32 oracle vs reference flow"
+        assert np.abs(w32 - rw).max() <= 2.5e-3, f"{name} step {s}: fp32 probabilities vs reference flow"
