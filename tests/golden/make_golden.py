@@ -245,6 +245,57 @@ def flush_sequence(name, seed, B, H, steps, times_range, block=32, group=32, str
     save(name, **out)
 
 
+# ------------------------------------------------------------------------------------------
+# 4. the attention module that drives the cache: LlamaAttention_hqe.forward, prefill + decode steps
+# ------------------------------------------------------------------------------------------
+def rotary(positions, head_dim, theta=10000.0):
+    inv = 1.0 / (theta ** (torch.arange(0, head_dim, 2, dtype=torch.float32) / head_dim))
+    ang = positions.float().unsqueeze(-1) * inv
+    ang = torch.cat((ang, ang), dim=-1)
+    return ang.cos().half(), ang.sin().half()
+
+
+def attention_module_case(name, seed, strategy, B, hidden, nh, nkv, prefill, steps, shares):
+    """Run the reference's attention layer (eager prefill, then one token at a time) on seeded hidden states
+    and record, per call: the input, the layer output, the tier counts it derived when it flushed, and the
+    lengths / tier sizes afterwards."""
+    from transformers.models.llama.configuration_llama import LlamaConfig
+    cfg = LlamaConfig(hidden_size=hidden, num_attention_heads=nh, num_key_value_heads=nkv, head_dim=128,
+                      intermediate_size=2 * hidden, num_hidden_layers=1, attention_bias=False, attention_dropout=0.0)
+    cfg._attn_implementation = "eager"
+    cfg.quant_strategy, cfg.times_range = strategy, True
+    cfg.bit_0, cfg.bit_4, cfg.bit_2, cfg.bit_1 = shares
+    gen = torch.Generator().manual_seed(seed)
+    attn = ref.llama_hqe.LlamaAttention_hqe(cfg, 0)
+    out = {"meta": np.array([B, hidden, nh, nkv, prefill, steps]), "shares": np.array(shares, dtype=np.float64),
+           "strategy": np.array(strategy)}
+    with torch.no_grad():
+        for pname in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            w = getattr(attn, pname).weight
+            w.copy_(torch.randn(w.shape, generator=gen) * w.shape[1] ** -0.5)
+        attn = attn.half()
+        for pname in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            out[f"w_{pname}"] = npy(getattr(attn, pname).weight)
+        attn.last_weights.set_max_length(prefill + steps)
+        cache, aux = None, None
+        pos = 0
+        for call in range(steps + 1):
+            S = prefill if call == 0 else 1
+            x = torch.randn(B, S, hidden, generator=gen).half()
+            cos, sin = rotary(torch.arange(pos, pos + S).unsqueeze(0).expand(B, S), 128)
+            mask = None
+            if call == 0:
+                mask = torch.full((S, S), torch.finfo(torch.float16).min, dtype=torch.float16).triu(1).view(1, 1, S, S)
+            y, _, cache, aux_out = attn(x, (cos, sin), mask, past_key_value=cache, auxiliary_parameters=None, use_cache=True)
+            pos += S
+            out[f"c{call}_x"], out[f"c{call}_y"] = npy(x), npy(y)
+            if aux_out is not None:
+                out[f"c{call}_ratio"], out[f"c{call}_bit_num"] = npy(aux_out[0]), npy(aux_out[1])
+            sizes = [0 if cache[i] is None else cache[i].numel() for i in (1, 5, 13, 21, 29, 3, 9, 17, 25, 33)]
+            out[f"c{call}_state"] = np.array([attn.current_length, attn.history_reserve_length, cache[41]] + sizes)
+    save(name, **out)
+
+
 def main():
     codec_cases()
     normal_codec_cases()
@@ -267,6 +318,10 @@ def main():
     flush_sequence("flush_n64", 15, 2, 1,
                    [(256 + 7, [64, 64, 64, 0, 64, 0]), (128, [64, 0, 64, 64, 128, 64])], times_range=True,
                    block=64, group=64, strategy="high_uniform_group_low_normal_group")
+    # the attention layer around the cache: prefill 420 tokens (two blocks evicted), 75 decode steps (three more flushes)
+    attention_module_case("attn_llama_n", 21, "high_uniform_group_low_normal_group", 2, 256, 2, 1, 420, 75,
+                          (0.25, 0.25, 0.25, 0.25))
+    attention_module_case("attn_llama_u", 22, "uniform_group", 1, 512, 4, 1, 200, 40, (0.1, 0.4, 0.3, 0.2))
 
 
 if __name__ == "__main__":

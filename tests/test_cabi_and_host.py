@@ -152,3 +152,27 @@ def test_make_sum_equal_matches_oracle(lib):
         a = make_sum_equal(torch.tensor(arr, dtype=torch.int32), target)
         b = O.make_sum_equal(arr.copy(), target)
         assert a.tolist() == b.tolist()
+
+
+@pytest.mark.parametrize("name", ["attn_llama_n", "attn_llama_u"])
+def test_tier_schedule_matches_reference_layer(name):
+    """The data-independent flush arithmetic of the attention layer (shares -> six token counts, lengths
+    before and after every flush) against what the reference's LlamaAttention_hqe derived, call by call."""
+    from conftest import load_golden
+    from hqekv_b200.model.attention_hqe import TierSchedule
+    z = load_golden(name)
+    B, hidden, nh, nkv, prefill, steps = (int(v) for v in z["meta"])
+    sch = TierSchedule(*(float(v) for v in z["shares"]))
+    flushes = 0
+    for call in range(steps + 1):
+        sch.append(prefill if call == 0 else 1)
+        if sch.due():
+            ratio, bit_num = sch.counts()
+            assert np.array_equal(bit_num.numpy(), z[f"c{call}_bit_num"]), f"{name} call {call}"
+            assert np.array_equal(ratio.numpy(), z[f"c{call}_ratio"]), f"{name} call {call}: shares"
+            sch.commit(int(bit_num[-1]), True)
+            flushes += 1
+        else:
+            assert f"c{call}_bit_num" not in z.files
+        assert [sch.current_length, sch.history_reserve_length] == [int(v) for v in z[f"c{call}_state"][:2]], f"{name} call {call}"
+    assert flushes >= 2

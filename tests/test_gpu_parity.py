@@ -480,3 +480,45 @@ def test_decode_long_context_shard_properties(ops, cuda_device):
     rel = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
     assert rel <= ATTN_REL_TOL, f"128k decode rel err {rel:.3e}"
     assert (w.float().sum(-1) - 1).abs().max().item() < 2e-2
+
+
+# ---------------------------------------------------------------------------------------------
+# the attention layer around the cache
+# ---------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("name", ["attn_llama_n", "attn_llama_u"])
+def test_attention_layer_against_reference_layer(ops, cuda_device, name):
+    """HqeAttention with the reference layer's weights on the reference layer's inputs: prefill, then one token
+    per call, flushing whenever 32 tokens are unquantised.  Exact: the tier counts of every flush, the lengths
+    and the size of every tier after every call (so the same blocks were ranked into the same tiers, evicted
+    blocks included).  Layer output: 1e-2 of the largest output of the call (fp16 GEMMs on different hardware,
+    and the reference's decode rounds per-tier logits to fp16)."""
+    from hqekv_b200.model.attention_hqe import HqeAttention, rotary_tables, causal_mask
+    z = load_golden(name)
+    B, hidden, nh, nkv, prefill, steps = (int(v) for v in z["meta"])
+    attn = HqeAttention(hidden, nh, nkv, 128, str(z["strategy"]), True, *(float(v) for v in z["shares"]))
+    with torch.no_grad():
+        for pname in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            getattr(attn, pname).weight.copy_(torch.from_numpy(z[f"w_{pname}"]).float())
+    attn = attn.half().to(cuda_device)
+    attn.set_max_length(prefill + steps)
+    cache, pos, worst = None, 0, 0.0
+    with torch.no_grad():
+        for call in range(steps + 1):
+            S = prefill if call == 0 else 1
+            x = torch.from_numpy(z[f"c{call}_x"]).to(cuda_device)
+            cos, sin = rotary_tables(torch.arange(pos, pos + S).unsqueeze(0).expand(B, S), 128, 10000.0)
+            mask = causal_mask(S, S, torch.float16, cuda_device) if call == 0 else None
+            y, _, cache, aux = attn(x, (cos.to(cuda_device), sin.to(cuda_device)), mask, cache, None)
+            pos += S
+            if f"c{call}_bit_num" in z.files:
+                assert aux is not None and np.array_equal(aux[1].cpu().numpy(), z[f"c{call}_bit_num"]), f"{name} call {call}"
+            else:
+                assert aux is None
+            sizes = [0 if cache[i] is None else cache[i].numel() for i in (1, 5, 13, 21, 29, 3, 9, 17, 25, 33)]
+            state = [attn.current_length, attn.history_reserve_length, cache[41]] + sizes
+            assert state == [int(v) for v in z[f"c{call}_state"]], f"{name} call {call}: state {state}"
+            want = z[f"c{call}_y"].astype(np.float32)
+            err = np.abs(y.float().cpu().numpy() - want).max() / np.abs(want).max()
+            worst = max(worst, err)
+            assert err <= 1e-2, f"{name} call {call}: layer output rel err {err:.3e}"
+    assert cache[28] is not None or cache[20] is not None
