@@ -188,13 +188,13 @@ class HqeAttention(nn.Module):
         rounded to the activations' dtype) for the ring — what the reference's flash branch computes
         (model/llama_hqe.py:141-166); its eager branch (:168-182) produces the same rows inside a full
         [S, S] matrix."""
-        B, _, S, _ = q.shape
+        B, nh, S, Dh = q.shape
         rep = self.num_key_value_groups
-        kr = k.repeat_interleave(rep, dim=1) if rep > 1 else k
-        vr = v.repeat_interleave(rep, dim=1) if rep > 1 else v
-        out = nn.functional.scaled_dot_product_attention(q, kr, vr, is_causal=S > 1, scale=self.scaling)
+        out = nn.functional.scaled_dot_product_attention(q, k, v, is_causal=S > 1, scale=self.scaling, enable_gqa=rep > 1)
         tail = min(S, SEED_QUERIES)
-        scores = torch.matmul(q[:, :, -tail:, :], kr.transpose(2, 3)) * self.scaling
+        # query heads of one kv head are adjacent: [B, kv, rep * tail, D] x [B, kv, D, S]
+        qt = q[:, :, -tail:, :].reshape(B, self.num_kv_heads, rep * tail, Dh)
+        scores = (torch.matmul(qt, k.transpose(2, 3)) * self.scaling).view(B, nh, tail, S)
         if attention_mask is not None:
             scores = scores + attention_mask[:, :, -tail:, :]
             scores = torch.max(scores, torch.tensor(torch.finfo(scores.dtype).min, device=scores.device))

@@ -1,0 +1,110 @@
+"""Decoder stack around :class:`HqeAttention`: the model-level caller of the decode path.
+
+Plain torch restatement of what ``LlamaDecoderLayer_hqe`` / ``LlamaModel_hqe``
+(model/llama_hqe.py:255-440) and their Qwen3 twins do with the attention layer: pre-norm residual
+blocks (RMSNorm -> attention -> RMSNorm -> SwiGLU MLP), one cache tuple per layer, and the
+``auxiliary_parameters`` (tier counts) of the first layer handed to all the others so that every layer
+flushes with the same counts (:407-430).  Weights are whatever the caller loads; nothing here depends on
+a transformers release.
+"""
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+from torch import nn
+
+from .attention_hqe import HeadRMSNorm, HqeAttention, rotary_tables
+
+
+@dataclass
+class DecoderConfig:
+    hidden_size: int = 4096
+    intermediate_size: int = 14336
+    num_layers: int = 32
+    num_heads: int = 32
+    num_kv_heads: int = 8
+    head_dim: int = 128
+    rms_eps: float = 1e-5
+    rope_theta: float = 500000.0
+    qk_norm: bool = False          # Qwen3: RMSNorm on every q / k head
+    vocab_size: int = 0            # 0: no embedding / lm_head (hidden states in, hidden states out)
+    quant_strategy: str = "high_uniform_group_low_normal_group"
+    times_range: bool = True
+    bit_0: float = 0.25
+    bit_4: float = 0.25
+    bit_2: float = 0.25
+    bit_1: float = 0.25
+
+
+LLAMA31_8B = DecoderConfig()
+QWEN3_8B = DecoderConfig(intermediate_size=12288, num_layers=36, rms_eps=1e-6, rope_theta=1000000.0, qk_norm=True)
+
+
+class SwiGLU(nn.Module):
+    def __init__(self, hidden: int, inter: int):
+        super().__init__()
+        self.gate_proj = nn.Linear(hidden, inter, bias=False)
+        self.up_proj = nn.Linear(hidden, inter, bias=False)
+        self.down_proj = nn.Linear(inter, hidden, bias=False)
+
+    def forward(self, x):
+        return self.down_proj(nn.functional.silu(self.gate_proj(x)) * self.up_proj(x))
+
+
+class HqeDecoderLayer(nn.Module):
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.self_attn = HqeAttention(cfg.hidden_size, cfg.num_heads, cfg.num_kv_heads, cfg.head_dim, cfg.quant_strategy,
+                                      cfg.times_range, cfg.bit_0, cfg.bit_4, cfg.bit_2, cfg.bit_1, cfg.qk_norm, cfg.rms_eps)
+        self.mlp = SwiGLU(cfg.hidden_size, cfg.intermediate_size)
+        self.input_layernorm = HeadRMSNorm(cfg.hidden_size, cfg.rms_eps)
+        self.post_attention_layernorm = HeadRMSNorm(cfg.hidden_size, cfg.rms_eps)
+
+    def forward(self, hidden_states, position_embeddings, attention_mask, past_key_value, auxiliary_parameters):
+        h, _, past_key_value, auxiliary_parameters = self.self_attn(
+            self.input_layernorm(hidden_states), position_embeddings, attention_mask, past_key_value, auxiliary_parameters)
+        hidden_states = hidden_states + h
+        hidden_states = hidden_states + self.mlp(self.post_attention_layernorm(hidden_states))
+        return hidden_states, past_key_value, auxiliary_parameters
+
+
+class HqeDecoder(nn.Module):
+    """Stack of decoder layers with per-layer tiered caches.  ``forward(inputs, caches, position)`` takes token
+    ids [B, S] (``vocab_size > 0``) or hidden states [B, S, hidden]; returns (logits or hidden states, caches)."""
+
+    def __init__(self, cfg: DecoderConfig):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = nn.Embedding(cfg.vocab_size, cfg.hidden_size) if cfg.vocab_size else None
+        self.layers = nn.ModuleList(HqeDecoderLayer(cfg) for _ in range(cfg.num_layers))
+        self.norm = HeadRMSNorm(cfg.hidden_size, cfg.rms_eps)
+        self.lm_head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False) if cfg.vocab_size else None
+
+    def start_sequence(self, max_length: int):
+        """Forget the previous sequence and size the importance rings (model/llama_hqe.py:557, 691-695)."""
+        for layer in self.layers:
+            layer.self_attn.reset()
+            layer.self_attn.set_max_length(max_length)
+
+    def forward(self, inputs: torch.Tensor, caches: Optional[List[tuple]] = None, position: int = 0):
+        x = self.embed_tokens(inputs) if self.embed_tokens is not None else inputs
+        B, S, _ = x.shape
+        pos = torch.arange(position, position + S, device=x.device).unsqueeze(0).expand(B, S)
+        rope = rotary_tables(pos, self.cfg.head_dim, self.cfg.rope_theta, x.dtype)
+        caches = [None] * len(self.layers) if caches is None else list(caches)
+        aux = None  # the first layer derives the tier counts, the others reuse them
+        for i, layer in enumerate(self.layers):
+            x, caches[i], aux = layer(x, rope, None, caches[i], aux)
+        x = self.norm(x)
+        return (self.lm_head(x) if self.lm_head is not None else x), caches
+
+
+def init_like_pretrained(model: nn.Module, seed: int = 0):
+    """Random weights with the scale of a trained transformer (projection rows of unit norm in expectation),
+    drawn on the module's device: stands in for a checkpoint where none can be loaded."""
+    gen = torch.Generator(device=next(model.parameters()).device).manual_seed(seed)
+    with torch.no_grad():
+        for p in model.parameters():
+            if p.dim() == 2:
+                p.copy_(torch.randn(p.shape, generator=gen, device=p.device, dtype=torch.float32).mul_(p.shape[1] ** -0.5))
+    return model

@@ -522,3 +522,34 @@ def test_attention_layer_against_reference_layer(ops, cuda_device, name):
             worst = max(worst, err)
             assert err <= 1e-2, f"{name} call {call}: layer output rel err {err:.3e}"
     assert cache[28] is not None or cache[20] is not None
+
+
+def test_decoder_stack_shares_tier_counts_and_matches_dense_attention(ops, cuda_device):
+    """Two-layer decoder (Qwen3 flavour: q/k RMSNorm) on the tiered cache: every layer flushes with the first
+    layer's tier counts, the caches account for every position, and a decode step's attention equals dense fp32
+    attention over the reconstructed cache of that layer (2e-3)."""
+    from hqekv_b200.model.decoder import DecoderConfig, HqeDecoder, init_like_pretrained
+    cfg = DecoderConfig(hidden_size=256, intermediate_size=512, num_layers=2, num_heads=2, num_kv_heads=1, qk_norm=True,
+                        rope_theta=10000.0)
+    model = init_like_pretrained(HqeDecoder(cfg).half().to(cuda_device), 3).eval()
+    gen = torch.Generator(device=cuda_device).manual_seed(5)
+    ctx, steps, B = 300, 70, 2
+    model.start_sequence(ctx + steps)
+    with torch.no_grad():
+        h, caches = model(torch.randn(B, ctx, 256, generator=gen, device=cuda_device).half(), None, 0)
+        row = h[:, -1:, :]
+        for s in range(steps):
+            row, caches = model(row, caches, ctx + s)
+            assert torch.isfinite(row).all()
+    a0, a1 = model.layers[0].self_attn, model.layers[1].self_attn
+    assert (a0.current_length, a0.history_reserve_length) == (a1.current_length, a1.history_reserve_length)
+    for c, a in zip(caches, (a0, a1)):
+        sizes_k = sum(0 if c[i] is None else c[i].numel() for i in (1, 5, 13, 21, 29))
+        sizes_v = sum(0 if c[i] is None else c[i].numel() for i in (3, 9, 17, 25, 33))
+        assert sizes_k == sizes_v == a.history_reserve_length and c[39].shape[2] == a.current_length
+        assert c[41] == ctx + steps
+    assert a0.history_reserve_length < ctx + steps - a0.current_length          # something was evicted
+    assert caches[0][28] is not None                                            # the Gaussian-codebook tier is in use
+    # one more attention call on layer 1's cache against dense attention over its reconstruction
+    q = torch.randn(B, 2, 1, 128, generator=gen, device=cuda_device).half()
+    check_attention(ops, caches[1], q, 32, 32, "decoder layer 1 cache", cfg.quant_strategy)
