@@ -38,9 +38,10 @@ class TierSchedule:
     arithmetic in the reference's order of operations, because the rounding decides block counts."""
 
     def __init__(self, bit_0: float, bit_4: float, bit_2: float, bit_1: float):
-        self.ratio_e_0 = torch.tensor([bit_0], dtype=torch.float32)
+        # host-side bookkeeping: CPU tensors whatever the default device is
+        self.ratio_e_0 = torch.tensor([bit_0], dtype=torch.float32, device="cpu")
         self.ratio_e = self.ratio_e_0.clone()
-        self.ratio_q = torch.tensor([bit_4, bit_2, bit_1], dtype=torch.float32)
+        self.ratio_q = torch.tensor([bit_4, bit_2, bit_1], dtype=torch.float32, device="cpu")
         self.current_length = 0           # tokens in the fp16 residual window
         self.history_reserve_length = 0   # tokens in the tiers
 
@@ -59,7 +60,7 @@ class TierSchedule:
     def counts(self):
         """(compress_ratio, bit_num): shares and token counts of the flush that is due."""
         _, total, block_num = self.lengths()
-        head = torch.tensor([FP16_TOKENS / total, 0], dtype=torch.float32)
+        head = torch.tensor([FP16_TOKENS / total, 0], dtype=torch.float32, device="cpu")
         ratio = torch.cat((head, self.ratio_q, self.ratio_e))
         ratio[2:] = (1 - ratio[0]) * ratio[2:]
         bit_num = torch.round(block_num * ratio).to(torch.int)
