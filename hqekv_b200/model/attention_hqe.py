@@ -221,11 +221,11 @@ class HqeAttention(nn.Module):
         return past_key_value, (ratio, k_bits, v_bits)
 
     # -- the layer ------------------------------------------------------------------------------
-    def forward(self, hidden_states: torch.Tensor, position_embeddings: Tuple[torch.Tensor, torch.Tensor],
-                attention_mask: Optional[torch.Tensor] = None, past_key_value: Optional[tuple] = None,
-                auxiliary_parameters: Optional[tuple] = None, output_attentions: bool = False, use_cache: bool = True):
-        B, S, _ = hidden_states.shape
-        q, k, v = self._project(hidden_states, position_embeddings)
+    def attend(self, q, k, v, attention_mask=None, past_key_value=None, auxiliary_parameters=None):
+        """Everything between the projections: cache append, attention, ring update, flush when due.
+        q [B, nh, S, D], k / v [B, nkv, S, D] already normalised and rotated.  Returns (context [B, S, nh*D],
+        attn_weights, past_key_value, auxiliary_parameters)."""
+        B, _, S, _ = q.shape
         kv_seq_len = S
         self.schedule.append(S)
         if past_key_value is not None:
@@ -238,13 +238,20 @@ class HqeAttention(nn.Module):
         else:
             attn_weights, attn_output = self._prefill(q, k, v, attention_mask)
             past_key_value = (None,) * 39 + (k, v, kv_seq_len)
-        attn_output = attn_output.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim)
-        attn_output = self.o_proj(attn_output)
+        context = attn_output.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim)
 
         self.last_weights.update(attn_weights)
         if self.schedule.due():
             past_key_value, auxiliary_parameters = self._flush(past_key_value, auxiliary_parameters)
         else:
             auxiliary_parameters = None
-        return attn_output, (attn_weights if output_attentions else None), (past_key_value if use_cache else None), \
-            auxiliary_parameters
+        return context, attn_weights, past_key_value, auxiliary_parameters
+
+    def forward(self, hidden_states: torch.Tensor, position_embeddings: Tuple[torch.Tensor, torch.Tensor],
+                attention_mask: Optional[torch.Tensor] = None, past_key_value: Optional[tuple] = None,
+                auxiliary_parameters: Optional[tuple] = None, output_attentions: bool = False, use_cache: bool = True):
+        q, k, v = self._project(hidden_states, position_embeddings)
+        context, attn_weights, past_key_value, auxiliary_parameters = self.attend(q, k, v, attention_mask, past_key_value,
+                                                                                 auxiliary_parameters)
+        return self.o_proj(context), (attn_weights if output_attentions else None), \
+            (past_key_value if use_cache else None), auxiliary_parameters

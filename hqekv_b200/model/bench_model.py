@@ -4,7 +4,8 @@
 
 Prefills ``ctx`` synthetic hidden-state rows through every layer (dense causal attention, ring seeding, first
 flush), then decodes ``steps`` tokens one at a time, each step feeding the previous step's output row back in;
-every 32nd step every layer flushes its residual window.  Prints one JSON line: decode tokens/s over all steps
+every 32nd step every layer flushes its residual window.  The dense parts of a decode step (norms, projections,
+rotary, MLP) are replayed from CUDA graphs unless ``--no-graphs``; the cache-facing calls are issued eagerly.  Prints one JSON line: decode tokens/s over all steps
 (flush steps included), the same without the flush steps, prefill seconds, and the cache footprint against an
 fp16 cache.  Timed with CUDA events on the current stream; weights are random (no checkpoint is read), so the
 numbers measure the runtime, not a model's quality.
@@ -15,7 +16,7 @@ import time
 
 import torch
 
-from .decoder import LLAMA31_8B, QWEN3_8B, DecoderConfig, HqeDecoder, init_like_pretrained
+from .decoder import LLAMA31_8B, QWEN3_8B, DecoderConfig, GraphedDecodeStep, HqeDecoder, init_like_pretrained
 
 MODELS = {"llama31-8b": LLAMA31_8B, "qwen3-8b": QWEN3_8B}
 
@@ -38,6 +39,7 @@ def main(argv=None):
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--strategy", default="high_uniform_group_low_normal_group")
+    ap.add_argument("--no-graphs", action="store_true", help="issue the dense parts of a decode step eagerly")
     args = ap.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("bench_model needs a GPU")
@@ -67,12 +69,13 @@ def main(argv=None):
         row = h[:, -1:, :].contiguous()
         del h
         pos = args.ctx
+        step = model if args.no_graphs else GraphedDecodeStep(model, args.batch)
         ev = [torch.cuda.Event(enable_timing=True) for _ in range(total_steps + 1)]
         flushed = []
         ev[0].record()
         for s in range(total_steps):
             before = model.layers[0].self_attn.history_reserve_length
-            row, caches = model(row, caches, pos)
+            row, caches = step(row, caches, pos)
             pos += 1
             flushed.append(model.layers[0].self_attn.history_reserve_length != before)
             ev[s + 1].record()
@@ -92,7 +95,8 @@ def main(argv=None):
         "flush_steps": int(sum(timed_flush)), "steps": len(timed), "warmup": args.warmup,
         "prefill_s": round(prefill_s, 3),
         "config": {"model": args.model, "layers": cfg.num_layers, "batch": args.batch, "context": args.ctx,
-                   "strategy": args.strategy, "shares_evict_4_2_1": [cfg.bit_0, cfg.bit_4, cfg.bit_2, cfg.bit_1]},
+                   "strategy": args.strategy,
+                   "dense_parts": "eager" if args.no_graphs else "cuda graphs", "shares_evict_4_2_1": [cfg.bit_0, cfg.bit_4, cfg.bit_2, cfg.bit_1]},
         "cached_tokens": cached_tokens, "positions": pos,
         "cache_bytes": cache_nbytes(caches), "fp16_cache_bytes": fp16_bytes,
         "data": "synthetic hidden states, random-init weights", "dtype": "f16",

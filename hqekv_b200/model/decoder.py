@@ -99,6 +99,93 @@ class HqeDecoder(nn.Module):
         return (self.lm_head(x) if self.lm_head is not None else x), caches
 
 
+class GraphedDecodeStep:
+    """Single-token decode of an :class:`HqeDecoder` with the dense parts replayed from CUDA graphs.
+
+    Between two layers' cache accesses everything has static shapes: o_proj + residual + norm + MLP of layer
+    i and norm + q/k/v projections + rotary of layer i+1.  Each such segment is captured once into a CUDA
+    graph over static buffers; per layer the host then issues one graph replay plus the cache-facing calls
+    (append to the residual window, ``qkv_matmul_hqe_2``, ring update, the flush when it is due), whose
+    shapes change from step to step.  Results are those of ``HqeDecoder.forward`` on a [B, 1, hidden] input."""
+
+    def __init__(self, model: HqeDecoder, batch: int):
+        cfg, self.model = model.cfg, model
+        p = next(model.parameters())
+        dev, dt = p.device, p.dtype
+        z = lambda *shape: torch.zeros(*shape, device=dev, dtype=dt)  # noqa: E731
+        n = len(model.layers)
+        self.x = z(batch, 1, cfg.hidden_size) if model.embed_tokens is None else None
+        self.ids = torch.zeros(batch, 1, dtype=torch.long, device=dev) if model.embed_tokens is not None else None
+        self.h = z(batch, 1, cfg.hidden_size)            # residual stream
+        self.cos, self.sin = z(batch, 1, cfg.head_dim), z(batch, 1, cfg.head_dim)
+        self.q = [z(batch, cfg.num_heads, 1, cfg.head_dim) for _ in range(n)]
+        self.k = [z(batch, cfg.num_kv_heads, 1, cfg.head_dim) for _ in range(n)]
+        self.v = [z(batch, cfg.num_kv_heads, 1, cfg.head_dim) for _ in range(n)]
+        self.ctx = [z(batch, 1, cfg.num_heads * cfg.head_dim) for _ in range(n)]
+        self.out = z(batch, 1, cfg.vocab_size or cfg.hidden_size)
+        self.pos = torch.zeros(batch, 1, dtype=torch.long, device=dev)
+        self.graphs = []
+        self._capture()
+
+    def _pre(self, i):
+        layer = self.model.layers[i]
+        q, k, v = layer.self_attn._project(layer.input_layernorm(self.h), (self.cos, self.sin))
+        self.q[i].copy_(q)
+        self.k[i].copy_(k)
+        self.v[i].copy_(v)
+
+    def _post(self, i):
+        layer = self.model.layers[i]
+        self.h.add_(layer.self_attn.o_proj(self.ctx[i]))
+        self.h.add_(layer.mlp(layer.post_attention_layernorm(self.h)))
+
+    def _segment(self, s):
+        n = len(self.model.layers)
+        if s == 0:
+            m = self.model
+            self.h.copy_(m.embed_tokens(self.ids) if m.embed_tokens is not None else self.x)
+            cos, sin = rotary_tables(self.pos, m.cfg.head_dim, m.cfg.rope_theta, self.h.dtype)
+            self.cos.copy_(cos)
+            self.sin.copy_(sin)
+        else:
+            self._post(s - 1)
+        if s < n:
+            self._pre(s)
+        else:
+            y = self.model.norm(self.h)
+            self.out.copy_(self.model.lm_head(y) if self.model.lm_head is not None else y)
+
+    @torch.no_grad()
+    def _capture(self):
+        n = len(self.model.layers)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):  # library workspaces and autotuning happen outside the capture
+            for s in range(n + 1):
+                self._segment(s)
+        torch.cuda.current_stream().wait_stream(side)
+        pool = None
+        for s in range(n + 1):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, pool=pool):
+                self._segment(s)
+            pool = g.pool()
+            self.graphs.append(g)
+
+    @torch.no_grad()
+    def __call__(self, inputs: torch.Tensor, caches: List[tuple], position: int):
+        (self.ids if self.ids is not None else self.x).copy_(inputs)
+        self.pos.fill_(position)
+        caches = list(caches)
+        aux = None
+        self.graphs[0].replay()
+        for i, layer in enumerate(self.model.layers):
+            ctx, _, caches[i], aux = layer.self_attn.attend(self.q[i], self.k[i], self.v[i], None, caches[i], aux)
+            self.ctx[i].copy_(ctx)
+            self.graphs[i + 1].replay()
+        return self.out.clone(), caches
+
+
 def init_like_pretrained(model: nn.Module, seed: int = 0):
     """Random weights with the scale of a trained transformer (projection rows of unit norm in expectation),
     drawn on the module's device: stands in for a checkpoint where none can be loaded."""
