@@ -131,11 +131,13 @@ class PeerGather:
         """This rank's rows inside its own gathered buffer ([B, nh_q/world, 1, D])."""
         return self.buffers[slot][self.rank]
 
-    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int):
+    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int,
+               quant_strategy: str = "uniform_group"):
         """Fused decode of this rank's heads; returns (attn_weights_local, gathered [world, B, nh_q/world, 1, D])."""
-        from ._lib import check, decode_workspace, stream_ptr
+        from ._lib import CODEC_NORMAL, CODEC_UNIFORM, check, decode_workspace, stream_ptr
         from .quant._cache import cached_cache_desc
-        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+        low_codec = CODEC_UNIFORM if quant_strategy == "uniform_group" else CODEC_NORMAL
+        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size, low_codec)
         q = q.contiguous()
         weights = torch.empty(q.shape[0], q.shape[1], 1, L, dtype=torch.float16, device=dev)
         out = self.local_block(slot)
@@ -196,11 +198,13 @@ class FlaggedPeerGather:
         torch.cuda.synchronize(device)
         dist.barrier(group)  # nobody sends before every receive buffer is zero
 
-    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int):
+    def decode(self, slot: int, q: torch.Tensor, past_key_value: tuple, block_size: int, group_size: int,
+               quant_strategy: str = "uniform_group"):
         """Fused decode of this rank's heads; returns (attn_weights_local, gathered [world, B, nh_q/world, 1, D])."""
-        from ._lib import check, decode_workspace, stream_ptr
+        from ._lib import CODEC_NORMAL, CODEC_UNIFORM, check, decode_workspace, stream_ptr
         from .quant._cache import cached_cache_desc
-        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size)
+        low_codec = CODEC_UNIFORM if quant_strategy == "uniform_group" else CODEC_NORMAL
+        desc, keep, L, dev = cached_cache_desc(past_key_value, q.shape[1], block_size, group_size, low_codec)
         q = q.contiguous()
         weights = torch.empty(q.shape[0], q.shape[1], 1, L, dtype=torch.float16, device=dev)
         gathered = self.buffers[slot]

@@ -22,7 +22,13 @@ from .quant._cache import build_cache_desc
 from .quant.pack_unpack import uniform_group_quantize_pack_last_dim
 
 TIER_MIXES = {"all8": (1.0, 0.0, 0.0), "all4": (0.0, 1.0, 0.0), "all2": (0.0, 0.0, 1.0), "all1": (0.0, 0.0, 0.0, 1.0),
-              "mixed": (0.25, 0.5, 0.25)}
+              "mixed": (0.25, 0.5, 0.25),
+              # trailing "n": quant_strategy 'high_uniform_group_low_normal_group' (1-bit tier = Gaussian codebook)
+              "all1n": (0.0, 0.0, 0.0, 1.0), "mixed1n": (0.25, 0.25, 0.25, 0.25)}
+
+
+def _strategy(mix):
+    return "high_uniform_group_low_normal_group" if mix.endswith("n") else "uniform_group"
 
 
 def _graph_time(fn, reps):
@@ -51,8 +57,8 @@ def decode_point(dev, ctx, mix, group, batch, layers, peak_gbs):
                                 TIER_MIXES[mix], 0.0, group, True, layers)
     items = []
     for layer in range(layers):
-        cache, q = synthetic.build_cache(cfg, dev, seed=layer % 4)
-        desc, keep, L, _ = build_cache_desc(cache, cfg.nh_q, group, group)
+        cache, q = synthetic.build_cache(cfg, dev, seed=layer % 4, quant_strategy=_strategy(mix))
+        desc, keep, L, _ = build_cache_desc(cache, cfg.nh_q, group, group, 1 if mix.endswith("n") else 0)
         ws = torch.zeros(lib.hqkv_decode_workspace_bytes(desc), dtype=torch.uint8, device=dev)
         w = torch.empty(batch, cfg.nh_q, 1, L, dtype=torch.float16, device=dev)
         o = torch.empty(batch, cfg.nh_q, 1, 128, dtype=torch.float16, device=dev)
@@ -93,6 +99,8 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--out", default="sweep.jsonl")
     ap.add_argument("--quick", action="store_true")
+    ap.add_argument("--mixes", default="", help="comma-separated tier mixes instead of the default set, e.g. all1,all1n")
+    ap.add_argument("--ctxs", default="", help="comma-separated context lengths instead of the default set")
     args = ap.parse_args()
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
@@ -100,9 +108,14 @@ def main():
     peak = float(json.load(open(peaks))["hbm_gbs"]) if os.path.exists(peaks) else 6650.0
     os.makedirs(os.path.dirname(args.out) or ".", exist_ok=True)
     ctxs = (1024 + 128, 4096, 32768) if args.quick else (1024 + 128, 4096, 16384, 32768, 131072)
+    if args.ctxs:
+        ctxs = tuple(int(c) for c in args.ctxs.split(","))
+    mixes = ("mixed",) if args.quick else ("all8", "all4", "all2", "all1", "mixed")
+    if args.mixes:
+        mixes = tuple(args.mixes.split(","))
     points = []
     for ctx in ctxs:
-        for mix in (("mixed",) if args.quick else ("all8", "all4", "all2", "all1", "mixed")):
+        for mix in mixes:
             for group in ((32,) if args.quick else (32, 128)):
                 for batch in (1, 8, 32):
                     per_layer = batch * 8 * ctx * 288          # upper bound, bytes
