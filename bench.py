@@ -118,12 +118,13 @@ class ClockSampler:
 # -------------------------------------------------------------------------------------------------
 # CPU arm: the numpy oracle (a port of the reference's pure-PyTorch dequant + matmul path) on the host
 # -------------------------------------------------------------------------------------------------
-def cpu_decode_seconds(cache_host, q_host, group, threads):
+def cpu_decode_seconds(cache_host, q_host, group, threads, strategy="uniform_group"):
     """Seconds for one layer's decode attention on the host: dense dequantisation of every tier
     (KV_cache_reconstruct_hqe) + fp32 softmax(q K^T) V, kv heads spread over `threads` threads."""
     from concurrent.futures import ThreadPoolExecutor
     from oracle import hqkv_oracle as O
-    H = next(x for x in (cache_host[40], cache_host[8], cache_host[16], cache_host[24]) if x is not None).shape[1]
+    H = next(x for x in (cache_host[40], cache_host[2], cache_host[8], cache_host[16], cache_host[24], cache_host[32])
+             if x is not None).shape[1]
     rep = q_host.shape[1] // H
 
     def head_slice(h):
@@ -137,7 +138,7 @@ def cpu_decode_seconds(cache_host, q_host, group, threads):
 
     def run(h):
         c, q = head_slice(h)
-        return O.decode_attention(q, c, None, group, group, dequant="fp16")
+        return O.decode_attention(q, c, None, group, group, dequant="fp16", quant_strategy=strategy)
 
     t0 = time.perf_counter()
     if threads > 1:
@@ -175,6 +176,7 @@ def main():
     config = {"workload": cfg.name, "layers": layers, "batch": cfg.batch, "context": cfg.context,
               "q_heads": cfg.nh_q, "kv_heads": cfg.nh_kv, "head_dim": cfg.head_dim, "group": cfg.group,
               "residual": cfg.residual, "evicted_frac": cfg.evict, "tier_ratio_8_4_2": list(cfg.ratios),
+              "fp16_tokens": cfg.fp16_tokens, "quant_strategy": cfg.strategy,
               "parallelism": f"kv-head-shard x{world}" if world > 1 else "single-gpu",
               "l2": "one step streams layers x cache bytes (>> 126 MB L2); no flush needed"}
 
@@ -193,8 +195,8 @@ def main():
         cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in cache)
         q_host = q.cpu().numpy()
         for _ in range(max(1, min(args.warmup, 1))):
-            cpu_decode_seconds(cache_host, q_host, cfg.group, threads)
-        times = [cpu_decode_seconds(cache_host, q_host, cfg.group, threads) for _ in range(max(1, min(args.steps, 5)))]
+            cpu_decode_seconds(cache_host, q_host, cfg.group, threads, cfg.strategy)
+        times = [cpu_decode_seconds(cache_host, q_host, cfg.group, threads, cfg.strategy) for _ in range(max(1, min(args.steps, 5)))]
         per_layer = statistics.median(times)
         step_s = per_layer * layers
         value = cfg.batch / step_s
@@ -252,9 +254,9 @@ def main():
             from hqekv_b200.sharding import FlaggedPeerGather, PeerGather
             peer = (PeerGather if args.peer_gather == "barrier" else FlaggedPeerGather)(
                 max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
-            _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+            _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
             dist.all_gather_into_tensor(gathered[0], o_ref)
-            _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group)
+            _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group, cfg.strategy)
             torch.cuda.synchronize()
             ok = torch.tensor([int(torch.equal(got, gathered[0]) and peer.status() == 0)], device=dev)
             dist.all_reduce(ok, op=dist.ReduceOp.MIN)
@@ -269,9 +271,9 @@ def main():
 
     def decode_layer(i, q):
         if peer is not None:
-            w, g = peer.decode(i, q, caches[i], cfg.group, cfg.group)
+            w, g = peer.decode(i, q, caches[i], cfg.group, cfg.group, cfg.strategy)
             return g[rank]
-        w, o = qkv_matmul_hqe_2(q, caches[i], None, cfg.head_dim, "uniform_group", cfg.group, cfg.group)
+        w, o = qkv_matmul_hqe_2(q, caches[i], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
         if world > 1:
             dist.all_gather_into_tensor(gathered[i], o)
         return o
@@ -415,7 +417,7 @@ def main():
     peak, peak_kind = load_peaks()
     descs = []
     for i in range(layers):
-        desc, keep, Ld, _ = build_cache_desc(caches[i], nh_q_local, cfg.group, cfg.group)
+        desc, keep, Ld, _ = build_cache_desc(caches[i], nh_q_local, cfg.group, cfg.group, 0 if cfg.strategy == "uniform_group" else 1)
         need = lib.hqkv_decode_workspace_bytes(desc)
         ws = torch.zeros(need, dtype=torch.uint8, device=dev)
         w = torch.empty(cfg.batch, nh_q_local, 1, Ld, dtype=torch.float16, device=dev)
@@ -474,8 +476,8 @@ def main():
         cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in caches[0])
         qh = qs[0].cpu().numpy()
         threads = 1
-        cpu_decode_seconds(cache_host, qh, cfg.group, threads)
-        ts = [cpu_decode_seconds(cache_host, qh, cfg.group, threads) for _ in range(3)]
+        cpu_decode_seconds(cache_host, qh, cfg.group, threads, cfg.strategy)
+        ts = [cpu_decode_seconds(cache_host, qh, cfg.group, threads, cfg.strategy) for _ in range(3)]
         per_layer = statistics.median(ts)
         cpu_baseline = {"value": cfg.batch / (per_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
                         "sample": f"one layer of {cfg.name} ({L} cached tokens, {cfg.nh_kv} kv heads) through the numpy "

@@ -25,6 +25,8 @@ class CacheConfig:
     group: int            # K block / group size and V group size
     k_outliers: bool      # 4 random K channels per head scaled x10
     layers: int = 1
+    fp16_tokens: int = 0  # tokens kept in the 16-bit tier (the reference's models keep 64)
+    strategy: str = "uniform_group"   # or 'high_uniform_group_low_normal_group' (1-bit tier = Gaussian codebook)
 
 
 CONFIGS = {
@@ -36,6 +38,10 @@ CONFIGS = {
     "cfg2": CacheConfig("cfg2-qwen3-8b-b8-16k", 8, 32, 8, 128, 16384, 128, (0.25, 0.50, 0.25), 0.0, 64, True, 36),
     # long-context sizing, heads sharded over 8 GPUs
     "cfg3": CacheConfig("cfg3-llama3.1-8b-b4-128k", 4, 32, 8, 128, 131072, 256, (0.10, 0.25, 0.65), 0.30, 32, False, 32),
+    # the setting the reference's own model files run (pred_long_bench_hq.py:135-141): 64 fp16 tokens, no 8-bit
+    # tier, equal 4 / 2 / 1-bit shares with the 1-bit tier in the Gaussian codebook, a quarter evicted
+    "cfgm": CacheConfig("cfgm-llama3.1-8b-32k-model-shares", 1, 32, 8, 128, 32768, 128, (0.0, 1 / 3, 1 / 3, 1 / 3), 0.25,
+                        32, False, 32, 64, "high_uniform_group_low_normal_group"),
 }
 
 
@@ -48,12 +54,14 @@ def tier_counts(cfg: CacheConfig):
     assert flushed % block == 0, "context - residual must be a multiple of the block size"
     nblocks = flushed // block
     ev = int(round(nblocks * cfg.evict))
-    keep = nblocks - ev
+    f16 = min(cfg.fp16_tokens // block, nblocks - ev)
+    keep = nblocks - ev - f16
     one = round(keep * cfg.ratios[3]) if len(cfg.ratios) > 3 else 0  # optional uniform 1-bit share
     raw = torch.tensor([0, round(keep * cfg.ratios[0]), round(keep * cfg.ratios[1]), round(keep * cfg.ratios[2]), one],
                        dtype=torch.int32)
     raw = make_sum_equal(raw, keep, start_idx=4 if one else 3)
     counts = [int(v) * block for v in raw.tolist()] + [ev * block]
+    counts[0] = f16 * block
     assert sum(counts) == flushed
     return counts
 
@@ -91,10 +99,11 @@ def synthetic_importance(cfg: CacheConfig, device, seed: int, length: int):
 
 
 def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range: bool = False,
-                quant_strategy: str = "uniform_group"):
+                quant_strategy: str = None):
     """Prefill-shaped K/V -> one flush through KV_cache_hqe_2 -> (cache tuple, q).  With
     ``times_range=False`` K and V are ranked identically, so every rank of a head-sharded run selects
     the same blocks without exchanging value ranges."""
+    quant_strategy = quant_strategy or cfg.strategy
     K, V, q = make_kv(cfg, device, seed, heads)
     flushed = cfg.context - cfg.residual
     counts = tier_counts(cfg)
