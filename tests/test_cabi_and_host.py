@@ -58,6 +58,28 @@ def test_argument_validation_needs_no_gpu(lib):
     assert b"pointers are null" in L.hqkv_last_error()
 
 
+def test_gaussian_codebook_entry_points_validate_without_gpu(lib):
+    """The 1-bit Gaussian-codebook tier: codec flags are checked before any device work."""
+    L = lib.lib
+    assert L.hqkv_gemv_normal_group(None, None, None, None, 1, 4, 1, 128, 128, 32, 2, None, None) == -1
+    assert b"1 bit only" in L.hqkv_last_error()
+    assert L.hqkv_gemv_normal_group(None, None, None, None, 1, 4, 1, 128, 128, 32, 1, None, None) == -1
+    assert b"null pointer" in L.hqkv_last_error()
+    assert L.hqkv_normal1_quantize_pack(None, 4, 48, 4, 48, 48, 1, 32, None, None, None, None) == -1
+    assert b"multiple of the group" in L.hqkv_last_error()
+    assert L.hqkv_normal1_quantize_pack(None, 0, 32, 1, 32, 32, 1, 32, None, None, None, None) == 0     # empty input
+    assert L.hqkv_normal1_dequantize_unpack(None, None, None, 4, 64, 48, None, None) == -1
+    src = lib.FlushSrc()
+    src.low_codec = 7
+    assert L.hqkv_flush_build_v(src, 1, 1, 128, 32, 4, None, 32, None, None, None, None) == -1
+    assert b"low_codec" in L.hqkv_last_error()
+    desc = lib.CacheDesc()
+    desc.B, desc.H, desc.nh_q, desc.D, desc.group_k, desc.group_v = 1, 8, 32, 128, 32, 32
+    desc.tier[3].bits, desc.tier[3].n_k, desc.tier[3].n_v, desc.tier[3].codec = 2, 32, 32, lib.CODEC_NORMAL
+    assert L.hqkv_decode_attention(desc, None, None, None, None, 0, None) == -1
+    assert b"codec" in L.hqkv_last_error()
+
+
 def test_peer_entry_points_validate_without_gpu(lib):
     """kv-head sharding entry points: argument checks run before anything touches a device."""
     import ctypes as C
