@@ -180,7 +180,10 @@ class GraphedDecodeStep:
         aux = None
         self.graphs[0].replay()
         for i, layer in enumerate(self.model.layers):
-            ctx, _, caches[i], aux = layer.self_attn.attend(self.q[i], self.k[i], self.v[i], None, caches[i], aux)
+            k, v = self.k[i], self.v[i]
+            if caches[i][-3] is None:  # an empty residual window would adopt the static rows as its storage
+                k, v = k.clone(), v.clone()
+            ctx, _, caches[i], aux = layer.self_attn.attend(self.q[i], k, v, None, caches[i], aux)
             self.ctx[i].copy_(ctx)
             self.graphs[i + 1].replay()
         return self.out.clone(), caches

@@ -550,17 +550,27 @@ def test_decoder_stack_shares_tier_counts_and_matches_dense_attention(ops, cuda_
         assert c[41] == ctx + steps
     assert a0.history_reserve_length < ctx + steps - a0.current_length          # something was evicted
     assert caches[0][28] is not None                                            # the Gaussian-codebook tier is in use
-    # the same steps with the dense parts replayed from CUDA graphs give the same rows and the same caches
+    # the same steps with the dense parts replayed from CUDA graphs: a twin model is fed the eager model's rows
+    # step by step (the recurrence through random weights amplifies rounding noise, so the runs are compared
+    # call by call, not after 70 free-running steps)
+    import copy
     from hqekv_b200.model.decoder import GraphedDecodeStep
-    model.start_sequence(ctx + steps)
+    twin = copy.deepcopy(model)
+    for m in (model, twin):
+        m.start_sequence(ctx + steps)
     gen2 = torch.Generator(device=cuda_device).manual_seed(5)
     with torch.no_grad():
-        h, caches_g = model(torch.randn(B, ctx, 256, generator=gen2, device=cuda_device).half(), None, 0)
-        step = GraphedDecodeStep(model, B)
-        row_g = h[:, -1:, :]
+        x0 = torch.randn(B, ctx, 256, generator=gen2, device=cuda_device).half()
+        h, caches = model(x0, None, 0)
+        _, caches_g = twin(x0, None, 0)
+        step = GraphedDecodeStep(twin, B)
+        row = h[:, -1:, :]
         for s in range(steps):
-            row_g, caches_g = step(row_g, caches_g, ctx + s)
-    assert (row_g.float() - row.float()).abs().max() <= 2e-2 * row.float().abs().max()
+            nxt, caches = model(row, caches, ctx + s)
+            nxt_g, caches_g = step(row, caches_g, ctx + s)
+            err = (nxt_g.float() - nxt.float()).abs().max() / nxt.float().abs().max()
+            assert err <= 1e-2, f"graphed decode step {s}: rel err {err:.3e}"
+            row = nxt
     for cg, ce in zip(caches_g, caches):
         assert [None if t is None else tuple(t.shape) for t in cg[:41]] == [None if t is None else tuple(t.shape) for t in ce[:41]]
     # one more attention call on layer 1's cache against dense attention over its reconstruction
