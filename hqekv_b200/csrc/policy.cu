@@ -13,15 +13,30 @@ constexpr int D = 128;
 // ------------------------------------------------------------------------------------------------
 // importance ring
 // ------------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) head_sum_kernel(const __half* __restrict__ w, int B, int nh, int64_t L,
-                                                       int64_t bh_stride, __half* __restrict__ out) {
+// One thread per position.  The adds run in the reference's order (batch first, rounded to fp16 per head,
+// then heads, one fp32 accumulator each); the loads of eight heads are issued together, because a
+// position's B * nh values lie B * nh rows apart and a chain of dependent 2-byte loads is all latency.
+constexpr int HEAD_SUM_THREADS = 128;
+__global__ void __launch_bounds__(HEAD_SUM_THREADS) head_sum_kernel(const __half* __restrict__ w, int B, int nh, int64_t L,
+                                                                    int64_t bh_stride, __half* __restrict__ out) {
   const int64_t l = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (l >= L) return;
   float over_heads = 0.f;
-  for (int h = 0; h < nh; ++h) {
-    float over_batch = 0.f;
-    for (int b = 0; b < B; ++b) over_batch = __fadd_rn(over_batch, __half2float(w[(static_cast<int64_t>(b) * nh + h) * bh_stride + l]));
-    over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch)));
+  for (int h0 = 0; h0 < nh; h0 += 8) {
+    float over_batch[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) over_batch[j] = 0.f;
+    for (int b = 0; b < B; ++b) {
+      __half v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        v[j] = h0 + j < nh ? w[(static_cast<int64_t>(b) * nh + h0 + j) * bh_stride + l] : __float2half_rn(0.f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) over_batch[j] = __fadd_rn(over_batch[j], __half2float(v[j]));
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      if (h0 + j < nh) over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch[j])));
   }
   out[l] = __float2half_rn(over_heads);
 }
@@ -31,7 +46,14 @@ __global__ void __launch_bounds__(256) token_importance_kernel(const __half* __r
   const int64_t l = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (l >= L) return;
   float acc = 0.f;
-  for (int r = 0; r < rows; ++r) acc = __fadd_rn(acc, __half2float(ring[r * stride + l]));
+  for (int r0 = 0; r0 < rows; r0 += 4) {  // four loads in flight, adds in row order
+    __half v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = r0 + j < rows ? ring[(r0 + j) * stride + l] : __float2half_rn(0.f);
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (r0 + j < rows) acc = __fadd_rn(acc, __half2float(v[j]));
+  }
   const int64_t age = L - l;
   const float count = static_cast<float>(age < rows ? age : rows);
   out[l] = h_divf(__float2half_rn(acc), count);
@@ -635,7 +657,8 @@ extern "C" int hqkv_head_sum(const void* w, int B, int nh, int64_t L, int64_t bh
   HQKV_REQUIRE(B > 0 && nh > 0 && L >= 0 && bh_stride >= L, "head_sum: bad sizes");
   if (L == 0) return HQKV_OK;
   HQKV_REQUIRE(w && out, "head_sum: null pointer");
-  head_sum_kernel<<<static_cast<unsigned>(ceil_div(L, 256)), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  head_sum_kernel<<<static_cast<unsigned>(ceil_div(L, HEAD_SUM_THREADS)), HEAD_SUM_THREADS, 0,
+                    static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(w), B, nh, L, bh_stride, static_cast<__half*>(out));
   HQKV_LAUNCH_CHECK("head_sum");
   return HQKV_OK;
