@@ -106,10 +106,16 @@ class GraphedDecodeStep:
     i and norm + q/k/v projections + rotary of layer i+1.  Each such segment is captured once into a CUDA
     graph over static buffers; per layer the host then issues one graph replay plus the cache-facing calls
     (append to the residual window, ``qkv_matmul_hqe_2``, ring update, the flush when it is due), whose
-    shapes change from step to step.  Results are those of ``HqeDecoder.forward`` on a [B, 1, hidden] input."""
+    shapes change from step to step.  Results are those of ``HqeDecoder.forward`` on a [B, 1, hidden] input.
 
-    def __init__(self, model: HqeDecoder, batch: int):
+    ``fused=True`` (default) also shortens the dense parts themselves: the q / k / v projection weights of a layer
+    are moved into one matrix (the three ``nn.Linear`` weights become views of it), likewise gate / up, so a
+    single-row step runs two wide GEMVs instead of five narrow ones; RMSNorm is one fused kernel; the rotary
+    embedding is applied to q and k together as x * cos + roll(x, D/2) * (+-sin)."""
+
+    def __init__(self, model: HqeDecoder, batch: int, fused: bool = True):
         cfg, self.model = model.cfg, model
+        self.fused = fused
         p = next(model.parameters())
         dev, dt = p.device, p.dtype
         z = lambda *shape: torch.zeros(*shape, device=dev, dtype=dt)  # noqa: E731
@@ -124,20 +130,63 @@ class GraphedDecodeStep:
         self.ctx = [z(batch, 1, cfg.num_heads * cfg.head_dim) for _ in range(n)]
         self.out = z(batch, 1, cfg.vocab_size or cfg.hidden_size)
         self.pos = torch.zeros(batch, 1, dtype=torch.long, device=dev)
+        self.sin_signed = z(batch, 1, 1, cfg.head_dim)
+        self.wqkv, self.wgu, self.qk_weight = [], [], []
+        if fused:
+            for layer in model.layers:
+                self._fuse(layer)
         self.graphs = []
         self._capture()
 
+    @torch.no_grad()
+    def _fuse(self, layer):
+        """Move q/k/v (and gate/up) weights into one matrix each; the Linear modules keep working on views."""
+        a, m = layer.self_attn, layer.mlp
+        for mods, store in (((a.q_proj, a.k_proj, a.v_proj), self.wqkv), ((m.gate_proj, m.up_proj), self.wgu)):
+            w = torch.cat([x.weight for x in mods], dim=0)
+            at = 0
+            for x in mods:
+                n = x.weight.shape[0]
+                x.weight = nn.Parameter(w[at:at + n], requires_grad=False)
+                at += n
+            store.append(w)
+        if a.q_norm is not None:  # per-head RMSNorm weights of the q heads, then of the k heads
+            self.qk_weight.append(torch.cat((a.q_norm.weight.expand(a.num_heads, -1),
+                                             a.k_norm.weight.expand(a.num_kv_heads, -1)), dim=0).contiguous())
+        else:
+            self.qk_weight.append(None)
+
+    @staticmethod
+    def _norm(x, mod):
+        return nn.functional.rms_norm(x, (x.shape[-1],), mod.weight, mod.eps)
+
     def _pre(self, i):
         layer = self.model.layers[i]
-        q, k, v = layer.self_attn._project(layer.input_layernorm(self.h), (self.cos, self.sin))
-        self.q[i].copy_(q)
-        self.k[i].copy_(k)
-        self.v[i].copy_(v)
+        a = layer.self_attn
+        if not self.fused:
+            q, k, v = a._project(layer.input_layernorm(self.h), (self.cos, self.sin))
+            self.q[i].copy_(q)
+            self.k[i].copy_(k)
+            self.v[i].copy_(v)
+            return
+        B, nh, nkv, D = self.h.shape[0], a.num_heads, a.num_kv_heads, a.head_dim
+        qkv = nn.functional.linear(self._norm(self.h, layer.input_layernorm), self.wqkv[i]).view(B, 1, nh + 2 * nkv, D)
+        qk = qkv[:, :, :nh + nkv]
+        if self.qk_weight[i] is not None:
+            qk = nn.functional.rms_norm(qk, (D,), None, a.q_norm.eps) * self.qk_weight[i]
+        qk = qk * self.cos.unsqueeze(2) + torch.roll(qk, D // 2, -1) * self.sin_signed
+        self.q[i].copy_(qk[:, :, :nh].transpose(1, 2))
+        self.k[i].copy_(qk[:, :, nh:].transpose(1, 2))
+        self.v[i].copy_(qkv[:, :, nh + nkv:].transpose(1, 2))
 
     def _post(self, i):
         layer = self.model.layers[i]
         self.h.add_(layer.self_attn.o_proj(self.ctx[i]))
-        self.h.add_(layer.mlp(layer.post_attention_layernorm(self.h)))
+        if not self.fused:
+            self.h.add_(layer.mlp(layer.post_attention_layernorm(self.h)))
+            return
+        g, u = nn.functional.linear(self._norm(self.h, layer.post_attention_layernorm), self.wgu[i]).chunk(2, dim=-1)
+        self.h.add_(layer.mlp.down_proj(nn.functional.silu(g) * u))
 
     def _segment(self, s):
         n = len(self.model.layers)
@@ -147,12 +196,14 @@ class GraphedDecodeStep:
             cos, sin = rotary_tables(self.pos, m.cfg.head_dim, m.cfg.rope_theta, self.h.dtype)
             self.cos.copy_(cos)
             self.sin.copy_(sin)
+            half = m.cfg.head_dim // 2  # rotate_half(x) = roll(x, D/2) with the first half negated
+            self.sin_signed.copy_(torch.cat((-sin[..., :half], sin[..., half:]), dim=-1).unsqueeze(2))
         else:
             self._post(s - 1)
         if s < n:
             self._pre(s)
         else:
-            y = self.model.norm(self.h)
+            y = self._norm(self.h, self.model.norm) if self.fused else self.model.norm(self.h)
             self.out.copy_(self.model.lm_head(y) if self.model.lm_head is not None else y)
 
     @torch.no_grad()
