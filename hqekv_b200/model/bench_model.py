@@ -12,6 +12,7 @@ numbers measure the runtime, not a model's quality.
 """
 import argparse
 import json
+import os
 import time
 
 import torch
@@ -41,6 +42,9 @@ def main(argv=None):
     ap.add_argument("--strategy", default="high_uniform_group_low_normal_group")
     ap.add_argument("--no-graphs", action="store_true", help="issue the dense parts of a decode step eagerly")
     args = ap.parse_args(argv)
+    # every flush re-allocates every tier a little larger than before: segments that can grow keep the caching
+    # allocator from fragmenting into driver allocations (read when the allocator first runs)
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
     if not torch.cuda.is_available():
         raise SystemExit("bench_model needs a GPU")
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -92,6 +96,7 @@ def main(argv=None):
         "value_without_flush_steps": round(args.batch * len(plain) / (sum(plain) / 1e3), 2) if plain else None,
         "ms_per_step_median": round(sorted(timed)[len(timed) // 2], 3),
         "ms_flush_step_mean": round(sum(m for m, f in zip(timed, timed_flush) if f) / max(1, sum(timed_flush)), 3),
+        "ms_flush_steps": [round(m, 1) for m, f in zip(timed, timed_flush) if f],
         "flush_steps": int(sum(timed_flush)), "steps": len(timed), "warmup": args.warmup,
         "prefill_s": round(prefill_s, 3),
         "config": {"model": args.model, "layers": cfg.num_layers, "batch": args.batch, "context": args.ctx,
