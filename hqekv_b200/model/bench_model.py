@@ -20,6 +20,26 @@ import torch
 from .decoder import LLAMA31_8B, QWEN3_8B, DecoderConfig, GraphedDecodeStep, HqeDecoder, init_like_pretrained
 
 MODELS = {"llama31-8b": LLAMA31_8B, "qwen3-8b": QWEN3_8B}
+# tier mixes handed to the layers from outside instead of the model files' own shares:
+# name -> (shares of the surviving tokens in the 8 / 4 / 2-bit tiers, share of the newly flushed tokens evicted)
+TIER_MIXES = {"cfg1": ((0.20, 0.40, 0.40), 0.10), "cfg2": ((0.25, 0.50, 0.25), 0.0)}
+
+
+def external_counts(schedule, mix):
+    """(shares, K counts, V counts) for the flush that is due: the cached + new tokens split by ``mix`` into the
+    8 / 4 / 2-bit tiers after evicting a share of the NEW blocks (tokens only ever move down, so asking for the
+    same shares of a growing total keeps the tiers at those shares)."""
+    from .attention_hqe import BLOCK
+    from .public_func import make_sum_equal
+    ratios, evict = TIER_MIXES[mix]
+    compress, total, blocks = schedule.lengths()
+    ev = int(round(evict * (compress // BLOCK)))
+    keep = blocks - ev
+    raw = torch.tensor([0] + [round(keep * r) for r in ratios] + [0], dtype=torch.int32, device="cpu")
+    raw = make_sum_equal(raw, keep, start_idx=3)
+    counts = torch.cat((raw, torch.tensor([ev], dtype=torch.int32))) * BLOCK
+    shares = counts.float() / total
+    return shares, counts, counts.clone()
 
 
 def cache_nbytes(caches):
@@ -41,6 +61,9 @@ def main(argv=None):
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--strategy", default="high_uniform_group_low_normal_group")
     ap.add_argument("--no-graphs", action="store_true", help="issue the dense parts of a decode step eagerly")
+    ap.add_argument("--tiers", choices=["model"] + sorted(TIER_MIXES), default="model",
+                    help="model: the shares the reference's model files derive (64 fp16 tokens, 4/2/1-bit, eviction); "
+                         "cfg1 / cfg2: 8/4/2-bit mixes of the benchmark configurations, handed in as auxiliary parameters")
     args = ap.parse_args(argv)
     # every flush re-allocates every tier a little larger than before: segments that can grow keep the caching
     # allocator from fragmenting into driver allocations (read when the allocator first runs)
@@ -66,7 +89,19 @@ def main(argv=None):
     with torch.no_grad():
         torch.cuda.synchronize()
         t0 = time.perf_counter()
-        h, caches = model(x, None, 0)
+        sched = model.layers[0].self_attn.schedule
+
+        def aux_for(n_new):
+            """Counts for the flush this call will trigger (None: none is due, or the layers derive their own)."""
+            if args.tiers == "model" or sched.current_length + n_new < 32:
+                return None
+            sched.append(n_new)
+            try:
+                return external_counts(sched, args.tiers)
+            finally:
+                sched.append(-n_new)
+
+        h, caches = model(x, None, 0, aux_for(args.ctx))
         torch.cuda.synchronize()
         prefill_s = time.perf_counter() - t0
         del x
@@ -79,7 +114,7 @@ def main(argv=None):
         ev[0].record()
         for s in range(total_steps):
             before = model.layers[0].self_attn.history_reserve_length
-            row, caches = step(row, caches, pos)
+            row, caches = step(row, caches, pos, aux_for(1))
             pos += 1
             flushed.append(model.layers[0].self_attn.history_reserve_length != before)
             ev[s + 1].record()
@@ -100,7 +135,7 @@ def main(argv=None):
         "flush_steps": int(sum(timed_flush)), "steps": len(timed), "warmup": args.warmup,
         "prefill_s": round(prefill_s, 3),
         "config": {"model": args.model, "layers": cfg.num_layers, "batch": args.batch, "context": args.ctx,
-                   "strategy": args.strategy,
+                   "strategy": args.strategy, "tiers": args.tiers,
                    "dense_parts": "eager" if args.no_graphs else "cuda graphs", "shares_evict_4_2_1": [cfg.bit_0, cfg.bit_4, cfg.bit_2, cfg.bit_1]},
         "cached_tokens": cached_tokens, "positions": pos,
         "cache_bytes": cache_nbytes(caches), "fp16_cache_bytes": fp16_bytes,

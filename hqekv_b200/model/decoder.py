@@ -86,13 +86,16 @@ class HqeDecoder(nn.Module):
             layer.self_attn.reset()
             layer.self_attn.set_max_length(max_length)
 
-    def forward(self, inputs: torch.Tensor, caches: Optional[List[tuple]] = None, position: int = 0):
+    def forward(self, inputs: torch.Tensor, caches: Optional[List[tuple]] = None, position: int = 0,
+                auxiliary_parameters: Optional[tuple] = None):
+        """``auxiliary_parameters``: (shares, K counts, V counts) to flush with instead of the counts the first
+        layer derives from its configured shares (the reference's layers accept them the same way)."""
         x = self.embed_tokens(inputs) if self.embed_tokens is not None else inputs
         B, S, _ = x.shape
         pos = torch.arange(position, position + S, device=x.device).unsqueeze(0).expand(B, S)
         rope = rotary_tables(pos, self.cfg.head_dim, self.cfg.rope_theta, x.dtype)
         caches = [None] * len(self.layers) if caches is None else list(caches)
-        aux = None  # the first layer derives the tier counts, the others reuse them
+        aux = auxiliary_parameters  # None: the first layer derives the tier counts, the others reuse them
         for i, layer in enumerate(self.layers):
             x, caches[i], aux = layer(x, rope, None, caches[i], aux)
         x = self.norm(x)
@@ -224,11 +227,12 @@ class GraphedDecodeStep:
             self.graphs.append(g)
 
     @torch.no_grad()
-    def __call__(self, inputs: torch.Tensor, caches: List[tuple], position: int):
+    def __call__(self, inputs: torch.Tensor, caches: List[tuple], position: int,
+                 auxiliary_parameters: Optional[tuple] = None):
         (self.ids if self.ids is not None else self.x).copy_(inputs)
         self.pos.fill_(position)
         caches = list(caches)
-        aux = None
+        aux = auxiliary_parameters
         self.graphs[0].replay()
         for i, layer in enumerate(self.model.layers):
             k, v = self.k[i], self.v[i]
