@@ -13,32 +13,43 @@ constexpr int D = 128;
 // ------------------------------------------------------------------------------------------------
 // importance ring
 // ------------------------------------------------------------------------------------------------
-// One thread per position.  The adds run in the reference's order (batch first, rounded to fp16 per head,
-// then heads, one fp32 accumulator each); the loads of eight heads are issued together, because a
-// position's B * nh values lie B * nh rows apart and a chain of dependent 2-byte loads is all latency.
+// 32 positions per CTA, four warps.  The adds run in the reference's order (batch first with one fp32
+// accumulator per head, rounded to fp16; then the heads, one fp32 accumulator), but a position's B * nh
+// values lie a whole row apart, so a single chain of loads is all latency: warp w sums the batch for heads
+// 8w .. 8w+7 of a pass of 32 heads (eight loads in flight per thread, every load a coalesced 64-byte row
+// piece), the per-head results meet in shared memory, and warp 0 adds them in head order.
 constexpr int HEAD_SUM_THREADS = 128;
 __global__ void __launch_bounds__(HEAD_SUM_THREADS) head_sum_kernel(const __half* __restrict__ w, int B, int nh, int64_t L,
                                                                     int64_t bh_stride, __half* __restrict__ out) {
-  const int64_t l = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  if (l >= L) return;
+  __shared__ float per_head[32][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t l = static_cast<int64_t>(blockIdx.x) * 32 + lane;
+  const bool live = l < L;
   float over_heads = 0.f;
-  for (int h0 = 0; h0 < nh; h0 += 8) {
+  for (int h0 = 0; h0 < nh; h0 += 32) {
+    const int hw = h0 + 8 * warp;
     float over_batch[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) over_batch[j] = 0.f;
+#pragma unroll 2
     for (int b = 0; b < B; ++b) {
       __half v[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j)
-        v[j] = h0 + j < nh ? w[(static_cast<int64_t>(b) * nh + h0 + j) * bh_stride + l] : __float2half_rn(0.f);
+        v[j] = live && hw + j < nh ? w[(static_cast<int64_t>(b) * nh + hw + j) * bh_stride + l] : __float2half_rn(0.f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) over_batch[j] = __fadd_rn(over_batch[j], __half2float(v[j]));
     }
 #pragma unroll
-    for (int j = 0; j < 8; ++j)
-      if (h0 + j < nh) over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch[j])));
+    for (int j = 0; j < 8; ++j) per_head[8 * warp + j][lane] = __half2float(__float2half_rn(over_batch[j]));
+    __syncthreads();
+    if (warp == 0) {
+      const int n = nh - h0 < 32 ? nh - h0 : 32;
+      for (int h = 0; h < n; ++h) over_heads = __fadd_rn(over_heads, per_head[h][lane]);
+    }
+    __syncthreads();
   }
-  out[l] = __float2half_rn(over_heads);
+  if (warp == 0 && live) out[l] = __float2half_rn(over_heads);
 }
 
 __global__ void __launch_bounds__(256) token_importance_kernel(const __half* __restrict__ ring, int rows,
@@ -429,10 +440,10 @@ __device__ __forceinline__ __half k_src_value(const BuildArgs& A, int src, int64
   return dequant_2r(code, A.scale[src][gi], A.zero[src][gi]);
 }
 
-__global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant__ BuildArgs A) {
-  const int64_t jg = blockIdx.x;  // destination group
-  const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
-  const int d = threadIdx.x;
+constexpr int BUILD_K_GROUPS = 4;   // destination groups per CTA (a group alone is too little work to pay for a CTA)
+constexpr int BUILD_V_TOKENS = 8;   // destination tokens per warp
+
+__device__ __forceinline__ void build_k_group(const BuildArgs& A, int64_t jg, int bh, int b, int h, int d) {
   const int32_t enc = A.plan[jg * A.group];
   const int src = (enc >> 28) - 1;
   const int64_t pos0 = enc & 0x0FFFFFFF;
@@ -493,12 +504,17 @@ __global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant_
   A.out_zero[row * Gd + jg] = lo;
 }
 
-// V side: one warp per (destination token, batch*head); a lane owns 4 consecutive channels.
-__global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constant__ BuildArgs A) {
-  const int lane = threadIdx.x & 31;
-  const int64_t j = static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5);
-  if (j >= A.n_dst) return;  // whole warp leaves together
+__global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant__ BuildArgs A) {
   const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
+  const int64_t groups = A.n_dst >> A.gshift;
+  for (int i = 0; i < BUILD_K_GROUPS; ++i) {
+    const int64_t jg = static_cast<int64_t>(blockIdx.x) * BUILD_K_GROUPS + i;  // destination group
+    if (jg < groups) build_k_group(A, jg, bh, b, h, threadIdx.x);
+  }
+}
+
+// V side: a warp per destination token of a (batch, head); a lane owns 4 consecutive channels.
+__device__ __forceinline__ void build_v_token(const BuildArgs& A, int64_t j, int bh, int b, int h, int lane) {
   const int32_t enc = A.plan[j];
   const int src = (enc >> 28) - 1;
   const int64_t pos = enc & 0x0FFFFFFF;
@@ -594,6 +610,14 @@ __global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constan
   }
 }
 
+__global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constant__ BuildArgs A) {
+  const int lane = threadIdx.x & 31;
+  const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
+  const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * BUILD_V_TOKENS;
+  for (int i = 0; i < BUILD_V_TOKENS; ++i)
+    if (j0 + i < A.n_dst) build_v_token(A, j0 + i, bh, b, h, lane);  // the whole warp takes the same branch
+}
+
 __global__ void __launch_bounds__(256) gather_columns_kernel(const __half* __restrict__ in, int64_t in_stride,
                                                              const int64_t* __restrict__ ids, int64_t n,
                                                              __half* __restrict__ out, int64_t out_stride) {
@@ -657,7 +681,7 @@ extern "C" int hqkv_head_sum(const void* w, int B, int nh, int64_t L, int64_t bh
   HQKV_REQUIRE(B > 0 && nh > 0 && L >= 0 && bh_stride >= L, "head_sum: bad sizes");
   if (L == 0) return HQKV_OK;
   HQKV_REQUIRE(w && out, "head_sum: null pointer");
-  head_sum_kernel<<<static_cast<unsigned>(ceil_div(L, HEAD_SUM_THREADS)), HEAD_SUM_THREADS, 0,
+  head_sum_kernel<<<static_cast<unsigned>(ceil_div(L, 32)), HEAD_SUM_THREADS, 0,
                     static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(w), B, nh, L, bh_stride, static_cast<__half*>(out));
   HQKV_LAUNCH_CHECK("head_sum");
@@ -771,7 +795,7 @@ extern "C" int hqkv_flush_build_k(const hqkv_flush_src_t* src_host, int B, int H
   if (n_dst == 0) return HQKV_OK;
   HQKV_REQUIRE(n_dst % group == 0, "flush_build_k: n_dst (%lld) is not a multiple of the group %d", (long long)n_dst,
                group);
-  flush_build_k_kernel<<<dim3(static_cast<unsigned>(n_dst / group), B * H), D, 0,
+  flush_build_k_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst / group, BUILD_K_GROUPS)), B * H), D, 0,
                          static_cast<cudaStream_t>(stream)>>>(A);
   HQKV_LAUNCH_CHECK("flush_build_k");
   return HQKV_OK;
@@ -785,7 +809,7 @@ extern "C" int hqkv_flush_build_v(const hqkv_flush_src_t* src_host, int B, int H
                            "flush_build_v");
   if (rc) return rc;
   if (n_dst == 0) return HQKV_OK;
-  flush_build_v_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst, 4)), B * H), 128, 0,
+  flush_build_v_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst, 4 * BUILD_V_TOKENS)), B * H), 128, 0,
                          static_cast<cudaStream_t>(stream)>>>(A);
   HQKV_LAUNCH_CHECK("flush_build_v");
   return HQKV_OK;
