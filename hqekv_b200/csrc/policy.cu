@@ -415,6 +415,7 @@ struct BuildArgs {
   int64_t res_b_stride, res_h_stride;
   int B, H, group, gshift, dst_tier, dst_bits;
   int normal_dst;  // the destination is the 1-bit tier in the Gaussian-codebook codec
+  int per_warp;    // V side: destination tokens per warp
   const int32_t* plan;  // [n_dst]
   int64_t n_dst;
   void* out_data;
@@ -440,8 +441,7 @@ __device__ __forceinline__ __half k_src_value(const BuildArgs& A, int src, int64
   return dequant_2r(code, A.scale[src][gi], A.zero[src][gi]);
 }
 
-constexpr int BUILD_K_GROUPS = 4;   // destination groups per CTA (a group alone is too little work to pay for a CTA)
-constexpr int BUILD_V_TOKENS = 8;   // destination tokens per warp
+constexpr int BUILD_V_TOKENS_MAX = 8;  // destination tokens per warp when the grid would be scheduling-bound
 
 __device__ __forceinline__ void build_k_group(const BuildArgs& A, int64_t jg, int bh, int b, int h, int d) {
   const int32_t enc = A.plan[jg * A.group];
@@ -506,11 +506,7 @@ __device__ __forceinline__ void build_k_group(const BuildArgs& A, int64_t jg, in
 
 __global__ void __launch_bounds__(D) flush_build_k_kernel(const __grid_constant__ BuildArgs A) {
   const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
-  const int64_t groups = A.n_dst >> A.gshift;
-  for (int i = 0; i < BUILD_K_GROUPS; ++i) {
-    const int64_t jg = static_cast<int64_t>(blockIdx.x) * BUILD_K_GROUPS + i;  // destination group
-    if (jg < groups) build_k_group(A, jg, bh, b, h, threadIdx.x);
-  }
+  build_k_group(A, blockIdx.x, bh, b, h, threadIdx.x);  // one destination group per CTA
 }
 
 // V side: a warp per destination token of a (batch, head); a lane owns 4 consecutive channels.
@@ -613,8 +609,8 @@ __device__ __forceinline__ void build_v_token(const BuildArgs& A, int64_t j, int
 __global__ void __launch_bounds__(128) flush_build_v_kernel(const __grid_constant__ BuildArgs A) {
   const int lane = threadIdx.x & 31;
   const int bh = blockIdx.y, b = bh / A.H, h = bh - b * A.H;
-  const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * BUILD_V_TOKENS;
-  for (int i = 0; i < BUILD_V_TOKENS; ++i)
+  const int64_t j0 = (static_cast<int64_t>(blockIdx.x) * 4 + (threadIdx.x >> 5)) * A.per_warp;
+  for (int i = 0; i < A.per_warp; ++i)
     if (j0 + i < A.n_dst) build_v_token(A, j0 + i, bh, b, h, lane);  // the whole warp takes the same branch
 }
 
@@ -795,7 +791,7 @@ extern "C" int hqkv_flush_build_k(const hqkv_flush_src_t* src_host, int B, int H
   if (n_dst == 0) return HQKV_OK;
   HQKV_REQUIRE(n_dst % group == 0, "flush_build_k: n_dst (%lld) is not a multiple of the group %d", (long long)n_dst,
                group);
-  flush_build_k_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst / group, BUILD_K_GROUPS)), B * H), D, 0,
+  flush_build_k_kernel<<<dim3(static_cast<unsigned>(n_dst / group), B * H), D, 0,
                          static_cast<cudaStream_t>(stream)>>>(A);
   HQKV_LAUNCH_CHECK("flush_build_k");
   return HQKV_OK;
@@ -809,7 +805,11 @@ extern "C" int hqkv_flush_build_v(const hqkv_flush_src_t* src_host, int B, int H
                            "flush_build_v");
   if (rc) return rc;
   if (n_dst == 0) return HQKV_OK;
-  flush_build_v_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst, 4 * BUILD_V_TOKENS)), B * H), 128, 0,
+  // a token row is little work for a warp: above ~16k CTAs the launch is bound by CTA scheduling, so warps
+  // take several tokens each; smaller launches keep one token per warp for the parallelism
+  const int64_t ctas = ceil_div(n_dst, 4) * B * H;
+  A.per_warp = static_cast<int>(ctas > 16384 ? (ctas / 16384 < BUILD_V_TOKENS_MAX ? ctas / 16384 + 1 : BUILD_V_TOKENS_MAX) : 1);
+  flush_build_v_kernel<<<dim3(static_cast<unsigned>(ceil_div(n_dst, 4 * A.per_warp)), B * H), 128, 0,
                          static_cast<cudaStream_t>(stream)>>>(A);
   HQKV_LAUNCH_CHECK("flush_build_v");
   return HQKV_OK;
