@@ -13,7 +13,7 @@ LIB_PATH = os.path.join(HERE, "libhqkv.so")
 
 NUM_TIERS = 5
 TIER_BITS = (16, 8, 4, 2, 1)
-WS_COUNTER_BYTES = 4096
+WS_HEADER_BYTES = 12288
 CODEC_UNIFORM, CODEC_NORMAL = 0, 1
 
 
@@ -57,6 +57,13 @@ _SIGNATURES = {
     "hqkv_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "hqkv_unpack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "hqkv_decode_workspace_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
+    "hqkv_decode_workspace_zero_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
+    "hqkv_decode_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
+    "hqkv_decode_logits": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    "hqkv_decode_weighted_sum": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
+                                           C.c_void_p]),
+    "hqkv_decode_attention_masked": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p,
+                                               C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "hqkv_decode_attention": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                         C.c_size_t, C.c_void_p]),
     "hqkv_decode_attention_phases": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
@@ -138,14 +145,22 @@ def require_cuda(*tensors):
             raise RuntimeError("hqekv_b200 operators run on CUDA tensors only (no CPU path)")
 
 
-# ---- per-device scratch for the decode call (counters must start at zero; every call restores them)
+# ---- scratch for the decode call: one buffer per (device, stream).  The library wants it zeroed once (arrival
+#      counters, status word, output accumulators); every call that completes leaves it zero again.  Calls on
+#      different streams get different buffers, so they cannot race on the counters.  A buffer that was handed
+#      out is never released while the process lives: a CUDA graph captured earlier still holds its address.
 _decode_ws = {}
+_decode_ws_retired = []
 
 
-def decode_workspace(device, nbytes):
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+def decode_workspace(device, nbytes, stream=None):
+    if stream is None:
+        stream = stream_ptr(device)
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device(), stream)
     buf = _decode_ws.get(key)
     if buf is None or buf.numel() < nbytes:
+        if buf is not None:
+            _decode_ws_retired.append(buf)
         grow = max(nbytes, 1 << 20)
         buf = torch.zeros(grow, dtype=torch.uint8, device=device)
         _decode_ws[key] = buf

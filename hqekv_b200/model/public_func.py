@@ -115,6 +115,12 @@ class last_attn_weights:
         self.max_length = max_length
 
     def update(self, attn_weights: torch.Tensor):
+        cap = self.max_length if self.weights is None else self.weights.shape[1]
+        if attn_weights.shape[-1] > cap:
+            # the reference fails here too (shape mismatch of the row assignment, model/public_func.py:247-255);
+            # the kernels below write L halfs into a ring row and must never be handed a shorter one
+            raise ValueError(f"attn_weights holds {attn_weights.shape[-1]} positions but the ring is sized for {cap} "
+                             "(call set_max_length with the longest sequence before the first update)")
         require_cuda(attn_weights)
         if self.weights is None:
             self.weights = torch.zeros(self.last_length, self.max_length, dtype=attn_weights.dtype,

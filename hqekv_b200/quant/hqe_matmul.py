@@ -51,9 +51,10 @@ def _launch(desc, q, attn_weights, attn_output, dev):
     need = lib.hqkv_decode_workspace_bytes(desc)
     if need == 0:
         _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), None, 0, None))
-    ws = decode_workspace(dev, need)
+    st = stream_ptr(dev)
+    ws = decode_workspace(dev, need, st)
     rc = lib.hqkv_decode_attention(desc, q.data_ptr(), attn_weights.data_ptr(), attn_output.data_ptr(), ws.data_ptr(),
-                                   ws.numel(), stream_ptr(dev))
+                                   ws.numel(), st)
     if rc:
         _raise_from_status(rc)
 
@@ -64,13 +65,27 @@ def _raise_from_status(rc):
     check(rc)
 
 
-def _not_built(name):
-    def f(*args, **kwargs):
-        raise NotImplementedError(f"{name}: this cache layout variant of the reference is not built in hqekv_b200; "
-                                  "use qkv_matmul_hqe_2")
-    f.__name__ = name
-    return f
+def qkv_matmul_hqe(q: torch.Tensor, past_key_value: Tuple, attention_mask: torch.Tensor, head_dim: int,
+                   quant_strategy: str, block_size: int = 32, group_size: int = 32):
+    """quant/hqe_matmul.py:27-92: the variant whose index scatter / gather happens inside the GEMV kernels
+    (cuda_bmm_forward_qk_group_hq / cuda_bmm_forward_wv_group_hq) instead of between per-tier launches.  The
+    fused decode does exactly that, so this is the same call.  Like the reference it accepts only
+    'high_uniform_group_low_normal_group' (:43-47: uniform-group high tiers, Gaussian-codebook 1-bit tier)
+    and raises ValueError('invalid quant_strategy') otherwise."""
+    if quant_strategy != "high_uniform_group_low_normal_group":
+        raise ValueError("invalid quant_strategy")
+    return qkv_matmul_hqe_2(q, past_key_value, attention_mask, head_dim, quant_strategy, block_size, group_size)
 
 
-qkv_matmul_hqe = _not_built("qkv_matmul_hqe")
-qkv_matmul_hqe_1 = _not_built("qkv_matmul_hqe_1")
+def qkv_matmul_hqe_1(q: torch.Tensor, past_key_value: Tuple, attention_mask: torch.Tensor, head_dim: int,
+                     quant_strategy: str, block_size: int = 32, group_size: int = 32):
+    """quant/hqe_matmul.py:94-147: decode over the SEQUENTIAL layout of quant/hqe_1.py - no index lists, the
+    logical order is tier order (16, 8, 4, 2, 1 bit) then the residual window; the 1-bit tier is always read in
+    the Gaussian-codebook codec (cuda_bmm_forward_qk_group_hq_seq passes std / mean and the centre,
+    quant/matmul.py:436-505).  The same fused kernel with identity index lists; ``quant_strategy`` is not looked
+    at, as in the reference."""
+    if len(past_key_value) != 42:
+        raise ValueError("invalid past_key_value")
+    from .hqe_1 import sequential_index_lists
+    return qkv_matmul_hqe_2(q, sequential_index_lists(past_key_value), attention_mask, head_dim,
+                            "high_uniform_group_low_normal_group", block_size, group_size)

@@ -27,11 +27,13 @@ class CacheConfig:
     layers: int = 1
     fp16_tokens: int = 0  # tokens kept in the 16-bit tier (the reference's models keep 64)
     strategy: str = "uniform_group"   # or 'high_uniform_group_low_normal_group' (1-bit tier = Gaussian codebook)
+    importance: str = "random"        # 'random': softmax of random logits; 'qk': softmax(q.K^T) of 8 random queries over the cache's own K
 
 
 CONFIGS = {
     # single layer, CPU-checkable
-    "cfg0": CacheConfig("cfg0-llama-1layer-4k", 1, 32, 8, 128, 4096, 128, (0.25, 0.50, 0.25), 0.10, 32, True, 1),
+    "cfg0": CacheConfig("cfg0-llama-1layer-4k", 1, 32, 8, 128, 4096, 128, (0.25, 0.50, 0.25), 0.10, 32, True, 1,
+                        importance="qk"),
     # Llama-3.1-8B decode at 32k context (the configuration the headline metric is quoted on)
     "cfg1": CacheConfig("cfg1-llama3.1-8b-32k", 1, 32, 8, 128, 32768, 128, (0.20, 0.40, 0.40), 0.10, 32, False, 32),
     # Qwen3-8B, batch 8, 16k, group 64, no eviction
@@ -89,11 +91,23 @@ def make_kv(cfg: CacheConfig, device, seed: int, heads=None):
     return K, V, q
 
 
-def synthetic_importance(cfg: CacheConfig, device, seed: int, length: int):
-    """Token importance of ``length`` tokens: mean of 8 random softmax rows with the peakedness of real
-    attention, as fp16 (the same on every rank: it depends on the seed only)."""
+def synthetic_importance(cfg: CacheConfig, device, seed: int, length: int, K: torch.Tensor = None):
+    """Token importance of ``length`` tokens as fp16.
+
+    'random' (default): mean of 8 random softmax rows with the peakedness of real attention; it depends on the
+    seed only, so every rank of a head-sharded run ranks identically.
+    'qk' (the single-layer configuration): what the importance ring would hold after 8 decode steps with random
+    queries - softmax(q.K^T / sqrt(d)) over the first ``length`` tokens of ``K`` [B, H, T, D], summed over batch
+    and query heads per step and averaged over the 8 steps."""
     gen = torch.Generator(device=device)
     gen.manual_seed(seed * 7919 + 17)
+    if cfg.importance == "qk":
+        assert K is not None and K.shape[1] == cfg.nh_kv, "the q.K^T importance needs all kv heads of K"
+        rep = cfg.nh_q // cfg.nh_kv
+        q = torch.randn(8, cfg.batch, cfg.nh_kv, rep, cfg.head_dim, generator=gen, device=device).half().float()
+        logits = torch.einsum("sbhrd,bhtd->sbhrt", q, K[:, :, :length].float()) / math.sqrt(cfg.head_dim)
+        rows = torch.softmax(logits, dim=-1).sum(dim=(1, 2, 3))   # [8, length]: one head-summed row per step
+        return rows.sum(0).div_(8).half()
     logits = torch.randn(8, length, generator=gen, device=device) * 2.0
     return torch.softmax(logits, dim=-1).sum(0).div_(8).half()
 
@@ -107,7 +121,7 @@ def build_cache(cfg: CacheConfig, device, seed: int = 0, heads=None, times_range
     K, V, q = make_kv(cfg, device, seed, heads)
     flushed = cfg.context - cfg.residual
     counts = tier_counts(cfg)
-    imp = synthetic_importance(cfg, device, seed, flushed)
+    imp = synthetic_importance(cfg, device, seed, flushed, K)
     ids = get_block_token_idx(cfg.group, flushed // cfg.group, imp)
     cache = (None,) * 39 + (K, V, cfg.context)
     bit_num = torch.tensor(counts, dtype=torch.int32)

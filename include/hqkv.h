@@ -133,13 +133,18 @@ typedef struct {
   hqkv_tier_t tier[HQKV_NUM_TIERS];
 } hqkv_cache_desc_t;
 
-/* Bytes of scratch hqkv_decode_attention needs for this cache (0 on invalid input). */
+/* Bytes of scratch hqkv_decode_attention needs for this cache on the current device (0 on invalid input). */
 size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
+/* Leading part of that scratch (arrival counters, status word, output accumulators) that must be zero before
+ * a call: hqkv_decode_workspace_zero_bytes() <= hqkv_decode_workspace_bytes(); 0 on invalid input. */
+size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cache_host);
 
 /*
  * One decode step of attention over the whole tiered cache: q.K^T for every tier with the
  * packed codes dequantised in registers, softmax in fp32, p.V for every tier, plus the fp16
- * residual window and the fp16 tier, in two kernel launches.  Stands in for qkv_matmul_hqe_2
+ * residual window and the fp16 tier, in ONE kernel launch (a persistent grid: every warp takes a
+ * range of K tiles, waits - bounded - until the K side of its (batch, kv head) pairs is complete, then
+ * takes a range of V tiles).  Stands in for qkv_matmul_hqe_2
  * (quant/hqe_matmul.py:354-451) and everything below it: the layout glue of
  * cuda_bmm_fA_qB_uniform_group (quant/matmul.py:263-299), gemv_forward_cuda_uniform_group and
  * bgemv_kernel_uniform_group_{8,4,2} (quant/csrc/gemv_cuda_uniform.cu:1533-1599, 411-733), the
@@ -148,25 +153,77 @@ size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
  *   q            fp16 [B, nh_q, 1, D]
  *   attn_weights fp16 [B, nh_q, 1, L]   L = sum_t n_k + n_new; normalised probabilities at logical positions
  *   attn_output  fp16 [B, nh_q, 1, D]
- *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Its first
- *                HQKV_WS_COUNTER_BYTES bytes hold arrival counters that must be zero before the
- *                first call; every call leaves them zero again.  Calls that share a workspace
- *                must be ordered on one stream.
+ *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Zero it once after
+ *                allocating it (at least its first hqkv_decode_workspace_zero_bytes() bytes): that part
+ *                holds arrival counters, a status word and the output accumulators, and every call
+ *                that completes leaves it zero again.  Calls that share a workspace must be ordered
+ *                on one stream.
  * The K-side and V-side token counts of a tier may differ only in order, not in total
- * (sum n_k == sum n_v).  The 1-bit tier is read as a uniform tier (code * scale + zero), like the others.
+ * (sum n_k == sum n_v).  A 1-bit tier is read in the codec its `codec` field names.
+ *
+ * Ordering contract for callers that chain kernels with programmatic dependent launch: the kernel
+ * reads the cache tiers (codes, scales, zeros, index lists) BEFORE it waits for the kernels ahead of it
+ * in the stream; q, the residual window and the scratch are read after that wait.  A kernel
+ * that writes a tier must therefore have completed (not merely have triggered its dependents) before
+ * a decode call on the same stream is launched; an ordinary launch always satisfies this.
+ *
+ * All CTAs of the launch must be resident at once (the grid is sized for an otherwise idle GPU: two
+ * CTAs per SM).  If other work keeps SMs occupied for longer than the spin limit (about half a second)
+ * the waiting CTAs give up, record 1 + (batch * H + kv head) in the status word and finish with an
+ * invalid result - no trap, no endless loop; hqkv_decode_status reads that word.
  */
-#define HQKV_WS_COUNTER_BYTES 4096
+#define HQKV_WS_HEADER_BYTES 12288
 int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * The same call restricted to one of its two launches: phases = 1 runs the K pass only (logits and
- * per-CTA softmax statistics into the workspace), 2 the V pass only (needs the workspace a K pass
- * of the same cache left), 3 both.  A measurement aid for timing the two kernels separately; it has
- * no counterpart in the reference.
+ * hqkv_decode_attention with an additive mask on the logits (after the softmax scale, before the softmax):
+ * element (b, head, pos) of the mask is mask[b * mask_b_stride + head * mask_h_stride + pos] (fp16; a stride
+ * of 0 broadcasts; -inf removes a position).  Stands in for ``attn_weights += attention_mask`` of the
+ * no-eviction flavour (quant/quant_matmul_hq.py:101, :164).
+ */
+int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host, const void* q, const void* mask,
+                                 int64_t mask_b_stride, int64_t mask_h_stride, void* attn_weights, void* attn_output,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Status word of a decode workspace: synchronises `stream`, then *status_host = 0 (every call since the
+ * workspace was zeroed met its waits) or 1 + the (batch, kv head) pair whose K side was not complete
+ * in time.  No counterpart in the reference (its kernels do not wait on one another).
+ */
+int hqkv_decode_status(const void* workspace, void* stream, int* status_host);
+
+/*
+ * The same call restricted to one half of the work: phases = 1 runs the K ranges only (logits and
+ * per-CTA softmax statistics into the workspace), 2 the V ranges only (needs the workspace a K-only
+ * call of the same cache left), 3 both.  A K-only call must be followed by a V-only call on the same
+ * workspace before the next full call (the V ranges put the arrival counters back to zero).  Serves
+ * cuda_bmm_forward_qk_group_hq / cuda_bmm_forward_wv_group_hq style callers and the timing of the two
+ * halves; the split itself has no counterpart in the reference.
  */
 int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
                                  void* attn_output, void* workspace, size_t workspace_bytes, int phases, void* stream);
+
+/*
+ * The K half as an operator of its own: out[b, h, 0, pos] = fp16(softmax_scale * q_h . K^_pos) for every cached
+ * token at its logical position, all tiers and the residual window in one launch (pass softmax_scale = 1 for the
+ * raw product).  Stands in for cuda_bmm_forward_qk_group_hq (quant/matmul.py:351-434) =
+ * kvhq_gemv.gemv_forward_cuda_qk_group_hq (quant/csrc/gemv_cuda.h:78-109), and with identity index lists for
+ * the _seq forms (quant/matmul.py:436-505, gemv_cuda.h:111-137).  logits_f16: fp16 [B, nh_q, 1, L].  Workspace as for
+ * hqkv_decode_attention; the call leaves it ready for any other call.
+ */
+int hqkv_decode_logits(const hqkv_cache_desc_t* cache_host, const void* q, void* logits_f16, void* workspace,
+                       size_t workspace_bytes, void* stream);
+
+/*
+ * The V half as an operator of its own: out[b, h, 0, :] = sum_pos w[b, h, 0, pos] * V^_pos over every tier and
+ * the residual window, for caller-supplied weights w (fp16 [B, nh_q, 1, L], indexed by logical position).  Stands
+ * in for cuda_bmm_forward_wv_group_hq (quant/matmul.py:507-579) = kvhq_gemv.gemv_forward_cuda_wv_group_hq
+ * (quant/csrc/gemv_cuda.h:139-170) and the _seq forms (quant/matmul.py:581-649, gemv_cuda.h:172-198).
+ * out: fp16 [B, nh_q, 1, D].
+ */
+int hqkv_decode_weighted_sum(const hqkv_cache_desc_t* cache_host, const void* weights_f16, void* out, void* workspace,
+                             size_t workspace_bytes, void* stream);
 
 /*
  * kv-head sharding over the GPUs of one node (one process per GPU; reference: none - the reference is
@@ -216,17 +273,23 @@ int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int 
  * Who needs it: a host that has given the whole GPU to its own memory pool, a latency-critical loop
  * that may not allocate after start-up (cudaMalloc can synchronise the device and can fail late), or a
  * language binding with no device allocator of its own.  Inputs and outputs are still the caller's; only the scratch of the
- * two kernels comes from a fixed array of HQKV_STATIC_SCRATCH_BYTES inside the library, resident on
+ * decode kernel comes from a fixed array of HQKV_STATIC_SCRATCH_BYTES inside the library, resident on
  * every GPU that loads it for the life of the process.  The call allocates and frees nothing.
  *
  *  - Limit: caches whose hqkv_decode_workspace_bytes() exceeds HQKV_STATIC_SCRATCH_BYTES are refused
  *    with HQKV_E_WORKSPACE (16 MiB covers batch 1 up to ~100k cached tokens with 32 query heads; the
  *    need grows with B * nh_q * L * 4 bytes).
  *  - The first call on each device looks up the array's device address (cudaGetSymbolAddress with
- *    that device current).  Make that first call outside any stream capture.
+ *    that device current).  Make that first call outside any stream capture, and make it at start-up,
+ *    before the host's own pool takes the remaining memory: with CUDA's lazy module loading that call
+ *    may be the one that loads the library's module onto the device, which is when the array itself
+ *    is placed (CUDA_MODULE_LOADING=EAGER moves that to context creation).
  *  - All calls on a device share the one array, which keeps the previous call's contents (the
- *    arrival counters are cleared at the start of every call).  Two calls that overlap on the GPU,
- *    e.g. on different streams, race on it: order them on one stream or with events.
+ *    arrival counters, the status word and the output accumulators are cleared by a stream-ordered
+ *    memset at the start of every call; that memset sits between the previous kernel and this one, so
+ *    this entry point gives up the overlap of consecutive decode kernels that the regular one has).
+ *    Two calls that overlap on the GPU, e.g. on different streams, race on it: order them on one
+ *    stream or with events.
  */
 #define HQKV_STATIC_SCRATCH_BYTES (16u << 20)
 size_t hqkv_decode_static_scratch_bytes(void);
@@ -306,7 +369,8 @@ int hqkv_block_rank(void* importance, const void* range_or_null, int block, int 
  *                                 (source_tier+1)<<28 | position in that source (source_tier -1 = residual)
  *   plan_ids   int64 [5][total]   final idx list of every tier (already re-ranked if anything was evicted)
  *   survivors  int64 [total]      ascending ids of the tokens that are not evicted
- *   counts     int32 [8]          final size of the five tiers, number of survivors, 0, 0
+ *   counts     int32 [8]          final size of the five tiers, number of survivors, 1 if any token was
+ *                                 evicted else 0, 0
  * The caller reads `counts` back (one small copy) to size the new tier tensors.
  */
 int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_t* tier_n_host, int64_t hist, int64_t compress,

@@ -2,6 +2,7 @@
 validation works without a GPU (it runs before any CUDA call), the host-side logic (tuple slot map,
 tier counts, error conventions) behaves like the reference's, and nothing falls back to a CPU path."""
 import ctypes
+import sys
 import os
 import re
 
@@ -152,6 +153,83 @@ def test_reference_import_names(lib):
     assert quant.hqe_2.KV_cache_hqe_2.__module__ == "hqekv_b200.quant.hqe_2"
     assert hqe_matmul.qkv_matmul_hqe_2.__module__ == "hqekv_b200.quant.hqe_matmul"
     assert callable(kvhq_gemv.gemv_forward_cuda_uniform_group)
+
+
+# The project-import statements of the reference's model files, verbatim: model/llama_hqe.py:20-25 (the
+# Llama fork also imports fast_hadamard_transform at :20) and model/qwen3_hqe.py:21-25.
+_LLAMA_HQE_IMPORTS = """
+import fast_hadamard_transform
+from model.public_func import (get_block_token_idx, make_sum_equal, last_attn_weights)
+
+from quant.hqe import KV_cache_hqe
+from quant.hqe_2 import KV_cache_hqe_2
+from quant.hqe_matmul import qkv_matmul_hqe, qkv_matmul_hqe_2
+"""
+_QWEN3_HQE_IMPORTS = """
+from model.public_func import (get_block_token_idx, make_sum_equal, last_attn_weights)
+
+from quant.hqe import KV_cache_hqe
+from quant.hqe_2 import KV_cache_hqe_2
+from quant.hqe_matmul import qkv_matmul_hqe, qkv_matmul_hqe_2
+"""
+# quant/hqe_matmul.py:5-24 of the reference (for a user who keeps that file and swaps only the modules under it)
+_HQE_MATMUL_IMPORTS = """
+from model.public_func import last_attn_weights
+
+from hqe import KV_cache_hqe
+from hqe_1 import KV_cache_hqe_1, KV_cache_reconstruct_hqe
+
+from matmul import (cuda_bmm_fA_qB_uniform_group,
+                    cuda_bmm_forward_qk_group_hq,
+                    cuda_bmm_forward_qk_group_hq_seq,
+                    cuda_bmm_forward_qk_uniform_group_token,
+                    cuda_bmm_forward_wv_group_hq,
+                    cuda_bmm_forward_wv_group_hq_seq,
+                    cuda_bmm_forward_wv_group_outlier_hq,
+                    cuda_bmm_fA_qB_uniform_group_outlier,
+                    cuda_bmm_fA_qB_wv_uniform_group,
+                    cuda_bmm_fA_qB_wv_uniform_group_outlier,
+                    cuda_bmm_fA_qB_normal_group,
+                    cuda_bmm_fA_qB_normal_group_outlier,
+                    cuda_bmm_forward_qk_normal_group_token,
+                    cuda_bmm_fA_qB_wv_normal_group_outlier)
+"""
+
+
+@pytest.mark.parametrize("text", [_LLAMA_HQE_IMPORTS, _QWEN3_HQE_IMPORTS, _HQE_MATMUL_IMPORTS],
+                         ids=["llama_hqe", "qwen3_hqe", "hqe_matmul"])
+def test_reference_files_import_lines_resolve(lib, text):
+    """After install_reference_names() the import statements of the reference's own files run unchanged
+    (fast_hadamard_transform is a third-party package of the reference's environment: an empty stand-in)."""
+    import types
+    import hqekv_b200
+    hqekv_b200.install_reference_names()
+    sys.modules.setdefault("fast_hadamard_transform", types.ModuleType("fast_hadamard_transform"))
+    ns = {}
+    exec(text, ns)
+    for name in ("KV_cache_hqe",):
+        assert ns[name].__module__.startswith("hqekv_b200.")
+    if "KV_cache_hqe_2" in ns:
+        assert ns["KV_cache_hqe_2"].__module__ == "hqekv_b200.quant.hqe_2"
+        assert ns["qkv_matmul_hqe"].__module__ == "hqekv_b200.quant.hqe_matmul"
+    with pytest.raises(NotImplementedError):
+        ns["KV_cache_hqe"]()  # imported by the model files, never called by them
+
+
+def test_importance_ring_refuses_rows_longer_than_its_capacity(lib):
+    """A probability row longer than the ring's rows (or a ring whose max length was never set) must raise before
+    any kernel is launched: the head-sum kernel writes L halfs into a ring row."""
+    from hqekv_b200.model.public_func import last_attn_weights
+    ring = last_attn_weights()
+    w = torch.zeros(1, 4, 1, 64, dtype=torch.float16)
+    with pytest.raises(ValueError, match="ring is sized for 0"):
+        ring.update(w)
+    ring.set_max_length(32)
+    with pytest.raises(ValueError, match="ring is sized for 32"):
+        ring.update(w)
+    ring.set_max_length(64)
+    with pytest.raises(RuntimeError, match="CUDA tensors only"):   # fits: now only the CPU tensor is refused
+        ring.update(w)
 
 
 def test_tier_counts_of_the_configurations(lib):

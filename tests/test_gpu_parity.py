@@ -321,7 +321,7 @@ def test_decode_cfg0_flush_matches_oracle_flush(ops, cuda_device):
     K, V, q = synthetic.make_kv(cfg, cuda_device, 0)
     flushed = cfg.context - cfg.residual
     counts = synthetic.tier_counts(cfg)
-    imp = synthetic.synthetic_importance(cfg, cuda_device, 0, flushed)
+    imp = synthetic.synthetic_importance(cfg, cuda_device, 0, flushed, K)
     imp_np = imp.cpu().numpy().copy()
     ids = ops.pf.get_block_token_idx(cfg.group, flushed // cfg.group, imp)
     ids_np = O.block_rank(cfg.group, flushed // cfg.group, imp_np)
