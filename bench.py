@@ -41,7 +41,9 @@ def parse_args():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "reference-cuda"],
+                    help="reference: the reference's CPU path on the host cores; reference-cuda: the reference's own CUDA "
+                         "kernels (needs baseline/_ref, see baseline/build_ref.py), one GPU")
     ap.add_argument("--workload", default="cfg1")
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
@@ -116,38 +118,218 @@ class ClockSampler:
 
 
 # -------------------------------------------------------------------------------------------------
-# CPU arm: the numpy oracle (a port of the reference's pure-PyTorch dequant + matmul path) on the host
+# CPU arm: the reference's own pure-PyTorch path on the host cores (or its numpy restatement)
 # -------------------------------------------------------------------------------------------------
-def cpu_decode_seconds(cache_host, q_host, group, threads, strategy="uniform_group"):
-    """Seconds for one layer's decode attention on the host: dense dequantisation of every tier
-    (KV_cache_reconstruct_hqe) + fp32 softmax(q K^T) V, kv heads spread over `threads` threads."""
+def cpu_threads():
+    return os.cpu_count() or 1
+
+
+def build_cache_on_host(cfg, seed=0):
+    """One layer's cache of the workload built WITHOUT the CUDA library: seeded K, V, q with the configuration's
+    distributions, ranked and flushed by the numpy oracle.  Returns (cache tuple of numpy arrays, q)."""
+    import numpy as np
+    import torch
+    from hqekv_b200 import configs
+    from oracle import hqkv_oracle as O
+    g = torch.Generator().manual_seed(seed)
+    shape = (cfg.batch, cfg.nh_kv, cfg.context, cfg.head_dim)
+    K = torch.randn(shape, generator=g)
+    V = torch.randn(shape, generator=g)
+    if cfg.k_outliers:
+        for h in range(cfg.nh_kv):
+            K[:, h][:, :, torch.randperm(cfg.head_dim, generator=g)[:4]] *= 10
+    q = torch.randn(cfg.batch, cfg.nh_q, 1, cfg.head_dim, generator=g).half().numpy()
+    K, V = K.half().numpy(), V.half().numpy()
+    flushed = cfg.context - cfg.residual
+    counts = np.array(configs.tier_counts(cfg))
+    imp = torch.softmax(torch.randn(8, flushed, generator=g) * 2.0, dim=-1).sum(0).div_(8).half().numpy()
+    ids = O.block_rank(cfg.group, flushed // cfg.group, imp.copy())
+    cache = (None,) * 39 + (K, V, cfg.context)
+    return O.flush(cache, flushed, 0, ids, counts, counts.copy(), imp, cfg.strategy, None, cfg.group, cfg.group, False), q
+
+
+def cpu_layer_timer(cache_host, q_host, cfg):
+    """Returns (fn, kind, cores): fn() runs ONE layer's decode attention on the host - dense dequantisation of every
+    tier + fp32 softmax(q K^T / sqrt(d)) V, the path the reference offers without its CUDA extension.
+    kind 'reference': the reference's own KV_cache_reconstruct_hqe (quant/hqe_2.py:967-1084), imported unmodified
+    from the staged copy oracle/_ref through oracle/ref_shim.py, + torch fp32 attention, all host threads.
+    kind 'port': the numpy oracle (same arithmetic restated), kv heads spread over the host threads."""
+    import numpy as np
+    import torch
+    from oracle import ref_shim
+    threads = cpu_threads()
+    if ref_shim.available():
+        ref = ref_shim.load_reference()
+        torch.set_num_threads(threads)
+        cache_t = tuple(torch.from_numpy(np.ascontiguousarray(x)) if isinstance(x, np.ndarray) else x for x in cache_host)
+        q_t = torch.from_numpy(q_host)
+        H = cfg.nh_kv
+        rep = cfg.nh_q // H
+
+        def run():
+            K, V = ref.hqe_2.KV_cache_reconstruct_hqe(cache_t, cfg.strategy, cfg.group, cfg.group)
+            qf = q_t.float().view(cfg.batch, H, rep, cfg.head_dim)
+            logits = torch.matmul(qf, K.float().transpose(2, 3)) / (cfg.head_dim ** 0.5)
+            p = torch.softmax(logits, dim=-1)
+            return torch.matmul(p, V.float())
+        return run, "reference", threads
+
     from concurrent.futures import ThreadPoolExecutor
     from oracle import hqkv_oracle as O
-    H = next(x for x in (cache_host[40], cache_host[2], cache_host[8], cache_host[16], cache_host[24], cache_host[32])
-             if x is not None).shape[1]
-    rep = q_host.shape[1] // H
+    H = cfg.nh_kv
+    rep = cfg.nh_q // H
+    workers = min(H, threads)
 
     def head_slice(h):
         out = []
         for i, item in enumerate(cache_host):
-            if item is None or i == 41 or item.ndim < 4:
-                out.append(item)
-            else:
-                out.append(item[:, h:h + 1])
+            out.append(item if (item is None or i == 41 or item.ndim < 4) else item[:, h:h + 1])
         return tuple(out), q_host[:, h * rep:(h + 1) * rep]
 
-    def run(h):
-        c, q = head_slice(h)
-        return O.decode_attention(q, c, None, group, group, dequant="fp16", quant_strategy=strategy)
+    def one(h):
+        c, qq = head_slice(h)
+        return O.decode_attention(qq, c, None, cfg.group, cfg.group, dequant="fp16", quant_strategy=cfg.strategy)
 
-    t0 = time.perf_counter()
-    if threads > 1:
-        with ThreadPoolExecutor(threads) as ex:
-            list(ex.map(run, range(H)))
-    else:
-        for h in range(H):
-            run(h)
-    return time.perf_counter() - t0
+    def run():
+        with ThreadPoolExecutor(workers) as ex:
+            return list(ex.map(one, range(H)))
+    return run, "port", workers
+
+
+def time_cpu_layer(cache_host, q_host, cfg, layers, reps):
+    """cpu_baseline record: one layer timed `reps` times after one warm-up, scaled to the layers of a step."""
+    run, kind, cores = cpu_layer_timer(cache_host, q_host, cfg)
+    run()
+    ts = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        run()
+        ts.append(time.perf_counter() - t0)
+    per_layer = statistics.median(ts)
+    value = cfg.batch / (per_layer * layers)
+    sample = (f"one layer of {cfg.name} (all {cfg.nh_kv} kv heads) timed {reps} times on the host after one warm-up, "
+              f"median {per_layer:.3f} s, scaled x{layers} layers to a full step")
+    return {"value": value, "unit": UNIT, "cores": cores, "kind": kind, "sample": sample,
+            "extrapolated_from_layers": 1, "seconds_per_layer": per_layer}
+
+
+def workload_config(cfg, layers, world, cached_tokens, cache_bytes):
+    return {"workload": cfg.name, "layers": layers, "batch": cfg.batch, "context": cfg.context,
+            "q_heads": cfg.nh_q, "kv_heads": cfg.nh_kv, "head_dim": cfg.head_dim, "group": cfg.group,
+            "residual": cfg.residual, "evicted_frac": cfg.evict, "tier_ratio_8_4_2": list(cfg.ratios),
+            "fp16_tokens": cfg.fp16_tokens, "quant_strategy": cfg.strategy,
+            "parallelism": f"kv-head-shard x{world}" if world > 1 else "single-gpu",
+            "l2": "one step streams layers x cache bytes (>> 126 MB L2); no flush needed",
+            "cached_tokens": cached_tokens, "cache_bytes_per_layer_per_gpu": cache_bytes}
+
+
+def host_cache_stats(cache_host, cfg):
+    """(logical length, algorithmic bytes) of a host cache tuple: the figures the GPU arm reports for its caches."""
+    import numpy as np
+    L = sum(cache_host[s].size for s in (1, 5, 13, 21, 29) if cache_host[s] is not None)
+    L += cache_host[39].shape[2] if cache_host[39] is not None else 0
+    nbytes = sum(x.nbytes for i, x in enumerate(cache_host[:36]) if isinstance(x, np.ndarray) and x.dtype != np.int64)
+    nbytes += sum(cache_host[i].nbytes for i in (39, 40) if cache_host[i] is not None)
+    return L, nbytes
+
+
+def host_cache_stats_of_config(cfg):
+    """(logical length, algorithmic bytes per layer) of a configuration's cache, from its token counts alone."""
+    from hqekv_b200 import configs
+    counts = configs.tier_counts(cfg)
+    L = sum(counts[:5]) + cfg.residual
+    per_head = 0
+    for n, bits in zip(counts[:5], (16, 8, 4, 2, 1)):
+        per_head += 2 * n * 256 if bits == 16 else 2 * n * (16 * bits + 512 // cfg.group)
+    per_head += cfg.residual * 512
+    return L, per_head * cfg.batch * cfg.nh_kv
+
+
+def run_reference_cpu(args, cfg, layers, world):
+    """The reference arm: the reference's CPU path for this workload.  Loads neither the CUDA library nor a GPU."""
+    cache_host, q_host = build_cache_on_host(cfg, seed=0)
+    L, nbytes = host_cache_stats(cache_host, cfg)
+    rec = time_cpu_layer(cache_host, q_host, cfg, layers, max(1, min(args.steps, 5)))
+    step_s = rec["seconds_per_layer"] * layers
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": rec["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(cfg, layers, max(world, args.gpus), L, nbytes // max(world, args.gpus)),
+        "cpu_baseline": rec,
+        "e2e": {"value": rec["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0}))
+
+
+def load_reference_cuda():
+    """The reference's own quant/hqe_matmul.py on top of its own kvhq_gemv extension, from baseline/_ref (built by
+    baseline/build_ref.py; nothing of this package is on that path).  Returns (module, None) or (None, reason)."""
+    import glob
+    import types
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not glob.glob(os.path.join(ref, "quant", "kvhq_gemv*.so")):
+        return None, "baseline/_ref holds no kvhq_gemv extension (python baseline/build_ref.py --reference <checkout>)"
+    sys.modules.setdefault("fast_hadamard_transform", types.ModuleType("fast_hadamard_transform"))  # imported, not used here
+    sys.path[:0] = [ref, os.path.join(ref, "quant")]
+    try:
+        import hqe_matmul as ref_hm
+    except Exception as e:  # a missing dependency of the reference's environment
+        return None, f"the reference modules do not import here: {type(e).__name__}: {e}"
+    return ref_hm, None
+
+
+def run_reference_cuda(args, cfg, layers, config):
+    """Time the reference's unmodified qkv_matmul_hqe_2 (per-tier transposes + kvhq_gemv launches + torch softmax,
+    quant/hqe_matmul.py:354-451) on the same cache tuples this package's flush builds, and compare its outputs with
+    this package's decode of the same tuple."""
+    import torch
+    ref_hm, why = load_reference_cuda()
+    if ref_hm is None:
+        print(json.dumps({"impl": "reference-cuda", "unavailable": why}))
+        return
+    from hqekv_b200 import synthetic
+    from hqekv_b200.quant.hqe_matmul import qkv_matmul_hqe_2
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    caches, qs = [], []
+    for layer in range(layers):
+        cache, q = synthetic.build_cache(cfg, dev, seed=layer)
+        caches.append(cache)
+        qs.append(q)
+    torch.cuda.synchronize()
+
+    def step():
+        return [ref_hm.qkv_matmul_hqe_2(qs[i], caches[i], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
+                for i in range(layers)]
+
+    for _ in range(max(args.warmup, 3)):
+        outs = step()
+    torch.cuda.synchronize()
+    # agreement with this package's decode on the first layer (the reference rounds logits and per-tier partial
+    # outputs to fp16, so it is the looser of the two against an fp32 oracle)
+    w_ref, o_ref = outs[0]
+    w_our, o_our = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
+    torch.cuda.synchronize()
+    rel = float(((o_ref.float() - o_our.float()).abs().amax(-1) / o_our.float().abs().amax(-1)).max())
+    wdiff = float((w_ref.float() - w_our.float()).abs().max())
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    steps = max(args.steps, 20)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms_per_step = e0.elapsed_time(e1) / steps
+    value = cfg.batch / (ms_per_step * 1e-3)
+    print(json.dumps({
+        "impl": "reference-cuda", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": 1, "steps": steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
+        "note": "the reference's own CUDA extension (kvhq_gemv, built for sm_100 from its sources) driven by its own "
+                "quant/hqe_matmul.py:qkv_matmul_hqe_2, eager launches on the default stream, CUDA events around "
+                f"{steps} steps of {layers} layers",
+        "agreement_with_this_package": {"attn_output_max_rel_diff": rel, "attn_weights_max_abs_diff": wdiff}}))
 
 
 def main():
@@ -162,6 +344,18 @@ def main():
                os.path.abspath(__file__)] + sys.argv[1:]
         sys.exit(subprocess.call(cmd))
 
+    from hqekv_b200 import configs
+    cfg = configs.CONFIGS[args.workload]
+    layers = args.layers or cfg.layers
+
+    # ---------------------------------------------------------------------------------------------
+    # reference arm: the reference's CPU path on the host cores; rank 0 alone, no GPU, no CUDA library
+    # ---------------------------------------------------------------------------------------------
+    if args.impl == "reference":
+        if rank == 0:
+            run_reference_cpu(args, cfg, layers, world)
+        return
+
     import numpy as np
     import torch
     from hqekv_b200 import build
@@ -171,44 +365,10 @@ def main():
     from hqekv_b200.quant._cache import build_cache_desc
     from hqekv_b200.quant.hqe_matmul import qkv_matmul_hqe_2
 
-    cfg = synthetic.CONFIGS[args.workload]
-    layers = args.layers or cfg.layers
-    config = {"workload": cfg.name, "layers": layers, "batch": cfg.batch, "context": cfg.context,
-              "q_heads": cfg.nh_q, "kv_heads": cfg.nh_kv, "head_dim": cfg.head_dim, "group": cfg.group,
-              "residual": cfg.residual, "evicted_frac": cfg.evict, "tier_ratio_8_4_2": list(cfg.ratios),
-              "fp16_tokens": cfg.fp16_tokens, "quant_strategy": cfg.strategy,
-              "parallelism": f"kv-head-shard x{world}" if world > 1 else "single-gpu",
-              "l2": "one step streams layers x cache bytes (>> 126 MB L2); no flush needed"}
-
-    # ---------------------------------------------------------------------------------------------
-    # reference arm: CPU only
-    # ---------------------------------------------------------------------------------------------
-    if args.impl == "reference":
-        if rank != 0:
-            return
-        dev = torch.device("cuda:0") if torch.cuda.is_available() else None
-        if dev is None:
-            print(json.dumps({"impl": "reference", "unavailable": "no CUDA device to build the synthetic cache on"}))
-            return
-        threads = min(cfg.nh_kv, os.cpu_count() or 1)
-        cache, q = synthetic.build_cache(cfg, dev, seed=0)
-        cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in cache)
-        q_host = q.cpu().numpy()
-        for _ in range(max(1, min(args.warmup, 1))):
-            cpu_decode_seconds(cache_host, q_host, cfg.group, threads, cfg.strategy)
-        times = [cpu_decode_seconds(cache_host, q_host, cfg.group, threads, cfg.strategy) for _ in range(max(1, min(args.steps, 5)))]
-        per_layer = statistics.median(times)
-        step_s = per_layer * layers
-        value = cfg.batch / step_s
-        sample = (f"one layer of {cfg.name} (all {cfg.nh_kv} kv heads, {synthetic.logical_length(cache)} cached tokens), "
-                  f"median of {len(times)}, scaled x{layers} layers to a full step")
-        print(json.dumps({
-            "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": step_s * 1e3, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": config,
-            "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port", "sample": sample},
-            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "gpu_launches": 0}))
+    if args.impl == "reference-cuda":
+        if rank == 0:
+            L0, nbytes0 = host_cache_stats_of_config(cfg)
+            run_reference_cuda(args, cfg, layers, workload_config(cfg, layers, 1, L0, nbytes0))
         return
 
     # ---------------------------------------------------------------------------------------------
@@ -237,8 +397,7 @@ def main():
     torch.cuda.synchronize()
     L = synthetic.logical_length(caches[0])
     bytes_per_layer = synthetic.cache_bytes(caches[0], nh_q_local)
-    config["cached_tokens"] = L
-    config["cache_bytes_per_layer_per_gpu"] = bytes_per_layer
+    config = workload_config(cfg, layers, world, L, bytes_per_layer)
 
     gathered = [torch.empty(world, cfg.batch, nh_q_local, 1, cfg.head_dim, dtype=torch.float16, device=dev)
                 for _ in range(layers)] if world > 1 else None
@@ -249,6 +408,7 @@ def main():
     # barrier; off: NCCL all-gather per layer, also the fallback when symmetric memory is not available
     # or the result differs from NCCL's on the first layer (checked every run).
     peer = None
+    exchange = None
     if world > 1 and args.peer_gather != "off":
         try:
             from hqekv_b200.sharding import FlaggedPeerGather, PeerGather
@@ -267,7 +427,7 @@ def main():
                 print(f"[bench] peer-store gather unavailable ({type(e).__name__}: {e}); using NCCL all-gather", file=sys.stderr)
             peer = None
     if world > 1:
-        config["exchange"] = (f"peer stores from the decode kernel ({args.peer_gather})" if peer else "nccl all_gather per layer")
+        exchange = (f"peer stores from the decode kernel ({args.peer_gather})" if peer else "nccl all_gather per layer")
 
     def decode_layer(i, q):
         if peer is not None:
@@ -302,7 +462,7 @@ def main():
                 print(f"[bench] CUDA graph capture failed ({type(e).__name__}: {e}); launching eagerly", file=sys.stderr)
             graph = None
             torch.cuda.synchronize()
-    config["launch"] = "cuda_graph" if graph is not None else "eager"
+    launch = "cuda_graph" if graph is not None else "eager"
 
     def run_step():
         if graph is not None:
@@ -476,25 +636,18 @@ def main():
                      "whole_step_GBps": bytes_per_layer * layers / (ms_per_step * 1e-3) / 1e9,
                      "whole_step_frac": bytes_per_layer * layers / (ms_per_step * 1e-3) / 1e9 / peak})
 
-    # ---- CPU baseline on rank 0, N=1: one layer of the same workload through the oracle
+    # ---- CPU baseline on rank 0, N=1: one layer of the same workload through the same host path the reference arm times
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         cache_host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in caches[0])
-        qh = qs[0].cpu().numpy()
-        threads = 1
-        cpu_decode_seconds(cache_host, qh, cfg.group, threads, cfg.strategy)
-        ts = [cpu_decode_seconds(cache_host, qh, cfg.group, threads, cfg.strategy) for _ in range(3)]
-        per_layer = statistics.median(ts)
-        cpu_baseline = {"value": cfg.batch / (per_layer * layers), "unit": UNIT, "cores": threads, "kind": "port",
-                        "sample": f"one layer of {cfg.name} ({L} cached tokens, {cfg.nh_kv} kv heads) through the numpy "
-                                  f"oracle (dense dequantisation + fp32 attention), median of 3, scaled x{layers} layers"}
+        cpu_baseline = time_cpu_layer(cache_host, qs[0].cpu().numpy(), cfg, layers, 3)
 
     if rank == 0:
         print(json.dumps({
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
-            "data": "synthetic", "config": config, "clocks": clocks, "e2e": e2e,
+            "data": "synthetic", "config": config, "launch": launch, "exchange": exchange, "clocks": clocks, "e2e": e2e,
             "gpu_launches": args.steps * layers * (2 if (peer is not None and args.peer_gather == "flagged") else 1),
             "roofline": roofline, "cpu_baseline": cpu_baseline,
             "tokens_per_sec_per_gpu": value / world}), flush=True)

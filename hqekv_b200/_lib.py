@@ -9,7 +9,7 @@ import os
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libhqkv.so")
+LIB_PATH = os.environ.get("HQKV_LIB") or os.path.join(HERE, "libhqkv.so")  # HQKV_LIB: another build of the same library
 
 NUM_TIERS = 5
 TIER_BITS = (16, 8, 4, 2, 1)
@@ -46,6 +46,8 @@ class FlushSrc(C.Structure):
 _SIGNATURES = {
     "hqkv_last_error": (C.c_char_p, []),
     "hqkv_version": (C.c_int, []),
+    "hqkv_checks_enabled": (C.c_int, []),
+    "hqkv_check_failures": (C.c_int, [C.c_int, C.POINTER(C.c_uint)]),
     "hqkv_quantize_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                                      C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     "hqkv_normal1_quantize_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,

@@ -37,17 +37,28 @@ def needs_build():
     return any(os.path.getmtime(d) > built for d in deps)
 
 
-def build(force=False, verbose=False):
-    """Compile every .cu into objects and link the shared library.  Returns its path."""
+CHECKED_LIB_PATH = os.path.join(HERE, "libhqkv_checked.so")
+
+
+def build(force=False, verbose=False, checks=False):
+    """Compile every .cu into objects and link the shared library.  Returns its path.
+    ``checks``: the bounds-check build (-DHQKV_CHECKS) into libhqkv_checked.so; load it with HQKV_LIB=<path>."""
+    if os.environ.get("HQKV_LIB") and not checks:
+        return os.environ["HQKV_LIB"]  # the caller points at a library it built itself
+    if checks:
+        return _compile(CHECKED_LIB_PATH, os.path.join(HERE, "build", "checked"), ["-DHQKV_CHECKS"], verbose)
     if not force and not needs_build():
         return LIB_PATH
-    objdir = os.path.join(HERE, "build")
+    return _compile(LIB_PATH, os.path.join(HERE, "build"), [], verbose)
+
+
+def _compile(lib_path, objdir, extra, verbose):
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
     procs = []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))
-        cmd = [nvcc, *NVCC_FLAGS, "-I", INCLUDE, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *extra, "-I", INCLUDE, "-I", CSRC, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, obj, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -59,13 +70,13 @@ def build(force=False, verbose=False):
         if verbose and out:
             print(out)
         objs.append(obj)
-    link = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-Xcompiler", "-fPIC"]  # static cudart (nvcc default)
+    link = [nvcc, "-shared", "-o", lib_path, *objs, "-Xcompiler", "-fPIC"]  # static cudart (nvcc default)
     r = subprocess.run(link, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}")
-    return LIB_PATH
+    return lib_path
 
 
 if __name__ == "__main__":
-    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv)
+    path = build(force="--force" in sys.argv, verbose="-v" in sys.argv, checks="--checks" in sys.argv)
     print(path)

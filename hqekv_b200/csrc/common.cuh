@@ -26,6 +26,24 @@ int check_cuda(cudaError_t e, const char* what);
 
 #define HQKV_LAUNCH_CHECK(name) HQKV_CUDA((cudaGetLastError()))
 
+// ---- bounds-check build (-DHQKV_CHECKS) --------------------------------------------------------
+// Every index that comes out of a caller-supplied list (logical positions of the decode, token ids of the
+// flush plan) is range-checked before it addresses memory; a violation is counted in a device counter of
+// the translation unit and the access is skipped - no trap.  hqkv_check_failures() reports the sum.  The
+// regular build compiles the checks away.  (The stand-in for compute-sanitizer's memcheck on small cases.)
+#ifdef HQKV_CHECKS
+#define HQKV_CHECKS_ENABLED 1
+#define HQKV_DEFINE_CHECK_COUNTER static __device__ unsigned int g_check_failures = 0u;
+#define HQKV_INDEX_OK(idx, bound) \
+  ((static_cast<unsigned long long>(idx) < static_cast<unsigned long long>(bound)) ? true : (atomicAdd(&g_check_failures, 1u), false))
+#else
+#define HQKV_CHECKS_ENABLED 0
+#define HQKV_DEFINE_CHECK_COUNTER
+#define HQKV_INDEX_OK(idx, bound) true
+#endif
+unsigned decode_check_failures(bool reset);  // decode.cu
+unsigned policy_check_failures(bool reset);  // policy.cu
+
 static inline bool valid_group(int g) { return g == 32 || g == 64 || g == 128; }
 static inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) % a) == 0; }
 static inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }

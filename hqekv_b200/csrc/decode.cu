@@ -29,7 +29,7 @@ namespace hqkv {
 
 constexpr int NWARPS = 8;
 constexpr int NTHREADS = NWARPS * 32;
-constexpr int MAX_BHL = 8;                          // (batch, kv head) pairs one CTA may touch on one side
+constexpr int MAX_BHL = 6;                          // (batch, kv head) pairs one CTA may touch on one side
 constexpr int NUM_ITEM_TIERS = HQKV_NUM_TIERS + 1;  // [5] = fp16 residual window (token-major K and V)
 constexpr int CTAS_PER_SM = 2;
 constexpr int WS_KDONE_OFF = 0, WS_VDONE_OFF = 4096, WS_STATUS_OFF = 8192;  // inside the zeroed workspace header
@@ -43,8 +43,11 @@ struct DecodeParams {
   int phases;     // bit 0: K ranges, bit 1: V ranges
   int kc_max;     // slots per (batch, kv head) in k_part
   int warp_smem;  // bytes of one warp's shared-memory region
+  int cta_smem;   // bytes of the CTA-shared block ahead of the warps' regions
   int wk, wv;     // weight of all tiles of one (batch, kv head) on the K / V side
   int k_first, v_first;  // first tier that has tiles on that side
+  int w_unit;            // weight of the smallest tile (1: all tiles weigh the same)
+  int small;             // 1: every weight product below fits 32 bits (the common case: cheap integer division)
   float scale;
   const __half* q;
   const __half* mask;      // non-null: additive mask on the logits, fp16, element (b, head, pos) at b*mask_bstride + head*mask_hstride + pos
@@ -54,7 +57,7 @@ struct DecodeParams {
   __half* out;
   float* logits;   // [B*nh_q][L]
   float2* k_part;  // [B*H][kc_max][MAX_REP]
-  double* v_acc;   // [B*H][rep][D] output accumulators: zero between calls
+  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K ranges, summed into by the V ranges
   unsigned* kdone;  // [B*H] CTAs whose K ranges of this (batch, kv head) are complete
   unsigned* vdone;  // [B*H] the same for the V ranges
   unsigned* status; // 0, or 1 + (batch, kv head) whose K side did not complete within the spin limit
@@ -70,17 +73,22 @@ struct DecodeParams {
 };
 
 struct CtaShared {
-  float gm[MAX_BHL][MAX_REP], gl[MAX_BHL][MAX_REP];  // global max / sum-exp of the CTA's V-side (batch, kv head) pairs
-  int k_slot[MAX_BHL];    // K side: this CTA's slot in k_part for its pair i
-  int kp_cnt[MAX_BHL];    // V side: CTAs that publish K statistics for pair i
-  int v_cnt[MAX_BHL];     // V side: CTAs that add V partials for pair i
+  float gm[8][MAX_REP], gl[8][MAX_REP];  // global max / sum-exp of the CTA's V-side (batch, kv head) pairs
+  int k_slot[8];          // K side: this CTA's slot in k_part for its pair i
+  int kp_cnt[8];          // V side: CTAs that publish K statistics for pair i
+  int v_cnt[8];           // V side: CTAs that add V partials for pair i
   int wbh[NWARPS];        // (batch, kv head) whose partial output each warp holds at the end (-1: none)
-  unsigned is_last[MAX_BHL];
+  unsigned is_last[8];
   unsigned bar_n;
   unsigned pad_[3];
 };
-constexpr int CTA_SHARED_BYTES = 1024;
-static_assert(sizeof(CtaShared) <= CTA_SHARED_BYTES, "CTA-shared block");
+constexpr int CTA_HEAD_BYTES = 1024;
+static_assert(sizeof(CtaShared) <= CTA_HEAD_BYTES, "CTA-shared block");
+// after it: q of the CTA's K-side (batch, kv head) pairs, MAX_BHL slots of 4 (8) rows of Q_PITCH halfs
+__host__ __device__ constexpr int q_slot_bytes(bool rep8) { return (rep8 ? 8 : 4) * Q_PITCH * 2; }
+__host__ __device__ constexpr int cta_shared_bytes(bool rep8) { return CTA_HEAD_BYTES + MAX_BHL * q_slot_bytes(rep8); }
+// two CTAs per SM: 2 x (dynamic + 1 KB reserved) must fit the 228 KB of an SM
+static_assert(2 * (cta_shared_bytes(false) + NWARPS * ws_bytes(false) + 1024) <= 233472, "two CTAs per SM");
 
 // ------------------------------------------------------------------------------------------------
 // work lists
@@ -96,6 +104,15 @@ template <bool K> __device__ __forceinline__ int t_tiles(const TierDev& T) { ret
 template <bool K> __device__ __forceinline__ int t_w(const TierDev& T) { return K ? T.k_w : T.v_w; }
 template <bool K> __device__ __forceinline__ int t_w0(const TierDev& T) { return K ? T.k_w0 : T.v_w0; }
 
+__device__ __noinline__ long long div_big(long long a, long long b) { return a / b; }  // one copy of the 64-bit division
+__device__ __forceinline__ long long cta_bound(long long total, int c, int n, int small) {
+  if (small) return static_cast<unsigned>(total) * static_cast<unsigned>(c) / static_cast<unsigned>(n);
+  return div_big(total * c, n);
+}
+__device__ __forceinline__ int div_ll(long long a, int b, int small) {
+  return small ? static_cast<int>(static_cast<unsigned>(a) / static_cast<unsigned>(b)) : static_cast<int>(div_big(a, b));
+}
+
 template <bool K>
 __device__ __forceinline__ void cursor_weight(const DecodeParams& P, Cursor& c) {
   const TierDev& T = P.tier[c.tier];
@@ -103,10 +120,10 @@ __device__ __forceinline__ void cursor_weight(const DecodeParams& P, Cursor& c) 
 }
 // first tile whose start weight is >= a
 template <bool K>
-__device__ __forceinline__ Cursor cursor_at(const DecodeParams& P, long long a) {
+__device__ __noinline__ Cursor cursor_at(const DecodeParams& P, long long a) {
   const int W = K ? P.wk : P.wv;
   Cursor c;
-  c.bh = static_cast<int>(a / W);
+  c.bh = div_ll(a, W, P.small);
   const int r = static_cast<int>(a - static_cast<long long>(c.bh) * W);
   c.tier = NUM_ITEM_TIERS;
   c.tile = 0;
@@ -115,7 +132,8 @@ __device__ __forceinline__ Cursor cursor_at(const DecodeParams& P, long long a) 
     const TierDev& T = P.tier[t];
     const int n = t_tiles<K>(T), w = t_w<K>(T), w0 = t_w0<K>(T);
     if (n > 0 && c.tier == NUM_ITEM_TIERS) {
-      const int tile = r <= w0 ? 0 : (r - w0 + w - 1) / w;
+      const int d = r - w0;  // weights are 3 or 4 in practice: no general integer division for those
+      const int tile = d <= 0 ? 0 : (w == 4 ? (d + 3) >> 2 : w == 3 ? (d + 2) / 3 : (d + w - 1) / w);
       if (tile < n) {
         c.tier = t;
         c.tile = tile;
@@ -144,18 +162,17 @@ __device__ __forceinline__ void cursor_next(const DecodeParams& P, Cursor& c) {
   cursor_weight<K>(P, c);
 }
 
-__device__ __forceinline__ long long cta_bound(long long total, int c, int n) { return total * c / n; }
-
 // CTAs whose range [A_c, A_c+1) meets the weights [bh*W, (bh+1)*W) of one (batch, kv head): first and count
-__device__ __forceinline__ void contributors(long long total, int n, int W, int bh, int& first, int& count) {
+__device__ __forceinline__ void contributors(long long total, int n, int W, int bh, int small, int& first, int& count) {
   const long long x = static_cast<long long>(bh) * W, y = x + W;
-  first = static_cast<int>(((x + 1) * n + total - 1) / total) - 1;
-  int last = static_cast<int>((y * n + total - 1) / total) - 1;
+  first = div_ll((x + 1) * n + total - 1, static_cast<int>(total), small) - 1;
+  int last = div_ll(y * n + total - 1, static_cast<int>(total), small) - 1;
   if (last > n - 1) last = n - 1;
   count = last - first + 1;
 }
 
-__device__ __forceinline__ void k_request(const DecodeParams& P, const Cursor& c, unsigned char* wsm) {
+// (not inlined: called from several places, once per tile)
+__device__ __noinline__ void k_request(const DecodeParams& P, const Cursor c, unsigned char* wsm) {
   if (c.tier >= HQKV_NUM_TIERS) return;
   const TierDev& T = P.tier[c.tier];
   const int t0 = c.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
@@ -168,8 +185,9 @@ __device__ __forceinline__ void k_request(const DecodeParams& P, const Cursor& c
   }
 }
 
-__device__ __forceinline__ void v_request(const DecodeParams& P, const Cursor& c, unsigned char* wsm, uint32_t (&pos)[4]) {
-  if (c.tier >= HQKV_NUM_TIERS) return;
+__device__ __noinline__ uint4 v_request(const DecodeParams& P, const Cursor c, unsigned char* wsm) {
+  uint32_t pos[4] = {0u, 0u, 0u, 0u};
+  if (c.tier >= HQKV_NUM_TIERS) return make_uint4(0u, 0u, 0u, 0u);
   const TierDev& T = P.tier[c.tier];
   const int t0 = c.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
   const int ng = D >> P.gv_shift;
@@ -180,6 +198,7 @@ __device__ __forceinline__ void v_request(const DecodeParams& P, const Cursor& c
     case 1: v_tile_request<1>(T, wsm, c.bh, t0, ntok, ng, pos); break;
     default: break;
   }
+  return make_uint4(pos[0], pos[1], pos[2], pos[3]);
 }
 
 // Cross-GPU barrier of one call, run by up to `world` threads of one CTA: thread r tells peer r "my stores
@@ -217,41 +236,44 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
   extern __shared__ __align__(128) unsigned char smem[];
   CtaShared& cs = *reinterpret_cast<CtaShared*>(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  unsigned char* wsm = smem + CTA_SHARED_BYTES + warp * P.warp_smem;
+  unsigned char* wsm = smem + P.cta_smem + warp * P.warp_smem;
   const bool rep8 = P.rep > 4;
   const int rep = P.rep;
 
   // The next kernel of the stream - the next decode call, if it was launched with programmatic stream
   // serialisation - may place its CTAs as soon as CTAs of this grid have finished; it requests its
   // first K tiles and then waits for this grid to complete.
+#ifndef HQKV_X_LD_LATE
   asm volatile("griddepcontrol.launch_dependents;");
+#endif
 
   const int BH = P.B * P.H;
   const int cta = blockIdx.x, ncta = gridDim.x;
   const long long wk_tot = static_cast<long long>(BH) * P.wk, wv_tot = static_cast<long long>(BH) * P.wv;
   const bool do_k = (P.phases & 1) != 0, do_v = (P.phases & 2) != 0;  // a side that is not run may be empty (weight 0)
-  const long long Ak0 = cta_bound(wk_tot, cta, ncta), Ak1 = cta_bound(wk_tot, cta + 1, ncta);
-  const long long Av0 = cta_bound(wv_tot, cta, ncta), Av1 = cta_bound(wv_tot, cta + 1, ncta);
+  const long long Ak0 = cta_bound(wk_tot, cta, ncta, P.small), Ak1 = cta_bound(wk_tot, cta + 1, ncta, P.small);
+  const long long Av0 = cta_bound(wv_tot, cta, ncta, P.small), Av1 = cta_bound(wv_tot, cta + 1, ncta, P.small);
   // (batch, kv head) pairs whose weights meet this CTA's range, K side and V side
-  const int kbh0 = do_k ? static_cast<int>(Ak0 / P.wk) : 0;
-  const int nkb = do_k ? (Ak1 > 0 ? static_cast<int>((Ak1 - 1) / P.wk) : -1) - kbh0 + 1 : 0;
-  const int vbh0 = do_v ? static_cast<int>(Av0 / P.wv) : 0;
-  const int nvb = do_v ? (Av1 > 0 ? static_cast<int>((Av1 - 1) / P.wv) : -1) - vbh0 + 1 : 0;
+  const int kbh0 = do_k ? div_ll(Ak0, P.wk, P.small) : 0;
+  const int nkb = do_k ? (Ak1 > 0 ? div_ll(Ak1 - 1, P.wk, P.small) : -1) - kbh0 + 1 : 0;
+  const int vbh0 = do_v ? div_ll(Av0, P.wv, P.small) : 0;
+  const int nvb = do_v ? (Av1 > 0 ? div_ll(Av1 - 1, P.wv, P.small) : -1) - vbh0 + 1 : 0;
 
-  if (tid < MAX_BHL) {
+  if (tid < 8) {
     int first = 0, count = 0;
-    if (tid < nkb) contributors(wk_tot, ncta, P.wk, kbh0 + tid, first, count);
+    if (tid < nkb) contributors(wk_tot, ncta, P.wk, kbh0 + tid, P.small, first, count);
     cs.k_slot[tid] = cta - first;
     count = 0;
-    if (tid < nvb && !P.probs_in) contributors(wk_tot, ncta, P.wk, vbh0 + tid, first, count);
+    if (tid < nvb && !P.probs_in) contributors(wk_tot, ncta, P.wk, vbh0 + tid, P.small, first, count);
     cs.kp_cnt[tid] = count;
     count = 0;
-    if (tid < nvb) contributors(wv_tot, ncta, P.wv, vbh0 + tid, first, count);
+    if (tid < nvb) contributors(wv_tot, ncta, P.wv, vbh0 + tid, P.small, first, count);
     cs.v_cnt[tid] = count;
   }
   float2* kstat = reinterpret_cast<float2*>(wsm + WS_KSTAT);  // [MAX_BHL][MAX_REP] of this warp
   kstat[lane] = make_float2(-INFINITY, 0.f);
   kstat[lane + 32] = make_float2(-INFINITY, 0.f);
+  if (!do_k) __syncthreads();  // the tables above are read by other warps (with K ranges: after later barriers)
 
   // ---------------------------------------------------------------------------------------------
   // K ranges
@@ -275,15 +297,38 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
     va1 = Av0 + (Av1 - Av0) * (warp + 1) / NWARPS;
     vcur = cursor_at<false>(P, a0);
     vhave = vcur.s < va1;
-    if (!do_k && vhave) v_request(P, vcur, wsm, vpos);
+    if (!do_k && vhave) {
+      const uint4 r = v_request(P, vcur, wsm);
+      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
+    }
   }
   // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
   // the previous decode call of the stream may still be using: wait for the kernels before it.
   asm volatile("griddepcontrol.wait;" ::: "memory");
 
   if (do_k) {
+    // q of this CTA's K-side pairs -> shared memory (rows of heads that do not exist are zero)
+    {
+      const int rows = rep8 ? 8 : 4;
+      __half* qsm = reinterpret_cast<__half*>(smem + CTA_HEAD_BYTES);
+      for (int i = tid; i < nkb * rows * (D / 2); i += NTHREADS) {
+        const int c2 = i & (D / 2 - 1), row = (i >> 6) % rows, slot = (i >> 6) / rows;
+        const int bh = kbh0 + slot, b = bh / P.H, kvh = bh - b * P.H;
+        uint32_t v = 0u;
+        if (row < rep) v = __ldcg(reinterpret_cast<const uint32_t*>(P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + row) * D) + c2);
+        *reinterpret_cast<uint32_t*>(qsm + (slot * rows + row) * Q_PITCH + 2 * c2) = v;
+      }
+      __syncthreads();
+    }
+    // The first CTA of a (batch, kv head) pair's K side clears the pair's output accumulators: the V ranges add
+    // into them only after the K side of the pair is complete, and this CTA is part of it.  (The scratch may have
+    // held another cache's logits there a call ago.)
+    for (int i = 0; i < nkb; ++i)
+      if (cs.k_slot[i] == 0) {
+        double* accum = P.v_acc + static_cast<int64_t>(kbh0 + i) * rep * D;
+        for (int e = tid; e < rep * D; e += NTHREADS) accum[e] = 0.0;
+      }
     KWarpState st;
-    st.qmode = -1;
     st.pm = -INFINITY;
     st.pl = 0.f;
 #pragma unroll
@@ -293,54 +338,53 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
         st.m[i][e] = -INFINITY;
         st.l[i][e] = 0.f;
       }
-    int cur_bh = -1;
+    int cur_bh = have ? cur.bh : -1;
     float2* tmp = reinterpret_cast<float2*>(wsm + WS_K_ZQ);
     while (have) {
-      if (cur.bh != cur_bh) {
-        if (cur_bh >= 0) k_emit_stats(st, kstat + (cur_bh - kbh0) * MAX_REP, tmp, rep);
-        cur_bh = cur.bh;
-        st.qmode = -1;
-      }
       const int b = cur.bh / P.H, kvh = cur.bh - b * P.H;
-      const __half* q_kvh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D;
+      const __half* qs = reinterpret_cast<const __half*>(smem + CTA_HEAD_BYTES) + (cur.bh - kbh0) * (rep8 ? 8 : 4) * Q_PITCH;
       float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * P.L;
       st.mask0 = P.mask ? P.mask + b * P.mask_bstride + static_cast<int64_t>(kvh * rep) * P.mask_hstride : nullptr;
       st.mask_hstride = P.mask_hstride;
       const TierDev& T = P.tier[cur.tier];
       const int t0 = cur.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
       if (cur.tier == HQKV_NUM_TIERS) {
-        k_need_q(st, q_kvh, rep, rep8 ? 2 : 0);
-        k_residual_tile(T, wsm, st, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
+        k_residual_tile(T, wsm, st, qs, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
       } else if (T.bits == 16) {
-        k_need_q(st, q_kvh, rep, rep8 ? 2 : 0);
-        k_f16_span(T, wsm, st, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
+        k_f16_span(T, wsm, st, qs, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
       } else if (T.bits == 8) {
-        k_tile_compute<8>(T, wsm, st, q_kvh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
+        k_tile_compute<8>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
       } else if (T.bits == 4) {
-        k_tile_compute<4>(T, wsm, st, q_kvh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
+        k_tile_compute<4>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
       } else if (T.bits == 2) {
-        k_tile_compute<2>(T, wsm, st, q_kvh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
+        k_tile_compute<2>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
       } else {
-        k_tile_compute<1>(T, wsm, st, q_kvh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
+        k_tile_compute<1>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
       }
       cursor_next<true>(P, cur);
       have = cur.s < a1;
       __syncwarp();  // every lane is done with the tile in shared memory
+      if (!have || cur.bh != cur_bh) {  // the warp leaves this (batch, kv head): its running pairs go to the table
+        k_emit_stats(st, kstat + (cur_bh - kbh0) * MAX_REP, tmp, rep);
+        cur_bh = cur.bh;
+      }
       if (have) k_request(P, cur, wsm);
     }
-    if (cur_bh >= 0) k_emit_stats(st, kstat + (cur_bh - kbh0) * MAX_REP, tmp, rep);
     // the first V tile does not depend on the logits: request it before waiting for the K side
-    if (do_v && vhave) v_request(P, vcur, wsm, vpos);
+    if (do_v && vhave) {
+      const uint4 r = v_request(P, vcur, wsm);
+      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
+    }
 
     // ---- publish: one (max, sum-exp) per head for every (batch, kv head) pair of this CTA's K range
     __syncthreads();
-    if (tid < MAX_BHL * MAX_REP) {
+    if (tid < 8 * MAX_REP) {
       const int i = tid >> 3, head = tid & 7;
       if (i < nkb) {
         float m = -INFINITY, l = 0.f;
 #pragma unroll
         for (int w = 0; w < NWARPS; ++w) {
-          const float2 v = reinterpret_cast<const float2*>(smem + CTA_SHARED_BYTES + w * P.warp_smem + WS_KSTAT)[tid];
+          const float2 v = reinterpret_cast<const float2*>(smem + P.cta_smem + w * P.warp_smem + WS_KSTAT)[tid];
           softmax_merge(m, l, v.x, v.y);
         }
         P.k_part[(static_cast<int64_t>(kbh0 + i) * P.kc_max + cs.k_slot[i]) * MAX_REP + head] = make_float2(m, l);
@@ -350,13 +394,16 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
     __syncthreads();
     if (tid < nkb) atomicAdd(&P.kdone[kbh0 + tid], 1u);
   }
+#ifdef HQKV_X_LD_LATE
+  asm volatile("griddepcontrol.launch_dependents;");
+#endif
   if (!do_v) return;
 
   // ---------------------------------------------------------------------------------------------
   // wait for the K side of this CTA's V-side pairs; fold the published pairs (warp i takes pair i)
   // ---------------------------------------------------------------------------------------------
   if (P.probs_in) {  // weights are given: nothing to wait for, nothing to normalise by
-    if (tid < MAX_BHL * MAX_REP) {
+    if (tid < 8 * MAX_REP) {
       (&cs.gm[0][0])[tid] = 0.f;
       (&cs.gl[0][0])[tid] = 1.f;
     }
@@ -449,7 +496,10 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
     }
     cursor_next<false>(P, vcur);
     vhave = vcur.s < va1;
-    if (vhave) v_request(P, vcur, wsm, vpos);
+    if (vhave) {
+      const uint4 r = v_request(P, vcur, wsm);
+      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
+    }
   }
   if (lane == 0) cs.wbh[warp] = cur_bh;
 
@@ -471,7 +521,7 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
         run = tag;
         v = 0.f;
       }
-      const unsigned char* o = smem + CTA_SHARED_BYTES + w * P.warp_smem;
+      const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
       v += reinterpret_cast<const float*>(o + ws_v_out(rep8))[h * D + ch] +
            reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
     }
@@ -480,7 +530,7 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
   // ---- the last CTA of a (batch, kv head) normalises and writes the output
   __threadfence();
   __syncthreads();
-  if (tid < MAX_BHL) {
+  if (tid < 8) {
     unsigned last = 0u;
     if (tid < nvb) {
       const unsigned prev = atomicAdd(&P.vdone[vbh0 + tid], 1u);
@@ -499,7 +549,6 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
     double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
     for (int e = tid * 2; e < rep * D; e += NTHREADS * 2) {
       const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + e));
-      *reinterpret_cast<double2*>(accum + e) = make_double2(0.0, 0.0);  // ready for the next call
       const float inv = 1.f / cs.gl[i][e >> 7];
       const __half2 o = __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
       const int64_t at = (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + e;
@@ -644,19 +693,17 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.v_scale = static_cast<const __half*>(s.v_scale);
     d.v_zero = static_cast<const __half*>(s.v_zero);
     d.v_idx = s.v_idx;
-    // tiles: about the same number of bytes whatever the width; the weight follows the tokens (32 = 1)
+    // tiles: about the same number of bytes whatever the width
     const int b = d.bits;
     HQKV_REQUIRE(static_cast<int64_t>(s.n_k) * D * b / 8 < (1ll << 31), "decode: tier %d K plane of one head exceeds 2 GiB", t);
     d.k_tile_tokens = (b == 8 || b == 16) ? 64 : 128;
     d.v_tile_tokens = b == 8 ? 64 : b == 16 ? 16 : 128;
     d.k_tiles = static_cast<int>(ceil_div(d.n_k, d.k_tile_tokens));
     d.v_tiles = static_cast<int>(ceil_div(d.n_v, d.v_tile_tokens));
-    d.k_w = d.k_tile_tokens / 32;
-    d.v_w = b == 16 ? 1 : d.v_tile_tokens / 32;
-    d.k_w0 = static_cast<int>(wk);
-    d.v_w0 = static_cast<int>(wv);
-    wk += static_cast<int64_t>(d.k_tiles) * d.k_w;
-    wv += static_cast<int64_t>(d.v_tiles) * d.v_w;
+    // weights: a tile is first of all one load latency and one pass of per-tile work, so a 64-token tile or a tile
+    // of the fp16 tier (read straight from global memory) counts three quarters of a 128-token tile
+    d.k_w = d.k_tile_tokens == 64 ? 3 : 4;
+    d.v_w = (b == 16 || d.v_tile_tokens == 64) ? 3 : 4;
     if (d.k_tiles > 0 && P.k_first < 0) P.k_first = t;
     if (d.v_tiles > 0 && P.v_first < 0) P.v_first = t;
     nk_total += d.n_k;
@@ -676,24 +723,43 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   r.v_data = c->new_v;
   r.k_tile_tokens = r.v_tile_tokens = 16;
   r.k_tiles = r.v_tiles = static_cast<int>(ceil_div(c->n_new, 16));
-  r.k_w = r.v_w = 1;
-  r.k_w0 = static_cast<int>(wk);
-  r.v_w0 = static_cast<int>(wv);
-  wk += r.k_tiles;
-  wv += r.v_tiles;
+  r.k_w = r.v_w = 3;
   if (r.k_tiles > 0 && P.k_first < 0) P.k_first = HQKV_NUM_TIERS;
   if (r.v_tiles > 0 && P.v_first < 0) P.v_first = HQKV_NUM_TIERS;
   const int64_t L = ((sides & 1) ? nk_total : nv_total) + c->n_new;
   HQKV_REQUIRE(L > 0, "decode: the cache is empty");
   HQKV_REQUIRE(L < (1ll << 30), "decode: cache too long");
   P.L = static_cast<int>(L);
+  const bool rep8 = P.rep > 4;
+  const int64_t BH = static_cast<int64_t>(c->B) * c->H;
+  const int ctas_per_sm = rep8 ? 1 : CTAS_PER_SM;
+  {
+    // With no more tiles than warps on the GPU every warp takes at most one tile of a side and what a tile costs
+    // is its chain of latencies, whatever its size: all tiles weigh the same.
+    int64_t tk = 0, tv = 0;
+    for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
+      tk += P.tier[t].k_tiles;
+      tv += P.tier[t].v_tiles;
+    }
+    const int64_t warps = static_cast<int64_t>(ctas_per_sm) * sm_count() * NWARPS;
+    const bool one_wave = (tk > tv ? tk : tv) * BH <= warps;
+    P.w_unit = one_wave ? 1 : 3;
+    for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
+      TierDev& d = P.tier[t];
+      if (one_wave) d.k_w = d.v_w = 1;
+      d.k_w0 = static_cast<int>(wk);
+      d.v_w0 = static_cast<int>(wv);
+      wk += static_cast<int64_t>(d.k_tiles) * d.k_w;
+      wv += static_cast<int64_t>(d.v_tiles) * d.v_w;
+    }
+  }
+  HQKV_REQUIRE(wk < (1ll << 30) && wv < (1ll << 30), "decode: cache too long");
   P.wk = static_cast<int>(wk);
   P.wv = static_cast<int>(wv);
-  const bool rep8 = P.rep > 4;
   P.warp_smem = ws_bytes(rep8);
-  lay.smem_bytes = CTA_SHARED_BYTES + NWARPS * P.warp_smem;
-  lay.ctas_per_sm = rep8 ? 1 : CTAS_PER_SM;
-  const int64_t BH = static_cast<int64_t>(c->B) * c->H;
+  P.cta_smem = cta_shared_bytes(rep8);
+  lay.smem_bytes = P.cta_smem + NWARPS * P.warp_smem;
+  lay.ctas_per_sm = ctas_per_sm;
   const int max_cta = lay.ctas_per_sm * sm_count();
   P.kc_max = static_cast<int>(max_cta / BH) + 3;
   lay.acc_off = HQKV_WS_HEADER_BYTES;
@@ -706,19 +772,25 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   return HQKV_OK;
 }
 
-// CTAs of one launch: every warp gets about one 32-token unit of the longer side at least, every CTA
+// CTAs of one launch: every warp gets about a quarter of a tile of the longer side at least, every CTA
 // meets at most MAX_BHL (batch, kv head) pairs, and all CTAs are resident at once (the wait between the
 // K ranges and the V ranges relies on it).
 static int grid_size(const DecodeParams& P, const Layout& lay) {
   const int64_t BH = static_cast<int64_t>(P.B) * P.H;
   const int64_t w = (P.wk > P.wv ? P.wk : P.wv) * BH;
-  int64_t n = ceil_div(w, NWARPS);
-  const int64_t lo = ceil_div(BH, 4);
+  int64_t n = ceil_div(w, NWARPS * P.w_unit);
+  const int64_t lo = ceil_div(BH, 3);
+#ifdef HQKV_X_GRID_PER_SM
+  const int64_t hi = static_cast<int64_t>(HQKV_X_GRID_PER_SM) * sm_count();
+#else
   const int64_t hi = static_cast<int64_t>(lay.ctas_per_sm) * sm_count();
+#endif
   if (n < lo) n = lo;
   if (n > hi) n = hi;
   return static_cast<int>(n);
 }
+// a CTA's range of n equal parts of BH pairs meets at most BH / n + 3 of them
+static bool pairs_per_cta_ok(const DecodeParams& P, int n) { return (static_cast<int64_t>(P.B) * P.H) / n + 3 <= MAX_BHL; }
 
 }  // namespace hqkv
 
@@ -735,7 +807,7 @@ extern "C" size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cach
   DecodeParams P;
   Layout lay;
   if (build_params(cache_host, P, lay) != HQKV_OK) return 0;
-  return lay.logits_off;
+  return HQKV_WS_HEADER_BYTES;
 }
 
 namespace hqkv {
@@ -838,15 +910,22 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
     HQKV_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
       HQKV_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     CTA_SHARED_BYTES + NWARPS * ws_bytes(true)));
+                                     cta_shared_bytes(true) + NWARPS * ws_bytes(true)));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
   }
   // programmatic stream serialisation: the grid may start while the kernel before it drains, if that
   // kernel allows it (the previous decode call does); everything it does before its
   // griddepcontrol.wait reads only the cache tiers
+  const int n_cta = grid_size(P, lay);
+  {
+    const long long wmax = static_cast<long long>(P.wk > P.wv ? P.wk : P.wv) * P.B * P.H;
+    P.small = (wmax + 1) * (n_cta + 1) < (1ll << 31) ? 1 : 0;
+  }
+  HQKV_REQUIRE(pairs_per_cta_ok(P, n_cta), "decode: B*H = %d is too large for %d query heads per kv head on this GPU", P.B * P.H,
+               P.rep);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid_size(P, lay));
+  cfg.gridDim = dim3(n_cta);
   cfg.blockDim = dim3(NTHREADS);
   cfg.dynamicSmemBytes = lay.smem_bytes;
   cfg.stream = st;
@@ -901,6 +980,16 @@ extern "C" int hqkv_decode_logits(const hqkv_cache_desc_t* cache_host, const voi
 extern "C" int hqkv_decode_weighted_sum(const hqkv_cache_desc_t* cache_host, const void* weights_f16, void* out,
                                         void* workspace, size_t workspace_bytes, void* stream) {
   HQKV_REQUIRE(weights_f16 && aligned(weights_f16, 2), "decode_weighted_sum: null or misaligned weights");
+  {
+    // no K ranges run in this call, so nobody clears the output accumulators: a stream-ordered memset does
+    DecodeParams P;
+    Layout lay;
+    int rc = build_params(cache_host, P, lay, 2);
+    if (rc) return rc;
+    HQKV_REQUIRE(workspace && workspace_bytes >= lay.total, "decode_weighted_sum: workspace too small");
+    HQKV_CUDA(cudaMemsetAsync(static_cast<unsigned char*>(workspace) + lay.acc_off, 0, lay.logits_off - lay.acc_off,
+                              static_cast<cudaStream_t>(stream)));
+  }
   return decode_launch(cache_host, nullptr, nullptr, out, workspace, workspace_bytes, 2, hqkv::PeerArgs(), stream, weights_f16);
 }
 
@@ -910,6 +999,29 @@ extern "C" int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host,
   HQKV_REQUIRE(mask != nullptr, "decode_masked: null mask");
   return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
                        nullptr, mask, mask_b_stride, mask_h_stride);
+}
+
+namespace hqkv {
+unsigned decode_check_failures(bool reset) {
+#if HQKV_CHECKS_ENABLED
+  unsigned v = 0, z = 0;
+  if (cudaMemcpyFromSymbol(&v, g_check_failures, sizeof(v)) != cudaSuccess) return ~0u;
+  if (reset) cudaMemcpyToSymbol(g_check_failures, &z, sizeof(z));
+  return v;
+#else
+  (void)reset;
+  return 0u;
+#endif
+}
+}  // namespace hqkv
+
+extern "C" int hqkv_checks_enabled(void) { return HQKV_CHECKS_ENABLED; }
+
+extern "C" int hqkv_check_failures(int reset, unsigned* count_host) {
+  HQKV_REQUIRE(count_host != nullptr, "check_failures: null pointer");
+  HQKV_CUDA(cudaDeviceSynchronize());
+  *count_host = hqkv::decode_check_failures(reset != 0) + hqkv::policy_check_failures(reset != 0);
+  return HQKV_OK;
 }
 
 extern "C" int hqkv_decode_status(const void* workspace, void* stream, int* status_host) {
@@ -969,9 +1081,9 @@ extern "C" int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host,
   void* scratch = nullptr;
   int rc = static_scratch_address(&scratch);
   if (rc) return rc;
-  // The array keeps whatever the previous call left.  Only the arrival counters, the status word and
-  // the output accumulators have to start at zero; a finished call leaves them zero, an aborted one
-  // might not, so they are cleared every time (a stream-ordered memset, not an allocation).
+  // The array keeps whatever the previous call left.  Only the arrival counters and the status word have
+  // to start at zero; a finished call leaves them zero, an aborted one might not, so they are cleared
+  // every time (a stream-ordered memset, not an allocation).
   HQKV_CUDA(cudaMemsetAsync(scratch, 0, hqkv_decode_workspace_zero_bytes(cache_host), static_cast<cudaStream_t>(stream)));
   return hqkv_decode_attention(cache_host, q, attn_weights, attn_output, scratch, HQKV_STATIC_SCRATCH_BYTES, stream);
 }

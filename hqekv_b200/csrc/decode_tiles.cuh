@@ -16,6 +16,8 @@
 
 namespace hqkv {
 
+HQKV_DEFINE_CHECK_COUNTER
+
 constexpr int D = 128;      // head dim
 constexpr int MAX_REP = 8;  // query heads per kv head (n of the m16n8k16 tile)
 constexpr float LOG2E = 1.4426950408889634f;
@@ -49,6 +51,7 @@ constexpr int WS_K_Z = WS_K_S + 2048;            // 2048: K zero rows
 constexpr int WS_K_ZQ = WS_K_Z + 2048;           // 128: sum_c zero*q per group of the tile and head, float [4][8]
 constexpr int WS_K_END = WS_K_ZQ + 128;          // 12416
 constexpr int WS_KSTAT = WS_K_END;               // 512: (max, sum-exp) per (batch, kv head) slot and head, float2 [8][8]
+constexpr int WS_KPOS = WS_KSTAT + 512;          // 256: logical positions of the 64 tokens of a sub-span, uint32 [64]
 constexpr int WS_V_S = 8192;                     // 1024: V scales of the tile as in memory [token][group]
 constexpr int WS_V_Z = WS_V_S + 1024;            // 1024
 constexpr int WS_V_P = WS_V_Z + 1024;            // 1088: exp(logit - max) of heads 0-3, half [4][136]
@@ -60,7 +63,7 @@ constexpr int WS_V_P_BYTES = 4 * V_PROW * 2;     // 1088
 __host__ __device__ constexpr int ws_v_out(bool rep8) { return WS_V_P + (rep8 ? 2 : 1) * WS_V_P_BYTES; }
 __host__ __device__ constexpr int ws_v_zt(bool rep8) { return ws_v_out(rep8) + (rep8 ? 8 : 4) * D * 4; }
 __host__ __device__ constexpr int ws_bytes(bool rep8) { return ws_v_zt(rep8) + 128; }
-static_assert(WS_KSTAT + 512 <= ws_bytes(false), "K statistics fit the region");
+static_assert(WS_KPOS + 256 <= ws_bytes(false), "K statistics and positions fit the region");
 static_assert(WS_KSTAT >= ws_v_out(false) && WS_KSTAT >= WS_V_P + WS_V_P_BYTES, "K statistics do not overlap a V tile's staged inputs");
 
 // ------------------------------------------------------------------------------------------------
@@ -139,24 +142,15 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* 
 // 16-bit halves of two words -> one half2 register (low half from a)
 __device__ __forceinline__ uint32_t pack_lo16(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }
 
-// B fragments of q for one walk over a tile: rows are channels 16*kt + 2*tig + (0,1 | 8,9), column
-// n = g is a query head of this kv head:
-//   mode 0 / 1: head 4*mode + (g & 3)  (quantised tiles: columns 4-7 repeat 0-3; with at most four query
-//               heads per kv head mode 0 also serves the fp16 tiles, which read columns 0..rep-1)
-//   mode 2:     head g                  (fp16 tiles with eight query heads per kv head)
-// Heads beyond rep read as zero.
-__device__ __forceinline__ void load_qfrag(const __half* q_kvh, int rep, int mode, uint2 (&qf)[8]) {
-  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
-  const int head = mode == 2 ? g : 4 * mode + (g & 3);
-  const __half* qh = q_kvh + head * D + 2 * tig;
-#pragma unroll
-  for (int kt = 0; kt < 8; ++kt) {
-    qf[kt] = make_uint2(0u, 0u);
-    if (head < rep) {
-      qf[kt].x = __ldcg(reinterpret_cast<const uint32_t*>(qh + 16 * kt));
-      qf[kt].y = __ldcg(reinterpret_cast<const uint32_t*>(qh + 16 * kt + 8));
-    }
-  }
+// q of one (batch, kv head) in shared memory: one row of Q_PITCH halfs per query head (rows beyond the heads that
+// exist are zero).  The pitch of 68 words puts the rows of four heads four banks apart, so the B-fragment reads of
+// a warp (head g & 3 or g, channels 16*kt + 2*tig + (0,1 | 8,9)) are free of bank conflicts.
+constexpr int Q_PITCH = D + 8;
+// B fragment of q for the 16-channel step kt: column n = g is the query head of row qrow (set per lane), rows are
+// channels 16*kt + 2*tig + (0,1) in .x and + (8,9) in .y
+__device__ __forceinline__ uint2 q_frag(const __half* qrow_tig, int kt) {
+  return make_uint2(*reinterpret_cast<const uint32_t*>(qrow_tig + 16 * kt),
+                    *reinterpret_cast<const uint32_t*>(qrow_tig + 16 * kt + 8));
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -289,26 +283,28 @@ __device__ __forceinline__ void k_tile_request(const TierDev& T, unsigned char* 
 // zero rows (channels 2*tig and 2*tig+1) at the half of the tile's first group.
 // Gaussian-codebook tier (s_even / s_odd non-null: the std rows at the same halves): a value is
 // std * C * (2 code - 1) + mean, so the term that does not depend on the code is sum_c (mean - C std) q.
-__device__ __forceinline__ void k_tile_zq(float* zq, const uint2 (&qf)[8], const __half* z_even, const __half* z_odd,
+__device__ __forceinline__ void k_tile_zq(float* zq, const __half* qrow_tig, const __half* z_even, const __half* z_odd,
                                           const __half* s_even = nullptr, const __half* s_odd = nullptr) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int gam = g & 3;
   float zacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+#pragma unroll 2
   for (int kt = 0; kt < 8; ++kt) {
     const int o = (16 * kt) * K_SROW + gam;
     const uint32_t a0 = pack_lo16(__half_as_ushort(z_even[o]), __half_as_ushort(z_odd[o]));
     const uint32_t a2 = pack_lo16(__half_as_ushort(z_even[o + 8 * K_SROW]), __half_as_ushort(z_odd[o + 8 * K_SROW]));
-    mma16816(zacc, a0, 0u, a2, 0u, qf[kt].x, qf[kt].y);
+    const uint2 bq = q_frag(qrow_tig, kt);
+    mma16816(zacc, a0, 0u, a2, 0u, bq.x, bq.y);
   }
   if (s_even) {
     float sacc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
+#pragma unroll 2
     for (int kt = 0; kt < 8; ++kt) {
       const int o = (16 * kt) * K_SROW + gam;
       const uint32_t a0 = pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o]));
       const uint32_t a2 = pack_lo16(__half_as_ushort(s_even[o + 8 * K_SROW]), __half_as_ushort(s_odd[o + 8 * K_SROW]));
-      mma16816(sacc, a0, 0u, a2, 0u, qf[kt].x, qf[kt].y);
+      const uint2 bq = q_frag(qrow_tig, kt);
+      mma16816(sacc, a0, 0u, a2, 0u, bq.x, bq.y);
     }
     zacc[0] = fmaf(-HQKV_NORMAL1_CENTER, sacc[0], zacc[0]);
     zacc[1] = fmaf(-HQKV_NORMAL1_CENTER, sacc[1], zacc[1]);
@@ -381,8 +377,6 @@ __device__ __forceinline__ void softmax_push4(float& m, float& l, const float (&
 
 // What a warp carries from tile to tile while it stays on one (batch, kv head) of the K side.
 struct KWarpState {
-  uint2 qf[8];       // B fragments of q, see load_qfrag
-  int qmode;         // which fragments qf holds (-1: none)
   float m[2][2];     // quantised tiles: this lane's running (max, sum-exp), [half of the heads][e] for head
   float l[2][2];     //   4*half + 2*(tig & 1) + e
   float pm, pl;      // fp16 tiles: this lane's running pair for head lane & (rep - 1)
@@ -390,17 +384,10 @@ struct KWarpState {
   int64_t mask_hstride;    // elements between the mask rows of consecutive query heads (0: one row for all heads)
 };
 
-__device__ __forceinline__ void k_need_q(KWarpState& st, const __half* q_kvh, int rep, int mode) {
-  if (st.qmode != mode) {
-    load_qfrag(q_kvh, rep, mode, st.qf);
-    st.qmode = mode;
-  }
-}
-
 // One tile of a quantised tier, already requested: all heads of this kv head.
-// row0: logit row of head 0 of this kv head; q_kvh: q row of the same head.
+// row0: logit row of head 0 of this kv head; qs: q rows of this kv head in shared memory (Q_PITCH halfs each).
 template <int BITS>
-__device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* wsm, KWarpState& st, const __half* q_kvh,
+__device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* wsm, KWarpState& st, const __half* qs,
                                                int rep, int L, int gk_shift, float qk_scale, int tile_t0, int ntok,
                                                float* row0) {
   using TL = KTile<BITS>;
@@ -438,12 +425,13 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
   cp_async_wait<4>();  // the scale / zero rows
   __syncwarp();
   for (int hh = 0; hh < nh; ++hh) {
-    k_need_q(st, q_kvh, rep, hh);
+    // as a B column this lane is n = g: query head 4*hh + (g & 3) (columns 4-7 repeat 0-3)
+    const __half* qrow_tig = qs + (4 * hh + (g & 3)) * Q_PITCH + 2 * tig;
     if (normal)
-      k_tile_zq(zq, st.qf, zrow + (2 * tig) * K_SROW + sh_even, zrow + (2 * tig + 1) * K_SROW + sh_odd,
+      k_tile_zq(zq, qrow_tig, zrow + (2 * tig) * K_SROW + sh_even, zrow + (2 * tig + 1) * K_SROW + sh_odd,
                 srow + (2 * tig) * K_SROW + sh_even, srow + (2 * tig + 1) * K_SROW + sh_odd);
     else
-      k_tile_zq(zq, st.qf, zrow + (2 * tig) * K_SROW + sh_even, zrow + (2 * tig + 1) * K_SROW + sh_odd);
+      k_tile_zq(zq, qrow_tig, zrow + (2 * tig) * K_SROW + sh_even, zrow + (2 * tig + 1) * K_SROW + sh_odd);
 #pragma unroll 1
     for (int j = 0; j < TL::NSUB; ++j) {
       const int sub_t0 = j * K_SPAN;
@@ -461,14 +449,11 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
       const int my_tok = sub_t0 + (BITS == 8 ? 32 * r + 2 * g : BITS == 4 ? 32 * r + 4 * g : BITS == 2 ? 8 * g + 4 * r
                                                                 : 16 * (g & 3) + 4 * (g >> 2) + 8 * r);
       const bool live = my_tok < ntok;
-      uint32_t pos[4] = {0u, 0u, 0u, 0u};
-      if (live) {
-        const int64_t* ip = T.k_idx + tile_t0 + my_tok;
-        pos[0] = ld_pos(ip);
-        pos[1] = ld_pos(ip + 1);
-        pos[2] = ld_pos(ip + (BITS == 8 ? 16 : 2));
-        pos[3] = ld_pos(ip + (BITS == 8 ? 17 : 3));
-      }
+      // the sub-span's logical positions: requested now (one coalesced 8-byte load per token), handed to the
+      // lanes that own the tokens through shared memory after the MMA loop
+      uint32_t pos_a = 0u, pos_b = 0u;
+      if (sub_t0 + lane < ntok) pos_a = ld_pos(T.k_idx + tile_t0 + sub_t0 + lane);
+      if (sub_t0 + 32 + lane < ntok) pos_b = ld_pos(T.k_idx + tile_t0 + sub_t0 + 32 + lane);
       // as a B column this lane is n = g: columns 0-3 carry the scale group of tokens 0-31 of the
       // sub-span, columns 4-7 that of tokens 32-63
       const int gam = ((tile_t0 + sub_t0 + 32 * (g >> 2)) >> gk_shift) - g0;
@@ -478,7 +463,9 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
       float acc[4][4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-#pragma unroll
+      // two 16-channel steps per iteration (short loop body: with one tile per warp every warp runs this code
+      // once, so it is fetched rather than reused)
+#pragma unroll 1
       for (int kk = 0; kk < 4; ++kk) {
         if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
           if (kk == 0) cp_async_wait<3>();
@@ -526,7 +513,7 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
           const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
           const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o + 8 * K_SROW]),
                                                  __half_as_ushort(s_odd[o + 8 * K_SROW])));
-          const uint2 qv = st.qf[2 * kk + k2];
+          const uint2 qv = q_frag(qrow_tig, 2 * kk + k2);
           const __half2 hi0 = __hmul2(u32_as_h2(qv.x), s0);
           const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
           const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
@@ -539,6 +526,22 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
         }
       }
       // Epilogue from registers.
+      uint32_t pos[4];
+      {
+        uint32_t* kpos = reinterpret_cast<uint32_t*>(wsm + WS_KPOS);
+        __syncwarp();  // the previous sub-span's readers are done
+        kpos[lane] = pos_a;
+        kpos[lane + 32] = pos_b;
+        __syncwarp();
+        const int o = my_tok - sub_t0;
+        if constexpr (BITS == 8) {
+          const uint2 p01 = *reinterpret_cast<const uint2*>(kpos + o), p23 = *reinterpret_cast<const uint2*>(kpos + o + 16);
+          pos[0] = p01.x, pos[1] = p01.y, pos[2] = p23.x, pos[3] = p23.y;
+        } else {
+          const uint4 p = *reinterpret_cast<const uint4*>(kpos + o);
+          pos[0] = p.x, pos[1] = p.y, pos[2] = p.z, pos[3] = p.w;
+        }
+      }
       float val[4][2];
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -570,11 +573,12 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
         if (st.mask0 != nullptr && on) {
           const __half* mrow = st.mask0 + head * st.mask_hstride;
 #pragma unroll
-          for (int i = 0; i < 4; ++i) x[i] += __half2float(mrow[pos[i]]);
+          for (int i = 0; i < 4; ++i)
+            if (HQKV_INDEX_OK(pos[i], L)) x[i] += __half2float(mrow[pos[i]]);
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if (on) row[pos[i]] = x[i];
+          if (on && HQKV_INDEX_OK(pos[i], L)) row[pos[i]] = x[i];
         softmax_push4(st.m[hh][e], st.l[hh][e], x);
       }
     }
@@ -597,6 +601,7 @@ __device__ __forceinline__ void k_write_tile(KWarpState& st, const float* tile, 
   for (int t = lane >> rep_shift; t < ntok; t += tpr) {
     const int64_t pos = idx ? static_cast<int64_t>(ld_pos(idx + t)) : first_pos + t;
     float x = tile[t * K_TROW + h];
+    if (!HQKV_INDEX_OK(pos, L)) continue;
     if (st.mask0 != nullptr) {
       x += __half2float(st.mask0[h * st.mask_hstride + pos]);
       const_cast<float*>(tile)[t * K_TROW + h] = x;  // the second pass reads it back (own element: no race)
@@ -614,9 +619,11 @@ __device__ __forceinline__ void k_write_tile(KWarpState& st, const float* tile, 
 
 // fp16 tier, channel-major rows [D][n]: four tokens per 8-byte slot, no scales; B = q exactly.
 // One span of 64 tokens per call.
-__device__ __forceinline__ void k_f16_span(const TierDev& T, unsigned char* wsm, KWarpState& st, int bh, int rep, int rep_shift,
-                                           int L, float qk_scale, int span_t0, float* row0) {
+__device__ __forceinline__ void k_f16_span(const TierDev& T, unsigned char* wsm, KWarpState& st, const __half* qs, int bh, int rep,
+                                           int rep_shift, int L, float qk_scale, int span_t0, float* row0) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  // B column n = g is query head g (with at most four heads the rows 4-7 do not exist: columns 4-7 repeat 0-3)
+  const __half* qrow_tig = qs + (rep > 4 ? g : (g & 3)) * Q_PITCH + 2 * tig;
   const int n = T.n_k;
   const int64_t nslot = n / K_SLOT;
   const uint2* base = reinterpret_cast<const uint2*>(T.k_data) + static_cast<int64_t>(bh) * D * nslot;
@@ -626,7 +633,7 @@ __device__ __forceinline__ void k_f16_span(const TierDev& T, unsigned char* wsm,
   float acc[K_SLOT][4];
 #pragma unroll
   for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
-#pragma unroll
+#pragma unroll 2
   for (int kt = 0; kt < 8; ++kt) {
     uint2 w[4][2];
 #pragma unroll
@@ -647,8 +654,9 @@ __device__ __forceinline__ void k_f16_span(const TierDev& T, unsigned char* wsm,
         a[2][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x5410);
         a[3][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x7632);
       }
+    const uint2 bq = q_frag(qrow_tig, kt);
 #pragma unroll
-    for (int i = 0; i < K_SLOT; ++i) mma16816(acc[i], a[i][0], a[i][1], a[i][2], a[i][3], st.qf[kt].x, st.qf[kt].y);
+    for (int i = 0; i < K_SLOT; ++i) mma16816(acc[i], a[i][0], a[i][1], a[i][2], a[i][3], bq.x, bq.y);
   }
   float* tile = reinterpret_cast<float*>(wsm + WS_CODES);
   __syncwarp();
@@ -665,9 +673,10 @@ __device__ __forceinline__ void k_f16_span(const TierDev& T, unsigned char* wsm,
 }
 
 // fp16 residual window, token-major [r][D]: A fragments are read directly; one 16-token tile per call.
-__device__ __forceinline__ void k_residual_tile(const TierDev& T, unsigned char* wsm, KWarpState& st, int bh, int rep, int rep_shift,
-                                                int L, float qk_scale, int tile_t0, float* row0) {
+__device__ __forceinline__ void k_residual_tile(const TierDev& T, unsigned char* wsm, KWarpState& st, const __half* qs, int bh,
+                                                int rep, int rep_shift, int L, float qk_scale, int tile_t0, float* row0) {
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const __half* qrow_tig = qs + (rep > 4 ? g : (g & 3)) * Q_PITCH + 2 * tig;
   const int n = T.n_k;
   const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
   const int t[2] = {min(tile_t0 + g, n - 1), min(tile_t0 + g + 8, n - 1)};
@@ -682,7 +691,10 @@ __device__ __forceinline__ void k_residual_tile(const TierDev& T, unsigned char*
       a[kt][2 + r] = *reinterpret_cast<const uint32_t*>(p + 8);
     }
 #pragma unroll
-  for (int kt = 0; kt < 8; ++kt) mma16816(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], st.qf[kt].x, st.qf[kt].y);
+  for (int kt = 0; kt < 8; ++kt) {
+    const uint2 bq = q_frag(qrow_tig, kt);
+    mma16816(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq.x, bq.y);
+  }
   float* tile = reinterpret_cast<float*>(wsm + WS_CODES);
   __syncwarp();
 #pragma unroll
@@ -853,7 +865,7 @@ __device__ __forceinline__ void v_tile_probs(const float* gm, const float* gl, c
 #pragma unroll
       for (int j = 0; j < PER; ++j) {
         const int t = lane + 32 * j;
-        const unsigned short v = (h < rep && t < ntok) ? __ldcg(row + pos[j]) : static_cast<unsigned short>(0);
+        const unsigned short v = (h < rep && t < ntok && HQKV_INDEX_OK(pos[j], L)) ? __ldcg(row + pos[j]) : static_cast<unsigned short>(0);
         prow[hh][t] = __ushort_as_half(v);
       }
     }
@@ -865,7 +877,7 @@ __device__ __forceinline__ void v_tile_probs(const float* gm, const float* gl, c
     const int h = min(h0 + hh, rep - 1);
     const float* row = logit0 + static_cast<int64_t>(h) * L;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) x[hh][j] = lane + 32 * j < ntok ? __ldcg(row + pos[j]) : -INFINITY;
+    for (int j = 0; j < PER; ++j) x[hh][j] = (lane + 32 * j < ntok && HQKV_INDEX_OK(pos[j], L)) ? __ldcg(row + pos[j]) : -INFINITY;
   }
 #pragma unroll
   for (int hh = 0; hh < 4; ++hh) {
@@ -878,7 +890,7 @@ __device__ __forceinline__ void v_tile_probs(const float* gm, const float* gl, c
       const int t = lane + 32 * j;
       const float e = on ? fast_exp2(fmaf(x[hh][j], LOG2E, -mh)) : 0.f;  // exp2(-inf) = 0 beyond the tile
       prow[hh][t] = __float2half_rn(e);
-      if (on && t < ntok) wrow[pos[j]] = __float2half_rn(e * inv);
+      if (on && t < ntok && HQKV_INDEX_OK(pos[j], L)) wrow[pos[j]] = __float2half_rn(e * inv);
     }
   }
 }

@@ -8,6 +8,19 @@
 
 namespace hqkv {
 
+HQKV_DEFINE_CHECK_COUNTER
+unsigned policy_check_failures(bool reset) {
+#if HQKV_CHECKS_ENABLED
+  unsigned v = 0, z = 0;
+  if (cudaMemcpyFromSymbol(&v, g_check_failures, sizeof(v)) != cudaSuccess) return ~0u;
+  if (reset) cudaMemcpyToSymbol(g_check_failures, &z, sizeof(z));
+  return v;
+#else
+  (void)reset;
+  return 0u;
+#endif
+}
+
 constexpr int D = 128;
 
 // ------------------------------------------------------------------------------------------------
@@ -271,7 +284,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
     for (int k = 5; k >= 0; --k)
       if (j < A.cum[k] && j >= (k ? A.cum[k - 1] : 0)) t = k;
     if (t >= 0) {
-      A.tgt[A.sorted_ids[j]] = static_cast<int8_t>(t);
+      if (HQKV_INDEX_OK(A.sorted_ids[j], total)) A.tgt[A.sorted_ids[j]] = static_cast<int8_t>(t);
       if (t == 5) any_evict = 1;
     }
   }
@@ -291,7 +304,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
       if (j0 + u < iters && s < total) enum_slot(A, s, src[u], pos, id[u]);
     }
 #pragma unroll
-    for (int u = 0; u < PLAN_BATCH; ++u) tg[u] = src[u] != -2 ? A.tgt[id[u]] : -1;
+    for (int u = 0; u < PLAN_BATCH; ++u) tg[u] = (src[u] != -2 && HQKV_INDEX_OK(id[u], total)) ? A.tgt[id[u]] : -1;
 #pragma unroll
     for (int u = 0; u < PLAN_BATCH; ++u) {
       if (src[u] == -2) continue;

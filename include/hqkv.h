@@ -38,6 +38,17 @@ const char* hqkv_last_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int hqkv_version(void);
 
+/*
+ * Bounds-check build.  A library compiled with -DHQKV_CHECKS (python -m hqekv_b200.build --checks writes
+ * libhqkv_checked.so) range-checks every index it takes out of a caller-supplied list - the logical positions in
+ * the tiers' index lists, the token ids of the flush plan - before it addresses memory with it; a violation is
+ * counted and the access skipped, nothing traps.  hqkv_checks_enabled() tells which build is loaded;
+ * hqkv_check_failures() synchronises the device and reports (optionally clears) the count, always 0 in the
+ * regular build.  No counterpart in the reference (its kernels check nothing).
+ */
+int hqkv_checks_enabled(void);
+int hqkv_check_failures(int reset, unsigned* count_host);
+
 /* ---------------------------------------------------------------------------------------------
  * Codec
  * ------------------------------------------------------------------------------------------- */
@@ -135,8 +146,8 @@ typedef struct {
 
 /* Bytes of scratch hqkv_decode_attention needs for this cache on the current device (0 on invalid input). */
 size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
-/* Leading part of that scratch (arrival counters, status word, output accumulators) that must be zero before
- * a call: hqkv_decode_workspace_zero_bytes() <= hqkv_decode_workspace_bytes(); 0 on invalid input. */
+/* Leading part of that scratch (arrival counters, status word) that must be zero before a call:
+ * HQKV_WS_HEADER_BYTES whatever the cache; 0 on invalid input. */
 size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cache_host);
 
 /*
@@ -153,11 +164,11 @@ size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cache_host);
  *   q            fp16 [B, nh_q, 1, D]
  *   attn_weights fp16 [B, nh_q, 1, L]   L = sum_t n_k + n_new; normalised probabilities at logical positions
  *   attn_output  fp16 [B, nh_q, 1, D]
- *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Zero it once after
- *                allocating it (at least its first hqkv_decode_workspace_zero_bytes() bytes): that part
- *                holds arrival counters, a status word and the output accumulators, and every call
- *                that completes leaves it zero again.  Calls that share a workspace must be ordered
- *                on one stream.
+ *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Zero its first
+ *                HQKV_WS_HEADER_BYTES bytes once after allocating it: they hold arrival counters and a
+ *                status word, and every call that completes leaves them zero again, so one workspace
+ *                serves calls on caches of any shape.  Calls that share a workspace must be ordered on
+ *                one stream.
  * The K-side and V-side token counts of a tier may differ only in order, not in total
  * (sum n_k == sum n_v).  A 1-bit tier is read in the codec its `codec` field names.
  *
@@ -285,7 +296,7 @@ int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int 
  *    may be the one that loads the library's module onto the device, which is when the array itself
  *    is placed (CUDA_MODULE_LOADING=EAGER moves that to context creation).
  *  - All calls on a device share the one array, which keeps the previous call's contents (the
- *    arrival counters, the status word and the output accumulators are cleared by a stream-ordered
+ *    arrival counters and the status word are cleared by a stream-ordered
  *    memset at the start of every call; that memset sits between the previous kernel and this one, so
  *    this entry point gives up the overlap of consecutive decode kernels that the regular one has).
  *    Two calls that overlap on the GPU, e.g. on different streams, race on it: order them on one

@@ -1,8 +1,12 @@
 """Import the reference's own Python modules on a CPU-only machine.
 
-Used only by ``make_golden.py`` (the script that produced the committed
-``*.npz`` fixtures).  Nothing in the test-suite or the product imports this
-module: the reference tree is not available where the GPU tests run.
+TEST INFRASTRUCTURE ONLY.  Used by ``tests/golden/make_golden.py`` (the script that produced the committed
+``*.npz`` fixtures) and by the CPU arm of ``bench.py`` (``--impl reference``), which times the reference's own
+dense reconstruction when a staged copy of its modules exists (``oracle/_ref``, made by ``oracle/build_ref.py``).
+Nothing in the product package imports this module.
+
+Where the reference modules are read from: the directory named by ``HQEKV_REFERENCE_ROOT``, else the staged copy
+``oracle/_ref`` beside this file; there is no other default.
 
 The reference modules are imported *unmodified*; these stand-ins make them
 executable without a GPU:
@@ -32,7 +36,13 @@ import types
 
 import torch
 
-REFERENCE_ROOT = os.environ.get("HQEKV_REFERENCE_ROOT", "/root/reference")
+STAGED = os.path.join(os.path.dirname(os.path.abspath(__file__)), "_ref")
+REFERENCE_ROOT = os.environ.get("HQEKV_REFERENCE_ROOT") or STAGED
+
+
+def available() -> bool:
+    """True if the reference modules of the hot path can be found."""
+    return os.path.isfile(os.path.join(REFERENCE_ROOT, "quant", "hqe_2.py"))
 
 
 class _CpuLaunch:
@@ -112,8 +122,9 @@ def load_reference_model():
 
 def load_reference():
     """Return a namespace with the reference modules of the hot path."""
-    if not os.path.isdir(REFERENCE_ROOT):
-        raise RuntimeError(f"reference tree not found at {REFERENCE_ROOT}")
+    if not available():
+        raise RuntimeError(f"reference modules not found under {REFERENCE_ROOT}: set HQEKV_REFERENCE_ROOT to a checkout of "
+                           "skywclouds/HqeKV or stage a copy with oracle/build_ref.py")
     for p in (REFERENCE_ROOT, os.path.join(REFERENCE_ROOT, "quant")):
         if p not in sys.path:
             sys.path.insert(0, p)

@@ -5,7 +5,7 @@ Run once, where a checkout of the reference is available (point ``HQEKV_REFERENC
     python tests/golden/make_golden.py [fixture names; none = all]
 
 It imports the reference's own ``quant/pack_unpack.py``, ``model/public_func.py``,
-``quant/hqe_2.py``, ``quant/hqe_matmul.py`` and ``model/llama_hqe.py`` through ``ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
+``quant/hqe_2.py``, ``quant/hqe_matmul.py`` and ``model/llama_hqe.py`` through ``oracle/ref_shim.py`` (CPU, fp16) and stores seeded inputs together with
 the outputs the reference produced as ``*.npz`` files.  The tests read only the ``.npz``
 files; the reference is not needed to run them.
 
@@ -19,8 +19,8 @@ import numpy as np
 import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-sys.path.insert(0, HERE)
-import ref_shim  # noqa: E402
+sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
+from oracle import ref_shim  # noqa: E402
 
 ref = ref_shim.load_reference_model()
 pu, pf, hq, hm = ref.pack_unpack, ref.public_func, ref.hqe_2, ref.hqe_matmul

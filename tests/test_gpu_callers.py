@@ -124,7 +124,7 @@ def test_forward_qk_and_wv_group_hq(ops, cuda_device, sequential):
     w2, o2 = ops.hm.qkv_matmul_hqe_2(q, ref_cache, None, 128, NORMAL, 32, 32)
     assert torch.equal(o1, o2) and torch.equal(w1, w2)
     with pytest.raises(ValueError, match="invalid matrix"):
-        ops.mm.cuda_bmm_forward_qk_group_hq(32, H, q, *([None] * 19), None)
+        ops.mm.cuda_bmm_forward_qk_group_hq(32, H, q, *([None] * 18), None)
 
 
 def test_hybrid_quant_compress_is_the_flush_without_eviction(ops, cuda_device):

@@ -15,12 +15,13 @@ from oracle import hqkv_oracle as O
 pytestmark = pytest.mark.gpu
 
 ATTN_REL_TOL = 2e-3        # max |out - oracle| / max |oracle| per head
-# Probabilities are returned in fp16 (subnormal below 6.1e-5, quantum 2^-24) and the logits come from
-# K dequantised to fp16 for the tensor-core operand: with x10 outlier channels that is ~1e-3 rms on a
-# logit, i.e. on the relative value of a probability.  (The reference rounds the logits themselves to
-# fp16, which is an order of magnitude coarser.)
+# Probabilities are returned in fp16 (subnormal below 6.1e-5, quantum 2^-24).  The kernel carries the logits in
+# fp32 (q * scale enters the tensor pipe exactly, as hi + lo), so a probability differs from the fp32 oracle's by
+# its final rounding to fp16 plus fp32 summation-order noise: within ONE fp16 ulp (2^-10 relative).  (The
+# reference rounds the logits themselves to fp16, which is an order of magnitude coarser.)
 WEIGHT_ABS_TOL = 2.0 ** -24
-WEIGHT_REL_TOL = 1e-2
+WEIGHT_REL_TOL = 2.0 ** -10
+MEASURED = {"attn_rel": 0.0, "weight_rel": 0.0}   # largest errors seen over the whole module, reported at the end
 
 
 def dev_cache(cache_np, device):
@@ -269,9 +270,14 @@ def check_attention(ops, cache_t, q, block, group, what, strategy="uniform_group
     assert per_head.max() <= ATTN_REL_TOL, f"{what}: attention output rel err {per_head.max():.3e} > {ATTN_REL_TOL}"
     w_f = w.float().cpu().numpy()
     werr = np.abs(w_f - ow)
-    assert (werr <= WEIGHT_ABS_TOL + WEIGHT_REL_TOL * ow).all(), \
-        f"{what}: probability error {werr.max():.3e} at p={ow.flat[werr.argmax()]:.3e}"
+    excess = werr - (WEIGHT_ABS_TOL + WEIGHT_REL_TOL * ow)
+    k = int(excess.argmax())
+    assert excess.flat[k] <= 0, \
+        f"{what}: probability {w_f.flat[k]:.6e} vs oracle {ow.flat[k]:.6e} (error {werr.flat[k]:.3e}, allowed " \
+        f"{WEIGHT_ABS_TOL + WEIGHT_REL_TOL * ow.flat[k]:.3e}); largest error {werr.max():.3e} at p={ow.flat[werr.argmax()]:.3e}"
     assert abs(w_f.sum(-1) - 1).max() < 2e-2, f"{what}: probabilities do not sum to 1"
+    MEASURED["attn_rel"] = max(MEASURED["attn_rel"], float(per_head.max()))
+    MEASURED["weight_rel"] = max(MEASURED["weight_rel"], float((np.maximum(werr - WEIGHT_ABS_TOL, 0) / np.maximum(ow, 1e-30)).max()))
     return per_head.max()
 
 
@@ -352,7 +358,48 @@ def test_decode_full_size_properties(ops, cuda_device):
     rel = ((out.float() - ref).abs().amax(-1) / ref.abs().amax(-1)).max().item()
     assert rel <= ATTN_REL_TOL, f"32k decode rel err {rel:.3e}"
     pw = p.view(1, 32, 1, L)
-    assert bool(((w.float() - pw).abs() <= WEIGHT_ABS_TOL + WEIGHT_REL_TOL * pw).all())
+    # (this reference dequantises K to fp16 with two roundings, which moves a logit by ~1e-3: the bound on the
+    # probabilities is the looser one that goes with it; the one-ulp bound is checked against the fp32 oracle)
+    assert bool(((w.float() - pw).abs() <= WEIGHT_ABS_TOL + 1e-2 * pw).all())
+
+
+def test_decode_cfg1_layer_vs_oracle(ops, cuda_device):
+    """One layer of the benchmark workload (Llama-3.1-8B shape, 29 504 cached tokens, 8 kv heads) against the
+    numpy oracle itself - fp32 dequantisation, fp32 attention - at the same 2e-3 / one-ulp bounds."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CONFIGS["cfg1"]
+    cache, q = synthetic.build_cache(cfg, cuda_device, seed=2)
+    check_attention(ops, cache, q, cfg.group, cfg.group, "cfg1 layer vs oracle")
+
+
+def test_decode_cfg2_heads_vs_oracle(ops, cuda_device):
+    """The batch-8 configuration (Qwen3-8B shape: context 16384, group 64, no eviction, 25/50/25 % in 8/4/2 bit, K
+    with outlier channels) on two of its kv heads (eight query heads), against the numpy oracle."""
+    from hqekv_b200 import synthetic
+    c2 = synthetic.CONFIGS["cfg2"]
+    cfg = synthetic.CacheConfig("cfg2-two-heads", c2.batch, 8, 2, 128, c2.context, c2.residual, c2.ratios, c2.evict,
+                                c2.group, c2.k_outliers, 1)
+    cache, q = synthetic.build_cache(cfg, cuda_device, seed=4, times_range=True)
+    assert synthetic.logical_length(cache) == 16384
+    check_attention(ops, cache, q, cfg.group, cfg.group, "cfg2 two heads vs oracle")
+
+
+def test_decode_batch64_vs_oracle(ops, cuda_device):
+    """Batch 64 x 8 kv heads = 512 (batch, kv head) pairs (the largest batch of the kernel sweep), context 1024."""
+    from hqekv_b200 import synthetic
+    cfg = synthetic.CacheConfig("sweep-b64", 64, 32, 8, 128, 1024 + 24, 24, (0.25, 0.5, 0.25), 0.0, 32, True, 1)
+    cache, q = synthetic.build_cache(cfg, cuda_device, seed=6)
+    check_attention(ops, cache, q, 32, 32, "batch 64")
+
+
+def test_decode_status_word_stays_zero(ops, cuda_device):
+    """After all the calls above every wait of the decode kernel was met: the status word of the scratch is 0."""
+    import ctypes
+    from hqekv_b200 import _lib
+    for key, ws in _lib._decode_ws.items():
+        st = ctypes.c_int(-1)
+        _lib.check(_lib.lib.hqkv_decode_status(ws.data_ptr(), None, ctypes.byref(st)))
+        assert st.value == 0, f"workspace {key}: status {st.value}"
 
 
 def test_decode_errors(ops, cuda_device):
@@ -576,3 +623,12 @@ def test_decoder_stack_shares_tier_counts_and_matches_dense_attention(ops, cuda_
     # one more attention call on layer 1's cache against dense attention over its reconstruction
     q = torch.randn(B, 2, 1, 128, generator=gen, device=cuda_device).half()
     check_attention(ops, caches[1], q, 32, 32, "decoder layer 1 cache", cfg.quant_strategy)
+
+
+
+def test_zz_report_measured_maxima():
+    """Not a check of its own: prints the largest errors the decode checks of this module measured (run with -s
+    to see them) and asserts they are within the documented bounds."""
+    print(f"\nmeasured maxima: attention output rel err {MEASURED['attn_rel']:.3e} (bound {ATTN_REL_TOL}), "
+          f"probability rel err beyond the subnormal quantum {MEASURED['weight_rel']:.3e} (bound {WEIGHT_REL_TOL:.3e})")
+    assert MEASURED["attn_rel"] <= ATTN_REL_TOL and MEASURED["weight_rel"] <= WEIGHT_REL_TOL
