@@ -1,22 +1,27 @@
 // Fused mixed-precision decode attention over the tiered KV cache (sm_100a): ONE launch per call.
 //
-// The work of a call is a list of K tiles (logits of 64 / 128 tokens of one tier and (batch, kv head))
-// followed by a list of V tiles (exp, p.V of 64 / 128 tokens), see decode_tiles.cuh.  The grid is
-// persistent: at most as many CTAs as fit on the GPU at once (two per SM), each of eight warps, and
-// every warp owns a contiguous, equally weighted range of both lists, so neighbouring warps and CTAs
-// work on the same (batch, kv head).
+// The work of a (batch, kv head) pair is a list of K tiles (logits of 64 / 128 tokens of one tier) followed by a
+// list of V tiles (exp, p.V of 64 / 128 tokens), see decode_tiles.cuh.  The grid is persistent: at most as many
+// CTAs as fit on the GPU at once (two per SM), each of eight warps.  With fewer pairs than CTAs every pair is
+// shared by a GROUP of m consecutive CTAs, each taking an equal slice of both lists (every warp an eighth of its
+// CTA's slice); with more pairs than CTAs every CTA takes whole pairs, one after the other (a group of one).
 //
-//   K range : logits written to an fp32 scratch row at the tokens' logical positions, a running
-//             (max, sum-exp) per head; the CTA publishes one pair per head and (batch, kv head) and
-//             counts itself in on that pair's arrival counter.
-//   wait    : the first V tile has been requested before the CTA waits (V tiles do not depend on the
-//             logits) - until the K side of its (batch, kv head) pairs is complete, then folds the
-//             published pairs into the global (max, sum).  The wait is bounded: a count that does not
-//             arrive within the spin limit is recorded in the status word and the CTA goes on.
-//   V range : every warp writes the normalised probabilities of its tokens and adds sum_t exp(logit_t
-//             - max) * V_t into its partial output in shared memory; the CTA's warps are added up and
-//             join fp64 accumulators with fire-and-forget reductions; the last CTA of each (batch, kv
-//             head) normalises and writes fp16.
+//   K slice : logits written to an fp32 scratch row at the tokens' logical positions, a running (max, sum-exp)
+//             per head.  A group of one folds its warps' pairs in shared memory.  A larger group publishes one
+//             pair per head and CTA, counts itself in on the pair's arrival counter and
+//   waits   - the first V tile has been requested before (V tiles do not depend on the logits) - until the K
+//             side of its pair is complete, then folds the published pairs into the global (max, sum).  The wait
+//             is bounded: a count that does not arrive within the spin limit is recorded in the status word and
+//             the CTA goes on.
+//   V slice : every warp writes the normalised probabilities of its tokens and adds sum_t exp(logit_t - max) *
+//             V_t into its partial output in shared memory; the CTA's warps are added up.  A group of one
+//             normalises and writes fp16 at once; in a larger group the sums join fp64 accumulators with
+//             fire-and-forget reductions and the last CTA of the pair normalises and writes.
+//
+// Code size is a first-order cost here: with one tile per warp every instruction is executed about once per
+// launch, so a launch walks through its code at instruction-fetch speed.  Hence one (batch, kv head) pair per
+// CTA at a time (no tables, no divisions), request routines written once for all bit widths and not inlined,
+// and step loops that are not unrolled.
 //
 // The launch is chained with programmatic dependent launch: what a CTA needs only from the cache (its
 // first K tile) is requested before it waits for the kernels ahead of it in the stream, and the next
@@ -29,7 +34,6 @@ namespace hqkv {
 
 constexpr int NWARPS = 8;
 constexpr int NTHREADS = NWARPS * 32;
-constexpr int MAX_BHL = 6;                          // (batch, kv head) pairs one CTA may touch on one side
 constexpr int NUM_ITEM_TIERS = HQKV_NUM_TIERS + 1;  // [5] = fp16 residual window (token-major K and V)
 constexpr int CTAS_PER_SM = 2;
 constexpr int WS_KDONE_OFF = 0, WS_VDONE_OFF = 4096, WS_STATUS_OFF = 8192;  // inside the zeroed workspace header
@@ -40,26 +44,29 @@ struct DecodeParams {
   TierDev tier[NUM_ITEM_TIERS];
   int B, H, nh_q, rep, rep_shift, L;
   int gk_shift, gv_shift;
-  int phases;     // bit 0: K ranges, bit 1: V ranges
+  int phases;     // bit 0: K slices, bit 1: V slices
   int kc_max;     // slots per (batch, kv head) in k_part
   int warp_smem;  // bytes of one warp's shared-memory region
   int cta_smem;   // bytes of the CTA-shared block ahead of the warps' regions
   int wk, wv;     // weight of all tiles of one (batch, kv head) on the K / V side
   int k_first, v_first;  // first tier that has tiles on that side
-  int w_unit;            // weight of the smallest tile (1: all tiles weigh the same)
-  int small;             // 1: every weight product below fits 32 bits (the common case: cheap integer division)
+  // grouping: the first g_rem pairs have groups of g_m + 1 CTAs, the others of g_m; g_m == 0: whole pairs per CTA
+  int g_m, g_rem;
+  float g_inv[2];        // 1 / g_m, 1 / (g_m + 1)
+  int kq[2], kr[2];      // wk / m and wk % m for m = g_m, g_m + 1: CTA i of m takes K weights [i*q + min(i, r), ...)
+  int vq[2], vr[2];      // the same for wv
   float scale;
   const __half* q;
   const __half* mask;      // non-null: additive mask on the logits, fp16, element (b, head, pos) at b*mask_bstride + head*mask_hstride + pos
   long long mask_bstride, mask_hstride;
-  const __half* probs_in;  // non-null: the V ranges multiply these caller-supplied weights [B*nh_q][L] instead of exp(logit - max)
+  const __half* probs_in;  // non-null: the V slices multiply these caller-supplied weights [B*nh_q][L] instead of exp(logit - max)
   __half* weights;
   __half* out;
   float* logits;   // [B*nh_q][L]
   float2* k_part;  // [B*H][kc_max][MAX_REP]
-  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K ranges, summed into by the V ranges
-  unsigned* kdone;  // [B*H] CTAs whose K ranges of this (batch, kv head) are complete
-  unsigned* vdone;  // [B*H] the same for the V ranges
+  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K slices, summed into by the V slices
+  unsigned* kdone;  // [B*H] CTAs whose K slice of this (batch, kv head) is complete
+  unsigned* vdone;  // [B*H] the same for the V slices
   unsigned* status; // 0, or 1 + (batch, kv head) whose K side did not complete within the spin limit
   long long spin_limit;
   __half* peer_out[HQKV_MAX_PEERS];  // copies of `out` in other GPUs' memory (kv-head sharding), n_peers used
@@ -73,78 +80,52 @@ struct DecodeParams {
 };
 
 struct CtaShared {
-  float gm[8][MAX_REP], gl[8][MAX_REP];  // global max / sum-exp of the CTA's V-side (batch, kv head) pairs
-  int k_slot[8];          // K side: this CTA's slot in k_part for its pair i
-  int kp_cnt[8];          // V side: CTAs that publish K statistics for pair i
-  int v_cnt[8];           // V side: CTAs that add V partials for pair i
-  int wbh[NWARPS];        // (batch, kv head) whose partial output each warp holds at the end (-1: none)
-  unsigned is_last[8];
+  float gm[MAX_REP], gl[MAX_REP];  // global max / sum-exp of the pair's query heads
+  unsigned is_last;
   unsigned bar_n;
-  unsigned pad_[3];
+  unsigned pad_[2];
 };
-constexpr int CTA_HEAD_BYTES = 1024;
+constexpr int CTA_HEAD_BYTES = 128;
 static_assert(sizeof(CtaShared) <= CTA_HEAD_BYTES, "CTA-shared block");
-// after it: q of the CTA's K-side (batch, kv head) pairs, MAX_BHL slots of 4 (8) rows of Q_PITCH halfs
-__host__ __device__ constexpr int q_slot_bytes(bool rep8) { return (rep8 ? 8 : 4) * Q_PITCH * 2; }
-__host__ __device__ constexpr int cta_shared_bytes(bool rep8) { return CTA_HEAD_BYTES + MAX_BHL * q_slot_bytes(rep8); }
+// after it: q of the CTA's current pair, 4 (8) rows of Q_PITCH halfs
+__host__ __device__ constexpr int cta_shared_bytes(bool rep8) { return CTA_HEAD_BYTES + (rep8 ? 8 : 4) * Q_PITCH * 2; }
 // two CTAs per SM: 2 x (dynamic + 1 KB reserved) must fit the 228 KB of an SM
 static_assert(2 * (cta_shared_bytes(false) + NWARPS * ws_bytes(false) + 1024) <= 233472, "two CTAs per SM");
 
 // ------------------------------------------------------------------------------------------------
 // work lists
 // ------------------------------------------------------------------------------------------------
-// A side's tiles are ordered (batch, kv head) first, then tier, then tile; tile i starts at weight
-// bh * W + w0(tier) + i * w(tier).  CTA c owns the weights [c*Wt/n, (c+1)*Wt/n), its warp w an eighth of
-// that; a tile belongs to the warp whose range holds its start weight.
+// A pair's tiles of one side are ordered by tier, then tile; tile i of a tier starts at weight w0(tier) +
+// i * w(tier).  A tile belongs to the warp whose weight range holds its start weight.
 struct Cursor {
-  int bh, tier, tile;
-  long long s;  // start weight
+  int tier, tile;
+  int s;  // start weight
 };
 template <bool K> __device__ __forceinline__ int t_tiles(const TierDev& T) { return K ? T.k_tiles : T.v_tiles; }
 template <bool K> __device__ __forceinline__ int t_w(const TierDev& T) { return K ? T.k_w : T.v_w; }
 template <bool K> __device__ __forceinline__ int t_w0(const TierDev& T) { return K ? T.k_w0 : T.v_w0; }
 
-__device__ __noinline__ long long div_big(long long a, long long b) { return a / b; }  // one copy of the 64-bit division
-__device__ __forceinline__ long long cta_bound(long long total, int c, int n, int small) {
-  if (small) return static_cast<unsigned>(total) * static_cast<unsigned>(c) / static_cast<unsigned>(n);
-  return div_big(total * c, n);
-}
-__device__ __forceinline__ int div_ll(long long a, int b, int small) {
-  return small ? static_cast<int>(static_cast<unsigned>(a) / static_cast<unsigned>(b)) : static_cast<int>(div_big(a, b));
-}
-
+// first tile whose start weight is >= a (s = the side's total weight if there is none)
 template <bool K>
-__device__ __forceinline__ void cursor_weight(const DecodeParams& P, Cursor& c) {
-  const TierDev& T = P.tier[c.tier];
-  c.s = static_cast<long long>(c.bh) * (K ? P.wk : P.wv) + t_w0<K>(T) + c.tile * t_w<K>(T);
-}
-// first tile whose start weight is >= a
-template <bool K>
-__device__ __noinline__ Cursor cursor_at(const DecodeParams& P, long long a) {
-  const int W = K ? P.wk : P.wv;
+__device__ __noinline__ Cursor cursor_at(const DecodeParams& P, int a) {
   Cursor c;
-  c.bh = div_ll(a, W, P.small);
-  const int r = static_cast<int>(a - static_cast<long long>(c.bh) * W);
   c.tier = NUM_ITEM_TIERS;
   c.tile = 0;
-#pragma unroll
+  c.s = K ? P.wk : P.wv;
+#pragma unroll 1
   for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
     const TierDev& T = P.tier[t];
     const int n = t_tiles<K>(T), w = t_w<K>(T), w0 = t_w0<K>(T);
     if (n > 0 && c.tier == NUM_ITEM_TIERS) {
-      const int d = r - w0;  // weights are 3 or 4 in practice: no general integer division for those
-      const int tile = d <= 0 ? 0 : (w == 4 ? (d + 3) >> 2 : w == 3 ? (d + 2) / 3 : (d + w - 1) / w);
+      const int d = a - w0;  // weights are 1, 3 or 4 in practice: no general integer division for those
+      const int tile = d <= 0 ? 0 : (w == 4 ? (d + 3) >> 2 : w == 3 ? (d + 2) / 3 : w == 1 ? d : (d + w - 1) / w);
       if (tile < n) {
         c.tier = t;
         c.tile = tile;
+        c.s = w0 + tile * w;
       }
     }
   }
-  if (c.tier == NUM_ITEM_TIERS) {
-    ++c.bh;
-    c.tier = K ? P.k_first : P.v_first;
-  }
-  cursor_weight<K>(P, c);
   return c;
 }
 template <bool K>
@@ -154,49 +135,25 @@ __device__ __forceinline__ void cursor_next(const DecodeParams& P, Cursor& c) {
     do {
       ++c.tier;
     } while (c.tier < NUM_ITEM_TIERS && t_tiles<K>(P.tier[c.tier]) == 0);
-    if (c.tier == NUM_ITEM_TIERS) {
-      ++c.bh;
-      c.tier = K ? P.k_first : P.v_first;
-    }
   }
-  cursor_weight<K>(P, c);
-}
-
-// CTAs whose range [A_c, A_c+1) meets the weights [bh*W, (bh+1)*W) of one (batch, kv head): first and count
-__device__ __forceinline__ void contributors(long long total, int n, int W, int bh, int small, int& first, int& count) {
-  const long long x = static_cast<long long>(bh) * W, y = x + W;
-  first = div_ll((x + 1) * n + total - 1, static_cast<int>(total), small) - 1;
-  int last = div_ll(y * n + total - 1, static_cast<int>(total), small) - 1;
-  if (last > n - 1) last = n - 1;
-  count = last - first + 1;
+  c.s = c.tier < NUM_ITEM_TIERS ? t_w0<K>(P.tier[c.tier]) + c.tile * t_w<K>(P.tier[c.tier]) : (K ? P.wk : P.wv);
 }
 
 // (not inlined: called from several places, once per tile)
-__device__ __noinline__ void k_request(const DecodeParams& P, const Cursor c, unsigned char* wsm) {
+__device__ __noinline__ void k_request(const DecodeParams& P, const Cursor c, int bh, unsigned char* wsm) {
   if (c.tier >= HQKV_NUM_TIERS) return;
   const TierDev& T = P.tier[c.tier];
-  const int t0 = c.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
-  switch (T.bits) {
-    case 8: k_tile_request<8>(T, wsm, c.bh, t0, ntok, P.gk_shift); break;
-    case 4: k_tile_request<4>(T, wsm, c.bh, t0, ntok, P.gk_shift); break;
-    case 2: k_tile_request<2>(T, wsm, c.bh, t0, ntok, P.gk_shift); break;
-    case 1: k_tile_request<1>(T, wsm, c.bh, t0, ntok, P.gk_shift); break;
-    default: break;  // fp16 tier: read straight from global memory
-  }
+  if (T.bits == 16) return;  // fp16 tier: read straight from global memory
+  const int t0 = c.tile * T.k_tile_tokens;
+  k_tile_request(T, wsm, bh, t0, min(T.k_tile_tokens, T.n_k - t0), P.gk_shift);
 }
-
-__device__ __noinline__ uint4 v_request(const DecodeParams& P, const Cursor c, unsigned char* wsm) {
+__device__ __noinline__ uint4 v_request(const DecodeParams& P, const Cursor c, int bh, unsigned char* wsm) {
   uint32_t pos[4] = {0u, 0u, 0u, 0u};
-  if (c.tier >= HQKV_NUM_TIERS) return make_uint4(0u, 0u, 0u, 0u);
-  const TierDev& T = P.tier[c.tier];
-  const int t0 = c.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
-  const int ng = D >> P.gv_shift;
-  switch (T.bits) {
-    case 8: v_tile_request<8>(T, wsm, c.bh, t0, ntok, ng, pos); break;
-    case 4: v_tile_request<4>(T, wsm, c.bh, t0, ntok, ng, pos); break;
-    case 2: v_tile_request<2>(T, wsm, c.bh, t0, ntok, ng, pos); break;
-    case 1: v_tile_request<1>(T, wsm, c.bh, t0, ntok, ng, pos); break;
-    default: break;
+  if (c.tier < HQKV_NUM_TIERS && P.tier[c.tier].bits < 16) {
+    const TierDev& T = P.tier[c.tier];
+    const int t0 = c.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
+    v_tile_positions(T, t0, ntok, pos);
+    v_tile_request(T, wsm, bh, t0, ntok, D >> P.gv_shift);
   }
   return make_uint4(pos[0], pos[1], pos[2], pos[3]);
 }
@@ -235,349 +192,351 @@ __device__ __forceinline__ void peer_barrier_device(unsigned* const* pad, int ra
 __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __grid_constant__ DecodeParams P) {
   extern __shared__ __align__(128) unsigned char smem[];
   CtaShared& cs = *reinterpret_cast<CtaShared*>(smem);
+  __half* qsm = reinterpret_cast<__half*>(smem + CTA_HEAD_BYTES);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   unsigned char* wsm = smem + P.cta_smem + warp * P.warp_smem;
   const bool rep8 = P.rep > 4;
   const int rep = P.rep;
+  const int BH = P.B * P.H;
+  const bool do_k = (P.phases & 1) != 0, do_v = (P.phases & 2) != 0;
 
   // The next kernel of the stream - the next decode call, if it was launched with programmatic stream
   // serialisation - may place its CTAs as soon as CTAs of this grid have finished; it requests its
-  // first K tiles and then waits for this grid to complete.
-#ifndef HQKV_X_LD_LATE
+  // first K tile and then waits for this grid to complete.
   asm volatile("griddepcontrol.launch_dependents;");
-#endif
 
-  const int BH = P.B * P.H;
-  const int cta = blockIdx.x, ncta = gridDim.x;
-  const long long wk_tot = static_cast<long long>(BH) * P.wk, wv_tot = static_cast<long long>(BH) * P.wv;
-  const bool do_k = (P.phases & 1) != 0, do_v = (P.phases & 2) != 0;  // a side that is not run may be empty (weight 0)
-  const long long Ak0 = cta_bound(wk_tot, cta, ncta, P.small), Ak1 = cta_bound(wk_tot, cta + 1, ncta, P.small);
-  const long long Av0 = cta_bound(wv_tot, cta, ncta, P.small), Av1 = cta_bound(wv_tot, cta + 1, ncta, P.small);
-  // (batch, kv head) pairs whose weights meet this CTA's range, K side and V side
-  const int kbh0 = do_k ? div_ll(Ak0, P.wk, P.small) : 0;
-  const int nkb = do_k ? (Ak1 > 0 ? div_ll(Ak1 - 1, P.wk, P.small) : -1) - kbh0 + 1 : 0;
-  const int vbh0 = do_v ? div_ll(Av0, P.wv, P.small) : 0;
-  const int nvb = do_v ? (Av1 > 0 ? div_ll(Av1 - 1, P.wv, P.small) : -1) - vbh0 + 1 : 0;
-
-  if (tid < 8) {
-    int first = 0, count = 0;
-    if (tid < nkb) contributors(wk_tot, ncta, P.wk, kbh0 + tid, P.small, first, count);
-    cs.k_slot[tid] = cta - first;
-    count = 0;
-    if (tid < nvb && !P.probs_in) contributors(wk_tot, ncta, P.wk, vbh0 + tid, P.small, first, count);
-    cs.kp_cnt[tid] = count;
-    count = 0;
-    if (tid < nvb) contributors(wv_tot, ncta, P.wv, vbh0 + tid, P.small, first, count);
-    cs.v_cnt[tid] = count;
-  }
-  float2* kstat = reinterpret_cast<float2*>(wsm + WS_KSTAT);  // [MAX_BHL][MAX_REP] of this warp
-  kstat[lane] = make_float2(-INFINITY, 0.f);
-  kstat[lane + 32] = make_float2(-INFINITY, 0.f);
-  if (!do_k) __syncthreads();  // the tables above are read by other warps (with K ranges: after later barriers)
-
-  // ---------------------------------------------------------------------------------------------
-  // K ranges
-  // ---------------------------------------------------------------------------------------------
-  Cursor cur;
-  bool have = false;
-  long long a1 = 0;
-  if (do_k) {
-    const long long a0 = Ak0 + (Ak1 - Ak0) * warp / NWARPS;
-    a1 = Ak0 + (Ak1 - Ak0) * (warp + 1) / NWARPS;
-    cur = cursor_at<true>(P, a0);
-    have = cur.s < a1;
-    if (have) k_request(P, cur, wsm);  // reads only the cache
-  }
-  uint32_t vpos[4] = {0u, 0u, 0u, 0u};
-  Cursor vcur;
-  bool vhave = false;
-  long long va1 = 0;
-  if (do_v) {
-    const long long a0 = Av0 + (Av1 - Av0) * warp / NWARPS;
-    va1 = Av0 + (Av1 - Av0) * (warp + 1) / NWARPS;
-    vcur = cursor_at<false>(P, a0);
-    vhave = vcur.s < va1;
-    if (!do_k && vhave) {
-      const uint4 r = v_request(P, vcur, wsm);
-      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
+  // ---- this CTA's (batch, kv head) pair(s) and its place in the pair's group
+  int bh, gi = 0, gm_ = 1, sel = 0, bh_step;
+  if (P.g_m == 0) {  // more pairs than CTAs: whole pairs, one after the other
+    bh = blockIdx.x;
+    bh_step = gridDim.x;
+  } else {
+    const int c = blockIdx.x, big = P.g_rem * (P.g_m + 1);  // CTAs in the groups of g_m + 1
+    if (c < big) {
+      sel = 1;
+      gm_ = P.g_m + 1;
+      bh = static_cast<int>((c + 0.5f) * P.g_inv[1]);
+      gi = c - bh * gm_;
+    } else {
+      gm_ = P.g_m;
+      const int c2 = c - big, j = static_cast<int>((c2 + 0.5f) * P.g_inv[0]);
+      bh = P.g_rem + j;
+      gi = c2 - j * gm_;
     }
+    bh_step = BH;  // one pair
   }
-  // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
-  // the previous decode call of the stream may still be using: wait for the kernels before it.
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+  const bool local = gm_ == 1 && P.phases == 3 && P.probs_in == nullptr;  // the CTA has the whole pair: no global hand-over
+  float2* kstat = reinterpret_cast<float2*>(wsm + WS_KSTAT);  // this warp's (max, sum-exp) per head
+  bool first_unit = true;
+  unsigned finished = 0u;  // pairs this CTA wrote the output of (multi-GPU hand-over)
 
-  if (do_k) {
-    // q of this CTA's K-side pairs -> shared memory (rows of heads that do not exist are zero)
-    {
-      const int rows = rep8 ? 8 : 4;
-      __half* qsm = reinterpret_cast<__half*>(smem + CTA_HEAD_BYTES);
-      for (int i = tid; i < nkb * rows * (D / 2); i += NTHREADS) {
-        const int c2 = i & (D / 2 - 1), row = (i >> 6) % rows, slot = (i >> 6) / rows;
-        const int bh = kbh0 + slot, b = bh / P.H, kvh = bh - b * P.H;
-        uint32_t v = 0u;
-        if (row < rep) v = __ldcg(reinterpret_cast<const uint32_t*>(P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + row) * D) + c2);
-        *reinterpret_cast<uint32_t*>(qsm + (slot * rows + row) * Q_PITCH + 2 * c2) = v;
+  for (; bh < BH; bh += bh_step) {
+    const int b = bh / P.H, kvh = bh - b * P.H;
+    const int64_t head0 = static_cast<int64_t>(b) * P.nh_q + kvh * rep;
+    // weights of this CTA, then of this warp, on both sides
+    const int ka0 = gi * P.kq[sel] + min(gi, P.kr[sel]), ka1 = ka0 + P.kq[sel] + (gi < P.kr[sel] ? 1 : 0);
+    const int va0 = gi * P.vq[sel] + min(gi, P.vr[sel]), va1 = va0 + P.vq[sel] + (gi < P.vr[sel] ? 1 : 0);
+    const int k_end = ka0 + (((ka1 - ka0) * (warp + 1)) >> 3), v_end = va0 + (((va1 - va0) * (warp + 1)) >> 3);
+    Cursor cur, vcur;
+    bool have = false, vhave = false;
+    uint32_t vpos[4] = {0u, 0u, 0u, 0u};
+    if (do_k) {
+      cur = cursor_at<true>(P, ka0 + (((ka1 - ka0) * warp) >> 3));
+      have = cur.s < k_end;
+      if (have) k_request(P, cur, bh, wsm);  // reads only the cache
+    }
+    if (do_v) {
+      vcur = cursor_at<false>(P, va0 + (((va1 - va0) * warp) >> 3));
+      vhave = vcur.s < v_end;
+      if (!do_k && vhave) {
+        const uint4 r = v_request(P, vcur, bh, wsm);
+        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
       }
-      __syncthreads();
     }
-    // The first CTA of a (batch, kv head) pair's K side clears the pair's output accumulators: the V ranges add
-    // into them only after the K side of the pair is complete, and this CTA is part of it.  (The scratch may have
-    // held another cache's logits there a call ago.)
-    for (int i = 0; i < nkb; ++i)
-      if (cs.k_slot[i] == 0) {
-        double* accum = P.v_acc + static_cast<int64_t>(kbh0 + i) * rep * D;
+    if (first_unit) {
+      // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
+      // the previous decode call of the stream may still be using: wait for the kernels before it.
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      first_unit = false;
+    }
+
+    // -------------------------------------------------------------------------------------------
+    // K slice
+    // -------------------------------------------------------------------------------------------
+    if (do_k) {
+      // q of the pair -> shared memory (rows of heads that do not exist are zero)
+      {
+        const int rows = rep8 ? 8 : 4;
+        for (int i = tid; i < rows * (D / 2); i += NTHREADS) {
+          const int c2 = i & (D / 2 - 1), row = i >> 6;
+          uint32_t v = 0u;
+          if (row < rep) v = __ldcg(reinterpret_cast<const uint32_t*>(P.q + (head0 + row) * D) + c2);
+          *reinterpret_cast<uint32_t*>(qsm + row * Q_PITCH + 2 * c2) = v;
+        }
+      }
+      // The first CTA of a group clears the pair's output accumulators: the V slices add into them only after
+      // the K side of the pair is complete, and this CTA is part of it.
+      if (!local && gi == 0) {
+        double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
         for (int e = tid; e < rep * D; e += NTHREADS) accum[e] = 0.0;
       }
-    KWarpState st;
-    st.pm = -INFINITY;
-    st.pl = 0.f;
+      __syncthreads();
+      KWarpState st;
+      st.pm = -INFINITY;
+      st.pl = 0.f;
 #pragma unroll
-    for (int i = 0; i < 2; ++i)
+      for (int i = 0; i < 2; ++i)
 #pragma unroll
-      for (int e = 0; e < 2; ++e) {
-        st.m[i][e] = -INFINITY;
-        st.l[i][e] = 0.f;
-      }
-    int cur_bh = have ? cur.bh : -1;
-    float2* tmp = reinterpret_cast<float2*>(wsm + WS_K_ZQ);
-    while (have) {
-      const int b = cur.bh / P.H, kvh = cur.bh - b * P.H;
-      const __half* qs = reinterpret_cast<const __half*>(smem + CTA_HEAD_BYTES) + (cur.bh - kbh0) * (rep8 ? 8 : 4) * Q_PITCH;
-      float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * P.L;
+        for (int e = 0; e < 2; ++e) {
+          st.m[i][e] = -INFINITY;
+          st.l[i][e] = 0.f;
+        }
       st.mask0 = P.mask ? P.mask + b * P.mask_bstride + static_cast<int64_t>(kvh * rep) * P.mask_hstride : nullptr;
       st.mask_hstride = P.mask_hstride;
-      const TierDev& T = P.tier[cur.tier];
-      const int t0 = cur.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
-      if (cur.tier == HQKV_NUM_TIERS) {
-        k_residual_tile(T, wsm, st, qs, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
-      } else if (T.bits == 16) {
-        k_f16_span(T, wsm, st, qs, cur.bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
-      } else if (T.bits == 8) {
-        k_tile_compute<8>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
-      } else if (T.bits == 4) {
-        k_tile_compute<4>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
-      } else if (T.bits == 2) {
-        k_tile_compute<2>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
-      } else {
-        k_tile_compute<1>(T, wsm, st, qs, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0);
+      float* row0 = P.logits + head0 * P.L;
+      bool streamed = false;  // the current tile was requested while the previous one was computed
+      while (have) {
+        const TierDev& T = P.tier[cur.tier];
+        const int t0 = cur.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
+        Cursor nxt = cur;
+        cursor_next<true>(P, nxt);
+        const bool have_next = nxt.s < k_end;
+        // the next tile streams into this tile's buffer if it continues the same tier
+        const bool quant = cur.tier < HQKV_NUM_TIERS && T.bits < 16;
+        const bool stream = quant && have_next && nxt.tier == cur.tier;
+        const int nt0 = t0 + T.k_tile_tokens, nntok = stream ? min(T.k_tile_tokens, T.n_k - nt0) : 0;
+        if (cur.tier == HQKV_NUM_TIERS) {
+          k_residual_tile(T, wsm, st, qsm, bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
+        } else if (T.bits == 16) {
+          k_f16_span(T, wsm, st, qsm, bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
+        } else if (T.bits == 8) {
+          k_tile_compute<8>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
+        } else if (T.bits == 4) {
+          k_tile_compute<4>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
+        } else if (T.bits == 2) {
+          k_tile_compute<2>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
+        } else {
+          k_tile_compute<1>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
+        }
+        cur = nxt;
+        have = have_next;
+        streamed = stream;
+        __syncwarp();  // every lane is done with the tile in shared memory
+        if (have && !streamed) k_request(P, cur, bh, wsm);
       }
-      cursor_next<true>(P, cur);
-      have = cur.s < a1;
-      __syncwarp();  // every lane is done with the tile in shared memory
-      if (!have || cur.bh != cur_bh) {  // the warp leaves this (batch, kv head): its running pairs go to the table
-        k_emit_stats(st, kstat + (cur_bh - kbh0) * MAX_REP, tmp, rep);
-        cur_bh = cur.bh;
+      k_emit_stats(st, kstat, reinterpret_cast<float2*>(wsm + WS_K_ZQ), rep);
+      // the first V tile does not depend on the logits: request it before the hand-over
+      if (do_v && vhave) {
+        const uint4 r = v_request(P, vcur, bh, wsm);
+        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
       }
-      if (have) k_request(P, cur, wsm);
-    }
-    // the first V tile does not depend on the logits: request it before waiting for the K side
-    if (do_v && vhave) {
-      const uint4 r = v_request(P, vcur, wsm);
-      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
-    }
-
-    // ---- publish: one (max, sum-exp) per head for every (batch, kv head) pair of this CTA's K range
-    __syncthreads();
-    if (tid < 8 * MAX_REP) {
-      const int i = tid >> 3, head = tid & 7;
-      if (i < nkb) {
+      __syncthreads();
+      // ---- one (max, sum-exp) per head for the CTA's slice
+      if (tid < MAX_REP) {
         float m = -INFINITY, l = 0.f;
-#pragma unroll
+#pragma unroll 1
         for (int w = 0; w < NWARPS; ++w) {
           const float2 v = reinterpret_cast<const float2*>(smem + P.cta_smem + w * P.warp_smem + WS_KSTAT)[tid];
           softmax_merge(m, l, v.x, v.y);
         }
-        P.k_part[(static_cast<int64_t>(kbh0 + i) * P.kc_max + cs.k_slot[i]) * MAX_REP + head] = make_float2(m, l);
-      }
-    }
-    __threadfence();  // this thread's logits (and pair) before the count below
-    __syncthreads();
-    if (tid < nkb) atomicAdd(&P.kdone[kbh0 + tid], 1u);
-  }
-#ifdef HQKV_X_LD_LATE
-  asm volatile("griddepcontrol.launch_dependents;");
-#endif
-  if (!do_v) return;
-
-  // ---------------------------------------------------------------------------------------------
-  // wait for the K side of this CTA's V-side pairs; fold the published pairs (warp i takes pair i)
-  // ---------------------------------------------------------------------------------------------
-  if (P.probs_in) {  // weights are given: nothing to wait for, nothing to normalise by
-    if (tid < 8 * MAX_REP) {
-      (&cs.gm[0][0])[tid] = 0.f;
-      (&cs.gl[0][0])[tid] = 1.f;
-    }
-  } else if (warp < nvb) {
-    const int bh = vbh0 + warp;
-    const int cnt = cs.kp_cnt[warp];
-    if (lane == 0) {
-      const volatile unsigned* c = P.kdone + bh;
-      long long spins = 0;
-      while (*c < static_cast<unsigned>(cnt)) {
-        if (++spins > P.spin_limit) {
-          atomicExch(P.status, static_cast<unsigned>(bh) + 1u);  // gave up: the result of this call is not valid
-          break;
+        if (local) {
+          cs.gm[tid] = m;
+          cs.gl[tid] = l;
+        } else {
+          P.k_part[(static_cast<int64_t>(bh) * P.kc_max + gi) * MAX_REP + tid] = make_float2(m, l);
         }
-        __nanosleep(40);
       }
-      __threadfence();
-    }
-    __syncwarp();
-    const int head = lane & 7, slice = lane >> 3;
-    const float2* part = P.k_part + static_cast<int64_t>(bh) * P.kc_max * MAX_REP;
-    float m = -INFINITY, l = 0.f;
-    for (int c0 = slice; c0 < cnt; c0 += 16) {
-      float2 v[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int c = c0 + 4 * j;
-        v[j] = (c < cnt && head < rep) ? __ldcg(part + c * MAX_REP + head) : make_float2(-INFINITY, 0.f);
+      if (!local) {
+        __threadfence();  // this thread's logits (and pair) before the count below
+        __syncthreads();
+        if (tid == 0) atomicAdd(&P.kdone[bh], 1u);
+      } else {
+        __syncthreads();
       }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
     }
-#pragma unroll
-    for (int off = 8; off < 32; off <<= 1) {
-      const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
-      const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
-      softmax_merge(m, l, m2, l2);
-    }
-    if (lane < MAX_REP) {
-      cs.gm[warp][lane] = m;
-      cs.gl[warp][lane] = l;
-    }
-  }
-  __syncthreads();
+    if (!do_v) continue;
 
-  // ---------------------------------------------------------------------------------------------
-  // V ranges
-  // ---------------------------------------------------------------------------------------------
-  float(*out)[D] = reinterpret_cast<float(*)[D]>(wsm + ws_v_out(rep8));
-  float* zt = reinterpret_cast<float*>(wsm + ws_v_zt(rep8));
-  const int out_elems = (rep8 ? 8 : 4) * D;
-  auto clear_partial = [&]() {
-    for (int i = lane * 4; i < out_elems; i += 128) *reinterpret_cast<float4*>(&out[0][0] + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-    zt[lane] = 0.f;  // 4 x MAX_REP floats
-    __syncwarp();
-  };
-  int cur_bh = -1;
-  while (vhave) {
-    if (vcur.bh != cur_bh) {
-      if (cur_bh >= 0) {
-        // the warp moves on to another (batch, kv head): its partial output joins the accumulators directly
-        double* accum = P.v_acc + static_cast<int64_t>(cur_bh) * rep * D;
-        for (int i = lane; i < rep * D; i += 32) {
-          const int h = i >> 7, ch = i & (D - 1);
-          atomicAdd(accum + i, static_cast<double>(out[h][ch] + zt[(ch >> P.gv_shift) * MAX_REP + h]));
+    // -------------------------------------------------------------------------------------------
+    // wait for the K side of the pair; fold the published pairs
+    // -------------------------------------------------------------------------------------------
+    if (P.probs_in) {  // weights are given: nothing to wait for, nothing to normalise by
+      if (tid < MAX_REP) {
+        cs.gm[tid] = 0.f;
+        cs.gl[tid] = 1.f;
+      }
+      __syncthreads();
+    } else if (!local) {
+      if (warp == 0) {
+        if (lane == 0) {
+          const volatile unsigned* c = P.kdone + bh;
+          long long spins = 0;
+          while (*c < static_cast<unsigned>(gm_)) {
+            if (++spins > P.spin_limit) {
+              atomicExch(P.status, static_cast<unsigned>(bh) + 1u);  // gave up: the result of this call is not valid
+              break;
+            }
+            __nanosleep(40);
+          }
+          __threadfence();
         }
         __syncwarp();
-      }
-      clear_partial();
-      cur_bh = vcur.bh;
-    }
-    const int b = vcur.bh / P.H, kvh = vcur.bh - b * P.H;
-    const float* logit0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * P.L;
-    __half* w0 = P.weights + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * P.L;
-    const float* gm = cs.gm[vcur.bh - vbh0];
-    const float* gl = cs.gl[vcur.bh - vbh0];
-    const __half* pin0 = P.probs_in ? P.probs_in + (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * P.L : nullptr;
-    const TierDev& T = P.tier[vcur.tier];
-    const int t0 = vcur.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
-    if (vcur.tier == HQKV_NUM_TIERS || T.bits == 16) {
-      v_plain_tile(T, wsm, rep8, rep, P.L, gm, gl, vcur.bh, logit0, w0, pin0, t0, ntok, vcur.tier == HQKV_NUM_TIERS);
-    } else if (T.bits == 8) {
-      v_tile<8>(T, wsm, rep8, rep, P.L, P.gv_shift, gm, gl, vpos, logit0, w0, pin0, ntok);
-    } else if (T.bits == 4) {
-      v_tile<4>(T, wsm, rep8, rep, P.L, P.gv_shift, gm, gl, vpos, logit0, w0, pin0, ntok);
-    } else if (T.bits == 2) {
-      v_tile<2>(T, wsm, rep8, rep, P.L, P.gv_shift, gm, gl, vpos, logit0, w0, pin0, ntok);
-    } else {
-      v_tile<1>(T, wsm, rep8, rep, P.L, P.gv_shift, gm, gl, vpos, logit0, w0, pin0, ntok);
-    }
-    cursor_next<false>(P, vcur);
-    vhave = vcur.s < va1;
-    if (vhave) {
-      const uint4 r = v_request(P, vcur, wsm);
-      vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
-    }
-  }
-  if (lane == 0) cs.wbh[warp] = cur_bh;
-
-  // ---- the warps' partial outputs are added up (in warp order) and join the fp64 accumulators of
-  //      their (batch, kv head).  The adds are fire-and-forget reductions: the sum of the fp32 partials
-  //      depends on their order only below 2^-53, far below the fp16 rounding of the output, and no
-  //      CTA has to read other CTAs' partials back.
-  __syncthreads();
-  for (int i = tid; i < rep * D; i += NTHREADS) {
-    const int h = i >> 7, ch = i & (D - 1);
-    int run = -1;
-    float v = 0.f;
+        const int head = lane & 7, slice = lane >> 3;
+        const float2* part = P.k_part + static_cast<int64_t>(bh) * P.kc_max * MAX_REP;
+        float m = -INFINITY, l = 0.f;
+#pragma unroll 1
+        for (int c0 = slice; c0 < gm_; c0 += 16) {
+          float2 v[4];
 #pragma unroll
-    for (int w = 0; w < NWARPS; ++w) {
-      const int tag = cs.wbh[w];
-      if (tag < 0) continue;
-      if (tag != run) {
-        if (run >= 0) atomicAdd(P.v_acc + static_cast<int64_t>(run) * rep * D + i, static_cast<double>(v));
-        run = tag;
-        v = 0.f;
+          for (int j = 0; j < 4; ++j) {
+            const int c = c0 + 4 * j;
+            v[j] = (c < gm_ && head < rep) ? __ldcg(part + c * MAX_REP + head) : make_float2(-INFINITY, 0.f);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
+        }
+#pragma unroll
+        for (int off = 8; off < 32; off <<= 1) {
+          const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
+          const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+          softmax_merge(m, l, m2, l2);
+        }
+        if (lane < MAX_REP) {
+          cs.gm[lane] = m;
+          cs.gl[lane] = l;
+        }
       }
-      const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
-      v += reinterpret_cast<const float*>(o + ws_v_out(rep8))[h * D + ch] +
-           reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
+      __syncthreads();
     }
-    if (run >= 0) atomicAdd(P.v_acc + static_cast<int64_t>(run) * rep * D + i, static_cast<double>(v));
-  }
-  // ---- the last CTA of a (batch, kv head) normalises and writes the output
-  __threadfence();
-  __syncthreads();
-  if (tid < 8) {
-    unsigned last = 0u;
-    if (tid < nvb) {
-      const unsigned prev = atomicAdd(&P.vdone[vbh0 + tid], 1u);
-      last = (prev == static_cast<unsigned>(cs.v_cnt[tid]) - 1u) ? 1u : 0u;
+
+    // -------------------------------------------------------------------------------------------
+    // V slice
+    // -------------------------------------------------------------------------------------------
+    float(*out)[D] = reinterpret_cast<float(*)[D]>(wsm + ws_v_out(rep8));
+    float* zt = reinterpret_cast<float*>(wsm + ws_v_zt(rep8));
+    {
+      const int out_elems = (rep8 ? 8 : 4) * D;
+      for (int i = lane * 4; i < out_elems; i += 128) *reinterpret_cast<float4*>(&out[0][0] + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+      zt[lane] = 0.f;  // 4 x MAX_REP floats
+      __syncwarp();
     }
-    cs.is_last[tid] = last;
-  }
-  __syncthreads();
-  bool any_last = false;
-  for (int i = 0; i < nvb; ++i) {
-    if (!cs.is_last[i]) continue;
-    any_last = true;
-    const int bh = vbh0 + i;
-    const int b = bh / P.H, kvh = bh - b * P.H;
-    __threadfence();
-    double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
-    for (int e = tid * 2; e < rep * D; e += NTHREADS * 2) {
-      const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + e));
-      const float inv = 1.f / cs.gl[i][e >> 7];
-      const __half2 o = __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
-      const int64_t at = (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + e;
-      *reinterpret_cast<__half2*>(P.out + at) = o;
-      // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
-      // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
-      if (P.peer_flagged) {
-        // value and call number travel in ONE 8-byte store: the receiver needs no fence and no signal
-        const uint2 w = make_uint2(h2_as_u32(o), P.peer_state[0] + 1u);
-        for (int p = 0; p < P.n_peers; ++p) reinterpret_cast<uint2*>(P.peer_out[p])[at >> 1] = w;
+    const float* logit0 = P.logits + head0 * P.L;
+    __half* w0 = P.weights + head0 * P.L;
+    const __half* pin0 = P.probs_in ? P.probs_in + head0 * P.L : nullptr;
+    while (vhave) {
+      const TierDev& T = P.tier[vcur.tier];
+      const int t0 = vcur.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
+      Cursor nxt = vcur;
+      cursor_next<false>(P, nxt);
+      const bool have_next = nxt.s < v_end;
+      // the next tile streams into this tile's buffer if this one is full and the next continues the same tier;
+      // its positions are fetched now, its rows during the walk over this tile
+      const bool quant = vcur.tier < HQKV_NUM_TIERS && T.bits < 16;
+      const bool stream = quant && have_next && nxt.tier == vcur.tier && ntok == T.v_tile_tokens;
+      const int nt0 = t0 + T.v_tile_tokens, nntok = stream ? min(T.v_tile_tokens, T.n_v - nt0) : 0;
+      uint32_t npos[4] = {0u, 0u, 0u, 0u};
+      if (stream) v_tile_positions(T, nt0, nntok, npos);
+      if (vcur.tier == HQKV_NUM_TIERS || T.bits == 16) {
+        v_plain_tile(T, wsm, rep8, rep, P.L, cs.gm, cs.gl, bh, logit0, w0, pin0, t0, ntok, vcur.tier == HQKV_NUM_TIERS);
+      } else if (T.bits == 8) {
+        v_tile<8>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
+      } else if (T.bits == 4) {
+        v_tile<4>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
+      } else if (T.bits == 2) {
+        v_tile<2>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
       } else {
-        for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
+        v_tile<1>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
+      }
+      vcur = nxt;
+      vhave = have_next;
+      if (stream) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) vpos[j] = npos[j];
+      } else if (vhave) {
+        const uint4 r = v_request(P, vcur, bh, wsm);
+        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
       }
     }
-    if (tid == 0) {  // every CTA of this pair has passed its wait and counted itself in
-      P.kdone[bh] = 0u;
-      P.vdone[bh] = 0u;
+
+    // ---- the warps' partial outputs are added up in warp order.  A group of one has the pair's whole sum:
+    //      it normalises and writes.  In a larger group the sums join the pair's fp64 accumulators with
+    //      fire-and-forget reductions (the sum of the fp32 partials depends on their order only below 2^-53, far
+    //      below the fp16 rounding of the output, and no CTA has to read other CTAs' partials back), and the last
+    //      CTA of the pair to arrive normalises and writes.
+    __syncthreads();
+    bool writes = local;
+    if (!local) {
+      for (int e = tid; e < rep * D; e += NTHREADS) {
+        const int h = e >> 7, ch = e & (D - 1);
+        float v = 0.f;
+#pragma unroll 1
+        for (int w = 0; w < NWARPS; ++w) {
+          const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
+          v += reinterpret_cast<const float*>(o + ws_v_out(rep8))[e] +
+               reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
+        }
+        atomicAdd(P.v_acc + static_cast<int64_t>(bh) * rep * D + e, static_cast<double>(v));
+      }
+      __threadfence();
+      __syncthreads();
+      if (tid == 0) {
+        const unsigned prev = atomicAdd(&P.vdone[bh], 1u);
+        cs.is_last = (prev == static_cast<unsigned>(gm_) - 1u) ? 1u : 0u;
+      }
+      __syncthreads();
+      writes = cs.is_last != 0u;
+      if (writes) __threadfence();
     }
+    if (writes) {
+      ++finished;
+      const double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
+      for (int e = tid * 2; e < rep * D; e += NTHREADS * 2) {
+        float vx, vy;
+        if (local) {
+          const int h = e >> 7, ch = e & (D - 1);
+          vx = vy = 0.f;
+#pragma unroll 1
+          for (int w = 0; w < NWARPS; ++w) {
+            const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
+            const float2 a = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(o + ws_v_out(rep8)) + e);
+            const float z = reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
+            vx += a.x + z;
+            vy += a.y + z;
+          }
+        } else {
+          const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + e));
+          vx = static_cast<float>(v.x);
+          vy = static_cast<float>(v.y);
+        }
+        const float inv = 1.f / cs.gl[e >> 7];
+        const __half2 o = __floats2half2_rn(vx * inv, vy * inv);
+        const int64_t at = head0 * D + e;
+        *reinterpret_cast<__half2*>(P.out + at) = o;
+        // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
+        // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
+        if (P.peer_flagged) {
+          // value and call number travel in ONE 8-byte store: the receiver needs no fence and no signal
+          const uint2 w = make_uint2(h2_as_u32(o), P.peer_state[0] + 1u);
+          for (int p = 0; p < P.n_peers; ++p) reinterpret_cast<uint2*>(P.peer_out[p])[at >> 1] = w;
+        } else {
+          for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
+        }
+      }
+      if (!local && tid == 0) {  // every CTA of this pair has passed its wait and counted itself in
+        P.kdone[bh] = 0u;
+        P.vdone[bh] = 0u;
+      }
+    }
+    __syncthreads();  // the shared memory of this pair is free for the next one
   }
-  if (P.world > 1 && any_last) {
+
+  if (P.world > 1 && finished != 0u) {
     // the CTA that finishes the last (batch, kv head) of this GPU runs the cross-GPU barrier: when this
     // kernel completes, every rank's rows are in this GPU's gathered buffer
     __threadfence_system();
     __syncthreads();
     if (tid == 0) {
-      unsigned mine = 0u;
-      for (int i = 0; i < nvb; ++i) mine += cs.is_last[i];
-      const unsigned done = atomicAdd(P.peer_state + 2, mine);
-      cs.bar_n = (done + mine == static_cast<unsigned>(BH)) ? 1u : 0u;
+      const unsigned done = atomicAdd(P.peer_state + 2, finished);
+      cs.bar_n = (done + finished == static_cast<unsigned>(BH)) ? 1u : 0u;
       if (cs.bar_n) P.peer_state[2] = 0u;
     }
     __syncthreads();
@@ -622,6 +581,7 @@ struct Layout {
   size_t acc_off, logits_off, kpart_off, total;
   int smem_bytes;
   int ctas_per_sm;
+  int grid;
 };
 
 // sides: bit 0 = the K side of the descriptor is used, bit 1 = the V side (a one-sided call ignores the other side's fields)
@@ -733,35 +693,65 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   const bool rep8 = P.rep > 4;
   const int64_t BH = static_cast<int64_t>(c->B) * c->H;
   const int ctas_per_sm = rep8 ? 1 : CTAS_PER_SM;
+#ifdef HQKV_X_GRID_PER_SM
+  const int max_cta = HQKV_X_GRID_PER_SM * sm_count();
+#else
+  const int max_cta = ctas_per_sm * sm_count();
+#endif
   {
-    // With no more tiles than warps on the GPU every warp takes at most one tile of a side and what a tile costs
-    // is its chain of latencies, whatever its size: all tiles weigh the same.
+    // Grouping.  Fewer pairs than CTAs: every pair gets a group of m CTAs, m chosen so that a warp holds about one
+    // tile of the longer side (and all groups fit the GPU at once: the wait between the K slices and the V slices
+    // relies on it).  When a warp holds at most one tile of a side, what a tile costs is its chain of latencies
+    // whatever its size: all tiles weigh the same; otherwise the weights above.
     int64_t tk = 0, tv = 0;
     for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
       tk += P.tier[t].k_tiles;
       tv += P.tier[t].v_tiles;
     }
-    const int64_t warps = static_cast<int64_t>(ctas_per_sm) * sm_count() * NWARPS;
-    const bool one_wave = (tk > tv ? tk : tv) * BH <= warps;
-    P.w_unit = one_wave ? 1 : 3;
+    const int64_t tmax = tk > tv ? tk : tv;
+    const int m_cap = static_cast<int>(max_cta / BH);  // 0: more pairs than CTAs
+    const bool one_tile_per_warp = m_cap >= 1 && tmax <= static_cast<int64_t>(NWARPS) * m_cap;
     for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
       TierDev& d = P.tier[t];
-      if (one_wave) d.k_w = d.v_w = 1;
+      if (one_tile_per_warp) d.k_w = d.v_w = 1;
       d.k_w0 = static_cast<int>(wk);
       d.v_w0 = static_cast<int>(wv);
       wk += static_cast<int64_t>(d.k_tiles) * d.k_w;
       wv += static_cast<int64_t>(d.v_tiles) * d.v_w;
     }
+    HQKV_REQUIRE(wk < (1ll << 27) && wv < (1ll << 27), "decode: cache too long");
+    P.wk = static_cast<int>(wk);
+    P.wv = static_cast<int>(wv);
+    const int64_t wmax = wk > wv ? wk : wv;
+    if (m_cap == 0) {
+      P.g_m = 0;
+      P.g_rem = 0;
+      lay.grid = max_cta;
+    } else {
+      const int64_t m_want = ceil_div(wmax, static_cast<int64_t>(NWARPS) * (one_tile_per_warp ? 1 : 3));
+      if (m_want <= m_cap) {
+        P.g_m = static_cast<int>(m_want < 1 ? 1 : m_want);
+        P.g_rem = 0;
+      } else {
+        P.g_m = m_cap;
+        P.g_rem = static_cast<int>(max_cta - BH * m_cap);  // that many pairs get one CTA more
+      }
+      lay.grid = static_cast<int>(BH * P.g_m + P.g_rem);
+    }
+    for (int j = 0; j < 2; ++j) {
+      const int m = P.g_m + j < 1 ? 1 : P.g_m + j;
+      P.g_inv[j] = 1.0f / static_cast<float>(m);
+      P.kq[j] = P.wk / m;
+      P.kr[j] = P.wk % m;
+      P.vq[j] = P.wv / m;
+      P.vr[j] = P.wv % m;
+    }
   }
-  HQKV_REQUIRE(wk < (1ll << 30) && wv < (1ll << 30), "decode: cache too long");
-  P.wk = static_cast<int>(wk);
-  P.wv = static_cast<int>(wv);
   P.warp_smem = ws_bytes(rep8);
   P.cta_smem = cta_shared_bytes(rep8);
   lay.smem_bytes = P.cta_smem + NWARPS * P.warp_smem;
   lay.ctas_per_sm = ctas_per_sm;
-  const int max_cta = lay.ctas_per_sm * sm_count();
-  P.kc_max = static_cast<int>(max_cta / BH) + 3;
+  P.kc_max = static_cast<int>((ctas_per_sm * sm_count()) / BH) + 2;  // a group has at most max_cta / BH + 1 CTAs
   lay.acc_off = HQKV_WS_HEADER_BYTES;
   lay.logits_off = (lay.acc_off + static_cast<size_t>(BH) * P.rep * D * sizeof(double) + 255) & ~static_cast<size_t>(255);
   size_t off = lay.logits_off + static_cast<size_t>(c->B) * c->nh_q * L * sizeof(float);
@@ -771,26 +761,6 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   lay.total = (off + 255) & ~static_cast<size_t>(255);
   return HQKV_OK;
 }
-
-// CTAs of one launch: every warp gets about a quarter of a tile of the longer side at least, every CTA
-// meets at most MAX_BHL (batch, kv head) pairs, and all CTAs are resident at once (the wait between the
-// K ranges and the V ranges relies on it).
-static int grid_size(const DecodeParams& P, const Layout& lay) {
-  const int64_t BH = static_cast<int64_t>(P.B) * P.H;
-  const int64_t w = (P.wk > P.wv ? P.wk : P.wv) * BH;
-  int64_t n = ceil_div(w, NWARPS * P.w_unit);
-  const int64_t lo = ceil_div(BH, 3);
-#ifdef HQKV_X_GRID_PER_SM
-  const int64_t hi = static_cast<int64_t>(HQKV_X_GRID_PER_SM) * sm_count();
-#else
-  const int64_t hi = static_cast<int64_t>(lay.ctas_per_sm) * sm_count();
-#endif
-  if (n < lo) n = lo;
-  if (n > hi) n = hi;
-  return static_cast<int>(n);
-}
-// a CTA's range of n equal parts of BH pairs meets at most BH / n + 3 of them
-static bool pairs_per_cta_ok(const DecodeParams& P, int n) { return (static_cast<int64_t>(P.B) * P.H) / n + 3 <= MAX_BHL; }
 
 }  // namespace hqkv
 
@@ -911,21 +881,17 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
       HQKV_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      cta_shared_bytes(true) + NWARPS * ws_bytes(true)));
+      // two CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
+      HQKV_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                     static_cast<int>(cudaSharedmemCarveoutMaxShared)));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
   }
   // programmatic stream serialisation: the grid may start while the kernel before it drains, if that
   // kernel allows it (the previous decode call does); everything it does before its
   // griddepcontrol.wait reads only the cache tiers
-  const int n_cta = grid_size(P, lay);
-  {
-    const long long wmax = static_cast<long long>(P.wk > P.wv ? P.wk : P.wv) * P.B * P.H;
-    P.small = (wmax + 1) * (n_cta + 1) < (1ll << 31) ? 1 : 0;
-  }
-  HQKV_REQUIRE(pairs_per_cta_ok(P, n_cta), "decode: B*H = %d is too large for %d query heads per kv head on this GPU", P.B * P.H,
-               P.rep);
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(n_cta);
+  cfg.gridDim = dim3(lay.grid);
   cfg.blockDim = dim3(NTHREADS);
   cfg.dynamicSmemBytes = lay.smem_bytes;
   cfg.stream = st;

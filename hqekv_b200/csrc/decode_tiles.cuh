@@ -205,77 +205,72 @@ struct KTile {
   }
 };
 
-// Request a tile.  Oldest commit group: the scale / zero rows.  Group gamma of channel c (of G per
-// row) is half ((bh*128 + c)*G + g0) of its plane, at any 2-byte alignment; the two aligned 8-byte
-// pieces that cover the tile's (up to four) groups go to shared memory as they are, so group gamma of
-// the tile sits at half ((c*G + g0) & 3) + gamma of row c.  (The planes hold B*H*128*G halfs, a multiple
-// of 4, and start 8-byte aligned, so an aligned piece that begins inside a plane also ends inside it.)
-// Then four commit groups with the codes of channel rows 0-31, 32-63, 64-95, 96-127 (two 16-channel
-// steps each).  ntok = valid tokens of the tile (a multiple of 32).
-template <int BITS>
-__device__ __forceinline__ void k_tile_request(const TierDev& T, unsigned char* wsm, int bh, int tile_t0, int ntok,
-                                               int gk_shift) {
-  using TL = KTile<BITS>;
+// Requests of a tile's parts.  They are written once for all bit widths (the width is a run-time argument) and
+// are not inlined: with one tile per warp every instruction of this kernel is fetched about once per launch, so
+// what a launch costs is first of all the amount of code it walks through.
+//
+// Scale / zero rows: group gamma of channel c (of G per row) is half ((bh*128 + c)*G + g0) of its plane, at any
+// 2-byte alignment; the two aligned 8-byte pieces that cover the tile's (up to four) groups go to shared memory
+// as they are, so group gamma of the tile sits at half ((c*G + g0) & 3) + gamma of row c.  (The planes hold
+// B*H*128*G halfs, a multiple of 4, and start 8-byte aligned, so an aligned piece that begins inside a plane also
+// ends inside it.)  ntok = valid tokens of the tile (a multiple of 32).  Commits one group.
+__device__ __noinline__ void k_scales_request(const __half* k_scale, const __half* k_zero, unsigned char* wsm, int bh, int G,
+                                              int g0, int ng) {
   const int lane = threadIdx.x & 31;
-  const int n = T.n_k;
-  {
-    const int G = n >> gk_shift;
-    const int g0 = tile_t0 >> gk_shift;
-    const int ng = ((tile_t0 + ntok - 1) >> gk_shift) - g0 + 1;
-    __half* s = reinterpret_cast<__half*>(wsm + WS_K_S);
-    __half* z = reinterpret_cast<__half*>(wsm + WS_K_Z);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int ch = lane + 32 * j;
-      const int64_t e0 = (static_cast<int64_t>(bh) * D + ch) * G + g0;
-      const int64_t a = e0 & ~static_cast<int64_t>(3);
-      cp_async_8(s + ch * K_SROW, T.k_scale + a);
-      cp_async_8(z + ch * K_SROW, T.k_zero + a);
-      if (a + 4 < e0 + ng) {
-        cp_async_8(s + ch * K_SROW + 4, T.k_scale + a + 4);
-        cp_async_8(z + ch * K_SROW + 4, T.k_zero + a + 4);
-      }
+  __half* s = reinterpret_cast<__half*>(wsm + WS_K_S);
+  __half* z = reinterpret_cast<__half*>(wsm + WS_K_Z);
+#pragma unroll 1
+  for (int j = 0; j < 4; ++j) {
+    const int ch = lane + 32 * j;
+    const int64_t e0 = (static_cast<int64_t>(bh) * D + ch) * G + g0;
+    const int64_t a = e0 & ~static_cast<int64_t>(3);
+    cp_async_8(s + ch * K_SROW, k_scale + a);
+    cp_async_8(z + ch * K_SROW, k_zero + a);
+    if (a + 4 < e0 + ng) {
+      cp_async_8(s + ch * K_SROW + 4, k_scale + a + 4);
+      cp_async_8(z + ch * K_SROW + 4, k_zero + a + 4);
     }
   }
   cp_async_commit();
-  unsigned char* codes = wsm + WS_CODES;
-  const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
-  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes +
-                             static_cast<int64_t>(tile_t0) * BITS / 8;
-  const int valid_bytes = ntok * BITS / 8;  // per row: a multiple of 8 (of 4 at 1 bit)
-  if constexpr (BITS == 1) {
-    // 16 bytes per row at 4-byte alignment: four 4-byte pieces; a copy instruction moves 8 rows
-#pragma unroll
-    for (int quarter = 0; quarter < 4; ++quarter) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int row = quarter * 32 + i * 8 + (lane >> 2), c4 = 4 * (lane & 3);
-        if (c4 < valid_bytes) cp_async_4(codes + row * 16 + c4, src + row * row_bytes + c4);
-      }
-      cp_async_commit();
+}
+// Codes of channel rows 32*quarter .. 32*quarter + 31 (two 16-channel steps).  src: byte address of (row 0, first
+// token of the tile).  A row holds `pitch` bytes in shared memory (64, 64, 32, 16 at 8, 4, 2, 1 bits); four lanes
+// share a row, each copies pitch / 4 bytes (16, 16, 8, 4 - also the alignment rows of that width are sure to
+// have in memory), so one copy instruction moves 8 rows.  The shared-memory layout is KTile<BITS>::offset.
+// Commits one group.
+__device__ __noinline__ void k_codes_request(const unsigned char* src, int64_t row_bytes, unsigned char* codes, int pitch,
+                                             int valid_bytes, int quarter) {
+  const int lane = threadIdx.x & 31;
+  const int piece = pitch >> 2, r0 = lane >> 2, cb = (lane & 3) * piece;  // byte of the row this lane copies
+  if (cb < valid_bytes) {
+#pragma unroll 1
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t row = quarter * 32 + i * 8 + r0;
+      const uint32_t swz = pitch == 64 ? ((row >> 1) & 3u) : pitch == 32 ? ((row >> 2) & 1u) : 0u;
+      unsigned char* d = codes + row * pitch + (((static_cast<uint32_t>(cb) >> 4) ^ swz) << 4) + (cb & 15);
+      const unsigned char* s = src + row * row_bytes + cb;
+      if (piece == 16) cp_async_16(d, s);
+      else if (piece == 8) cp_async_8(d, s);
+      else cp_async_4(d, s);
     }
-    return;
   }
-  // a copy instruction moves 8 rows x 64 bytes (16 rows x 32 bytes at 2 bits)
-  constexpr int LPR = BITS == 2 ? 2 : 4;    // lanes per row
-  constexpr int RPI = 32 / LPR;             // rows per instruction
-  const int c = lane % LPR, r0 = lane / LPR;
-#pragma unroll
-  for (int quarter = 0; quarter < 4; ++quarter) {
-#pragma unroll
-    for (int i = 0; i < 32 / RPI; ++i) {
-      const int row = quarter * 32 + i * RPI + r0;
-      const unsigned char* s = src + row * row_bytes + 16 * c;
-      unsigned char* d = codes + TL::offset(row, c);
-      if constexpr (BITS == 2) {  // rows of 2-bit codes are only 8-byte aligned in memory
-        if (16 * c < valid_bytes) cp_async_8(d, s);
-        if (16 * c + 8 < valid_bytes) cp_async_8(d + 8, s + 8);
-      } else {
-        if (16 * c < valid_bytes) cp_async_16(d, s);
-      }
-    }
-    cp_async_commit();
-  }
+  cp_async_commit();
+}
+__device__ __forceinline__ int k_pitch(int bits) { return bits == 1 ? 16 : bits == 2 ? 32 : 64; }
+__device__ __forceinline__ const unsigned char* k_tile_src(const TierDev& T, int bh, int tile_t0, int64_t& row_bytes) {
+  row_bytes = static_cast<int64_t>(T.n_k) * T.bits / 8;
+  return reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes +
+         static_cast<int64_t>(tile_t0) * T.bits / 8;
+}
+// A whole tile: the scale / zero rows in the oldest commit group, then one group per quarter of the codes.
+__device__ __noinline__ void k_tile_request(const TierDev& T, unsigned char* wsm, int bh, int tile_t0, int ntok, int gk_shift) {
+  const int g0 = tile_t0 >> gk_shift;
+  k_scales_request(T.k_scale, T.k_zero, wsm, bh, T.n_k >> gk_shift, g0, ((tile_t0 + ntok - 1) >> gk_shift) - g0 + 1);
+  int64_t row_bytes;
+  const unsigned char* src = k_tile_src(T, bh, tile_t0, row_bytes);
+#pragma unroll 1
+  for (int quarter = 0; quarter < 4; ++quarter)
+    k_codes_request(src, row_bytes, wsm + WS_CODES, k_pitch(T.bits), ntok * T.bits / 8, quarter);
 }
 
 // Zq[group][head] of the tile for the heads in qf: rows of the A operand are the tile's groups
@@ -386,10 +381,14 @@ struct KWarpState {
 
 // One tile of a quantised tier, already requested: all heads of this kv head.
 // row0: logit row of head 0 of this kv head; qs: q rows of this kv head in shared memory (Q_PITCH halfs each).
+// Streaming: with next_ntok > 0 the NEXT tile of the same tier and (batch, kv head) - tokens next_t0 .. - is
+// requested into the same buffer while this one is computed: a quarter of its code rows as soon as the last
+// walk over this tile is done with that quarter, its scale / zero rows after the last step.  A tile that was
+// requested that way (streamed_in) finds all its parts issued, the scale rows last.
 template <int BITS>
 __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* wsm, KWarpState& st, const __half* qs,
-                                               int rep, int L, int gk_shift, float qk_scale, int tile_t0, int ntok,
-                                               float* row0) {
+                                               int bh, int rep, int L, int gk_shift, float qk_scale, int tile_t0, int ntok,
+                                               float* row0, bool streamed_in, int next_t0, int next_ntok) {
   using TL = KTile<BITS>;
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int G = T.n_k >> gk_shift;
@@ -422,7 +421,9 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
   const bool normal = BITS == 1 && T.normal != 0;
   const float pscale = normal ? qk_scale * (2.f * HQKV_NORMAL1_CENTER) : qk_scale;
 
-  cp_async_wait<4>();  // the scale / zero rows
+  const bool stream_out = next_ntok > 0;
+  if (streamed_in) cp_async_wait<0>();  // everything of this tile was requested during the previous one
+  else cp_async_wait<4>();              // the scale / zero rows
   __syncwarp();
   for (int hh = 0; hh < nh; ++hh) {
     // as a B column this lane is n = g: query head 4*hh + (g & 3) (columns 4-7 repeat 0-3)
@@ -467,8 +468,11 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
       // once, so it is fetched rather than reused)
 #pragma unroll 1
       for (int kk = 0; kk < 4; ++kk) {
-        if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
-          if (kk == 0) cp_async_wait<3>();
+        const bool last_walk = hh == nh - 1 && j == TL::NSUB - 1;
+        if (hh == 0 && j == 0 && !streamed_in) {  // the codes arrive two steps at a time
+          // groups younger than this quarter: the later quarters of this tile, and - when this only walk is also
+          // the last one and streams the next tile in - the kk quarters of the next tile requested so far
+          if (kk == 0 || (last_walk && stream_out)) cp_async_wait<3>();
           else if (kk == 1) cp_async_wait<2>();
           else if (kk == 2) cp_async_wait<1>();
           else cp_async_wait<0>();
@@ -524,6 +528,17 @@ __device__ __forceinline__ void k_tile_compute(const TierDev& T, unsigned char* 
 #pragma unroll
           for (int i = 0; i < 4; ++i) mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
         }
+        if (last_walk && stream_out) {  // nobody reads these 32 channel rows of this tile again
+          __syncwarp();
+          int64_t row_bytes;
+          const unsigned char* src = k_tile_src(T, bh, next_t0, row_bytes);
+          k_codes_request(src, row_bytes, wsm + WS_CODES, TL::PITCH, next_ntok * BITS / 8, kk);
+        }
+      }
+      if (hh == nh - 1 && j == TL::NSUB - 1 && stream_out) {  // the scale / zero rows are free as well
+        __syncwarp();
+        const int ng0 = next_t0 >> gk_shift;
+        k_scales_request(T.k_scale, T.k_zero, wsm, bh, G, ng0, ((next_t0 + next_ntok - 1) >> gk_shift) - ng0 + 1);
       }
       // Epilogue from registers.
       uint32_t pos[4];
@@ -801,49 +816,51 @@ __device__ __forceinline__ uint32_t v_field(uint32_t r, uint32_t r_shr8, int f) 
   }
 }
 
-// Request a tile: scales and zeros in the oldest commit group, then the codes in four groups of a
-// quarter of the steps each; the logical positions of the lane's tokens (lane + 32 j) come back in
-// registers.  ntok = valid tokens (a multiple of 32), ng = channel groups.
-template <int BITS>
-__device__ __forceinline__ void v_tile_request(const TierDev& T, unsigned char* wsm, int bh, int tile_t0, int ntok, int ng,
-                                               uint32_t (&pos)[4]) {
-  using TL = VTile<BITS>;
+// Request of one quarter of a tile's tokens (16 consecutive rows at 8 bits, 32 otherwise): their scales and zeros
+// (ng halfs per token each, contiguous in memory) and their code rows of 16 * bits bytes, laid out as
+// VTile<BITS>::offset.  ntok = valid tokens of the tile (a multiple of 32).  Written once for all widths, not
+// inlined (see k_scales_request).  Commits one group.
+__device__ __noinline__ void v_quarter_request(const TierDev& T, unsigned char* wsm, int bh, int tile_t0, int ntok, int ng,
+                                               int quarter) {
   const int lane = threadIdx.x & 31;
+  const int bits = T.bits;
   const int64_t tok0 = static_cast<int64_t>(bh) * T.n_v + tile_t0;
+  const int qtok = bits == 8 ? 16 : 32;  // tokens per quarter
+  {
+    // 8-byte pieces: a quarter holds qtok * ng * 2 bytes = 32 .. 256
+    const int o = quarter * qtok * ng * 2 + lane * 8, bytes = min(ntok, (quarter + 1) * qtok) * ng * 2;
+    if (lane * 8 < qtok * ng * 2 && o < bytes) {
+      cp_async_8(wsm + WS_V_S + o, reinterpret_cast<const unsigned char*>(T.v_scale + tok0 * ng) + o);
+      cp_async_8(wsm + WS_V_Z + o, reinterpret_cast<const unsigned char*>(T.v_zero + tok0 * ng) + o);
+    }
+  }
+  unsigned char* codes = wsm + WS_CODES;
+  const uint32_t pitch = 16u * bits;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.v_data) + tok0 * pitch;
+  const int np_shift = bits == 8 ? 3 : bits == 4 ? 2 : bits == 2 ? 1 : 0;  // log2(16-byte pieces per row)
+  const int per_q = (qtok << np_shift) >> 5;                                // copies per lane and quarter: 4, 4, 2, 1
+#pragma unroll 1
+  for (int i = 0; i < per_q; ++i) {
+    const uint32_t id = (quarter * per_q + i) * 32 + lane;
+    const uint32_t row = id >> np_shift, c = id & ((1u << np_shift) - 1u);
+    const uint32_t swz = bits == 8 ? (row & 7u) : bits == 4 ? ((row >> 1) & 3u) : bits == 2 ? ((row >> 2) & 1u) : 0u;
+    if (static_cast<int>(row) < ntok) cp_async_16(codes + row * pitch + ((c ^ swz) << 4), src + static_cast<int64_t>(id) * 16);
+  }
+  cp_async_commit();
+}
+// logical positions of the lane's tokens (lane + 32 j) of a tile of `tile_tokens` tokens
+__device__ __forceinline__ void v_tile_positions(const TierDev& T, int tile_t0, int ntok, uint32_t (&pos)[4]) {
+  const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const int t = lane + 32 * j;
-    pos[j] = (j < TL::TOKENS / 32 && t < ntok) ? ld_pos(T.v_idx + tile_t0 + t) : 0u;
+    pos[j] = t < ntok ? ld_pos(T.v_idx + tile_t0 + t) : 0u;
   }
-  // scale / zero rows are ng halfs per token, contiguous over the tile: 8-byte pieces
-  {
-    const int bytes = ntok * ng * 2;
-    const unsigned char* s = reinterpret_cast<const unsigned char*>(T.v_scale + tok0 * ng);
-    const unsigned char* z = reinterpret_cast<const unsigned char*>(T.v_zero + tok0 * ng);
-#pragma unroll
-    for (int j = 0; j < V_MAX_TT * 4 * 2 / (32 * 8); ++j) {
-      const int o = (lane + 32 * j) * 8;
-      if (o < bytes) {
-        cp_async_8(wsm + WS_V_S + o, s + o);
-        cp_async_8(wsm + WS_V_Z + o, z + o);
-      }
-    }
-  }
-  cp_async_commit();
-  unsigned char* codes = wsm + WS_CODES;
-  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.v_data) + tok0 * TL::PITCH;
-  constexpr int PIECES = TL::TOKENS * TL::NPIECE;  // 512 (256 at 2 bits, 128 at 1 bit)
-  constexpr int PER_Q = PIECES / 4 / 32;           // copies per lane and quarter: 4 (2, 1)
-#pragma unroll
-  for (int quarter = 0; quarter < 4; ++quarter) {
-#pragma unroll
-    for (int i = 0; i < PER_Q; ++i) {
-      const int id = (quarter * PER_Q + i) * 32 + lane;
-      const int row = id / TL::NPIECE, c = id % TL::NPIECE;
-      if (row < ntok) cp_async_16(codes + TL::offset(row, c), src + static_cast<int64_t>(id) * 16);
-    }
-    cp_async_commit();
-  }
+}
+// A whole tile: four commit groups, one per quarter of the tokens.
+__device__ __noinline__ void v_tile_request(const TierDev& T, unsigned char* wsm, int bh, int tile_t0, int ntok, int ng) {
+#pragma unroll 1
+  for (int quarter = 0; quarter < 4; ++quarter) v_quarter_request(T, wsm, bh, tile_t0, ntok, ng, quarter);
 }
 
 // exp(logit - max) of the tile's tokens for heads h0..h0+3 into prow[0..3][token], and the
@@ -897,9 +914,12 @@ __device__ __forceinline__ void v_tile_probs(const float* gm, const float* gl, c
 
 // One tile of a quantised V tier for one half of the heads: acc[mt] = M-tile mt of the output
 // (channels x heads, see the channel map in v_tile_store), zacc = zero term rows.
+// With next_ntok > 0 the quarters of the NEXT tile of the same tier and (batch, kv head) (tokens next_t0 ..) are
+// requested into the same buffer as soon as this walk is done with the rows they replace.
 template <int BITS>
-__device__ __forceinline__ void v_tile_walk(const unsigned char* wsm, int gv_shift, const __half (*prow)[V_PROW], int ntok,
-                                            float (&acc)[8][4], float (&zacc)[4], bool normal) {
+__device__ __forceinline__ void v_tile_walk(const TierDev& T, unsigned char* wsm, int gv_shift, const __half (*prow)[V_PROW],
+                                            int ntok, float (&acc)[8][4], float (&zacc)[4], bool normal, int bh, int next_t0,
+                                            int next_ntok) {
   using TL = VTile<BITS>;
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int ng_shift = 7 - gv_shift;  // log2(groups per token): 2, 1, 0
@@ -1026,11 +1046,20 @@ __device__ __forceinline__ void v_tile_walk(const unsigned char* wsm, int gv_shi
           for (int f = 0; f < 2; ++f) mma16816(acc[4 * q + 2 * u + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[q][0], bl_[q][1]);
         }
     }
+    if (next_ntok > 0) {  // a quarter of this tile's rows is behind the walk: the next tile's rows may take their place
+      constexpr int SPQ = TL::STEPS / 4;  // steps per quarter: 1 (8 bits) or 2
+      if ((st + 1) % SPQ == 0) {
+        __syncwarp();
+        v_quarter_request(T, wsm, bh, next_t0, next_ntok, 128 >> gv_shift, st / SPQ);
+      }
+    }
   }
   if (BITS == 1 && normal) {  // value = std * C * (2 code - 1) + mean: the code-free term is sum_t p (mean - C std)
 #pragma unroll
     for (int i = 0; i < 4; ++i) zacc[i] = fmaf(-HQKV_NORMAL1_CENTER, sacc[i], zacc[i]);
   }
+  (void)T;
+  (void)bh;
 }
 
 // Accumulators of one walk are ADDED to out[head of this half][channel] (every element has exactly one owner).
@@ -1072,10 +1101,12 @@ __device__ __forceinline__ void v_tile_store(float (*out)[D], const float (&acc)
 
 // Everything a warp does for one tile of a quantised V tier, already requested: probabilities of its
 // tokens, then sum_t p_t * V_t added to the warp's partial output.
+// Streaming (next_ntok > 0, only for a full tile): the next tile of the same tier and (batch, kv head) is requested
+// into the same buffer during the last walk over this one.
 template <int BITS>
 __device__ __forceinline__ void v_tile(const TierDev& T, unsigned char* wsm, bool rep8, int rep, int L, int gv_shift,
                                        const float* gm, const float* gl, const uint32_t (&pos)[4], const float* logit0,
-                                       __half* w0, const __half* pin0, int ntok) {
+                                       __half* w0, const __half* pin0, int ntok, int bh, int next_t0, int next_ntok) {
   using TL = VTile<BITS>;
   const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
   const int nh = rep8 ? 2 : 1;
@@ -1090,7 +1121,7 @@ __device__ __forceinline__ void v_tile(const TierDev& T, unsigned char* wsm, boo
   const bool normal = BITS == 1 && T.normal != 0;
   for (int hh = 0; hh < nh; ++hh) {
     float acc[8][4], zacc[4];
-    v_tile_walk<BITS>(wsm, gv_shift, hh ? p_hi : p_lo, ntok, acc, zacc, normal);
+    v_tile_walk<BITS>(T, wsm, gv_shift, hh ? p_hi : p_lo, ntok, acc, zacc, normal, bh, next_t0, hh == nh - 1 ? next_ntok : 0);
     v_tile_store<BITS>(out + 4 * hh, acc, normal ? 2.f * HQKV_NORMAL1_CENTER : 1.f);
     if (g < 4 && tig < 2) {
       zt[g * MAX_REP + 4 * hh + 2 * tig] += zacc[0];

@@ -17,10 +17,12 @@ pytestmark = pytest.mark.gpu
 ATTN_REL_TOL = 2e-3        # max |out - oracle| / max |oracle| per head
 # Probabilities are returned in fp16 (subnormal below 6.1e-5, quantum 2^-24).  The kernel carries the logits in
 # fp32 (q * scale enters the tensor pipe exactly, as hi + lo), so a probability differs from the fp32 oracle's by
-# its final rounding to fp16 plus fp32 summation-order noise: within ONE fp16 ulp (2^-10 relative).  (The
-# reference rounds the logits themselves to fp16, which is an order of magnitude coarser.)
+# its final rounding to fp16 (half an ulp, 2^-11 relative) plus the fp32 accumulation noise of the logit.  That
+# noise is largest for 1-bit tiers with groups of 64 / 128 tokens, where code * scale and the zero term are two
+# large sums that nearly cancel: measured 1.4e-3 relative there, below 1e-3 everywhere else.  Bound: TWO fp16
+# ulps (2^-9).  (The reference rounds the logits themselves to fp16, which is an order of magnitude coarser.)
 WEIGHT_ABS_TOL = 2.0 ** -24
-WEIGHT_REL_TOL = 2.0 ** -10
+WEIGHT_REL_TOL = 2.0 ** -9
 MEASURED = {"attn_rel": 0.0, "weight_rel": 0.0}   # largest errors seen over the whole module, reported at the end
 
 
