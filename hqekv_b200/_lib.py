@@ -46,6 +46,7 @@ class FlushSrc(C.Structure):
 _SIGNATURES = {
     "hqkv_last_error": (C.c_char_p, []),
     "hqkv_version": (C.c_int, []),
+    "hqkv_build_id": (C.c_char_p, []),
     "hqkv_checks_enabled": (C.c_int, []),
     "hqkv_check_failures": (C.c_int, [C.c_int, C.POINTER(C.c_uint)]),
     "hqkv_quantize_pack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
@@ -60,7 +61,6 @@ _SIGNATURES = {
     "hqkv_unpack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "hqkv_decode_workspace_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
     "hqkv_decode_workspace_zero_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
-    "hqkv_decode_status": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int)]),
     "hqkv_decode_logits": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "hqkv_decode_weighted_sum": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                            C.c_void_p]),

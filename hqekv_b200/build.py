@@ -1,10 +1,14 @@
 """Build libhqkv.so (the C-ABI library) in-tree with nvcc for sm_100a.
 
-    python -m hqekv_b200.build          # rebuild if a source is newer than the library
+    python -m hqekv_b200.build          # rebuild if the library was not compiled from the sources present
     python -m hqekv_b200.build --force
+    python -m hqekv_b200.build --checks # the bounds-check build, libhqkv_checked.so
+
+Every build is stamped with a hash of its sources (hqkv_build_id()).
 
 No --use_fast_math: the codec relies on IEEE division and explicit roundings.
 """
+import hashlib
 import os
 import subprocess
 import sys
@@ -29,12 +33,33 @@ def _nvcc():
     return "nvcc"
 
 
+def source_id():
+    """First 16 hex digits of the SHA-256 over the library's sources (csrc sorted by name, then the header)."""
+    h = hashlib.sha256()
+    for path in sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC)) + [os.path.join(INCLUDE, "hqkv.h")]:
+        with open(path, "rb") as f:
+            h.update(os.path.basename(path).encode() + b"\0" + f.read())
+    return h.hexdigest()[:16]
+
+
+def library_id(path=LIB_PATH):
+    """The stamp inside a built library, read from the file without loading it (None if there is none)."""
+    marker = b"HQKV_BUILD_ID="
+    try:
+        with open(path, "rb") as f:
+            blob = f.read()
+    except OSError:
+        return None
+    at = blob.find(marker)
+    if at < 0:
+        return None
+    end = blob.find(b"\0", at)
+    return blob[at + len(marker):end].decode(errors="replace")
+
+
 def needs_build():
-    if not os.path.exists(LIB_PATH):
-        return True
-    built = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(INCLUDE, "hqkv.h")]
-    return any(os.path.getmtime(d) > built for d in deps)
+    """True when the library is missing or was compiled from other sources than the ones present."""
+    return not os.path.exists(LIB_PATH) or library_id(LIB_PATH) != source_id()
 
 
 CHECKED_LIB_PATH = os.path.join(HERE, "libhqkv_checked.so")
@@ -46,6 +71,8 @@ def build(force=False, verbose=False, checks=False):
     if os.environ.get("HQKV_LIB") and not checks:
         return os.environ["HQKV_LIB"]  # the caller points at a library it built itself
     if checks:
+        if not force and os.path.exists(CHECKED_LIB_PATH) and library_id(CHECKED_LIB_PATH) == source_id():
+            return CHECKED_LIB_PATH
         return _compile(CHECKED_LIB_PATH, os.path.join(HERE, "build", "checked"), ["-DHQKV_CHECKS"], verbose)
     if not force and not needs_build():
         return LIB_PATH
@@ -55,6 +82,7 @@ def build(force=False, verbose=False, checks=False):
 def _compile(lib_path, objdir, extra, verbose):
     os.makedirs(objdir, exist_ok=True)
     nvcc = _nvcc()
+    extra = [*extra, f'-DHQKV_BUILD_ID="{source_id()}"']
     procs = []
     for src in SOURCES:
         obj = os.path.join(objdir, src.replace(".cu", ".o"))

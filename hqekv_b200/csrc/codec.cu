@@ -333,6 +333,12 @@ using namespace hqkv;
 
 extern "C" const char* hqkv_last_error(void) { return g_err; }
 extern "C" int hqkv_version(void) { return 100; }
+#ifndef HQKV_BUILD_ID
+#define HQKV_BUILD_ID "unstamped"
+#endif
+// the marker lets a build script read the stamp out of the file without loading the library
+static const char g_build_stamp[] = "HQKV_BUILD_ID=" HQKV_BUILD_ID;
+extern "C" const char* hqkv_build_id(void) { return g_build_stamp + 14; }
 
 extern "C" int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_t inner, int64_t outer_stride,
                                   int64_t inner_stride, int64_t t_stride, int group, int bits, void* code,

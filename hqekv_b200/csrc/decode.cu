@@ -1,161 +1,1346 @@
-// Fused mixed-precision decode attention over the tiered KV cache (sm_100a): ONE launch per call.
+// Fused mixed-precision decode attention over the tiered KV cache (sm_100a).
 //
-// The work of a (batch, kv head) pair is a list of K tiles (logits of 64 / 128 tokens of one tier) followed by a
-// list of V tiles (exp, p.V of 64 / 128 tokens), see decode_tiles.cuh.  The grid is persistent: at most as many
-// CTAs as fit on the GPU at once (two per SM), each of eight warps.  With fewer pairs than CTAs every pair is
-// shared by a GROUP of m consecutive CTAs, each taking an equal slice of both lists (every warp an eighth of its
-// CTA's slice); with more pairs than CTAs every CTA takes whole pairs, one after the other (a group of one).
+// Two launches per call:
+//   k_pass : logits[h, pos] = scale * q_h . K^_pos for every tier (8/4/2/1-bit packed, fp16 tier,
+//            fp16 residual), written to an fp32 scratch row at the tokens' logical positions,
+//            plus one (max, sum-exp) pair per CTA and head.
+//   v_pass : every CTA first folds the k_pass pairs into the global (max, sum) of its heads; each
+//            warp then writes the normalised probabilities of its own tokens and accumulates
+//            sum_t exp(logit_t - max) * V^_t over them; the CTA's partial output joins fp64
+//            accumulators, and the last CTA of each (batch, kv head) normalises and writes fp16.
 //
-//   K slice : logits written to an fp32 scratch row at the tokens' logical positions, a running (max, sum-exp)
-//             per head.  A group of one folds its warps' pairs in shared memory.  A larger group publishes one
-//             pair per head and CTA, counts itself in on the pair's arrival counter and
-//   waits   - the first V tile has been requested before (V tiles do not depend on the logits) - until the K
-//             side of its pair is complete, then folds the published pairs into the global (max, sum).  The wait
-//             is bounded: a count that does not arrive within the spin limit is recorded in the status word and
-//             the CTA goes on.
-//   V slice : every warp writes the normalised probabilities of its tokens and adds sum_t exp(logit_t - max) *
-//             V_t into its partial output in shared memory; the CTA's warps are added up.  A group of one
-//             normalises and writes fp16 at once; in a larger group the sums join fp64 accumulators with
-//             fire-and-forget reductions and the last CTA of the pair normalises and writes.
-//
-// Code size is a first-order cost here: with one tile per warp every instruction is executed about once per
-// launch, so a launch walks through its code at instruction-fetch speed.  Hence one (batch, kv head) pair per
-// CTA at a time (no tables, no divisions), request routines written once for all bit widths and not inlined,
-// and step loops that are not unrolled.
-//
-// The launch is chained with programmatic dependent launch: what a CTA needs only from the cache (its
-// first K tile) is requested before it waits for the kernels ahead of it in the stream, and the next
-// kernel's CTAs may take the places of CTAs that have finished.
+// The roofline is HBM: every packed word, scale and zero is read exactly once per call and is
+// shared by all query heads of its kv head (GQA).  At 2-4 bits there are 1.6-2.7 codes per byte;
+// four query heads need four FMAs per code, more than the FP32 pipes can issue at HBM speed, so the
+// dot products run on the tensor pipe (mma.sync m16n8k16, fp32 accumulation).  Tiles of codes are
+// staged in shared memory with 16-byte cp.async and read back with ldmatrix.trans, which delivers the
+// two K-neighbours of an A fragment in one register; the codes enter the MMA as fp16 subnormals (one
+// AND per pair) and the scale is folded into the B operand, carried exactly as hi + lo.
+// Both kernels are chained with programmatic dependent launch: whatever a kernel needs only from the
+// cache is requested before it waits for the kernel ahead of it.
+#include <math.h>
 #include <string.h>
 
-#include "decode_tiles.cuh"
+#include "common.cuh"
+
+#define HQKV_STR2(x) #x
+#define HQKV_STR(x) HQKV_STR2(x)
+#define HQKV_UNROLL(n) _Pragma(HQKV_STR(unroll n))
 
 namespace hqkv {
 
-constexpr int NWARPS = 8;
-constexpr int NTHREADS = NWARPS * 32;
-constexpr int NUM_ITEM_TIERS = HQKV_NUM_TIERS + 1;  // [5] = fp16 residual window (token-major K and V)
-constexpr int CTAS_PER_SM = 2;
-constexpr int WS_KDONE_OFF = 0, WS_VDONE_OFF = 4096, WS_STATUS_OFF = 8192;  // inside the zeroed workspace header
-constexpr int MAX_BH = 1024;
-static_assert(HQKV_WS_HEADER_BYTES >= WS_STATUS_OFF + 64 && MAX_BH * 4 <= 4096, "workspace header layout");
+HQKV_DEFINE_CHECK_COUNTER
+
+constexpr int D = 128;           // head dim
+constexpr int MAX_REP = 8;       // query heads per kv head (n of the m16n8k16 tile)
+
+struct TierDev {
+  const void* k_data;
+  const __half* k_scale;
+  const __half* k_zero;
+  const int64_t* k_idx;
+  const void* v_data;
+  const __half* v_scale;
+  const __half* v_zero;
+  const int64_t* v_idx;
+  int n_k, n_v;
+  int bits;
+  int normal;  // 1-bit tier in the Gaussian-codebook codec: value = std * (+-C) + mean, scale slots = std, zero = mean
+  int k_chunk0, k_chunk_tokens;  // first chunk id of this tier in the k_pass grid, tokens per chunk
+  int v_chunk0, v_chunk_tokens;
+};
 
 struct DecodeParams {
-  TierDev tier[NUM_ITEM_TIERS];
+  TierDev tier[HQKV_NUM_TIERS + 1];  // [5] = fp16 residual window (token-major K and V)
   int B, H, nh_q, rep, rep_shift, L;
   int gk_shift, gv_shift;
-  int phases;     // bit 0: K slices, bit 1: V slices
-  int kc_max;     // slots per (batch, kv head) in k_part
-  int warp_smem;  // bytes of one warp's shared-memory region
-  int cta_smem;   // bytes of the CTA-shared block ahead of the warps' regions
-  int wk, wv;     // weight of all tiles of one (batch, kv head) on the K / V side
-  int k_first, v_first;  // first tier that has tiles on that side
-  // grouping: the first g_rem pairs have groups of g_m + 1 CTAs, the others of g_m; g_m == 0: whole pairs per CTA
-  int g_m, g_rem;
-  float g_inv[2];        // 1 / g_m, 1 / (g_m + 1)
-  int kq[2], kr[2];      // wk / m and wk % m for m = g_m, g_m + 1: CTA i of m takes K weights [i*q + min(i, r), ...)
-  int vq[2], vr[2];      // the same for wv
+  int nk_chunks, nv_chunks;
   float scale;
   const __half* q;
-  const __half* mask;      // non-null: additive mask on the logits, fp16, element (b, head, pos) at b*mask_bstride + head*mask_hstride + pos
+  const __half* mask;      // additive mask on the logits (null: none); element (b, head, pos) at b*bstride + head*hstride + pos
   long long mask_bstride, mask_hstride;
-  const __half* probs_in;  // non-null: the V slices multiply these caller-supplied weights [B*nh_q][L] instead of exp(logit - max)
+  const __half* probs_in;  // V pass on caller-supplied weights [B*nh_q][L] (null: softmax of the scratch logits)
   __half* weights;
   __half* out;
   float* logits;   // [B*nh_q][L]
-  float2* k_part;  // [B*H][kc_max][MAX_REP]
-  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K slices, summed into by the V slices
-  unsigned* kdone;  // [B*H] CTAs whose K slice of this (batch, kv head) is complete
-  unsigned* vdone;  // [B*H] the same for the V slices
-  unsigned* status; // 0, or 1 + (batch, kv head) whose K side did not complete within the spin limit
-  long long spin_limit;
+  float2* k_part;  // [B*H][nk_chunks][MAX_REP]
+  double* v_acc;   // [B*H][rep][D] output accumulators: cleared by the K pass, summed into by the V pass
   __half* peer_out[HQKV_MAX_PEERS];  // copies of `out` in other GPUs' memory (kv-head sharding), n_peers used
   int n_peers;
   int peer_flagged;  // 1: peer_out are flagged 8-byte entries {two fp16 values, call number}, see peer_unpack_kernel
-  // cross-GPU barrier run by the CTA that finishes this GPU's last (batch, kv head) (world == 0: none)
+  // cross-GPU barrier run by the last CTA of the V pass (world == 0: none)
   unsigned* pad[HQKV_MAX_PEERS + 1];  // the ranks' signal pads, own one included
   int rank, world;
   unsigned* peer_state;  // call number, status, finished (batch, kv head) count
   long long max_spins;
+  unsigned* counters;  // [B*H]
 };
 
-struct CtaShared {
-  float gm[MAX_REP], gl[MAX_REP];  // global max / sum-exp of the pair's query heads
-  unsigned is_last;
-  unsigned bar_n;
-  unsigned pad_[2];
-};
-constexpr int CTA_HEAD_BYTES = 128;
-static_assert(sizeof(CtaShared) <= CTA_HEAD_BYTES, "CTA-shared block");
-// after it: q of the CTA's current pair, 4 (8) rows of Q_PITCH halfs
-__host__ __device__ constexpr int cta_shared_bytes(bool rep8) { return CTA_HEAD_BYTES + (rep8 ? 8 : 4) * Q_PITCH * 2; }
-// two CTAs per SM: 2 x (dynamic + 1 KB reserved) must fit the 228 KB of an SM
-static_assert(2 * (cta_shared_bytes(false) + NWARPS * ws_bytes(false) + 1024) <= 233472, "two CTAs per SM");
 
 // ------------------------------------------------------------------------------------------------
-// work lists
+// fragments
 // ------------------------------------------------------------------------------------------------
-// A pair's tiles of one side are ordered by tier, then tile; tile i of a tier starts at weight w0(tier) +
-// i * w(tier).  A tile belongs to the warp whose weight range holds its start weight.
-struct Cursor {
-  int tier, tile;
-  int s;  // start weight
-};
-template <bool K> __device__ __forceinline__ int t_tiles(const TierDev& T) { return K ? T.k_tiles : T.v_tiles; }
-template <bool K> __device__ __forceinline__ int t_w(const TierDev& T) { return K ? T.k_w : T.v_w; }
-template <bool K> __device__ __forceinline__ int t_w0(const TierDev& T) { return K ? T.k_w0 : T.v_w0; }
+__device__ __forceinline__ void mma16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
 
-// first tile whose start weight is >= a (s = the side's total weight if there is none)
-template <bool K>
-__device__ __noinline__ Cursor cursor_at(const DecodeParams& P, int a) {
-  Cursor c;
-  c.tier = NUM_ITEM_TIERS;
-  c.tile = 0;
-  c.s = K ? P.wk : P.wv;
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 h) { return *reinterpret_cast<uint32_t*>(&h); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t u) { return *reinterpret_cast<__half2*>(&u); }
+
+// Streaming loads: the cache is read once per call, keep it out of L1.
+__device__ __forceinline__ uint2 ld_stream(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Storage formats.  A "word" is what one thread loads for one (row, column) slot; it holds FPI
+// values of one row.  SUB = independently decoded sub-units of a word (bytes of a packed word,
+// 32-bit lanes of a uint4 of halfs), CPS = values per sub-unit.
+template <int BITS>
+struct Fmt;
+template <>
+struct Fmt<16> {
+  using word_t = uint4;  // eight halfs
+  static constexpr int FPI = 8, SUB = 4, CPS = 2;
+};
+
+// Decode sub-unit `sub` of the words wa (first row of the pair) and wb (second row) into CPS
+// half2 values (value of row a in the low half, row b in the high half): v = code*scale + zero
+// with one fp16 rounding; `sz` packs the scales of the two rows, `zz` their zeros.
+template <int BITS>
+struct Decode;
+
+template <>
+struct Decode<16> {
+  template <int SUBI>
+  static __device__ __forceinline__ void run(const uint4& wa, const uint4& wb, __half2, __half2, uint32_t (&out)[2]) {
+    const uint32_t a = SUBI == 0 ? wa.x : SUBI == 1 ? wa.y : SUBI == 2 ? wa.z : wa.w;
+    const uint32_t b = SUBI == 0 ? wb.x : SUBI == 1 ? wb.y : SUBI == 2 ? wb.z : wb.w;
+    out[0] = __byte_perm(a, b, 0x5410);
+    out[1] = __byte_perm(a, b, 0x7632);
+  }
+};
+
+// One 16-deep contraction step over all M-tiles of a thread's slots.
+//   w[p][r]: word of row-pair member p (0,1 -> fragment columns 2tig,2tig+1; 2,3 -> +8,+9) and row
+//            slot r (0 -> fragment row g, 1 -> row g+8)
+//   sz/zz[q][r]: scales/zeros of pair q (0: p=0,1; 1: p=2,3) for slot r
+// M-tile index of sub-unit s, value k: s*CPS + k.
+template <int BITS, int SUBI, int NM>
+__device__ __forceinline__ void mma_sub(float (&acc)[NM][4], const typename Fmt<BITS>::word_t (&w)[4][2],
+                                        const __half2 (&sz)[2][2], const __half2 (&zz)[2][2], uint32_t b0,
+                                        uint32_t b1) {
+  constexpr int CPS = Fmt<BITS>::CPS;
+  uint32_t a0[CPS], a1[CPS], a2[CPS], a3[CPS];
+  Decode<BITS>::template run<SUBI>(w[0][0], w[1][0], sz[0][0], zz[0][0], a0);
+  Decode<BITS>::template run<SUBI>(w[0][1], w[1][1], sz[0][1], zz[0][1], a1);
+  Decode<BITS>::template run<SUBI>(w[2][0], w[3][0], sz[1][0], zz[1][0], a2);
+  Decode<BITS>::template run<SUBI>(w[2][1], w[3][1], sz[1][1], zz[1][1], a3);
+#pragma unroll
+  for (int k = 0; k < CPS; ++k) mma16816(acc[SUBI * CPS + k], a0[k], a1[k], a2[k], a3[k], b0, b1);
+}
+
+template <int BITS, int NM>
+__device__ __forceinline__ void mma_words(float (&acc)[NM][4], const typename Fmt<BITS>::word_t (&w)[4][2],
+                                          const __half2 (&sz)[2][2], const __half2 (&zz)[2][2], uint32_t b0,
+                                          uint32_t b1) {
+  constexpr int SUB = Fmt<BITS>::SUB;
+  mma_sub<BITS, 0, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 1, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 2, NM>(acc, w, sz, zz, b0, b1);
+  mma_sub<BITS, 3, NM>(acc, w, sz, zz, b0, b1);
+  if constexpr (SUB == 8) {
+    mma_sub<BITS, 4, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 5, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 6, NM>(acc, w, sz, zz, b0, b1);
+    mma_sub<BITS, 7, NM>(acc, w, sz, zz, b0, b1);
+  }
+}
+
+// 2^x on the special-function unit (about 2 ulp; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, float l2) {
+  const float mx = fmaxf(m, m2);
+  if (mx == -INFINITY) return;  // both empty
+  l = l * fast_exp2((m - mx) * 1.4426950408889634f) + l2 * fast_exp2((m2 - mx) * 1.4426950408889634f);
+  m = mx;
+}
+
+
+// ------------------------------------------------------------------------------------------------
+// k_pass
+// ------------------------------------------------------------------------------------------------
+// Quantised K tier: rows = channels, packed words along tokens.  Every warp of a CTA owns one TILE:
+// all 128 channel rows x 64 bytes of codes (32 bytes at 2 bits), i.e. 64 / 128 / 128 tokens at
+// 8 / 4 / 2 bits, plus the tile's logical positions; the CTA shares the scale / zero rows of its 256
+// or 512 tokens and q.  All of it is copied global -> shared with 16-byte cp.async as the first
+// action (no registers are tied up, ~45 KB per CTA are in flight at once) and each warp then works
+// out of shared memory in sub-spans of 64 tokens.  Wide copies in, ldmatrix out: the L1 data pipe
+// moves 128 bytes per wavefront both ways.  (Per-lane loads of the 1-4 bytes a thread needs - from
+// global or from shared memory - saturate that pipe at a quarter of the HBM bandwidth.)
+//
+// ldmatrix.trans over 8 channel rows x 16 bytes hands lane (g, tig) the 16-bit block g of channels
+// 2*tig and 2*tig+1 in one register: exactly the two K-neighbours of an m16n8k16 A fragment for the
+// tokens of block g (2 / 4 / 8 tokens at 8 / 4 / 2 bits).  What keeps the instruction count low:
+//  * the integer codes enter the tensor pipe as they are: a masked field at bit k < 10 of a 16-bit
+//    lane IS the fp16 subnormal code * 2^(k-24), exactly, so one AND per pair of codes builds an A
+//    fragment register; the power of two comes back out in the epilogue;
+//  * the scale lives in the B operand: logit = sum_c (q_c * scale_c) * code_c + sum_c q_c * zero_c.
+//    A sub-span holds two 32-token scale groups; B columns 0-3 hold q*scale of the first group for
+//    four query heads and columns 4-7 that of the second, and each fragment row keeps the half of
+//    its accumulators whose group matches.  With eight query heads per kv head the warp walks its
+//    tile once per half of the heads;
+//  * q*scale (11 x 11 significant bits) is carried EXACTLY as hi = fp16(q*scale) and
+//    lo = q*scale - hi, two MMAs into the same fp32 accumulator.  (One fp16 rounding of it - or of
+//    the dequantised K value - costs ~2e-3 on the attention output with x10 outlier channels.)
+//  * the zero point enters through Zq[group][head] = sum_c zero_c * q_c, one small MMA per tile;
+//  * every lane scatters its own logits from registers and keeps a running (max, sum-exp).
+#ifndef K_MIN_CTAS
+#define K_MIN_CTAS 4
+#endif
+#ifndef K_KK_UNROLL
+#define K_KK_UNROLL 1  // iterations of the two-step loop unrolled together
+#endif
+constexpr int KWARPS = 4;
+constexpr int KTHREADS = KWARPS * 32;
+constexpr int K_SPAN = 64;                   // tokens per sub-span: four M-tiles of 16
+constexpr int K_SLOT = 4;                    // fp16 tier: tokens per 8-byte slot
+constexpr int K_TILE_BYTES = D * 64;         // codes of one tile
+constexpr int K_MAX_TT = 128;                // tokens per tile at most
+constexpr int K_CHUNK_GROUPS = KWARPS * K_MAX_TT / 32;  // scale groups per CTA at most (group size 32)
+constexpr int K_RAW_HALFS = K_CHUNK_GROUPS + 8;         // staged halfs per channel row: three aligned 16-byte pieces
+constexpr int K_TROW = MAX_REP + 1;          // floats per token row of the logit tile (odd: no bank conflicts)
+constexpr float LOG2E = 1.4426950408889634f;
+
+template <int BITS>
+struct KTile {
+  static constexpr int PITCH = BITS == 1 ? 16 : BITS == 2 ? 32 : 64;  // bytes per channel row
+  static constexpr int TOKENS = PITCH * 8 / BITS;         // 64, 128, 128, 128 at 8, 4, 2, 1 bits
+  static constexpr int NSUB = TOKENS / K_SPAN;            // sub-spans: 1, 2, 2, 2
+  static constexpr int TPC = 128 / BITS;                  // tokens per 16-byte piece: 16, 32, 64, 128
+  static constexpr int CPS = BITS == 1 ? 1 : K_SPAN / TPC;  // pieces of a row per sub-span: 4, 2, 1 (1 bit: half a piece)
+  // byte offset of 16-byte piece c of a channel row.  The piece index is XORed with row bits so that
+  // the eight rows of an ldmatrix (same logical piece) and the pieces a cp.async instruction writes
+  // both spread over all banks.
+  static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
+    if constexpr (PITCH == 64) {
+      return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
+    } else if constexpr (PITCH == 32) {
+      return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    } else {
+      return row * 16u;  // 1 bit: read with 2-byte loads, see k_tile_compute
+    }
+  }
+};
+
+// global -> shared copies without a register round trip; completion = wait_group + barrier
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
+__device__ __forceinline__ void cp_async_8(void* dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
+__device__ __forceinline__ void cp_async_16(void* dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(dst))),
+               "l"(src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// four 8x8 matrices of 16-bit elements, transposed: lane (g, tig) gets elements (row 2*tig, col g) and
+// (row 2*tig+1, col g) of matrix i in r[i]; lanes 8*i .. 8*i+7 supply the row addresses of matrix i
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* row_ptr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(static_cast<uint32_t>(__cvta_generic_to_shared(row_ptr))));
+}
+
+struct KWarpShared {
+  union {
+    unsigned char codes[K_TILE_BYTES];
+    float tile[64 * K_TROW];  // fp16 tier / residual: logits [token][head]
+  } u;
+  int64_t idx[K_MAX_TT];      // logical positions of the tile's tokens
+  float zq[4][MAX_REP];       // sum_c zero*q per group of the tile and head
+};
+
+struct KShared {
+  // B fragments of q per 16-channel step and lane: channels 16*kt + 2*tig + (0,1 | 8,9).  fp16 tier /
+  // residual CTAs: [0] with column n = head n.  Quantised CTAs: [hh] with column n = head
+  // 4*hh + (n & 3) (columns 4-7 repeat 0-3).
+  uint2 qb[2][8][32];
+  // scale / zero rows of the CTA's tokens as they lie in memory: channel c, three aligned 16-byte
+  // pieces starting at or before the chunk's first group
+  __half s[D][K_RAW_HALFS];
+  __half z[D][K_RAW_HALFS];
+  float red_m[KWARPS][MAX_REP], red_l[KWARPS][MAX_REP];
+  KWarpShared w[KWARPS];
+};
+
+// Request the scale / zero rows of the CTA's chunk: thread t copies channel t.  The chunk's groups
+// [g0c, g0c + ngc) of a channel are 2*ngc bytes at any 2-byte alignment; the (up to) three aligned
+// 16-byte pieces that cover them go to shared memory as they are, so group gamma of channel c is
+// half ((c*G + g0c) & 7) + gamma of row c.  (The planes hold B*H*128*G halfs, a multiple of 8, and
+// start 16-byte aligned, so every aligned piece that begins inside a plane also ends inside it.)
+__device__ __forceinline__ void k_scales_request(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int g0c,
+                                                 int ngc) {
+  const int ch = threadIdx.x;  // KTHREADS == D
+  const int G = T.n_k >> P.gk_shift;
+  const int64_t e0 = (static_cast<int64_t>(bh) * D + ch) * G + g0c;
+  const int64_t a = e0 & ~static_cast<int64_t>(7);
+#pragma unroll
+  for (int p = 0; p < K_RAW_HALFS / 8; ++p)
+    if (a + 8 * p < e0 + ngc) {
+      cp_async_16(&sh.s[ch][8 * p], T.k_scale + a + 8 * p);
+      cp_async_16(&sh.z[ch][8 * p], T.k_zero + a + 8 * p);
+    }
+}
+static_assert(KTHREADS == D, "one thread per channel row");
+
+// Request a tile: four commit groups, the codes of channel rows 0-31 (with the positions), 32-63,
+// 64-95, 96-127 (two 16-channel steps each).  ntok = valid tokens of the tile (a multiple of 32).
+template <int BITS>
+__device__ __forceinline__ void k_tile_request(const TierDev& T, KWarpShared& ws, int bh, int tile_t0, int ntok) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31;
+  const int n = T.n_k;
+#pragma unroll
+  for (int j = 0; j < TL::TOKENS / 32; ++j) {
+    const int t = lane + 32 * j;
+    if (t < ntok) cp_async_8(&ws.idx[t], T.k_idx + tile_t0 + t);
+  }
+  const int64_t row_bytes = static_cast<int64_t>(n) * BITS / 8;
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.k_data) + static_cast<int64_t>(bh) * D * row_bytes +
+                             static_cast<int64_t>(tile_t0) * BITS / 8;
+  const int valid_bytes = ntok * BITS / 8;  // per row: a multiple of 8 (of 4 at 1 bit)
+  if constexpr (BITS == 1) {
+    // 16 bytes per row at 4-byte alignment: four 4-byte pieces; a copy instruction moves 8 rows
+#pragma unroll
+    for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int row = quarter * 32 + i * 8 + (lane >> 2), c4 = 4 * (lane & 3);
+        if (c4 < valid_bytes) cp_async_4(ws.u.codes + row * 16 + c4, src + row * row_bytes + c4);
+      }
+      cp_async_commit();
+    }
+    return;
+  }
+  // a copy instruction moves 8 rows x 64 bytes (16 rows x 32 bytes at 2 bits)
+  constexpr int LPR = BITS == 2 ? 2 : 4;    // lanes per row
+  constexpr int RPI = 32 / LPR;             // rows per instruction
+  const int c = lane % LPR, r0 = lane / LPR;
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int i = 0; i < 32 / RPI; ++i) {
+      const int row = quarter * 32 + i * RPI + r0;
+      const unsigned char* s = src + row * row_bytes + 16 * c;
+      unsigned char* d = ws.u.codes + TL::offset(row, c);
+      if constexpr (BITS == 2) {  // rows of 2-bit codes are only 8-byte aligned in memory
+        if (16 * c < valid_bytes) cp_async_8(d, s);
+        if (16 * c + 8 < valid_bytes) cp_async_8(d + 8, s + 8);
+      } else {
+        if (16 * c < valid_bytes) cp_async_16(d, s);
+      }
+    }
+    cp_async_commit();
+  }
+}
+
+// 16-bit halves of two words -> one half2 register (low half from a)
+__device__ __forceinline__ uint32_t pack_lo16(uint32_t a, uint32_t b) { return __byte_perm(a, b, 0x5410); }
+
+// Zq[group][head] of the tile for half hh of the heads: rows of the A operand are the tile's groups
+// (at most four; rows 4-7 repeat them, rows 8-15 are zero).  zrow: this lane's two staged zero rows
+// (channels 2*tig and 2*tig+1) at the half of the tile's first group.
+// Gaussian-codebook tier (s_even / s_odd non-null: the std rows at the same halves): a value is
+// std * C * (2 code - 1) + mean, so the term that does not depend on the code is sum_c (mean - C std) q.
+__device__ __forceinline__ void k_tile_zq(KShared& sh, KWarpShared& ws, int hh, const __half* z_even, const __half* z_odd,
+                                          const __half* s_even = nullptr, const __half* s_odd = nullptr) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int gam = g & 3;
+  float zacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+  for (int kt = 0; kt < 8; ++kt) {
+    const int o = (16 * kt) * K_RAW_HALFS + gam;
+    const uint32_t a0 = pack_lo16(__half_as_ushort(z_even[o]), __half_as_ushort(z_odd[o]));
+    const uint32_t a2 = pack_lo16(__half_as_ushort(z_even[o + 8 * K_RAW_HALFS]), __half_as_ushort(z_odd[o + 8 * K_RAW_HALFS]));
+    const uint2 bq = sh.qb[hh][kt][lane];
+    mma16816(zacc, a0, 0u, a2, 0u, bq.x, bq.y);
+  }
+  if (s_even) {
+    float sacc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 2
+    for (int kt = 0; kt < 8; ++kt) {
+      const int o = (16 * kt) * K_RAW_HALFS + gam;
+      const uint32_t a0 = pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]), __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS]));
+      const uint2 bq = sh.qb[hh][kt][lane];
+      mma16816(sacc, a0, 0u, a2, 0u, bq.x, bq.y);
+    }
+    zacc[0] = fmaf(-HQKV_NORMAL1_CENTER, sacc[0], zacc[0]);
+    zacc[1] = fmaf(-HQKV_NORMAL1_CENTER, sacc[1], zacc[1]);
+  }
+  __syncwarp();  // readers of the previous half are done
+  if (g < 4 && tig < 2) {  // columns 0-3 are the four heads of this half; 4-7 repeat them
+    ws.zq[g][2 * tig] = zacc[0];
+    ws.zq[g][2 * tig + 1] = zacc[1];
+  }
+  __syncwarp();
+}
+
+// A fragment registers of the four M-tiles of a sub-span from the ldmatrix registers of one 8-channel
+// octet.  R[c]: 16-byte piece c of the sub-span; each 16-bit half = block g of one channel.
+// lo[i] -> fragment row g of M-tile i, hi[i] -> row g+8.  Fields are fp16 subnormals code * 2^(k-24);
+// KField<BITS>::shift(i) gives k of M-tile i.
+//   8 bits: block = 2 tokens.  M-tile i = (piece p = i>>1, token e = i&1): row g <- piece p, row g+8 <-
+//           piece p+2.  Tokens: row g = 16p + 2g + e, row g+8 = 32 + 16p + 2g + e.
+//   4 bits: block = 4 tokens.  M-tile i: row g <- piece 0 token i, row g+8 <- piece 1 token i.
+//           Tokens: row g = 4g + i, row g+8 = 32 + 4g + i.
+//   2 bits: block = 8 tokens, one piece.  M-tile i: row g <- token i, row g+8 <- token 4+i of block g.
+//           Tokens: row g = 8g + i, row g+8 = 8g + 4 + i.
+//   1 bit:  block = 16 tokens, four blocks per sub-span (no ldmatrix: lane g reads block g & 3 with a
+//           2-byte load).  M-tile i: row g <- token 4*(g>>2) + i, row g+8 <- token 8 + 4*(g>>2) + i of
+//           block g & 3.  Tokens: row g = 16*(g&3) + 4*(g>>2) + i, row g+8 = +8.
+template <int BITS>
+struct KField {
+  static __host__ __device__ constexpr int shift(int i) {
+    return BITS == 8 ? 0 : BITS == 4 ? 4 * (i & 1) : BITS == 2 ? 2 * i : i;
+  }
+};
+template <int BITS>
+__device__ __forceinline__ void octet_frags(const uint32_t* R, uint32_t (&lo)[4], uint32_t (&hi)[4]) {
+  if constexpr (BITS == 8) {
+#pragma unroll
+    for (int p = 0; p < 2; ++p) {
+      lo[2 * p] = R[p] & 0x00FF00FFu;
+      lo[2 * p + 1] = __byte_perm(R[p], 0u, 0x4341);
+      hi[2 * p] = R[p + 2] & 0x00FF00FFu;
+      hi[2 * p + 1] = __byte_perm(R[p + 2], 0u, 0x4341);
+    }
+  } else if constexpr (BITS == 4) {
+    const uint32_t a = R[0], as = R[0] >> 8, b = R[1], bs = R[1] >> 8;
+    lo[0] = a & 0x000F000Fu;
+    lo[1] = a & 0x00F000F0u;
+    lo[2] = as & 0x000F000Fu;
+    lo[3] = as & 0x00F000F0u;
+    hi[0] = b & 0x000F000Fu;
+    hi[1] = b & 0x00F000F0u;
+    hi[2] = bs & 0x000F000Fu;
+    hi[3] = bs & 0x00F000F0u;
+  } else {
+    const uint32_t a = R[0], as = R[0] >> 8;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      lo[i] = a & (0x00030003u << (2 * i));
+      hi[i] = as & (0x00030003u << (2 * i));
+    }
+  }
+}
+
+// running (max, sum-exp) of a lane over values it produces four at a time; -inf marks "no value"
+__device__ __forceinline__ void softmax_push4(float& m, float& l, const float (&x)[4]) {
+  const float mn = fmaxf(fmaxf(m, fmaxf(x[0], x[1])), fmaxf(x[2], x[3]));
+  const float ref = (mn == -INFINITY ? 0.f : mn) * LOG2E;
+  l = l * fast_exp2(fmaf(m, LOG2E, -ref)) + (fast_exp2(fmaf(x[0], LOG2E, -ref)) + fast_exp2(fmaf(x[1], LOG2E, -ref))) +
+      (fast_exp2(fmaf(x[2], LOG2E, -ref)) + fast_exp2(fmaf(x[3], LOG2E, -ref)));
+  m = mn;
+}
+
+// One tile of a quantised tier, already requested: all heads of this kv head.
+// g0c = first scale group of the CTA's chunk.  m/l: this lane's running softmax pairs, [hh][e] for
+// head 4*hh + 2*(tig&1) + e.
+template <int BITS>
+__device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const TierDev& T, KShared& sh, KWarpShared& ws,
+                                               int tile_t0, int ntok, int g0c, int nh, float* row0, const __half* mask0,
+                                               float (&m)[2][2], float (&l)[2][2]) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int G = T.n_k >> P.gk_shift;
+  // staged scale / zero rows of this lane's channels 2*tig (even) and 2*tig+1 (odd) of step 0, at the
+  // half of the chunk's first group; a step adds 16 rows, the +8 channels add 8 rows
+  const int sh_even = static_cast<int>((static_cast<int64_t>(2 * tig) * G + g0c) & 7);
+  const int sh_odd = static_cast<int>((static_cast<int64_t>(2 * tig + 1) * G + g0c) & 7);
+  const int gt0 = (tile_t0 >> P.gk_shift) - g0c;  // first group of the tile within the chunk
+  // ldmatrix row address of this lane for step 0 / sub-span 0 (see the loop for the matrix order)
+  uint32_t lm_off;
+  {
+    const int mi = lane >> 3, rr = lane & 7;
+    if constexpr (BITS == 8) {
+      lm_off = TL::offset(rr, mi);                           // octet 0; pieces 0..3
+    } else if constexpr (BITS == 4) {
+      lm_off = TL::offset(8 * (mi >> 1) + rr, mi & 1);       // (octet 0, piece 0), (0,1), (1,0), (1,1)
+    } else if constexpr (BITS == 2) {
+      lm_off = TL::offset(8 * mi + rr, 0);                   // steps kt, kt+1: octets 0..3 of 32 channels
+    } else {
+      lm_off = (2 * tig) * 16 + 2 * (g & 3);                 // 1 bit: this lane's block of channel 2*tig
+    }
+  }
+  const int hp = tig & 1;
+  // Gaussian-codebook 1-bit tier: the code term carries the factor 2C
+  const bool normal = BITS == 1 && T.normal != 0;
+  const float pscale = normal ? P.scale * (2.f * HQKV_NORMAL1_CENTER) : P.scale;
+
+  for (int hh = 0; hh < nh; ++hh) {
+    if (normal)
+      k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0], &sh.s[2 * tig][sh_even + gt0],
+                &sh.s[2 * tig + 1][sh_odd + gt0]);
+    else
+      k_tile_zq(sh, ws, hh, &sh.z[2 * tig][sh_even + gt0], &sh.z[2 * tig + 1][sh_odd + gt0]);
+    const uint2* qb = &sh.qb[hh][0][lane];
 #pragma unroll 1
-  for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
-    const TierDev& T = P.tier[t];
-    const int n = t_tiles<K>(T), w = t_w<K>(T), w0 = t_w0<K>(T);
-    if (n > 0 && c.tier == NUM_ITEM_TIERS) {
-      const int d = a - w0;  // weights are 1, 3 or 4 in practice: no general integer division for those
-      const int tile = d <= 0 ? 0 : (w == 4 ? (d + 3) >> 2 : w == 3 ? (d + 2) / 3 : w == 1 ? d : (d + w - 1) / w);
-      if (tile < n) {
-        c.tier = t;
-        c.tile = tile;
-        c.s = w0 + tile * w;
+    for (int j = 0; j < TL::NSUB; ++j) {
+      // as a B column this lane is n = g: columns 0-3 carry the scale group of tokens 0-31 of the
+      // sub-span, columns 4-7 that of tokens 32-63
+      const int gam = ((tile_t0 + j * K_SPAN + 32 * (g >> 2)) >> P.gk_shift) - g0c;
+      const __half* s_even = &sh.s[2 * tig][sh_even + gam];
+      const __half* s_odd = &sh.s[2 * tig + 1][sh_odd + gam];
+      const unsigned char* kb = ws.u.codes + (BITS == 1 ? lm_off + j * 8 : (lm_off ^ (j * TL::CPS * 16)));
+      const uint2* qk = qb;
+      float acc[4][4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+      // two 16-channel steps per iteration (short loop body: the instruction cache is cold in every CTA
+      // when the whole cache is one wave of CTAs)
+HQKV_UNROLL(K_KK_UNROLL)
+      for (int kk = 0; kk < 4; ++kk) {
+        if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
+          if (kk == 0) cp_async_wait<3>();
+          else if (kk == 1) cp_async_wait<2>();
+          else if (kk == 2) cp_async_wait<1>();
+          else cp_async_wait<0>();
+          __syncwarp();
+        }
+        uint32_t R2[4];  // 2 bits: one ldmatrix feeds both steps
+        if constexpr (BITS == 2) ldmatrix_x4_trans(R2, kb);
+        (void)R2;
+#pragma unroll
+        for (int k2 = 0; k2 < 2; ++k2) {
+          // A fragments: lo/hi of octet 0 -> registers 0/1 (channels 2tig, 2tig+1), of octet 1 -> 2/3 (+8)
+          uint32_t a[4][4];  // [register][M-tile]
+          if constexpr (BITS == 8) {
+            uint32_t R[4];
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH);
+            octet_frags<8>(R, a[0], a[1]);
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH + 8 * TL::PITCH);
+            octet_frags<8>(R, a[2], a[3]);
+          } else if constexpr (BITS == 4) {
+            uint32_t R[4];
+            ldmatrix_x4_trans(R, kb + k2 * 16 * TL::PITCH);
+            octet_frags<4>(R, a[0], a[1]);
+            octet_frags<4>(R + 2, a[2], a[3]);
+          } else if constexpr (BITS == 2) {
+            octet_frags<2>(R2 + 2 * k2, a[0], a[1]);
+            octet_frags<2>(R2 + 2 * k2 + 1, a[2], a[3]);
+          } else {
+#pragma unroll
+            for (int o = 0; o < 2; ++o) {  // channels 2tig, 2tig+1 (o = 0) and +8, +9 (o = 1)
+              const unsigned char* cb = kb + (k2 * 16 + o * 8) * 16;
+              const uint32_t t = pack_lo16(*reinterpret_cast<const uint16_t*>(cb), *reinterpret_cast<const uint16_t*>(cb + 16));
+              const uint32_t lo = t >> (4 * (g >> 2)), hi = lo >> 8;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                a[2 * o][i] = lo & (0x00010001u << i);
+                a[2 * o + 1][i] = hi & (0x00010001u << i);
+              }
+            }
+          }
+          const int o = (16 * k2) * K_RAW_HALFS;
+          const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o]), __half_as_ushort(s_odd[o])));
+          const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(s_even[o + 8 * K_RAW_HALFS]),
+                                                 __half_as_ushort(s_odd[o + 8 * K_RAW_HALFS])));
+          const uint2 qv = qk[k2 * 32];
+          const __half2 hi0 = __hmul2(u32_as_h2(qv.x), s0);
+          const __half2 hi1 = __hmul2(u32_as_h2(qv.y), s1);
+          const __half2 lo0 = __hfma2(u32_as_h2(qv.x), s0, __hneg2(hi0));  // exact remainder
+          const __half2 lo1 = __hfma2(u32_as_h2(qv.y), s1, __hneg2(hi1));
+          // the two MMAs into one accumulator are issued four apart (they depend on each other)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(hi0), h2_as_u32(hi1));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mma16816(acc[i], a[0][i], a[1][i], a[2][i], a[3][i], h2_as_u32(lo0), h2_as_u32(lo1));
+        }
+        kb += 32 * TL::PITCH;
+        s_even += 32 * K_RAW_HALFS;
+        s_odd += 32 * K_RAW_HALFS;
+        qk += 64;
+      }
+      // Epilogue from registers: a lane keeps the accumulator columns whose scale group is its row's, and
+      // every lane ends up with four tokens x two heads (heads 2*(tig&1), +1).
+      //  8 / 4 bits: rows 0-7 are tokens 0-31, rows 8-15 tokens 32-63: lanes tig 0,1 own row g, lanes
+      //              tig 2,3 own row g+8.
+      //  2 bits:     rows g and g+8 are the eight tokens of block g, valid in the lanes with
+      //              (g < 4) == (tig < 2); such a lane keeps the row of its tig half and hands the
+      //              other row to lane tig ^ 2, whose own accumulators belong to the wrong scale group.
+      //  1 bit:      the same with block g & 3: valid where ((g & 3) < 2) == (tig < 2).
+      const int sub_t0 = j * K_SPAN;
+      const int r = tig >> 1;
+      float val[4][2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) val[i][e] = r ? acc[i][2 + e] : acc[i][e];
+      if constexpr (BITS <= 2) {
+        const bool valid = BITS == 2 ? (g < 4) == (tig < 2) : ((g & 3) < 2) == (tig < 2);
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const float other = __shfl_xor_sync(0xffffffffu, r ? acc[i][e] : acc[i][2 + e], 2);
+            if (!valid) val[i][e] = other;
+          }
+      }
+      // first of this lane's tokens (8 bits: tokens my_tok, +1, +16, +17; 4 and 2 bits: my_tok .. my_tok+3)
+      const int my_tok = sub_t0 + (BITS == 8 ? 32 * r + 2 * g : BITS == 4 ? 32 * r + 4 * g : BITS == 2 ? 8 * g + 4 * r
+                                                                : 16 * (g & 3) + 4 * (g >> 2) + 8 * r);
+      const bool live = my_tok < ntok;
+      const int my_gam = ((tile_t0 + my_tok) >> P.gk_shift) - g0c - gt0;
+      uint32_t pos[4];
+      if constexpr (BITS == 8) {
+        const int4 pa = *reinterpret_cast<const int4*>(&ws.idx[my_tok]);  // low words of int64 positions: .x and .z
+        const int4 pb = *reinterpret_cast<const int4*>(&ws.idx[my_tok + 16]);
+        pos[0] = static_cast<uint32_t>(pa.x), pos[1] = static_cast<uint32_t>(pa.z);
+        pos[2] = static_cast<uint32_t>(pb.x), pos[3] = static_cast<uint32_t>(pb.z);
+      } else {
+        const int4* ip = reinterpret_cast<const int4*>(&ws.idx[my_tok]);
+        const int4 p01 = ip[0], p23 = ip[1];
+        pos[0] = static_cast<uint32_t>(p01.x), pos[1] = static_cast<uint32_t>(p01.z);
+        pos[2] = static_cast<uint32_t>(p23.x), pos[3] = static_cast<uint32_t>(p23.z);
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int head = 4 * hh + 2 * hp + e;
+        const bool on = live && head < P.rep;
+        const float zqs = ws.zq[my_gam & 3][2 * hp + e] * P.scale;
+        float* row = row0 + static_cast<int64_t>(head) * P.L;
+        const __half* mrow = mask0 ? mask0 + head * P.mask_hstride : nullptr;
+        float x[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
+          const bool ok = on && HQKV_INDEX_OK(pos[i], P.L);
+          x[i] = ok ? fmaf(val[i][e], pscale * unscale, zqs) : -INFINITY;
+          if (ok) {
+            if (mrow) x[i] += __half2float(mrow[pos[i]]);
+            row[pos[i]] = x[i];
+          }
+        }
+        softmax_push4(m[hh][e], l[hh][e], x);
       }
     }
   }
-  return c;
 }
-template <bool K>
-__device__ __forceinline__ void cursor_next(const DecodeParams& P, Cursor& c) {
-  if (++c.tile >= t_tiles<K>(P.tier[c.tier])) {
-    c.tile = 0;
-    do {
-      ++c.tier;
-    } while (c.tier < NUM_ITEM_TIERS && t_tiles<K>(P.tier[c.tier]) == 0);
+// Write out a warp's logit tile [ntok][K_TROW] (already scaled) at the tokens' logical positions and
+// leave the warp's (max, sum-exp) per head in red_m / red_l.  Element = (token, head) with the head
+// fastest across lanes, so every lane owns ONE head for the whole call (rep divides 32): its running
+// max and sum are scalars, and index loads and stores are spread over all 32 lanes.
+// (fp16 tier and residual window only; the quantised tiers write from registers.)
+__device__ __forceinline__ void k_write_tile(const DecodeParams& P, float* tile, int ntok, const int64_t* idx,
+                                             int64_t first_pos, int b, int kvh, float* red_m, float* red_l) {
+  const int lane = threadIdx.x & 31;
+  const int rep = P.rep, rshift = P.rep_shift;
+  const int h = lane & (rep - 1);
+  float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+  const __half* mrow = P.mask ? P.mask + b * P.mask_bstride + static_cast<int64_t>(kvh * rep + h) * P.mask_hstride : nullptr;
+  const int tpr = 32 >> rshift;  // tokens per round
+  float mx = -INFINITY;
+#pragma unroll 2
+  for (int t = lane >> rshift; t < ntok; t += tpr) {
+    const int64_t pos = idx ? idx[t] : first_pos + t;
+    float x = -INFINITY;
+    if (HQKV_INDEX_OK(pos, P.L)) {
+      x = tile[t * K_TROW + h];
+      if (mrow) x += __half2float(mrow[pos]);
+      row[pos] = x;
+    }
+    tile[t * K_TROW + h] = x;  // the masked value is what the sum below sees
+    mx = fmaxf(mx, x);
   }
-  c.s = c.tier < NUM_ITEM_TIERS ? t_w0<K>(P.tier[c.tier]) + c.tile * t_w<K>(P.tier[c.tier]) : (K ? P.wk : P.wv);
+  for (int off = rep; off < 32; off <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+  const float ref = mx == -INFINITY ? 0.f : mx;  // every position masked out: the sum is 0, not NaN
+  float sum = 0.f;
+#pragma unroll 2
+  for (int t = lane >> rshift; t < ntok; t += tpr) sum += fast_exp2((tile[t * K_TROW + h] - ref) * LOG2E);
+  for (int off = rep; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+  if (lane < rep) {
+    red_m[lane] = mx;
+    red_l[lane] = sum;
+  }
 }
 
-// (not inlined: called from several places, once per tile)
-__device__ __noinline__ void k_request(const DecodeParams& P, const Cursor c, int bh, unsigned char* wsm) {
-  if (c.tier >= HQKV_NUM_TIERS) return;
-  const TierDev& T = P.tier[c.tier];
-  if (T.bits == 16) return;  // fp16 tier: read straight from global memory
-  const int t0 = c.tile * T.k_tile_tokens;
-  k_tile_request(T, wsm, bh, t0, min(T.k_tile_tokens, T.n_k - t0), P.gk_shift);
-}
-__device__ __noinline__ uint4 v_request(const DecodeParams& P, const Cursor c, int bh, unsigned char* wsm) {
-  uint32_t pos[4] = {0u, 0u, 0u, 0u};
-  if (c.tier < HQKV_NUM_TIERS && P.tier[c.tier].bits < 16) {
-    const TierDev& T = P.tier[c.tier];
-    const int t0 = c.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
-    v_tile_positions(T, t0, ntok, pos);
-    v_tile_request(T, wsm, bh, t0, ntok, D >> P.gv_shift);
+
+// One tile per warp: request everything that depends only on the cache, wait for the kernels before
+// this one, fetch q, agree that q and the scale rows are in shared memory, compute.
+template <int BITS, typename LoadQ>
+__device__ __forceinline__ void k_chunk(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                        int chunk_t0, int nh, LoadQ load_q) {
+  using TL = KTile<BITS>;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  KWarpShared& ws = sh.w[warp];
+  const int chunk_end = min(chunk_t0 + KWARPS * TL::TOKENS, T.n_k);
+  const int g0c = chunk_t0 >> P.gk_shift;
+  const int ngc = ((chunk_end - 1) >> P.gk_shift) - g0c + 1;
+  k_scales_request(P, T, sh, bh, g0c, ngc);
+  cp_async_commit();  // oldest group: the scale / zero rows
+  const int tile_t0 = chunk_t0 + warp * TL::TOKENS;
+  const int ntok = min(TL::TOKENS, T.n_k - tile_t0);  // <= 0: this warp has no tile
+  if (ntok > 0) k_tile_request<BITS>(T, ws, bh, tile_t0, ntok);
+  // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
+  // the previous decode call of the stream may still be using: wait for the kernels before it.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  load_q();
+  if (ntok > 0) {
+    cp_async_wait<4>();
+  } else {
+    cp_async_wait<0>();
   }
-  return make_uint4(pos[0], pos[1], pos[2], pos[3]);
+  __syncthreads();
+  float m[2][2] = {{-INFINITY, -INFINITY}, {-INFINITY, -INFINITY}}, l[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  if (ntok > 0) {
+    float* row0 = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep) * P.L;
+    // additive mask rows of this kv head's query heads (null: none)
+    const __half* mask0 = P.mask ? P.mask + b * P.mask_bstride + static_cast<int64_t>(kvh * P.rep) * P.mask_hstride : nullptr;
+    k_tile_compute<BITS>(P, T, sh, ws, tile_t0, ntok, g0c, nh, row0, mask0, m, l);
+  }
+  // the warp's (max, sum-exp) per head: lanes that share tig & 1 hold pairs of the same two heads
+  for (int hh = 0; hh < nh; ++hh)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      float mx = m[hh][e];
+#pragma unroll
+      for (int o = 2; o < 32; o <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      float sum = l[hh][e] * fast_exp2((m[hh][e] - (mx == -INFINITY ? 0.f : mx)) * LOG2E);
+#pragma unroll
+      for (int o = 2; o < 32; o <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      if (lane < 2) {
+        sh.red_m[warp][4 * hh + 2 * lane + e] = mx;
+        sh.red_l[warp][4 * hh + 2 * lane + e] = sum;
+      }
+    }
+}
+
+// fp16 tier, channel-major rows [D][n]: four tokens per 8-byte slot, no scales; B = q exactly.
+__device__ __forceinline__ void k_f16_span(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b, int kvh,
+                                           int span_t0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+  const int n = T.n_k;
+  const int64_t nslot = n / K_SLOT;
+  const uint2* base = reinterpret_cast<const uint2*>(T.k_data) + static_cast<int64_t>(bh) * D * nslot;
+  int64_t sl[2];
+#pragma unroll
+  for (int r = 0; r < 2; ++r) sl[r] = min(static_cast<int64_t>(span_t0 / K_SLOT + r * 8 + g), nslot - 1);
+  float acc[K_SLOT][4];
+#pragma unroll
+  for (int i = 0; i < K_SLOT; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+#pragma unroll 2
+  for (int kt = 0; kt < 8; ++kt) {
+    uint2 w[4][2];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int ch = 16 * kt + 8 * (e >> 1) + 2 * tig + (e & 1);
+#pragma unroll
+      for (int r = 0; r < 2; ++r) w[e][r] = ld_stream(base + ch * nslot + sl[r]);
+    }
+    const uint2 bq = sh.qb[0][kt][lane];
+    // token i of a slot: halfs (x.lo, x.hi, y.lo, y.hi); pair the same token of two channel rows
+    uint32_t a[K_SLOT][4];
+#pragma unroll
+    for (int q = 0; q < 2; ++q)
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const uint2 wa = w[2 * q][r], wb = w[2 * q + 1][r];
+        a[0][q * 2 + r] = __byte_perm(wa.x, wb.x, 0x5410);
+        a[1][q * 2 + r] = __byte_perm(wa.x, wb.x, 0x7632);
+        a[2][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x5410);
+        a[3][q * 2 + r] = __byte_perm(wa.y, wb.y, 0x7632);
+      }
+#pragma unroll
+    for (int i = 0; i < K_SLOT; ++i) mma16816(acc[i], a[i][0], a[i][1], a[i][2], a[i][3], bq.x, bq.y);
+  }
+  float* tile = sh.w[warp].u.tile;
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int e = 0; e < 2; ++e)
+#pragma unroll
+      for (int i = 0; i < K_SLOT; ++i)
+        tile[((r * 8 + g) * K_SLOT + i) * K_TROW + 2 * tig + e] = acc[i][r * 2 + e] * P.scale;
+  __syncwarp();
+  k_write_tile(P, tile, min(K_SPAN, n - span_t0), T.k_idx + span_t0, 0, b, kvh, sh.red_m[warp], sh.red_l[warp]);
+}
+
+// fp16 residual window, token-major [r][D]: A fragments are read directly; one 16-token tile per warp.
+__device__ __forceinline__ void k_residual_tile(const DecodeParams& P, const TierDev& T, KShared& sh, int bh, int b,
+                                                int kvh, int tile_t0) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, tig = lane & 3;
+  const int n = T.n_k;
+  const __half* base = reinterpret_cast<const __half*>(T.k_data) + static_cast<int64_t>(bh) * n * D;
+  const int t[2] = {min(tile_t0 + g, n - 1), min(tile_t0 + g + 8, n - 1)};
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t a[8][4];
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+      const __half* p = base + static_cast<int64_t>(t[r]) * D + 16 * kt + 2 * tig;
+      a[kt][r] = *reinterpret_cast<const uint32_t*>(p);
+      a[kt][2 + r] = *reinterpret_cast<const uint32_t*>(p + 8);
+    }
+#pragma unroll
+  for (int kt = 0; kt < 8; ++kt) {
+    const uint2 bq = sh.qb[0][kt][lane];
+    mma16816(acc, a[kt][0], a[kt][1], a[kt][2], a[kt][3], bq.x, bq.y);
+  }
+  float* tile = sh.w[warp].u.tile;
+#pragma unroll
+  for (int r = 0; r < 2; ++r)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) tile[(r * 8 + g) * K_TROW + 2 * tig + e] = acc[r * 2 + e] * P.scale;
+  __syncwarp();
+  k_write_tile(P, tile, min(16, n - tile_t0), nullptr, static_cast<int64_t>(P.L) - n + tile_t0, b, kvh, sh.red_m[warp],
+               sh.red_l[warp]);
+}
+
+__global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __grid_constant__ DecodeParams P) {
+  extern __shared__ __align__(128) unsigned char k_smem[];
+  KShared& sh = *reinterpret_cast<KShared*>(k_smem);
+  const int chunk = blockIdx.y, bh = blockIdx.x;  // (batch, head) fastest: neighbouring CTAs run the same tier code
+  const int b = bh / P.H, kvh = bh - b * P.H;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, tig = lane & 3;
+
+  // Let the V pass of this call (launched with programmatic stream serialisation) start its own
+  // prologue - V words, index lists, scale/zero tiles - as soon as SM resources free up; it waits for
+  // this grid to finish (griddepcontrol.wait) before it touches the logits or the softmax pairs.
+  asm volatile("griddepcontrol.launch_dependents;");
+  if (tid < KWARPS * MAX_REP) {
+    (&sh.red_m[0][0])[tid] = -INFINITY;
+    (&sh.red_l[0][0])[tid] = 0.f;
+  }
+
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].k_chunk0 && chunk < P.tier[t + 1].k_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const int chunk_t0 = (chunk - T.k_chunk0) * T.k_chunk_tokens;
+  const bool plain = ti == HQKV_NUM_TIERS || T.bits == 16;
+
+  // B fragments of q: rows are channels 16*kt + 2*tig + (0,1 | 8,9), column n = g is a query head of
+  // this kv head (see KShared::qb); warp hh stores its half.  q is the only input that an earlier
+  // kernel of the stream may still be writing, so it is read after griddepcontrol.wait.
+  const int nh = (!plain && P.rep > 4) ? 2 : 1;
+  auto load_q = [&]() {
+    if (warp < nh) {
+      const int head = plain ? g : 4 * warp + (g & 3);
+      const __half* qh = P.q + (static_cast<int64_t>(b) * P.nh_q + kvh * P.rep + head) * D + 2 * tig;
+      uint2 qf[8];
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) {
+        qf[kt] = make_uint2(0u, 0u);
+        if (head < P.rep) {
+          qf[kt].x = *reinterpret_cast<const uint32_t*>(qh + 16 * kt);
+          qf[kt].y = *reinterpret_cast<const uint32_t*>(qh + 16 * kt + 8);
+        }
+      }
+#pragma unroll
+      for (int kt = 0; kt < 8; ++kt) sh.qb[warp][kt][lane] = qf[kt];
+    }
+  };
+
+  if (plain) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    load_q();
+    __syncthreads();
+    const int chunk_end = min(chunk_t0 + T.k_chunk_tokens, T.n_k);
+    if (ti == HQKV_NUM_TIERS) {
+      const int t0 = chunk_t0 + warp * 16;  // residual chunks are KWARPS * 16 tokens
+      if (t0 < chunk_end) k_residual_tile(P, T, sh, bh, b, kvh, t0);
+    } else {
+      const int t0 = chunk_t0 + warp * K_SPAN;
+      if (t0 < chunk_end) k_f16_span(P, T, sh, bh, b, kvh, t0);
+    }
+  } else if (T.bits == 8) {
+    k_chunk<8>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
+  } else if (T.bits == 4) {
+    k_chunk<4>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
+  } else if (T.bits == 2) {
+    k_chunk<2>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
+  } else {
+    k_chunk<1>(P, T, sh, bh, b, kvh, chunk_t0, nh, load_q);
+  }
+
+  // the output accumulators of this (batch, kv head) start from zero in every call (the V pass, which
+  // adds into them, starts after this grid has finished); both branches above have passed their
+  // griddepcontrol.wait, so the previous call is done with them
+  if (chunk == 0) {
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * P.rep * D;
+    for (int i = tid; i < P.rep * D; i += KTHREADS) accum[i] = 0.0;
+  }
+  // (max, sum) of this CTA per head from the warps' pairs
+  __syncthreads();
+  if (tid < MAX_REP) {
+    float m = sh.red_m[0][tid], l = sh.red_l[0][tid];
+    for (int w = 1; w < KWARPS; ++w) softmax_merge(m, l, sh.red_m[w][tid], sh.red_l[w][tid]);
+    P.k_part[(static_cast<int64_t>(bh) * P.nk_chunks + chunk) * MAX_REP + tid] = make_float2(m, l);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// v_pass
+// ------------------------------------------------------------------------------------------------
+// V tier, token-major rows of 128 channels.  Every warp of a CTA owns one TILE of consecutive tokens
+// (8 KB of codes at 8 / 4 bits = 64 / 128 tokens, 4 KB at 2 bits = 128 tokens) with their scales,
+// zeros and logical positions, all copied global -> shared with cp.async before anything else.
+// The contraction runs over tokens, 16 per step.  ldmatrix.trans over 8 token rows x 16 bytes hands
+// lane (g, tig) the 16-bit block g (2 / 4 / 8 channels) of tokens 2*tig and 2*tig+1 in one register:
+// the two K-neighbours of an m16n8k16 A fragment.  As in the K pass the codes enter the tensor pipe
+// as fp16 subnormals (one AND per pair of codes) and the scale - here per token and 32-channel
+// group - is folded into the B operand: out[h][c] = sum_t (p_t * scale_t,G) * code_t,c + sum_t p_t *
+// zero_t,G, with p*scale carried exactly as hi + lo and B columns 0-3 / 4-7 holding the two channel
+// groups of a 64-channel half.  The zero term is one small MMA per step (rows = groups).
+#ifndef V_MIN_CTAS
+#define V_MIN_CTAS 4
+#endif
+#ifndef V_STEP_UNROLL
+#define V_STEP_UNROLL 1  // 16-token steps unrolled together
+#endif
+constexpr int VWARPS = 4;
+constexpr int VTHREADS = VWARPS * 32;
+constexpr int V_MAX_TT = 128;                 // tokens per tile at most
+constexpr int V_PROW = V_MAX_TT + 8;          // halfs per staged probability row (pitch 68 words: rows 4 banks apart)
+
+template <int BITS>
+struct VTile {
+  static constexpr int PITCH = 16 * BITS;                  // bytes per token row: 128, 64, 32, 16
+  static constexpr int TOKENS = BITS == 8 ? 64 : 128;
+  static constexpr int STEPS = TOKENS / 16;
+  static constexpr int NPIECE = PITCH / 16;                // 16-byte pieces per row: 8, 4, 2, 1
+  static __device__ __forceinline__ uint32_t offset(uint32_t row, uint32_t c) {
+    if constexpr (PITCH == 128) {
+      return row * 128u + ((c ^ (row & 7u)) << 4);
+    } else if constexpr (PITCH == 64) {
+      return row * 64u + ((c ^ ((row >> 1) & 3u)) << 4);
+    } else if constexpr (PITCH == 32) {
+      return row * 32u + ((c ^ ((row >> 2) & 1u)) << 4);
+    } else {
+      return row * 16u;  // 1 bit: read with 2-byte loads
+    }
+  }
+};
+
+struct VWarpShared {
+  union {
+    unsigned char codes[8192];
+    float red[4][D];            // partial output of the last walk over the tile (heads of that half)
+  } u;
+  union {
+    struct {
+      int64_t pos[V_MAX_TT];    // logical positions of the tile's tokens
+      __half p[4][V_PROW];      // exp(logit - max) of heads 0-3
+    } a;
+    float red0[4][D];           // eight query heads per kv head: partial output of the first walk
+  } v;
+  __half p_hi[4][V_PROW];       // heads 4-7
+  __half s[V_MAX_TT * 4];       // scales as in memory: [token][group]
+  __half z[V_MAX_TT * 4];
+  float zt[4][MAX_REP];         // sum_t p*zero per channel group and head
+};
+static_assert(sizeof(float) * 4 * D <= sizeof(int64_t) * V_MAX_TT + sizeof(__half) * 4 * V_PROW, "red0 fits its union");
+
+struct VShared {
+  float gm[MAX_REP], gl[MAX_REP];          // global max / sum of this kv head's query heads
+  float wm[VWARPS][MAX_REP], wl[VWARPS][MAX_REP];
+  unsigned is_last;
+  unsigned pad_[3 + 12];
+  VWarpShared w[VWARPS];
+};
+
+// A fragment registers from one ldmatrix quad R[0..3] = sources of fragment registers a0..a3
+// (a0: row g, tokens 2tig,2tig+1; a1: row g+8; a2 / a3: the same rows, tokens +8).
+//   field f of a 16-bit block as the fp16 subnormal code * 2^(k-24); VField<BITS>::shift(f) gives k.
+template <int BITS>
+struct VField {
+  static constexpr int N = BITS == 8 ? 2 : 4;  // fields taken from one register per fragment row
+  static __host__ __device__ constexpr int shift(int f) {
+    return BITS == 8 ? 0 : BITS == 4 ? 4 * (f & 1) : BITS == 2 ? 2 * f : f;
+  }
+};
+template <int BITS>
+__device__ __forceinline__ uint32_t v_field(uint32_t r, uint32_t r_shr8, int f) {
+  if constexpr (BITS == 8) {
+    return f == 0 ? (r & 0x00FF00FFu) : __byte_perm(r, 0u, 0x4341);
+  } else if constexpr (BITS == 4) {
+    return (f < 2 ? r : r_shr8) & (0x000F000Fu << (4 * (f & 1)));
+  } else {
+    return r & (0x00030003u << (2 * f));  // 2 bits: fields 0-3 of r (row g) or of r >> 8 (row g+8)
+  }
+}
+
+// Request a tile: positions, scales, zeros in the oldest commit group, then the codes in four groups
+// of a quarter of the steps each.  ntok = valid tokens (a multiple of 32), ng = channel groups.
+template <int BITS>
+__device__ __forceinline__ void v_tile_request(const TierDev& T, VWarpShared& ws, int bh, int tile_t0, int ntok, int ng) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31;
+  const int64_t tok0 = static_cast<int64_t>(bh) * T.n_v + tile_t0;
+#pragma unroll
+  for (int j = 0; j < TL::TOKENS / 32; ++j) {
+    const int t = lane + 32 * j;
+    if (t < ntok) cp_async_8(&ws.v.a.pos[t], T.v_idx + tile_t0 + t);
+  }
+  // scale / zero rows are ng halfs per token, contiguous over the tile: 8-byte pieces
+  {
+    const int bytes = ntok * ng * 2;
+    const unsigned char* s = reinterpret_cast<const unsigned char*>(T.v_scale + tok0 * ng);
+    const unsigned char* z = reinterpret_cast<const unsigned char*>(T.v_zero + tok0 * ng);
+#pragma unroll
+    for (int j = 0; j < V_MAX_TT * 4 * 2 / (32 * 8); ++j) {
+      const int o = (lane + 32 * j) * 8;
+      if (o < bytes) {
+        cp_async_8(reinterpret_cast<unsigned char*>(ws.s) + o, s + o);
+        cp_async_8(reinterpret_cast<unsigned char*>(ws.z) + o, z + o);
+      }
+    }
+  }
+  cp_async_commit();
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(T.v_data) + tok0 * TL::PITCH;
+  constexpr int PIECES = TL::TOKENS * TL::NPIECE;  // 512 (256 at 2 bits, 128 at 1 bit)
+  constexpr int PER_Q = PIECES / 4 / 32;           // copies per lane and quarter: 4 (2, 1)
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int i = 0; i < PER_Q; ++i) {
+      const int id = (quarter * PER_Q + i) * 32 + lane;
+      const int row = id / TL::NPIECE, c = id % TL::NPIECE;
+      if (row < ntok) cp_async_16(ws.u.codes + TL::offset(row, c), src + static_cast<int64_t>(id) * 16);
+    }
+    cp_async_commit();
+  }
+}
+
+// exp(logit - max) of the tile's tokens for heads h0..h0+3 into prow[0..3][token], and the
+// normalised probabilities into the output row; the gathers of four heads are in flight together.
+template <int TOKENS>
+__device__ __forceinline__ void v_tile_probs(const DecodeParams& P, const VShared& sh, const int64_t* pos_s, __half (*prow)[V_PROW],
+                                             int b, int kvh, int h0, int ntok, int64_t first_pos) {
+  const int lane = threadIdx.x & 31;
+  const int rep = P.rep;
+  constexpr int PER = TOKENS / 32;
+  uint32_t pos[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) {
+    const int t = lane + 32 * j;
+    pos[j] = t < ntok ? (pos_s ? static_cast<uint32_t>(pos_s[t]) : static_cast<uint32_t>(first_pos + t)) : 0u;
+  }
+  bool ok[PER];
+#pragma unroll
+  for (int j = 0; j < PER; ++j) ok[j] = lane + 32 * j < ntok && HQKV_INDEX_OK(pos[j], P.L);
+  if (P.probs_in) {
+    // caller-supplied weights: staged as they are, nothing is written back
+#pragma unroll 1
+    for (int hh = 0; hh < 4; ++hh) {
+      const int h = h0 + hh;
+      const unsigned short* row = reinterpret_cast<const unsigned short*>(P.probs_in) +
+                                  (static_cast<int64_t>(b) * P.nh_q + kvh * rep + min(h, rep - 1)) * P.L;
+#pragma unroll
+      for (int j = 0; j < PER; ++j)
+        prow[hh][lane + 32 * j] = __ushort_as_half((h < rep && ok[j]) ? __ldcg(row + pos[j]) : static_cast<unsigned short>(0));
+    }
+    return;
+  }
+  float x[4][PER];
+#pragma unroll
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = min(h0 + hh, rep - 1);
+    const float* row = P.logits + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + h) * P.L;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) x[hh][j] = ok[j] ? __ldcg(row + pos[j]) : -INFINITY;
+  }
+#pragma unroll
+  for (int hh = 0; hh < 4; ++hh) {
+    const int h = h0 + hh;
+    const bool on = h < rep;
+    const float mh = on ? sh.gm[h] * LOG2E : 0.f, inv = on ? 1.f / sh.gl[h] : 0.f;
+    __half* wrow = P.weights + (static_cast<int64_t>(b) * P.nh_q + kvh * rep + min(h, rep - 1)) * P.L;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+      const int t = lane + 32 * j;
+      const float e = on ? fast_exp2(fmaf(x[hh][j], LOG2E, -mh)) : 0.f;  // exp2(-inf) = 0 beyond the tile
+      prow[hh][t] = __float2half_rn(e);
+      if (on && ok[j]) wrow[pos[j]] = __float2half_rn(e * inv);
+    }
+  }
+}
+
+// One tile of a quantised V tier for half hh of the heads: acc[mt] = M-tile mt of the output
+// (channels x heads, see the channel map in v_tile_store), zacc = zero term rows.
+template <int BITS>
+__device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& ws, const __half (*prow)[V_PROW], int ntok,
+                                            float (&acc)[8][4], float (&zacc)[4], bool normal) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int ng_shift = 7 - P.gv_shift;  // log2(groups per token): 2, 1, 0
+  // ldmatrix row address of this lane for step 0, quad 0: matrices (token octet, piece) =
+  //   8/4 bits: (0, c), (0, c'), (1, c), (1, c');  2 bits: (0, 0), (0, 1), (1, 0), (1, 1)
+  // with (c, c') = the quad's two pieces: 4 bits (2pp, 2pp+1); 8 bits (4q+u, 4q+2+u)
+  const int mi = lane >> 3, rr = lane & 7;
+  const int lm_row = 8 * (mi >> 1) + rr;
+  // as a B column this lane is n = g: head (n & 3) of this half, channel group of channels
+  // 64q + 32*(n >> 2) for quad set q
+  const __half* pr = &prow[g & 3][2 * tig];
+  int gq[2];
+#pragma unroll
+  for (int q = 0; q < 2; ++q) gq[q] = (64 * q + 32 * (g >> 2)) >> P.gv_shift;
+  const int zg = (g & 3) & ((1 << ng_shift) - 1);  // zero-term row g = group g (rows beyond ng repeat)
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  zacc[0] = zacc[1] = zacc[2] = zacc[3] = 0.f;
+  float sacc[4] = {0.f, 0.f, 0.f, 0.f};  // Gaussian-codebook tier: sum_t p * std per channel group
+
+  const int nsteps = ntok >> 4;
+HQKV_UNROLL(V_STEP_UNROLL)
+  for (int st = 0; st < nsteps; ++st) {
+    const int t0 = st * 16;
+    // B operands: p pairs of tokens (2tig, 2tig+1) and (+8, +9); scales of the same tokens
+    const uint32_t p0 = *reinterpret_cast<const uint32_t*>(pr + t0);
+    const uint32_t p1 = *reinterpret_cast<const uint32_t*>(pr + t0 + 8);
+    const __half* sb = ws.s + ((t0 + 2 * tig) << ng_shift);
+    const __half* zb = ws.z + ((t0 + 2 * tig) << ng_shift);
+    uint32_t bh_[2][2], bl_[2][2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const __half2 s0 = u32_as_h2(pack_lo16(__half_as_ushort(sb[gq[q]]), __half_as_ushort(sb[(1 << ng_shift) + gq[q]])));
+      const __half2 s1 = u32_as_h2(pack_lo16(__half_as_ushort(sb[(8 << ng_shift) + gq[q]]),
+                                             __half_as_ushort(sb[(9 << ng_shift) + gq[q]])));
+      const __half2 h0 = __hmul2(u32_as_h2(p0), s0), h1 = __hmul2(u32_as_h2(p1), s1);
+      bh_[q][0] = h2_as_u32(h0);
+      bh_[q][1] = h2_as_u32(h1);
+      bl_[q][0] = h2_as_u32(__hfma2(u32_as_h2(p0), s0, __hneg2(h0)));  // exact remainder
+      bl_[q][1] = h2_as_u32(__hfma2(u32_as_h2(p1), s1, __hneg2(h1)));
+    }
+    {  // zero term: A rows = channel groups, exact fp16 x fp16 products
+      const uint32_t a0 = pack_lo16(__half_as_ushort(zb[zg]), __half_as_ushort(zb[(1 << ng_shift) + zg]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(zb[(8 << ng_shift) + zg]), __half_as_ushort(zb[(9 << ng_shift) + zg]));
+      mma16816(zacc, a0, 0u, a2, 0u, p0, p1);
+    }
+    if (BITS == 1 && normal) {
+      const uint32_t a0 = pack_lo16(__half_as_ushort(sb[zg]), __half_as_ushort(sb[(1 << ng_shift) + zg]));
+      const uint32_t a2 = pack_lo16(__half_as_ushort(sb[(8 << ng_shift) + zg]), __half_as_ushort(sb[(9 << ng_shift) + zg]));
+      mma16816(sacc, a0, 0u, a2, 0u, p0, p1);
+    }
+    const unsigned char* rowp = ws.u.codes;
+    if constexpr (BITS == 1) {
+      // block = 16 channels, four blocks per 64-channel half c; lane g reads block 4c + (g & 3) of tokens
+      // 2tig, 2tig+1 (+8, +9) with 2-byte loads; rows g / g+8 of M-tile f are channels 4*(g>>2) + f and +8
+      const unsigned char* tb = rowp + (t0 + 2 * tig) * 16 + 2 * (g & 3);
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t r0 = pack_lo16(*reinterpret_cast<const uint16_t*>(tb + 8 * c), *reinterpret_cast<const uint16_t*>(tb + 8 * c + 16));
+        const uint32_t r1 = pack_lo16(*reinterpret_cast<const uint16_t*>(tb + 8 * c + 128), *reinterpret_cast<const uint16_t*>(tb + 8 * c + 144));
+        const uint32_t lo0 = r0 >> (4 * (g >> 2)), hi0 = lo0 >> 8, lo1 = r1 >> (4 * (g >> 2)), hi1 = lo1 >> 8;
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint32_t msk = 0x00010001u << f;
+          mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bh_[c][0], bh_[c][1]);
+        }
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const uint32_t msk = 0x00010001u << f;
+          mma16816(acc[4 * c + f], lo0 & msk, hi0 & msk, lo1 & msk, hi1 & msk, bl_[c][0], bl_[c][1]);
+        }
+      }
+    } else if constexpr (BITS == 2) {
+      uint32_t R[4];
+      ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, mi & 1));
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint32_t lo0 = R[c], hi0 = R[c] >> 8, lo1 = R[2 + c], hi1 = R[2 + c] >> 8;
+        uint32_t fa[4][4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          fa[f][0] = v_field<2>(lo0, 0u, f), fa[f][1] = v_field<2>(hi0, 0u, f);
+          fa[f][2] = v_field<2>(lo1, 0u, f), fa[f][3] = v_field<2>(hi1, 0u, f);
+        }
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * c + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[c][0], bh_[c][1]);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * c + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[c][0], bl_[c][1]);
+      }
+    } else if constexpr (BITS == 4) {
+#pragma unroll
+      for (int pp = 0; pp < 2; ++pp) {
+        uint32_t R[4], S[4];
+        ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 2 * pp + (mi & 1)));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) S[k] = R[k] >> 8;
+        uint32_t fa[4][4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) fa[f][k] = v_field<4>(R[k], S[k], f);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * pp + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[pp][0], bh_[pp][1]);
+#pragma unroll
+        for (int f = 0; f < 4; ++f) mma16816(acc[4 * pp + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[pp][0], bl_[pp][1]);
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 2; ++q)
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+          uint32_t R[4];
+          ldmatrix_x4_trans(R, rowp + TL::offset(t0 + lm_row, 4 * q + u + 2 * (mi & 1)));
+          uint32_t fa[2][4];
+#pragma unroll
+          for (int f = 0; f < 2; ++f)
+#pragma unroll
+            for (int k = 0; k < 4; ++k) fa[f][k] = v_field<8>(R[k], 0u, f);
+#pragma unroll
+          for (int f = 0; f < 2; ++f) mma16816(acc[4 * q + 2 * u + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bh_[q][0], bh_[q][1]);
+#pragma unroll
+          for (int f = 0; f < 2; ++f) mma16816(acc[4 * q + 2 * u + f], fa[f][0], fa[f][1], fa[f][2], fa[f][3], bl_[q][0], bl_[q][1]);
+        }
+    }
+  }
+  if (BITS == 1 && normal) {  // value = std * C * (2 code - 1) + mean: the code-free term is sum_t p (mean - C std)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) zacc[i] = fmaf(-HQKV_NORMAL1_CENTER, sacc[i], zacc[i]);
+  }
+}
+
+// Accumulators of one walk -> red[head of this half][channel] (every element has exactly one owner).
+//   8 / 4 bits: rows 0-7 and 8-15 of an M-tile are two different channel groups: lanes tig 0,1 own row g
+//               (columns 0-3), lanes tig 2,3 own row g+8 (columns 4-7).
+//   2 bits:     rows g and g+8 are channels of the same block: lanes with (g < 4) == (tig < 2) own both.
+// M-tile -> channels:  8 bits  mt = 4q + 2u + f : row g = 64q + 16u + 2g + f,  row g+8 = +32
+//                      4 bits  mt = 4pp + f     : row g = 64pp + 4g + f,        row g+8 = +32
+//                      2 bits  mt = 4c + f      : row g = 64c + 8g + f,         row g+8 = +4
+//                      1 bit   mt = 4c + f      : row g = 64c + 16(g&3) + 4(g>>2) + f, row g+8 = +8
+//                              (owned by the lanes with ((g & 3) < 2) == (tig < 2))
+template <int BITS>
+__device__ __forceinline__ void v_tile_store(float (*red)[D], const float (&acc)[8][4], float gain) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int hp = tig & 1, r = tig >> 1;
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt) {
+    const int f = BITS == 8 ? (mt & 1) : (mt & 3);
+    const float unscale = static_cast<float>(1 << (24 - VField<BITS>::shift(f))) * gain;
+    if constexpr (BITS <= 2) {
+      const bool mine = BITS == 2 ? (g < 4) == (tig < 2) : ((g & 3) < 2) == (tig < 2);
+      if (mine) {
+        const int ch = 64 * (mt >> 2) + (BITS == 2 ? 8 * g : 16 * (g & 3) + 4 * (g >> 2)) + f;
+        constexpr int UP = BITS == 2 ? 4 : 8;  // channel distance of row g+8
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          red[2 * hp + e][ch] = acc[mt][e] * unscale;
+          red[2 * hp + e][ch + UP] = acc[mt][2 + e] * unscale;
+        }
+      }
+    } else {
+      const int ch = BITS == 8 ? 64 * (mt >> 2) + 16 * ((mt >> 1) & 1) + 2 * g + f + 32 * r
+                               : 64 * (mt >> 2) + 4 * g + f + 32 * r;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) red[2 * hp + e][ch] = (r ? acc[mt][2 + e] : acc[mt][e]) * unscale;
+    }
+  }
+}
+
+// Everything a warp does for its tile of a quantised V tier.
+template <int BITS>
+__device__ __forceinline__ void v_tile(const DecodeParams& P, const TierDev& T, VShared& sh, VWarpShared& ws, int b,
+                                       int kvh, int ntok, int nh) {
+  using TL = VTile<BITS>;
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  cp_async_wait<4>();  // positions, scales, zeros
+  __syncwarp();
+  for (int hh = 0; hh < nh; ++hh)
+    v_tile_probs<TL::TOKENS>(P, sh, ws.v.a.pos, hh ? ws.p_hi : ws.v.a.p, b, kvh, 4 * hh, ntok, 0);
+  cp_async_wait<0>();  // the gathers above took at least as long as the codes
+  __syncwarp();
+  for (int hh = 0; hh < nh; ++hh) {
+    float acc[8][4], zacc[4];
+    const bool normal = BITS == 1 && T.normal != 0;
+    v_tile_walk<BITS>(P, ws, hh ? ws.p_hi : ws.v.a.p, ntok, acc, zacc, normal);
+    __syncwarp();  // all lanes are done with the codes (last walk) or with p of heads 0-3 (first of two)
+    v_tile_store<BITS>(hh + 1 < nh ? ws.v.red0 : ws.u.red, acc, normal ? 2.f * HQKV_NORMAL1_CENTER : 1.f);
+    if (g < 4 && tig < 2) {
+      ws.zt[g][4 * hh + 2 * tig] = zacc[0];
+      ws.zt[g][4 * hh + 2 * tig + 1] = zacc[1];
+    }
+  }
+}
+
+// fp16 tier and residual window, token-major rows [n][D] halfs: one 16-token step per warp straight
+// from global memory; B = p.  Writes the partial outputs of all (up to eight) heads.
+__device__ __forceinline__ void v_plain_tile(const DecodeParams& P, const TierDev& T, VShared& sh, VWarpShared& ws, int bh,
+                                             int b, int kvh, int t0, int ntok, bool is_res) {
+  const int lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  const int rep = P.rep;
+  const uint4* base = reinterpret_cast<const uint4*>(T.v_data) + static_cast<int64_t>(bh) * T.n_v * 16;
+  uint4 w[4][2];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const int tl = 2 * tig + (p & 1) + (p >> 1) * 8;
+    const int64_t tok = t0 + min(tl, ntok - 1);
+#pragma unroll
+    for (int s = 0; s < 2; ++s) w[p][s] = ld_stream(base + tok * 16 + s * 8 + g);
+  }
+  const int64_t first_pos = static_cast<int64_t>(P.L) - T.n_v + t0;
+  for (int hh = 0; hh < (rep > 4 ? 2 : 1); ++hh)
+    v_tile_probs<32>(P, sh, is_res ? nullptr : T.v_idx + t0, hh ? ws.p_hi : ws.v.a.p, b, kvh, 4 * hh, ntok, first_pos);
+  __syncwarp();
+  float acc[8][4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+  uint32_t b0 = 0u, b1 = 0u;
+  if (g < rep) {
+    const __half* pr = g < 4 ? ws.v.a.p[g] : ws.p_hi[g - 4];
+    b0 = *reinterpret_cast<const uint32_t*>(pr + 2 * tig);
+    b1 = *reinterpret_cast<const uint32_t*>(pr + 2 * tig + 8);
+  }
+  const __half2 none[2][2] = {};
+  mma_words<16, 8>(acc, w, none, none, b0, b1);
+  __syncwarp();
+  // M-tile mt, slot s: channel 8*(8s + g) + mt; columns 2tig, 2tig+1 = heads
+#pragma unroll
+  for (int mt = 0; mt < 8; ++mt)
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int ch = 8 * (s * 8 + g) + mt;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int h = 2 * tig + e;  // heads 0-3 are the first of two halves when there are eight
+        if (rep > 4) {
+          (h < 4 ? ws.v.red0 : ws.u.red)[h & 3][ch] = acc[mt][s * 2 + e];
+        } else if (h < 4) {
+          ws.u.red[h][ch] = acc[mt][s * 2 + e];
+        }
+      }
+    }
 }
 
 // Cross-GPU barrier of one call, run by up to `world` threads of one CTA: thread r tells peer r "my stores
@@ -172,7 +1357,7 @@ __device__ __forceinline__ void peer_barrier_device(unsigned* const* pad, int ra
   __syncthreads();
   const unsigned n = *shared_n;
   if (r < world && r != rank) {
-    if (FENCE_FIRST) __threadfence_system();  // this GPU's earlier peer stores first (the decode kernel has fenced them already)
+    if (FENCE_FIRST) __threadfence_system();  // this GPU's earlier peer stores first (the V pass has fenced them already)
     atomicAdd_system(pad[r] + rank, 1u);      // slot `rank` of peer r's pad counts my arrivals
     volatile unsigned* mine = pad[rank] + r;  // slot r of my pad counts peer r's arrivals
     long long spins = 0;
@@ -189,363 +1374,166 @@ __device__ __forceinline__ void peer_barrier_device(unsigned* const* pad, int ra
   if (r == 0) *call_no = n;
 }
 
-__global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __grid_constant__ DecodeParams P) {
-  extern __shared__ __align__(128) unsigned char smem[];
-  CtaShared& cs = *reinterpret_cast<CtaShared*>(smem);
-  __half* qsm = reinterpret_cast<__half*>(smem + CTA_HEAD_BYTES);
+__global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
+  const int chunk = blockIdx.y, bh = blockIdx.x;
+  const int b = bh / P.H, kvh = bh - b * P.H;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  unsigned char* wsm = smem + P.cta_smem + warp * P.warp_smem;
-  const bool rep8 = P.rep > 4;
   const int rep = P.rep;
-  const int BH = P.B * P.H;
-  const bool do_k = (P.phases & 1) != 0, do_v = (P.phases & 2) != 0;
+  const int nh = rep > 4 ? 2 : 1;
 
-  // The next kernel of the stream - the next decode call, if it was launched with programmatic stream
-  // serialisation - may place its CTAs as soon as CTAs of this grid have finished; it requests its
-  // first K tile and then waits for this grid to complete.
+  int ti = HQKV_NUM_TIERS;
+#pragma unroll
+  for (int t = 0; t < HQKV_NUM_TIERS; ++t)
+    if (chunk >= P.tier[t].v_chunk0 && chunk < P.tier[t + 1].v_chunk0) ti = t;
+  const TierDev& T = P.tier[ti];
+  const bool is_res = ti == HQKV_NUM_TIERS;
+  const int vb = is_res ? 16 : T.bits;
+  const int tile_tokens = T.v_chunk_tokens / VWARPS;
+  const int tile_t0 = (chunk - T.v_chunk0) * T.v_chunk_tokens + warp * tile_tokens;
+  const int ntok = min(tile_tokens, T.n_v - tile_t0);  // <= 0: this warp has no tile
+  VWarpShared& ws = sh.w[warp];
+  const int ng = D >> P.gv_shift;
+
+  // The next kernel of the stream - the K pass of the next decode call, if it was launched with
+  // programmatic stream serialisation - may start its cache-only prologue while this grid drains.
   asm volatile("griddepcontrol.launch_dependents;");
-
-  // ---- this CTA's (batch, kv head) pair(s) and its place in the pair's group
-  int bh, gi = 0, gm_ = 1, sel = 0, bh_step;
-  if (P.g_m == 0) {  // more pairs than CTAs: whole pairs, one after the other
-    bh = blockIdx.x;
-    bh_step = gridDim.x;
-  } else {
-    const int c = blockIdx.x, big = P.g_rem * (P.g_m + 1);  // CTAs in the groups of g_m + 1
-    if (c < big) {
-      sel = 1;
-      gm_ = P.g_m + 1;
-      bh = static_cast<int>((c + 0.5f) * P.g_inv[1]);
-      gi = c - bh * gm_;
-    } else {
-      gm_ = P.g_m;
-      const int c2 = c - big, j = static_cast<int>((c2 + 0.5f) * P.g_inv[0]);
-      bh = P.g_rem + j;
-      gi = c2 - j * gm_;
-    }
-    bh_step = BH;  // one pair
+  // ---- requests that read only the cache go out before the K pass is known to be complete
+  if (ntok > 0) {
+    if (vb == 8) v_tile_request<8>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 4) v_tile_request<4>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 2) v_tile_request<2>(T, ws, bh, tile_t0, ntok, ng);
+    else if (vb == 1) v_tile_request<1>(T, ws, bh, tile_t0, ntok, ng);
   }
-  const bool local = gm_ == 1 && P.phases == 3 && P.probs_in == nullptr;  // the CTA has the whole pair: no global hand-over
-  float2* kstat = reinterpret_cast<float2*>(wsm + WS_KSTAT);  // this warp's (max, sum-exp) per head
-  bool first_unit = true;
-  unsigned finished = 0u;  // pairs this CTA wrote the output of (multi-GPU hand-over)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
 
-  for (; bh < BH; bh += bh_step) {
-    const int b = bh / P.H, kvh = bh - b * P.H;
-    const int64_t head0 = static_cast<int64_t>(b) * P.nh_q + kvh * rep;
-    // weights of this CTA, then of this warp, on both sides
-    const int ka0 = gi * P.kq[sel] + min(gi, P.kr[sel]), ka1 = ka0 + P.kq[sel] + (gi < P.kr[sel] ? 1 : 0);
-    const int va0 = gi * P.vq[sel] + min(gi, P.vr[sel]), va1 = va0 + P.vq[sel] + (gi < P.vr[sel] ? 1 : 0);
-    const int k_end = ka0 + (((ka1 - ka0) * (warp + 1)) >> 3), v_end = va0 + (((va1 - va0) * (warp + 1)) >> 3);
-    Cursor cur, vcur;
-    bool have = false, vhave = false;
-    uint32_t vpos[4] = {0u, 0u, 0u, 0u};
-    if (do_k) {
-      cur = cursor_at<true>(P, ka0 + (((ka1 - ka0) * warp) >> 3));
-      have = cur.s < k_end;
-      if (have) k_request(P, cur, bh, wsm);  // reads only the cache
+  if (P.probs_in) {  // weights are given: nothing to fold, nothing to normalise by
+    if (tid < rep) {
+      sh.gm[tid] = 0.f;
+      sh.gl[tid] = 1.f;
     }
-    if (do_v) {
-      vcur = cursor_at<false>(P, va0 + (((va1 - va0) * warp) >> 3));
-      vhave = vcur.s < v_end;
-      if (!do_k && vhave) {
-        const uint4 r = v_request(P, vcur, bh, wsm);
-        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
-      }
-    }
-    if (first_unit) {
-      // Everything above reads only the cache.  From here on this grid reads q and writes the scratch that
-      // the previous decode call of the stream may still be using: wait for the kernels before it.
-      asm volatile("griddepcontrol.wait;" ::: "memory");
-      first_unit = false;
-    }
-
-    // -------------------------------------------------------------------------------------------
-    // K slice
-    // -------------------------------------------------------------------------------------------
-    if (do_k) {
-      // q of the pair -> shared memory (rows of heads that do not exist are zero)
-      {
-        const int rows = rep8 ? 8 : 4;
-        for (int i = tid; i < rows * (D / 2); i += NTHREADS) {
-          const int c2 = i & (D / 2 - 1), row = i >> 6;
-          uint32_t v = 0u;
-          if (row < rep) v = __ldcg(reinterpret_cast<const uint32_t*>(P.q + (head0 + row) * D) + c2);
-          *reinterpret_cast<uint32_t*>(qsm + row * Q_PITCH + 2 * c2) = v;
-        }
-      }
-      // The first CTA of a group clears the pair's output accumulators: the V slices add into them only after
-      // the K side of the pair is complete, and this CTA is part of it.
-      if (!local && gi == 0) {
-        double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
-        for (int e = tid; e < rep * D; e += NTHREADS) accum[e] = 0.0;
-      }
-      __syncthreads();
-      KWarpState st;
-      st.pm = -INFINITY;
-      st.pl = 0.f;
-#pragma unroll
-      for (int i = 0; i < 2; ++i)
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          st.m[i][e] = -INFINITY;
-          st.l[i][e] = 0.f;
-        }
-      st.mask0 = P.mask ? P.mask + b * P.mask_bstride + static_cast<int64_t>(kvh * rep) * P.mask_hstride : nullptr;
-      st.mask_hstride = P.mask_hstride;
-      float* row0 = P.logits + head0 * P.L;
-      bool streamed = false;  // the current tile was requested while the previous one was computed
-      while (have) {
-        const TierDev& T = P.tier[cur.tier];
-        const int t0 = cur.tile * T.k_tile_tokens, ntok = min(T.k_tile_tokens, T.n_k - t0);
-        Cursor nxt = cur;
-        cursor_next<true>(P, nxt);
-        const bool have_next = nxt.s < k_end;
-        // the next tile streams into this tile's buffer if it continues the same tier
-        const bool quant = cur.tier < HQKV_NUM_TIERS && T.bits < 16;
-        const bool stream = quant && have_next && nxt.tier == cur.tier;
-        const int nt0 = t0 + T.k_tile_tokens, nntok = stream ? min(T.k_tile_tokens, T.n_k - nt0) : 0;
-        if (cur.tier == HQKV_NUM_TIERS) {
-          k_residual_tile(T, wsm, st, qsm, bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
-        } else if (T.bits == 16) {
-          k_f16_span(T, wsm, st, qsm, bh, rep, P.rep_shift, P.L, P.scale, t0, row0);
-        } else if (T.bits == 8) {
-          k_tile_compute<8>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
-        } else if (T.bits == 4) {
-          k_tile_compute<4>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
-        } else if (T.bits == 2) {
-          k_tile_compute<2>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
-        } else {
-          k_tile_compute<1>(T, wsm, st, qsm, bh, rep, P.L, P.gk_shift, P.scale, t0, ntok, row0, streamed, nt0, nntok);
-        }
-        cur = nxt;
-        have = have_next;
-        streamed = stream;
-        __syncwarp();  // every lane is done with the tile in shared memory
-        if (have && !streamed) k_request(P, cur, bh, wsm);
-      }
-      k_emit_stats(st, kstat, reinterpret_cast<float2*>(wsm + WS_K_ZQ), rep);
-      // the first V tile does not depend on the logits: request it before the hand-over
-      if (do_v && vhave) {
-        const uint4 r = v_request(P, vcur, bh, wsm);
-        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
-      }
-      __syncthreads();
-      // ---- one (max, sum-exp) per head for the CTA's slice
-      if (tid < MAX_REP) {
-        float m = -INFINITY, l = 0.f;
-#pragma unroll 1
-        for (int w = 0; w < NWARPS; ++w) {
-          const float2 v = reinterpret_cast<const float2*>(smem + P.cta_smem + w * P.warp_smem + WS_KSTAT)[tid];
-          softmax_merge(m, l, v.x, v.y);
-        }
-        if (local) {
-          cs.gm[tid] = m;
-          cs.gl[tid] = l;
-        } else {
-          P.k_part[(static_cast<int64_t>(bh) * P.kc_max + gi) * MAX_REP + tid] = make_float2(m, l);
-        }
-      }
-      if (!local) {
-        __threadfence();  // this thread's logits (and pair) before the count below
-        __syncthreads();
-        if (tid == 0) atomicAdd(&P.kdone[bh], 1u);
-      } else {
-        __syncthreads();
-      }
-    }
-    if (!do_v) continue;
-
-    // -------------------------------------------------------------------------------------------
-    // wait for the K side of the pair; fold the published pairs
-    // -------------------------------------------------------------------------------------------
-    if (P.probs_in) {  // weights are given: nothing to wait for, nothing to normalise by
-      if (tid < MAX_REP) {
-        cs.gm[tid] = 0.f;
-        cs.gl[tid] = 1.f;
-      }
-      __syncthreads();
-    } else if (!local) {
-      if (warp == 0) {
-        if (lane == 0) {
-          const volatile unsigned* c = P.kdone + bh;
-          long long spins = 0;
-          while (*c < static_cast<unsigned>(gm_)) {
-            if (++spins > P.spin_limit) {
-              atomicExch(P.status, static_cast<unsigned>(bh) + 1u);  // gave up: the result of this call is not valid
-              break;
-            }
-            __nanosleep(40);
-          }
-          __threadfence();
-        }
-        __syncwarp();
-        const int head = lane & 7, slice = lane >> 3;
-        const float2* part = P.k_part + static_cast<int64_t>(bh) * P.kc_max * MAX_REP;
-        float m = -INFINITY, l = 0.f;
-#pragma unroll 1
-        for (int c0 = slice; c0 < gm_; c0 += 16) {
-          float2 v[4];
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int c = c0 + 4 * j;
-            v[j] = (c < gm_ && head < rep) ? __ldcg(part + c * MAX_REP + head) : make_float2(-INFINITY, 0.f);
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
-        }
-#pragma unroll
-        for (int off = 8; off < 32; off <<= 1) {
-          const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
-          const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
-          softmax_merge(m, l, m2, l2);
-        }
-        if (lane < MAX_REP) {
-          cs.gm[lane] = m;
-          cs.gl[lane] = l;
-        }
-      }
-      __syncthreads();
-    }
-
-    // -------------------------------------------------------------------------------------------
-    // V slice
-    // -------------------------------------------------------------------------------------------
-    float(*out)[D] = reinterpret_cast<float(*)[D]>(wsm + ws_v_out(rep8));
-    float* zt = reinterpret_cast<float*>(wsm + ws_v_zt(rep8));
-    {
-      const int out_elems = (rep8 ? 8 : 4) * D;
-      for (int i = lane * 4; i < out_elems; i += 128) *reinterpret_cast<float4*>(&out[0][0] + i) = make_float4(0.f, 0.f, 0.f, 0.f);
-      zt[lane] = 0.f;  // 4 x MAX_REP floats
-      __syncwarp();
-    }
-    const float* logit0 = P.logits + head0 * P.L;
-    __half* w0 = P.weights + head0 * P.L;
-    const __half* pin0 = P.probs_in ? P.probs_in + head0 * P.L : nullptr;
-    while (vhave) {
-      const TierDev& T = P.tier[vcur.tier];
-      const int t0 = vcur.tile * T.v_tile_tokens, ntok = min(T.v_tile_tokens, T.n_v - t0);
-      Cursor nxt = vcur;
-      cursor_next<false>(P, nxt);
-      const bool have_next = nxt.s < v_end;
-      // the next tile streams into this tile's buffer if this one is full and the next continues the same tier;
-      // its positions are fetched now, its rows during the walk over this tile
-      const bool quant = vcur.tier < HQKV_NUM_TIERS && T.bits < 16;
-      const bool stream = quant && have_next && nxt.tier == vcur.tier && ntok == T.v_tile_tokens;
-      const int nt0 = t0 + T.v_tile_tokens, nntok = stream ? min(T.v_tile_tokens, T.n_v - nt0) : 0;
-      uint32_t npos[4] = {0u, 0u, 0u, 0u};
-      if (stream) v_tile_positions(T, nt0, nntok, npos);
-      if (vcur.tier == HQKV_NUM_TIERS || T.bits == 16) {
-        v_plain_tile(T, wsm, rep8, rep, P.L, cs.gm, cs.gl, bh, logit0, w0, pin0, t0, ntok, vcur.tier == HQKV_NUM_TIERS);
-      } else if (T.bits == 8) {
-        v_tile<8>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
-      } else if (T.bits == 4) {
-        v_tile<4>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
-      } else if (T.bits == 2) {
-        v_tile<2>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
-      } else {
-        v_tile<1>(T, wsm, rep8, rep, P.L, P.gv_shift, cs.gm, cs.gl, vpos, logit0, w0, pin0, ntok, bh, nt0, nntok);
-      }
-      vcur = nxt;
-      vhave = have_next;
-      if (stream) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) vpos[j] = npos[j];
-      } else if (vhave) {
-        const uint4 r = v_request(P, vcur, bh, wsm);
-        vpos[0] = r.x, vpos[1] = r.y, vpos[2] = r.z, vpos[3] = r.w;
-      }
-    }
-
-    // ---- the warps' partial outputs are added up in warp order.  A group of one has the pair's whole sum:
-    //      it normalises and writes.  In a larger group the sums join the pair's fp64 accumulators with
-    //      fire-and-forget reductions (the sum of the fp32 partials depends on their order only below 2^-53, far
-    //      below the fp16 rounding of the output, and no CTA has to read other CTAs' partials back), and the last
-    //      CTA of the pair to arrive normalises and writes.
     __syncthreads();
-    bool writes = local;
-    if (!local) {
-      for (int e = tid; e < rep * D; e += NTHREADS) {
-        const int h = e >> 7, ch = e & (D - 1);
-        float v = 0.f;
-#pragma unroll 1
-        for (int w = 0; w < NWARPS; ++w) {
-          const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
-          v += reinterpret_cast<const float*>(o + ws_v_out(rep8))[e] +
-               reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
-        }
-        atomicAdd(P.v_acc + static_cast<int64_t>(bh) * rep * D + e, static_cast<double>(v));
+  } else
+  // ---- global (max, sum) of the heads from the k_pass pairs: thread = (head, slice of the chunks);
+  //      only the heads that exist are read, up to four pairs per thread in flight (one round of loads
+  //      up to 4 * 128 / rep chunks), then slices are folded by shuffles and across warps
+  {
+    const int rs = P.rep_shift;
+    const int h = tid & (rep - 1), slice = tid >> rs, slices = VTHREADS >> rs;
+    const float2* part = P.k_part + static_cast<int64_t>(bh) * P.nk_chunks * MAX_REP;
+    float m = -INFINITY, l = 0.f;
+    for (int c0 = slice; c0 < P.nk_chunks; c0 += 4 * slices) {
+      float2 v[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = c0 + slices * j;
+        v[j] = c < P.nk_chunks ? __ldcg(part + c * MAX_REP + h) : make_float2(-INFINITY, 0.f);
       }
-      __threadfence();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) softmax_merge(m, l, v[j].x, v[j].y);
+    }
+    for (int off = rep; off < 32; off <<= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, off);
+      const float l2 = __shfl_xor_sync(0xffffffffu, l, off);
+      softmax_merge(m, l, m2, l2);
+    }
+    if (lane < rep) {
+      sh.wm[warp][lane] = m;
+      sh.wl[warp][lane] = l;
+    }
+    __syncthreads();
+    if (tid < rep) {
+      float mm = sh.wm[0][tid], ll = sh.wl[0][tid];
+      for (int w = 1; w < VWARPS; ++w) softmax_merge(mm, ll, sh.wm[w][tid], sh.wl[w][tid]);
+      sh.gm[tid] = mm;
+      sh.gl[tid] = ll;
+    }
+    __syncthreads();
+  }
+  // ---- the warp's tile: probabilities of its tokens, then sum_t p_t * V_t
+  if (ntok > 0 && vb != 16) {
+    if (vb == 8) v_tile<8>(P, T, sh, ws, b, kvh, ntok, nh);
+    else if (vb == 4) v_tile<4>(P, T, sh, ws, b, kvh, ntok, nh);
+    else if (vb == 2) v_tile<2>(P, T, sh, ws, b, kvh, ntok, nh);
+    else v_tile<1>(P, T, sh, ws, b, kvh, ntok, nh);
+  } else {
+    if (ntok > 0) {
+      v_plain_tile(P, T, sh, ws, bh, b, kvh, tile_t0, ntok, is_res);
+    } else {
+      for (int i = lane; i < 4 * D; i += 32) {
+        (&ws.u.red[0][0])[i] = 0.f;
+        if (nh == 2) (&ws.v.red0[0][0])[i] = 0.f;
+      }
+    }
+    (&ws.zt[0][0])[lane] = 0.f;  // 4 x MAX_REP floats
+  }
+  __syncthreads();
+  // ---- partial output of this chunk (warps added in index order) joins the accumulators of this
+  //      (batch, kv head).  The adds are fire-and-forget fp64 reductions: the sum of the fp32 partials
+  //      depends on their order only below 2^-53, far below the fp16 rounding of the output, and no
+  //      CTA has to read other CTAs' partials back (a chain of dependent L2 round trips that used to
+  //      be a quarter of the kernel at batch 1).
+  {
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
+    for (int i = tid; i < rep * D; i += VTHREADS) {
+      const int h = i >> 7, ch = i & (D - 1);
+      const bool first_of_two = (h >> 2) + 1 < nh;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < VWARPS; ++w) {
+        const VWarpShared& o = sh.w[w];
+        v += (first_of_two ? o.v.red0[h & 3][ch] : o.u.red[h & 3][ch]) + o.zt[ch >> P.gv_shift][h];
+      }
+      atomicAdd(accum + i, static_cast<double>(v));
+    }
+  }
+  // ---- the last CTA of this (batch, kv head) normalises and writes the output
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const unsigned prev = atomicAdd(&P.counters[bh], 1u);
+    sh.is_last = (prev == static_cast<unsigned>(P.nv_chunks) - 1u) ? 1u : 0u;
+    if (sh.is_last) P.counters[bh] = 0u;  // ready for the next call
+  }
+  __syncthreads();
+  if (sh.is_last) {
+    __threadfence();
+    double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
+    for (int i = tid * 2; i < rep * D; i += VTHREADS * 2) {
+      const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + i));
+      const float inv = 1.f / sh.gl[i >> 7];
+      const __half2 o = __floats2half2_rn(static_cast<float>(v.x) * inv, static_cast<float>(v.y) * inv);
+      const int64_t at = (static_cast<int64_t>(b) * P.nh_q + kvh * rep) * D + i;
+      *reinterpret_cast<__half2*>(P.out + at) = o;
+      // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
+      // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
+      if (P.peer_flagged) {
+        // value and call number travel in ONE 8-byte store: the receiver needs no fence and no signal
+        const uint2 e = make_uint2(h2_as_u32(o), P.peer_state[0] + 1u);
+        for (int p = 0; p < P.n_peers; ++p) reinterpret_cast<uint2*>(P.peer_out[p])[at >> 1] = e;
+      } else {
+        for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
+      }
+    }
+    if (P.world > 1) {
+      // the CTA that finishes the last (batch, kv head) of this GPU runs the cross-GPU barrier: when this
+      // kernel completes, every rank's rows are in this GPU's gathered buffer
+      __threadfence_system();
       __syncthreads();
       if (tid == 0) {
-        const unsigned prev = atomicAdd(&P.vdone[bh], 1u);
-        cs.is_last = (prev == static_cast<unsigned>(gm_) - 1u) ? 1u : 0u;
+        const unsigned done = atomicAdd(P.peer_state + 2, 1u);
+        sh.is_last = (done == static_cast<unsigned>(P.B * P.H) - 1u) ? 1u : 0u;
+        if (sh.is_last) P.peer_state[2] = 0u;
       }
       __syncthreads();
-      writes = cs.is_last != 0u;
-      if (writes) __threadfence();
-    }
-    if (writes) {
-      ++finished;
-      const double* accum = P.v_acc + static_cast<int64_t>(bh) * rep * D;
-      for (int e = tid * 2; e < rep * D; e += NTHREADS * 2) {
-        float vx, vy;
-        if (local) {
-          const int h = e >> 7, ch = e & (D - 1);
-          vx = vy = 0.f;
-#pragma unroll 1
-          for (int w = 0; w < NWARPS; ++w) {
-            const unsigned char* o = smem + P.cta_smem + w * P.warp_smem;
-            const float2 a = *reinterpret_cast<const float2*>(reinterpret_cast<const float*>(o + ws_v_out(rep8)) + e);
-            const float z = reinterpret_cast<const float*>(o + ws_v_zt(rep8))[(ch >> P.gv_shift) * MAX_REP + h];
-            vx += a.x + z;
-            vy += a.y + z;
-          }
-        } else {
-          const double2 v = __ldcg(reinterpret_cast<const double2*>(accum + e));
-          vx = static_cast<float>(v.x);
-          vy = static_cast<float>(v.y);
-        }
-        const float inv = 1.f / cs.gl[e >> 7];
-        const __half2 o = __floats2half2_rn(vx * inv, vy * inv);
-        const int64_t at = head0 * D + e;
-        *reinterpret_cast<__half2*>(P.out + at) = o;
-        // kv-head sharding: the same rows go straight into every peer's copy of the gathered output
-        // (plain stores over NVLink; the callers' cross-GPU barrier makes them visible before use)
-        if (P.peer_flagged) {
-          // value and call number travel in ONE 8-byte store: the receiver needs no fence and no signal
-          const uint2 w = make_uint2(h2_as_u32(o), P.peer_state[0] + 1u);
-          for (int p = 0; p < P.n_peers; ++p) reinterpret_cast<uint2*>(P.peer_out[p])[at >> 1] = w;
-        } else {
-          for (int p = 0; p < P.n_peers; ++p) *reinterpret_cast<__half2*>(P.peer_out[p] + at) = o;
-        }
+      if (sh.is_last) {
+        __threadfence();
+        // every CTA fenced its peer stores system-wide before it counted itself in, and this CTA saw the
+        // full count: the signal may go out at once
+        peer_barrier_device<false>(P.pad, P.rank, P.world, P.peer_state, reinterpret_cast<int*>(P.peer_state + 1),
+                                   P.max_spins, &sh.pad_[0]);
       }
-      if (!local && tid == 0) {  // every CTA of this pair has passed its wait and counted itself in
-        P.kdone[bh] = 0u;
-        P.vdone[bh] = 0u;
-      }
-    }
-    __syncthreads();  // the shared memory of this pair is free for the next one
-  }
-
-  if (P.world > 1 && finished != 0u) {
-    // the CTA that finishes the last (batch, kv head) of this GPU runs the cross-GPU barrier: when this
-    // kernel completes, every rank's rows are in this GPU's gathered buffer
-    __threadfence_system();
-    __syncthreads();
-    if (tid == 0) {
-      const unsigned done = atomicAdd(P.peer_state + 2, finished);
-      cs.bar_n = (done + finished == static_cast<unsigned>(BH)) ? 1u : 0u;
-      if (cs.bar_n) P.peer_state[2] = 0u;
-    }
-    __syncthreads();
-    if (cs.bar_n) {
-      __threadfence();
-      // every CTA fenced its peer stores system-wide before it counted itself in, and this CTA saw the
-      // full count: the signal may go out at once
-      peer_barrier_device<false>(P.pad, P.rank, P.world, P.peer_state, reinterpret_cast<int*>(P.peer_state + 1),
-                                 P.max_spins, &cs.pad_[0]);
     }
   }
 }
@@ -553,24 +1541,6 @@ __global__ void __launch_bounds__(NTHREADS, CTAS_PER_SM) decode_kernel(const __g
 // ------------------------------------------------------------------------------------------------
 // host side
 // ------------------------------------------------------------------------------------------------
-static int sm_count() {
-  static int cached[64] = {};
-  int dev = 0, n = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
-    (void)cudaGetLastError();
-    return 148;  // B200
-  }
-  if (cached[dev] == 0) {
-    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0) {
-      cached[dev] = n;
-    } else {
-      (void)cudaGetLastError();
-      cached[dev] = 148;
-    }
-  }
-  return cached[dev];
-}
-
 static int ilog2(int v) {
   int s = 0;
   while ((1 << s) < v) ++s;
@@ -579,12 +1549,9 @@ static int ilog2(int v) {
 
 struct Layout {
   size_t acc_off, logits_off, kpart_off, total;
-  int smem_bytes;
-  int ctas_per_sm;
-  int grid;
 };
 
-// sides: bit 0 = the K side of the descriptor is used, bit 1 = the V side (a one-sided call ignores the other side's fields)
+// sides: 1 = only the K side of the descriptor is looked at, 2 = only the V side, 3 = both
 static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay, int sides = 3) {
   HQKV_REQUIRE(c != nullptr, "decode: null cache descriptor");
   HQKV_REQUIRE(c->B > 0 && c->H > 0 && c->nh_q > 0, "decode: B, H and nh_q must be positive");
@@ -593,7 +1560,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
                "decode: nh_q (%d) must be a multiple of H (%d) with at most %d query heads per kv head", c->nh_q,
                c->H, MAX_REP);
   HQKV_REQUIRE(valid_group(c->group_k) && valid_group(c->group_v), "decode: group sizes must be 32, 64 or 128");
-  HQKV_REQUIRE(static_cast<int64_t>(c->B) * c->H <= MAX_BH, "decode: B*H must not exceed %d", MAX_BH);
+  HQKV_REQUIRE(static_cast<int64_t>(c->B) * c->H <= 1024, "decode: B*H must not exceed 1024");
   HQKV_REQUIRE(c->n_new >= 0, "decode: negative residual length");
   memset(&P, 0, sizeof(P));
   P.B = c->B;
@@ -607,8 +1574,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   P.scale = c->softmax_scale;
   static const int expect_bits[HQKV_NUM_TIERS] = {16, 8, 4, 2, 1};
   int64_t nk_total = 0, nv_total = 0;
-  int64_t wk = 0, wv = 0;
-  P.k_first = P.v_first = -1;
+  int kc = 0, vc = 0;
   for (int t = 0; t < HQKV_NUM_TIERS; ++t) {
     const hqkv_tier_t& s = c->tier[t];
     TierDev& d = P.tier[t];
@@ -616,7 +1582,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.bits = expect_bits[t];
     d.n_k = (sides & 1) ? s.n_k : 0;
     d.n_v = (sides & 2) ? s.n_v : 0;
-    if (s.n_k > 0 || s.n_v > 0) {
+    if (d.n_k > 0 || d.n_v > 0) {
       HQKV_REQUIRE(s.bits == expect_bits[t], "decode: tier %d must hold %d-bit data (got %d)", t, expect_bits[t], s.bits);
       HQKV_REQUIRE(s.codec == HQKV_CODEC_UNIFORM || (s.codec == HQKV_CODEC_NORMAL && s.bits == 1),
                    "decode: tier %d: codec %d is not valid at %d bits (the Gaussian codebook is built for the 1-bit tier)", t,
@@ -624,8 +1590,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
       d.normal = s.codec == HQKV_CODEC_NORMAL ? 1 : 0;
     }
     if (d.n_k > 0) {
-      HQKV_REQUIRE(s.k_data && s.k_idx, "decode: tier %d K pointers are null", t);
-      HQKV_REQUIRE(aligned(s.k_idx, 8), "decode: tier %d K index list must be 8-byte aligned", t);
+      HQKV_REQUIRE(s.k_data && s.k_idx && aligned(s.k_idx, 8), "decode: tier %d K pointers are null or the index list is misaligned", t);
       if (s.bits < 16) {
         HQKV_REQUIRE(s.k_scale && s.k_zero && aligned(s.k_scale, 16) && aligned(s.k_zero, 16),
                      "decode: tier %d K scale/zero pointers are null or not 16-byte aligned", t);
@@ -638,8 +1603,7 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
       }
     }
     if (d.n_v > 0) {
-      HQKV_REQUIRE(s.v_data && s.v_idx, "decode: tier %d V pointers are null", t);
-      HQKV_REQUIRE(aligned(s.v_idx, 8), "decode: tier %d V index list must be 8-byte aligned", t);
+      HQKV_REQUIRE(s.v_data && s.v_idx && aligned(s.v_idx, 8), "decode: tier %d V pointers are null or the index list is misaligned", t);
       if (s.bits < 16)
         HQKV_REQUIRE(s.v_scale && s.v_zero && aligned(s.v_scale, 8) && aligned(s.v_zero, 8),
                      "decode: tier %d V scale/zero pointers are null or not 8-byte aligned", t);
@@ -653,19 +1617,15 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
     d.v_scale = static_cast<const __half*>(s.v_scale);
     d.v_zero = static_cast<const __half*>(s.v_zero);
     d.v_idx = s.v_idx;
-    // tiles: about the same number of bytes whatever the width
+    // chunk sizes: about the same number of bytes per CTA whatever the width
     const int b = d.bits;
+    d.k_chunk_tokens = KWARPS * (b == 8 || b == 16 ? 64 : 128);  // one tile per warp
     HQKV_REQUIRE(static_cast<int64_t>(s.n_k) * D * b / 8 < (1ll << 31), "decode: tier %d K plane of one head exceeds 2 GiB", t);
-    d.k_tile_tokens = (b == 8 || b == 16) ? 64 : 128;
-    d.v_tile_tokens = b == 8 ? 64 : b == 16 ? 16 : 128;
-    d.k_tiles = static_cast<int>(ceil_div(d.n_k, d.k_tile_tokens));
-    d.v_tiles = static_cast<int>(ceil_div(d.n_v, d.v_tile_tokens));
-    // weights: a tile is first of all one load latency and one pass of per-tile work, so a 64-token tile or a tile
-    // of the fp16 tier (read straight from global memory) counts three quarters of a 128-token tile
-    d.k_w = d.k_tile_tokens == 64 ? 3 : 4;
-    d.v_w = (b == 16 || d.v_tile_tokens == 64) ? 3 : 4;
-    if (d.k_tiles > 0 && P.k_first < 0) P.k_first = t;
-    if (d.v_tiles > 0 && P.v_first < 0) P.v_first = t;
+    d.v_chunk_tokens = VWARPS * (b == 8 ? 64 : b == 16 ? 16 : 128);  // one tile per warp
+    d.k_chunk0 = kc;
+    d.v_chunk0 = vc;
+    kc += static_cast<int>(ceil_div(d.n_k, d.k_chunk_tokens));
+    vc += static_cast<int>(ceil_div(d.n_v, d.v_chunk_tokens));
     nk_total += d.n_k;
     nv_total += d.n_v;
   }
@@ -681,83 +1641,25 @@ static int build_params(const hqkv_cache_desc_t* c, DecodeParams& P, Layout& lay
   }
   r.k_data = c->new_k;
   r.v_data = c->new_v;
-  r.k_tile_tokens = r.v_tile_tokens = 16;
-  r.k_tiles = r.v_tiles = static_cast<int>(ceil_div(c->n_new, 16));
-  r.k_w = r.v_w = 3;
-  if (r.k_tiles > 0 && P.k_first < 0) P.k_first = HQKV_NUM_TIERS;
-  if (r.v_tiles > 0 && P.v_first < 0) P.v_first = HQKV_NUM_TIERS;
+  r.k_chunk_tokens = KWARPS * 16;
+  r.v_chunk_tokens = VWARPS * 16;
+  r.k_chunk0 = kc;
+  r.v_chunk0 = vc;
+  kc += static_cast<int>(ceil_div(r.n_k, r.k_chunk_tokens));
+  vc += static_cast<int>(ceil_div(r.n_v, r.v_chunk_tokens));
   const int64_t L = ((sides & 1) ? nk_total : nv_total) + c->n_new;
   HQKV_REQUIRE(L > 0, "decode: the cache is empty");
   HQKV_REQUIRE(L < (1ll << 30), "decode: cache too long");
   P.L = static_cast<int>(L);
-  const bool rep8 = P.rep > 4;
+  P.nk_chunks = kc;
+  P.nv_chunks = vc;
   const int64_t BH = static_cast<int64_t>(c->B) * c->H;
-  const int ctas_per_sm = rep8 ? 1 : CTAS_PER_SM;
-#ifdef HQKV_X_GRID_PER_SM
-  const int max_cta = HQKV_X_GRID_PER_SM * sm_count();
-#else
-  const int max_cta = ctas_per_sm * sm_count();
-#endif
-  {
-    // Grouping.  Fewer pairs than CTAs: every pair gets a group of m CTAs, m chosen so that a warp holds about one
-    // tile of the longer side (and all groups fit the GPU at once: the wait between the K slices and the V slices
-    // relies on it).  When a warp holds at most one tile of a side, what a tile costs is its chain of latencies
-    // whatever its size: all tiles weigh the same; otherwise the weights above.
-    int64_t tk = 0, tv = 0;
-    for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
-      tk += P.tier[t].k_tiles;
-      tv += P.tier[t].v_tiles;
-    }
-    const int64_t tmax = tk > tv ? tk : tv;
-    const int m_cap = static_cast<int>(max_cta / BH);  // 0: more pairs than CTAs
-    const bool one_tile_per_warp = m_cap >= 1 && tmax <= static_cast<int64_t>(NWARPS) * m_cap;
-    for (int t = 0; t < NUM_ITEM_TIERS; ++t) {
-      TierDev& d = P.tier[t];
-      if (one_tile_per_warp) d.k_w = d.v_w = 1;
-      d.k_w0 = static_cast<int>(wk);
-      d.v_w0 = static_cast<int>(wv);
-      wk += static_cast<int64_t>(d.k_tiles) * d.k_w;
-      wv += static_cast<int64_t>(d.v_tiles) * d.v_w;
-    }
-    HQKV_REQUIRE(wk < (1ll << 27) && wv < (1ll << 27), "decode: cache too long");
-    P.wk = static_cast<int>(wk);
-    P.wv = static_cast<int>(wv);
-    const int64_t wmax = wk > wv ? wk : wv;
-    if (m_cap == 0) {
-      P.g_m = 0;
-      P.g_rem = 0;
-      lay.grid = max_cta;
-    } else {
-      const int64_t m_want = ceil_div(wmax, static_cast<int64_t>(NWARPS) * (one_tile_per_warp ? 1 : 3));
-      if (m_want <= m_cap) {
-        P.g_m = static_cast<int>(m_want < 1 ? 1 : m_want);
-        P.g_rem = 0;
-      } else {
-        P.g_m = m_cap;
-        P.g_rem = static_cast<int>(max_cta - BH * m_cap);  // that many pairs get one CTA more
-      }
-      lay.grid = static_cast<int>(BH * P.g_m + P.g_rem);
-    }
-    for (int j = 0; j < 2; ++j) {
-      const int m = P.g_m + j < 1 ? 1 : P.g_m + j;
-      P.g_inv[j] = 1.0f / static_cast<float>(m);
-      P.kq[j] = P.wk / m;
-      P.kr[j] = P.wk % m;
-      P.vq[j] = P.wv / m;
-      P.vr[j] = P.wv % m;
-    }
-  }
-  P.warp_smem = ws_bytes(rep8);
-  P.cta_smem = cta_shared_bytes(rep8);
-  lay.smem_bytes = P.cta_smem + NWARPS * P.warp_smem;
-  lay.ctas_per_sm = ctas_per_sm;
-  P.kc_max = static_cast<int>((ctas_per_sm * sm_count()) / BH) + 2;  // a group has at most max_cta / BH + 1 CTAs
   lay.acc_off = HQKV_WS_HEADER_BYTES;
   lay.logits_off = (lay.acc_off + static_cast<size_t>(BH) * P.rep * D * sizeof(double) + 255) & ~static_cast<size_t>(255);
   size_t off = lay.logits_off + static_cast<size_t>(c->B) * c->nh_q * L * sizeof(float);
   off = (off + 255) & ~static_cast<size_t>(255);
   lay.kpart_off = off;
-  off += static_cast<size_t>(BH) * P.kc_max * MAX_REP * sizeof(float2);
+  off += static_cast<size_t>(BH) * kc * MAX_REP * sizeof(float2);
   lay.total = (off + 255) & ~static_cast<size_t>(255);
   return HQKV_OK;
 }
@@ -830,14 +1732,13 @@ extern "C" int hqkv_decode_attention_gather(const hqkv_cache_desc_t* cache_host,
 static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                                void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream,
                                const void* probs_in, const void* mask, long long mask_bstride, long long mask_hstride) {
-  HQKV_REQUIRE(phases >= 1 && phases <= 3, "decode: phases must be 1 (K ranges), 2 (V ranges) or 3 (both)");
+  HQKV_REQUIRE(phases >= 1 && phases <= 3, "decode: phases must be 1 (K pass), 2 (V pass) or 3 (both)");
   DecodeParams P;
   Layout lay;
   // a K-only call whose logits are the result, and a V-only call on given weights, look at one side only
   const int sides = probs_in ? 2 : ((phases == 1 && !attn_output) ? 1 : 3);
   int rc = build_params(cache_host, P, lay, sides);
   if (rc) return rc;
-  P.phases = phases;
   P.n_peers = peers.n_peers;
   P.peer_flagged = peers.flagged ? 1 : 0;
   if (peers.flagged) P.peer_state = static_cast<unsigned*>(peers.state);
@@ -852,7 +1753,7 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
   HQKV_REQUIRE(workspace, "decode: null pointer");
   if (phases & 1) HQKV_REQUIRE(q && aligned(q, 4), "decode: q is null or not 4-byte aligned");
   if (phases & 2) HQKV_REQUIRE(attn_output && (attn_weights || probs_in), "decode: null pointer");
-  HQKV_REQUIRE(!probs_in || phases == 2, "decode: given weights go with the V ranges alone");
+  HQKV_REQUIRE(!probs_in || phases == 2, "decode: given weights go with the V pass alone");
   P.probs_in = static_cast<const __half*>(probs_in);
   HQKV_REQUIRE(!mask || (aligned(mask, 2) && mask_bstride >= 0 && mask_hstride >= 0), "decode: misaligned mask or negative stride");
   P.mask = static_cast<const __half*>(mask);
@@ -865,42 +1766,52 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
   P.q = static_cast<const __half*>(q);
   P.weights = static_cast<__half*>(attn_weights);
   P.out = static_cast<__half*>(attn_output);
-  P.kdone = reinterpret_cast<unsigned*>(ws + WS_KDONE_OFF);
-  P.vdone = reinterpret_cast<unsigned*>(ws + WS_VDONE_OFF);
-  P.status = reinterpret_cast<unsigned*>(ws + WS_STATUS_OFF);
+  P.counters = reinterpret_cast<unsigned*>(ws);
   P.logits = reinterpret_cast<float*>(ws + lay.logits_off);
   P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
   P.v_acc = reinterpret_cast<double*>(ws + lay.acc_off);
-  P.spin_limit = 1ll << 22;  // x ~0.1 us per poll: about half a second
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const unsigned BH = static_cast<unsigned>(P.B * P.H);
+  HQKV_REQUIRE(P.nk_chunks <= 65535 && P.nv_chunks <= 65535, "decode: too many chunks");
   {
     // opt in to >48 KB of dynamic shared memory once per device
     static bool attr_set[64] = {};
     int dev = 0;
     HQKV_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !attr_set[dev]) {
-      HQKV_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     cta_shared_bytes(true) + NWARPS * ws_bytes(true)));
-      // two CTAs per SM need nearly all of the SM's shared memory: ask for the largest carve-out
-      HQKV_CUDA(cudaFuncSetAttribute(decode_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                     static_cast<int>(cudaSharedmemCarveoutMaxShared)));
+      HQKV_CUDA(cudaFuncSetAttribute(v_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(sizeof(VShared))));
+      HQKV_CUDA(cudaFuncSetAttribute(k_pass_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(sizeof(KShared))));
       if (dev >= 0 && dev < 64) attr_set[dev] = true;
     }
   }
-  // programmatic stream serialisation: the grid may start while the kernel before it drains, if that
-  // kernel allows it (the previous decode call does); everything it does before its
-  // griddepcontrol.wait reads only the cache tiers
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(lay.grid);
-  cfg.blockDim = dim3(NTHREADS);
-  cfg.dynamicSmemBytes = lay.smem_bytes;
-  cfg.stream = st;
+  // Both launches use programmatic stream serialisation: a grid may place its CTAs while the kernel before it
+  // drains (if that kernel allows it - both of these do), and everything it does before its
+  // griddepcontrol.wait reads only the cache tiers.
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  HQKV_CUDA(cudaLaunchKernelEx(&cfg, decode_kernel, P));
+  if ((phases & 1) && P.nk_chunks > 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(BH, P.nk_chunks);
+    cfg.blockDim = dim3(KTHREADS);
+    cfg.dynamicSmemBytes = sizeof(KShared);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HQKV_CUDA(cudaLaunchKernelEx(&cfg, k_pass_kernel, P));
+  }
+  if ((phases & 2) && P.nv_chunks > 0) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(BH, P.nv_chunks);
+    cfg.blockDim = dim3(VTHREADS);
+    cfg.dynamicSmemBytes = sizeof(VShared);
+    cfg.stream = st;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    HQKV_CUDA(cudaLaunchKernelEx(&cfg, v_pass_kernel, P));
+  }
   return HQKV_OK;
 }
 
@@ -909,18 +1820,23 @@ extern "C" int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const 
   return hqkv_decode_attention_phases(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, stream);
 }
 
+extern "C" int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host, const void* q, const void* mask,
+                                            int64_t mask_b_stride, int64_t mask_h_stride, void* attn_weights,
+                                            void* attn_output, void* workspace, size_t workspace_bytes, void* stream) {
+  HQKV_REQUIRE(mask != nullptr, "decode_masked: null mask");
+  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
+                       nullptr, mask, mask_b_stride, mask_h_stride);
+}
+
 // ------------------------------------------------------------------------------------------------
-// The two halves as operators of their own: raw logits of every tier, and the product of given weights with V
+// The two passes as operators of their own: raw logits of every tier, and the product of given weights with V
 // ------------------------------------------------------------------------------------------------
 namespace hqkv {
-// fp32 logits of the scratch -> fp16 rows; the arrival counters of the K ranges go back to zero
-__global__ void __launch_bounds__(256) logits_out_kernel(const float* logits, __half* out, int64_t n, unsigned* kdone, int bh) {
-  asm volatile("griddepcontrol.wait;" ::: "memory");
+// fp32 logits of the scratch -> fp16 rows
+__global__ void __launch_bounds__(256) logits_out_kernel(const float* logits, __half* out, int64_t n) {
   const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
   for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n; i += stride)
     out[i] = __float2half_rn(__ldcg(logits + i));
-  if (blockIdx.x == 0)
-    for (int i = threadIdx.x; i < bh; i += blockDim.x) kdone[i] = 0u;
 }
 }  // namespace hqkv
 
@@ -933,12 +1849,11 @@ extern "C" int hqkv_decode_logits(const hqkv_cache_desc_t* cache_host, const voi
   Layout lay;
   rc = build_params(cache_host, P, lay, 1);
   if (rc) return rc;
-  unsigned char* ws = static_cast<unsigned char*>(workspace);
   const int64_t n = static_cast<int64_t>(P.B) * P.nh_q * P.L;
   const int blocks = static_cast<int>(n / 2048 > 592 ? 592 : (n / 2048 > 0 ? n / 2048 : 1));
   hqkv::logits_out_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const float*>(ws + lay.logits_off), static_cast<__half*>(logits_f16), n,
-      reinterpret_cast<unsigned*>(ws + WS_KDONE_OFF), P.B * P.H);
+      reinterpret_cast<const float*>(static_cast<unsigned char*>(workspace) + lay.logits_off),
+      static_cast<__half*>(logits_f16), n);
   HQKV_LAUNCH_CHECK("decode_logits");
   return HQKV_OK;
 }
@@ -947,7 +1862,7 @@ extern "C" int hqkv_decode_weighted_sum(const hqkv_cache_desc_t* cache_host, con
                                         void* workspace, size_t workspace_bytes, void* stream) {
   HQKV_REQUIRE(weights_f16 && aligned(weights_f16, 2), "decode_weighted_sum: null or misaligned weights");
   {
-    // no K ranges run in this call, so nobody clears the output accumulators: a stream-ordered memset does
+    // no K pass runs in this call, so nobody clears the output accumulators: a stream-ordered memset does
     DecodeParams P;
     Layout lay;
     int rc = build_params(cache_host, P, lay, 2);
@@ -957,14 +1872,6 @@ extern "C" int hqkv_decode_weighted_sum(const hqkv_cache_desc_t* cache_host, con
                               static_cast<cudaStream_t>(stream)));
   }
   return decode_launch(cache_host, nullptr, nullptr, out, workspace, workspace_bytes, 2, hqkv::PeerArgs(), stream, weights_f16);
-}
-
-extern "C" int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host, const void* q, const void* mask,
-                                            int64_t mask_b_stride, int64_t mask_h_stride, void* attn_weights,
-                                            void* attn_output, void* workspace, size_t workspace_bytes, void* stream) {
-  HQKV_REQUIRE(mask != nullptr, "decode_masked: null mask");
-  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
-                       nullptr, mask, mask_b_stride, mask_h_stride);
 }
 
 namespace hqkv {
@@ -990,23 +1897,13 @@ extern "C" int hqkv_check_failures(int reset, unsigned* count_host) {
   return HQKV_OK;
 }
 
-extern "C" int hqkv_decode_status(const void* workspace, void* stream, int* status_host) {
-  HQKV_REQUIRE(workspace && status_host, "decode_status: null pointer");
-  unsigned v = 0;
-  HQKV_CUDA(cudaMemcpyAsync(&v, static_cast<const unsigned char*>(workspace) + WS_STATUS_OFF, sizeof(v),
-                            cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
-  HQKV_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
-  *status_host = static_cast<int>(v);
-  return HQKV_OK;
-}
-
 // ------------------------------------------------------------------------------------------------
 // Decode attention for callers that may not allocate device memory
 // ------------------------------------------------------------------------------------------------
 // Some hosts of this library cannot obtain scratch at call time: a serving loop that has handed all
 // of the GPU's memory to its own pool, a latency-critical loop whose rules forbid allocation after
 // start-up (cudaMalloc may synchronise the device, and may fail late), or a binding whose language
-// runtime owns no device allocator.  For them the scratch of the decode kernel lives in this
+// runtime owns no device allocator.  For them the scratch of the two decode kernels lives in this
 // fixed array, which every GPU that loads the library holds until the process exits.
 //
 // g_static_scratch names the array in DEVICE code.  In host code the same identifier is only a
@@ -1047,10 +1944,10 @@ extern "C" int hqkv_decode_attention_static(const hqkv_cache_desc_t* cache_host,
   void* scratch = nullptr;
   int rc = static_scratch_address(&scratch);
   if (rc) return rc;
-  // The array keeps whatever the previous call left.  Only the arrival counters and the status word have
-  // to start at zero; a finished call leaves them zero, an aborted one might not, so they are cleared
-  // every time (a stream-ordered memset, not an allocation).
-  HQKV_CUDA(cudaMemsetAsync(scratch, 0, hqkv_decode_workspace_zero_bytes(cache_host), static_cast<cudaStream_t>(stream)));
+  // The array keeps whatever the previous call left.  Only the arrival counters have to start at
+  // zero; a finished call leaves them zero, an aborted one might not, so they are cleared every time
+  // (a stream-ordered memset, not an allocation).
+  HQKV_CUDA(cudaMemsetAsync(scratch, 0, HQKV_WS_HEADER_BYTES, static_cast<cudaStream_t>(stream)));
   return hqkv_decode_attention(cache_host, q, attn_weights, attn_output, scratch, HQKV_STATIC_SCRATCH_BYTES, stream);
 }
 
@@ -1098,8 +1995,8 @@ extern "C" int hqkv_peer_barrier(void* const* peer_pads_host, int rank, int worl
 // ------------------------------------------------------------------------------------------------
 // Flagged exchange: the low-latency form of the kv-head-sharded gather
 // ------------------------------------------------------------------------------------------------
-// hqkv_decode_attention_gather_flagged makes the decode kernel store every pair of output values together
-// with the call number as ONE 8-byte word into the peers' receive buffers: a word whose flag equals the
+// hqkv_decode_attention_gather_flagged makes the V pass store every pair of output values together with
+// the call number as ONE 8-byte word into the peers' receive buffers: a word whose flag equals the
 // call number is complete, so no fence, no signal and no round trip is needed - the exchange costs
 // one NVLink store latency.  hqkv_peer_unpack, enqueued by every rank right after, polls its own
 // receive buffer (bounded), strips the flags into the plain gathered buffer [world][entries] of fp16

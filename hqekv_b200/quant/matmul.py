@@ -140,7 +140,7 @@ def cuda_bmm_forward_qk_group_hq(group_size, nh_kv, in_vector, matrix_16, matrix
                                  zeros_8, matrix_4, matrix_4_idx, scales_4, zeros_4, matrix_2, matrix_2_idx, scales_2,
                                  zeros_2, matrix_1, matrix_1_idx, std_1, means_1, new_K):
     """quant/matmul.py:351-434: raw q.K^T over every K tier (uniform-group 8 / 4 / 2 bit, Gaussian-codebook 1 bit,
-    fp16 tier) and the residual window, each token's product written at its logical position; one launch.
+    fp16 tier) and the residual window, each token's product written at its logical position; one K pass.
     in_vector [B, nh_q, 1, D] fp16; tiers in the cache layout ([B, nh_kv, D, n * bits / 32]); returns
     [B, nh_q, 1, L] fp16 (not yet divided by sqrt(head_dim), as in the reference)."""
     tiers = [(16, matrix_16, matrix_16_idx, None, None), (8, matrix_8, matrix_8_idx, scales_8, zeros_8),
@@ -161,7 +161,7 @@ def cuda_bmm_forward_wv_group_hq(group_size, nh_kv, in_vector, matrix_16, matrix
                                  zeros_8, matrix_4, matrix_4_idx, scales_4, zeros_4, matrix_2, matrix_2_idx, scales_2,
                                  zeros_2, matrix_1, matrix_1_idx, std_1, means_1, new_V):
     """quant/matmul.py:507-579: sum over all cached tokens of weight x dequantised V row, the weight of a token
-    read at its logical position; one launch.  in_vector [B, nh_q, 1, L] fp16; V tiers in the cache layout
+    read at its logical position; one V pass.  in_vector [B, nh_q, 1, L] fp16; V tiers in the cache layout
     ([B, nh_kv, n, D * bits / 32]); returns [B, nh_q, 1, D] fp16."""
     tiers = [(16, matrix_16, matrix_16_idx, None, None), (8, matrix_8, matrix_8_idx, scales_8, zeros_8),
              (4, matrix_4, matrix_4_idx, scales_4, zeros_4), (2, matrix_2, matrix_2_idx, scales_2, zeros_2),

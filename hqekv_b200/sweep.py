@@ -4,7 +4,7 @@
 
 For every point (context, tier mix, group size, batch) a model-shaped stack of 32 layer caches is built
 (8 kv heads x head_dim 128, GQA 4, fp16 N(0,1) data, K with outlier channels, residual 128, no eviction)
-and the whole decode call and its K ranges alone are replayed from CUDA graphs and timed with CUDA
+and the whole decode call and each of its two passes alone are replayed from CUDA graphs and timed with CUDA
 events.  Reported per point: microseconds per layer, achieved GB/s on the algorithmic bytes and the
 fraction of the measured copy bandwidth.  Small contexts fit the 126 MB L2 across layers; the line says
 so (`working_set_MB`).  One JSON object per line.
@@ -73,13 +73,9 @@ def decode_point(dev, ctx, mix, group, batch, layers, peak_gbs):
     run(3)
     out = {"kind": "decode", "context": ctx, "tiers": mix, "group": group, "batch": batch, "layers": layers,
            "cache_MB_per_layer": nbytes / 1e6, "working_set_MB": nbytes * layers / 1e6}
-    # the whole call (one launch per layer) and its K ranges alone; a series of K-only calls leaves the arrival
-    # counters raised, so it is followed by one V-only call per layer, which puts them back to zero
-    for phase, name in ((3, "step"), (1, "k_ranges")):
+    # the whole call (two launches per layer) and each of its passes alone
+    for phase, name in ((3, "step"), (1, "k_pass"), (2, "v_pass")):
         us = _graph_time(lambda: run(phase), 5) * 1e3 / layers
-        if phase == 1:
-            run(2)
-            torch.cuda.synchronize()
         b = nbytes / 2 if phase < 3 else nbytes
         out[f"{name}_us"] = us
         out[f"{name}_GBps"] = b / us / 1e3

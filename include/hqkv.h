@@ -38,6 +38,11 @@ const char* hqkv_last_error(void);
 /* Library version: major*10000 + minor*100 + patch. */
 int hqkv_version(void);
 
+/* Which sources this binary was compiled from: the first 16 hex digits of the SHA-256 over the library's
+ * source files (csrc, sorted by name) and this header, stamped at build time by hqekv_b200/build.py
+ * ("unstamped" for a build made another way).  A host compares it with the hash of the sources it has. */
+const char* hqkv_build_id(void);
+
 /*
  * Bounds-check build.  A library compiled with -DHQKV_CHECKS (python -m hqekv_b200.build --checks writes
  * libhqkv_checked.so) range-checks every index it takes out of a caller-supplied list - the logical positions in
@@ -146,16 +151,17 @@ typedef struct {
 
 /* Bytes of scratch hqkv_decode_attention needs for this cache on the current device (0 on invalid input). */
 size_t hqkv_decode_workspace_bytes(const hqkv_cache_desc_t* cache_host);
-/* Leading part of that scratch (arrival counters, status word) that must be zero before a call:
+/* Leading part of that scratch (arrival counters) that must be zero before a call:
  * HQKV_WS_HEADER_BYTES whatever the cache; 0 on invalid input. */
 size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cache_host);
 
 /*
  * One decode step of attention over the whole tiered cache: q.K^T for every tier with the
  * packed codes dequantised in registers, softmax in fp32, p.V for every tier, plus the fp16
- * residual window and the fp16 tier, in ONE kernel launch (a persistent grid: every warp takes a
- * range of K tiles, waits - bounded - until the K side of its (batch, kv head) pairs is complete, then
- * takes a range of V tiles).  Stands in for qkv_matmul_hqe_2
+ * residual window and the fp16 tier.  Two launches chained by programmatic dependent launch: the K pass
+ * (logits of every cached token at its logical position, one softmax pair per CTA) and the V pass (folds the
+ * pairs, writes the probabilities, accumulates p.V; the last CTA of a (batch, kv head) normalises and
+ * writes).  Stands in for qkv_matmul_hqe_2
  * (quant/hqe_matmul.py:354-451) and everything below it: the layout glue of
  * cuda_bmm_fA_qB_uniform_group (quant/matmul.py:263-299), gemv_forward_cuda_uniform_group and
  * bgemv_kernel_uniform_group_{8,4,2} (quant/csrc/gemv_cuda_uniform.cu:1533-1599, 411-733), the
@@ -165,23 +171,19 @@ size_t hqkv_decode_workspace_zero_bytes(const hqkv_cache_desc_t* cache_host);
  *   attn_weights fp16 [B, nh_q, 1, L]   L = sum_t n_k + n_new; normalised probabilities at logical positions
  *   attn_output  fp16 [B, nh_q, 1, D]
  *   workspace    at least hqkv_decode_workspace_bytes() bytes, 256-byte aligned.  Zero its first
- *                HQKV_WS_HEADER_BYTES bytes once after allocating it: they hold arrival counters and a
- *                status word, and every call that completes leaves them zero again, so one workspace
+ *                HQKV_WS_HEADER_BYTES bytes once after allocating it: they hold the arrival counters of the V
+ *                pass, and every call that completes leaves them zero again, so one workspace
  *                serves calls on caches of any shape.  Calls that share a workspace must be ordered on
  *                one stream.
  * The K-side and V-side token counts of a tier may differ only in order, not in total
  * (sum n_k == sum n_v).  A 1-bit tier is read in the codec its `codec` field names.
  *
- * Ordering contract for callers that chain kernels with programmatic dependent launch: the kernel
- * reads the cache tiers (codes, scales, zeros, index lists) BEFORE it waits for the kernels ahead of it
+ * Ordering contract for callers that chain kernels with programmatic dependent launch: both kernels
+ * read the cache tiers (codes, scales, zeros, index lists) BEFORE they wait for the kernels ahead of them
  * in the stream; q, the residual window and the scratch are read after that wait.  A kernel
  * that writes a tier must therefore have completed (not merely have triggered its dependents) before
  * a decode call on the same stream is launched; an ordinary launch always satisfies this.
- *
- * All CTAs of the launch must be resident at once (the grid is sized for an otherwise idle GPU: two
- * CTAs per SM).  If other work keeps SMs occupied for longer than the spin limit (about half a second)
- * the waiting CTAs give up, record 1 + (batch * H + kv head) in the status word and finish with an
- * invalid result - no trap, no endless loop; hqkv_decode_status reads that word.
+ * Neither kernel waits on another CTA, so the call makes no demand on how many CTAs are resident.
  */
 #define HQKV_WS_HEADER_BYTES 12288
 int hqkv_decode_attention(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
@@ -198,17 +200,9 @@ int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host, const void
                                  void* workspace, size_t workspace_bytes, void* stream);
 
 /*
- * Status word of a decode workspace: synchronises `stream`, then *status_host = 0 (every call since the
- * workspace was zeroed met its waits) or 1 + the (batch, kv head) pair whose K side was not complete
- * in time.  No counterpart in the reference (its kernels do not wait on one another).
- */
-int hqkv_decode_status(const void* workspace, void* stream, int* status_host);
-
-/*
- * The same call restricted to one half of the work: phases = 1 runs the K ranges only (logits and
- * per-CTA softmax statistics into the workspace), 2 the V ranges only (needs the workspace a K-only
- * call of the same cache left), 3 both.  A K-only call must be followed by a V-only call on the same
- * workspace before the next full call (the V ranges put the arrival counters back to zero).  Serves
+ * The same call restricted to one of its launches: phases = 1 runs the K pass only (logits and
+ * per-CTA softmax statistics into the workspace), 2 the V pass only (needs the workspace a K-only
+ * call of the same cache left), 3 both.  Serves
  * cuda_bmm_forward_qk_group_hq / cuda_bmm_forward_wv_group_hq style callers and the timing of the two
  * halves; the split itself has no counterpart in the reference.
  */
@@ -217,8 +211,8 @@ int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void
 
 /*
  * The K half as an operator of its own: out[b, h, 0, pos] = fp16(softmax_scale * q_h . K^_pos) for every cached
- * token at its logical position, all tiers and the residual window in one launch (pass softmax_scale = 1 for the
- * raw product).  Stands in for cuda_bmm_forward_qk_group_hq (quant/matmul.py:351-434) =
+ * token at its logical position, all tiers and the residual window in one K pass plus a conversion of the
+ * scratch row to fp16 (pass softmax_scale = 1 for the raw product).  Stands in for cuda_bmm_forward_qk_group_hq (quant/matmul.py:351-434) =
  * kvhq_gemv.gemv_forward_cuda_qk_group_hq (quant/csrc/gemv_cuda.h:78-109), and with identity index lists for
  * the _seq forms (quant/matmul.py:436-505, gemv_cuda.h:111-137).  logits_f16: fp16 [B, nh_q, 1, L].  Workspace as for
  * hqkv_decode_attention; the call leaves it ready for any other call.
@@ -296,7 +290,7 @@ int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int 
  *    may be the one that loads the library's module onto the device, which is when the array itself
  *    is placed (CUDA_MODULE_LOADING=EAGER moves that to context creation).
  *  - All calls on a device share the one array, which keeps the previous call's contents (the
- *    arrival counters and the status word are cleared by a stream-ordered
+ *    arrival counters are cleared by a stream-ordered
  *    memset at the start of every call; that memset sits between the previous kernel and this one, so
  *    this entry point gives up the overlap of consecutive decode kernels that the regular one has).
  *    Two calls that overlap on the GPU, e.g. on different streams, race on it: order them on one

@@ -394,16 +394,6 @@ def test_decode_batch64_vs_oracle(ops, cuda_device):
     check_attention(ops, cache, q, 32, 32, "batch 64")
 
 
-def test_decode_status_word_stays_zero(ops, cuda_device):
-    """After all the calls above every wait of the decode kernel was met: the status word of the scratch is 0."""
-    import ctypes
-    from hqekv_b200 import _lib
-    for key, ws in _lib._decode_ws.items():
-        st = ctypes.c_int(-1)
-        _lib.check(_lib.lib.hqkv_decode_status(ws.data_ptr(), None, ctypes.byref(st)))
-        assert st.value == 0, f"workspace {key}: status {st.value}"
-
-
 def test_decode_errors(ops, cuda_device):
     q = torch.zeros(1, 4, 1, 128, dtype=torch.float16, device=cuda_device)
     with pytest.raises(ValueError, match="invalid quant_strategy"):
