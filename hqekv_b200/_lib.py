@@ -61,6 +61,8 @@ _SIGNATURES = {
     "hqkv_unpack": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int, C.c_void_p, C.c_void_p]),
     "hqkv_decode_workspace_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
     "hqkv_decode_workspace_zero_bytes": (C.c_size_t, [C.POINTER(CacheDesc)]),
+    "hqkv_decode_attention_headsum": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
+                                              C.c_void_p, C.c_size_t, C.c_void_p]),
     "hqkv_decode_logits": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     "hqkv_decode_weighted_sum": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t,
                                            C.c_void_p]),

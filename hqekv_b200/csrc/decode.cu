@@ -23,10 +23,6 @@
 
 #include "common.cuh"
 
-#define HQKV_STR2(x) #x
-#define HQKV_STR(x) HQKV_STR2(x)
-#define HQKV_UNROLL(n) _Pragma(HQKV_STR(unroll n))
-
 namespace hqkv {
 
 HQKV_DEFINE_CHECK_COUNTER
@@ -60,6 +56,8 @@ struct DecodeParams {
   const __half* mask;      // additive mask on the logits (null: none); element (b, head, pos) at b*bstride + head*hstride + pos
   long long mask_bstride, mask_hstride;
   const __half* probs_in;  // V pass on caller-supplied weights [B*nh_q][L] (null: softmax of the scratch logits)
+  __half* head_sum;        // [L] sum of the probabilities over batch and heads, written by the V pass (null: not wanted)
+  unsigned* hs_count;      // [nv_chunks] arrival counters of that sum
   __half* weights;
   __half* out;
   float* logits;   // [B*nh_q][L]
@@ -212,12 +210,7 @@ __device__ __forceinline__ void softmax_merge(float& m, float& l, float m2, floa
 //    the dequantised K value - costs ~2e-3 on the attention output with x10 outlier channels.)
 //  * the zero point enters through Zq[group][head] = sum_c zero_c * q_c, one small MMA per tile;
 //  * every lane scatters its own logits from registers and keeps a running (max, sum-exp).
-#ifndef K_MIN_CTAS
-#define K_MIN_CTAS 4
-#endif
-#ifndef K_KK_UNROLL
-#define K_KK_UNROLL 1  // iterations of the two-step loop unrolled together
-#endif
+constexpr int K_MIN_CTAS = 4;  // CTAs per SM the K pass is compiled for
 constexpr int KWARPS = 4;
 constexpr int KTHREADS = KWARPS * 32;
 constexpr int K_SPAN = 64;                   // tokens per sub-span: four M-tiles of 16
@@ -526,7 +519,7 @@ __device__ __forceinline__ void k_tile_compute(const DecodeParams& P, const Tier
       for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
       // two 16-channel steps per iteration (short loop body: the instruction cache is cold in every CTA
       // when the whole cache is one wave of CTAs)
-HQKV_UNROLL(K_KK_UNROLL)
+#pragma unroll 1
       for (int kk = 0; kk < 4; ++kk) {
         if (hh == 0 && j == 0) {  // the codes arrive two steps at a time
           if (kk == 0) cp_async_wait<3>();
@@ -639,16 +632,21 @@ HQKV_UNROLL(K_KK_UNROLL)
         float* row = row0 + static_cast<int64_t>(head) * P.L;
         const __half* mrow = mask0 ? mask0 + head * P.mask_hstride : nullptr;
         float x[4];
+        bool ok[4];
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float unscale = static_cast<float>(1 << (24 - KField<BITS>::shift(i)));
-          const bool ok = on && HQKV_INDEX_OK(pos[i], P.L);
-          x[i] = ok ? fmaf(val[i][e], pscale * unscale, zqs) : -INFINITY;
-          if (ok) {
-            if (mrow) x[i] += __half2float(mrow[pos[i]]);
-            row[pos[i]] = x[i];
-          }
+          ok[i] = on && HQKV_INDEX_OK(pos[i], P.L);
+          x[i] = ok[i] ? fmaf(val[i][e], pscale * unscale, zqs) : -INFINITY;
         }
+        if (mrow) {  // one branch for the calls without a mask
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+            if (ok[i]) x[i] += __half2float(mrow[pos[i]]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if (ok[i]) row[pos[i]] = x[i];
         softmax_push4(m[hh][e], l[hh][e], x);
       }
     }
@@ -922,12 +920,7 @@ __global__ void __launch_bounds__(KTHREADS, K_MIN_CTAS) k_pass_kernel(const __gr
 // group - is folded into the B operand: out[h][c] = sum_t (p_t * scale_t,G) * code_t,c + sum_t p_t *
 // zero_t,G, with p*scale carried exactly as hi + lo and B columns 0-3 / 4-7 holding the two channel
 // groups of a 64-channel half.  The zero term is one small MMA per step (rows = groups).
-#ifndef V_MIN_CTAS
-#define V_MIN_CTAS 4
-#endif
-#ifndef V_STEP_UNROLL
-#define V_STEP_UNROLL 1  // 16-token steps unrolled together
-#endif
+constexpr int V_MIN_CTAS = 4;  // CTAs per SM the V pass is compiled for
 constexpr int VWARPS = 4;
 constexpr int VTHREADS = VWARPS * 32;
 constexpr int V_MAX_TT = 128;                 // tokens per tile at most
@@ -1122,7 +1115,7 @@ __device__ __forceinline__ void v_tile_walk(const DecodeParams& P, VWarpShared& 
   float sacc[4] = {0.f, 0.f, 0.f, 0.f};  // Gaussian-codebook tier: sum_t p * std per channel group
 
   const int nsteps = ntok >> 4;
-HQKV_UNROLL(V_STEP_UNROLL)
+#pragma unroll 1
   for (int st = 0; st < nsteps; ++st) {
     const int t0 = st * 16;
     // B operands: p pairs of tokens (2tig, 2tig+1) and (+8, +9); scales of the same tokens
@@ -1536,6 +1529,39 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
       }
     }
   }
+  // ---- importance row: sum of the probabilities over batch, then over heads, for the tokens of this chunk.
+  //      The CTAs of all (batch, kv head) pairs that hold this chunk index wrote these tokens' probabilities; the
+  //      last of them to arrive adds them in fixed order with the roundings of attn_weights.sum(0).sum(0) on fp16
+  //      tensors (fp32 accumulation, one fp16 rounding per sum; model/public_func.py:253-254 of the reference).
+  if (P.head_sum) {
+    __threadfence();  // this CTA's probabilities
+    __syncthreads();
+    if (tid == 0) {
+      const unsigned prev = atomicAdd(&P.hs_count[chunk], 1u);
+      sh.is_last = (prev == static_cast<unsigned>(P.B * P.H) - 1u) ? 1u : 0u;
+      if (sh.is_last) P.hs_count[chunk] = 0u;  // ready for the next call
+    }
+    __syncthreads();
+    if (sh.is_last) {
+      __threadfence();
+      const int c0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
+      const int n = min(T.v_chunk_tokens, T.n_v - c0);
+      for (int t = tid; t < n; t += VTHREADS) {
+        const int64_t pos = is_res ? static_cast<int64_t>(P.L) - T.n_v + c0 + t : T.v_idx[c0 + t];
+        if (!HQKV_INDEX_OK(pos, P.L)) continue;
+        const unsigned short* w = reinterpret_cast<const unsigned short*>(P.weights) + pos;
+        float over_heads = 0.f;
+#pragma unroll 4
+        for (int h = 0; h < P.nh_q; ++h) {
+          float over_batch = 0.f;
+          for (int bb = 0; bb < P.B; ++bb)
+            over_batch = __fadd_rn(over_batch, __half2float(__ushort_as_half(__ldcg(w + (static_cast<int64_t>(bb) * P.nh_q + h) * P.L))));
+          over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch)));
+        }
+        P.head_sum[pos] = __float2half_rn(over_heads);
+      }
+    }
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1695,7 +1721,10 @@ struct PeerArgs {
 static int decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                          void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream,
                          const void* probs_in = nullptr, const void* mask = nullptr, long long mask_bstride = 0,
-                         long long mask_hstride = 0);
+                         long long mask_hstride = 0, void* head_sum = nullptr);
+// the V pass emits the importance row itself up to these sizes (a CTA reads B*nh_q probabilities per token)
+constexpr int HEAD_SUM_MAX_ROWS = 64;
+constexpr int HEAD_SUM_MAX_CHUNKS = (HQKV_WS_HEADER_BYTES - 4096) / 4;
 }
 
 extern "C" int hqkv_decode_attention_phases(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
@@ -1731,7 +1760,8 @@ extern "C" int hqkv_decode_attention_gather(const hqkv_cache_desc_t* cache_host,
 
 static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                                void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream,
-                               const void* probs_in, const void* mask, long long mask_bstride, long long mask_hstride) {
+                               const void* probs_in, const void* mask, long long mask_bstride, long long mask_hstride,
+                               void* head_sum) {
   HQKV_REQUIRE(phases >= 1 && phases <= 3, "decode: phases must be 1 (K pass), 2 (V pass) or 3 (both)");
   DecodeParams P;
   Layout lay;
@@ -1767,6 +1797,8 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
   P.weights = static_cast<__half*>(attn_weights);
   P.out = static_cast<__half*>(attn_output);
   P.counters = reinterpret_cast<unsigned*>(ws);
+  P.hs_count = reinterpret_cast<unsigned*>(ws + 4096);
+  P.head_sum = static_cast<__half*>(head_sum);
   P.logits = reinterpret_cast<float*>(ws + lay.logits_off);
   P.k_part = reinterpret_cast<float2*>(ws + lay.kpart_off);
   P.v_acc = reinterpret_cast<double*>(ws + lay.acc_off);
@@ -1826,6 +1858,22 @@ extern "C" int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host,
   HQKV_REQUIRE(mask != nullptr, "decode_masked: null mask");
   return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
                        nullptr, mask, mask_b_stride, mask_h_stride);
+}
+
+extern "C" int hqkv_decode_attention_headsum(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                             void* attn_output, void* head_sum_row, void* workspace,
+                                             size_t workspace_bytes, void* stream) {
+  HQKV_REQUIRE(head_sum_row && aligned(head_sum_row, 2), "decode_headsum: null or misaligned row");
+  DecodeParams P;
+  Layout lay;
+  int rc = build_params(cache_host, P, lay);
+  if (rc) return rc;
+  const bool fused = P.B * P.nh_q <= HEAD_SUM_MAX_ROWS && P.nv_chunks <= HEAD_SUM_MAX_CHUNKS;
+  rc = decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
+                     nullptr, nullptr, 0, 0, fused ? head_sum_row : nullptr);
+  if (rc || fused) return rc;
+  // larger batches: one more launch over the probabilities just written
+  return hqkv_head_sum(attn_weights, P.B, P.nh_q, P.L, P.L, head_sum_row, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -114,6 +114,19 @@ class last_attn_weights:
     def set_max_length(self, max_length: int):
         self.max_length = max_length
 
+    def decode_row(self, device) -> torch.Tensor:
+        """The ring row that the head sum of the next decode step belongs in, for a decode call that writes it
+        itself (``qkv_matmul_hqe_2(..., head_sum_out=row)``, which refuses a row shorter than the cache); follow
+        it with ``advance(L)``.  The pair does what ``update`` does on a decode step (:253-255) without a pass of
+        its own over the probabilities."""
+        if self.weights is None:
+            self.weights = torch.zeros(self.last_length, self.max_length, dtype=torch.float16, device=device)
+        return self.weights[self.next_line]
+
+    def advance(self, L: int):
+        self.kv_seq_len = L
+        self.next_line = (self.next_line + 1) % self.last_length
+
     def update(self, attn_weights: torch.Tensor):
         cap = self.max_length if self.weights is None else self.weights.shape[1]
         if attn_weights.shape[-1] > cap:

@@ -12,8 +12,12 @@ from ._cache import UNIFORM_STRATEGIES, cached_cache_desc
 
 
 def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: torch.Tensor, head_dim: int,
-                     quant_strategy: str, block_size: int = 32, group_size: int = 32):
+                     quant_strategy: str, block_size: int = 32, group_size: int = 32, *, head_sum_out=None):
     """softmax(q K^T / sqrt(d)) V over all tiers and the fp16 residual window.
+
+    ``head_sum_out`` (keyword only, not in the reference's signature): a float16 row of at least L elements that
+    receives ``attn_weights.sum(0).sum(0)`` - the importance row last_attn_weights.update would compute from the
+    result (model/public_func.py:253-254) - written by the decode call itself.
 
     q [B, nh_q, 1, D] float16; ``past_key_value`` the 42-slot tuple.  ``attention_mask`` is accepted
     and ignored, as on the reference path (its use is commented out at quant/hqe_matmul.py:431);
@@ -39,22 +43,30 @@ def qkv_matmul_hqe_2(q: torch.Tensor, past_key_value: Tuple, attention_mask: tor
     B, nh_q, D = q.shape[0], q.shape[1], q.shape[3]
     attn_weights = torch.empty(B, nh_q, 1, L, dtype=torch.float16, device=dev)
     attn_output = torch.empty(B, nh_q, 1, D, dtype=torch.float16, device=dev)
+    if head_sum_out is not None:
+        if (head_sum_out.dtype != torch.float16 or head_sum_out.device != dev or head_sum_out.dim() != 1
+                or head_sum_out.numel() < L or head_sum_out.stride(0) != 1):
+            raise ValueError("head_sum_out must be a contiguous float16 row of at least L elements on the cache's device")
     if dev.index is None or dev.index == torch.cuda.current_device():
-        _launch(desc, q, attn_weights, attn_output, dev)
+        _launch(desc, q, attn_weights, attn_output, dev, head_sum_out)
     else:
         with torch.cuda.device(dev):
-            _launch(desc, q, attn_weights, attn_output, dev)
+            _launch(desc, q, attn_weights, attn_output, dev, head_sum_out)
     return attn_weights, attn_output
 
 
-def _launch(desc, q, attn_weights, attn_output, dev):
+def _launch(desc, q, attn_weights, attn_output, dev, head_sum_out=None):
     need = lib.hqkv_decode_workspace_bytes(desc)
     if need == 0:
         _raise_from_status(lib.hqkv_decode_attention(desc, ptr(q), ptr(attn_weights), ptr(attn_output), None, 0, None))
     st = stream_ptr(dev)
     ws = decode_workspace(dev, need, st)
-    rc = lib.hqkv_decode_attention(desc, q.data_ptr(), attn_weights.data_ptr(), attn_output.data_ptr(), ws.data_ptr(),
-                                   ws.numel(), st)
+    if head_sum_out is None:
+        rc = lib.hqkv_decode_attention(desc, q.data_ptr(), attn_weights.data_ptr(), attn_output.data_ptr(), ws.data_ptr(),
+                                       ws.numel(), st)
+    else:
+        rc = lib.hqkv_decode_attention_headsum(desc, q.data_ptr(), attn_weights.data_ptr(), attn_output.data_ptr(),
+                                               head_sum_out.data_ptr(), ws.data_ptr(), ws.numel(), st)
     if rc:
         _raise_from_status(rc)
 

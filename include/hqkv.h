@@ -200,6 +200,19 @@ int hqkv_decode_attention_masked(const hqkv_cache_desc_t* cache_host, const void
                                  void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * hqkv_decode_attention that also writes the importance row of the step: head_sum_row[pos] (fp16 [L]) =
+ * attn_weights.sum(0).sum(0) with the roundings of fp16 tensors (fp32 accumulation over the batch, one fp16
+ * rounding, fp32 accumulation over the heads in head order, one fp16 rounding) - bit-identical to hqkv_head_sum
+ * on the probabilities.  Stands in for last_attn_weights.update on a decode step
+ * (model/public_func.py:243-257; called at model/llama_hqe.py:199-200).  Up to B * nh_q = 64 the V pass emits the
+ * row itself (the last CTA to finish a chunk of tokens adds the probabilities the others have just written);
+ * beyond that the call adds one hqkv_head_sum launch.
+ */
+int hqkv_decode_attention_headsum(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
+                                  void* attn_output, void* head_sum_row, void* workspace, size_t workspace_bytes,
+                                  void* stream);
+
+/*
  * The same call restricted to one of its launches: phases = 1 runs the K pass only (logits and
  * per-CTA softmax statistics into the workspace), 2 the V pass only (needs the workspace a K-only
  * call of the same cache left), 3 both.  Serves

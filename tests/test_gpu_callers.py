@@ -127,6 +127,34 @@ def test_forward_qk_and_wv_group_hq(ops, cuda_device, sequential):
         ops.mm.cuda_bmm_forward_qk_group_hq(32, H, q, *([None] * 18), None)
 
 
+@pytest.mark.parametrize("batch,nh_q,nh_kv", [(1, 32, 8), (2, 8, 2), (8, 32, 8)])
+def test_decode_writes_the_importance_row(ops, cuda_device, batch, nh_q, nh_kv):
+    """qkv_matmul_hqe_2(head_sum_out=row): the row equals last_attn_weights.update on the returned probabilities
+    bit for bit (emitted by the V pass up to B * nh_q = 64, by one more launch beyond), the other results are those
+    of the plain call, and consecutive calls do not disturb one another (the arrival counters return to zero)."""
+    cache, q = small_cache(cuda_device, "uniform_group", batch=batch, nh_q=nh_q, nh_kv=nh_kv)
+    w0, o0 = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group")
+    L = w0.shape[-1]
+    want = ops.pf.last_attn_weights(last_length=4)
+    want.set_max_length(L + 8)
+    got = ops.pf.last_attn_weights(last_length=4)
+    got.set_max_length(L + 8)
+    for step in range(3):
+        want.update(w0)
+        row = got.decode_row(cuda_device)
+        w, o = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", head_sum_out=row)
+        got.advance(w.shape[-1])
+        assert torch.equal(w, w0) and torch.equal(o, o0), f"step {step}: results differ from the plain call"
+    torch.cuda.synchronize()
+    bits_equal(got.weights, want.weights.cpu().numpy(), "ring rows written by the decode call")
+    assert got.next_line == want.next_line and got.kv_seq_len == want.kv_seq_len
+    # the row against the oracle's rounding order on the same probabilities
+    ref = O.head_sum_probabilities(w0.cpu().numpy())
+    bits_equal(got.weights[0, :L], ref.reshape(-1), "importance row vs oracle")
+    with pytest.raises(ValueError, match="head_sum_out"):
+        ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", head_sum_out=row[: L - 1])
+
+
 def test_hybrid_quant_compress_is_the_flush_without_eviction(ops, cuda_device):
     """KV_cache_compress (five counts) builds the same tuple as KV_cache_hqe_2 with an eviction count of zero -
     every slot bit for bit against the oracle's flush - and KV_cache_reconstruct returns the oracle's dense cache."""
