@@ -141,8 +141,10 @@ def main():
         for mix in mixes:
             for group in groups:
                 for batch in batches:
-                    per_layer = batch * 8 * ctx * 288 / world   # upper bound, bytes on one GPU
-                    if per_layer * 32 > 60e9 or (batch >= 32 and ctx > 16384 * world and not args.batches):
+                    shares = TIER_MIXES[mix] + (0.0,) * (4 - len(TIER_MIXES[mix]))
+                    avg_bits = sum(sh * b for sh, b in zip(shares, (8, 4, 2, 1)))
+                    per_layer = batch * 8 * ctx * 2 * (16 * avg_bits + 512 / group) / world   # bytes on one GPU
+                    if per_layer * 32 > 100e9 or (batch >= 32 and ctx > 16384 * world and not args.batches):
                         continue
                     points.append((ctx, mix, group, batch))
     with open(args.out if rank == 0 else os.devnull, "w") as f:

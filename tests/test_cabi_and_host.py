@@ -104,6 +104,16 @@ def test_peer_entry_points_validate_without_gpu(lib):
     assert L.hqkv_peer_unpack(C.c_void_p(4096), C.c_void_p(4096), 0, 2, 256, C.c_void_p(4096), 0, None) == -1  # bounded waits only
 
 
+def test_library_is_stamped_with_its_sources(lib):
+    """hqkv_build_id() is the hash of the sources the binary was compiled from; the build script reads the same stamp
+    out of the file and rebuilds on a mismatch."""
+    from hqekv_b200 import build
+    stamp = lib.lib.hqkv_build_id().decode()
+    assert len(stamp) == 16 and stamp == build.library_id(lib.LIB_PATH)
+    if not os.environ.get("HQKV_LIB"):
+        assert stamp == build.source_id() and not build.needs_build()
+
+
 def test_workspace_size_of_the_benchmark_cache(lib):
     """Llama-3.1-8B at 32k: 5888/11744/11744 tokens in the 8/4/2-bit tiers + 128 residual."""
     desc = lib.CacheDesc()
@@ -117,7 +127,8 @@ def test_workspace_size_of_the_benchmark_cache(lib):
             setattr(tier, f, 256)
     need = lib.lib.hqkv_decode_workspace_bytes(desc)
     L = 5888 + 11744 * 2 + 128
-    assert need >= 4096 + 32 * L * 4
+    assert need >= lib.WS_HEADER_BYTES + 32 * L * 4
+    assert lib.lib.hqkv_decode_workspace_zero_bytes(desc) == lib.WS_HEADER_BYTES
     assert need < 16 << 20
     del dummy
 
