@@ -206,6 +206,84 @@ __global__ void __launch_bounds__(64) quantize_cols2_kernel(const __half* __rest
   mn_out[(row + 1) * G + gi] = __high2half(lo);
 }
 
+// The same for groups of 32 tokens, a tile of 8 groups x 128 channels per CTA.  The kernel above writes every word
+// with its own 4-byte store one code row apart from its neighbour's and reads every value twice; here a thread
+// keeps the 32 values of a group in registers (one pass), the tile's words and scale / zero halfs meet in shared
+// memory, and the CTA stores each channel's 8 groups as one contiguous run (32 x BITS bytes of codes, 16 bytes of
+// scales), consecutive threads on consecutive words.  256 threads: thread = (channel pair cp, group lane gl), groups
+// gl and gl + 4 of the tile.  Arithmetic and results are those of the kernel above.
+constexpr int QT_GROUPS = 8;     // groups per tile
+constexpr int QT_CH = 128;       // channels per tile
+template <int BITS>
+__global__ void __launch_bounds__(256) quantize_cols_tile_kernel(const __half* __restrict__ x, int64_t inner, int64_t T,
+                                                                 int64_t outer_stride, int64_t t_stride,
+                                                                 uint32_t* __restrict__ code, __half* __restrict__ scale,
+                                                                 __half* __restrict__ mn_out) {
+  constexpr int GROUP = 32;
+  constexpr int FPI = 32 / BITS;          // codes per word
+  constexpr int WPG = GROUP / FPI;        // words per group = BITS
+  constexpr int ROW = QT_GROUPS * WPG + 1;  // words per staged channel row (+1: rows land in different banks)
+  __shared__ uint32_t s_words[QT_CH * ROW];
+  __shared__ __half s_scale[QT_CH * QT_GROUPS], s_min[QT_CH * QT_GROUPS];
+  const float levels = static_cast<float>((1 << BITS) - 1);
+  const int tid = threadIdx.x, cp = tid & 63, gl = tid >> 6;
+  const int64_t G = T / GROUP;
+  const int64_t g_first = static_cast<int64_t>(blockIdx.x) * QT_GROUPS;
+  const int ngr = static_cast<int>(G - g_first < QT_GROUPS ? G - g_first : QT_GROUPS);
+  const int64_t d0 = static_cast<int64_t>(blockIdx.y) * QT_CH;
+  const int nch = static_cast<int>(inner - d0 < QT_CH ? inner - d0 : QT_CH);  // even: the host checks inner % 2 == 0
+  const int64_t o = blockIdx.z;
+  const int ch = 2 * cp;
+  if (ch < nch) {
+    for (int gq = gl; gq < ngr; gq += 4) {
+      const __half* src = x + o * outer_stride + d0 + ch + (g_first + gq) * GROUP * t_stride;
+      __half2 v[GROUP];
+#pragma unroll
+      for (int t = 0; t < GROUP; ++t) v[t] = *reinterpret_cast<const __half2*>(src + t * t_stride);
+      __half2 lo = v[0], hi = v[0];
+#pragma unroll
+      for (int t = 1; t < GROUP; ++t) {
+        lo = __hmin2_nan(lo, v[t]);
+        hi = __hmax2_nan(hi, v[t]);
+      }
+      const __half sc0 = quant_scale(__low2half(lo), __low2half(hi), levels);
+      const __half sc1 = quant_scale(__high2half(lo), __high2half(hi), levels);
+      const QuantGroup g0 = quant_group(__low2half(lo), sc0, levels), g1 = quant_group(__high2half(lo), sc1, levels);
+      uint32_t* w0 = s_words + ch * ROW + gq * WPG;
+      uint32_t* w1 = w0 + ROW;
+#pragma unroll
+      for (int w = 0; w < WPG; ++w) {
+        uint32_t word0 = 0, word1 = 0;
+#pragma unroll
+        for (int i = 0; i < FPI; ++i) {
+          const uint32_t c2 = quant_code_fast2(v[w * FPI + i], g0, g1);
+          word0 |= (c2 & 0xFFFFu) << (i * BITS);
+          word1 |= (c2 >> 16) << (i * BITS);
+        }
+        w0[w] = word0;
+        w1[w] = word1;
+      }
+      s_scale[ch * QT_GROUPS + gq] = sc0;
+      s_min[ch * QT_GROUPS + gq] = __low2half(lo);
+      s_scale[(ch + 1) * QT_GROUPS + gq] = sc1;
+      s_min[(ch + 1) * QT_GROUPS + gq] = __high2half(lo);
+    }
+  }
+  __syncthreads();
+  const int64_t row0 = o * inner + d0;
+  const int64_t W = T / FPI;
+  const int wpr = ngr * WPG;  // words of one channel row in this tile
+  for (int i = tid; i < nch * wpr; i += 256) {
+    const int r = i / wpr, w = i - r * wpr;
+    code[(row0 + r) * W + g_first * WPG + w] = s_words[r * ROW + w];
+  }
+  for (int i = tid; i < nch * ngr; i += 256) {
+    const int r = i / ngr, g = i - r * ngr;
+    scale[(row0 + r) * G + g_first + g] = s_scale[r * QT_GROUPS + g];
+    mn_out[(row0 + r) * G + g_first + g] = s_min[r * QT_GROUPS + g];
+  }
+}
+
 // ------------------------------------------------------------------------------------------------
 // unpack + two-rounding dequantise; one thread writes 8 consecutive fp16 values (16 bytes)
 // ------------------------------------------------------------------------------------------------
@@ -369,7 +447,16 @@ extern "C" int hqkv_quantize_pack(const void* x, int64_t rows, int64_t T, int64_
     HQKV_REQUIRE(outer <= 65535 && ceil_div(inner, 128) <= 65535, "quantize_pack: too many rows for the column path");
     dim3 grid(static_cast<unsigned>(T / group), static_cast<unsigned>(ceil_div(inner, 128)),
               static_cast<unsigned>(outer));
-    if (inner % 2 == 0 && aligned(x, 4) && outer_stride % 2 == 0 && t_stride % 2 == 0) {
+    if (group == 32 && inner % 2 == 0 && aligned(x, 4) && outer_stride % 2 == 0 && t_stride % 2 == 0) {
+      dim3 gridt(static_cast<unsigned>(ceil_div(T / group, QT_GROUPS)), static_cast<unsigned>(ceil_div(inner, QT_CH)),
+                 static_cast<unsigned>(outer));
+      switch (bits) {
+        case 8: quantize_cols_tile_kernel<8><<<gridt, 256, 0, st>>>(xs, inner, T, outer_stride, t_stride, c, s, m); break;
+        case 4: quantize_cols_tile_kernel<4><<<gridt, 256, 0, st>>>(xs, inner, T, outer_stride, t_stride, c, s, m); break;
+        case 2: quantize_cols_tile_kernel<2><<<gridt, 256, 0, st>>>(xs, inner, T, outer_stride, t_stride, c, s, m); break;
+        default: quantize_cols_tile_kernel<1><<<gridt, 256, 0, st>>>(xs, inner, T, outer_stride, t_stride, c, s, m); break;
+      }
+    } else if (inner % 2 == 0 && aligned(x, 4) && outer_stride % 2 == 0 && t_stride % 2 == 0) {
       dim3 grid2(static_cast<unsigned>(T / group), static_cast<unsigned>(ceil_div(inner, 128)),
                  static_cast<unsigned>(outer));
       switch (bits) {

@@ -105,6 +105,21 @@ def test_codec_random_vs_oracle(ops, cuda_device, bit, group):
     bits_equal(deq, O.dequantize_unpack_last_dim(oc, os_, om, group, bit), "dequantised")
 
 
+@pytest.mark.parametrize("bit", [8, 4, 2, 1])
+def test_codec_column_path_ragged_tiles(ops, cuda_device, bit):
+    """The tiled column kernel (groups of 32, tiles of 8 groups x 128 channels) on shapes that leave partial tiles
+    both ways: 11 and 19 groups, 96 and 200 channels, several (batch, head) planes; bit-exact with the oracle."""
+    rng = np.random.default_rng(300 + bit)
+    for groups, ch in ((11, 96), (19, 200), (8, 128)):
+        k = (rng.standard_normal((2, 3, 32 * groups, ch)) * np.where(rng.random(ch) < 0.05, 10, 1)).astype(np.float16)
+        kt = torch.from_numpy(k).to(cuda_device).transpose(2, 3)
+        code, scale, mn = ops.pu.uniform_group_quantize_pack_last_dim(kt, 32, bit)
+        oc, os_, om = O.quantize_pack_last_dim(np.ascontiguousarray(np.swapaxes(k, 2, 3)), 32, bit)
+        bits_equal(code, oc, f"{groups} groups x {ch} channels: code")
+        bits_equal(scale, os_, f"{groups} groups x {ch} channels: scale")
+        bits_equal(mn, om, f"{groups} groups x {ch} channels: mn")
+
+
 def test_codec_constant_group_and_roundtrip(ops, cuda_device):
     x = torch.full((1, 1, 2, 64), 3.5, dtype=torch.float16, device=cuda_device)
     x[0, 0, 1, :32] = torch.arange(32, device=cuda_device).half()
