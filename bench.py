@@ -48,10 +48,11 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--peer-gather", choices=["off", "flagged", "barrier"], default="flagged",
+    ap.add_argument("--peer-gather", choices=["off", "flagged", "flagged-unpack", "barrier"], default="flagged",
                     help="multi-GPU: the decode kernel stores its rows into the peers' buffers (symmetric memory) "
-                         "instead of an NCCL all-gather per layer: 'flagged' = values travel with the call number, "
-                         "'barrier' = plain stores + cross-GPU barrier")
+                         "instead of an NCCL all-gather per layer: 'flagged' = values travel with the call number and the "
+                         "decode kernel's last CTA unpacks them, 'flagged-unpack' = the same with a separate unpack "
+                         "launch, 'barrier' = plain stores + cross-GPU barrier")
     return ap.parse_args()
 
 
@@ -425,8 +426,9 @@ def main():
                 for _ in range(layers)] if world > 1 else None
 
     # Multi-GPU exchange of the per-head outputs.  Default: the decode kernel stores its rows, each pair of
-    # values in one 8-byte word with the call number, into every peer's receive buffer and a bounded
-    # unpack kernel follows (sharding.FlaggedPeerGather).  --peer-gather barrier: plain stores + cross-GPU
+    # values in one 8-byte word with the call number, into every peer's receive buffer, and the CTA that finishes
+    # a GPU's last head polls (bounded) and unpacks that GPU's own receive buffer (sharding.FlaggedPeerGather;
+    # flagged-unpack: a separate unpack kernel does that).  --peer-gather barrier: plain stores + cross-GPU
     # barrier; off: NCCL all-gather per layer, also the fallback when symmetric memory is not available
     # or the result differs from NCCL's on the first layer (checked every run).
     peer = None
@@ -434,8 +436,11 @@ def main():
     if world > 1 and args.peer_gather != "off":
         try:
             from hqekv_b200.sharding import FlaggedPeerGather, PeerGather
-            peer = (PeerGather if args.peer_gather == "barrier" else FlaggedPeerGather)(
-                max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
+            if args.peer_gather == "barrier":
+                peer = PeerGather(max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
+            else:  # flagged: the decode kernel unpacks too; flagged-unpack: a separate unpack launch follows
+                peer = FlaggedPeerGather(max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev,
+                                         fused_unpack=args.peer_gather == "flagged")
             _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
             dist.all_gather_into_tensor(gathered[0], o_ref)
             _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group, cfg.strategy)
@@ -693,7 +698,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
             "data": "synthetic", "config": config, "launch": launch, "exchange": exchange,
             "importance_row_exchange_us": importance_row_us, "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * layers * (3 if (peer is not None and args.peer_gather == "flagged") else 2),
+            "gpu_launches": args.steps * layers * (3 if (peer is not None and args.peer_gather == "flagged-unpack") else 2),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "parity": parity, "build_id": build_id,
             "tokens_per_sec_per_gpu": value / world}), flush=True)
     if world > 1:
