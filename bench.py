@@ -30,10 +30,10 @@ if ROOT not in sys.path:
 METRIC = "decode-attn tokens/sec at 32k ctx"
 UNIT = "tokens/s"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload (one cfg1 layer), from
-# the ncu capture summarised in profiles/decode_k_pass_v_pass_cfg1.md.  Only valid for that workload on
-# one GPU; other workloads report null.
-NCU_TRAFFIC_BYTES = {}
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the default workload (one cfg1 layer), from one ncu
+# capture of the two kernels (cold caches: logits and index lists are read from DRAM there, in the chained run they
+# are L2 hits).  Only valid for that workload on one GPU; other workloads report null.
+NCU_TRAFFIC_BYTES = {"k_pass_kernel": 19390464, "v_pass_kernel": 23248128}
 
 
 def parse_args():
@@ -48,11 +48,13 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=0, help="override the number of layers (0 = the workload's)")
     ap.add_argument("--no-graph", action="store_true", help="launch eagerly instead of replaying a CUDA graph")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--peer-gather", choices=["off", "flagged", "flagged-unpack", "barrier"], default="flagged",
+    ap.add_argument("--max-windows", type=int, default=200,
+                    help="the timed window of --steps steps is repeated until about a second has been timed, at most "
+                         "this many times (1 for a run under a profiler)")
+    ap.add_argument("--peer-gather", choices=["off", "flagged", "barrier"], default="flagged",
                     help="multi-GPU: the decode kernel stores its rows into the peers' buffers (symmetric memory) "
-                         "instead of an NCCL all-gather per layer: 'flagged' = values travel with the call number and the "
-                         "decode kernel's last CTA unpacks them, 'flagged-unpack' = the same with a separate unpack "
-                         "launch, 'barrier' = plain stores + cross-GPU barrier")
+                         "instead of an NCCL all-gather per layer: 'flagged' = values travel with the call number, "
+                         "'barrier' = plain stores + cross-GPU barrier")
     return ap.parse_args()
 
 
@@ -426,9 +428,8 @@ def main():
                 for _ in range(layers)] if world > 1 else None
 
     # Multi-GPU exchange of the per-head outputs.  Default: the decode kernel stores its rows, each pair of
-    # values in one 8-byte word with the call number, into every peer's receive buffer, and the CTA that finishes
-    # a GPU's last head polls (bounded) and unpacks that GPU's own receive buffer (sharding.FlaggedPeerGather;
-    # flagged-unpack: a separate unpack kernel does that).  --peer-gather barrier: plain stores + cross-GPU
+    # values in one 8-byte word with the call number, into every peer's receive buffer and a bounded
+    # unpack kernel follows (sharding.FlaggedPeerGather).  --peer-gather barrier: plain stores + cross-GPU
     # barrier; off: NCCL all-gather per layer, also the fallback when symmetric memory is not available
     # or the result differs from NCCL's on the first layer (checked every run).
     peer = None
@@ -436,11 +437,8 @@ def main():
     if world > 1 and args.peer_gather != "off":
         try:
             from hqekv_b200.sharding import FlaggedPeerGather, PeerGather
-            if args.peer_gather == "barrier":
-                peer = PeerGather(max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
-            else:  # flagged: the decode kernel unpacks too; flagged-unpack: a separate unpack launch follows
-                peer = FlaggedPeerGather(max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev,
-                                         fused_unpack=args.peer_gather == "flagged")
+            peer = (PeerGather if args.peer_gather == "barrier" else FlaggedPeerGather)(
+                max(layers, 2), cfg.batch, nh_q_local, cfg.head_dim, dev)
             _, o_ref = qkv_matmul_hqe_2(qs[0], caches[0], None, cfg.head_dim, cfg.strategy, cfg.group, cfg.group)
             dist.all_gather_into_tensor(gathered[0], o_ref)
             _, got = peer.decode(0, qs[0], caches[0], cfg.group, cfg.group, cfg.strategy)
@@ -548,7 +546,7 @@ def main():
         """A window of a few milliseconds is fragile: the window is repeated until about a second has been timed
         (at most 200 times, the same count on every rank) and the median window is reported."""
         first = timed_window(step_fn)
-        n = max(1, min(200, int(1000.0 / max(first, 1e-3))))
+        n = max(1, min(args.max_windows, int(1000.0 / max(first, 1e-3))))
         windows = sorted([first] + [timed_window(step_fn) for _ in range(n - 1)])
         return windows[len(windows) // 2], len(windows)
 
@@ -698,7 +696,7 @@ def main():
             "scaling": "strong", "vs_baseline": None, "dtype": "f16-in/f32-acc",
             "data": "synthetic", "config": config, "launch": launch, "exchange": exchange,
             "importance_row_exchange_us": importance_row_us, "clocks": clocks, "e2e": e2e,
-            "gpu_launches": args.steps * layers * (3 if (peer is not None and args.peer_gather == "flagged-unpack") else 2),
+            "gpu_launches": args.steps * layers * (3 if (peer is not None and args.peer_gather == "flagged") else 2),
             "roofline": roofline, "cpu_baseline": cpu_baseline, "parity": parity, "build_id": build_id,
             "tokens_per_sec_per_gpu": value / world}), flush=True)
     if world > 1:

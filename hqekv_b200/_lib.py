@@ -78,9 +78,6 @@ _SIGNATURES = {
                                                C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "hqkv_decode_attention_gather_flagged": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
                                                        C.c_size_t, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p]),
-    "hqkv_decode_attention_gather_fused": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
-                                                   C.c_size_t, C.POINTER(C.c_void_p), C.c_int, C.c_void_p, C.c_void_p,
-                                                   C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "hqkv_peer_unpack": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "hqkv_peer_barrier": (C.c_int, [C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_void_p, C.c_longlong, C.c_void_p]),
     "hqkv_decode_attention_static": (C.c_int, [C.POINTER(CacheDesc), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),

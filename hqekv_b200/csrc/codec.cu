@@ -335,7 +335,7 @@ static int launch_quant_rows(const __half* x, int64_t rows, int64_t T, int64_t i
   const int64_t units = rows * (T / 8);
   const int threads = 256;
   int64_t blocks = ceil_div(units, threads);
-  if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond 64 CTAs per SM
+  if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond 64 CTAs per SM (measured: faster than one unit per thread)
   if (blocks < 1) blocks = 1;
   switch (group) {
     case 32:

@@ -66,11 +66,6 @@ struct DecodeParams {
   __half* peer_out[HQKV_MAX_PEERS];  // copies of `out` in other GPUs' memory (kv-head sharding), n_peers used
   int n_peers;
   int peer_flagged;  // 1: peer_out are flagged 8-byte entries {two fp16 values, call number}, see peer_unpack_kernel
-  // flagged exchange with the unpack folded into this kernel: the CTA that finishes this GPU's last (batch, kv head)
-  // polls the GPU's own receive buffer and writes the plain gathered buffer (null: a separate unpack kernel follows)
-  const uint2* recv_local;
-  uint32_t* gathered_plain;
-  int entries;       // 8-byte entries per rank
   // cross-GPU barrier run by the last CTA of the V pass (world == 0: none)
   unsigned* pad[HQKV_MAX_PEERS + 1];  // the ranks' signal pads, own one included
   int rank, world;
@@ -1515,10 +1510,9 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
       }
     }
     if (P.world > 1) {
-      // the CTA that finishes the last (batch, kv head) of this GPU completes the exchange: when this
+      // the CTA that finishes the last (batch, kv head) of this GPU runs the cross-GPU barrier: when this
       // kernel completes, every rank's rows are in this GPU's gathered buffer
-      if (P.recv_local) __threadfence();  // flagged words need no fence of their own; this orders the read of the call number
-      else __threadfence_system();
+      __threadfence_system();
       __syncthreads();
       if (tid == 0) {
         const unsigned done = atomicAdd(P.peer_state + 2, 1u);
@@ -1526,30 +1520,7 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
         if (sh.is_last) P.peer_state[2] = 0u;
       }
       __syncthreads();
-      if (sh.is_last && P.recv_local) {
-        // flagged exchange: wait (bounded) until every word of every other rank carries this call's number,
-        // strip the flags into the plain gathered buffer, advance the call number.  All finalisers of this GPU
-        // have read the call number before they counted themselves in.
-        const unsigned n = P.peer_state[0] + 1u;
-        for (int i = tid; i < P.world * P.entries; i += VTHREADS) {
-          const int r = i / P.entries;
-          if (r == P.rank) continue;  // own rows were written in place above
-          long long spins = 0;
-          uint2 e;
-          for (;;) {
-            asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(P.recv_local + i));
-            if (e.y == n) break;
-            if (++spins > P.max_spins) {
-              atomicExch(reinterpret_cast<int*>(P.peer_state + 1), r + 1);  // gave up waiting for rank r
-              break;
-            }
-            __nanosleep(20);
-          }
-          P.gathered_plain[i] = e.x;
-        }
-        __syncthreads();
-        if (tid == 0) P.peer_state[0] = n;
-      } else if (sh.is_last) {
+      if (sh.is_last) {
         __threadfence();
         // every CTA fenced its peer stores system-wide before it counted itself in, and this CTA saw the
         // full count: the signal may go out at once
@@ -1746,9 +1717,6 @@ struct PeerArgs {
   int rank = 0, world = 0;
   void* state = nullptr;
   long long max_spins = 0;
-  const void* recv_local = nullptr;  // flagged exchange unpacked by the decode kernel itself
-  void* gathered = nullptr;
-  int entries = 0;
 };
 static int decode_launch(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights, void* attn_output,
                          void* workspace, size_t workspace_bytes, int phases, const PeerArgs& peers, void* stream,
@@ -1811,16 +1779,6 @@ static int hqkv::decode_launch(const hqkv_cache_desc_t* cache_host, const void* 
     for (int r = 0; r < peers.world; ++r) P.pad[r] = static_cast<unsigned*>(peers.pads[r]);
     P.peer_state = static_cast<unsigned*>(peers.state);
     P.max_spins = peers.max_spins;
-  }
-  if (peers.recv_local) {
-    P.rank = peers.rank;
-    P.world = peers.world;
-    P.recv_local = static_cast<const uint2*>(peers.recv_local);
-    P.gathered_plain = static_cast<uint32_t*>(peers.gathered);
-    P.entries = peers.entries;
-    P.max_spins = peers.max_spins;
-    HQKV_REQUIRE(peers.entries == P.B * P.nh_q * D / 2, "decode_gather_fused: entries_per_rank must be B * nh_q * 64 (got %d)",
-                 peers.entries);
   }
   HQKV_REQUIRE(workspace, "decode: null pointer");
   if (phases & 1) HQKV_REQUIRE(q && aligned(q, 4), "decode: q is null or not 4-byte aligned");
@@ -2098,21 +2056,33 @@ __global__ void __launch_bounds__(256) peer_unpack_kernel(const uint2* recv, uin
   asm volatile("griddepcontrol.launch_dependents;");
   asm volatile("griddepcontrol.wait;" ::: "memory");  // this GPU's own decode call has finished
   const unsigned n = state[0] + 1u;
-  for (int i = threadIdx.x; i < world * entries; i += blockDim.x) {
-    const int r = i / entries;
-    if (r == rank) continue;  // own rows were written in place by the decode kernel
-    long long spins = 0;
-    uint2 e;
-    for (;;) {
-      asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(e.x), "=r"(e.y) : "l"(recv + i));
-      if (e.y == n) break;
-      if (++spins > max_spins) {
-        atomicExch(reinterpret_cast<int*>(state + 1), r + 1);  // gave up waiting for rank r
-        break;
-      }
-      __nanosleep(20);
+  // Four words per thread are requested together, so that a pass over words that have already arrived costs one
+  // round trip, not one per word; a word that is still old is polled on its own.
+  const int total = world * entries;
+  for (int base = threadIdx.x; base < total; base += 4 * 256) {
+    uint2 e[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = base + j * 256;
+      e[j] = make_uint2(0u, n);
+      if (i < total && i / entries != rank)  // own rows were written in place by the decode kernel
+        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(e[j].x), "=r"(e[j].y) : "l"(recv + i));
     }
-    plain[i] = e.x;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = base + j * 256;
+      if (i >= total || i / entries == rank) continue;
+      long long spins = 0;
+      while (e[j].y != n) {
+        if (++spins > max_spins) {
+          atomicExch(reinterpret_cast<int*>(state + 1), i / entries + 1);  // gave up waiting for that rank
+          break;
+        }
+        __nanosleep(20);
+        asm volatile("ld.volatile.global.v2.u32 {%0,%1}, [%2];" : "=r"(e[j].x), "=r"(e[j].y) : "l"(recv + i));
+      }
+      plain[i] = e[j].x;
+    }
   }
   __syncthreads();
   if (threadIdx.x == 0) state[0] = n;
@@ -2131,33 +2101,6 @@ extern "C" int hqkv_decode_attention_gather_flagged(const hqkv_cache_desc_t* cac
   pa.n_peers = n_peers;
   pa.flagged = true;
   pa.state = state;
-  return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, pa, stream);
-}
-
-extern "C" int hqkv_decode_attention_gather_fused(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
-                                                  void* attn_output, void* workspace, size_t workspace_bytes,
-                                                  void* const* peer_recv_host, int n_peers, const void* recv_local,
-                                                  void* gathered, int rank, int world, int entries_per_rank, void* state,
-                                                  long long max_spins, void* stream) {
-  HQKV_REQUIRE(world >= 2 && world <= HQKV_MAX_PEERS + 1 && rank >= 0 && rank < world, "decode_gather_fused: bad rank/world");
-  HQKV_REQUIRE(n_peers >= 1 && n_peers <= HQKV_MAX_PEERS, "decode_gather_fused: 1..%d peers (got %d)", HQKV_MAX_PEERS, n_peers);
-  HQKV_REQUIRE(peer_recv_host && recv_local && gathered && state && aligned(recv_local, 8) && aligned(gathered, 4) &&
-                   aligned(state, 4),
-               "decode_gather_fused: null or misaligned pointer");
-  HQKV_REQUIRE(entries_per_rank > 0 && max_spins > 0, "decode_gather_fused: sizes and the spin limit must be positive");
-  for (int p = 0; p < n_peers; ++p)
-    HQKV_REQUIRE(peer_recv_host[p] && aligned(peer_recv_host[p], 8), "decode_gather_fused: peer buffer %d is null or misaligned", p);
-  hqkv::PeerArgs pa;
-  pa.out = peer_recv_host;
-  pa.n_peers = n_peers;
-  pa.flagged = true;
-  pa.state = state;
-  pa.rank = rank;
-  pa.world = world;
-  pa.max_spins = max_spins;
-  pa.recv_local = recv_local;
-  pa.gathered = gathered;
-  pa.entries = entries_per_rank;
   return decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, pa, stream);
 }
 

@@ -12,7 +12,6 @@ namespace hqkv {
 
 constexpr int GEMV_WC = 32;     // word columns per CTA
 constexpr int GEMV_KS = 8;      // K slices per CTA
-constexpr int GEMV_MAX_REP = 8;
 
 template <int BITS, int REP, bool NORMAL>
 __global__ void __launch_bounds__(GEMV_WC* GEMV_KS) gemv_group_kernel(

@@ -157,24 +157,21 @@ class FlaggedPeerGather:
     """The low-latency form of :class:`PeerGather`: values travel with the call number in 8-byte words.
 
     Per slot a RECEIVE buffer of ``world * entries`` 8-byte words lives in symmetric memory; the decode
-    kernel of every rank stores {two fp16 values, call number} words into the peers' receive buffers, and
-    the CTA that finishes a rank's last head polls that rank's own receive buffer, bounded, and writes the
-    plain gathered tensor ``[world, B, nh_q/world, 1, D]`` (``hqkv_decode_attention_gather_fused``; with
-    ``fused_unpack=False`` the unpack is the separate launch ``hqkv_peer_unpack`` after
-    ``hqkv_decode_attention_gather_flagged``).
-    No fence, signal or collective is involved; the launches have fixed arguments (CUDA-graph safe).
+    kernel of every rank stores {two fp16 values, call number} words into the peers' receive buffers
+    (``hqkv_decode_attention_gather_flagged``), and ``hqkv_peer_unpack`` on every rank polls its own
+    receive buffer, bounded, and writes the plain gathered tensor ``[world, B, nh_q/world, 1, D]``.
+    No fence, signal or collective is involved; both launches have fixed arguments (CUDA-graph safe).
     A slot is reused only one full round of slots later, so ``slots`` must be at least 2.
     """
 
     def __init__(self, slots: int, batch: int, nh_q_local: int, head_dim: int, device, group=None,
-                 max_spins: int = 4_000_000, fused_unpack: bool = True):
+                 max_spins: int = 4_000_000):
         import ctypes as C
         import torch.distributed._symmetric_memory as symm_mem
         from ._lib import lib  # fails loudly without the CUDA library
         if slots < 2:
             raise ValueError("at least two slots: a receive buffer is reused only after the peers unpacked it")
         self._lib = lib
-        self._fused = fused_unpack
         group = group if group is not None else dist.group.WORLD
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         if not 2 <= self.world <= 8:
@@ -196,7 +193,7 @@ class FlaggedPeerGather:
                 arr[i] = base[p] + 8 * ((s * self.world + self.rank) * self._entries)
             self._peer_args.append(arr)
             self._recv_ptr.append(base[self.rank] + 8 * (s * self.world * self._entries))
-        self._state = torch.zeros(4, dtype=torch.int32, device=device)  # call number, status, finished heads
+        self._state = torch.zeros(2, dtype=torch.int32, device=device)  # call number, status
         self._max_spins = max_spins
         torch.cuda.synchronize(device)
         dist.barrier(group)  # nobody sends before every receive buffer is zero
@@ -214,12 +211,6 @@ class FlaggedPeerGather:
         out = gathered[self.rank]
         ws = decode_workspace(dev, self._lib.hqkv_decode_workspace_bytes(desc))
         st = stream_ptr(dev)
-        if self._fused:
-            check(self._lib.hqkv_decode_attention_gather_fused(
-                desc, q.data_ptr(), weights.data_ptr(), out.data_ptr(), ws.data_ptr(), ws.numel(), self._peer_args[slot],
-                len(self._peers), self._recv_ptr[slot], gathered.data_ptr(), self.rank, self.world, self._entries,
-                self._state.data_ptr(), self._max_spins, st))
-            return weights, gathered
         check(self._lib.hqkv_decode_attention_gather_flagged(desc, q.data_ptr(), weights.data_ptr(), out.data_ptr(),
                                                              ws.data_ptr(), ws.numel(), self._peer_args[slot],
                                                              len(self._peers), self._state.data_ptr(), st))

@@ -285,22 +285,6 @@ int hqkv_peer_unpack(const void* recv, void* gathered, int rank, int world, int 
                      long long max_spins, void* stream);
 
 /*
- * The flagged exchange in one call: hqkv_decode_attention_gather_flagged whose last step is the unpack.  The CTA
- * that finishes this GPU's last (batch, kv head) polls the GPU's own receive buffer recv_local (world *
- * entries_per_rank 8-byte words) until every other rank's words carry this call's number - bounded by max_spins
- * polls per word, a missing rank is recorded as rank + 1 in the status word at state + 4, no trap, no endless loop -
- * writes the values into `gathered` ([world][entries_per_rank] fp16 pairs; attn_output must be this rank's block
- * inside it) and advances the call number.  One launch less per layer than the pair above.  state: 12 bytes of
- * this GPU's memory, zero before the first call (call number, status, finished-head count).  The kernel waits for
- * kernels on OTHER GPUs only; every rank must launch its call for the waits to end.
- */
-int hqkv_decode_attention_gather_fused(const hqkv_cache_desc_t* cache_host, const void* q, void* attn_weights,
-                                       void* attn_output, void* workspace, size_t workspace_bytes,
-                                       void* const* peer_recv_host, int n_peers, const void* recv_local, void* gathered,
-                                       int rank, int world, int entries_per_rank, void* state, long long max_spins,
-                                       void* stream);
-
-/*
  * hqkv_decode_attention for callers that cannot allocate device memory.  It has no counterpart in the
  * reference, whose wrappers allocate freely through torch.
  *

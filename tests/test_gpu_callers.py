@@ -308,50 +308,3 @@ def test_flagged_exchange_loopback(ops, cuda_device):
         assert recv_state.tolist() == [call + 1, 0]
         got = gathered[:entries].view(torch.float16).view(B, nh_q, 1, D)
         assert torch.equal(got, o) and torch.equal(o, o_ref) and torch.equal(w, w_ref), f"call {call}"
-
-
-def test_fused_flagged_exchange_loopback_and_expiry(ops, cuda_device):
-    """hqkv_decode_attention_gather_fused on one GPU, the two ranks played one after the other.  Rank 0 stores its
-    words into the buffer rank 1 polls and polls a buffer nobody writes: its bounded wait runs out (status = 1 + the
-    missing rank), the kernel returns and the context stays usable.  Rank 1 then finds rank 0's words in its receive
-    buffer: its call completes with status 0 and the gathered buffer holds both ranks' rows.  Two rounds, so the call
-    numbers of both ranks advance."""
-    from hqekv_b200._lib import CODEC_UNIFORM, lib, stream_ptr
-    from hqekv_b200.quant._cache import build_cache_desc
-    cache, q = small_cache(cuda_device, "uniform_group", batch=1)
-    desc, keep, L, dev = build_cache_desc(cache, q.shape[1], 32, 32, CODEC_UNIFORM)
-    ws = torch.zeros(lib.hqkv_decode_workspace_bytes(desc), dtype=torch.uint8, device=dev)
-    B, nh_q, D = q.shape[0], q.shape[1], 128
-    entries = B * nh_q * D // 2
-    st = stream_ptr(dev)
-    w_ref, o_ref = ops.hm.qkv_matmul_hqe_2(q, cache, None, 128, "uniform_group", 32, 32)
-    state0 = torch.zeros(4, dtype=torch.int32, device=dev)
-    state1 = torch.zeros(4, dtype=torch.int32, device=dev)
-    recv0 = torch.zeros(2 * entries, 2, dtype=torch.int32, device=dev)   # rank 0's receive buffer: nobody writes it
-    recv1 = torch.zeros(2 * entries, 2, dtype=torch.int32, device=dev)   # rank 1's: rank 0 writes slot 0
-    for rnd in range(2):
-        # rank 0: own block is gathered0[0]; its peer (rank 1) takes rank 0's words at word 0 of recv1
-        gathered0 = torch.zeros(2, B, nh_q, 1, D, dtype=torch.float16, device=dev)
-        w = torch.empty(B, nh_q, 1, L, dtype=torch.float16, device=dev)
-        peers = (C.c_void_p * 1)(recv1.data_ptr())
-        rc = lib.hqkv_decode_attention_gather_fused(desc, q.data_ptr(), w.data_ptr(), gathered0[0].data_ptr(), ws.data_ptr(),
-                                                    ws.numel(), peers, 1, recv0.data_ptr(), gathered0.data_ptr(), 0, 2,
-                                                    entries, state0.data_ptr(), 200, st)
-        assert rc == 0, lib.hqkv_last_error().decode()
-        torch.cuda.synchronize()
-        assert state0.tolist()[:3] == [rnd + 1, 2, 0], "rank 0 gave up waiting for rank 1, advanced its call number"
-        assert torch.equal(gathered0[0], o_ref) and torch.equal(w, w_ref)
-        state0[1] = 0
-        # rank 1: own block is gathered1[1]; its words for rank 0 go to a scratch buffer; it polls recv1
-        gathered1 = torch.zeros(2, B, nh_q, 1, D, dtype=torch.float16, device=dev)
-        sink = torch.zeros(2 * entries, 2, dtype=torch.int32, device=dev)
-        peers = (C.c_void_p * 1)(sink.data_ptr() + 8 * entries)
-        rc = lib.hqkv_decode_attention_gather_fused(desc, q.data_ptr(), w.data_ptr(), gathered1[1].data_ptr(), ws.data_ptr(),
-                                                    ws.numel(), peers, 1, recv1.data_ptr(), gathered1.data_ptr(), 1, 2,
-                                                    entries, state1.data_ptr(), 1 << 20, st)
-        assert rc == 0, lib.hqkv_last_error().decode()
-        torch.cuda.synchronize()
-        assert state1.tolist()[:3] == [rnd + 1, 0, 0]
-        assert torch.equal(gathered1[0], o_ref) and torch.equal(gathered1[1], o_ref), f"round {rnd}"
-        assert sink[entries:, 1].eq(rnd + 1).all(), "rank 1's words carry its call number"
-    assert torch.ones(4, device=dev).sum().item() == 4.0
