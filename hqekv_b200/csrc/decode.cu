@@ -964,6 +964,9 @@ struct VWarpShared {
 };
 static_assert(sizeof(float) * 4 * D <= sizeof(int64_t) * V_MAX_TT + sizeof(__half) * 4 * V_PROW, "red0 fits its union");
 
+// importance row emitted by the V pass: staging limits (positions + per-head halfs live in the warps' tile buffers)
+constexpr int HS_TOKENS = 512;   // tokens of the largest chunk
+constexpr int HS_HEADS = 32;     // query heads it is built for (beyond that a separate launch sums the heads)
 struct VShared {
   float gm[MAX_REP], gl[MAX_REP];          // global max / sum of this kv head's query heads
   float wm[VWARPS][MAX_REP], wl[VWARPS][MAX_REP];
@@ -1367,6 +1370,67 @@ __device__ __forceinline__ void peer_barrier_device(unsigned* const* pad, int ra
   if (r == 0) *call_no = n;
 }
 
+static_assert(sizeof(VWarpShared) * VWARPS >= HS_TOKENS * 4 + HS_TOKENS * HS_HEADS * 2, "importance-row staging fits the tile buffers");
+// Importance row of one chunk of tokens, run by the last CTA to finish it (not inlined: its registers are its own).
+__device__ __noinline__ void head_sum_chunk(const DecodeParams& P, const TierDev& T, VShared& sh, int chunk, bool is_res) {
+  const int tid = threadIdx.x;
+  __threadfence();
+  const int c0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
+  const int n = min(T.v_chunk_tokens, T.n_v - c0);
+  // The warps' tile buffers are free by now: they stage the chunk's positions and, per token and head, the sum
+  // over the batch rounded to fp16.  Loads first, all of them independent: an item is (token, eight heads),
+  // four items - 32 gathers per batch entry - are in flight per thread; then one thread per token adds the
+  // heads in head order.
+  uint32_t* pos_s = reinterpret_cast<uint32_t*>(sh.w);                       // [HS_TOKENS]
+  __half* stage = reinterpret_cast<__half*>(pos_s + HS_TOKENS);              // [HS_TOKENS][HS_HEADS]
+  for (int t = tid; t < n; t += VTHREADS)
+    pos_s[t] = is_res ? static_cast<uint32_t>(P.L - T.n_v + c0 + t) : static_cast<uint32_t>(T.v_idx[c0 + t]);
+  __syncthreads();
+  const int nhq = P.nh_q, ngr = (nhq + 7) >> 3, items = n * ngr;
+  const unsigned short* w = reinterpret_cast<const unsigned short*>(P.weights);
+  for (int base = tid; base < items; base += 4 * VTHREADS) {
+    float ob[4][8];
+#pragma unroll
+    for (int q = 0; q < 4; ++q)
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ob[q][j] = 0.f;
+    for (int bb = 0; bb < P.B; ++bb) {
+      unsigned short v[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int item = base + q * VTHREADS;
+        const int gq = item / n, t = item - gq * n;  // token fastest: neighbouring threads read neighbouring positions
+        const bool live = item < items && HQKV_INDEX_OK(pos_s[t], P.L);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int h = 8 * gq + j;
+          v[q][j] = (live && h < nhq) ? __ldcg(w + (static_cast<int64_t>(bb) * nhq + h) * P.L + pos_s[t])
+                                      : static_cast<unsigned short>(0);
+        }
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ob[q][j] = __fadd_rn(ob[q][j], __half2float(__ushort_as_half(v[q][j])));
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int item = base + q * VTHREADS;
+      if (item >= items) continue;
+      const int gq = item / n, t = item - gq * n;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) stage[t * HS_HEADS + 8 * gq + j] = __float2half_rn(ob[q][j]);
+    }
+  }
+  __syncthreads();
+  for (int t = tid; t < n; t += VTHREADS) {
+    if (!HQKV_INDEX_OK(pos_s[t], P.L)) continue;
+    float over_heads = 0.f;
+    for (int h = 0; h < nhq; ++h) over_heads = __fadd_rn(over_heads, __half2float(stage[t * HS_HEADS + h]));
+    P.head_sum[pos_s[t]] = __float2half_rn(over_heads);
+  }
+}
+
 __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __grid_constant__ DecodeParams P) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   VShared& sh = *reinterpret_cast<VShared*>(smem_raw);
@@ -1542,25 +1606,7 @@ __global__ void __launch_bounds__(VTHREADS, V_MIN_CTAS) v_pass_kernel(const __gr
       if (sh.is_last) P.hs_count[chunk] = 0u;  // ready for the next call
     }
     __syncthreads();
-    if (sh.is_last) {
-      __threadfence();
-      const int c0 = (chunk - T.v_chunk0) * T.v_chunk_tokens;
-      const int n = min(T.v_chunk_tokens, T.n_v - c0);
-      for (int t = tid; t < n; t += VTHREADS) {
-        const int64_t pos = is_res ? static_cast<int64_t>(P.L) - T.n_v + c0 + t : T.v_idx[c0 + t];
-        if (!HQKV_INDEX_OK(pos, P.L)) continue;
-        const unsigned short* w = reinterpret_cast<const unsigned short*>(P.weights) + pos;
-        float over_heads = 0.f;
-#pragma unroll 4
-        for (int h = 0; h < P.nh_q; ++h) {
-          float over_batch = 0.f;
-          for (int bb = 0; bb < P.B; ++bb)
-            over_batch = __fadd_rn(over_batch, __half2float(__ushort_as_half(__ldcg(w + (static_cast<int64_t>(bb) * P.nh_q + h) * P.L))));
-          over_heads = __fadd_rn(over_heads, __half2float(__float2half_rn(over_batch)));
-        }
-        P.head_sum[pos] = __float2half_rn(over_heads);
-      }
-    }
+    if (sh.is_last) head_sum_chunk(P, T, sh, chunk, is_res);
   }
 }
 
@@ -1868,7 +1914,7 @@ extern "C" int hqkv_decode_attention_headsum(const hqkv_cache_desc_t* cache_host
   Layout lay;
   int rc = build_params(cache_host, P, lay);
   if (rc) return rc;
-  const bool fused = P.B * P.nh_q <= HEAD_SUM_MAX_ROWS && P.nv_chunks <= HEAD_SUM_MAX_CHUNKS;
+  const bool fused = P.B * P.nh_q <= HEAD_SUM_MAX_ROWS && P.nh_q <= HS_HEADS && P.nv_chunks <= HEAD_SUM_MAX_CHUNKS;
   rc = decode_launch(cache_host, q, attn_weights, attn_output, workspace, workspace_bytes, 3, hqkv::PeerArgs(), stream,
                      nullptr, nullptr, 0, 0, fused ? head_sum_row : nullptr);
   if (rc || fused) return rc;

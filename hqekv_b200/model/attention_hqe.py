@@ -233,17 +233,18 @@ class HqeAttention(nn.Module):
             new_k = k if past_key_value[-3] is None else torch.cat((past_key_value[-3], k), dim=2)
             new_v = v if past_key_value[-2] is None else torch.cat((past_key_value[-2], v), dim=2)
             past_key_value = tuple(past_key_value[:-3]) + (new_k, new_v, kv_seq_len)
-            # the decode call writes the step's importance row into the ring itself
-            row = self.last_weights.decode_row(q.device)
             attn_weights, attn_output = qkv_matmul_hqe_2(q, past_key_value, attention_mask, self.head_dim,
-                                                         self.quant_strategy, BLOCK, BLOCK, head_sum_out=row)
-            self.last_weights.advance(attn_weights.shape[-1])
+                                                         self.quant_strategy, BLOCK, BLOCK)
         else:
             attn_weights, attn_output = self._prefill(q, k, v, attention_mask)
             past_key_value = (None,) * 39 + (k, v, kv_seq_len)
-            self.last_weights.update(attn_weights)
         context = attn_output.transpose(1, 2).reshape(B, S, self.num_heads * self.head_dim)
 
+        # The ring row of the step: one more launch over the probabilities just written (still in L2).  The decode
+        # call can write the row itself (qkv_matmul_hqe_2(head_sum_out=...)), one launch less, but measured slower
+        # at batch 1: the last CTA to finish a chunk then gathers that chunk's 16 k probabilities alone, while this
+        # launch spreads the same gathers over the whole GPU (37.5 against 26.4 us per layer at 32 k context).
+        self.last_weights.update(attn_weights)
         if self.schedule.due():
             past_key_value, auxiliary_parameters = self._flush(past_key_value, auxiliary_parameters)
         else:
