@@ -116,6 +116,7 @@ def main():
     ap.add_argument("--ctxs", default="", help="comma-separated context lengths instead of the default set")
     ap.add_argument("--batches", default="", help="comma-separated batch sizes instead of 1,8,32")
     ap.add_argument("--groups", default="", help="comma-separated group sizes instead of the default set")
+    ap.add_argument("--quantize-only", action="store_true", help="skip the decode points")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -137,7 +138,7 @@ def main():
     batches = tuple(int(b) for b in args.batches.split(",")) if args.batches else (1, 8, 32)
     groups = tuple(int(g) for g in args.groups.split(",")) if args.groups else ((32,) if args.quick else (32, 128))
     points = []
-    for ctx in ctxs:
+    for ctx in (() if args.quantize_only else ctxs):
         for mix in mixes:
             for group in groups:
                 for batch in batches:
