@@ -117,6 +117,7 @@ def main():
     ap.add_argument("--batches", default="", help="comma-separated batch sizes instead of 1,8,32")
     ap.add_argument("--groups", default="", help="comma-separated group sizes instead of the default set")
     ap.add_argument("--quantize-only", action="store_true", help="skip the decode points")
+    ap.add_argument("--quantize-tokens", default="", help="comma-separated token counts of the quantise+pack points")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -160,7 +161,9 @@ def main():
             torch.distributed.barrier()
             torch.cuda.synchronize()
             return 0
-        for tokens in ((4096, 32768) if args.quick else (1024, 8192, 32768, 131072)):
+        q_tokens = (tuple(int(t) for t in args.quantize_tokens.split(",")) if args.quantize_tokens
+                    else (4096, 32768) if args.quick else (1024, 8192, 32768, 131072))
+        for tokens in q_tokens:
             for bit in (8, 4, 2):
                 r = quantize_point(dev, tokens, bit, 32, peak)
                 f.write(json.dumps(r) + "\n")
