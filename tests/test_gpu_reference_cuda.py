@@ -1,0 +1,37 @@
+"""The reference's own CUDA kernels beside this package's decode, on the same cache tuple.
+
+Where the reference's extension has been built (baseline/_ref, by baseline/build_ref.py - a git-ignored copy that
+travels with the working tree), `bench.py --impl reference-cuda` drives the reference's unmodified qkv_matmul_hqe_2
+(quant/hqe_matmul.py:354-451: per-tier transposed copies, kvhq_gemv launches, index scatter, torch softmax) on the
+single-layer configuration (batch 1, 4096 tokens, 8/4/2-bit tiers, group 32) and reports how far its outputs are from
+this package's.  The reference rounds logits and every tier's partial output to fp16, so the two differ by a few
+fp16 ulps: the bounds below are what that flow allows (the fp16-flow oracle models it), not the 2e-3 of the fp32
+parity target.  Runs in a child process: the reference's flat module names (hqe_matmul, matmul, pack_unpack) must not
+meet this package's in one interpreter.  Skipped where the extension is absent.
+"""
+import glob
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_reference_cuda_kernels_agree_with_this_package():
+    if not glob.glob(os.path.join(ROOT, "baseline", "_ref", "quant", "kvhq_gemv*.so")):
+        pytest.skip("baseline/_ref holds no kvhq_gemv extension")
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference-cuda", "--workload", "cfg0",
+                        "--steps", "20", "--warmup", "3"], capture_output=True, text=True, timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("{")][-1]
+    rec = json.loads(line)
+    if "unavailable" in rec:
+        pytest.skip(rec["unavailable"])
+    agree = rec["agreement_with_this_package"]
+    assert agree["attn_output_max_rel_diff"] <= 1e-2, agree     # measured 4.3e-3
+    assert agree["attn_weights_max_abs_diff"] <= 2.0 ** -9, agree  # one fp16 ulp of a probability near 1; measured 2^-10
+    assert rec["value"] > 0 and rec["impl"] == "reference-cuda"
