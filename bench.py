@@ -334,6 +334,18 @@ def run_reference_cuda(args, cfg, layers, config):
     torch.cuda.synchronize()
     rel = float(((o_ref.float() - o_our.float()).abs().amax(-1) / o_our.float().abs().amax(-1)).max())
     wdiff = float((w_ref.float() - w_our.float()).abs().max())
+    agreement = {"attn_output_max_rel_diff": rel, "attn_weights_max_abs_diff": wdiff}
+    if w_ref.shape[-1] <= 8192:
+        # small enough for the checker: the oracle's restatement of the reference's fp16 flow (per-tier GEMV rounded to
+        # fp16, fp16 scaling, fp32 softmax rounded to fp16, per-tier partial outputs rounded to fp16) against what the
+        # reference's kernels really return
+        from oracle import hqkv_oracle as O
+        host = tuple(x.cpu().numpy() if torch.is_tensor(x) else x for x in caches[0])
+        fw, fo = O.decode_attention_fp16_flow(qs[0].cpu().numpy(), host, cfg.group, cfg.group, cfg.strategy)
+        fo_t, fw_t = torch.from_numpy(fo).float().to(dev), torch.from_numpy(fw).float().to(dev)
+        agreement["vs_fp16_flow_oracle"] = {
+            "attn_output_max_rel_diff": float(((o_ref.float() - fo_t).abs().amax(-1) / fo_t.abs().amax(-1)).max()),
+            "attn_weights_max_abs_diff": float((w_ref.float() - fw_t).abs().max())}
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     steps = max(args.steps, 20)
     torch.cuda.synchronize()
@@ -351,7 +363,7 @@ def run_reference_cuda(args, cfg, layers, config):
         "note": "the reference's own CUDA extension (kvhq_gemv, built for sm_100 from its sources) driven by its own "
                 "quant/hqe_matmul.py:qkv_matmul_hqe_2, eager launches on the default stream, CUDA events around "
                 f"{steps} steps of {layers} layers",
-        "agreement_with_this_package": {"attn_output_max_rel_diff": rel, "attn_weights_max_abs_diff": wdiff}}))
+        "agreement_with_this_package": agreement}))
 
 
 def main():
