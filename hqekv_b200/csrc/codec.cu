@@ -41,80 +41,89 @@ __global__ void __launch_bounds__(256) quantize_rows_kernel(const __half* __rest
   const float levels = static_cast<float>((1 << BITS) - 1);
   const int64_t units_per_row = T / 8;
   const int64_t total_units = rows * units_per_row;
-  // all lanes of a warp take part in the shuffles: iterate in whole-warp steps
-  const int64_t n_iter = (total_units + static_cast<int64_t>(gridDim.x) * blockDim.x - 1) /
-                         (static_cast<int64_t>(gridDim.x) * blockDim.x);
+  // all lanes of a warp take part in the shuffles: iterate in whole-warp steps; two units per thread and step, both
+  // loads issued before either is worked on (one 16-byte load in flight per thread did not cover the memory latency)
+  const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+  const int64_t n_iter = (total_units + 2 * stride - 1) / (2 * stride);
+  // packed source (the usual case): unit u is elements [8u, 8u+8) and no 64-bit division is needed;
+  // (row*T + t0) below is 8u either way
+  const bool packed = inner_stride == T && outer_stride == inner * T;
+  const int lane = threadIdx.x & 31;
   for (int64_t it = 0; it < n_iter; ++it) {
-    const int64_t u = (it * gridDim.x + blockIdx.x) * static_cast<int64_t>(blockDim.x) + threadIdx.x;
-    const bool live = u < total_units;
-    // packed source (the usual case): unit u is elements [8u, 8u+8) and no 64-bit division is needed;
-    // (row*T + t0) below is 8u either way
-    const bool packed = inner_stride == T && outer_stride == inner * T;
-    int64_t row = 0, t0 = live ? u * 8 : 0;
-    if (!packed && live) {
-      row = u / units_per_row;
-      t0 = (u % units_per_row) * 8;
-    }
-    __half v[8];
-    if (live) {
-      const __half* src = packed ? x + t0 : x + (row / inner) * outer_stride + (row % inner) * inner_stride + t0;
-      if (vec_ok) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(src);
-        *reinterpret_cast<uint4*>(v) = raw;
+    __half v[2][8];
+    int64_t row[2], t0[2];
+    bool live[2];
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int64_t u = (2 * it + k) * stride + static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+      live[k] = u < total_units;
+      row[k] = 0;
+      t0[k] = live[k] ? u * 8 : 0;
+      if (!packed && live[k]) {
+        row[k] = u / units_per_row;
+        t0[k] = (u % units_per_row) * 8;
+      }
+      if (live[k]) {
+        const __half* src = packed ? x + t0[k] : x + (row[k] / inner) * outer_stride + (row[k] % inner) * inner_stride + t0[k];
+        if (vec_ok) {
+          *reinterpret_cast<uint4*>(v[k]) = *reinterpret_cast<const uint4*>(src);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[k][i] = src[i];
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = src[i];
+        for (int i = 0; i < 8; ++i) v[k][i] = __float2half(0.f);
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = __float2half(0.f);
     }
-    // min / max of the group on half2 pairs (NaN propagates, as in torch.min / torch.max)
-    const __half2* v2 = reinterpret_cast<const __half2*>(v);
-    __half2 lo2 = __hmin2_nan(__hmin2_nan(v2[0], v2[1]), __hmin2_nan(v2[2], v2[3]));
-    __half2 hi2 = __hmax2_nan(__hmax2_nan(v2[0], v2[1]), __hmax2_nan(v2[2], v2[3]));
 #pragma unroll
-    for (int off = 1; off < LPG; off <<= 1) {
-      lo2 = __hmin2_nan(lo2, __shfl_xor_sync(0xffffffffu, lo2, off));
-      hi2 = __hmax2_nan(hi2, __shfl_xor_sync(0xffffffffu, hi2, off));
-    }
-    lo2 = __hmin2_nan(lo2, __lowhigh2highlow(lo2));
-    hi2 = __hmax2_nan(hi2, __lowhigh2highlow(hi2));
-    const __half lo = __low2half(lo2), hi = __low2half(hi2);
-    const __half sc = quant_scale(lo, hi, levels);
-    const QuantGroup qg = quant_group(lo, sc, levels);
-    uint64_t part = 0;
+    for (int k = 0; k < 2; ++k) {
+      // min / max of the group on half2 pairs (NaN propagates, as in torch.min / torch.max)
+      const __half2* v2 = reinterpret_cast<const __half2*>(v[k]);
+      __half2 lo2 = __hmin2_nan(__hmin2_nan(v2[0], v2[1]), __hmin2_nan(v2[2], v2[3]));
+      __half2 hi2 = __hmax2_nan(__hmax2_nan(v2[0], v2[1]), __hmax2_nan(v2[2], v2[3]));
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t c2 = quant_code_fast2(*reinterpret_cast<const __half2*>(&v[2 * i]), qg);
-      part |= static_cast<uint64_t>((c2 & 0xFFFFu) | ((c2 >> 16) << BITS)) << (2 * i * BITS);
-    }
-    const int lane = threadIdx.x & 31;
-    const int64_t out_bit = (row * T + t0) * BITS;  // bit offset of this unit in the packed row-major stream
-    if constexpr (BITS == 8) {
-      if (live) {
-        uint2 w;
-        w.x = static_cast<uint32_t>(part);
-        w.y = static_cast<uint32_t>(part >> 32);
-        *reinterpret_cast<uint2*>(code + out_bit / 32) = w;
+      for (int off = 1; off < LPG; off <<= 1) {
+        lo2 = __hmin2_nan(lo2, __shfl_xor_sync(0xffffffffu, lo2, off));
+        hi2 = __hmax2_nan(hi2, __shfl_xor_sync(0xffffffffu, hi2, off));
       }
-    } else if constexpr (BITS == 4) {
-      if (live) code[out_bit / 32] = static_cast<uint32_t>(part);
-    } else {
-      // 2 bits: 16 bits per thread, two lanes per word; 1 bit: 8 bits per thread, four lanes per word
-      constexpr int LPW = 32 / (8 * BITS);  // lanes per word
-      uint32_t w = static_cast<uint32_t>(part);
+      lo2 = __hmin2_nan(lo2, __lowhigh2highlow(lo2));
+      hi2 = __hmax2_nan(hi2, __lowhigh2highlow(hi2));
+      const __half lo = __low2half(lo2), hi = __low2half(hi2);
+      const __half sc = quant_scale(lo, hi, levels);
+      const QuantGroup qg = quant_group(lo, sc, levels);
+      uint64_t part = 0;
 #pragma unroll
-      for (int off = 1; off < LPW; off <<= 1) {
-        const uint32_t other = __shfl_down_sync(0xffffffffu, w, off);
-        w |= other << (8 * BITS * off);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t c2 = quant_code_fast2(v2[i], qg);
+        part |= static_cast<uint64_t>((c2 & 0xFFFFu) | ((c2 >> 16) << BITS)) << (2 * i * BITS);
       }
-      if (live && (lane % LPW) == 0) code[out_bit / 32] = w;
-    }
-    if (live && (lane % LPG) == 0) {
-      const int64_t gi = (row * T + t0) / GROUP;
-      scale[gi] = sc;
-      mn_out[gi] = lo;
+      const int64_t out_bit = (row[k] * T + t0[k]) * BITS;  // bit offset of this unit in the packed row-major stream
+      if constexpr (BITS == 8) {
+        if (live[k]) {
+          uint2 w;
+          w.x = static_cast<uint32_t>(part);
+          w.y = static_cast<uint32_t>(part >> 32);
+          *reinterpret_cast<uint2*>(code + out_bit / 32) = w;
+        }
+      } else if constexpr (BITS == 4) {
+        if (live[k]) code[out_bit / 32] = static_cast<uint32_t>(part);
+      } else {
+        // 2 bits: 16 bits per thread, two lanes per word; 1 bit: 8 bits per thread, four lanes per word
+        constexpr int LPW = 32 / (8 * BITS);  // lanes per word
+        uint32_t w = static_cast<uint32_t>(part);
+#pragma unroll
+        for (int off = 1; off < LPW; off <<= 1) {
+          const uint32_t other = __shfl_down_sync(0xffffffffu, w, off);
+          w |= other << (8 * BITS * off);
+        }
+        if (live[k] && (lane % LPW) == 0) code[out_bit / 32] = w;
+      }
+      if (live[k] && (lane % LPG) == 0) {
+        const int64_t gi = (row[k] * T + t0[k]) / GROUP;
+        scale[gi] = sc;
+        mn_out[gi] = lo;
+      }
     }
   }
 }
@@ -334,7 +343,7 @@ static int launch_quant_rows(const __half* x, int64_t rows, int64_t T, int64_t i
                              int group, bool vec_ok, uint32_t* code, __half* scale, __half* mn, cudaStream_t st) {
   const int64_t units = rows * (T / 8);
   const int threads = 256;
-  int64_t blocks = ceil_div(units, threads);
+  int64_t blocks = ceil_div(units, 2 * threads);  // two units per thread and step
   if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond 64 CTAs per SM (measured: faster than one unit per thread)
   if (blocks < 1) blocks = 1;
   switch (group) {
