@@ -343,8 +343,11 @@ static int launch_quant_rows(const __half* x, int64_t rows, int64_t T, int64_t i
                              int group, bool vec_ok, uint32_t* code, __half* scale, __half* mn, cudaStream_t st) {
   const int64_t units = rows * (T / 8);
   const int threads = 256;
-  int64_t blocks = ceil_div(units, 2 * threads);  // two units per thread and step
-  if (blocks > 148 * 64) blocks = 148 * 64;  // grid-stride beyond 64 CTAs per SM (measured: faster than one unit per thread)
+  // two units per thread and step; beyond 64 CTAs per SM the grid strides, sized so that every step is full
+  // (a last step that only some CTAs take costs a whole step's time)
+  const int64_t per_step = 2 * threads;
+  const int64_t steps = ceil_div(units, per_step * 148 * 64);
+  int64_t blocks = ceil_div(units, per_step * (steps < 1 ? 1 : steps));
   if (blocks < 1) blocks = 1;
   switch (group) {
     case 32:
