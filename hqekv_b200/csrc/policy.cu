@@ -4,6 +4,8 @@
 // floating-point reduction here runs in a fixed order with one fp32 accumulator.
 #include <string.h>
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 
 namespace hqkv {
@@ -209,9 +211,10 @@ __global__ void __launch_bounds__(RANK_THREADS) block_rank_kernel(__half* __rest
 }
 
 // ------------------------------------------------------------------------------------------------
-// flush plan: single CTA
+// flush plan: one thread-block cluster
 // ------------------------------------------------------------------------------------------------
 constexpr int PLAN_THREADS = 1024;
+constexpr int PLAN_CLUSTER = 8;   // CTAs of the cluster (the portable maximum)
 
 struct PlanArgs {
   const int64_t* tier_idx[HQKV_NUM_TIERS];
@@ -227,6 +230,8 @@ struct PlanArgs {
   int8_t* tgt;         // by token id
   int8_t* fin;         // by enumeration slot
   int32_t* rank;       // by token id: rank among survivors
+  int32_t* gcnt;       // [PLAN_CATS][PLAN_CLUSTER * PLAN_WARPS] per-warp category counts of the whole cluster
+  int32_t* flags;      // [0] = something is evicted
 };
 
 // Enumeration order of every cached token: residual (ascending id), then the 16-, 8-, 4-, 2-, 1-bit
@@ -253,42 +258,49 @@ __device__ __forceinline__ void enum_slot(const PlanArgs& A, int64_t slot, int& 
   id = 0;
 }
 
-// One CTA of 32 warps.  Every pass walks the enumeration (or the token ids) in warp-contiguous ranges,
-// PLAN_BATCH iterations at a time so that the dependent loads of a batch (index list -> target ->
-// rank) are in flight together; ordered positions come from per-warp counts, one scan over the 32
-// warps, and ballot / match prefixes inside a warp.  Categories: 2*t = kept member of tier t,
-// 2*t + 1 = arrival in tier t (destination order: kept members first, then arrivals, both in
-// enumeration order); 10 = surviving token id.
+// One cluster of PLAN_CLUSTER CTAs of 32 warps.  Every pass walks the enumeration (or the token ids) in
+// warp-contiguous ranges - warp w of CTA r is range r * 32 + w - PLAN_BATCH iterations at a time so that the
+// dependent loads of a batch (index list -> target -> rank) are in flight together; ordered positions come from
+// per-warp counts (left in global memory for the other CTAs), one scan over all warps of the cluster, and ballot /
+// match prefixes inside a warp.  The passes are separated by cluster barriers, which also order the global-memory
+// scratch between the CTAs.  Categories: 2*t = kept member of tier t, 2*t + 1 = arrival in tier t (destination
+// order: kept members first, then arrivals, both in enumeration order); 10 = surviving token id.
 constexpr int PLAN_WARPS = PLAN_THREADS / 32;
+constexpr int PLAN_GWARPS = PLAN_WARPS * PLAN_CLUSTER;
 constexpr int PLAN_BATCH = 8;
 constexpr int PLAN_CATS = 2 * HQKV_NUM_TIERS + 1;
 
 __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_constant__ PlanArgs A) {
-  __shared__ int cnt[PLAN_CATS][PLAN_WARPS];  // per-warp totals, then exclusive offsets over the warps
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  __shared__ int cnt[PLAN_CATS][PLAN_WARPS];  // this CTA's per-warp totals, then their exclusive offsets over the cluster
   __shared__ int tot[PLAN_CATS];
-  __shared__ int any_evict;
   const int64_t total = A.hist + A.compress;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int crank = static_cast<int>(cluster.block_rank());
+  const int gwarp = crank * PLAN_WARPS + warp;
+  const int64_t gtid = static_cast<int64_t>(crank) * PLAN_THREADS + tid;
+  constexpr int64_t GTHREADS = static_cast<int64_t>(PLAN_THREADS) * PLAN_CLUSTER;
   const unsigned lt = (1u << lane) - 1u;
-  // warp w owns elements [w * span, (w + 1) * span), span a multiple of 32
-  const int64_t iters = (total + PLAN_THREADS - 1) / PLAN_THREADS;
-  const int64_t span = iters * 32, first = warp * span;
-  if (tid == 0) any_evict = 0;
+  // warp gw owns elements [gw * span, (gw + 1) * span), span a multiple of 32
+  const int64_t iters = (total + GTHREADS - 1) / GTHREADS;
+  const int64_t span = iters * 32, first = gwarp * span;
+  if (gtid == 0) A.flags[0] = 0;
   if (tid < PLAN_CATS * PLAN_WARPS) (&cnt[0][0])[tid] = 0;
   // 1. targets by token id
-  for (int64_t i = tid; i < total; i += PLAN_THREADS) A.tgt[i] = -1;
-  __syncthreads();
-  for (int64_t j = tid; j < total; j += PLAN_THREADS) {
+  for (int64_t i = gtid; i < total; i += GTHREADS) A.tgt[i] = -1;
+  cluster.sync();
+  for (int64_t j = gtid; j < total; j += GTHREADS) {
     int t = -1;
 #pragma unroll
     for (int k = 5; k >= 0; --k)
       if (j < A.cum[k] && j >= (k ? A.cum[k - 1] : 0)) t = k;
     if (t >= 0) {
       if (HQKV_INDEX_OK(A.sorted_ids[j], total)) A.tgt[A.sorted_ids[j]] = static_cast<int8_t>(t);
-      if (t == 5) any_evict = 1;
+      if (t == 5) A.flags[0] = 1;
     }
   }
-  __syncthreads();
+  cluster.sync();
   // 2. final tier of every enumeration slot (0..4 tier, 5 evicted, 6 dropped: residual without target),
   //    survival by token id, and the per-warp category counts
   for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
@@ -318,7 +330,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
       if (f < HQKV_NUM_TIERS) atomicAdd(&cnt[2 * f + (src[u] == f ? 0 : 1)][warp], 1);
     }
   }
-  __syncthreads();
+  cluster.sync();
   // 3. survivor counts per warp range of token ids
   {
     int mine = 0;
@@ -337,17 +349,24 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
     if (lane == 0) cnt[PLAN_CATS - 1][warp] = mine;
   }
   __syncthreads();
-  // exclusive offsets of every category over the warps
+  // this CTA's per-warp totals -> global memory, for the scan over all warps of the cluster
+  if (tid < PLAN_CATS * PLAN_WARPS) {
+    const int c = tid / PLAN_WARPS, w = tid - c * PLAN_WARPS;
+    A.gcnt[c * PLAN_GWARPS + crank * PLAN_WARPS + w] = cnt[c][w];
+  }
+  cluster.sync();
+  // exclusive offsets of every category over the warps of the cluster (every CTA scans for its own warps)
   if (tid < PLAN_CATS) {
     int acc = 0;
-    for (int w = 0; w < PLAN_WARPS; ++w) {
-      const int c = cnt[tid][w];
-      cnt[tid][w] = acc;
+    for (int w = 0; w < PLAN_GWARPS; ++w) {
+      const int c = A.gcnt[tid * PLAN_GWARPS + w];
+      if (w >= crank * PLAN_WARPS && w < (crank + 1) * PLAN_WARPS) cnt[tid][w - crank * PLAN_WARPS] = acc;
       acc += c;
     }
     tot[tid] = acc;
   }
   __syncthreads();
+  const int any_evict = A.flags[0];
   // 4. survivor ranks by token id: rank[i] = survivors with a smaller id; survivors[rank] = id
   {
     int running = cnt[PLAN_CATS - 1][warp];
@@ -369,7 +388,7 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
       }
     }
   }
-  __syncthreads();
+  cluster.sync();
   // 5. destination lists
   {
     for (int64_t j0 = 0; j0 < iters; j0 += PLAN_BATCH) {
@@ -407,13 +426,16 @@ __global__ void __launch_bounds__(PLAN_THREADS) flush_plan_kernel(const __grid_c
       }
     }
   }
-  __syncthreads();
-  if (tid < HQKV_NUM_TIERS) A.counts[tid] = tot[2 * tid] + tot[2 * tid + 1];
-  if (tid == 0) {
-    A.counts[5] = tot[PLAN_CATS - 1];
-    A.counts[6] = any_evict;
-    A.counts[7] = 0;
+  if (crank == 0) {
+    if (tid < HQKV_NUM_TIERS) A.counts[tid] = tot[2 * tid] + tot[2 * tid + 1];
+    if (tid == 0) {
+      A.counts[5] = tot[PLAN_CATS - 1];
+      A.counts[6] = any_evict;
+      A.counts[7] = 0;
+    }
   }
+  cluster.sync();  // no CTA of the cluster exits while another may still read its shared memory - none does, but the
+                   // barrier is cheap and keeps the exit orderly
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -741,9 +763,9 @@ extern "C" int hqkv_block_rank(void* importance, const void* range_or_null, int 
 extern "C" size_t hqkv_flush_plan_workspace_bytes(int64_t total) {
   if (total < 0) return 0;
   const size_t t = static_cast<size_t>(total);
-  // tgt (1 B) + fin (1 B) + rank (4 B) per token, each region rounded to 256 bytes
+  // tgt (1 B) + fin (1 B) + rank (4 B) per token, each region rounded to 256 bytes; per-warp counts; flags
   auto up = [](size_t v) { return (v + 255) & ~static_cast<size_t>(255); };
-  return up(t) + up(t) + up(4 * t) + 256;
+  return up(t) + up(t) + up(4 * t) + up(sizeof(int32_t) * PLAN_CATS * PLAN_GWARPS) + 256;
 }
 
 extern "C" int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_t* tier_n_host, int64_t hist,
@@ -782,6 +804,8 @@ extern "C" int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_
   A.tgt = reinterpret_cast<int8_t*>(ws);
   A.fin = reinterpret_cast<int8_t*>(ws + up(total));
   A.rank = reinterpret_cast<int32_t*>(ws + 2 * up(total));
+  A.gcnt = reinterpret_cast<int32_t*>(ws + 2 * up(total) + up(4 * static_cast<size_t>(total)));
+  A.flags = A.gcnt + ((up(sizeof(int32_t) * PLAN_CATS * PLAN_GWARPS)) / sizeof(int32_t));
   A.hist = hist;
   A.compress = compress;
   A.sorted_ids = sorted_ids;
@@ -789,8 +813,18 @@ extern "C" int hqkv_flush_plan(const int64_t* const* tier_idx_host, const int32_
   A.plan_ids = plan_ids;
   A.survivors = survivors;
   A.counts = counts;
-  flush_plan_kernel<<<1, PLAN_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(A);
-  HQKV_LAUNCH_CHECK("flush_plan");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(PLAN_CLUSTER);
+  cfg.blockDim = dim3(PLAN_THREADS);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PLAN_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HQKV_CUDA(cudaLaunchKernelEx(&cfg, flush_plan_kernel, A));
   return HQKV_OK;
 }
 
