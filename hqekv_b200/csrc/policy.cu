@@ -153,30 +153,43 @@ __global__ void __launch_bounds__(128) token_range128_kernel(const __half* __res
 }
 
 // ------------------------------------------------------------------------------------------------
-// block ranking: one CTA, bitonic sort of (inverted key, block id) in shared memory
+// block ranking: one thread-block cluster; bitonic sort of (inverted key, block id) in the shared memory of its
+// first CTA
 // ------------------------------------------------------------------------------------------------
+// The elementwise pass, the block keys and the final expansion to token ids are spread over the CTAs of the
+// cluster (one launch of one CTA spent most of its time walking 32 k tokens with 1024 threads); the keys meet in
+// the first CTA's shared memory (distributed shared memory stores), which sorts them alone, and all CTAs read the
+// sorted keys back from there.  Cluster barriers separate the passes and order the in-place update of
+// `importance` between the CTAs.
 constexpr int RANK_THREADS = 1024;
+constexpr int RANK_CLUSTER = 8;
 constexpr int RANK_MAX_BLOCKS = 8192;
 
 __global__ void __launch_bounds__(RANK_THREADS) block_rank_kernel(__half* __restrict__ importance,
                                                                   const __half* __restrict__ range, int block,
                                                                   int nblocks, int npow2,
                                                                   int64_t* __restrict__ sorted_ids) {
-  extern __shared__ uint32_t keys[];  // npow2 entries
+  namespace cg = cooperative_groups;
+  cg::cluster_group cluster = cg::this_cluster();
+  extern __shared__ uint32_t keys[];  // npow2 entries; only the first CTA's copy is used
+  uint32_t* keys0 = cluster.map_shared_rank(keys, 0);
+  const int crank = static_cast<int>(cluster.block_rank());
+  const int64_t gtid = static_cast<int64_t>(crank) * RANK_THREADS + threadIdx.x;
+  constexpr int64_t GTHREADS = static_cast<int64_t>(RANK_THREADS) * RANK_CLUSTER;
   const int64_t total = static_cast<int64_t>(nblocks) * block;
   const float fblock = static_cast<float>(block);
   // elementwise: optional product with the range, then the in-place divide
-  for (int64_t i = threadIdx.x; i < total; i += RANK_THREADS) {
+  for (int64_t i = gtid; i < total; i += GTHREADS) {
     __half x = importance[i];
     if (range) x = h_mul(x, range[i]);
     importance[i] = h_divf(x, fblock);
   }
-  __syncthreads();
-  for (int k = threadIdx.x; k < npow2; k += RANK_THREADS) {
+  cluster.sync();
+  for (int64_t k = gtid; k < npow2; k += GTHREADS) {
     uint32_t composite = 0xFFFFFFFFu;
     if (k < nblocks) {
       float acc = 0.f;
-      const __half* p = importance + static_cast<int64_t>(k) * block;
+      const __half* p = importance + k * block;
       for (int i = 0; i < block; ++i) acc = __fadd_rn(acc, __half2float(p[i]));
       const __half key = __float2half_rn(acc);
       uint16_t bits = __half_as_ushort(key);
@@ -185,29 +198,33 @@ __global__ void __launch_bounds__(RANK_THREADS) block_rank_kernel(__half* __rest
       const uint16_t desc = static_cast<uint16_t>(0xFFFFu - asc);           // larger key first
       composite = (static_cast<uint32_t>(desc) << 16) | static_cast<uint32_t>(k);  // ties: lower id first
     }
-    keys[k] = composite;
+    keys0[k] = composite;
   }
-  __syncthreads();
-  for (int size = 2; size <= npow2; size <<= 1) {
-    for (int stride = size >> 1; stride > 0; stride >>= 1) {
-      for (int i = threadIdx.x; i < (npow2 >> 1); i += RANK_THREADS) {
-        const int lo = 2 * i - (i & (stride - 1));  // index with the `stride` bit clear
-        const int hi = lo + stride;
-        const bool up = (lo & size) == 0;
-        const uint32_t a = keys[lo], b = keys[hi];
-        if ((a > b) == up) {
-          keys[lo] = b;
-          keys[hi] = a;
+  cluster.sync();
+  if (crank == 0) {
+    for (int size = 2; size <= npow2; size <<= 1) {
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        for (int i = threadIdx.x; i < (npow2 >> 1); i += RANK_THREADS) {
+          const int lo = 2 * i - (i & (stride - 1));  // index with the `stride` bit clear
+          const int hi = lo + stride;
+          const bool up = (lo & size) == 0;
+          const uint32_t a = keys[lo], b = keys[hi];
+          if ((a > b) == up) {
+            keys[lo] = b;
+            keys[hi] = a;
+          }
         }
+        __syncthreads();
       }
-      __syncthreads();
     }
   }
-  for (int64_t i = threadIdx.x; i < total; i += RANK_THREADS) {
+  cluster.sync();
+  for (int64_t i = gtid; i < total; i += GTHREADS) {
     const int j = static_cast<int>(i / block);
-    const int64_t blk = keys[j] & 0xFFFFu;
+    const int64_t blk = keys0[j] & 0xFFFFu;
     sorted_ids[i] = blk * block + (i - static_cast<int64_t>(j) * block);
   }
+  cluster.sync();  // the first CTA's shared memory stays until every CTA has read the sorted keys
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -754,9 +771,20 @@ extern "C" int hqkv_block_rank(void* importance, const void* range_or_null, int 
   HQKV_REQUIRE(importance && sorted_ids, "block_rank: null pointer");
   int npow2 = 2;
   while (npow2 < nblocks) npow2 <<= 1;
-  block_rank_kernel<<<1, RANK_THREADS, npow2 * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half*>(importance), static_cast<const __half*>(range_or_null), block, nblocks, npow2, sorted_ids);
-  HQKV_LAUNCH_CHECK("block_rank");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(RANK_CLUSTER);
+  cfg.blockDim = dim3(RANK_THREADS);
+  cfg.dynamicSmemBytes = npow2 * sizeof(uint32_t);
+  cfg.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = RANK_CLUSTER;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  HQKV_CUDA(cudaLaunchKernelEx(&cfg, block_rank_kernel, static_cast<__half*>(importance),
+                               static_cast<const __half*>(range_or_null), block, nblocks, npow2, sorted_ids));
   return HQKV_OK;
 }
 
