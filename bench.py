@@ -1,18 +1,29 @@
 #!/usr/bin/env python
 """Decode-attention throughput of the hybrid mixed-precision KV cache on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload cfg1]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference|reference-cuda] [--workload cfg1]
 
 One "step" = the attention of one decode step of the whole model: for every layer, the fused decode
-(q.K^T, softmax, p.V over the 8/4/2-bit tiers and the fp16 residual window) over that layer's own
-cache.  Default workload (N=1): Llama-3.1-8B shape, 32 layers, batch 1, context 32768, 10 % evicted,
+(q.K^T, softmax, p.V over the 8/4/2-bit tiers and the fp16 residual window: two kernel launches) over that
+layer's own cache.  Default workload (N=1): Llama-3.1-8B shape, 32 layers, batch 1, context 32768, 10 % evicted,
 20/40/40 % of the rest in 8/4/2-bit, group 32, residual 128, synthetic N(0,1) data.  The 32 caches
 total ~1.2 GB, ten times the 126 MB L2, so every step streams its cache from HBM.
 
 N > 1 (launched by torch.distributed.run): kv heads are sharded over the ranks (strong scaling); each
-layer's per-head outputs are all-gathered over NCCL.
+layer's per-head outputs are exchanged by flagged peer stores from the decode kernel (--peer-gather; an NCCL
+all-gather per layer with 'off').
 
-Prints ONE JSON line on rank 0.
+Prints ONE JSON line on rank 0.  Keys beside the contract's: `value` is the median over `timed_windows` windows
+of exactly --steps steps each (a window is repeated until about a second has been timed); `e2e` the same
+metric through the public Python operator with q coming from and the outputs going to pinned host memory every
+step; `roofline` per kernel (algorithmic bytes / CUDA-event time against the measured copy bandwidth, DRAM
+traffic from an ncu capture); `cpu_baseline` the reference's CPU path on the host cores (one layer, scaled);
+`parity` the errors of the timed workload's first layer against the fp32 oracle; `build_id` the stamp of the
+library that ran; `importance_row_exchange_us` (N > 1) the other exchange of the sharded path, timed alone.
+
+--impl reference: the reference's own CPU implementation of the path on the host cores, no GPU and no CUDA library
+(rank 0 alone under torchrun).  --impl reference-cuda: the reference's own CUDA extension, where it has been built
+into baseline/_ref, on the same cache tuples.
 """
 import argparse
 import json
